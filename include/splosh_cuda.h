@@ -1,0 +1,194 @@
+/* splosh_cuda.h — C ABI of SploshCUDA, the B200 (sm_100a) implementation of Splosh's packed
+ * ragged step.
+ *
+ * The reference has no C ABI: its Swift `Engine` class calls Metal directly. Each entry point
+ * below names the Swift interface it stands in for (paths are relative to the reference's
+ * repository root), so that a Swift `Engine` facade can forward to it one call for one call.
+ *
+ * Threading: like the reference's engine ("The engine is not thread-safe; the scheduler owns it
+ * and serialises steps", Sources/SploshRuntime/Engine.swift:12) one thread owns an engine.
+ * One engine drives one GPU; N GPUs are N engines.
+ *
+ * All pointers in signatures are HOST pointers unless a name says `device`. Nothing here takes
+ * or returns a framework type. There is no CPU fallback: every compute entry point fails with
+ * SPL_ERR_UNSUPPORTED_DEVICE when no sm_100 device is present.
+ */
+#ifndef SPLOSH_CUDA_H
+#define SPLOSH_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* EngineError (Engine.swift:88-108) plus the two device conditions Metal reported through
+ * CommandGraphError.executionFailed (Sources/SploshCore/CommandGraph.swift:150-152). */
+typedef enum spl_status {
+    SPL_OK = 0,
+    SPL_ERR_KV_POOL_EXHAUSTED = 1,
+    SPL_ERR_CONTEXT_EXCEEDED = 2,
+    SPL_ERR_UNSUPPORTED_DEVICE = 3,
+    SPL_ERR_ALLOCATION_FAILED = 4,
+    SPL_ERR_INVALID_ROWS = 5,
+    SPL_ERR_SNAPSHOT_MISMATCH = 6,
+    SPL_ERR_INVALID_KERNEL_CHOICE = 7,
+    SPL_ERR_DEVICE = 8,
+    SPL_ERR_TIMEOUT = 9,
+    SPL_ERR_INVALID_ARGUMENT = 10
+} spl_status;
+
+/* ModelGeometry (Sources/SploshModel/ModelWeights.swift:66-88), a parameter here. Layer i is a
+ * gated-attention layer when i % 4 == 3, otherwise a gated-delta layer
+ * (Sources/SploshModel/LayerGraph.swift:22). */
+typedef struct spl_geometry {
+    int32_t layers, hidden, inter, vocab;
+    int32_t heads, kv_heads, head_dim, rotary_dim;
+    int32_t gdn_key_heads, gdn_value_heads, gdn_head_dim;
+    float eps, rope_theta;
+} spl_geometry;
+
+/* EngineConfig (Engine.swift:19-48). Zero in state_units / max_logit_rows / span_target takes the
+ * default (max_slots * 17, max_rows, 592). */
+typedef struct spl_config {
+    int32_t device;
+    int32_t max_slots, max_rows, kv_pages, max_context;
+    int32_t state_units, max_logit_rows;
+    int32_t span_target;        /* thread blocks the attention scan aims for; sets the span count */
+} spl_config;
+
+/* EngineRow (Engine.swift:50-62). */
+typedef struct spl_row {
+    int32_t slot, token, position;
+    uint8_t want_logits, verify;
+    uint8_t reserved[2];
+} spl_row;
+
+/* The per-step index tables Engine.step builds on the host (Engine.swift:1322-1398). Arrays are
+ * owned by whoever built them and must stay valid for the call they are passed to. */
+typedef struct spl_tables {
+    uint32_t rows, run_count, logit_rows, attn_block_count, step_pages, live_rows, spans, pages_per_span;
+    const uint32_t *tokens, *row_slot, *row_pos;      /* [rows] */
+    const uint32_t *runs;                             /* [run_count][3]: slot, first row, length */
+    const uint32_t *run_info;                         /* [run_count][2]: speculative, journal pending */
+    const uint32_t *row_read, *row_write;             /* [rows]: conv-history unit read / written */
+    const uint32_t *gather_index;                     /* [logit_rows] */
+    const uint32_t *attn_blocks;                      /* [attn_block_count][2]: first row, count <= 8 */
+    const uint32_t *page_table;                       /* [max_slots][max_pages] */
+} spl_tables;
+
+/* EngineStepStats (Engine.swift:64-69). */
+typedef struct spl_step_stats {
+    int32_t rows, launches;
+    double gpu_seconds, wall_seconds;
+} spl_step_stats;
+
+/* EngineMemory (Engine.swift:71-86). */
+typedef struct spl_memory_info {
+    int64_t weight_bytes, kv_pool_bytes, kv_bytes_per_page, kv_pages_total, kv_pages_used;
+    int64_t state_bytes_per_slot, state_bytes_total, state_units_used, scratch_bytes;
+    int64_t device_total_bytes, device_free_bytes;
+} spl_memory_info;
+
+/* Tensor kinds of one block (BlockWeights / MixerWeights, ModelWeights.swift:30-63). Layer -1
+ * addresses the model-level tensors (embed, head, final norm). */
+enum { SPL_Q4_QKV = 0, SPL_Q4_Z, SPL_Q4_A, SPL_Q4_B, SPL_Q4_OUT, SPL_Q4_Q, SPL_Q4_K, SPL_Q4_V, SPL_Q4_O,
+       SPL_Q4_GATE, SPL_Q4_UP, SPL_Q4_DOWN, SPL_Q4_EMBED, SPL_Q4_HEAD, SPL_Q4_KINDS };
+enum { SPL_VEC_INPUT_NORM = 0, SPL_VEC_POST_NORM, SPL_VEC_CONV, SPL_VEC_A_LOG, SPL_VEC_DT_BIAS, SPL_VEC_GDN_NORM,
+       SPL_VEC_Q_NORM, SPL_VEC_K_NORM, SPL_VEC_FINAL_NORM, SPL_VEC_KINDS };
+
+/* ---- Host-side bookkeeping: no GPU needed -------------------------------------------------
+ * The page allocator, state-unit pool and table builder that live inside the reference's Engine
+ * (Engine.swift:625-632, 810-868, 1316-1398). A Swift host that keeps its own may skip these and
+ * hand its tables to spl_step_tables. */
+typedef struct spl_host spl_host;
+spl_status spl_host_create(const spl_geometry *geometry, const spl_config *config, spl_host **out);
+void spl_host_destroy(spl_host *host);
+/* Engine.step's validation and table build (Engine.swift:1316-1398). `out` points into the host
+ * object and is valid until the next build on it. */
+spl_status spl_host_build_tables(spl_host *host, const spl_row *rows, int32_t count, spl_tables *out);
+/* The end of Engine.step (Engine.swift:1537): the step's slots have replayed their journals. */
+void spl_host_finish_step(spl_host *host, const spl_tables *tables);
+/* Engine.resetSlot's host half (Engine.swift:816-826); returns the state unit to be zeroed. */
+int32_t spl_host_reset_slot(spl_host *host, int32_t slot);
+void spl_host_discard_verify(spl_host *host, int32_t slot);                                   /* Engine.swift:829-832 */
+spl_status spl_host_accept_verify(spl_host *host, int32_t slot, int32_t rows, int32_t token_count); /* Engine.swift:836-846 */
+void spl_host_truncate(spl_host *host, int32_t slot, int32_t token_count);                    /* Engine.swift:865-868 */
+int32_t spl_host_pages_held(const spl_host *host, int32_t slot);                              /* Engine.swift:807 */
+int32_t spl_host_free_page_count(const spl_host *host);                                       /* Engine.swift:808 */
+int32_t spl_host_slot_unit(const spl_host *host, int32_t slot);
+int32_t spl_host_journal_pending(const spl_host *host, int32_t slot);
+int32_t spl_host_max_pages(const spl_host *host);
+const char *spl_host_last_error(const spl_host *host);
+/* BatchScheduler.accept, greedy branch (Sources/SploshRuntime/BatchScheduler.swift:1583-1587):
+ * the agreeing prefix of `drafts` against the block's arg-max ids, and the bonus token. */
+int32_t spl_greedy_accept(const int32_t *argmax_ids, const int32_t *drafts, int32_t draft_count, int32_t *bonus);
+
+/* ---- Engine ------------------------------------------------------------------------------- */
+typedef struct spl_engine spl_engine;
+/* Engine.init(device:weights:config:) (Engine.swift:355). Weights are set afterwards. */
+spl_status spl_engine_create(const spl_geometry *geometry, const spl_config *config, spl_engine **out);
+void spl_engine_destroy(spl_engine *engine);
+const char *spl_last_error_string(const spl_engine *engine);
+/* Q4Handle (Sources/SploshCore/Allocator.swift:34-88): MLX affine-4, group 64, row-major packed
+ * u32 [rows][inner/8] with bf16 scales and biases [rows][inner/64]. The caller keeps ownership of
+ * the host arrays; the engine copies them into its own device layout before returning. */
+spl_status spl_weights_set_q4(spl_engine *engine, int32_t layer, int32_t kind, int32_t rows, int32_t inner,
+                              const uint32_t *packed, const uint16_t *scales, const uint16_t *biases);
+/* TensorHandle for the bf16 vectors (norm weights, conv1d, A_log, dt_bias). */
+spl_status spl_weights_set_vector(spl_engine *engine, int32_t layer, int32_t kind, const uint16_t *bf16, int32_t count);
+/* Benchmarking: fill every q4 tensor on the device from the seeded streams the synthetic-model
+ * recipe defines (value n of tensor `name` = centred sum of the four 16-bit fields of
+ * SplitMix64(seed ^ fnv1a64(name), n), scaled to deviation 0.02, then quantised group by group). */
+spl_status spl_weights_synthesize_q4(spl_engine *engine, uint64_t seed);
+/* Engine.step(_:) (Engine.swift:1316): validate, build tables with the engine's own host state,
+ * run the pass, wait. */
+spl_status spl_step(spl_engine *engine, const spl_row *rows, int32_t count, spl_step_stats *stats);
+/* The same pass from tables the caller built (the north star's split: packer and allocator stay
+ * with the host language). */
+spl_status spl_step_tables(spl_engine *engine, const spl_tables *tables, spl_step_stats *stats);
+/* Engine.logits(_:) (Engine.swift:1202-1205): row i of the last step's logits, vocab floats. */
+spl_status spl_logits_row(spl_engine *engine, int32_t index, float *dst);
+/* Sampler.argmax over [0, vocab_limit) for every logit row of the last step, on the device
+ * (Sources/SploshRuntime/Sampler.swift:11-16, 94-96): the first index of the maximum. */
+spl_status spl_argmax(spl_engine *engine, int32_t vocab_limit, int32_t *ids);
+spl_status spl_slot_reset(spl_engine *engine, int32_t slot);                                  /* Engine.resetSlot */
+spl_status spl_verify_discard(spl_engine *engine, int32_t slot);                              /* Engine.discardVerify */
+spl_status spl_verify_accept(spl_engine *engine, int32_t slot, int32_t rows, int32_t token_count); /* Engine.acceptVerify */
+spl_status spl_slot_truncate(spl_engine *engine, int32_t slot, int32_t token_count);          /* Engine.truncate */
+int32_t spl_pages_held(const spl_engine *engine, int32_t slot);                               /* Engine.pagesHeld(by:) */
+int32_t spl_free_page_count(const spl_engine *engine);                                        /* Engine.freePageCount */
+spl_status spl_memory(const spl_engine *engine, spl_memory_info *out);                        /* Engine.memory */
+spl_host *spl_engine_host(spl_engine *engine);
+/* Engine.warmUp (Engine.swift:1191-1197): no-op placeholder for graph capture. */
+spl_status spl_warmup(spl_engine *engine);
+/* Engine.debugFillKV (Engine.swift:1218-1236): pseudo-random codes and scale 0.01 in every page
+ * the slot holds; and a U(-0.5, 0.5) recurrent state as the reference's tests draw it
+ * (Tests/SploshOracleTests/GdnCandidateTests.swift:146). */
+spl_status spl_debug_fill_kv(spl_engine *engine, int32_t slot);
+spl_status spl_debug_fill_state(spl_engine *engine, int32_t slot, uint64_t seed);
+/* Raw device buffers for tests. which: 0 state, 1 conv history, 2 journal (index = gated-delta
+ * layer ordinal); 3 k codes, 4 v codes, 5 k scale, 6 v scale (index = attention layer ordinal);
+ * 7 residual stream after the last step [rows][hidden]; 8 residual stream after block `index`
+ * (needs spl_debug_taps(engine, 1) before the step). Layouts: state [slot][value head][value j][key i];
+ * conv [unit][channel][3] oldest first; journal [slot][16][value head][260];
+ * codes [page][kv head][256][head_dim] (V codes are stored [page][kv head][head_dim][256]). */
+spl_status spl_debug_read(spl_engine *engine, int32_t which, int32_t index, void *dst, size_t bytes);
+spl_status spl_debug_taps(spl_engine *engine, int32_t enabled);
+/* Per-kernel-class device time of the last step when enabled (events around every launch; slow). */
+spl_status spl_debug_profile(spl_engine *engine, int32_t enabled);
+/* class: 0 q4 gemm, 1 norms and elementwise, 2 gated-delta, 3 attention, 4 head/argmax/other.
+ * Returns accumulated milliseconds and launches since the last reset (reset = enabling). */
+spl_status spl_debug_profile_read(spl_engine *engine, int32_t klass, double *milliseconds, int64_t *launches, double *bytes);
+
+/* ---- Single operators on host buffers (tests, micro-benchmarks) --------------------------- */
+/* Engine.gemm (Engine.swift:1651-1806) for one MLX affine-4 tensor: out[r][n] = sum_k
+ * bf16(a[r][k]) * w[n][k] (+ residual[r][n]). Allocates, copies in, runs, copies out. */
+spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t *scales, const uint16_t *biases,
+                          int32_t n, int32_t k, const float *activations, int32_t rows, const float *residual, float *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

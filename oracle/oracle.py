@@ -1,0 +1,216 @@
+"""ctypes binding of the CPU oracle (oracle/splosh_oracle.cpp). TEST INFRASTRUCTURE ONLY.
+
+Only tests/, __graft_entry__.smoke() and bench.py's cpu_baseline / reference arm may import this.
+"""
+import ctypes as C
+import os
+import subprocess
+import numpy as np
+
+from .tables import Tables
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+class Geometry(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("layers", "hidden", "inter", "vocab", "heads", "kv_heads", "head_dim", "rotary_dim",
+                                         "gdn_key_heads", "gdn_value_heads", "gdn_head_dim")] + [("eps", C.c_float), ("rope_theta", C.c_float)]
+
+    @property
+    def channels(self):
+        return (2 * self.gdn_key_heads + self.gdn_value_heads) * self.gdn_head_dim
+
+    @property
+    def value_dim(self):
+        return self.gdn_value_heads * self.gdn_head_dim
+
+    def with_(self, **kw):
+        out = Geometry.from_buffer_copy(bytes(self))
+        for k, v in kw.items():
+            setattr(out, k, v)
+        return out
+
+
+def tiny_geometry():
+    """The 4-layer hybrid of the first benchmark configuration."""
+    return Geometry(4, 1024, 2816, 32000, 8, 2, 128, 32, 4, 8, 128, 1e-6, 1e7)
+
+
+def b27_geometry():
+    """The 27B shape (Sources/SploshModel/ModelWeights.swift:66-88)."""
+    return Geometry(64, 5120, 17408, 248320, 24, 4, 256, 64, 16, 48, 128, 1e-6, 1e7)
+
+
+class _CTables(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("rows", "run_count", "logit_rows", "attn_block_count", "step_pages", "live_rows",
+                                          "spans", "pages_per_span")] + \
+               [(n, C.POINTER(C.c_uint32)) for n in ("tokens", "row_slot", "row_pos", "runs", "run_info", "row_read", "row_write",
+                                                     "gather_index", "attn_blocks", "page_table")]
+
+
+def build():
+    subprocess.run(["make", "-C", _HERE], check=True, capture_output=True)
+
+
+def lib():
+    global _LIB
+    if _LIB is None:
+        path = os.path.join(_HERE, "liboracle.so")
+        if not os.path.exists(path):
+            build()
+        L = C.CDLL(path)
+        L.orc_splitmix_at.restype = C.c_uint64; L.orc_splitmix_at.argtypes = [C.c_uint64, C.c_uint64]
+        L.orc_uniform_at.restype = C.c_float; L.orc_uniform_at.argtypes = [C.c_uint64, C.c_uint64]
+        L.orc_normal_at.restype = C.c_float; L.orc_normal_at.argtypes = [C.c_uint64, C.c_uint64, C.c_float]
+        L.orc_fnv1a64.restype = C.c_uint64; L.orc_fnv1a64.argtypes = [C.c_char_p]
+        L.orc_bf16.restype = C.c_uint16; L.orc_bf16.argtypes = [C.c_float]
+        L.orc_f16_round.restype = C.c_float; L.orc_f16_round.argtypes = [C.c_float]
+        L.orc_argmax.restype = C.c_int32; L.orc_argmax.argtypes = [C.c_void_p, C.c_int]
+        L.orc_model_create.restype = C.c_void_p; L.orc_model_create.argtypes = [C.POINTER(Geometry), C.c_uint64]
+        L.orc_model_destroy.argtypes = [C.c_void_p]
+        L.orc_tensor_seed.restype = C.c_uint64; L.orc_tensor_seed.argtypes = [C.c_uint64, C.c_int, C.c_int, C.c_int]
+        L.orc_engine_create.restype = C.c_void_p; L.orc_engine_create.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]
+        L.orc_engine_destroy.argtypes = [C.c_void_p]
+        L.orc_engine_reset_slot.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        L.orc_engine_buffer.restype = C.c_void_p; L.orc_engine_buffer.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_size_t)]
+        L.orc_step.restype = C.c_int; L.orc_step.argtypes = [C.c_void_p, C.POINTER(_CTables), C.c_void_p, C.c_void_p, C.c_int]
+        L.orc_model_q4.restype = C.c_int
+        L.orc_model_q4.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)] + [C.POINTER(C.c_void_p)] * 3
+        L.orc_model_vec.restype = C.c_int
+        L.orc_model_vec.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_void_p), C.POINTER(C.c_int)]
+        L.orc_threads.restype = C.c_int
+        _LIB = L
+    return _LIB
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+Q4_KINDS = ["qkv", "z", "a", "b", "out", "q", "k", "v", "o", "gate", "up", "down", "embed", "head"]
+VEC_KINDS = ["input_norm", "post_norm", "conv", "a_log", "dt_bias", "gdn_norm", "q_norm", "k_norm", "final_norm"]
+
+
+def bf16_round(x):
+    """Round an fp32 array to bf16 (nearest even) and back."""
+    bits = np.ascontiguousarray(x, np.float32).view(np.uint32)
+    return (((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16) << 16).astype(np.uint32).view(np.float32)
+
+
+def bf16_bits_to_float(bits):
+    return (np.asarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def quantize_mlx4(w):
+    w = np.ascontiguousarray(w, np.float32)
+    rows, inner = w.shape
+    packed = np.zeros((rows, inner // 8), np.uint32); scales = np.zeros((rows, inner // 64), np.uint16); biases = np.zeros_like(scales)
+    lib().orc_quantize_mlx4(_ptr(w), rows, inner, _ptr(packed), _ptr(scales), _ptr(biases))
+    return packed, scales, biases
+
+
+def dequant_mlx4(packed, scales, biases, columns):
+    packed = np.ascontiguousarray(packed, np.uint32); rows = packed.shape[0]
+    scales = np.ascontiguousarray(scales, np.float32); biases = np.ascontiguousarray(biases, np.float32)
+    out = np.zeros((rows, columns), np.float32)
+    lib().orc_dequant_mlx4(_ptr(packed), _ptr(scales), _ptr(biases), rows, columns, _ptr(out))
+    return out
+
+
+def decode_gguf(kind, raw):
+    """raw: uint8 [blocks, block_bytes] -> float32 [blocks, 256]."""
+    raw = np.ascontiguousarray(raw, np.uint8)
+    out = np.zeros((raw.shape[0], 256), np.float32)
+    if kind == "Q6_K":
+        assert raw.shape[1] == 210
+        lib().orc_decode_q6k(_ptr(raw), raw.shape[0], _ptr(out))
+    else:
+        assert raw.shape[1] == {"Q4_K": 144, "Q5_K": 176}[kind]
+        lib().orc_decode_q45k(_ptr(raw), raw.shape[0], 1 if kind == "Q5_K" else 0, _ptr(out))
+    return out
+
+
+def gemm_q4(packed, scales, biases, activations, residual=None):
+    n, k = packed.shape[0], packed.shape[1] * 8
+    a = np.ascontiguousarray(activations, np.float32)
+    out = np.zeros((a.shape[0], n), np.float32)
+    res = None if residual is None else np.ascontiguousarray(residual, np.float32)
+    lib().orc_gemm_q4(_ptr(np.ascontiguousarray(packed)), _ptr(np.ascontiguousarray(scales)), _ptr(np.ascontiguousarray(biases)),
+                      n, k, _ptr(a), a.shape[0], None if res is None else _ptr(res), _ptr(out))
+    return out
+
+
+class Model:
+    """A seeded synthetic model: projection weights ~N(0, 0.02) quantised to MLX affine-4, norm
+    weights bf16(1 + N(0, 0.02)), conv / A_log / dt_bias in the ranges of the reference's tests."""
+
+    def __init__(self, geometry, seed=0x5EED6D17):
+        self.g, self.seed = geometry, seed
+        self.handle = lib().orc_model_create(C.byref(geometry), seed)
+
+    def __del__(self):
+        if getattr(self, "handle", None):
+            lib().orc_model_destroy(self.handle); self.handle = None
+
+    def full(self, layer):
+        return layer % 4 == 3
+
+    def q4(self, layer, kind):
+        """(packed u32 [rows, inner/8], scales u16 [rows, inner/64], biases) as views of the oracle's memory."""
+        rows, inner = C.c_int(), C.c_int()
+        p, s, b = C.c_void_p(), C.c_void_p(), C.c_void_p()
+        if lib().orc_model_q4(self.handle, layer, Q4_KINDS.index(kind), C.byref(rows), C.byref(inner), C.byref(p), C.byref(s), C.byref(b)):
+            return None
+        r, k = rows.value, inner.value
+        packed = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint32)), (r, k // 8))
+        scales = np.ctypeslib.as_array(C.cast(s, C.POINTER(C.c_uint16)), (r, k // 64))
+        biases = np.ctypeslib.as_array(C.cast(b, C.POINTER(C.c_uint16)), (r, k // 64))
+        return packed, scales, biases
+
+    def vec(self, layer, kind):
+        p, n = C.c_void_p(), C.c_int()
+        if lib().orc_model_vec(self.handle, layer, VEC_KINDS.index(kind), C.byref(p), C.byref(n)):
+            return None
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint16)), (n.value,))
+
+
+class Engine:
+    """The oracle's device-state stand-in: KV pools, recurrent state, conv history, journal."""
+
+    def __init__(self, model, max_slots, kv_pages, max_pages, state_units):
+        self.model = model
+        self.shape = (max_slots, kv_pages, max_pages, state_units)
+        self.handle = lib().orc_engine_create(model.handle, max_slots, kv_pages, max_pages, state_units)
+
+    def __del__(self):
+        if getattr(self, "handle", None):
+            lib().orc_engine_destroy(self.handle); self.handle = None
+
+    def reset_slot(self, slot, unit):
+        lib().orc_engine_reset_slot(self.handle, slot, unit)
+
+    def buffer(self, which, index):
+        names = ["state", "conv", "journal", "k_codes", "v_codes", "k_scale", "v_scale"]
+        n = C.c_size_t()
+        p = lib().orc_engine_buffer(self.handle, names.index(which), index, C.byref(n))
+        dtype = np.int8 if which in ("k_codes", "v_codes") else np.float32
+        count = n.value // np.dtype(dtype).itemsize
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_int8 if dtype == np.int8 else C.c_float)), (count,))
+
+    def step(self, t: Tables, taps=False, max_layers=-1):
+        g = self.model.g
+        keep = [np.ascontiguousarray(getattr(t, n), np.uint32) for n in
+                ("tokens", "row_slot", "row_pos", "runs", "run_info", "row_read", "row_write", "gather_index", "attn_blocks", "page_table")]
+        ct = _CTables(t.rows, t.run_count, t.logit_rows, t.attn_block_count, t.step_pages, t.live_rows, t.spans, t.pages_per_span,
+                      *[a.ctypes.data_as(C.POINTER(C.c_uint32)) for a in keep])
+        logits = np.zeros((t.logit_rows, g.vocab), np.float32)
+        hidden = np.zeros((g.layers, t.rows, g.hidden), np.float32) if taps else None
+        rc = lib().orc_step(self.handle, C.byref(ct), _ptr(logits), None if hidden is None else _ptr(hidden), max_layers)
+        assert rc == 0
+        return (logits, hidden) if taps else logits
+
+
+def argmax(logits, limit):
+    logits = np.ascontiguousarray(logits, np.float32)
+    return np.array([lib().orc_argmax(_ptr(logits[i]), limit) for i in range(logits.shape[0])], np.int32)

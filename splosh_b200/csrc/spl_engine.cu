@@ -1,0 +1,835 @@
+// spl_engine.cu — the engine behind the C ABI: device memory, weight upload, and one packed
+// ragged step as a sequence of kernel launches on one stream.
+//
+// Stands in for Engine.init and Engine.step (Sources/SploshRuntime/Engine.swift:355-686, 1316-1540)
+// and for encodeLinear / encodeFull (:2001-2077, :2167-2290). The reference separates dependent
+// dispatches of one command encoder with barriers ("stages"); here stream order does that.
+#include <chrono>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <string>
+#include <vector>
+
+#include "spl_attention.cuh"
+#include "spl_elementwise.cuh"
+#include "spl_gdn.cuh"
+#include "spl_gemm.cuh"
+#include "spl_host.h"
+
+namespace {
+
+struct LayerWeights {
+    bool full = false;
+    SplQ4Dev in_proj, out_proj, gate_up, down;     // in_proj: qkv|z|a|b (gated-delta) or q|k|v (attention)
+    uint16_t *vec[SPL_VEC_KINDS] = {};
+};
+
+enum { KLASS_GEMM = 0, KLASS_ELEMENTWISE, KLASS_GDN, KLASS_ATTENTION, KLASS_OTHER, KLASS_COUNT };
+
+struct ProfileSlot { cudaEvent_t begin, end; int klass; double bytes; };
+
+}  // namespace
+
+struct spl_engine {
+    spl_geometry g;
+    spl_config c;
+    spl_host *host = nullptr;
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    std::string error;
+
+    std::vector<LayerWeights> layers;
+    SplQ4Dev head;
+    uint32_t *embed_packed = nullptr; uint16_t *embed_scales = nullptr, *embed_biases = nullptr;
+    uint16_t *final_norm = nullptr;
+    float *inv_freq = nullptr;
+    size_t weight_bytes = 0;
+
+    // Per-session state.
+    std::vector<int8_t *> k_codes, v_codes;
+    std::vector<float *> k_scale, v_scale, state, conv, journal;
+    size_t kv_page_bytes = 0, kv_pool_bytes = 0, state_layer_bytes = 0, conv_unit_bytes = 0, journal_bytes = 0;
+
+    // Activations and scratch.
+    float *h = nullptr, *proj = nullptr, *gate_up = nullptr, *gdn_act = nullptr, *partials = nullptr, *attn_partials = nullptr, *logits = nullptr;
+    float *taps = nullptr;
+    __nv_bfloat16 *xn = nullptr, *core = nullptr, *act = nullptr, *hsn = nullptr;
+    float *xn_sums = nullptr, *core_sums = nullptr, *act_sums = nullptr, *hsn_sums = nullptr;   // per-64 sums of each operand
+    __half *q = nullptr;
+    int32_t *argmax_ids = nullptr;
+    int proj_ld = 0, gate_up_ld = 0, core_ld = 0, logits_ld = 0;
+    size_t partial_floats = 0, attn_partial_floats = 0, scratch_bytes = 0;
+
+    // Step tables: one pinned blob copied in one transfer.
+    uint32_t *tables_host = nullptr, *tables_dev = nullptr;
+    size_t tables_words = 0;
+    uint32_t *d_tokens, *d_row_slot, *d_row_pos, *d_row_read, *d_row_write, *d_runs, *d_run_info, *d_gather, *d_blocks, *d_page_table;
+    spl_tables last = {};
+    int last_rows = 0, last_logit_rows = 0;
+
+    bool taps_enabled = false, profile = false;
+    std::vector<ProfileSlot> profile_slots;
+    size_t profile_used = 0;
+    double klass_ms[KLASS_COUNT] = {}, klass_bytes[KLASS_COUNT] = {};
+    int64_t klass_launches[KLASS_COUNT] = {};
+    int launches = 0;
+    cudaEvent_t ev_begin = nullptr, ev_end = nullptr;
+
+    spl_status fail(spl_status code, const std::string &text) { error = text; return code; }
+};
+
+namespace {
+
+#define SPL_CUDA(call)                                                                                  \
+    do {                                                                                                \
+        cudaError_t err__ = (call);                                                                     \
+        if (err__ != cudaSuccess) {                                                                     \
+            return e->fail(err__ == cudaErrorMemoryAllocation ? SPL_ERR_ALLOCATION_FAILED : SPL_ERR_DEVICE, \
+                           std::string(#call) + ": " + cudaGetErrorString(err__));                      \
+        }                                                                                               \
+    } while (0)
+
+template <typename T>
+spl_status device_alloc(spl_engine *e, T **ptr, size_t count, size_t *account = nullptr) {
+    SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(ptr), std::max<size_t>(count, 1) * sizeof(T)));
+    if (account) *account += count * sizeof(T);
+    return SPL_OK;
+}
+
+int round16(int v) { return (v + 15) / 16 * 16; }
+
+struct Shapes {
+    int C, VD, VH, AD, KV;
+    int gdn_z, gdn_a, gdn_b, gdn_n;        // column offsets in the fused gated-delta input projection
+    int att_k, att_v, att_n;               // column offsets in the fused attention input projection
+    explicit Shapes(const spl_geometry &g) {
+        C = (2 * g.gdn_key_heads + g.gdn_value_heads) * g.gdn_head_dim; VD = g.gdn_value_heads * g.gdn_head_dim; VH = g.gdn_value_heads;
+        AD = g.heads * g.head_dim; KV = g.kv_heads * g.head_dim;
+        gdn_z = C; gdn_a = C + VD; gdn_b = gdn_a + round16(VH); gdn_n = gdn_b + round16(VH);
+        att_k = 2 * AD; att_v = att_k + KV; att_n = att_v + KV;
+    }
+};
+
+spl_status alloc_q4(spl_engine *e, SplQ4Dev &w, int n, int k) {
+    w.n = n; w.n16 = (n + 15) / 16; w.k = k;
+    const size_t groups = size_t(w.n16) * (k / 64);
+    SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&w.codes), groups * 512));
+    SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&w.sb), groups * 64));
+    SPL_CUDA(cudaMemsetAsync(w.codes, 0, groups * 512, e->stream));
+    SPL_CUDA(cudaMemsetAsync(w.sb, 0, groups * 64, e->stream));
+    e->weight_bytes += groups * 576;
+    return SPL_OK;
+}
+
+void profile_begin(spl_engine *e, int klass, double bytes) {
+    ++e->launches;
+    if (!e->profile) return;
+    if (e->profile_used == e->profile_slots.size()) {
+        ProfileSlot s; cudaEventCreate(&s.begin); cudaEventCreate(&s.end); s.klass = klass; s.bytes = 0;
+        e->profile_slots.push_back(s);
+    }
+    ProfileSlot &s = e->profile_slots[e->profile_used];
+    s.klass = klass; s.bytes = bytes;
+    cudaEventRecord(s.begin, e->stream);
+}
+void profile_end(spl_engine *e) {
+    if (!e->profile) return;
+    cudaEventRecord(e->profile_slots[e->profile_used].end, e->stream);
+    ++e->profile_used;
+}
+void profile_collect(spl_engine *e) {
+    if (!e->profile) return;
+    for (size_t i = 0; i < e->profile_used; ++i) {
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e->profile_slots[i].begin, e->profile_slots[i].end);
+        e->klass_ms[e->profile_slots[i].klass] += ms;
+        e->klass_bytes[e->profile_slots[i].klass] += e->profile_slots[i].bytes;
+        e->klass_launches[e->profile_slots[i].klass] += 1;
+    }
+    e->profile_used = 0;
+}
+
+// ---- GEMM launch ------------------------------------------------------------------------------
+template <int RT, int NBW>
+void launch_gemm_variant(spl_engine *e, const SplQ4Dev &w, const __nv_bfloat16 *act, const float *sums, float *out, int out_ld, const float *residual, int rows) {
+    const int groups = w.k / 64, total_chunks = groups / 4;
+    const int tiles = (w.n16 + SPL_GEMM_WARPS * NBW - 1) / (SPL_GEMM_WARPS * NBW);
+    int splits = std::max(1, std::min(296 / std::max(tiles, 1), total_chunks / 2));
+    // Partials must fit the scratch buffer.
+    while (splits > 1 && size_t(splits) * RT * 8 * out_ld > e->partial_floats) --splits;
+    const int cps = (total_chunks + splits - 1) / splits;
+    splits = (total_chunks + cps - 1) / cps;
+    const size_t smem = size_t(2) * RT * 8 * SPL_GEMM_LDS * sizeof(__nv_bfloat16) + size_t(2) * RT * 8 * 4 * sizeof(float);
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(spl_gemm_q4_kernel<RT, NBW>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        configured = true;
+    }
+    profile_begin(e, KLASS_GEMM, double(w.bytes()));
+    spl_gemm_q4_kernel<RT, NBW><<<dim3(tiles, splits), SPL_GEMM_WARPS * 32, smem, e->stream>>>(
+        w.codes, w.sb, act, sums, w.k, out, out_ld, residual, e->partials, rows, w.n16, groups, cps);
+    if (splits > 1) {
+        ++e->launches;
+        const size_t total = size_t(rows) * out_ld / 4;
+        const int blocks = int(std::min<size_t>((total + 255) / 256, 2048));
+        spl_gemm_reduce_kernel<<<blocks, 256, 0, e->stream>>>(e->partials, splits, RT * 8, rows, out_ld, residual, out);
+    }
+    profile_end(e);
+}
+
+void launch_gemm(spl_engine *e, const SplQ4Dev &w, const __nv_bfloat16 *act, const float *act_sums, float *out, int out_ld, const float *residual, int rows) {
+    for (int r0 = 0; r0 < rows; r0 += 64) {
+        const int count = std::min(64, rows - r0);
+        const __nv_bfloat16 *a = act + size_t(r0) * w.k;
+        const float *sm = act_sums + size_t(r0) * (w.k / 64);
+        float *o = out + size_t(r0) * out_ld;
+        const float *res = residual ? residual + size_t(r0) * out_ld : nullptr;
+        // Two n16 blocks a warp only where registers allow it and the columns still fill the GPU.
+        const bool wide_n = w.n16 >= 2 * SPL_GEMM_WARPS * 148 / 2;
+        if (count <= 8) { if (wide_n) launch_gemm_variant<1, 2>(e, w, a, sm, o, out_ld, res, count); else launch_gemm_variant<1, 1>(e, w, a, sm, o, out_ld, res, count); }
+        else if (count <= 16) { if (wide_n) launch_gemm_variant<2, 2>(e, w, a, sm, o, out_ld, res, count); else launch_gemm_variant<2, 1>(e, w, a, sm, o, out_ld, res, count); }
+        else if (count <= 32) launch_gemm_variant<4, 1>(e, w, a, sm, o, out_ld, res, count);
+        else launch_gemm_variant<8, 1>(e, w, a, sm, o, out_ld, res, count);
+    }
+}
+
+template <int HD>
+void launch_scan(spl_engine *e, int mt, dim3 grid, const SplAttnParams &p, int layer) {
+    const int8_t *kc = e->k_codes[layer], *vc = e->v_codes[layer];
+    const float *ks = e->k_scale[layer], *vs = e->v_scale[layer];
+#define SPL_SCAN(MT)                                                                                                   \
+    {                                                                                                                  \
+        const size_t smem = size_t(16 * MT) * (HD + 4) * 2 + size_t(16 * MT) * SPL_ATTN_PS * 2 + size_t(8) * 16 * MT * 4; \
+        static bool configured = false;                                                                                \
+        if (!configured) { cudaFuncSetAttribute(spl_attn_scan_kernel<MT, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); configured = true; } \
+        spl_attn_scan_kernel<MT, HD><<<grid, 128, smem, e->stream>>>(e->q, e->d_blocks, e->d_row_slot, e->d_row_pos, e->d_page_table, \
+                                                                     kc, ks, vc, vs, e->attn_partials, p);              \
+    }
+    if (mt <= 1) SPL_SCAN(1) else if (mt == 2) SPL_SCAN(2) else if (mt == 3) SPL_SCAN(3) else SPL_SCAN(4)
+#undef SPL_SCAN
+}
+
+spl_status check_launch(spl_engine *e, const char *what) {
+    const cudaError_t err = cudaGetLastError();
+    if (err != cudaSuccess) return e->fail(SPL_ERR_DEVICE, std::string(what) + ": " + cudaGetErrorString(err));
+    return SPL_OK;
+}
+
+spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
+    const auto wall0 = std::chrono::steady_clock::now();
+    const spl_geometry &g = e->g;
+    const Shapes sh(g);
+    const int R = int(t->rows);
+    if (R <= 0 || R > e->c.max_rows) return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: row count outside the engine's limit");
+    if (int(t->logit_rows) > e->host->config.max_logit_rows) return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: too many logit rows");
+    for (size_t l = 0; l < e->layers.size(); ++l) {
+        const LayerWeights &L = e->layers[l];
+        if (!L.in_proj.codes || !L.vec[SPL_VEC_INPUT_NORM]) return e->fail(SPL_ERR_INVALID_ARGUMENT, "weights of a block are not set");
+    }
+    if (!e->head.codes || !e->embed_packed || !e->final_norm) return e->fail(SPL_ERR_INVALID_ARGUMENT, "model-level weights are not set");
+    SPL_CUDA(cudaSetDevice(e->device));
+    // Tables: pack into the pinned blob, one copy.
+    uint32_t *hb = e->tables_host;
+    size_t off = 0;
+    auto put = [&](const uint32_t *src, size_t n, uint32_t **dev) { *dev = e->tables_dev + off; if (n) memcpy(hb + off, src, n * 4); off += (n + 3) / 4 * 4; };
+    put(t->tokens, R, &e->d_tokens); put(t->row_slot, R, &e->d_row_slot); put(t->row_pos, R, &e->d_row_pos);
+    put(t->row_read, R, &e->d_row_read); put(t->row_write, R, &e->d_row_write);
+    put(t->runs, size_t(t->run_count) * 3, &e->d_runs); put(t->run_info, size_t(t->run_count) * 2, &e->d_run_info);
+    put(t->gather_index, t->logit_rows, &e->d_gather); put(t->attn_blocks, size_t(t->attn_block_count) * 2, &e->d_blocks);
+    put(t->page_table, size_t(e->c.max_slots) * e->host->max_pages, &e->d_page_table);
+    if (off > e->tables_words) return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: tables exceed the engine's buffers");
+    e->launches = 0;
+    SPL_CUDA(cudaEventRecord(e->ev_begin, e->stream));
+    SPL_CUDA(cudaMemcpyAsync(e->tables_dev, hb, off * 4, cudaMemcpyHostToDevice, e->stream));
+
+    const int H = g.hidden;
+    profile_begin(e, KLASS_ELEMENTWISE, 0);
+    spl_embed_q4_kernel<<<R, 128, 0, e->stream>>>(e->embed_packed, e->embed_scales, e->embed_biases, e->d_tokens, e->h, H);
+    profile_end(e);
+
+    int linear_index = 0, full_index = 0;
+    const int span_rows_needed = int(t->spans);
+    (void)span_rows_needed;
+    for (int l = 0; l < g.layers; ++l) {
+        const LayerWeights &L = e->layers[l];
+        const int live = (l + 1 == g.layers) ? int(t->live_rows) : R;
+        profile_begin(e, KLASS_ELEMENTWISE, 0);
+        spl_rmsnorm_kernel<<<R, 256, 0, e->stream>>>(e->h, H, L.vec[SPL_VEC_INPUT_NORM], nullptr, e->xn, e->xn_sums, H, g.eps);
+        profile_end(e);
+        launch_gemm(e, L.in_proj, e->xn, e->xn_sums, e->proj, e->proj_ld, nullptr, R);
+        if (!L.full) {
+            SplGdnParams p;
+            p.rows = R; p.runs = int(t->run_count); p.channels = sh.C; p.key_heads = g.gdn_key_heads; p.value_heads = g.gdn_value_heads;
+            p.head_dim = g.gdn_head_dim; p.proj_ld = e->proj_ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps;
+            profile_begin(e, KLASS_GDN, 0);
+            spl_gdn_conv_kernel<<<dim3((sh.C + 255) / 256, t->run_count), 256, 0, e->stream>>>(
+                e->proj, L.vec[SPL_VEC_CONV], e->conv[linear_index], e->d_runs, e->d_row_read, e->d_row_write, e->gdn_act, p);
+            profile_end(e);
+            profile_begin(e, KLASS_GDN, 0);
+            spl_gdn_recurrence_kernel<<<dim3(g.gdn_value_heads, t->run_count), 256, 0, e->stream>>>(
+                e->gdn_act, e->proj, L.vec[SPL_VEC_A_LOG], L.vec[SPL_VEC_DT_BIAS], L.vec[SPL_VEC_GDN_NORM], e->state[linear_index],
+                e->journal[linear_index], e->d_runs, e->d_run_info, e->core, e->core_sums, p);
+            profile_end(e);
+            ++linear_index;
+        } else {
+            SplAttnParams p;
+            p.rows = R; p.live = live; p.heads = g.heads; p.kv_heads = g.kv_heads; p.head_dim = g.head_dim; p.rotary = g.rotary_dim;
+            p.max_pages = e->host->max_pages; p.proj_ld = e->proj_ld; p.k_offset = sh.att_k; p.v_offset = sh.att_v;
+            p.spans = int(t->spans); p.pages_per_span = int(t->pages_per_span); p.eps = g.eps; p.scale = 1.0f / sqrtf(float(g.head_dim));
+            profile_begin(e, KLASS_ATTENTION, 0);
+            spl_attn_prepare_kernel<<<dim3(g.heads + g.kv_heads, R), 128, 0, e->stream>>>(
+                e->proj, L.vec[SPL_VEC_Q_NORM], L.vec[SPL_VEC_K_NORM], e->inv_freq, e->d_row_slot, e->d_row_pos, e->d_page_table, e->q,
+                e->k_codes[full_index], e->k_scale[full_index], e->v_codes[full_index], e->v_scale[full_index], p);
+            profile_end(e);
+            if (live > 0) {
+                // Blocks are in row order: those that begin below `live` hold the computed rows.
+                int blocks = 0, max_count = 1;
+                for (; blocks < int(t->attn_block_count); ++blocks) {
+                    if (int(t->attn_blocks[blocks * 2]) >= live) break;
+                    max_count = std::max(max_count, int(t->attn_blocks[blocks * 2 + 1]));
+                }
+                if (size_t(live) * g.heads * t->spans * (g.head_dim + 2) > e->attn_partial_floats)
+                    return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: attention partials exceed the engine's buffers");
+                const int mt = (max_count * (g.heads / g.kv_heads) + 15) / 16;
+                profile_begin(e, KLASS_ATTENTION, 0);
+                if (g.head_dim == 256) launch_scan<256>(e, mt, dim3(g.kv_heads * t->spans, blocks), p, full_index);
+                else launch_scan<128>(e, mt, dim3(g.kv_heads * t->spans, blocks), p, full_index);
+                profile_end(e);
+                profile_begin(e, KLASS_ATTENTION, 0);
+                spl_attn_merge_kernel<<<dim3(g.heads, live), g.head_dim, 0, e->stream>>>(e->attn_partials, e->proj, e->core, e->core_sums, p);
+                profile_end(e);
+            }
+            ++full_index;
+        }
+        if (live > 0) {
+            launch_gemm(e, L.out_proj, e->core, e->core_sums, e->h, H, e->h, live);
+            profile_begin(e, KLASS_ELEMENTWISE, 0);
+            spl_rmsnorm_kernel<<<live, 256, 0, e->stream>>>(e->h, H, L.vec[SPL_VEC_POST_NORM], nullptr, e->xn, e->xn_sums, H, g.eps);
+            profile_end(e);
+            launch_gemm(e, L.gate_up, e->xn, e->xn_sums, e->gate_up, e->gate_up_ld, nullptr, live);
+            profile_begin(e, KLASS_ELEMENTWISE, 0);
+            const size_t total = size_t(live) * g.inter / 4;
+            spl_silu_mul_kernel<<<int(std::min<size_t>((total + 255) / 256, 4096)), 256, 0, e->stream>>>(e->gate_up, e->gate_up_ld, g.inter, live, e->act, e->act_sums);
+            profile_end(e);
+            launch_gemm(e, L.down, e->act, e->act_sums, e->h, H, e->h, live);
+        }
+        if (e->taps_enabled) SPL_CUDA(cudaMemcpyAsync(e->taps + size_t(l) * e->c.max_rows * H, e->h, size_t(R) * H * 4, cudaMemcpyDeviceToDevice, e->stream));
+    }
+    if (t->logit_rows > 0) {
+        profile_begin(e, KLASS_OTHER, 0);
+        spl_rmsnorm_kernel<<<t->logit_rows, 256, 0, e->stream>>>(e->h, H, e->final_norm, e->d_gather, e->hsn, e->hsn_sums, H, g.eps);
+        profile_end(e);
+        launch_gemm(e, e->head, e->hsn, e->hsn_sums, e->logits, e->logits_ld, nullptr, int(t->logit_rows));
+    }
+    SPL_CUDA(cudaEventRecord(e->ev_end, e->stream));
+    const spl_status launched = check_launch(e, "step launch");
+    if (launched != SPL_OK) return launched;
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    profile_collect(e);
+    e->last_rows = R; e->last_logit_rows = int(t->logit_rows);
+    if (stats) {
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e->ev_begin, e->ev_end);
+        stats->rows = R; stats->launches = e->launches; stats->gpu_seconds = ms / 1000.0;
+        stats->wall_seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - wall0).count();
+    }
+    return SPL_OK;
+}
+
+spl_status upload_q4_into(spl_engine *e, SplQ4Dev &w, int nb_first, int rows, int inner, const uint32_t *packed, const uint16_t *scales,
+                          const uint16_t *biases, bool device_source) {
+    const size_t words = size_t(rows) * inner / 8, groups = size_t(rows) * inner / 64;
+    const uint32_t *dp = packed; const uint16_t *ds = scales, *db = biases;
+    uint32_t *sp = nullptr; uint16_t *ss = nullptr, *sbias = nullptr;
+    if (!device_source) {
+        SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&sp), words * 4));
+        SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&ss), groups * 2));
+        SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&sbias), groups * 2));
+        SPL_CUDA(cudaMemcpyAsync(sp, packed, words * 4, cudaMemcpyHostToDevice, e->stream));
+        SPL_CUDA(cudaMemcpyAsync(ss, scales, groups * 2, cudaMemcpyHostToDevice, e->stream));
+        SPL_CUDA(cudaMemcpyAsync(sbias, biases, groups * 2, cudaMemcpyHostToDevice, e->stream));
+        dp = sp; ds = ss; db = sbias;
+    }
+    const int nb_count = (rows + 15) / 16;
+    const size_t total = size_t(nb_count) * (inner / 64) * 128;
+    spl_repack_q4_kernel<<<int(std::min<size_t>((total + 255) / 256, 16384)), 256, 0, e->stream>>>(
+        dp, ds, db, rows, inner, reinterpret_cast<uint32_t *>(w.codes), w.sb, nb_first, nb_count);
+    const spl_status launched = check_launch(e, "repack");
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    if (sp) { cudaFree(sp); cudaFree(ss); cudaFree(sbias); }
+    return launched;
+}
+
+// Where a tensor kind lands: which fused device tensor and at which 16-column block.
+struct Placement { SplQ4Dev *dst; int nb_first; int rows; int inner; };
+
+spl_status place(spl_engine *e, int layer, int kind, Placement *out) {
+    const spl_geometry &g = e->g;
+    const Shapes sh(g);
+    if (layer < 0) {
+        if (kind == SPL_Q4_HEAD) { *out = {&e->head, 0, g.vocab, g.hidden}; return SPL_OK; }
+        return e->fail(SPL_ERR_INVALID_ARGUMENT, "model-level q4 kind must be embed or head");
+    }
+    if (layer >= g.layers) return e->fail(SPL_ERR_INVALID_ARGUMENT, "layer out of range");
+    LayerWeights &L = e->layers[layer];
+    switch (kind) {
+    case SPL_Q4_QKV: if (L.full) break; *out = {&L.in_proj, 0, sh.C, g.hidden}; return SPL_OK;
+    case SPL_Q4_Z: if (L.full) break; *out = {&L.in_proj, sh.gdn_z / 16, sh.VD, g.hidden}; return SPL_OK;
+    case SPL_Q4_A: if (L.full) break; *out = {&L.in_proj, sh.gdn_a / 16, sh.VH, g.hidden}; return SPL_OK;
+    case SPL_Q4_B: if (L.full) break; *out = {&L.in_proj, sh.gdn_b / 16, sh.VH, g.hidden}; return SPL_OK;
+    case SPL_Q4_OUT: if (L.full) break; *out = {&L.out_proj, 0, g.hidden, sh.VD}; return SPL_OK;
+    case SPL_Q4_Q: if (!L.full) break; *out = {&L.in_proj, 0, 2 * sh.AD, g.hidden}; return SPL_OK;
+    case SPL_Q4_K: if (!L.full) break; *out = {&L.in_proj, sh.att_k / 16, sh.KV, g.hidden}; return SPL_OK;
+    case SPL_Q4_V: if (!L.full) break; *out = {&L.in_proj, sh.att_v / 16, sh.KV, g.hidden}; return SPL_OK;
+    case SPL_Q4_O: if (!L.full) break; *out = {&L.out_proj, 0, g.hidden, sh.AD}; return SPL_OK;
+    case SPL_Q4_GATE: *out = {&L.gate_up, 0, g.inter, g.hidden}; return SPL_OK;
+    case SPL_Q4_UP: *out = {&L.gate_up, g.inter / 16, g.inter, g.hidden}; return SPL_OK;
+    case SPL_Q4_DOWN: *out = {&L.down, 0, g.hidden, g.inter}; return SPL_OK;
+    }
+    return e->fail(SPL_ERR_INVALID_ARGUMENT, "q4 kind does not belong to this layer's mixer");
+}
+
+int vec_count(const spl_geometry &g, int kind) {
+    const Shapes sh(g);
+    switch (kind) {
+    case SPL_VEC_INPUT_NORM: case SPL_VEC_POST_NORM: case SPL_VEC_FINAL_NORM: return g.hidden;
+    case SPL_VEC_CONV: return sh.C * 4;
+    case SPL_VEC_A_LOG: case SPL_VEC_DT_BIAS: return sh.VH;
+    case SPL_VEC_GDN_NORM: return g.gdn_head_dim;
+    case SPL_VEC_Q_NORM: case SPL_VEC_K_NORM: return g.head_dim;
+    }
+    return -1;
+}
+
+spl_status create(const spl_geometry *gp, const spl_config *cp, spl_engine *e) {
+    const spl_geometry &g = e->g = *gp;
+    e->c = *cp;
+    const Shapes sh(g);
+    if (g.layers <= 0 || g.hidden % 256 || g.inter % 256 || sh.VD % 256 || sh.AD % 256 || g.gdn_head_dim != 128 ||
+        (g.head_dim != 128 && g.head_dim != 256) || g.heads % g.kv_heads || g.gdn_value_heads % g.gdn_key_heads || g.vocab % 16 ||
+        g.inter % 16 || sh.C % 16 || g.rotary_dim > g.head_dim || g.rotary_dim % 2 || 8 * (g.heads / g.kv_heads) > 64)
+        return e->fail(SPL_ERR_INVALID_ARGUMENT, "unsupported geometry");
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) return e->fail(SPL_ERR_UNSUPPORTED_DEVICE, "unsupported device: no CUDA device");
+    if (cp->device < 0 || cp->device >= count) return e->fail(SPL_ERR_UNSUPPORTED_DEVICE, "unsupported device: ordinal out of range");
+    cudaDeviceProp prop;
+    SPL_CUDA(cudaGetDeviceProperties(&prop, cp->device));
+    if (prop.major != 10) return e->fail(SPL_ERR_UNSUPPORTED_DEVICE, "unsupported device: kernels are built for sm_100a only");
+    e->device = cp->device;
+    SPL_CUDA(cudaSetDevice(e->device));
+    spl_status hs = spl_host_create(gp, cp, &e->host);
+    if (hs != SPL_OK) return e->fail(hs, "invalid engine configuration");
+    e->c = e->host->config;
+    SPL_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+    SPL_CUDA(cudaEventCreate(&e->ev_begin));
+    SPL_CUDA(cudaEventCreate(&e->ev_end));
+    const int R = e->c.max_rows, H = g.hidden;
+
+    e->layers.resize(g.layers);
+    for (int l = 0; l < g.layers; ++l) {
+        LayerWeights &L = e->layers[l];
+        L.full = l % 4 == 3;
+        spl_status s;
+        if ((s = alloc_q4(e, L.in_proj, L.full ? sh.att_n : sh.gdn_n, H)) != SPL_OK) return s;
+        if ((s = alloc_q4(e, L.out_proj, H, L.full ? sh.AD : sh.VD)) != SPL_OK) return s;
+        if ((s = alloc_q4(e, L.gate_up, 2 * g.inter, H)) != SPL_OK) return s;
+        if ((s = alloc_q4(e, L.down, H, g.inter)) != SPL_OK) return s;
+    }
+    spl_status s;
+    if ((s = alloc_q4(e, e->head, g.vocab, H)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->embed_packed, size_t(g.vocab) * H / 8, &e->weight_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->embed_scales, size_t(g.vocab) * H / 64, &e->weight_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->embed_biases, size_t(g.vocab) * H / 64, &e->weight_bytes)) != SPL_OK) return s;
+    {
+        std::vector<float> freq(std::max(1, g.rotary_dim / 2));
+        for (int i = 0; i < g.rotary_dim / 2; ++i) freq[i] = float(std::pow(double(g.rope_theta), -2.0 * double(i) / double(g.rotary_dim)));
+        if ((s = device_alloc(e, &e->inv_freq, freq.size())) != SPL_OK) return s;
+        SPL_CUDA(cudaMemcpy(e->inv_freq, freq.data(), freq.size() * 4, cudaMemcpyHostToDevice));
+    }
+    // Session state.
+    const size_t page_vecs = size_t(g.kv_heads) * SPL_PAGE_TOKENS;
+    e->kv_page_bytes = (page_vecs * g.head_dim + page_vecs * 4) * 2;
+    e->state_layer_bytes = size_t(g.gdn_value_heads) * 128 * 128 * 4;
+    e->conv_unit_bytes = size_t(sh.C) * 3 * 4;
+    e->journal_bytes = size_t(e->c.max_slots) * SPL_JOURNAL_ROWS * g.gdn_value_heads * SPL_JOURNAL_WIDTH * 4;
+    for (int l = 0; l < g.layers; ++l) {
+        if (l % 4 == 3) {
+            int8_t *kc, *vc; float *ks, *vs;
+            const size_t codes = size_t(e->c.kv_pages) * page_vecs * g.head_dim, scales = size_t(e->c.kv_pages) * page_vecs;
+            if ((s = device_alloc(e, &kc, codes, &e->kv_pool_bytes)) != SPL_OK) return s;
+            if ((s = device_alloc(e, &vc, codes, &e->kv_pool_bytes)) != SPL_OK) return s;
+            if ((s = device_alloc(e, &ks, scales, &e->kv_pool_bytes)) != SPL_OK) return s;
+            if ((s = device_alloc(e, &vs, scales, &e->kv_pool_bytes)) != SPL_OK) return s;
+            // A scale that was never stored reads as NaN, so a masked token that leaks shows.
+            SPL_CUDA(cudaMemsetAsync(kc, 0xFF, codes, e->stream)); SPL_CUDA(cudaMemsetAsync(vc, 0xFF, codes, e->stream));
+            SPL_CUDA(cudaMemsetAsync(ks, 0xFF, scales * 4, e->stream)); SPL_CUDA(cudaMemsetAsync(vs, 0xFF, scales * 4, e->stream));
+            e->k_codes.push_back(kc); e->v_codes.push_back(vc); e->k_scale.push_back(ks); e->v_scale.push_back(vs);
+        } else {
+            float *st, *cv, *jr;
+            if ((s = device_alloc(e, &st, size_t(e->c.max_slots) * e->state_layer_bytes / 4)) != SPL_OK) return s;
+            if ((s = device_alloc(e, &cv, size_t(e->c.state_units) * e->conv_unit_bytes / 4)) != SPL_OK) return s;
+            if ((s = device_alloc(e, &jr, e->journal_bytes / 4)) != SPL_OK) return s;
+            SPL_CUDA(cudaMemsetAsync(st, 0, size_t(e->c.max_slots) * e->state_layer_bytes, e->stream));
+            SPL_CUDA(cudaMemsetAsync(cv, 0, size_t(e->c.state_units) * e->conv_unit_bytes, e->stream));
+            SPL_CUDA(cudaMemsetAsync(jr, 0, e->journal_bytes, e->stream));
+            e->state.push_back(st); e->conv.push_back(cv); e->journal.push_back(jr);
+        }
+    }
+    // Activations.
+    e->proj_ld = std::max(sh.gdn_n, sh.att_n); e->gate_up_ld = 2 * g.inter; e->core_ld = std::max(sh.VD, sh.AD); e->logits_ld = g.vocab;
+    const int LR = e->c.max_logit_rows;
+    if ((s = device_alloc(e, &e->h, size_t(R) * H, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->xn, size_t(R) * H, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->proj, size_t(R) * e->proj_ld, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->gdn_act, size_t(R) * sh.C, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->core, size_t(R) * e->core_ld, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->gate_up, size_t(R) * e->gate_up_ld, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->act, size_t(R) * g.inter, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->q, size_t(R) * sh.AD, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->xn_sums, size_t(R) * H / 64, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->core_sums, size_t(R) * e->core_ld / 64, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->act_sums, size_t(R) * g.inter / 64, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->hsn_sums, size_t(LR) * H / 64, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->hsn, size_t(LR) * H, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->logits, size_t(LR) * e->logits_ld, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->argmax_ids, size_t(LR), &e->scratch_bytes)) != SPL_OK) return s;
+    e->partial_floats = size_t(16) * 64 * std::max(H, 4096);
+    if ((s = device_alloc(e, &e->partials, e->partial_floats, &e->scratch_bytes)) != SPL_OK) return s;
+    e->attn_partial_floats = size_t(std::max(16 * R, 64 * std::min(R, 128))) * g.heads * (g.head_dim + 2);
+    if ((s = device_alloc(e, &e->attn_partials, e->attn_partial_floats, &e->scratch_bytes)) != SPL_OK) return s;
+    e->tables_words = size_t(R) * 5 + size_t(e->c.max_slots) * 5 + size_t(LR) + size_t(R) * 2 + size_t(e->c.max_slots) * e->host->max_pages + 64;
+    SPL_CUDA(cudaMallocHost(reinterpret_cast<void **>(&e->tables_host), e->tables_words * 4));
+    if ((s = device_alloc(e, &e->tables_dev, e->tables_words)) != SPL_OK) return s;
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    return SPL_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+spl_status spl_engine_create(const spl_geometry *geometry, const spl_config *config, spl_engine **out) {
+    if (!geometry || !config || !out) return SPL_ERR_INVALID_ARGUMENT;
+    spl_engine *e = new spl_engine;
+    const spl_status s = create(geometry, config, e);
+    *out = e;               // returned even on failure so the caller can read the error string
+    return s;
+}
+
+void spl_engine_destroy(spl_engine *e) {
+    if (!e) return;
+    if (e->stream) cudaStreamSynchronize(e->stream);
+    auto release_q4 = [](SplQ4Dev &w) { cudaFree(w.codes); cudaFree(w.sb); };
+    for (LayerWeights &L : e->layers) {
+        release_q4(L.in_proj); release_q4(L.out_proj); release_q4(L.gate_up); release_q4(L.down);
+        for (uint16_t *v : L.vec) cudaFree(v);
+    }
+    release_q4(e->head);
+    cudaFree(e->embed_packed); cudaFree(e->embed_scales); cudaFree(e->embed_biases); cudaFree(e->final_norm); cudaFree(e->inv_freq);
+    for (auto p : e->k_codes) cudaFree(p); for (auto p : e->v_codes) cudaFree(p);
+    for (auto p : e->k_scale) cudaFree(p); for (auto p : e->v_scale) cudaFree(p);
+    for (auto p : e->state) cudaFree(p); for (auto p : e->conv) cudaFree(p); for (auto p : e->journal) cudaFree(p);
+    cudaFree(e->h); cudaFree(e->xn); cudaFree(e->proj); cudaFree(e->gdn_act); cudaFree(e->core); cudaFree(e->gate_up); cudaFree(e->act);
+    cudaFree(e->q); cudaFree(e->hsn); cudaFree(e->logits); cudaFree(e->argmax_ids); cudaFree(e->partials); cudaFree(e->attn_partials);
+    cudaFree(e->taps); cudaFree(e->tables_dev); cudaFree(e->xn_sums); cudaFree(e->core_sums); cudaFree(e->act_sums); cudaFree(e->hsn_sums);
+    if (e->tables_host) cudaFreeHost(e->tables_host);
+    for (ProfileSlot &s : e->profile_slots) { cudaEventDestroy(s.begin); cudaEventDestroy(s.end); }
+    if (e->ev_begin) cudaEventDestroy(e->ev_begin);
+    if (e->ev_end) cudaEventDestroy(e->ev_end);
+    if (e->stream) cudaStreamDestroy(e->stream);
+    spl_host_destroy(e->host);
+    delete e;
+}
+
+const char *spl_last_error_string(const spl_engine *e) {
+    if (!e) return "no engine";
+    if (e->error.empty() && e->host) return e->host->error.c_str();
+    return e->error.c_str();
+}
+
+spl_status spl_weights_set_q4(spl_engine *e, int32_t layer, int32_t kind, int32_t rows, int32_t inner,
+                              const uint32_t *packed, const uint16_t *scales, const uint16_t *biases) {
+    if (!e || !packed || !scales || !biases) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_CUDA(cudaSetDevice(e->device));
+    if (layer < 0 && kind == SPL_Q4_EMBED) {
+        if (rows != e->g.vocab || inner != e->g.hidden) return e->fail(SPL_ERR_INVALID_ARGUMENT, "embedding shape does not match the geometry");
+        SPL_CUDA(cudaMemcpy(e->embed_packed, packed, size_t(rows) * inner / 2, cudaMemcpyHostToDevice));
+        SPL_CUDA(cudaMemcpy(e->embed_scales, scales, size_t(rows) * inner / 32, cudaMemcpyHostToDevice));
+        SPL_CUDA(cudaMemcpy(e->embed_biases, biases, size_t(rows) * inner / 32, cudaMemcpyHostToDevice));
+        return SPL_OK;
+    }
+    Placement pl;
+    const spl_status s = place(e, layer, kind, &pl);
+    if (s != SPL_OK) return s;
+    if (rows != pl.rows || inner != pl.inner) return e->fail(SPL_ERR_INVALID_ARGUMENT, "tensor shape does not match the geometry");
+    return upload_q4_into(e, *pl.dst, pl.nb_first, rows, inner, packed, scales, biases, false);
+}
+
+spl_status spl_weights_set_vector(spl_engine *e, int32_t layer, int32_t kind, const uint16_t *bf16, int32_t count) {
+    if (!e || !bf16 || kind < 0 || kind >= SPL_VEC_KINDS) return SPL_ERR_INVALID_ARGUMENT;
+    if (count != vec_count(e->g, kind)) return e->fail(SPL_ERR_INVALID_ARGUMENT, "vector length does not match the geometry");
+    SPL_CUDA(cudaSetDevice(e->device));
+    uint16_t **slot = nullptr;
+    if (kind == SPL_VEC_FINAL_NORM) slot = &e->final_norm;
+    else {
+        if (layer < 0 || layer >= e->g.layers) return e->fail(SPL_ERR_INVALID_ARGUMENT, "layer out of range");
+        slot = &e->layers[layer].vec[kind];
+    }
+    if (!*slot) SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(slot), size_t(count) * 2));
+    SPL_CUDA(cudaMemcpy(*slot, bf16, size_t(count) * 2, cudaMemcpyHostToDevice));
+    return SPL_OK;
+}
+
+static uint64_t fnv1a64(const char *s) {
+    uint64_t h = 0xcbf29ce484222325ull;
+    for (; *s; ++s) { h ^= uint8_t(*s); h *= 0x100000001b3ull; }
+    return h;
+}
+
+spl_status spl_weights_synthesize_q4(spl_engine *e, uint64_t seed) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_CUDA(cudaSetDevice(e->device));
+    static const char *names[SPL_Q4_KINDS] = {"linear_attn.in_proj_qkv", "linear_attn.in_proj_z", "linear_attn.in_proj_a", "linear_attn.in_proj_b",
+                                              "linear_attn.out_proj", "self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
+                                              "mlp.gate_proj", "mlp.up_proj", "mlp.down_proj", "embed_tokens", "lm_head"};
+    const float factor = 0.02f * (1.0f / 37837.2265625f);
+    // Staging for the largest tensor in MLX layout.
+    const size_t max_weights = size_t(std::max(e->g.vocab, std::max(2 * e->g.heads * e->g.head_dim, e->g.inter))) * std::max(e->g.hidden, e->g.inter);
+    uint32_t *sp; uint16_t *ss, *sbias;
+    SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&sp), max_weights / 2));
+    SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&ss), max_weights / 32));
+    SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&sbias), max_weights / 32));
+    spl_status result = SPL_OK;
+    for (int layer = -1; layer < e->g.layers && result == SPL_OK; ++layer) {
+        for (int kind = 0; kind < SPL_Q4_KINDS && result == SPL_OK; ++kind) {
+            char full[128];
+            Placement pl;
+            if (layer < 0) {
+                if (kind != SPL_Q4_EMBED && kind != SPL_Q4_HEAD) continue;
+                snprintf(full, sizeof full, "%s", names[kind]);
+                pl = {kind == SPL_Q4_HEAD ? &e->head : nullptr, 0, e->g.vocab, e->g.hidden};
+            } else {
+                if (kind >= SPL_Q4_EMBED) continue;
+                const bool full_layer = e->layers[layer].full;
+                if ((kind <= SPL_Q4_OUT && full_layer) || (kind >= SPL_Q4_Q && kind <= SPL_Q4_O && !full_layer)) continue;
+                snprintf(full, sizeof full, "layers.%d.%s", layer, names[kind]);
+                if ((result = place(e, layer, kind, &pl)) != SPL_OK) break;
+            }
+            const size_t slots = size_t(pl.rows) * pl.inner / 64;
+            uint32_t *dp = sp; uint16_t *ds = ss, *db = sbias;
+            if (!pl.dst) { dp = e->embed_packed; ds = e->embed_scales; db = e->embed_biases; }
+            spl_synth_q4_kernel<<<int(std::min<size_t>((slots + 127) / 128, 65535)), 128, 0, e->stream>>>(seed ^ fnv1a64(full), factor, pl.rows, pl.inner, dp, ds, db);
+            if ((result = check_launch(e, "synthesize")) != SPL_OK) break;
+            if (pl.dst) result = upload_q4_into(e, *pl.dst, pl.nb_first, pl.rows, pl.inner, sp, ss, sbias, true);
+        }
+    }
+    cudaStreamSynchronize(e->stream);
+    cudaFree(sp); cudaFree(ss); cudaFree(sbias);
+    return result;
+}
+
+spl_status spl_step_tables(spl_engine *e, const spl_tables *tables, spl_step_stats *stats) {
+    if (!e || !tables) return SPL_ERR_INVALID_ARGUMENT;
+    e->error.clear();
+    return run_step(e, tables, stats);
+}
+
+spl_status spl_step(spl_engine *e, const spl_row *rows, int32_t count, spl_step_stats *stats) {
+    if (!e || !rows) return SPL_ERR_INVALID_ARGUMENT;
+    e->error.clear();
+    spl_tables t;
+    const spl_status built = spl_host_build_tables(e->host, rows, count, &t);
+    if (built != SPL_OK) return e->fail(built, e->host->error);
+    const spl_status ran = run_step(e, &t, stats);
+    if (ran == SPL_OK) spl_host_finish_step(e->host, &t);
+    return ran;
+}
+
+spl_status spl_logits_row(spl_engine *e, int32_t index, float *dst) {
+    if (!e || !dst || index < 0 || index >= e->last_logit_rows) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_CUDA(cudaSetDevice(e->device));
+    SPL_CUDA(cudaMemcpyAsync(dst, e->logits + size_t(index) * e->logits_ld, size_t(e->g.vocab) * 4, cudaMemcpyDeviceToHost, e->stream));
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    return SPL_OK;
+}
+
+spl_status spl_argmax(spl_engine *e, int32_t vocab_limit, int32_t *ids) {
+    if (!e || !ids || vocab_limit <= 0 || vocab_limit > e->g.vocab) return SPL_ERR_INVALID_ARGUMENT;
+    if (e->last_logit_rows == 0) return SPL_OK;
+    SPL_CUDA(cudaSetDevice(e->device));
+    spl_argmax_kernel<<<e->last_logit_rows, 1024, 0, e->stream>>>(e->logits, e->logits_ld, vocab_limit, e->argmax_ids);
+    const spl_status launched = check_launch(e, "argmax");
+    if (launched != SPL_OK) return launched;
+    SPL_CUDA(cudaMemcpyAsync(ids, e->argmax_ids, size_t(e->last_logit_rows) * 4, cudaMemcpyDeviceToHost, e->stream));
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    return SPL_OK;
+}
+
+spl_status spl_slot_reset(spl_engine *e, int32_t slot) {
+    if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_CUDA(cudaSetDevice(e->device));
+    const int unit = spl_host_reset_slot(e->host, slot);
+    for (size_t l = 0; l < e->state.size(); ++l) {
+        SPL_CUDA(cudaMemsetAsync(reinterpret_cast<char *>(e->state[l]) + size_t(slot) * e->state_layer_bytes, 0, e->state_layer_bytes, e->stream));
+        SPL_CUDA(cudaMemsetAsync(reinterpret_cast<char *>(e->conv[l]) + size_t(unit) * e->conv_unit_bytes, 0, e->conv_unit_bytes, e->stream));
+    }
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    return SPL_OK;
+}
+spl_status spl_verify_discard(spl_engine *e, int32_t slot) {
+    if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    spl_host_discard_verify(e->host, slot); return SPL_OK;
+}
+spl_status spl_verify_accept(spl_engine *e, int32_t slot, int32_t rows, int32_t token_count) {
+    if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    const spl_status s = spl_host_accept_verify(e->host, slot, rows, token_count);
+    if (s != SPL_OK) e->error = e->host->error;
+    return s;
+}
+spl_status spl_slot_truncate(spl_engine *e, int32_t slot, int32_t token_count) {
+    if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    spl_host_truncate(e->host, slot, token_count); return SPL_OK;
+}
+int32_t spl_pages_held(const spl_engine *e, int32_t slot) { return spl_host_pages_held(e->host, slot); }
+int32_t spl_free_page_count(const spl_engine *e) { return spl_host_free_page_count(e->host); }
+spl_host *spl_engine_host(spl_engine *e) { return e ? e->host : nullptr; }
+spl_status spl_warmup(spl_engine *) { return SPL_OK; }
+
+spl_status spl_memory(const spl_engine *ce, spl_memory_info *out) {
+    spl_engine *e = const_cast<spl_engine *>(ce);
+    if (!e || !out) return SPL_ERR_INVALID_ARGUMENT;
+    const int linear = int(e->state.size());
+    out->weight_bytes = int64_t(e->weight_bytes); out->kv_pool_bytes = int64_t(e->kv_pool_bytes);
+    out->kv_bytes_per_page = int64_t(e->kv_page_bytes * e->k_codes.size());
+    out->kv_pages_total = e->c.kv_pages; out->kv_pages_used = e->c.kv_pages - spl_host_free_page_count(e->host);
+    out->state_bytes_per_slot = int64_t((e->state_layer_bytes + e->conv_unit_bytes) * linear);
+    out->state_units_used = e->c.state_units - int64_t(e->host->free_units.size());
+    out->state_bytes_total = int64_t(e->state_layer_bytes) * linear * e->c.max_slots + int64_t(e->conv_unit_bytes) * linear * out->state_units_used;
+    out->scratch_bytes = int64_t(e->scratch_bytes);
+    size_t free_b = 0, total_b = 0;
+    SPL_CUDA(cudaSetDevice(e->device));
+    SPL_CUDA(cudaMemGetInfo(&free_b, &total_b));
+    out->device_total_bytes = int64_t(total_b); out->device_free_bytes = int64_t(free_b);
+    return SPL_OK;
+}
+
+spl_status spl_debug_fill_kv(spl_engine *e, int32_t slot) {
+    if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_CUDA(cudaSetDevice(e->device));
+    const size_t page_vecs = size_t(e->g.kv_heads) * SPL_PAGE_TOKENS, page_codes = page_vecs * e->g.head_dim;
+    for (size_t l = 0; l < e->k_codes.size(); ++l)
+        for (uint32_t page : e->host->slot_pages[slot]) {
+            const uint64_t seed = 0x9E3779B97F4A7C15ull ^ (uint64_t(l) << 32) ^ page;
+            spl_fill_codes_kernel<<<64, 256, 0, e->stream>>>(reinterpret_cast<uint64_t *>(e->k_codes[l] + page * page_codes), page_codes / 8, seed);
+            spl_fill_codes_kernel<<<64, 256, 0, e->stream>>>(reinterpret_cast<uint64_t *>(e->v_codes[l] + page * page_codes), page_codes / 8, seed + 1);
+            spl_fill_float_kernel<<<4, 256, 0, e->stream>>>(e->k_scale[l] + page * page_vecs, page_vecs, 0.01f);
+            spl_fill_float_kernel<<<4, 256, 0, e->stream>>>(e->v_scale[l] + page * page_vecs, page_vecs, 0.01f);
+        }
+    const spl_status launched = check_launch(e, "fill kv");
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    return launched;
+}
+
+spl_status spl_debug_fill_state(spl_engine *e, int32_t slot, uint64_t seed) {
+    if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_CUDA(cudaSetDevice(e->device));
+    const size_t count = e->state_layer_bytes / 4;
+    for (size_t l = 0; l < e->state.size(); ++l)
+        spl_fill_uniform_kernel<<<256, 256, 0, e->stream>>>(e->state[l] + size_t(slot) * count, count, seed + l * 1315423911ull + uint64_t(slot), -0.5f, 0.5f);
+    const spl_status launched = check_launch(e, "fill state");
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    return launched;
+}
+
+spl_status spl_debug_taps(spl_engine *e, int32_t enabled) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_CUDA(cudaSetDevice(e->device));
+    if (enabled && !e->taps) SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&e->taps), size_t(e->g.layers) * e->c.max_rows * e->g.hidden * 4));
+    e->taps_enabled = enabled != 0;
+    return SPL_OK;
+}
+
+spl_status spl_debug_profile(spl_engine *e, int32_t enabled) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    e->profile = enabled != 0;
+    for (int k = 0; k < KLASS_COUNT; ++k) { e->klass_ms[k] = 0; e->klass_bytes[k] = 0; e->klass_launches[k] = 0; }
+    return SPL_OK;
+}
+spl_status spl_debug_profile_read(spl_engine *e, int32_t klass, double *milliseconds, int64_t *launches, double *bytes) {
+    if (!e || klass < 0 || klass >= KLASS_COUNT) return SPL_ERR_INVALID_ARGUMENT;
+    if (milliseconds) *milliseconds = e->klass_ms[klass];
+    if (launches) *launches = e->klass_launches[klass];
+    if (bytes) *bytes = e->klass_bytes[klass];
+    return SPL_OK;
+}
+
+spl_status spl_debug_read(spl_engine *e, int32_t which, int32_t index, void *dst, size_t bytes) {
+    if (!e || !dst) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_CUDA(cudaSetDevice(e->device));
+    const void *src = nullptr; size_t have = 0;
+    const size_t page_vecs = size_t(e->g.kv_heads) * SPL_PAGE_TOKENS, codes = size_t(e->c.kv_pages) * page_vecs * e->g.head_dim;
+    auto pick = [&](const std::vector<float *> &v, size_t n) { if (index >= 0 && index < int(v.size())) { src = v[index]; have = n; } };
+    switch (which) {
+    case 0: pick(e->state, size_t(e->c.max_slots) * e->state_layer_bytes); break;
+    case 1: pick(e->conv, size_t(e->c.state_units) * e->conv_unit_bytes); break;
+    case 2: pick(e->journal, e->journal_bytes); break;
+    case 3: if (index >= 0 && index < int(e->k_codes.size())) { src = e->k_codes[index]; have = codes; } break;
+    case 4: if (index >= 0 && index < int(e->v_codes.size())) { src = e->v_codes[index]; have = codes; } break;
+    case 5: pick(e->k_scale, size_t(e->c.kv_pages) * page_vecs * 4); break;
+    case 6: pick(e->v_scale, size_t(e->c.kv_pages) * page_vecs * 4); break;
+    case 7: src = e->h; have = size_t(e->last_rows) * e->g.hidden * 4; break;
+    case 8: if (e->taps && index >= 0 && index < e->g.layers) { src = e->taps + size_t(index) * e->c.max_rows * e->g.hidden; have = size_t(e->last_rows) * e->g.hidden * 4; } break;
+    }
+    if (!src || bytes > have) return e->fail(SPL_ERR_INVALID_ARGUMENT, "debug read outside the buffer");
+    SPL_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost));
+    return SPL_OK;
+}
+
+// One GEMM on host buffers: the whole path a caller without an engine sees.
+spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t *scales, const uint16_t *biases,
+                          int32_t n, int32_t k, const float *activations, int32_t rows, const float *residual, float *out) {
+    if (!packed || !scales || !biases || !activations || !out || n <= 0 || k <= 0 || k % 256 || rows <= 0) return SPL_ERR_INVALID_ARGUMENT;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return SPL_ERR_UNSUPPORTED_DEVICE;
+    spl_engine local;                     // only stream, partial scratch and error text are used
+    spl_engine *e = &local;
+    e->device = device;
+    SPL_CUDA(cudaSetDevice(device));
+    SPL_CUDA(cudaStreamCreate(&e->stream));
+    SplQ4Dev w;
+    spl_status s = alloc_q4(e, w, n, k);
+    const int ld = w.n16 * 16;
+    float *d_act32 = nullptr, *d_out = nullptr; __nv_bfloat16 *d_act = nullptr;
+    e->partial_floats = size_t(16) * 64 * ld;
+    if (s == SPL_OK) s = device_alloc(e, &d_act32, size_t(rows) * k);
+    if (s == SPL_OK) s = device_alloc(e, &d_act, size_t(rows) * k);
+    if (s == SPL_OK) s = device_alloc(e, &d_out, size_t(rows) * ld);
+    if (s == SPL_OK) s = device_alloc(e, &e->partials, e->partial_floats);
+    if (s == SPL_OK) s = upload_q4_into(e, w, 0, n, k, packed, scales, biases, false);
+    if (s == SPL_OK) {
+        std::vector<uint16_t> rounded(size_t(rows) * k);
+        for (size_t i = 0; i < rounded.size(); ++i) {
+            uint32_t bits; memcpy(&bits, &activations[i], 4);
+            rounded[i] = uint16_t((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16);
+        }
+        cudaMemcpy(d_act, rounded.data(), rounded.size() * 2, cudaMemcpyHostToDevice);
+        std::vector<float> sums(size_t(rows) * k / 64, 0.0f);
+        for (size_t i = 0; i < rounded.size(); ++i) {
+            const uint32_t bits = uint32_t(rounded[i]) << 16; float v; memcpy(&v, &bits, 4);
+            sums[i / 64] += v;
+        }
+        cudaMemcpy(d_act32, sums.data(), sums.size() * 4, cudaMemcpyHostToDevice);
+        if (residual) cudaMemcpy2D(d_out, size_t(ld) * 4, residual, size_t(n) * 4, size_t(n) * 4, rows, cudaMemcpyHostToDevice);
+        launch_gemm(e, w, d_act, d_act32, d_out, ld, residual ? d_out : nullptr, rows);
+        s = check_launch(e, "gemm");
+        if (cudaStreamSynchronize(e->stream) != cudaSuccess) s = SPL_ERR_DEVICE;
+        if (s == SPL_OK) cudaMemcpy2D(out, size_t(n) * 4, d_out, size_t(ld) * 4, size_t(n) * 4, rows, cudaMemcpyDeviceToHost);
+    }
+    cudaFree(w.codes); cudaFree(w.sb); cudaFree(d_act32); cudaFree(d_act); cudaFree(d_out); cudaFree(e->partials);
+    cudaStreamDestroy(e->stream);
+    e->stream = nullptr; e->partials = nullptr;
+    return s;
+}
+
+}  // extern "C"

@@ -1,0 +1,418 @@
+"""ctypes host over libsploshcuda.so, mirroring the reference's `Engine` API
+(Sources/SploshRuntime/Engine.swift:19-108 types, :810-868 slot lifecycle, :1316 step,
+:1202-1205 logits) so tests read like the reference's own drivers
+(Sources/SploshCLI/GenerateCommand.swift:375-469)."""
+import ctypes as C
+import os
+from dataclasses import dataclass
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+def library_path():
+    return os.path.join(_HERE, "libsploshcuda.so")
+
+
+class Geometry(C.Structure):
+    """ModelGeometry (Sources/SploshModel/ModelWeights.swift:66-88) as a parameter."""
+    _fields_ = [(n, C.c_int32) for n in ("layers", "hidden", "inter", "vocab", "heads", "kv_heads", "head_dim", "rotary_dim",
+                                         "gdn_key_heads", "gdn_value_heads", "gdn_head_dim")] + [("eps", C.c_float), ("rope_theta", C.c_float)]
+
+    @property
+    def channels(self):
+        return (2 * self.gdn_key_heads + self.gdn_value_heads) * self.gdn_head_dim
+
+    @property
+    def value_dim(self):
+        return self.gdn_value_heads * self.gdn_head_dim
+
+
+def tiny_geometry():
+    return Geometry(4, 1024, 2816, 32000, 8, 2, 128, 32, 4, 8, 128, 1e-6, 1e7)
+
+
+def b27_geometry(layers=64, vocab=248320):
+    return Geometry(layers, 5120, 17408, vocab, 24, 4, 256, 64, 16, 48, 128, 1e-6, 1e7)
+
+
+class _Config(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("device", "max_slots", "max_rows", "kv_pages", "max_context", "state_units",
+                                         "max_logit_rows", "span_target")]
+
+
+class _Row(C.Structure):
+    _fields_ = [("slot", C.c_int32), ("token", C.c_int32), ("position", C.c_int32), ("want_logits", C.c_uint8),
+                ("verify", C.c_uint8), ("reserved", C.c_uint8 * 2)]
+
+
+class _Tables(C.Structure):
+    _fields_ = [(n, C.c_uint32) for n in ("rows", "run_count", "logit_rows", "attn_block_count", "step_pages", "live_rows",
+                                          "spans", "pages_per_span")] + \
+               [(n, C.POINTER(C.c_uint32)) for n in ("tokens", "row_slot", "row_pos", "runs", "run_info", "row_read", "row_write",
+                                                     "gather_index", "attn_blocks", "page_table")]
+
+
+class _Stats(C.Structure):
+    _fields_ = [("rows", C.c_int32), ("launches", C.c_int32), ("gpu_seconds", C.c_double), ("wall_seconds", C.c_double)]
+
+
+class _Memory(C.Structure):
+    _fields_ = [(n, C.c_int64) for n in ("weight_bytes", "kv_pool_bytes", "kv_bytes_per_page", "kv_pages_total", "kv_pages_used",
+                                         "state_bytes_per_slot", "state_bytes_total", "state_units_used", "scratch_bytes",
+                                         "device_total_bytes", "device_free_bytes")]
+
+
+STATUS_NAMES = ["ok", "kvPoolExhausted", "contextExceeded", "unsupportedDevice", "allocationFailed", "invalidRows",
+                "snapshotMismatch", "invalidKernelChoice", "device", "timeout", "invalidArgument"]
+Q4_KINDS = ["qkv", "z", "a", "b", "out", "q", "k", "v", "o", "gate", "up", "down", "embed", "head"]
+VEC_KINDS = ["input_norm", "post_norm", "conv", "a_log", "dt_bias", "gdn_norm", "q_norm", "k_norm", "final_norm"]
+
+
+class EngineError(Exception):
+    """EngineError (Engine.swift:88-108): `.case` holds the Swift case name."""
+
+    def __init__(self, status, message):
+        self.status = status
+        self.case = STATUS_NAMES[status] if 0 <= status < len(STATUS_NAMES) else str(status)
+        super().__init__(f"{self.case}: {message}")
+
+
+@dataclass
+class EngineConfig:
+    max_slots: int = 8
+    max_rows: int = 64
+    kv_pages: int = 256
+    max_context: int = 32768
+    state_units: int = 0
+    max_logit_rows: int = 0
+    span_target: int = 0
+    device: int = 0
+
+    def c(self):
+        return _Config(self.device, self.max_slots, self.max_rows, self.kv_pages, self.max_context, self.state_units,
+                       self.max_logit_rows, self.span_target)
+
+
+@dataclass
+class EngineRow:
+    slot: int
+    token: int
+    position: int
+    want_logits: bool
+    verify: bool = False
+
+
+@dataclass
+class StepStats:
+    rows: int
+    launches: int
+    gpu_seconds: float
+    wall_seconds: float
+
+
+def lib():
+    """Load the C-ABI library. Fails loudly when it is missing: there is no other path."""
+    global _LIB
+    if _LIB is None:
+        path = library_path()
+        if not os.path.exists(path):
+            raise RuntimeError(f"{path} is missing: build it with `make -C splosh_b200/csrc` (or __graft_entry__.build())")
+        L = C.CDLL(path)
+        vp, i32, u64 = C.c_void_p, C.c_int32, C.c_uint64
+        sig = {
+            "spl_host_create": (i32, [C.POINTER(Geometry), C.POINTER(_Config), C.POINTER(vp)]),
+            "spl_host_destroy": (None, [vp]),
+            "spl_host_build_tables": (i32, [vp, C.POINTER(_Row), i32, C.POINTER(_Tables)]),
+            "spl_host_finish_step": (None, [vp, C.POINTER(_Tables)]),
+            "spl_host_reset_slot": (i32, [vp, i32]),
+            "spl_host_discard_verify": (None, [vp, i32]),
+            "spl_host_accept_verify": (i32, [vp, i32, i32, i32]),
+            "spl_host_truncate": (None, [vp, i32, i32]),
+            "spl_host_pages_held": (i32, [vp, i32]),
+            "spl_host_free_page_count": (i32, [vp]),
+            "spl_host_slot_unit": (i32, [vp, i32]),
+            "spl_host_journal_pending": (i32, [vp, i32]),
+            "spl_host_max_pages": (i32, [vp]),
+            "spl_host_last_error": (C.c_char_p, [vp]),
+            "spl_greedy_accept": (i32, [vp, vp, i32, C.POINTER(i32)]),
+            "spl_engine_create": (i32, [C.POINTER(Geometry), C.POINTER(_Config), C.POINTER(vp)]),
+            "spl_engine_destroy": (None, [vp]),
+            "spl_last_error_string": (C.c_char_p, [vp]),
+            "spl_weights_set_q4": (i32, [vp, i32, i32, i32, i32, vp, vp, vp]),
+            "spl_weights_set_vector": (i32, [vp, i32, i32, vp, i32]),
+            "spl_weights_synthesize_q4": (i32, [vp, u64]),
+            "spl_step": (i32, [vp, C.POINTER(_Row), i32, C.POINTER(_Stats)]),
+            "spl_step_tables": (i32, [vp, C.POINTER(_Tables), C.POINTER(_Stats)]),
+            "spl_logits_row": (i32, [vp, i32, vp]),
+            "spl_argmax": (i32, [vp, i32, vp]),
+            "spl_slot_reset": (i32, [vp, i32]),
+            "spl_verify_discard": (i32, [vp, i32]),
+            "spl_verify_accept": (i32, [vp, i32, i32, i32]),
+            "spl_slot_truncate": (i32, [vp, i32, i32]),
+            "spl_pages_held": (i32, [vp, i32]),
+            "spl_free_page_count": (i32, [vp]),
+            "spl_memory": (i32, [vp, C.POINTER(_Memory)]),
+            "spl_engine_host": (vp, [vp]),
+            "spl_warmup": (i32, [vp]),
+            "spl_debug_fill_kv": (i32, [vp, i32]),
+            "spl_debug_fill_state": (i32, [vp, i32, u64]),
+            "spl_debug_read": (i32, [vp, i32, i32, vp, C.c_size_t]),
+            "spl_debug_taps": (i32, [vp, i32]),
+            "spl_debug_profile": (i32, [vp, i32]),
+            "spl_debug_profile_read": (i32, [vp, i32, C.POINTER(C.c_double), C.POINTER(C.c_int64), C.POINTER(C.c_double)]),
+            "spl_op_gemm_q4": (i32, [i32, vp, vp, vp, i32, i32, vp, i32, vp, vp]),
+        }
+        for name, (res, args) in sig.items():
+            fn = getattr(L, name)
+            fn.restype, fn.argtypes = res, args
+        _LIB = L
+    return _LIB
+
+
+EXPORTS = None  # filled by tests from include/splosh_cuda.h
+
+
+def _ptr(a):
+    return a.ctypes.data_as(C.c_void_p)
+
+
+def _rows_array(rows):
+    arr = (_Row * len(rows))()
+    for i, r in enumerate(rows):
+        arr[i].slot, arr[i].token, arr[i].position = r.slot, r.token, r.position
+        arr[i].want_logits, arr[i].verify = int(bool(r.want_logits)), int(bool(r.verify))
+    return arr
+
+
+def _tables_dict(t, max_slots, max_pages):
+    def arr(p, n):
+        return np.ctypeslib.as_array(p, (n,)).copy() if n else np.zeros(0, np.uint32)
+    return dict(rows=t.rows, step_pages=t.step_pages, live_rows=t.live_rows, spans=t.spans, pages_per_span=t.pages_per_span,
+                tokens=arr(t.tokens, t.rows), row_slot=arr(t.row_slot, t.rows), row_pos=arr(t.row_pos, t.rows),
+                runs=arr(t.runs, t.run_count * 3), run_info=arr(t.run_info, t.run_count * 2),
+                row_read=arr(t.row_read, t.rows), row_write=arr(t.row_write, t.rows),
+                gather_index=arr(t.gather_index, t.logit_rows), attn_blocks=arr(t.attn_blocks, t.attn_block_count * 2),
+                page_table=arr(t.page_table, max_slots * max_pages).reshape(max_slots, max_pages))
+
+
+class Host:
+    """The host bookkeeping on its own (no GPU): page allocator, state units, table builder."""
+
+    def __init__(self, geometry, config, handle=None):
+        self.g, self.config = geometry, config
+        self._own = handle is None
+        if handle is None:
+            h = C.c_void_p()
+            cfg = config.c()
+            status = lib().spl_host_create(C.byref(geometry), C.byref(cfg), C.byref(h))
+            if status:
+                raise EngineError(status, "invalid host configuration")
+            handle = h
+        self.handle = handle
+        self.last = None
+
+    def __del__(self):
+        if getattr(self, "_own", False) and self.handle:
+            lib().spl_host_destroy(self.handle); self.handle = None
+
+    @property
+    def max_pages(self):
+        return lib().spl_host_max_pages(self.handle)
+
+    def build(self, rows):
+        t = _Tables()
+        arr = _rows_array(rows)
+        status = lib().spl_host_build_tables(self.handle, arr, len(rows), C.byref(t))
+        if status:
+            raise EngineError(status, lib().spl_host_last_error(self.handle).decode())
+        self.last = t
+        return _tables_dict(t, self.config.max_slots, self.max_pages)
+
+    def finish_step(self):
+        lib().spl_host_finish_step(self.handle, C.byref(self.last))
+
+    def reset_slot(self, slot):
+        return lib().spl_host_reset_slot(self.handle, slot)
+
+    def discard_verify(self, slot):
+        lib().spl_host_discard_verify(self.handle, slot)
+
+    def accept_verify(self, slot, rows, token_count):
+        status = lib().spl_host_accept_verify(self.handle, slot, rows, token_count)
+        if status:
+            raise EngineError(status, lib().spl_host_last_error(self.handle).decode())
+
+    def truncate(self, slot, token_count):
+        lib().spl_host_truncate(self.handle, slot, token_count)
+
+    def pages_held(self, slot):
+        return lib().spl_host_pages_held(self.handle, slot)
+
+    @property
+    def free_page_count(self):
+        return lib().spl_host_free_page_count(self.handle)
+
+    def slot_unit(self, slot):
+        return lib().spl_host_slot_unit(self.handle, slot)
+
+    def journal_pending(self, slot):
+        return lib().spl_host_journal_pending(self.handle, slot)
+
+
+def greedy_accept(argmax_ids, drafts):
+    """BatchScheduler.accept, greedy branch (BatchScheduler.swift:1583-1587)."""
+    ids = np.ascontiguousarray(argmax_ids, np.int32); d = np.ascontiguousarray(drafts, np.int32)
+    bonus = C.c_int32()
+    agreed = lib().spl_greedy_accept(_ptr(ids), _ptr(d), len(d), C.byref(bonus))
+    return agreed, bonus.value
+
+
+class Engine:
+    """Engine (Engine.swift:123): one per GPU, owned by one thread."""
+
+    def __init__(self, geometry, config=None):
+        self.g = geometry
+        self.config = config or EngineConfig()
+        h = C.c_void_p()
+        cfg = self.config.c()
+        status = lib().spl_engine_create(C.byref(geometry), C.byref(cfg), C.byref(h))
+        self.handle = h
+        if status:
+            message = lib().spl_last_error_string(h).decode() if h else ""
+            lib().spl_engine_destroy(h); self.handle = None
+            raise EngineError(status, message)
+        self.host = Host(geometry, self.config, handle=C.c_void_p(lib().spl_engine_host(self.handle)))
+        self.last_logit_rows = 0
+
+    def close(self):
+        if getattr(self, "handle", None):
+            lib().spl_engine_destroy(self.handle); self.handle = None
+
+    def __del__(self):
+        self.close()
+
+    def _check(self, status):
+        if status:
+            raise EngineError(status, lib().spl_last_error_string(self.handle).decode())
+
+    # ---- weights
+    def set_q4(self, layer, kind, packed, scales, biases):
+        packed = np.ascontiguousarray(packed, np.uint32); scales = np.ascontiguousarray(scales, np.uint16); biases = np.ascontiguousarray(biases, np.uint16)
+        self._check(lib().spl_weights_set_q4(self.handle, layer, Q4_KINDS.index(kind), packed.shape[0], packed.shape[1] * 8,
+                                              _ptr(packed), _ptr(scales), _ptr(biases)))
+
+    def set_vector(self, layer, kind, bits):
+        bits = np.ascontiguousarray(bits, np.uint16)
+        self._check(lib().spl_weights_set_vector(self.handle, layer, VEC_KINDS.index(kind), _ptr(bits), bits.size))
+
+    def synthesize_q4(self, seed):
+        self._check(lib().spl_weights_synthesize_q4(self.handle, seed))
+
+    def load_model(self, model):
+        """Copy every tensor of an object with .q4(layer, kind) / .vec(layer, kind) (the synthetic model of the tests)."""
+        for layer in range(self.g.layers):
+            full = layer % 4 == 3
+            for kind in (["q", "k", "v", "o"] if full else ["qkv", "z", "a", "b", "out"]) + ["gate", "up", "down"]:
+                self.set_q4(layer, kind, *model.q4(layer, kind))
+            for kind in ["input_norm", "post_norm"] + (["q_norm", "k_norm"] if full else ["conv", "a_log", "dt_bias", "gdn_norm"]):
+                self.set_vector(layer, kind, model.vec(layer, kind))
+        self.set_q4(-1, "embed", *model.q4(-1, "embed"))
+        self.set_q4(-1, "head", *model.q4(-1, "head"))
+        self.set_vector(-1, "final_norm", model.vec(-1, "final_norm"))
+
+    # ---- the step
+    def step(self, rows):
+        stats = _Stats()
+        arr = _rows_array(rows)
+        self._check(lib().spl_step(self.handle, arr, len(rows), C.byref(stats)))
+        self.last_logit_rows = sum(1 for r in rows if r.want_logits)
+        return StepStats(stats.rows, stats.launches, stats.gpu_seconds, stats.wall_seconds)
+
+    def step_tables(self, tables: _Tables, logit_rows):
+        stats = _Stats()
+        self._check(lib().spl_step_tables(self.handle, C.byref(tables), C.byref(stats)))
+        self.last_logit_rows = logit_rows
+        return StepStats(stats.rows, stats.launches, stats.gpu_seconds, stats.wall_seconds)
+
+    def logits(self, index):
+        out = np.empty(self.g.vocab, np.float32)
+        self._check(lib().spl_logits_row(self.handle, index, _ptr(out)))
+        return out
+
+    def all_logits(self):
+        return np.stack([self.logits(i) for i in range(self.last_logit_rows)]) if self.last_logit_rows else np.zeros((0, self.g.vocab), np.float32)
+
+    def argmax(self, vocab_limit=None):
+        ids = np.zeros(max(self.last_logit_rows, 1), np.int32)
+        self._check(lib().spl_argmax(self.handle, vocab_limit or self.g.vocab, _ptr(ids)))
+        return ids[:self.last_logit_rows]
+
+    # ---- slot lifecycle
+    def reset_slot(self, slot):
+        self._check(lib().spl_slot_reset(self.handle, slot))
+
+    def discard_verify(self, slot):
+        self._check(lib().spl_verify_discard(self.handle, slot))
+
+    def accept_verify(self, slot, rows, token_count):
+        self._check(lib().spl_verify_accept(self.handle, slot, rows, token_count))
+
+    def truncate(self, slot, token_count):
+        self._check(lib().spl_slot_truncate(self.handle, slot, token_count))
+
+    def pages_held(self, slot):
+        return lib().spl_pages_held(self.handle, slot)
+
+    @property
+    def free_page_count(self):
+        return lib().spl_free_page_count(self.handle)
+
+    @property
+    def memory(self):
+        m = _Memory()
+        self._check(lib().spl_memory(self.handle, C.byref(m)))
+        return {n: getattr(m, n) for n, _ in _Memory._fields_}
+
+    # ---- debugging and benchmarking
+    def debug_fill_kv(self, slot):
+        self._check(lib().spl_debug_fill_kv(self.handle, slot))
+
+    def debug_fill_state(self, slot, seed):
+        self._check(lib().spl_debug_fill_state(self.handle, slot, seed))
+
+    def debug_taps(self, enabled=True):
+        self._check(lib().spl_debug_taps(self.handle, int(enabled)))
+
+    def debug_profile(self, enabled=True):
+        self._check(lib().spl_debug_profile(self.handle, int(enabled)))
+
+    def profile_read(self):
+        out = {}
+        for klass, name in enumerate(["gemm_q4", "elementwise", "gdn", "attention", "other"]):
+            ms, n, b = C.c_double(), C.c_int64(), C.c_double()
+            self._check(lib().spl_debug_profile_read(self.handle, klass, C.byref(ms), C.byref(n), C.byref(b)))
+            out[name] = dict(ms=ms.value, launches=n.value, bytes=b.value)
+        return out
+
+    def debug_read(self, which, index, count, dtype=np.float32):
+        names = ["state", "conv", "journal", "k_codes", "v_codes", "k_scale", "v_scale", "hidden", "tap"]
+        out = np.empty(count, dtype)
+        self._check(lib().spl_debug_read(self.handle, names.index(which), index, _ptr(out), out.nbytes))
+        return out
+
+
+def gemm_q4(packed, scales, biases, activations, residual=None, device=0):
+    """One MLX affine-4 GEMM on host arrays through the C ABI (copies in, runs on the GPU, copies out)."""
+    packed = np.ascontiguousarray(packed, np.uint32); scales = np.ascontiguousarray(scales, np.uint16); biases = np.ascontiguousarray(biases, np.uint16)
+    a = np.ascontiguousarray(activations, np.float32)
+    n, k = packed.shape[0], packed.shape[1] * 8
+    out = np.empty((a.shape[0], n), np.float32)
+    res = None if residual is None else np.ascontiguousarray(residual, np.float32)
+    status = lib().spl_op_gemm_q4(device, _ptr(packed), _ptr(scales), _ptr(biases), n, k, _ptr(a), a.shape[0],
+                                  None if res is None else _ptr(res), _ptr(out))
+    if status:
+        raise EngineError(status, "spl_op_gemm_q4 failed")
+    return out
