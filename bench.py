@@ -1,0 +1,305 @@
+#!/usr/bin/env python
+"""Benchmark of the packed ragged step on B200.
+
+Workload (N = 1): the 27B-shape 4-bit model, 8 decoding sessions with seeded contexts of
+36K-42K tokens, each verifying an 8-token draft block: one 64-row packed step, KV cache int8,
+all rows accepted after each step as the reference's context benchmark does
+(Sources/SploshCLI/GenerateCommand.swift:375-469). Weights are seeded synthetic (quantised
+N(0, 0.02) stand-ins), KV pages hold pseudo-random codes with scale 0.01 and the recurrent state
+U(-0.5, 0.5), as the reference's Engine.debugFillKV and its tests fill them.
+
+With --gpus N each rank runs the same 8-session workload on its own GPU (sessions shard across
+GPUs with weights replicated and no collective on the data path): weak scaling.
+
+`--impl reference` times the CPU restatement of the step (oracle/) on the host cores instead.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+SESSIONS, BLOCK = 8, 8
+CONTEXT_LOW, CONTEXT_HIGH = 36 * 1024, 42 * 1024
+WEIGHT_SEED, TOKEN_SEED = 0x5EED6D17, 0xC0FFEE00
+
+
+def splitmix_at(seed, n):
+    mask = (1 << 64) - 1
+    z = (seed + (n + 1) * 0x9E3779B97F4A7C15) & mask
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & mask
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & mask
+    return z ^ (z >> 31)
+
+
+def contexts(rank):
+    return [CONTEXT_LOW + splitmix_at(TOKEN_SEED + rank, s) % (CONTEXT_HIGH - CONTEXT_LOW) for s in range(SESSIONS)]
+
+
+def weights_per_step(g):
+    """Weights streamed by one step (every block plus the head), and their bytes at 0.5625 B/weight."""
+    H, I = g.hidden, g.inter
+    C = (2 * g.gdn_key_heads + g.gdn_value_heads) * g.gdn_head_dim
+    VD, VH = g.gdn_value_heads * g.gdn_head_dim, g.gdn_value_heads
+    AD, KV = g.heads * g.head_dim, g.kv_heads * g.head_dim
+    mlp = 3 * H * I
+    linear = (C + VD + 2 * VH) * H + H * VD + mlp
+    full = (2 * AD + 2 * KV) * H + H * AD + mlp
+    n_full = g.layers // 4
+    total = (g.layers - n_full) * linear + n_full * full + g.vocab * H
+    return total, total * 0.5625
+
+
+def algorithmic_bytes(g, ctx, rows_per_session):
+    """HBM bytes one decode step must move: weights once, each session's KV once, its recurrent state in and out."""
+    _, wbytes = weights_per_step(g)
+    n_full = g.layers // 4
+    kv_per_token = n_full * 2 * g.kv_heads * (g.head_dim + 4)
+    kv = sum(ctx) * kv_per_token
+    state = len(ctx) * (g.layers - n_full) * g.gdn_value_heads * 128 * 128 * 4 * 2
+    return wbytes + kv + state, dict(weights=wbytes, kv=kv, state=state)
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons of one GPU while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.stop_flag = index, [], False
+        self.max_mhz = None
+
+    def run(self):
+        query = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+                "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        while not self.stop_flag:
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), f"--query-gpu={query}", "--format=csv,noheader,nounits"],
+                                     capture_output=True, text=True, timeout=5).stdout.strip().split(",")
+                self.samples.append([f.strip() for f in out])
+            except Exception:
+                pass
+            time.sleep(0.1)
+
+    def summary(self):
+        ok = [s for s in self.samples if len(s) == 6 and s[0].isdigit()]
+        if not ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in ok)]
+        return {"sm_mhz": float(np.median([int(s[0]) for s in ok])), "sm_max_mhz": float(ok[0][1]), "reasons": reasons}
+
+
+def measured_peak_gbs():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    return 6650.0, "fallback (6.65 TB/s, an earlier measurement on this pool)"
+
+
+class CpuSample:
+    """The oracle on a bounded sample of the same step: `layers` blocks of the 27B shape (3 gated-delta + 1 attention per 4)
+    and a head of `vocab` columns, 64 rows at `context` tokens of synthetic KV; extrapolated to 64 blocks and the full head."""
+
+    def __init__(self, rows_per_session=BLOCK, sessions=SESSIONS, context=2048, layers=4, vocab=32768):
+        from oracle import oracle as O
+        from oracle import tables as T
+        self.O, self.T = O, T
+        self.sessions, self.block, self.context, self.layers, self.vocab = sessions, rows_per_session, context, layers, vocab
+        g = O.b27_geometry().with_(layers=layers, vocab=vocab)
+        self.model = O.Model(g, WEIGHT_SEED)
+        pages = sessions * (context // 256 + 4)
+        self.host = T.Host(max_slots=sessions, max_rows=sessions * rows_per_session, kv_pages=pages, max_context=context + 1024,
+                           vocab=vocab, kv_heads=g.kv_heads, last_layer_full=True)
+        self.engine = O.Engine(self.model, sessions, pages, self.host.max_pages, self.host.state_units)
+        # Allocate each slot's pages with a throwaway row at the end of its context, then fill KV and state.
+        tb = self.host.build([T.Row(s, 1000, context - 1, False) for s in range(sessions)])
+        self.engine.step(tb); self.host.finish_step(tb)
+        rng = np.random.default_rng(1)
+        for index in range(layers // 4):
+            for which in ("k_codes", "v_codes"):
+                buf = self.engine.buffer(which, index); buf[:] = rng.integers(-127, 128, buf.size, dtype=np.int8)
+            for which in ("k_scale", "v_scale"):
+                self.engine.buffer(which, index)[:] = 0.01
+        for index in range(layers - layers // 4):
+            st = self.engine.buffer("state", index); st[:] = rng.uniform(-0.5, 0.5, st.size).astype(np.float32)
+        self.position = context
+        self.cores = O.lib().orc_threads()
+        self.sample = (f"{layers} blocks (3 gated-delta : 1 attention) of the 27B shape + a {vocab}-column head, {sessions * rows_per_session} rows, "
+                       f"{sessions} sessions at {context} tokens of synthetic KV; time = blocks x{64 / layers:g} + head x{248320 / vocab:.2f}")
+
+    def step(self):
+        """One 64-row verify step; returns the extrapolated seconds of a full 64-block step."""
+        T = self.T
+        rows = [T.Row(s, int(splitmix_at(TOKEN_SEED, s * 100 + i + self.position) % self.vocab), self.position + i, True, True)
+                for s in range(self.sessions) for i in range(self.block)]
+        tb = self.host.build(rows)
+        t0 = time.perf_counter(); self.engine.step(tb, max_layers=self.layers); t_blocks = time.perf_counter() - t0
+        self.host.finish_step(tb)
+        for s in range(self.sessions):
+            self.host.accept_verify(s, self.block, self.position + self.block)
+        self.position += self.block
+        # The head on the same rows: final norm + head GEMM = a step of zero blocks is not expressible, so time it as a bare GEMM.
+        packed, scales, biases = self.model.q4(-1, "head")
+        a = np.zeros((self.sessions * self.block, 5120), np.float32) + 0.5
+        t0 = time.perf_counter(); self.O.gemm_q4(packed, scales, biases, a); t_head = time.perf_counter() - t0
+        return t_blocks * (64 / self.layers) + t_head * (248320 / self.vocab)
+
+
+def cpu_baseline(steps=1):
+    sample = CpuSample()
+    seconds = float(np.mean([sample.step() for _ in range(steps)]))
+    return SESSIONS * BLOCK / seconds, sample.cores, sample.sample
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the CPU restatement of the step on all host threads, rank 0 only."""
+    if rank != 0:
+        return
+    sample = CpuSample()
+    for _ in range(max(args.warmup, 0)):
+        sample.step()
+    t0 = time.perf_counter()
+    seconds = [sample.step() for _ in range(args.steps)]
+    value = SESSIONS * BLOCK / float(np.mean(seconds))
+    line = {"metric": "packed_step_tok_per_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1000.0 * float(np.mean(seconds)), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 x int4 -> fp32 (int8 KV, fp32 state)", "data": "synthetic", "impl": "reference",
+            "config": {"workload": "27B-shape MLX 4-bit g64, 8 sessions x 8-row verify blocks = 64 rows per step (bounded sample, extrapolated)",
+                       "parallelism": "host cores", "sample_wall_seconds": time.perf_counter() - t0},
+            "cpu_baseline": {"value": value, "unit": "tok/s", "cores": sample.cores, "kind": "port", "sample": sample.sample},
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="splosh_b200")
+    ap.add_argument("--layers", type=int, default=64, help="blocks of the 27B shape (64 is the benchmark; fewer for ncu captures)")
+    ap.add_argument("--context-scale", type=float, default=1.0, help="scales the session contexts (1.0 is the benchmark)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+    args.warmup = max(args.warmup, 3)
+
+    import torch
+    import splosh_b200 as S
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+
+    g = S.b27_geometry(layers=args.layers)
+    ctx = [int(c * args.context_scale) for c in contexts(rank)]
+    steps_total = args.warmup + 2 * args.steps + 2
+    pages = sum((c + BLOCK * steps_total) // 256 + 2 for c in ctx)
+    cfg = S.EngineConfig(max_slots=SESSIONS, max_rows=SESSIONS * BLOCK, kv_pages=pages, max_context=max(ctx) + BLOCK * steps_total + 256, device=local)
+    engine = S.Engine(g, cfg)
+    from splosh_b200 import synthetic
+    synthetic.load_vectors(engine, WEIGHT_SEED)
+    engine.synthesize_q4(WEIGHT_SEED)
+
+    # Contexts: one throwaway row at the end of each allocates its pages; then KV and state are filled.
+    engine.step([S.EngineRow(s, 1000, ctx[s] - 1, False) for s in range(SESSIONS)])
+    for s in range(SESSIONS):
+        engine.debug_fill_kv(s)
+        engine.debug_fill_state(s, 0x5747 + s)
+    position = list(ctx)
+
+    def rows_for(step):
+        return [S.EngineRow(s, int(splitmix_at(TOKEN_SEED + rank, 1000003 * step + 97 * s + i) % g.vocab), position[s] + i, True, True)
+                for s in range(SESSIONS) for i in range(BLOCK)]
+
+    def one_step(step, read_ids):
+        stats = engine.step(rows_for(step))
+        ids = engine.argmax(248077 if g.vocab == 248320 else g.vocab) if read_ids else None
+        for s in range(SESSIONS):
+            position[s] += BLOCK
+            engine.accept_verify(s, BLOCK, position[s])
+        return stats, ids
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    step_index = 0
+    for _ in range(args.warmup):
+        one_step(step_index, True); step_index += 1
+
+    sampler = ClockSampler(local); sampler.start()
+    # Timed region 1: end to end through the C ABI with host rows in and token ids out.
+    barrier(); t0 = time.perf_counter()
+    gpu_seconds, launches = 0.0, 0
+    for _ in range(args.steps):
+        stats, ids = one_step(step_index, True); step_index += 1
+        gpu_seconds += stats.gpu_seconds; launches += stats.launches
+    barrier(); wall = time.perf_counter() - t0
+    sampler.stop_flag = True; sampler.join()
+    clocks = sampler.summary()
+
+    times = torch.tensor([wall, gpu_seconds], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    wall_max, gpu_max = float(times[0]), float(times[1])
+    rows_per_step = SESSIONS * BLOCK
+    total_rows = world * rows_per_step * args.steps
+
+    # Profiled pass (events around every launch): the dominant kernel's share and achieved bandwidth.
+    engine.debug_profile(True)
+    for _ in range(args.steps):
+        one_step(step_index, False); step_index += 1
+    prof = engine.profile_read()
+    engine.debug_profile(False)
+
+    if rank == 0:
+        peak, peak_source = measured_peak_gbs()
+        gemm = prof["gemm_q4"]
+        gemm_gbs = gemm["bytes"] / (gemm["ms"] * 1e-3) / 1e9 if gemm["ms"] > 0 else 0.0
+        step_bytes, parts = algorithmic_bytes(g, ctx, BLOCK)
+        step_ms = 1000.0 * gpu_max / args.steps
+        tables_bytes = (rows_per_step * 5 + SESSIONS * 5 + rows_per_step + rows_per_step // 4 + SESSIONS * engine.host.max_pages) * 4
+        line = {
+            "metric": "packed_step_tok_per_s", "value": total_rows / gpu_max, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16 x int4 -> fp32 (int8 KV, fp32 state)", "data": "synthetic",
+            "config": {"workload": f"27B-shape ({g.layers} blocks) MLX 4-bit g64, 8 sessions x 8-row verify blocks = 64 rows per step, contexts "
+                                   f"{min(ctx)}-{max(ctx)} tokens, int8 paged KV, all rows accepted each step", "sessions_per_gpu": SESSIONS,
+                       "rows_per_step": rows_per_step, "parallelism": f"sessions sharded, {world} replica(s)",
+                       "l2": "inputs larger than L2: 14.4 GB of weights and the KV pool stream every step"},
+            "e2e": {"value": total_rows / wall_max, "unit": "tok/s", "h2d_bytes_per_step": tables_bytes, "d2h_bytes_per_step": rows_per_step * 4},
+            "gpu_launches": launches,
+            "clocks": clocks,
+            "step": {"algorithmic_gb": step_bytes / 1e9, "weights_gb": parts["weights"] / 1e9, "kv_gb": parts["kv"] / 1e9, "state_gb": parts["state"] / 1e9,
+                     "hbm_gbs": step_bytes / (step_ms * 1e-3) / 1e9, "frac_of_peak": step_bytes / (step_ms * 1e-3) / 1e9 / peak,
+                     "class_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
+                     "class_launches_per_step": {k: v["launches"] / args.steps for k, v in prof.items()}},
+            "roofline": {"kernel": "spl_gemm_q4_kernel", "bound": "hbm", "achieved": gemm_gbs, "peak": peak, "unit": "GB/s",
+                         "frac": gemm_gbs / peak, "traffic": None, "peak_source": peak_source,
+                         "per_launch": {"algorithmic_bytes": gemm["bytes"] / max(gemm["launches"], 1), "ms": gemm["ms"] / max(gemm["launches"], 1)}},
+        }
+        if not args.no_cpu_baseline and world == 1:
+            value, cores, sample = cpu_baseline()
+            line["cpu_baseline"] = {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    engine.close()
+    if dist is not None:
+        dist.barrier(); dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

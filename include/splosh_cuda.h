@@ -171,7 +171,9 @@ spl_status spl_debug_fill_state(spl_engine *engine, int32_t slot, uint64_t seed)
 /* Raw device buffers for tests. which: 0 state, 1 conv history, 2 journal (index = gated-delta
  * layer ordinal); 3 k codes, 4 v codes, 5 k scale, 6 v scale (index = attention layer ordinal);
  * 7 residual stream after the last step [rows][hidden]; 8 residual stream after block `index`
- * (needs spl_debug_taps(engine, 1) before the step). Layouts: state [slot][value head][value j][key i];
+ * (needs spl_debug_taps(engine, 1) before the step); 9 the last block's fused input projection
+ * [rows][ld] fp32; 10 its mixer output [rows][ld] bf16; 11 its queries [rows][heads][head_dim] fp16;
+ * 12 its attention partials [rows][heads][spans][head_dim + 2] fp32. Layouts: state [slot][value head][value j][key i];
  * conv [unit][channel][3] oldest first; journal [slot][16][value head][260];
  * codes [page][kv head][256][head_dim] (V codes are stored [page][kv head][head_dim][256]). */
 spl_status spl_debug_read(spl_engine *engine, int32_t which, int32_t index, void *dst, size_t bytes);

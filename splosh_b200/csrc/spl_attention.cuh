@@ -44,7 +44,7 @@ spl_attn_prepare_kernel(const float *__restrict__ proj, const uint16_t *__restri
     ss = spl_warp_sum(ss);
     if (lane == 0) red[warp] = ss;
     __syncthreads();
-    const float inv = rsqrtf((red[0] + red[1] + red[2] + red[3]) / float(hd) + p.eps);
+    const float inv = 1.0f / sqrtf((red[0] + red[1] + red[2] + red[3]) / float(hd) + p.eps);
     for (int i = tid; i < hd; i += 128) xs[i] = x[i] * inv * spl_bf16_to_float(w[i]);
     __syncthreads();
     const uint32_t position = row_pos[row];
@@ -116,7 +116,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                      const uint32_t *__restrict__ row_pos, const uint32_t *__restrict__ page_table, const int8_t *__restrict__ k_codes,
                      const float *__restrict__ k_scale, const int8_t *__restrict__ v_codes, const float *__restrict__ v_scale,
                      float *partials, SplAttnParams p) {
-    constexpr int M = 16 * MT, QS = HD + 4, NQ = HD / 64, NV = HD / 32;
+    constexpr int M = 16 * MT, QS = HD + 4, NQ = HD / 64, NVW = HD / 32;   // NVW: n8 tiles of this warp's HD / 4 channels
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __half *Qs = reinterpret_cast<__half *>(smem_raw);                        // [M][QS]
     __half *Ps = Qs + M * QS;                                                 // [M][SPL_ATTN_PS]
@@ -151,9 +151,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
             limit[mt][hr] = (rb < int(count) && int(r0) + rb < p.live) ? first_pos + rb + 1 : 0u;
             ref[mt][hr] = -INFINITY; total[mt][hr] = 0.0f;
         }
-    float acc[MT][NV / 4 * 1][4] = {};        // value product: this warp's HD / 4 channels = NV / 4 n-tiles
-    static_assert(NV % 4 == 0, "head_dim must be a multiple of 128");
-    constexpr int NVW = NV / 4;
+    float acc[MT][NVW][4] = {};               // value product: this warp's HD / 4 channels
     __syncthreads();
 
     for (int pg = first_page; pg < last_page; ++pg) {

@@ -45,7 +45,7 @@ spl_rmsnorm_kernel(const float *__restrict__ input, int in_ld, const uint16_t *_
     float total = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) total += part[i];
-    const float inv = rsqrtf(total / float(dim) + eps);
+    const float inv = 1.0f / sqrtf(total / float(dim) + eps);
     for (int base = 0; base < dim; base += 1024) {
         const int i = base + threadIdx.x * 4;
         float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;

@@ -779,6 +779,10 @@ spl_status spl_debug_read(spl_engine *e, int32_t which, int32_t index, void *dst
     case 5: pick(e->k_scale, size_t(e->c.kv_pages) * page_vecs * 4); break;
     case 6: pick(e->v_scale, size_t(e->c.kv_pages) * page_vecs * 4); break;
     case 7: src = e->h; have = size_t(e->last_rows) * e->g.hidden * 4; break;
+    case 9: src = e->proj; have = size_t(e->last_rows) * e->proj_ld * 4; break;
+    case 10: src = e->core; have = size_t(e->last_rows) * e->core_ld * 2; break;
+    case 11: src = e->q; have = size_t(e->last_rows) * e->g.heads * e->g.head_dim * 2; break;
+    case 12: src = e->attn_partials; have = e->attn_partial_floats * 4; break;
     case 8: if (e->taps && index >= 0 && index < e->g.layers) { src = e->taps + size_t(index) * e->c.max_rows * e->g.hidden; have = size_t(e->last_rows) * e->g.hidden * 4; } break;
     }
     if (!src || bytes > have) return e->fail(SPL_ERR_INVALID_ARGUMENT, "debug read outside the buffer");

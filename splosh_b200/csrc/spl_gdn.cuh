@@ -122,8 +122,8 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
             const float kk = spl_warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
             if (lane == 0) {
                 const size_t row = start + base + tt;
-                scal[tt][0] = rsqrtf(qq + 1e-6f) * rsqrtf(float(D));
-                scal[tt][1] = rsqrtf(kk + 1e-6f);
+                scal[tt][0] = (1.0f / sqrtf(qq + 1e-6f)) * (1.0f / sqrtf(float(D)));
+                scal[tt][1] = 1.0f / sqrtf(kk + 1e-6f);
                 const float x = proj[row * p.proj_ld + p.a_offset + h] + bias;
                 const float softplus = x > 20.0f ? x : logf(1.0f + expf(x));
                 scal[tt][2] = expf(neg_a * softplus);
@@ -164,7 +164,7 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
         for (int tt = warp; tt < count; tt += 8) {
             const size_t row = start + base + tt;
             const float4 ov = *reinterpret_cast<const float4 *>(&o_s[tt][lane * 4]);
-            const float inv = rsqrtf(spl_warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w) / float(D) + p.eps);
+            const float inv = 1.0f / sqrtf(spl_warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w) / float(D) + p.eps);
             const float4 z = *reinterpret_cast<const float4 *>(proj + row * p.proj_ld + p.z_offset + h * D + lane * 4);
             const uint2 w = *reinterpret_cast<const uint2 *>(norm_weight + lane * 4);
             const float r0 = spl_bf16_to_float(uint16_t(w.x)) * ov.x * inv * spl_silu_exact(z.x);

@@ -1,0 +1,61 @@
+"""The MLX affine-4 dequant-GEMM through the C ABI (spl_op_gemm_q4, host buffers in and out)
+against the CPU oracle on the same seeded inputs.
+
+Tolerance: both sides form, per 64-group, the exact dot of bf16 activations with 4-bit codes and
+add dot * scale + sum * bias; they differ only in fp32 summation order, so |diff| <= 4e-6 of the
+largest output (the reference allows relErr 1e-2 for its kernel, GemmOracleTests.swift:165)."""
+import numpy as np
+import pytest
+
+import splosh_b200 as S
+
+pytestmark = pytest.mark.gpu
+TOL = 4e-6
+
+
+def case(oracle, n, k, rows, seed, residual=True):
+    rng = np.random.default_rng(seed)
+    w = rng.normal(0, 0.02, (n, k)).astype(np.float32)
+    packed, scales, biases = oracle.quantize_mlx4(w)
+    a = rng.normal(0, 1, (rows, k)).astype(np.float32)
+    res = rng.normal(0, 1, (rows, n)).astype(np.float32) if residual else None
+    want = oracle.gemm_q4(packed, scales, biases, a, res)
+    got = S.gemm_q4(packed, scales, biases, a, res)
+    assert not np.isnan(got).any()
+    assert np.abs(got - want).max() <= TOL * np.abs(want).max(), (n, k, rows)
+
+
+@pytest.mark.parametrize("rows", [1, 2, 3, 7, 8, 9, 16, 17, 31, 33, 48, 64, 65, 127, 130])
+def test_every_row_tier_and_ragged_row_counts(oracle, rows):
+    case(oracle, 1024, 1024, rows, rows)
+
+
+@pytest.mark.parametrize("n,k", [(48, 1024), (8, 1024), (16, 256), (3104, 1024), (5632, 1024), (1024, 2816), (24, 5120), (1000, 512)])
+def test_output_widths_that_do_not_fill_a_tile(oracle, n, k):
+    """48- and 8-row projections (the a and b projections), widths that are not a multiple of 16."""
+    case(oracle, n, k, 20, n + k, residual=n % 2 == 0)
+
+
+@pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408), (10240, 5120), (5120, 6144)])
+def test_27b_shapes_at_64_rows(oracle, n, k):
+    case(oracle, n, k, 64, 7)
+
+
+def test_linearity_at_full_size(oracle):
+    """A size-independent property: GEMM(a1 + a2) = GEMM(a1) + GEMM(a2) for activations exactly representable in bf16."""
+    rng = np.random.default_rng(11)
+    n, k, rows = 34816, 5120, 64
+    packed = rng.integers(0, 2 ** 32, (n, k // 8), dtype=np.uint64).astype(np.uint32)
+    scales = np.full((n, k // 64), 0x3C00, np.uint16)       # bf16 2^-7
+    biases = np.full((n, k // 64), 0xBD80, np.uint16)       # bf16 -2^-4
+    a1 = rng.integers(-8, 9, (rows, k)).astype(np.float32); a2 = rng.integers(-8, 9, (rows, k)).astype(np.float32)
+    y1, y2, y12 = (S.gemm_q4(packed, scales, biases, a) for a in (a1, a2, a1 + a2))
+    assert np.abs(y12 - (y1 + y2)).max() <= 1e-5 * np.abs(y12).max()
+
+
+def test_zero_rows_and_bad_shapes_are_rejected():
+    z16 = np.zeros((16, 32), np.uint32); s = np.zeros((16, 4), np.uint16)
+    with pytest.raises(S.EngineError):
+        S.gemm_q4(z16, s, s, np.zeros((0, 256), np.float32))
+    with pytest.raises(S.EngineError):
+        S.gemm_q4(np.zeros((16, 8), np.uint32), np.zeros((16, 1), np.uint16), np.zeros((16, 1), np.uint16), np.zeros((1, 64), np.float32))
