@@ -184,6 +184,28 @@ spl_status spl_debug_profile(spl_engine *engine, int32_t enabled);
  * Returns accumulated milliseconds and launches since the last reset (reset = enabling). */
 spl_status spl_debug_profile_read(spl_engine *engine, int32_t klass, double *milliseconds, int64_t *launches, double *bytes);
 
+/* ---- A GEMM for callers that must not allocate ---------------------------------------------
+ * No counterpart in the reference (Metal hands out buffers freely; nothing there is barred from
+ * allocating). Some CUDA hosts are: one that gave the whole GPU to its own pool at start-up and has
+ * nothing left for cudaMalloc to hand out, or a serving loop that bans allocator calls on its hot
+ * path because cudaMalloc and cudaFree synchronise the whole device.
+ * This entry point runs out[r][:] = GEMM(weights, activations[r][:]) (+ residual) on one of the
+ * engine's resident weights and calls no cudaMalloc, cudaFree or other allocating routine: the
+ * bf16 operand, its per-64 sums and the split-K partial sums live in a static device array of
+ * about 10.2 MiB that every GPU loading the library holds until exit.
+ *   - all three buffers are DEVICE pointers: activations fp32 [rows][inner], residual (may be
+ *     null, may alias out) and out fp32 [rows][ld], ld = the tensor's columns rounded up to 16;
+ *   - rows must be 1..64 and the tensor's inner dimension at most 17408, else SPL_ERR_INVALID_ROWS
+ *     / SPL_ERR_INVALID_ARGUMENT with the reason in spl_last_error_string;
+ *   - the first call on a device looks up the array's address (cudaGetSymbolAddress); make that
+ *     call before any stream capture begins;
+ *   - work is queued on `stream` (a cudaStream_t, null for the default stream) and not waited for;
+ *   - every call on a device shares the one array: two calls whose kernels can overlap on the GPU
+ *     (different streams, no dependency between them) race on it. */
+enum { SPL_RESIDENT_IN_PROJ = 0, SPL_RESIDENT_OUT_PROJ, SPL_RESIDENT_GATE_UP, SPL_RESIDENT_DOWN, SPL_RESIDENT_HEAD };
+spl_status spl_gemm_q4_static(spl_engine *engine, int32_t layer, int32_t which, const float *device_activations, int32_t rows,
+                              const float *device_residual, float *device_out, void *stream);
+
 /* ---- Single operators on host buffers (tests, micro-benchmarks) --------------------------- */
 /* Engine.gemm (Engine.swift:1651-1806) for one MLX affine-4 tensor: out[r][n] = sum_k
  * bf16(a[r][k]) * w[n][k] (+ residual[r][n]). Allocates, copies in, runs, copies out. */

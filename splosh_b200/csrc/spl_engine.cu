@@ -790,6 +790,108 @@ spl_status spl_debug_read(spl_engine *e, int32_t which, int32_t index, void *dst
     return SPL_OK;
 }
 
+}  // extern "C"
+
+// ---- A GEMM that allocates nothing ---------------------------------------------------------
+//
+// For callers that may not allocate device memory: a host that handed the whole GPU to its own
+// pool at start-up, or a serving loop that bans allocator calls on its hot path because
+// cudaMalloc and cudaFree synchronise the whole device. The scratch the ordinary path takes from the engine's buffers (the bf16 operand with its
+// per-64 sums, and the split-K partial sums) lives here in one file-scope device array, so every
+// GPU that loads the library holds SPL_STATIC_BYTES (about 10.2 MiB) until the process exits.
+#define SPL_STATIC_ROWS 64
+#define SPL_STATIC_INNER 17408
+#define SPL_STATIC_OPERAND_BYTES (SPL_STATIC_ROWS * SPL_STATIC_INNER * 2)
+#define SPL_STATIC_SUMS_BYTES (SPL_STATIC_ROWS * (SPL_STATIC_INNER / 64) * 4)
+#define SPL_STATIC_PARTIAL_BYTES (8u << 20)
+#define SPL_STATIC_BYTES (SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES + SPL_STATIC_PARTIAL_BYTES)
+static __device__ __align__(256) unsigned char spl_static_scratch[SPL_STATIC_BYTES];
+// The array's address on each device, asked for once per device. The symbol itself is only a
+// host-side handle: a kernel must be given what cudaGetSymbolAddress returns.
+static void *spl_static_address[64] = {};
+
+// fp32 rows -> the bf16 operand and its per-64 sums (Sources/Shaders/engine_na.metal:42-57).
+// Grid (rows), 256 threads.
+__global__ void __launch_bounds__(256)
+spl_operand_kernel(const float *__restrict__ input, __nv_bfloat16 *out, float *sums, int inner) {
+    const int row = blockIdx.x;
+    for (int base = 0; base < inner; base += 1024) {
+        const int i = base + threadIdx.x * 4;
+        float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
+        if (i < inner) {
+            const float4 v = *reinterpret_cast<const float4 *>(input + size_t(row) * inner + i);
+            const uint16_t b0 = spl_float_to_bf16(v.x), b1 = spl_float_to_bf16(v.y), b2 = spl_float_to_bf16(v.z), b3 = spl_float_to_bf16(v.w);
+            *reinterpret_cast<uint2 *>(out + size_t(row) * inner + i) = make_uint2(uint32_t(b0) | (uint32_t(b1) << 16), uint32_t(b2) | (uint32_t(b3) << 16));
+            r0 = spl_bf16_to_float(b0); r1 = spl_bf16_to_float(b1); r2 = spl_bf16_to_float(b2); r3 = spl_bf16_to_float(b3);
+        }
+        float gsum = (r0 + r1) + (r2 + r3);
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o);
+        if (i < inner && (threadIdx.x & 15) == 0) sums[size_t(row) * (inner / 64) + i / 64] = gsum;
+    }
+}
+
+template <int RT>
+static void launch_gemm_static(const SplQ4Dev &w, const __nv_bfloat16 *act, const float *sums, float *partials, float *out, int out_ld,
+                               const float *residual, int rows, cudaStream_t stream) {
+    const int groups = w.k / 64, total_chunks = groups / 4;
+    const int tiles = (w.n16 + SPL_GEMM_WARPS - 1) / SPL_GEMM_WARPS;
+    int splits = std::max(1, std::min(296 / std::max(tiles, 1), total_chunks / 2));
+    while (splits > 1 && size_t(splits) * RT * 8 * out_ld * 4 > SPL_STATIC_PARTIAL_BYTES) --splits;
+    const int cps = (total_chunks + splits - 1) / splits;
+    splits = (total_chunks + cps - 1) / cps;
+    const size_t smem = size_t(2) * RT * 8 * SPL_GEMM_LDS * sizeof(__nv_bfloat16) + size_t(2) * RT * 8 * 4 * sizeof(float);
+    cudaFuncSetAttribute(spl_gemm_q4_kernel<RT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+    spl_gemm_q4_kernel<RT, 1><<<dim3(tiles, splits), SPL_GEMM_WARPS * 32, smem, stream>>>(
+        w.codes, w.sb, act, sums, w.k, out, out_ld, residual, partials, rows, w.n16, groups, cps);
+    if (splits > 1) {
+        const size_t total = size_t(rows) * out_ld / 4;
+        spl_gemm_reduce_kernel<<<int(std::min<size_t>((total + 255) / 256, 2048)), 256, 0, stream>>>(partials, splits, RT * 8, rows, out_ld, residual, out);
+    }
+}
+
+extern "C" spl_status spl_gemm_q4_static(spl_engine *e, int32_t layer, int32_t which, const float *device_activations, int32_t rows,
+                                         const float *device_residual, float *device_out, void *stream_handle) {
+    if (!e || !device_activations || !device_out) return SPL_ERR_INVALID_ARGUMENT;
+    const SplQ4Dev *w = nullptr;
+    if (layer < 0) { if (which == SPL_RESIDENT_HEAD) w = &e->head; }
+    else if (layer < e->g.layers) {
+        const LayerWeights &L = e->layers[layer];
+        w = which == SPL_RESIDENT_IN_PROJ ? &L.in_proj : which == SPL_RESIDENT_OUT_PROJ ? &L.out_proj : which == SPL_RESIDENT_GATE_UP ? &L.gate_up
+          : which == SPL_RESIDENT_DOWN ? &L.down : nullptr;
+    }
+    if (!w || !w->codes) return e->fail(SPL_ERR_INVALID_ARGUMENT, "no such resident tensor");
+    if (rows < 1 || rows > SPL_STATIC_ROWS)
+        return e->fail(SPL_ERR_INVALID_ROWS, "spl_gemm_q4_static: rows must be 1..64 (the static scratch holds a 64-row operand)");
+    if (w->k > SPL_STATIC_INNER)
+        return e->fail(SPL_ERR_INVALID_ARGUMENT, "spl_gemm_q4_static: contraction longer than 17408 does not fit the static scratch");
+    SPL_CUDA(cudaSetDevice(e->device));
+    if (e->device >= 64) return e->fail(SPL_ERR_UNSUPPORTED_DEVICE, "spl_gemm_q4_static: device ordinal beyond 63");
+    if (!spl_static_address[e->device]) {
+        // First call on this device: resolve the array's device address (this device is current).
+        void *address = nullptr;
+        SPL_CUDA(cudaGetSymbolAddress(&address, spl_static_scratch));
+        spl_static_address[e->device] = address;
+    }
+    unsigned char *base = static_cast<unsigned char *>(spl_static_address[e->device]);
+    __nv_bfloat16 *operand = reinterpret_cast<__nv_bfloat16 *>(base);
+    float *sums = reinterpret_cast<float *>(base + SPL_STATIC_OPERAND_BYTES);
+    float *partials = reinterpret_cast<float *>(base + SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES);
+    cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+    const int ld = w->n16 * 16;
+    // Nothing in the scratch has to start at zero: the operand and sums of the rows in use are
+    // rewritten here, rows past `rows` are never read back, and every partial sum that the
+    // reduction reads was written by this call's GEMM.
+    spl_operand_kernel<<<rows, 256, 0, stream>>>(device_activations, operand, sums, w->k);
+    if (rows <= 8) launch_gemm_static<1>(*w, operand, sums, partials, device_out, ld, device_residual, rows, stream);
+    else if (rows <= 16) launch_gemm_static<2>(*w, operand, sums, partials, device_out, ld, device_residual, rows, stream);
+    else if (rows <= 32) launch_gemm_static<4>(*w, operand, sums, partials, device_out, ld, device_residual, rows, stream);
+    else launch_gemm_static<8>(*w, operand, sums, partials, device_out, ld, device_residual, rows, stream);
+    return check_launch(e, "spl_gemm_q4_static");
+}
+
+extern "C" {
+
 // One GEMM on host buffers: the whole path a caller without an engine sees.
 spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t *scales, const uint16_t *biases,
                           int32_t n, int32_t k, const float *activations, int32_t rows, const float *residual, float *out) {

@@ -164,6 +164,7 @@ def lib():
             "spl_debug_profile": (i32, [vp, i32]),
             "spl_debug_profile_read": (i32, [vp, i32, C.POINTER(C.c_double), C.POINTER(C.c_int64), C.POINTER(C.c_double)]),
             "spl_op_gemm_q4": (i32, [i32, vp, vp, vp, i32, i32, vp, i32, vp, vp]),
+            "spl_gemm_q4_static": (i32, [vp, i32, i32, vp, i32, vp, vp, vp]),
         }
         for name, (res, args) in sig.items():
             fn = getattr(L, name)
@@ -402,6 +403,19 @@ class Engine:
         out = np.empty(count, dtype)
         self._check(lib().spl_debug_read(self.handle, names.index(which), index, _ptr(out), out.nbytes))
         return out
+
+
+RESIDENT = ["in_proj", "out_proj", "gate_up", "down", "head"]
+
+
+def gemm_q4_static(engine, layer, which, device_activations, rows, device_residual, device_out, stream=None):
+    """The allocation-free GEMM on one of the engine's resident weights. The three buffer arguments are raw device
+    addresses (ints); nothing is allocated, copied or waited for."""
+    status = lib().spl_gemm_q4_static(engine.handle, layer, RESIDENT.index(which), C.c_void_p(device_activations), rows,
+                                      C.c_void_p(device_residual) if device_residual else None, C.c_void_p(device_out),
+                                      C.c_void_p(stream) if stream else None)
+    if status:
+        raise EngineError(status, lib().spl_last_error_string(engine.handle).decode())
 
 
 def gemm_q4(packed, scales, biases, activations, residual=None, device=0):
