@@ -288,7 +288,7 @@ def main():
                      "hbm_gbs": step_bytes / (step_ms * 1e-3) / 1e9, "frac_of_peak": step_bytes / (step_ms * 1e-3) / 1e9 / peak,
                      "class_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
                      "class_launches_per_step": {k: v["launches"] / args.steps for k, v in prof.items()}},
-            "roofline": {"kernel": "spl_gemm_q4_kernel", "bound": "hbm", "achieved": gemm_gbs, "peak": peak, "unit": "GB/s",
+            "roofline": {"kernel": "spl_gemm_q4_tc_kernel", "bound": "hbm", "achieved": gemm_gbs, "peak": peak, "unit": "GB/s",
                          "frac": gemm_gbs / peak, "traffic": None, "peak_source": peak_source,
                          "per_launch": {"algorithmic_bytes": gemm["bytes"] / max(gemm["launches"], 1), "ms": gemm["ms"] / max(gemm["launches"], 1)}},
         }

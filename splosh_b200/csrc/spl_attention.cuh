@@ -14,6 +14,7 @@
 // code = clamp(rint(x / scale), -127, 127) (engine_na.metal:2084-2093).
 #pragma once
 #include "spl_common.cuh"
+#include "spl_gemm_tc.cuh"
 
 struct SplAttnParams {
     int rows, live, heads, kv_heads, head_dim, rotary, max_pages;
@@ -303,8 +304,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
 
 // Merge span partials by log-sum-exp, apply the sigmoid output gate, round to the bf16 operand of
 // the output projection and emit its per-64 sums (engine.metal:2218-2255). Grid (heads, live rows), head_dim threads.
-__global__ void spl_attn_merge_kernel(const float *__restrict__ partials, const float *__restrict__ proj, __nv_bfloat16 *core, float *core_sums,
-                                      SplAttnParams p) {
+__global__ void spl_attn_merge_kernel(const float *__restrict__ partials, const float *__restrict__ proj, SplOperand core, SplAttnParams p) {
     __shared__ float warp_sums[8];
     const int head = blockIdx.x, row = blockIdx.y, j = threadIdx.x, hd = p.head_dim, record = hd + 2;
     const float *base = partials + (size_t(row) * p.heads + head) * p.spans * record;
@@ -317,9 +317,9 @@ __global__ void spl_attn_merge_kernel(const float *__restrict__ partials, const 
     }
     const float gate = proj[size_t(row) * p.proj_ld + head * 2 * hd + hd + j];
     const uint16_t bits = spl_float_to_bf16((acc / sum) * spl_sigmoid(gate));
-    reinterpret_cast<uint16_t *>(core)[(size_t(row) * p.heads + head) * hd + j] = bits;
+    reinterpret_cast<__half *>(core.values)[core.at(row, head * hd + j)] = __float2half_rn(spl_bf16_to_float(bits));
     const float wsum = spl_warp_sum(spl_bf16_to_float(bits));
     if ((j & 31) == 0) warp_sums[j >> 5] = wsum;
     __syncthreads();
-    if ((j & 63) == 0) core_sums[size_t(row) * (p.heads * hd / 64) + (head * hd + j) / 64] = warp_sums[j >> 5] + warp_sums[(j >> 5) + 1];
+    if ((j & 63) == 0) core.put_sum(row, (head * hd + j) / 64, warp_sums[j >> 5] + warp_sums[(j >> 5) + 1]);
 }

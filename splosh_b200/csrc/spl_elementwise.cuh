@@ -1,6 +1,7 @@
 // spl_elementwise.cuh — embedding, RMSNorm, SiLU gate, row gather and arg-max.
 #pragma once
 #include "spl_common.cuh"
+#include "spl_gemm_tc.cuh"
 
 // Embedding: gather a q4 row per token and dequantise it, h = scale * nibble + bias in fp32
 // (Sources/Shaders/engine.metal:39-57). The embedding keeps the MLX row-major layout.
@@ -23,14 +24,14 @@ __global__ void spl_embed_q4_kernel(const uint32_t *__restrict__ packed, const u
     }
 }
 
-// RMSNorm into a GEMM operand: bf16(x * rsqrt(mean x^2 + eps) * w) and the per-64 sums of the
-// rounded values, the stored weight applied directly (engine.metal:159-178, 1609-1640; operand
+// RMSNorm into a GEMM operand (layout: SplOperand in spl_gemm_tc.cuh): bf16(x * rsqrt(mean x^2 + eps) * w) and the
+// per-64 sums of the rounded values, the stored weight applied directly (engine.metal:159-178, 1609-1640; operand
 // rounding engine_na.metal:42-57). When `index` is not
 // null row r of the output reads input row index[r] (the logit-row gather, engine.metal:273-281).
 // Grid (rows), 256 threads.
 __global__ void __launch_bounds__(256)
 spl_rmsnorm_kernel(const float *__restrict__ input, int in_ld, const uint16_t *__restrict__ weight, const uint32_t *__restrict__ index,
-                   __nv_bfloat16 *out, float *sums, int dim, float eps) {
+                   SplOperand out, int dim, float eps) {
     __shared__ float part[8];
     const int row = blockIdx.x;
     const float *x = input + size_t(index ? index[row] : row) * in_ld;
@@ -56,20 +57,20 @@ spl_rmsnorm_kernel(const float *__restrict__ input, int in_ld, const uint16_t *_
             const uint16_t b1 = spl_float_to_bf16(v.y * inv * spl_bf16_to_float(uint16_t(w.x >> 16)));
             const uint16_t b2 = spl_float_to_bf16(v.z * inv * spl_bf16_to_float(uint16_t(w.y)));
             const uint16_t b3 = spl_float_to_bf16(v.w * inv * spl_bf16_to_float(uint16_t(w.y >> 16)));
-            *reinterpret_cast<uint2 *>(out + size_t(row) * dim + i) = make_uint2(uint32_t(b0) | (uint32_t(b1) << 16), uint32_t(b2) | (uint32_t(b3) << 16));
             r0 = spl_bf16_to_float(b0); r1 = spl_bf16_to_float(b1); r2 = spl_bf16_to_float(b2); r3 = spl_bf16_to_float(b3);
+            *reinterpret_cast<uint2 *>(out.values + out.at(row, i)) = spl_operand_pack4(r0, r1, r2, r3);
         }
         // Per-64 sums of the rounded values: sixteen consecutive threads hold one group.
         float gsum = (r0 + r1) + (r2 + r3);
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o);
-        if (i < dim && (threadIdx.x & 15) == 0) sums[size_t(row) * (dim / 64) + i / 64] = gsum;
+        if (i < dim && (threadIdx.x & 15) == 0) out.put_sum(row, i / 64, gsum);
     }
 }
 
 // act = bf16(silu(gate) * up) and its per-64 sums from the fused gate|up projection (engine.metal:200-219).
 // gate_up: [rows][ld] with gate at column 0 and up at column `inter`.
-__global__ void spl_silu_mul_kernel(const float *__restrict__ gate_up, int ld, int inter, int rows, __nv_bfloat16 *out, float *sums) {
+__global__ void spl_silu_mul_kernel(const float *__restrict__ gate_up, int ld, int inter, int rows, SplOperand out) {
     const size_t total = size_t(rows) * inter / 4;
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     const size_t bound = (total + 31) / 32 * 32;
@@ -82,13 +83,13 @@ __global__ void spl_silu_mul_kernel(const float *__restrict__ gate_up, int ld, i
             const float4 u = *reinterpret_cast<const float4 *>(gate_up + size_t(row) * ld + inter + col);
             const uint16_t b0 = spl_float_to_bf16(spl_silu_exact(g.x) * u.x), b1 = spl_float_to_bf16(spl_silu_exact(g.y) * u.y);
             const uint16_t b2 = spl_float_to_bf16(spl_silu_exact(g.z) * u.z), b3 = spl_float_to_bf16(spl_silu_exact(g.w) * u.w);
-            *reinterpret_cast<uint2 *>(out + size_t(row) * inter + col) = make_uint2(uint32_t(b0) | (uint32_t(b1) << 16), uint32_t(b2) | (uint32_t(b3) << 16));
             r0 = spl_bf16_to_float(b0); r1 = spl_bf16_to_float(b1); r2 = spl_bf16_to_float(b2); r3 = spl_bf16_to_float(b3);
+            *reinterpret_cast<uint2 *>(out.values + out.at(row, col)) = spl_operand_pack4(r0, r1, r2, r3);
         }
         float gsum = (r0 + r1) + (r2 + r3);
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o);
-        if (idx < total && (threadIdx.x & 15) == 0) sums[size_t(row) * (inter / 64) + col / 64] = gsum;
+        if (idx < total && (threadIdx.x & 15) == 0) out.put_sum(row, col / 64, gsum);
     }
 }
 

@@ -14,7 +14,7 @@
 #include "spl_attention.cuh"
 #include "spl_elementwise.cuh"
 #include "spl_gdn.cuh"
-#include "spl_gemm.cuh"
+#include "spl_gemm_tc.cuh"
 #include "spl_host.h"
 
 namespace {
@@ -54,8 +54,10 @@ struct spl_engine {
     // Activations and scratch.
     float *h = nullptr, *proj = nullptr, *gate_up = nullptr, *gdn_act = nullptr, *partials = nullptr, *attn_partials = nullptr, *logits = nullptr;
     float *taps = nullptr;
-    __nv_bfloat16 *xn = nullptr, *core = nullptr, *act = nullptr, *hsn = nullptr;
-    float *xn_sums = nullptr, *core_sums = nullptr, *act_sums = nullptr, *hsn_sums = nullptr;   // per-64 sums of each operand
+    __nv_bfloat16 *xn = nullptr, *core = nullptr, *act = nullptr, *hsn = nullptr;      // GEMM operands (tile layout)
+    float *xn_sums = nullptr, *core_sums = nullptr, *act_sums = nullptr, *hsn_sums = nullptr;
+    int rows_padded = 0, logit_rows_padded = 0;
+    int *tc_error = nullptr;
     __half *q = nullptr;
     int32_t *argmax_ids = nullptr;
     int proj_ld = 0, gate_up_ld = 0, core_ld = 0, logits_ld = 0;
@@ -112,13 +114,13 @@ struct Shapes {
 };
 
 spl_status alloc_q4(spl_engine *e, SplQ4Dev &w, int n, int k) {
-    w.n = n; w.n16 = (n + 15) / 16; w.k = k;
-    const size_t groups = size_t(w.n16) * (k / 64);
-    SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&w.codes), groups * 512));
-    SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&w.sb), groups * 64));
-    SPL_CUDA(cudaMemsetAsync(w.codes, 0, groups * 512, e->stream));
-    SPL_CUDA(cudaMemsetAsync(w.sb, 0, groups * 64, e->stream));
-    e->weight_bytes += groups * 576;
+    w.n = n; w.ld = round16(n); w.tiles = (n + 127) / 128; w.k = k;
+    const size_t units = size_t(w.tiles) * (k / 64);
+    SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&w.codes), units * 4096));
+    SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&w.sb), units * 512));
+    SPL_CUDA(cudaMemsetAsync(w.codes, 0, units * 4096, e->stream));
+    SPL_CUDA(cudaMemsetAsync(w.sb, 0, units * 512, e->stream));
+    e->weight_bytes += units * 4608;
     return SPL_OK;
 }
 
@@ -151,47 +153,64 @@ void profile_collect(spl_engine *e) {
 }
 
 // ---- GEMM launch ------------------------------------------------------------------------------
-template <int RT, int NBW>
-void launch_gemm_variant(spl_engine *e, const SplQ4Dev &w, const __nv_bfloat16 *act, const float *sums, float *out, int out_ld, const float *residual, int rows) {
-    const int groups = w.k / 64, total_chunks = groups / 4;
-    const int tiles = (w.n16 + SPL_GEMM_WARPS * NBW - 1) / (SPL_GEMM_WARPS * NBW);
-    int splits = std::max(1, std::min(296 / std::max(tiles, 1), total_chunks / 2));
-    // Partials must fit the scratch buffer.
-    while (splits > 1 && size_t(splits) * RT * 8 * out_ld > e->partial_floats) --splits;
-    const int cps = (total_chunks + splits - 1) / splits;
-    splits = (total_chunks + cps - 1) / cps;
-    const size_t smem = size_t(2) * RT * 8 * SPL_GEMM_LDS * sizeof(__nv_bfloat16) + size_t(2) * RT * 8 * 4 * sizeof(float);
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(spl_gemm_q4_kernel<RT, NBW>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        configured = true;
+// Rows per operand block for a step of `rows` rows.
+int operand_rn(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : 64; }
+
+// Splits of the contraction for a GEMM of `blocks` (tile, row block) pairs and `groups` quant
+// groups: the count that minimises waves x groups per block on `sms` single-block SMs, with a
+// fixed cost per block (pipeline fill) and a reduction pass counted in.
+int choose_splits(int blocks, int groups, int sms, size_t partial_capacity, size_t partial_per_split) {
+    int best = 1; double best_cost = 1e30;
+    for (int s = 1; s <= groups / 8 && s <= 32; ++s) {
+        const int gps = (groups + s - 1) / s, eff = (groups + gps - 1) / gps;
+        if (eff != s) continue;
+        if (s > 1 && size_t(s) * partial_per_split > partial_capacity) break;
+        const int waves = (blocks * s + sms - 1) / sms;
+        const double cost = double(waves) * (gps + 6.0) + (s > 1 ? 4.0 : 0.0);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
     }
-    profile_begin(e, KLASS_GEMM, double(w.bytes()));
-    spl_gemm_q4_kernel<RT, NBW><<<dim3(tiles, splits), SPL_GEMM_WARPS * 32, smem, e->stream>>>(
-        w.codes, w.sb, act, sums, w.k, out, out_ld, residual, e->partials, rows, w.n16, groups, cps);
-    if (splits > 1) {
-        ++e->launches;
-        const size_t total = size_t(rows) * out_ld / 4;
-        const int blocks = int(std::min<size_t>((total + 255) / 256, 2048));
-        spl_gemm_reduce_kernel<<<blocks, 256, 0, e->stream>>>(e->partials, splits, RT * 8, rows, out_ld, residual, out);
-    }
-    profile_end(e);
+    return best;
 }
 
-void launch_gemm(spl_engine *e, const SplQ4Dev &w, const __nv_bfloat16 *act, const float *act_sums, float *out, int out_ld, const float *residual, int rows) {
-    for (int r0 = 0; r0 < rows; r0 += 64) {
-        const int count = std::min(64, rows - r0);
-        const __nv_bfloat16 *a = act + size_t(r0) * w.k;
-        const float *sm = act_sums + size_t(r0) * (w.k / 64);
-        float *o = out + size_t(r0) * out_ld;
-        const float *res = residual ? residual + size_t(r0) * out_ld : nullptr;
-        // Two n16 blocks a warp only where registers allow it and the columns still fill the GPU.
-        const bool wide_n = w.n16 >= 2 * SPL_GEMM_WARPS * 148 / 2;
-        if (count <= 8) { if (wide_n) launch_gemm_variant<1, 2>(e, w, a, sm, o, out_ld, res, count); else launch_gemm_variant<1, 1>(e, w, a, sm, o, out_ld, res, count); }
-        else if (count <= 16) { if (wide_n) launch_gemm_variant<2, 2>(e, w, a, sm, o, out_ld, res, count); else launch_gemm_variant<2, 1>(e, w, a, sm, o, out_ld, res, count); }
-        else if (count <= 32) launch_gemm_variant<4, 1>(e, w, a, sm, o, out_ld, res, count);
-        else launch_gemm_variant<8, 1>(e, w, a, sm, o, out_ld, res, count);
+struct GemmOperand { const __nv_bfloat16 *values; const float *sums; int rn, blocks; };
+
+template <int RN>
+void launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows,
+                    float *partials, size_t partial_floats, int *error_flag, int *launches) {
+    const int groups = w.k / 64;
+    const int row_blocks = (rows + RN - 1) / RN, rows_padded = op.blocks * RN;
+    const int splits = choose_splits(w.tiles * row_blocks, groups, 148, partial_floats, size_t(rows_padded) * w.ld);
+    const int gps = (groups + splits - 1) / splits;
+    const size_t smem = spl_tc_smem_bytes(RN);
+    static bool configured = false;
+    if (!configured) {
+        cudaFuncSetAttribute(spl_gemm_q4_tc_kernel<RN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        configured = true;
     }
+    spl_gemm_q4_tc_kernel<RN><<<dim3(w.tiles, splits, row_blocks), SPL_TC_THREADS, smem, stream>>>(
+        w.codes, w.sb, op.values, op.sums, out, w.ld, residual, partials, rows, op.blocks, groups, gps, error_flag);
+    if (launches) ++*launches;
+    if (splits > 1) {
+        const size_t total = size_t(rows) * w.ld / 4;
+        const int blocks = int(std::min<size_t>((total + 255) / 256, 2048));
+        spl_gemm_reduce_kernel<<<blocks, 256, 0, stream>>>(partials, splits, rows_padded, rows, w.ld, residual, out);
+        if (launches) ++*launches;
+    }
+}
+
+// out[r][:] = GEMM(w, operand[r][:]) (+ residual) for the first `rows` rows of the operand.
+void launch_gemm_rows(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows,
+                      float *partials, size_t partial_floats, int *error_flag, int *launches) {
+    if (op.rn == 16) launch_gemm_tc<16>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches);
+    else if (op.rn == 32) launch_gemm_tc<32>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches);
+    else launch_gemm_tc<64>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches);
+}
+
+void launch_gemm(spl_engine *e, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows) {
+    profile_begin(e, KLASS_GEMM, double(w.bytes()) * ((rows + op.rn - 1) / op.rn));
+    --e->launches;      // profile_begin counted one; the launcher counts the kernels it really starts
+    launch_gemm_rows(e->stream, w, op, out, residual, rows, e->partials, e->partial_floats, e->tc_error, &e->launches);
+    profile_end(e);
 }
 
 template <int HD>
@@ -244,6 +263,10 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
     SPL_CUDA(cudaMemcpyAsync(e->tables_dev, hb, off * 4, cudaMemcpyHostToDevice, e->stream));
 
     const int H = g.hidden;
+    // GEMM operands of this step: row blocks of rn rows, in the tile layout the tensor cores read.
+    const int rn = operand_rn(R), blocks = (R + rn - 1) / rn;
+    const SplOperand xn{e->xn, e->xn_sums, rn, blocks}, core{e->core, e->core_sums, rn, blocks}, act{e->act, e->act_sums, rn, blocks};
+    const GemmOperand gxn{e->xn, e->xn_sums, rn, blocks}, gcore{e->core, e->core_sums, rn, blocks}, gact{e->act, e->act_sums, rn, blocks};
     profile_begin(e, KLASS_ELEMENTWISE, 0);
     spl_embed_q4_kernel<<<R, 128, 0, e->stream>>>(e->embed_packed, e->embed_scales, e->embed_biases, e->d_tokens, e->h, H);
     profile_end(e);
@@ -255,13 +278,13 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
         const LayerWeights &L = e->layers[l];
         const int live = (l + 1 == g.layers) ? int(t->live_rows) : R;
         profile_begin(e, KLASS_ELEMENTWISE, 0);
-        spl_rmsnorm_kernel<<<R, 256, 0, e->stream>>>(e->h, H, L.vec[SPL_VEC_INPUT_NORM], nullptr, e->xn, e->xn_sums, H, g.eps);
+        spl_rmsnorm_kernel<<<R, 256, 0, e->stream>>>(e->h, H, L.vec[SPL_VEC_INPUT_NORM], nullptr, xn, H, g.eps);
         profile_end(e);
-        launch_gemm(e, L.in_proj, e->xn, e->xn_sums, e->proj, e->proj_ld, nullptr, R);
+        launch_gemm(e, L.in_proj, gxn, e->proj, nullptr, R);
         if (!L.full) {
             SplGdnParams p;
             p.rows = R; p.runs = int(t->run_count); p.channels = sh.C; p.key_heads = g.gdn_key_heads; p.value_heads = g.gdn_value_heads;
-            p.head_dim = g.gdn_head_dim; p.proj_ld = e->proj_ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps;
+            p.head_dim = g.gdn_head_dim; p.proj_ld = L.in_proj.ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps;
             profile_begin(e, KLASS_GDN, 0);
             spl_gdn_conv_kernel<<<dim3((sh.C + 255) / 256, t->run_count), 256, 0, e->stream>>>(
                 e->proj, L.vec[SPL_VEC_CONV], e->conv[linear_index], e->d_runs, e->d_row_read, e->d_row_write, e->gdn_act, p);
@@ -269,13 +292,13 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
             profile_begin(e, KLASS_GDN, 0);
             spl_gdn_recurrence_kernel<<<dim3(g.gdn_value_heads, t->run_count), 256, 0, e->stream>>>(
                 e->gdn_act, e->proj, L.vec[SPL_VEC_A_LOG], L.vec[SPL_VEC_DT_BIAS], L.vec[SPL_VEC_GDN_NORM], e->state[linear_index],
-                e->journal[linear_index], e->d_runs, e->d_run_info, e->core, e->core_sums, p);
+                e->journal[linear_index], e->d_runs, e->d_run_info, core, p);
             profile_end(e);
             ++linear_index;
         } else {
             SplAttnParams p;
             p.rows = R; p.live = live; p.heads = g.heads; p.kv_heads = g.kv_heads; p.head_dim = g.head_dim; p.rotary = g.rotary_dim;
-            p.max_pages = e->host->max_pages; p.proj_ld = e->proj_ld; p.k_offset = sh.att_k; p.v_offset = sh.att_v;
+            p.max_pages = e->host->max_pages; p.proj_ld = L.in_proj.ld; p.k_offset = sh.att_k; p.v_offset = sh.att_v;
             p.spans = int(t->spans); p.pages_per_span = int(t->pages_per_span); p.eps = g.eps; p.scale = 1.0f / sqrtf(float(g.head_dim));
             profile_begin(e, KLASS_ATTENTION, 0);
             spl_attn_prepare_kernel<<<dim3(g.heads + g.kv_heads, R), 128, 0, e->stream>>>(
@@ -297,35 +320,41 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
                 else launch_scan<128>(e, mt, dim3(g.kv_heads * t->spans, blocks), p, full_index);
                 profile_end(e);
                 profile_begin(e, KLASS_ATTENTION, 0);
-                spl_attn_merge_kernel<<<dim3(g.heads, live), g.head_dim, 0, e->stream>>>(e->attn_partials, e->proj, e->core, e->core_sums, p);
+                spl_attn_merge_kernel<<<dim3(g.heads, live), g.head_dim, 0, e->stream>>>(e->attn_partials, e->proj, core, p);
                 profile_end(e);
             }
             ++full_index;
         }
         if (live > 0) {
-            launch_gemm(e, L.out_proj, e->core, e->core_sums, e->h, H, e->h, live);
+            launch_gemm(e, L.out_proj, gcore, e->h, e->h, live);
             profile_begin(e, KLASS_ELEMENTWISE, 0);
-            spl_rmsnorm_kernel<<<live, 256, 0, e->stream>>>(e->h, H, L.vec[SPL_VEC_POST_NORM], nullptr, e->xn, e->xn_sums, H, g.eps);
+            spl_rmsnorm_kernel<<<live, 256, 0, e->stream>>>(e->h, H, L.vec[SPL_VEC_POST_NORM], nullptr, xn, H, g.eps);
             profile_end(e);
-            launch_gemm(e, L.gate_up, e->xn, e->xn_sums, e->gate_up, e->gate_up_ld, nullptr, live);
+            launch_gemm(e, L.gate_up, gxn, e->gate_up, nullptr, live);
             profile_begin(e, KLASS_ELEMENTWISE, 0);
             const size_t total = size_t(live) * g.inter / 4;
-            spl_silu_mul_kernel<<<int(std::min<size_t>((total + 255) / 256, 4096)), 256, 0, e->stream>>>(e->gate_up, e->gate_up_ld, g.inter, live, e->act, e->act_sums);
+            spl_silu_mul_kernel<<<int(std::min<size_t>((total + 255) / 256, 4096)), 256, 0, e->stream>>>(e->gate_up, e->gate_up_ld, g.inter, live, act);
             profile_end(e);
-            launch_gemm(e, L.down, e->act, e->act_sums, e->h, H, e->h, live);
+            launch_gemm(e, L.down, gact, e->h, e->h, live);
         }
         if (e->taps_enabled) SPL_CUDA(cudaMemcpyAsync(e->taps + size_t(l) * e->c.max_rows * H, e->h, size_t(R) * H * 4, cudaMemcpyDeviceToDevice, e->stream));
     }
     if (t->logit_rows > 0) {
         profile_begin(e, KLASS_OTHER, 0);
-        spl_rmsnorm_kernel<<<t->logit_rows, 256, 0, e->stream>>>(e->h, H, e->final_norm, e->d_gather, e->hsn, e->hsn_sums, H, g.eps);
+        const int lrn = operand_rn(int(t->logit_rows)), lblocks = (int(t->logit_rows) + lrn - 1) / lrn;
+        spl_rmsnorm_kernel<<<t->logit_rows, 256, 0, e->stream>>>(e->h, H, e->final_norm, e->d_gather, SplOperand{e->hsn, e->hsn_sums, lrn, lblocks}, H, g.eps);
         profile_end(e);
-        launch_gemm(e, e->head, e->hsn, e->hsn_sums, e->logits, e->logits_ld, nullptr, int(t->logit_rows));
+        launch_gemm(e, e->head, GemmOperand{e->hsn, e->hsn_sums, operand_rn(int(t->logit_rows)), (int(t->logit_rows) + operand_rn(int(t->logit_rows)) - 1) / operand_rn(int(t->logit_rows))}, e->logits, nullptr, int(t->logit_rows));
     }
     SPL_CUDA(cudaEventRecord(e->ev_end, e->stream));
     const spl_status launched = check_launch(e, "step launch");
     if (launched != SPL_OK) return launched;
     SPL_CUDA(cudaStreamSynchronize(e->stream));
+    {
+        int flag = 0;
+        SPL_CUDA(cudaMemcpy(&flag, e->tc_error, sizeof flag, cudaMemcpyDeviceToHost));
+        if (flag) { cudaMemset(e->tc_error, 0, sizeof flag); return e->fail(SPL_ERR_TIMEOUT, "a GEMM block gave up waiting (role " + std::to_string(flag - 1) + ")"); }
+    }
     profile_collect(e);
     e->last_rows = R; e->last_logit_rows = int(t->logit_rows);
     if (stats) {
@@ -337,7 +366,7 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
     return SPL_OK;
 }
 
-spl_status upload_q4_into(spl_engine *e, SplQ4Dev &w, int nb_first, int rows, int inner, const uint32_t *packed, const uint16_t *scales,
+spl_status upload_q4_into(spl_engine *e, SplQ4Dev &w, int n0, int rows, int inner, const uint32_t *packed, const uint16_t *scales,
                           const uint16_t *biases, bool device_source) {
     const size_t words = size_t(rows) * inner / 8, groups = size_t(rows) * inner / 64;
     const uint32_t *dp = packed; const uint16_t *ds = scales, *db = biases;
@@ -351,18 +380,22 @@ spl_status upload_q4_into(spl_engine *e, SplQ4Dev &w, int nb_first, int rows, in
         SPL_CUDA(cudaMemcpyAsync(sbias, biases, groups * 2, cudaMemcpyHostToDevice, e->stream));
         dp = sp; ds = ss; db = sbias;
     }
-    const int nb_count = (rows + 15) / 16;
-    const size_t total = size_t(nb_count) * (inner / 64) * 128;
-    spl_repack_q4_kernel<<<int(std::min<size_t>((total + 255) / 256, 16384)), 256, 0, e->stream>>>(
-        dp, ds, db, rows, inner, reinterpret_cast<uint32_t *>(w.codes), w.sb, nb_first, nb_count);
-    const spl_status launched = check_launch(e, "repack");
+    int *bad = nullptr;
+    SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&bad), sizeof(int)));
+    SPL_CUDA(cudaMemsetAsync(bad, 0, sizeof(int), e->stream));
+    spl_repack_q4_kernel<<<int(std::min<size_t>((words + 255) / 256, 16384)), 256, 0, e->stream>>>(dp, ds, db, rows, inner, w.codes, w.sb, n0, bad);
+    spl_status launched = check_launch(e, "repack");
     SPL_CUDA(cudaStreamSynchronize(e->stream));
+    int flag = 0;
+    cudaMemcpy(&flag, bad, sizeof flag, cudaMemcpyDeviceToHost);
+    cudaFree(bad);
     if (sp) { cudaFree(sp); cudaFree(ss); cudaFree(sbias); }
+    if (launched == SPL_OK && flag) launched = e->fail(SPL_ERR_INVALID_ARGUMENT, "a quantisation scale is outside [2^-14, 8188]: scale * (code - 8) would not be exact in fp16");
     return launched;
 }
 
 // Where a tensor kind lands: which fused device tensor and at which 16-column block.
-struct Placement { SplQ4Dev *dst; int nb_first; int rows; int inner; };
+struct Placement { SplQ4Dev *dst; int n0; int rows; int inner; };   // n0: first column of the tensor inside the fused one
 
 spl_status place(spl_engine *e, int layer, int kind, Placement *out) {
     const spl_geometry &g = e->g;
@@ -375,16 +408,16 @@ spl_status place(spl_engine *e, int layer, int kind, Placement *out) {
     LayerWeights &L = e->layers[layer];
     switch (kind) {
     case SPL_Q4_QKV: if (L.full) break; *out = {&L.in_proj, 0, sh.C, g.hidden}; return SPL_OK;
-    case SPL_Q4_Z: if (L.full) break; *out = {&L.in_proj, sh.gdn_z / 16, sh.VD, g.hidden}; return SPL_OK;
-    case SPL_Q4_A: if (L.full) break; *out = {&L.in_proj, sh.gdn_a / 16, sh.VH, g.hidden}; return SPL_OK;
-    case SPL_Q4_B: if (L.full) break; *out = {&L.in_proj, sh.gdn_b / 16, sh.VH, g.hidden}; return SPL_OK;
+    case SPL_Q4_Z: if (L.full) break; *out = {&L.in_proj, sh.gdn_z, sh.VD, g.hidden}; return SPL_OK;
+    case SPL_Q4_A: if (L.full) break; *out = {&L.in_proj, sh.gdn_a, sh.VH, g.hidden}; return SPL_OK;
+    case SPL_Q4_B: if (L.full) break; *out = {&L.in_proj, sh.gdn_b, sh.VH, g.hidden}; return SPL_OK;
     case SPL_Q4_OUT: if (L.full) break; *out = {&L.out_proj, 0, g.hidden, sh.VD}; return SPL_OK;
     case SPL_Q4_Q: if (!L.full) break; *out = {&L.in_proj, 0, 2 * sh.AD, g.hidden}; return SPL_OK;
-    case SPL_Q4_K: if (!L.full) break; *out = {&L.in_proj, sh.att_k / 16, sh.KV, g.hidden}; return SPL_OK;
-    case SPL_Q4_V: if (!L.full) break; *out = {&L.in_proj, sh.att_v / 16, sh.KV, g.hidden}; return SPL_OK;
+    case SPL_Q4_K: if (!L.full) break; *out = {&L.in_proj, sh.att_k, sh.KV, g.hidden}; return SPL_OK;
+    case SPL_Q4_V: if (!L.full) break; *out = {&L.in_proj, sh.att_v, sh.KV, g.hidden}; return SPL_OK;
     case SPL_Q4_O: if (!L.full) break; *out = {&L.out_proj, 0, g.hidden, sh.AD}; return SPL_OK;
     case SPL_Q4_GATE: *out = {&L.gate_up, 0, g.inter, g.hidden}; return SPL_OK;
-    case SPL_Q4_UP: *out = {&L.gate_up, g.inter / 16, g.inter, g.hidden}; return SPL_OK;
+    case SPL_Q4_UP: *out = {&L.gate_up, g.inter, g.inter, g.hidden}; return SPL_OK;
     case SPL_Q4_DOWN: *out = {&L.down, 0, g.hidden, g.inter}; return SPL_OK;
     }
     return e->fail(SPL_ERR_INVALID_ARGUMENT, "q4 kind does not belong to this layer's mixer");
@@ -480,21 +513,33 @@ spl_status create(const spl_geometry *gp, const spl_config *cp, spl_engine *e) {
     e->proj_ld = std::max(sh.gdn_n, sh.att_n); e->gate_up_ld = 2 * g.inter; e->core_ld = std::max(sh.VD, sh.AD); e->logits_ld = g.vocab;
     const int LR = e->c.max_logit_rows;
     if ((s = device_alloc(e, &e->h, size_t(R) * H, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->xn, size_t(R) * H, &e->scratch_bytes)) != SPL_OK) return s;
+    e->rows_padded = (R + 63) / 64 * 64; e->logit_rows_padded = (e->c.max_logit_rows + 63) / 64 * 64;
+    const int RP = e->rows_padded, LP = e->logit_rows_padded;
+    if ((s = device_alloc(e, &e->xn, size_t(RP) * H, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->xn_sums, size_t(RP) * H / 64, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->core_sums, size_t(RP) * e->core_ld / 64, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->act_sums, size_t(RP) * g.inter / 64, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->hsn_sums, size_t(LP) * H / 64, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->tc_error, 64)) != SPL_OK) return s;
+    SPL_CUDA(cudaMemsetAsync(e->tc_error, 0, 64 * sizeof(int), e->stream));
+    SPL_CUDA(cudaMemsetAsync(e->xn, 0, size_t(RP) * H * 2, e->stream));
+    SPL_CUDA(cudaMemsetAsync(e->xn_sums, 0, size_t(RP) * H / 64 * 4, e->stream));
+    SPL_CUDA(cudaMemsetAsync(e->core_sums, 0, size_t(RP) * e->core_ld / 64 * 4, e->stream));
+    SPL_CUDA(cudaMemsetAsync(e->act_sums, 0, size_t(RP) * g.inter / 64 * 4, e->stream));
+    SPL_CUDA(cudaMemsetAsync(e->hsn_sums, 0, size_t(LP) * H / 64 * 4, e->stream));
     if ((s = device_alloc(e, &e->proj, size_t(R) * e->proj_ld, &e->scratch_bytes)) != SPL_OK) return s;
     if ((s = device_alloc(e, &e->gdn_act, size_t(R) * sh.C, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->core, size_t(R) * e->core_ld, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->core, size_t(RP) * e->core_ld, &e->scratch_bytes)) != SPL_OK) return s;
+    SPL_CUDA(cudaMemsetAsync(e->core, 0, size_t(RP) * e->core_ld * 2, e->stream));
     if ((s = device_alloc(e, &e->gate_up, size_t(R) * e->gate_up_ld, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->act, size_t(R) * g.inter, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->act, size_t(RP) * g.inter, &e->scratch_bytes)) != SPL_OK) return s;
+    SPL_CUDA(cudaMemsetAsync(e->act, 0, size_t(RP) * g.inter * 2, e->stream));
     if ((s = device_alloc(e, &e->q, size_t(R) * sh.AD, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->xn_sums, size_t(R) * H / 64, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->core_sums, size_t(R) * e->core_ld / 64, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->act_sums, size_t(R) * g.inter / 64, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->hsn_sums, size_t(LR) * H / 64, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->hsn, size_t(LR) * H, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->hsn, size_t(LP) * H, &e->scratch_bytes)) != SPL_OK) return s;
+    SPL_CUDA(cudaMemsetAsync(e->hsn, 0, size_t(LP) * H * 2, e->stream));
     if ((s = device_alloc(e, &e->logits, size_t(LR) * e->logits_ld, &e->scratch_bytes)) != SPL_OK) return s;
     if ((s = device_alloc(e, &e->argmax_ids, size_t(LR), &e->scratch_bytes)) != SPL_OK) return s;
-    e->partial_floats = size_t(16) * 64 * std::max(H, 4096);
+    e->partial_floats = size_t(16) * RP * std::max(H, 4096);
     if ((s = device_alloc(e, &e->partials, e->partial_floats, &e->scratch_bytes)) != SPL_OK) return s;
     e->attn_partial_floats = size_t(std::max(16 * R, 64 * std::min(R, 128))) * g.heads * (g.head_dim + 2);
     if ((s = device_alloc(e, &e->attn_partials, e->attn_partial_floats, &e->scratch_bytes)) != SPL_OK) return s;
@@ -532,7 +577,7 @@ void spl_engine_destroy(spl_engine *e) {
     for (auto p : e->state) cudaFree(p); for (auto p : e->conv) cudaFree(p); for (auto p : e->journal) cudaFree(p);
     cudaFree(e->h); cudaFree(e->xn); cudaFree(e->proj); cudaFree(e->gdn_act); cudaFree(e->core); cudaFree(e->gate_up); cudaFree(e->act);
     cudaFree(e->q); cudaFree(e->hsn); cudaFree(e->logits); cudaFree(e->argmax_ids); cudaFree(e->partials); cudaFree(e->attn_partials);
-    cudaFree(e->taps); cudaFree(e->tables_dev); cudaFree(e->xn_sums); cudaFree(e->core_sums); cudaFree(e->act_sums); cudaFree(e->hsn_sums);
+    cudaFree(e->taps); cudaFree(e->tables_dev); cudaFree(e->xn_sums); cudaFree(e->core_sums); cudaFree(e->act_sums); cudaFree(e->hsn_sums); cudaFree(e->tc_error);
     if (e->tables_host) cudaFreeHost(e->tables_host);
     for (ProfileSlot &s : e->profile_slots) { cudaEventDestroy(s.begin); cudaEventDestroy(s.end); }
     if (e->ev_begin) cudaEventDestroy(e->ev_begin);
@@ -563,7 +608,7 @@ spl_status spl_weights_set_q4(spl_engine *e, int32_t layer, int32_t kind, int32_
     const spl_status s = place(e, layer, kind, &pl);
     if (s != SPL_OK) return s;
     if (rows != pl.rows || inner != pl.inner) return e->fail(SPL_ERR_INVALID_ARGUMENT, "tensor shape does not match the geometry");
-    return upload_q4_into(e, *pl.dst, pl.nb_first, rows, inner, packed, scales, biases, false);
+    return upload_q4_into(e, *pl.dst, pl.n0, rows, inner, packed, scales, biases, false);
 }
 
 spl_status spl_weights_set_vector(spl_engine *e, int32_t layer, int32_t kind, const uint16_t *bf16, int32_t count) {
@@ -621,7 +666,7 @@ spl_status spl_weights_synthesize_q4(spl_engine *e, uint64_t seed) {
             if (!pl.dst) { dp = e->embed_packed; ds = e->embed_scales; db = e->embed_biases; }
             spl_synth_q4_kernel<<<int(std::min<size_t>((slots + 127) / 128, 65535)), 128, 0, e->stream>>>(seed ^ fnv1a64(full), factor, pl.rows, pl.inner, dp, ds, db);
             if ((result = check_launch(e, "synthesize")) != SPL_OK) break;
-            if (pl.dst) result = upload_q4_into(e, *pl.dst, pl.nb_first, pl.rows, pl.inner, sp, ss, sbias, true);
+            if (pl.dst) result = upload_q4_into(e, *pl.dst, pl.n0, pl.rows, pl.inner, sp, ss, sbias, true);
         }
     }
     cudaStreamSynchronize(e->stream);
@@ -780,7 +825,7 @@ spl_status spl_debug_read(spl_engine *e, int32_t which, int32_t index, void *dst
     case 6: pick(e->v_scale, size_t(e->c.kv_pages) * page_vecs * 4); break;
     case 7: src = e->h; have = size_t(e->last_rows) * e->g.hidden * 4; break;
     case 9: src = e->proj; have = size_t(e->last_rows) * e->proj_ld * 4; break;
-    case 10: src = e->core; have = size_t(e->last_rows) * e->core_ld * 2; break;
+    case 10: src = e->core; have = size_t(e->rows_padded) * e->core_ld * 2; break;
     case 11: src = e->q; have = size_t(e->last_rows) * e->g.heads * e->g.head_dim * 2; break;
     case 12: src = e->attn_partials; have = e->attn_partial_floats * 4; break;
     case 8: if (e->taps && index >= 0 && index < e->g.layers) { src = e->taps + size_t(index) * e->c.max_rows * e->g.hidden; have = size_t(e->last_rows) * e->g.hidden * 4; } break;
@@ -803,17 +848,18 @@ spl_status spl_debug_read(spl_engine *e, int32_t which, int32_t index, void *dst
 #define SPL_STATIC_INNER 17408
 #define SPL_STATIC_OPERAND_BYTES (SPL_STATIC_ROWS * SPL_STATIC_INNER * 2)
 #define SPL_STATIC_SUMS_BYTES (SPL_STATIC_ROWS * (SPL_STATIC_INNER / 64) * 4)
+#define SPL_STATIC_FLAG_BYTES 256      // the error word and the kernel's debug words
 #define SPL_STATIC_PARTIAL_BYTES (8u << 20)
-#define SPL_STATIC_BYTES (SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES + SPL_STATIC_PARTIAL_BYTES)
+#define SPL_STATIC_BYTES (SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES + SPL_STATIC_FLAG_BYTES + SPL_STATIC_PARTIAL_BYTES)
 static __device__ __align__(256) unsigned char spl_static_scratch[SPL_STATIC_BYTES];
 // The array's address on each device, asked for once per device. The symbol itself is only a
 // host-side handle: a kernel must be given what cudaGetSymbolAddress returns.
 static void *spl_static_address[64] = {};
 
-// fp32 rows -> the bf16 operand and its per-64 sums (Sources/Shaders/engine_na.metal:42-57).
-// Grid (rows), 256 threads.
+// fp32 rows -> the bf16 GEMM operand and its per-64 sums (Sources/Shaders/engine_na.metal:42-57;
+// layout: SplOperand). Grid (rows), 256 threads.
 __global__ void __launch_bounds__(256)
-spl_operand_kernel(const float *__restrict__ input, __nv_bfloat16 *out, float *sums, int inner) {
+spl_operand_kernel(const float *__restrict__ input, SplOperand out, int inner) {
     const int row = blockIdx.x;
     for (int base = 0; base < inner; base += 1024) {
         const int i = base + threadIdx.x * 4;
@@ -821,32 +867,13 @@ spl_operand_kernel(const float *__restrict__ input, __nv_bfloat16 *out, float *s
         if (i < inner) {
             const float4 v = *reinterpret_cast<const float4 *>(input + size_t(row) * inner + i);
             const uint16_t b0 = spl_float_to_bf16(v.x), b1 = spl_float_to_bf16(v.y), b2 = spl_float_to_bf16(v.z), b3 = spl_float_to_bf16(v.w);
-            *reinterpret_cast<uint2 *>(out + size_t(row) * inner + i) = make_uint2(uint32_t(b0) | (uint32_t(b1) << 16), uint32_t(b2) | (uint32_t(b3) << 16));
             r0 = spl_bf16_to_float(b0); r1 = spl_bf16_to_float(b1); r2 = spl_bf16_to_float(b2); r3 = spl_bf16_to_float(b3);
+            *reinterpret_cast<uint2 *>(out.values + out.at(row, i)) = spl_operand_pack4(r0, r1, r2, r3);
         }
         float gsum = (r0 + r1) + (r2 + r3);
 #pragma unroll
         for (int o = 8; o > 0; o >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o);
-        if (i < inner && (threadIdx.x & 15) == 0) sums[size_t(row) * (inner / 64) + i / 64] = gsum;
-    }
-}
-
-template <int RT>
-static void launch_gemm_static(const SplQ4Dev &w, const __nv_bfloat16 *act, const float *sums, float *partials, float *out, int out_ld,
-                               const float *residual, int rows, cudaStream_t stream) {
-    const int groups = w.k / 64, total_chunks = groups / 4;
-    const int tiles = (w.n16 + SPL_GEMM_WARPS - 1) / SPL_GEMM_WARPS;
-    int splits = std::max(1, std::min(296 / std::max(tiles, 1), total_chunks / 2));
-    while (splits > 1 && size_t(splits) * RT * 8 * out_ld * 4 > SPL_STATIC_PARTIAL_BYTES) --splits;
-    const int cps = (total_chunks + splits - 1) / splits;
-    splits = (total_chunks + cps - 1) / cps;
-    const size_t smem = size_t(2) * RT * 8 * SPL_GEMM_LDS * sizeof(__nv_bfloat16) + size_t(2) * RT * 8 * 4 * sizeof(float);
-    cudaFuncSetAttribute(spl_gemm_q4_kernel<RT, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-    spl_gemm_q4_kernel<RT, 1><<<dim3(tiles, splits), SPL_GEMM_WARPS * 32, smem, stream>>>(
-        w.codes, w.sb, act, sums, w.k, out, out_ld, residual, partials, rows, w.n16, groups, cps);
-    if (splits > 1) {
-        const size_t total = size_t(rows) * out_ld / 4;
-        spl_gemm_reduce_kernel<<<int(std::min<size_t>((total + 255) / 256, 2048)), 256, 0, stream>>>(partials, splits, RT * 8, rows, out_ld, residual, out);
+        if (i < inner && (threadIdx.x & 15) == 0) out.put_sum(row, i / 64, gsum);
     }
 }
 
@@ -876,17 +903,16 @@ extern "C" spl_status spl_gemm_q4_static(spl_engine *e, int32_t layer, int32_t w
     unsigned char *base = static_cast<unsigned char *>(spl_static_address[e->device]);
     __nv_bfloat16 *operand = reinterpret_cast<__nv_bfloat16 *>(base);
     float *sums = reinterpret_cast<float *>(base + SPL_STATIC_OPERAND_BYTES);
-    float *partials = reinterpret_cast<float *>(base + SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES);
+    int *flag = reinterpret_cast<int *>(base + SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES);
+    float *partials = reinterpret_cast<float *>(base + SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES + SPL_STATIC_FLAG_BYTES);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
-    const int ld = w->n16 * 16;
-    // Nothing in the scratch has to start at zero: the operand and sums of the rows in use are
-    // rewritten here, rows past `rows` are never read back, and every partial sum that the
-    // reduction reads was written by this call's GEMM.
-    spl_operand_kernel<<<rows, 256, 0, stream>>>(device_activations, operand, sums, w->k);
-    if (rows <= 8) launch_gemm_static<1>(*w, operand, sums, partials, device_out, ld, device_residual, rows, stream);
-    else if (rows <= 16) launch_gemm_static<2>(*w, operand, sums, partials, device_out, ld, device_residual, rows, stream);
-    else if (rows <= 32) launch_gemm_static<4>(*w, operand, sums, partials, device_out, ld, device_residual, rows, stream);
-    else launch_gemm_static<8>(*w, operand, sums, partials, device_out, ld, device_residual, rows, stream);
+    const int rn = operand_rn(rows);
+    // The array keeps what the last call left. Only the error word has to start at zero; the
+    // operand and sums of the rows in use are rewritten here, the block's other rows feed outputs
+    // that are never stored, and every partial sum the reduction reads is written by this call.
+    SPL_CUDA(cudaMemsetAsync(flag, 0, SPL_STATIC_FLAG_BYTES, stream));
+    spl_operand_kernel<<<rows, 256, 0, stream>>>(device_activations, SplOperand{operand, sums, rn, 1}, w->k);
+    launch_gemm_rows(stream, *w, GemmOperand{operand, sums, rn, 1}, device_out, device_residual, rows, partials, SPL_STATIC_PARTIAL_BYTES / 4, flag, nullptr);
     return check_launch(e, "spl_gemm_q4_static");
 }
 
@@ -895,7 +921,7 @@ extern "C" {
 // One GEMM on host buffers: the whole path a caller without an engine sees.
 spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t *scales, const uint16_t *biases,
                           int32_t n, int32_t k, const float *activations, int32_t rows, const float *residual, float *out) {
-    if (!packed || !scales || !biases || !activations || !out || n <= 0 || k <= 0 || k % 256 || rows <= 0) return SPL_ERR_INVALID_ARGUMENT;
+    if (!packed || !scales || !biases || !activations || !out || n <= 0 || k <= 0 || k % 256 || rows <= 0) return SPL_ERR_INVALID_ARGUMENT;   // inner dimensions are multiples of 256 in every geometry this library accepts
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return SPL_ERR_UNSUPPORTED_DEVICE;
     spl_engine local;                     // only stream, partial scratch and error text are used
@@ -905,33 +931,49 @@ spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t
     SPL_CUDA(cudaStreamCreate(&e->stream));
     SplQ4Dev w;
     spl_status s = alloc_q4(e, w, n, k);
-    const int ld = w.n16 * 16;
-    float *d_act32 = nullptr, *d_out = nullptr; __nv_bfloat16 *d_act = nullptr;
-    e->partial_floats = size_t(16) * 64 * ld;
+    const int ld = w.ld;
+    const int rn = operand_rn(rows), blocks = (rows + rn - 1) / rn;
+    float *d_act32 = nullptr, *d_out = nullptr, *d_sums = nullptr; __nv_bfloat16 *d_act = nullptr; int *d_flag = nullptr;
+    e->partial_floats = size_t(16) * blocks * rn * ld;
     if (s == SPL_OK) s = device_alloc(e, &d_act32, size_t(rows) * k);
-    if (s == SPL_OK) s = device_alloc(e, &d_act, size_t(rows) * k);
+    if (s == SPL_OK) s = device_alloc(e, &d_act, size_t(blocks) * rn * k);
+    if (s == SPL_OK) s = device_alloc(e, &d_sums, size_t(blocks) * rn * k / 64);
     if (s == SPL_OK) s = device_alloc(e, &d_out, size_t(rows) * ld);
+    if (s == SPL_OK) s = device_alloc(e, &d_flag, 64);
     if (s == SPL_OK) s = device_alloc(e, &e->partials, e->partial_floats);
     if (s == SPL_OK) s = upload_q4_into(e, w, 0, n, k, packed, scales, biases, false);
     if (s == SPL_OK) {
-        std::vector<uint16_t> rounded(size_t(rows) * k);
-        for (size_t i = 0; i < rounded.size(); ++i) {
-            uint32_t bits; memcpy(&bits, &activations[i], 4);
-            rounded[i] = uint16_t((bits + 0x7FFFu + ((bits >> 16) & 1u)) >> 16);
-        }
-        cudaMemcpy(d_act, rounded.data(), rounded.size() * 2, cudaMemcpyHostToDevice);
-        std::vector<float> sums(size_t(rows) * k / 64, 0.0f);
-        for (size_t i = 0; i < rounded.size(); ++i) {
-            const uint32_t bits = uint32_t(rounded[i]) << 16; float v; memcpy(&v, &bits, 4);
-            sums[i / 64] += v;
-        }
-        cudaMemcpy(d_act32, sums.data(), sums.size() * 4, cudaMemcpyHostToDevice);
-        if (residual) cudaMemcpy2D(d_out, size_t(ld) * 4, residual, size_t(n) * 4, size_t(n) * 4, rows, cudaMemcpyHostToDevice);
-        launch_gemm(e, w, d_act, d_act32, d_out, ld, residual ? d_out : nullptr, rows);
+        cudaMemsetAsync(d_act, 0, size_t(blocks) * rn * k * 2, e->stream);
+        cudaMemsetAsync(d_sums, 0, size_t(blocks) * rn * k / 64 * 4, e->stream);
+        cudaMemsetAsync(d_flag, 0, 64 * sizeof(int), e->stream);
+        if (getenv("SPL_TC_TRACE")) { const int magic[2] = {0x7ACE, int(strtol(getenv("SPL_TC_TRACE"), nullptr, 0))}; cudaMemcpyAsync(d_flag + 1, magic, sizeof magic, cudaMemcpyHostToDevice, e->stream); cudaStreamSynchronize(e->stream); }
+        cudaMemcpyAsync(d_act32, activations, size_t(rows) * k * 4, cudaMemcpyHostToDevice, e->stream);
+        spl_operand_kernel<<<rows, 256, 0, e->stream>>>(d_act32, SplOperand{d_act, d_sums, rn, blocks}, k);
+        if (residual) cudaMemcpy2DAsync(d_out, size_t(ld) * 4, residual, size_t(n) * 4, size_t(n) * 4, rows, cudaMemcpyHostToDevice, e->stream);
+        cudaEvent_t ev0, ev1; cudaEventCreate(&ev0); cudaEventCreate(&ev1);     // destroyed with the context; a handful per process
+        if (getenv("SPL_TC_TRACE"))      // warm the kernel so the timed launch below is a steady-state one
+            for (int warm = 0; warm < 3; ++warm)
+                launch_gemm_rows(e->stream, w, GemmOperand{d_act, d_sums, rn, blocks}, d_out, nullptr, rows, e->partials, e->partial_floats, d_flag, nullptr);
+        if (residual) cudaMemcpy2DAsync(d_out, size_t(ld) * 4, residual, size_t(n) * 4, size_t(n) * 4, rows, cudaMemcpyHostToDevice, e->stream);
+        cudaEventRecord(ev0, e->stream);
+        launch_gemm_rows(e->stream, w, GemmOperand{d_act, d_sums, rn, blocks}, d_out, residual ? d_out : nullptr, rows, e->partials, e->partial_floats, d_flag, nullptr);
+        cudaEventRecord(ev1, e->stream);
         s = check_launch(e, "gemm");
         if (cudaStreamSynchronize(e->stream) != cudaSuccess) s = SPL_ERR_DEVICE;
+        int flag = 0;
+        if (s == SPL_OK) { cudaMemcpy(&flag, d_flag, sizeof flag, cudaMemcpyDeviceToHost); if (flag) s = SPL_ERR_TIMEOUT; }
+        if (getenv("SPL_TC_TRACE")) {
+            float ms = 0; cudaEventElapsedTime(&ms, ev0, ev1);
+            fprintf(stderr, "gemm n %d k %d rows %d: %.1f us, %.0f GB/s\n", n, k, rows, ms * 1e3, double(w.bytes()) * blocks / (ms * 1e-3) / 1e9);
+            int t[64]; cudaMemcpy(t, d_flag, sizeof t, cudaMemcpyDeviceToHost);
+            if (t[2] & 0x100)
+                fprintf(stderr, "tc trace, cycles per group: copy [wait codes %d, wait act %d, issue %d] mma [wait act %d, wait A %d, issue %d] "
+                                "dequant(1 of 2 sets) [wait stage %d, convert %d, wait slot %d, store %d] epilogue [wait %d, work %d, final wait %d] groups %d\n",
+                        t[8], t[9], t[10], t[11], t[12], t[13], t[14], t[15], t[16], t[17], t[18], t[19], t[20], t[21]);
+        }
         if (s == SPL_OK) cudaMemcpy2D(out, size_t(n) * 4, d_out, size_t(ld) * 4, size_t(n) * 4, rows, cudaMemcpyDeviceToHost);
     }
+    cudaFree(d_sums); cudaFree(d_flag);
     cudaFree(w.codes); cudaFree(w.sb); cudaFree(d_act32); cudaFree(d_act); cudaFree(d_out); cudaFree(e->partials);
     cudaStreamDestroy(e->stream);
     e->stream = nullptr; e->partials = nullptr;

@@ -11,6 +11,7 @@
 //   journal  [slot][16 rows][value head][260]    fp32: k[128], delta[128], decay, 3 pad
 #pragma once
 #include "spl_common.cuh"
+#include "spl_gemm_tc.cuh"
 
 struct SplGdnParams {
     int rows, runs, channels, key_heads, value_heads, head_dim;
@@ -65,8 +66,7 @@ __device__ __forceinline__ float spl_gdn_update(float s, float decay, float k, f
 __global__ void __launch_bounds__(256)
 spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict__ proj, const uint16_t *__restrict__ a_log,
                           const uint16_t *__restrict__ dt_bias, const uint16_t *__restrict__ norm_weight, float *state, float *journal,
-                          const uint32_t *__restrict__ runs, const uint32_t *__restrict__ run_info, __nv_bfloat16 *core, float *core_sums,
-                          SplGdnParams p) {
+                          const uint32_t *__restrict__ runs, const uint32_t *__restrict__ run_info, SplOperand core, SplGdnParams p) {
     constexpr int D = SPL_GDN_D, TC = SPL_GDN_TC;
     __shared__ __align__(16) float q_s[TC][D], k_s[TC][D], v_s[TC][D], o_s[TC][D];
     __shared__ float scal[TC][4];        // invQ, invK, decay, beta
@@ -172,13 +172,13 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
             const float r2 = spl_bf16_to_float(uint16_t(w.y)) * ov.z * inv * spl_silu_exact(z.z);
             const float r3 = spl_bf16_to_float(uint16_t(w.y >> 16)) * ov.w * inv * spl_silu_exact(z.w);
             const uint16_t b0 = spl_float_to_bf16(r0), b1 = spl_float_to_bf16(r1), b2 = spl_float_to_bf16(r2), b3 = spl_float_to_bf16(r3);
-            *reinterpret_cast<uint2 *>(core + row * (size_t(VH) * D) + h * D + lane * 4) =
-                make_uint2(uint32_t(b0) | (uint32_t(b1) << 16), uint32_t(b2) | (uint32_t(b3) << 16));
+            *reinterpret_cast<uint2 *>(core.values + core.at(int(row), h * D + lane * 4)) =
+                spl_operand_pack4(spl_bf16_to_float(b0), spl_bf16_to_float(b1), spl_bf16_to_float(b2), spl_bf16_to_float(b3));
             // The following GEMM's per-64 sums: a 128-wide head is two quant groups, sixteen lanes each.
             float gsum = (spl_bf16_to_float(b0) + spl_bf16_to_float(b1)) + (spl_bf16_to_float(b2) + spl_bf16_to_float(b3));
 #pragma unroll
             for (int o = 8; o > 0; o >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o);
-            if ((lane & 15) == 0) core_sums[row * (size_t(VH) * D / 64) + h * 2 + (lane >> 4)] = gsum;
+            if ((lane & 15) == 0) core.put_sum(int(row), h * 2 + (lane >> 4), gsum);
         }
     }
     if (!speculative) {

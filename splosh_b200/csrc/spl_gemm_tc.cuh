@@ -1,0 +1,527 @@
+// spl_gemm_tc.cuh — MLX affine-4 (group 64) dequant-GEMM on the 5th-generation tensor cores.
+//
+// Stands in for Engine.gemm and the q4 kernels it selects (Sources/SploshRuntime/Engine.swift:1651-1806;
+// Sources/Shaders/engine_na.metal:188-428, 862-1011). The numerical contract is the reference's
+// accelerator path (engine_na.metal:42-57, 91-103):
+//
+//   out[r][n] = sum over 64-groups g of ( dot(a[r][g], code[n][g]) * scale[n][g] + sum(a[r][g]) * bias[n][g] ) (+ residual[r][n])
+//
+// with a the bf16-rounded activations and sum(a) the fp32 per-64 sums of the rounded values.
+//
+// Shape of the computation. The product is taken transposed, D[n][r] = w[n][k] * a[r][k]^T, so
+// that 128 output columns are the M dimension of one tcgen05.mma and the step's rows (16..64 per
+// tile) are its N dimension. Per quant group (K = 64, four k16 instructions):
+//   * TMA bulk copies bring four groups at a time into shared memory: 16 KiB of codes, and the
+//     activations' slice with its per-64 sums and the scale/bias words;
+//   * dequant warps (one thread per output column, two sets taking alternate groups) turn the codes
+//     into exact fp16 values scale * (code - 8) and write them into tensor memory as the A operand
+//     (tcgen05.st), so weights never pass through shared memory expanded and are never re-read;
+//   * the activations' producer already wrote them (bf16-rounded, held as fp16) in the
+//     128-byte-swizzled K-major image the tensor core reads as the B operand;
+//   * one thread issues the four tcgen05.mma; the accumulator stays in tensor memory for the
+//     whole contraction;
+//   * epilogue warps (again one thread per output column) add (bias + 8 scale) * sum per group in
+//     fp32 registers and, at the end, the accumulator (tcgen05.ld).
+// Everything is ordered by mbarriers. Every wait is bounded: a wait that runs out sets an error
+// word and the block unwinds, still releasing its tensor memory.
+//
+// Device layout of a weight (private to this library): for each tile of 128 output columns and each
+// group, 4,096 bytes of codes [half h][column n][16 bytes] holding k = 64 g + 32 h + 0..31, each
+// 32-bit word's nibbles in the order [k0 k2 k4 k6 k1 k3 k5 k7] so that (word >> 4j) & 0x000F000F is
+// the bf16 pair (k_2j, k_2j+1); and 128 words (scale | bias << 16) per (tile, group).
+#pragma once
+#include "spl_common.cuh"
+
+struct SplQ4Dev {
+    int n = 0;            // logical output columns
+    int ld = 0;           // columns rounded up to 16: the width of an output row
+    int tiles = 0;        // 128-column tiles
+    int k = 0;            // contraction length, a multiple of 64
+    uint32_t *codes = nullptr;      // [tiles][k/64][2][128][4] words
+    uint32_t *sb = nullptr;         // [tiles][k/64][128] words
+    size_t bytes() const { return size_t(ld) * (k / 64) * 36; }   // algorithmic: 32 B of codes + 4 B of scale and bias per (column, group)
+    size_t device_bytes() const { return size_t(tiles) * (k / 64) * (4096 + 512); }
+};
+
+// ---- operand (B side) layout ------------------------------------------------------------------
+// A GEMM's activation operand is the bf16-rounded activations held as fp16 (the tensor-core instruction wants
+// both operands in one 16-bit format, and the weights need fp16's 11 bits). A bf16 value of magnitude
+// 2^-14 .. 65504 is exact in fp16; a smaller one moves by at most 2^-25, below the fp32 accumulator's own
+// rounding for activations of order one. The per-64 sums are taken from the bf16 values themselves.
+// The operand is cut in 64-wide groups and in row blocks of RN rows (RN = 16, 32 or 64, fixed per step). Block (g, rb) is RN * 128 bytes: row r at (r / 8) * 1024 + (r % 8) * 128,
+// its eight 16-byte units XOR-swizzled by r % 8: the canonical K-major SWIZZLE_128B image. The
+// per-64 sums sit beside it as fp32 [g][rb][RN].
+// Four bf16-rounded values (as floats) -> four fp16 in two words.
+__device__ __forceinline__ uint2 spl_operand_pack4(float r0, float r1, float r2, float r3) {
+    const __half2 lo = __floats2half2_rn(r0, r1), hi = __floats2half2_rn(r2, r3);
+    return make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
+}
+
+struct SplOperand {
+    __nv_bfloat16 *values;      // 16-bit cells (fp16 bits of the bf16-rounded values)
+    float *sums;
+    int rn, blocks;            // rows per block, row blocks
+    __device__ __forceinline__ size_t at(int row, int k) const {
+        const int g = k >> 6, kk = k & 63, rb = row / rn, r = row % rn;
+        return (size_t(g) * blocks + rb) * (size_t(rn) * 64) + size_t(r >> 3) * 512 + (r & 7) * 64 + (((kk >> 3) ^ (r & 7)) << 3) + (kk & 7);
+    }
+    __device__ __forceinline__ void put_sum(int row, int g, float sum) const { sums[(size_t(g) * blocks + row / rn) * rn + row % rn] = sum; }
+};
+
+// ---- repack: MLX row-major -> tile layout, rows [n0, n0 + rows) of a fused tensor ------------
+__global__ void spl_repack_q4_kernel(const uint32_t *__restrict__ packed, const uint16_t *__restrict__ scales,
+                                     const uint16_t *__restrict__ biases, int rows, int k, uint32_t *codes, uint32_t *sb, int n0, int *out_of_range) {
+    const int groups = k / 64, words = k / 8;
+    const size_t total = size_t(rows) * words;
+    for (size_t idx = blockIdx.x * size_t(blockDim.x) + threadIdx.x; idx < total; idx += size_t(gridDim.x) * blockDim.x) {
+        const int row = int(idx / words), w = int(idx % words);
+        const uint32_t src = packed[idx];
+        // nibbles [0 1 2 3 4 5 6 7] -> [0 2 4 6 1 3 5 7]
+        uint32_t dst = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            dst |= ((src >> (8 * j)) & 0xFu) << (4 * j);
+            dst |= ((src >> (8 * j + 4)) & 0xFu) << (4 * j + 16);
+        }
+        const int n = n0 + row, tile = n >> 7, col = n & 127, g = w >> 3, h = (w >> 2) & 1, j = w & 3;
+        codes[(((size_t(tile) * groups + g) * 2 + h) * 128 + col) * 4 + j] = dst;
+        if ((w & 7) == 0) {
+            const uint16_t sbits = scales[size_t(row) * groups + g];
+            sb[(size_t(tile) * groups + g) * 128 + col] = uint32_t(sbits) | (uint32_t(biases[size_t(row) * groups + g]) << 16);
+            // The GEMM holds scale * (code - 8) in fp16: the scale must be zero or a normal fp16 number with room for a factor 8.
+            const float sc = fabsf(spl_bf16_to_float(sbits));
+            if (!(sc == 0.0f || (sc >= 6.103515625e-05f && sc <= 8188.0f))) atomicExch(out_of_range, 1);
+        }
+    }
+}
+
+// ---- seeded generator: value n of a tensor's stream, quantised group by group ---------------
+// Value = (sum of the four 16-bit fields of SplitMix64 output n, less 131070) * factor; then the
+// MLX rule: scale = bf16((max - min) / 15) (1 when flat), bias = bf16(min),
+// code = clamp(round_half_away((v - bias) / scale), 0, 15)  (DraftModel.swift:634-670, "minmax").
+// Every operation is a single IEEE operation so that a host generator reproduces it exactly.
+__global__ void spl_synth_q4_kernel(uint64_t seed, float factor, int rows, int k, uint32_t *packed, uint16_t *scales, uint16_t *biases) {
+    const int groups = k / 64;
+    const size_t total = size_t(rows) * groups;
+    for (size_t slot = blockIdx.x * size_t(blockDim.x) + threadIdx.x; slot < total; slot += size_t(gridDim.x) * blockDim.x) {
+        const size_t first = slot * 64;       // row * k + g * 64
+        float lo = INFINITY, hi = -INFINITY;
+        for (int i = 0; i < 64; ++i) {
+            const uint64_t z = spl_splitmix_at(seed, first + i);
+            const int sum = int(z & 0xFFFF) + int((z >> 16) & 0xFFFF) + int((z >> 32) & 0xFFFF) + int(z >> 48);
+            const float v = __fmul_rn(float(sum - 131070), factor);
+            lo = fminf(lo, v); hi = fmaxf(hi, v);
+        }
+        const uint16_t sbits = spl_float_to_bf16(hi > lo ? __fdiv_rn(__fsub_rn(hi, lo), 15.0f) : 1.0f);
+        const uint16_t bbits = spl_float_to_bf16(lo);
+        const float scale = spl_bf16_to_float(sbits), bias = spl_bf16_to_float(bbits);
+        scales[slot] = sbits; biases[slot] = bbits;
+        for (int w = 0; w < 8; ++w) {
+            uint32_t bits = 0;
+            for (int nib = 0; nib < 8; ++nib) {
+                const uint64_t z = spl_splitmix_at(seed, first + w * 8 + nib);
+                const int sum = int(z & 0xFFFF) + int((z >> 16) & 0xFFFF) + int((z >> 32) & 0xFFFF) + int(z >> 48);
+                const float v = __fmul_rn(float(sum - 131070), factor);
+                const float code = fminf(15.0f, fmaxf(0.0f, roundf(__fdiv_rn(__fsub_rn(v, bias), scale))));
+                bits |= uint32_t(code) << (4 * nib);
+            }
+            packed[slot * 8 + w] = bits;
+        }
+    }
+}
+
+// ---- PTX wrappers -----------------------------------------------------------------------------
+#define SPL_WAIT_LIMIT (1u << 22)     // polls before a wait gives up
+
+__device__ __forceinline__ uint32_t spl_smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void spl_mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(spl_smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void spl_mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(spl_smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void spl_mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(spl_smem_addr(bar)), "r"(bytes) : "memory");
+}
+// Bounded wait on a phase parity. Returns false when the limit ran out.
+__device__ __forceinline__ bool spl_mbar_wait(uint64_t *bar, uint32_t parity) {
+    const uint32_t addr = spl_smem_addr(bar);
+    for (uint32_t spin = 0; spin < SPL_WAIT_LIMIT; ++spin) {
+        uint32_t done;
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void spl_bulk_g2s(void *smem, const void *gmem, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(spl_smem_addr(smem)), "l"(gmem), "r"(bytes), "r"(spl_smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void spl_tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void spl_tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void spl_tc_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(spl_smem_addr(bar)) : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem descriptor]; one thread issues.
+__device__ __forceinline__ void spl_tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// K-major, 128-byte swizzle, rows of 128 bytes, eight-row groups 1,024 bytes apart.
+__device__ __forceinline__ uint64_t spl_tc_desc_sw128(uint32_t smem_byte_addr) {
+    uint64_t d = 0;
+    d |= uint64_t((smem_byte_addr & 0x3FFFFu) >> 4);        // start address
+    d |= uint64_t(1) << 16;                                 // leading byte offset (unused with this swizzle)
+    d |= uint64_t(1024 >> 4) << 32;                         // stride byte offset
+    d |= uint64_t(1) << 46;                                 // descriptor version of sm_100
+    d |= uint64_t(2) << 61;                                 // SWIZZLE_128B
+    return d;
+}
+// kind::f16 instruction descriptor: fp32 accumulate, A and B fp16 (format 0), both K-major, M = 128, N = n.
+__host__ __device__ constexpr uint32_t spl_tc_idesc(int n) {
+    return (1u << 4) | (0u << 7) | (0u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(128 >> 4) << 24);
+}
+
+#define SPL_TC_LD(N, regs, addr) spl_tc_ld##N(regs, addr)
+__device__ __forceinline__ void spl_tc_ld16(uint32_t (&r)[16], uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
+                   "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]) : "r"(taddr));
+}
+__device__ __forceinline__ void spl_tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void spl_tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+__device__ __forceinline__ void spl_tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+                   "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+
+// Eight 4-bit codes of a word -> four bf16x2 registers of exact values: 0x4300 | c is 128 + c.
+__device__ __forceinline__ void spl_codes4(uint32_t w, uint32_t *a) {
+    const __nv_bfloat162 bias128 = __floats2bfloat162_rn(128.0f, 128.0f);
+    uint32_t q0 = (w & 0x000F000Fu) | 0x43004300u;
+    uint32_t q1 = ((w >> 4) & 0x000F000Fu) | 0x43004300u;
+    uint32_t q2 = ((w >> 8) & 0x000F000Fu) | 0x43004300u;
+    uint32_t q3 = ((w >> 12) & 0x000F000Fu) | 0x43004300u;
+    __nv_bfloat162 c0 = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&q0), bias128);
+    __nv_bfloat162 c1 = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&q1), bias128);
+    __nv_bfloat162 c2 = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&q2), bias128);
+    __nv_bfloat162 c3 = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&q3), bias128);
+    a[0] = *reinterpret_cast<uint32_t *>(&c0); a[1] = *reinterpret_cast<uint32_t *>(&c1);
+    a[2] = *reinterpret_cast<uint32_t *>(&c2); a[3] = *reinterpret_cast<uint32_t *>(&c3);
+}
+
+// ---- the kernel -------------------------------------------------------------------------------
+// How the contract is kept without draining the accumulator after every group. With c the 4-bit code,
+//   scale * c + bias = scale * (c - 8) + (bias + 8 * scale).
+// scale is bf16 (8 significant bits) and |c - 8| <= 8, so scale * (c - 8) has at most 11 significant bits:
+// it is EXACT in fp16 (for scales in fp16's normal range, checked when a weight is loaded). The tensor cores
+// therefore multiply exact fp16 weights by the bf16-rounded activations (held as fp16) and accumulate every group of the
+// contraction in one fp32 accumulator; the other term, (bias + 8 scale) * sum(a), is an fp32 multiply-add
+// per group in the epilogue warps, which have nothing else to do until the end. The result is the
+// reference's sum of exact per-group terms up to the order of fp32 additions.
+#define SPL_TC_SUPER 4           // groups per shared-memory stage: one bulk copy brings 256 of the contraction
+#define SPL_TC_CSTAGES 4         // stages of codes (16 KiB each), handed back as soon as they are in registers
+#define SPL_TC_ASUPERS 3         // A operand stages in tensor memory: three times four groups of 32 columns; accumulators take the first 128 columns
+#define SPL_TC_ASTAGES (SPL_TC_ASUPERS * SPL_TC_SUPER)
+#define SPL_TC_THREADS 480       // warps 0-3 and 8-11 dequant (even / odd groups), 4-7 epilogue, 12 copies, 13-14 tensor-core issue
+
+// Stages of activations, sums and scale/bias words: they are held until the tensor core has finished with them.
+__host__ __device__ constexpr int spl_tc_bstages(int rn) { return rn >= 64 ? 4 : 6; }
+__host__ __device__ constexpr size_t spl_tc_bstage_bytes(int rn) { return size_t(SPL_TC_SUPER) * (size_t(rn) * 128 + size_t(rn) * 4 + 512); }
+__host__ __device__ constexpr size_t spl_tc_smem_bytes(int rn) {
+    return 1024 /* alignment slack */ + size_t(SPL_TC_CSTAGES) * SPL_TC_SUPER * 4096 + size_t(spl_tc_bstages(rn)) * spl_tc_bstage_bytes(rn) + 1024 /* barriers */;
+}
+
+// Grid (tiles, splits, row blocks in use). Block (t, s, rb) computes columns [128 t, 128 t + 128) of rows
+// [RN rb, RN rb + RN) over groups [s * gps, (s + 1) * gps) and writes them to `out`, or, when the
+// contraction is split, to partials[s][row][column] for spl_gemm_reduce_kernel.
+template <int RN>
+__global__ void __launch_bounds__(SPL_TC_THREADS, 1)
+spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__restrict__ sb, const __nv_bfloat16 *__restrict__ act,
+                      const float *__restrict__ act_sums, float *out, int out_ld, const float *residual, float *partials,
+                      int rows, int op_blocks, int groups, int groups_per_split, int *error_flag) {
+    constexpr int BST = spl_tc_bstages(RN), CST = SPL_TC_CSTAGES, AST = SPL_TC_ASTAGES;
+    constexpr int BTILE = SPL_TC_SUPER * RN * 128, WSTAGE = SPL_TC_SUPER * 4096, SSTAGE = SPL_TC_SUPER * RN, QSTAGE = SPL_TC_SUPER * 128;
+    extern __shared__ unsigned char spl_tc_smem_raw[];
+    // The swizzled activation tiles must sit on 1,024-byte boundaries.
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(spl_tc_smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char *b_ring = smem;                                                       // [BST][SUPER][RN * 128] activations
+    unsigned char *w_ring = b_ring + size_t(BST) * BTILE;                               // [CST][SUPER][4096] codes
+    uint32_t *q_ring = reinterpret_cast<uint32_t *>(w_ring + size_t(CST) * WSTAGE);     // [BST][SUPER][128] scale | bias << 16
+    float *s_ring = reinterpret_cast<float *>(q_ring + BST * QSTAGE);                   // [BST][SUPER][RN] per-64 sums
+    uint64_t *bars = reinterpret_cast<uint64_t *>(s_ring + BST * SSTAGE);
+    uint64_t *full_c = bars, *empty_c = full_c + CST, *full_b = empty_c + CST, *empty_b = full_b + BST;
+    uint64_t *full_a = empty_b + BST, *done = full_a + AST, *finished = done + AST;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(finished + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, split = blockIdx.y, rb = blockIdx.z, row_blocks = op_blocks;   // the operand's row blocks (>= gridDim.z)
+    const int rows_padded = op_blocks * RN;
+    const int g_first = split * groups_per_split;
+    const int g_count = min(groups_per_split, groups - g_first);
+    const int supers = (g_count + SPL_TC_SUPER - 1) / SPL_TC_SUPER;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < CST; ++i) { spl_mbar_init(&full_c[i], 1); spl_mbar_init(&empty_c[i], 8); }       // the eight dequant warps
+        for (int i = 0; i < BST; ++i) { spl_mbar_init(&full_b[i], 1); spl_mbar_init(&empty_b[i], 6); }       // the two issuing threads and the four epilogue warps
+        for (int i = 0; i < AST / 2; ++i) spl_mbar_init(&full_a[i], 4);      // one per unit of two groups
+        for (int i = 0; i < SPL_TC_ASUPERS; ++i) spl_mbar_init(&done[i], 2);      // one completion per four groups from each issuing thread
+        spl_mbar_init(finished, 2);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 13) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(spl_smem_addr(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    spl_tc_fence_before();
+    __syncthreads();
+    spl_tc_fence_after();
+    const uint32_t tmem = *tmem_slot;                 // lane 0, first allocated column
+    // Consecutive instructions into one accumulator wait for each other (the pipeline's latency is longer than
+    // so small an instruction), so the k16 steps rotate over NACC accumulators; the epilogue adds them in order.
+    constexpr int NACC = RN <= 32 ? 4 : 2;
+    const uint32_t tmem_d = tmem, tmem_a = tmem + 128;
+    bool ok = true;
+    // Debug trace: cycles per group that one thread of each role of block (0, 0, 0) spends in its waits and its work.
+    const bool trace = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && error_flag[1] == 0x7ACE && (error_flag[2] & 0x100);
+    long long t0 = 0, t1 = 0, t2 = 0, t3 = 0, t_mark = 0;
+#define SPL_T0() do { if (trace) t_mark = clock64(); } while (0)
+#define SPL_T1(acc) do { if (trace) { const long long now__ = clock64(); acc += now__ - t_mark; t_mark = now__; } } while (0)
+
+    if (warp == 12) {
+        // ---- copies. Codes have their own ring; activations, their sums and the scale/bias words share the other.
+        if (lane == 0) {
+            const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(codes) + (size_t(tile) * groups + g_first) * 4096;
+            const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(act) + ((size_t(g_first) * row_blocks + rb) * RN) * 128;
+            const float *ssrc = act_sums + (size_t(g_first) * row_blocks + rb) * RN;
+            const uint32_t *qsrc = sb + (size_t(tile) * groups + g_first) * 128;
+            // Every block of a GEMM reads the same activation lines. Blocks therefore walk the contraction from
+            // different starting points (the order of a sum of groups does not matter beyond fp32 rounding, and it
+            // is a fixed function of the tile), so that at any moment they ask L2 for different lines.
+            const int rot = (g_count % SPL_TC_SUPER == 0 && supers > 1) ? int((uint32_t(tile) * 2654435761u >> 12) % uint32_t(supers)) : 0;
+            for (int j0 = 0; j0 < supers && ok; ++j0) {
+                const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;      // the stage's source; j0 is its place in the pipeline
+                const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);         // with a rotation every stage is full
+                const int sc = j0 % CST, sbq = j0 % BST;
+                SPL_T0();
+                ok = spl_mbar_wait(&empty_c[sc], ((j0 / CST) & 1) ^ 1);
+                SPL_T1(t0);
+                if (!ok) break;
+                spl_mbar_expect_tx(&full_c[sc], uint32_t(n) * 4096);
+                spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[sc]);
+                SPL_T1(t2);
+                ok = spl_mbar_wait(&empty_b[sbq], ((j0 / BST) & 1) ^ 1);
+                SPL_T1(t1);
+                if (!ok) break;
+                spl_mbar_expect_tx(&full_b[sbq], uint32_t(n) * (RN * 128 + RN * 4 + 512));
+                spl_bulk_g2s(q_ring + sbq * QSTAGE, qsrc + size_t(j) * QSTAGE, uint32_t(n) * 512, &full_b[sbq]);
+                if (row_blocks == 1) {
+                    spl_bulk_g2s(b_ring + size_t(sbq) * BTILE, bsrc + size_t(j) * BTILE, uint32_t(n) * RN * 128, &full_b[sbq]);
+                    spl_bulk_g2s(s_ring + sbq * SSTAGE, ssrc + size_t(j) * SSTAGE, uint32_t(n) * RN * 4, &full_b[sbq]);
+                } else {
+                    for (int u = 0; u < n; ++u) {
+                        const size_t g = size_t(j) * SPL_TC_SUPER + u;
+                        spl_bulk_g2s(b_ring + size_t(sbq) * BTILE + u * RN * 128, bsrc + g * row_blocks * RN * 128, RN * 128, &full_b[sbq]);
+                        spl_bulk_g2s(s_ring + sbq * SSTAGE + u * RN, ssrc + g * row_blocks * RN, RN * 4, &full_b[sbq]);
+                    }
+                }
+                SPL_T1(t2);
+            }
+            if (trace) { error_flag[8] = int(t0 / g_count); error_flag[9] = int(t1 / g_count); error_flag[10] = int(t2 / g_count); }
+        }
+    } else if (warp >= 13) {
+        // ---- tensor-core issue: D[128 x RN] += A[128 x 64] (fp16, tensor memory) * B[RN x 64]^T (fp16, shared memory).
+        // Issuing one tcgen05.mma costs its thread about ninety cycles, so two threads share the work: warp 13 issues
+        // the first two k16 steps of every group and warp 14 the last two, each into accumulators of its own.
+        const int m = warp - 13;
+        if (lane == 0) {
+            constexpr uint32_t idesc = spl_tc_idesc(RN);
+            // Two groups (a "unit", K = 128) share one hand-over from the dequant warps.
+            const int units = (g_count + 1) / 2;
+            for (int un = 0; un < units && ok; ++un) {
+                const int j = un / 2, sbq = j % BST, au = un % (AST / 2);
+                SPL_T0();
+                if ((un & 1) == 0) ok = spl_mbar_wait(&full_b[sbq], (j / BST) & 1);
+                SPL_T1(t0);
+                ok = ok && spl_mbar_wait(&full_a[au], (un / (AST / 2)) & 1);
+                SPL_T1(t1);
+                if (!ok) break;
+                spl_tc_fence_after();
+#pragma unroll
+                for (int v = 0; v < 2; ++v) {
+                    const int i = 2 * un + v, u = i % SPL_TC_SUPER, sa = i % AST;
+                    if (i >= g_count) break;
+                    const uint32_t b_addr = spl_smem_addr(b_ring + size_t(sbq) * BTILE + u * RN * 128);
+#pragma unroll
+                    for (int l = 0; l < 2; ++l) {
+                        const int ks = 2 * m + l;
+                        const int a = NACC == 4 ? ks : m;                       // this thread's accumulator for the step
+                        const uint32_t accumulate = (i > 0 || (NACC == 2 && l > 0)) ? 1u : 0u;
+                        spl_tc_mma_ts(tmem_d + a * RN, tmem_a + sa * 32 + ks * 8, spl_tc_desc_sw128(b_addr + ks * 32), idesc, accumulate);
+                    }
+                }
+                if ((un & 1) == 1 || un == units - 1) {
+                    spl_tc_commit(&done[j % SPL_TC_ASUPERS]);     // the stage's A slots may be rewritten
+                    spl_tc_commit(&empty_b[sbq]);                 // its activations have been read
+                }
+                SPL_T1(t2);
+            }
+            if (trace && m == 0) { error_flag[11] = int(t0 / g_count); error_flag[12] = int(t1 / g_count); error_flag[13] = int(t2 / g_count); }
+            if (ok) spl_tc_commit(finished);
+        }
+    } else if (warp < 4 || warp >= 8) {
+        // ---- dequant: thread = output column; codes -> scale * (code - 8), exact in fp16 -> tensor memory. Warps 0-3
+        // take the even groups, warps 8-11 the odd ones; both sets write the lanes of their warp index mod 4.
+        const int quarter = warp & 3, col = quarter * 32 + lane, parity = warp >> 3;
+        const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+        const __half2 c1032 = __floats2half2_rn(1032.0f, 1032.0f);
+        for (int j = 0; j < supers && ok; ++j) {
+            const int sc = j % CST, sbq = j % BST;
+            SPL_T0();
+            ok = spl_mbar_wait(&full_c[sc], (j / CST) & 1) && spl_mbar_wait(&full_b[sbq], (j / BST) & 1);
+            SPL_T1(t0);
+            if (!ok) break;
+            const int n = min(SPL_TC_SUPER, g_count - j * SPL_TC_SUPER);
+            // This warp's unit of the stage: groups 2 * parity and 2 * parity + 1, read before either is converted so
+            // that the codes can be handed back at once.
+            uint4 lo[2], hi[2];
+            __half2 s2[2];
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+                const int u = 2 * parity + v;
+                if (u < n) {
+                    lo[v] = *reinterpret_cast<const uint4 *>(w_ring + size_t(sc) * WSTAGE + u * 4096 + col * 16);
+                    hi[v] = *reinterpret_cast<const uint4 *>(w_ring + size_t(sc) * WSTAGE + u * 4096 + 2048 + col * 16);
+                    const float sf = __uint_as_float(q_ring[sbq * QSTAGE + u * 128 + col] << 16);
+                    s2[v] = __float2half2_rn(sf);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) spl_mbar_arrive(&empty_c[sc]);
+            if (2 * parity >= n) continue;                       // a short last stage may leave the second set nothing
+            uint32_t a[2][32];
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+                const uint32_t w8[8] = {lo[v].x, lo[v].y, lo[v].z, lo[v].w, hi[v].x, hi[v].y, hi[v].z, hi[v].w};
+#pragma unroll
+                for (int w = 0; w < 8; ++w)
+#pragma unroll
+                    for (int p = 0; p < 4; ++p) {
+                        uint32_t q = ((w8[w] >> (4 * p)) & 0x000F000Fu) | 0x64006400u;       // fp16 1024 + code, twice
+                        const __half2 h = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&q), c1032), s2[v]);
+                        a[v][4 * w + p] = *reinterpret_cast<const uint32_t *>(&h);
+                    }
+            }
+            SPL_T1(t1);
+            if (j >= SPL_TC_ASUPERS) ok = spl_mbar_wait(&done[j % SPL_TC_ASUPERS], ((j / SPL_TC_ASUPERS) & 1) ^ 1);
+            SPL_T1(t2);
+            if (!ok) break;
+            spl_tc_fence_after();
+            const int un = 2 * j + parity;                       // the unit's index and its A slots
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+                const int i = j * SPL_TC_SUPER + 2 * parity + v, sa = i % AST;
+                if (2 * parity + v < n) {
+                    spl_tc_st16(tmem_a + lane_base + sa * 32, *reinterpret_cast<uint32_t (*)[16]>(&a[v][0]));
+                    spl_tc_st16(tmem_a + lane_base + sa * 32 + 16, *reinterpret_cast<uint32_t (*)[16]>(&a[v][16]));
+                }
+            }
+            spl_tc_st_wait();
+            spl_tc_fence_before();
+            __syncwarp();
+            if (lane == 0) spl_mbar_arrive(&full_a[un % (AST / 2)]);
+            SPL_T1(t3);
+        }
+        if (trace && warp == 0 && lane == 0) { error_flag[14] = int(t0 / g_count); error_flag[15] = int(t1 / g_count); error_flag[16] = int(t2 / g_count); error_flag[17] = int(t3 / g_count); }
+    } else {
+        // ---- epilogue: thread = output column. Per group acc[r] += (bias + 8 scale) * sum[r]; at the end the
+        // tensor cores' accumulator is added.
+        const int q = warp - 4, col = q * 32 + lane;
+        const uint32_t lane_base = uint32_t(q * 32) << 16;
+        float acc[RN];
+#pragma unroll
+        for (int r = 0; r < RN; ++r) acc[r] = 0.0f;
+        for (int j = 0; j < supers && ok; ++j) {
+            const int sbq = j % BST;
+            SPL_T0();
+            ok = spl_mbar_wait(&full_b[sbq], (j / BST) & 1);
+            SPL_T1(t0);
+            if (!ok) break;
+            const int n = min(SPL_TC_SUPER, g_count - j * SPL_TC_SUPER);
+            for (int u = 0; u < n; ++u) {
+                const uint32_t x = q_ring[sbq * QSTAGE + u * 128 + col];
+                const float bias8 = fmaf(8.0f, __uint_as_float(x << 16), __uint_as_float(x & 0xFFFF0000u));
+                const float *sums = s_ring + sbq * SSTAGE + u * RN;
+#pragma unroll
+                for (int r4 = 0; r4 < RN / 4; ++r4) {
+                    const float4 sm = *reinterpret_cast<const float4 *>(sums + 4 * r4);
+                    acc[4 * r4 + 0] = fmaf(sm.x, bias8, acc[4 * r4 + 0]); acc[4 * r4 + 1] = fmaf(sm.y, bias8, acc[4 * r4 + 1]);
+                    acc[4 * r4 + 2] = fmaf(sm.z, bias8, acc[4 * r4 + 2]); acc[4 * r4 + 3] = fmaf(sm.w, bias8, acc[4 * r4 + 3]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) spl_mbar_arrive(&empty_b[sbq]);
+            SPL_T1(t1);
+        }
+        SPL_T0();
+        if (ok) ok = spl_mbar_wait(finished, 0);
+        SPL_T1(t2);
+        if (trace && warp == 4 && lane == 0) { error_flag[18] = int(t0 / g_count); error_flag[19] = int(t1 / g_count); error_flag[20] = int(t2 / g_count); error_flag[21] = g_count; }
+        if (ok) {
+            spl_tc_fence_after();
+            const int n = tile * 128 + col;
+            const bool is_split = gridDim.y > 1;
+            float *dst = is_split ? partials + size_t(split) * rows_padded * out_ld : out;
+#pragma unroll
+            for (int c0 = 0; c0 < RN; c0 += 16) {
+                float total[16];
+#pragma unroll
+                for (int a = 0; a < NACC; ++a) {
+                    uint32_t v[16];
+                    spl_tc_ld16(v, tmem_d + lane_base + a * RN + c0);
+                    spl_tc_ld_wait();
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) total[r] = a == 0 ? __uint_as_float(v[r]) : total[r] + __uint_as_float(v[r]);
+                }
+                if (n < out_ld) {
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        const int row = rb * RN + c0 + r;
+                        if (row < rows) {
+                            const size_t index = size_t(row) * out_ld + n;
+                            const float value = acc[c0 + r] + total[r];
+                            dst[index] = (!is_split && residual) ? value + residual[index] : value;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (!ok) atomicExch(error_flag, 1 + warp);
+    spl_tc_fence_before();
+    __syncthreads();
+    if (warp == 13) {
+        spl_tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+// out[r][n] = sum over splits, in split order, of partials[s][r][n] (+ residual[r][n]).
+__global__ void spl_gemm_reduce_kernel(const float *__restrict__ partials, int splits, int rows_padded, int rows, int ld,
+                                       const float *residual, float *out) {
+    const size_t total = size_t(rows) * ld / 4;
+    for (size_t idx = blockIdx.x * size_t(blockDim.x) + threadIdx.x; idx < total; idx += size_t(gridDim.x) * blockDim.x) {
+        float4 sum = reinterpret_cast<const float4 *>(partials)[idx];
+        for (int s = 1; s < splits; ++s) {
+            const float4 p = reinterpret_cast<const float4 *>(partials + size_t(s) * rows_padded * ld)[idx];
+            sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
+        }
+        if (residual) {
+            const float4 r = reinterpret_cast<const float4 *>(residual)[idx];
+            sum.x += r.x; sum.y += r.y; sum.z += r.z; sum.w += r.w;
+        }
+        reinterpret_cast<float4 *>(out)[idx] = sum;
+    }
+}
