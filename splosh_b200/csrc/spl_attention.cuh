@@ -5,16 +5,26 @@
 // 2044-2094), the span scan sp_attn_scan_i8_r48c64s8 (Sources/Shaders/candidates/attn_scan_r.metal:46-202)
 // and sp_attn_merge (Sources/Shaders/engine.metal:2218-2255).
 //
-// HBM layout (per attention layer; pages of 256 tokens shared by all slots):
-//   k codes  [page][kv head][token 256][head_dim]  int8
-//   v codes  [page][kv head][head_dim][token 256]  int8   (transposed: P.V reads 16 consecutive
-//                                                          tokens of one channel as one 16-byte load)
+// HBM layout (per attention layer; pages of 256 tokens shared by all slots). A page of one kv head is two
+// chunks of 128 tokens; a chunk of K, of V and of each scale array is contiguous, so one bulk copy brings it
+// to shared memory, and inside a chunk the 16-byte pieces are ordered so that the thread that converts a
+// token's K (or a channel's V) reads consecutive pieces with its neighbours (no bank conflicts):
+//   k codes  [page][kv head][chunk 2][channel block head_dim/16][token 128][16 channels]   int8
+//   v codes  [page][kv head][chunk 2][token block 8][channel head_dim][16 tokens]          int8
 //   k scale, v scale  [page][kv head][token 256]   fp32, value = scale * code
 // A K or V vector is symmetric int8: scale = max|x| / 127 (1 when all zero),
 // code = clamp(rint(x / scale), -127, 127) (engine_na.metal:2084-2093).
 #pragma once
 #include "spl_common.cuh"
 #include "spl_gemm_tc.cuh"
+
+// Index of channel `d` of token `in_page` in the code arrays; vec = page * kv_heads + kv_head.
+__host__ __device__ __forceinline__ size_t spl_k_code_index(size_t vec, uint32_t in_page, int d, int hd) {
+    return vec * (SPL_PAGE_TOKENS * size_t(hd)) + size_t(in_page >> 7) * (128 * size_t(hd)) + size_t(d >> 4) * 2048 + (in_page & 127) * 16 + (d & 15);
+}
+__host__ __device__ __forceinline__ size_t spl_v_code_index(size_t vec, uint32_t in_page, int d, int hd) {
+    return vec * (SPL_PAGE_TOKENS * size_t(hd)) + size_t(in_page >> 7) * (128 * size_t(hd)) + size_t((in_page & 127) >> 4) * (16 * size_t(hd)) + size_t(d) * 16 + (in_page & 15);
+}
 
 struct SplAttnParams {
     int rows, live, heads, kv_heads, head_dim, rotary, max_pages;
@@ -79,227 +89,403 @@ spl_attn_prepare_kernel(const float *__restrict__ proj, const uint16_t *__restri
     const size_t vec = size_t(page) * p.kv_heads + head;
     const uint32_t in_page = position % SPL_PAGE_TOKENS;
     for (int n = 0, i = tid; i < hd; i += 128, ++n) {
-        k_codes[(vec * SPL_PAGE_TOKENS + in_page) * hd + i] = int8_t(fminf(127.0f, fmaxf(-127.0f, rintf(__fdiv_rn(vals[n], ks)))));
-        v_codes[(vec * hd + i) * SPL_PAGE_TOKENS + in_page] = int8_t(fminf(127.0f, fmaxf(-127.0f, rintf(__fdiv_rn(vv[n], vs)))));
+        k_codes[spl_k_code_index(vec, in_page, i, hd)] = int8_t(fminf(127.0f, fmaxf(-127.0f, rintf(__fdiv_rn(vals[n], ks)))));
+        v_codes[spl_v_code_index(vec, in_page, i, hd)] = int8_t(fminf(127.0f, fmaxf(-127.0f, rintf(__fdiv_rn(vv[n], vs)))));
     }
     if (tid == 0) { k_scale[vec * SPL_PAGE_TOKENS + in_page] = ks; v_scale[vec * SPL_PAGE_TOKENS + in_page] = vs; }
 }
 
-// Four int8 in a word -> two half2 (exact): fp16 0x6400 | u is 1024 + u, with u = x + 128.
-__device__ __forceinline__ void spl_s8x4_to_h2x2(uint32_t w, uint32_t &lo, uint32_t &hi) {
-    const uint32_t u = w ^ 0x80808080u;
-    uint32_t a = __byte_perm(u, 0x64646464u, 0x4140), b = __byte_perm(u, 0x64646464u, 0x4342);
-    const __half2 off = __floats2half2_rn(1152.0f, 1152.0f);
-    __half2 ha = __hsub2(*reinterpret_cast<__half2 *>(&a), off), hb = __hsub2(*reinterpret_cast<__half2 *>(&b), off);
-    lo = *reinterpret_cast<uint32_t *>(&ha); hi = *reinterpret_cast<uint32_t *>(&hb);
+// ---- the span scan on the tensor cores ----------------------------------------------------------
+// One block per (kv head, span of pages, attention block of <= 8 rows). The block's queries (rows x the
+// PER_KV heads that share the kv head) are the N = NQ columns of both products, which run TRANSPOSED so that
+// the int8 cache is the tensor cores' A operand, converted to fp16 on its way into tensor memory and never
+// written back to shared memory:
+//   S^T[128 tokens x NQ]   = K[128 x head_dim] Q^T          A = K (tensor memory, lane = token), B = Q (shared)
+//   O^T[head_dim x NQ]    += V^T[head_dim x 128] P^T        A = V^T (tensor memory, lane = channel), B = P (shared)
+// with the online softmax of attn_scan_r.metal:107-160 between them: s = acc * kScale[token] * scale, visible
+// when token < position + 1 of the query's row, P = bf16(p * vScale[token]) (held as fp16 x 4096, exact for
+// normal values). A softmax thread owns one token of the chunk, so a query's maximum over the chunk is a
+// warp reduction (redux) plus a four-way exchange; sums stay per thread until the end of the span.
+// When a maximum moves, the softmax warps rescale O^T in tensor memory before the next value product.
+//
+// Warps: 0 copies (bulk copies of whole 128-token chunks into a ring), 1 tensor-core issue, 4-7 K -> tensor
+// memory, 8-11 V -> tensor memory, 12-15 softmax, rescale and the partial's output. Every wait is bounded.
+// Tensor memory (512 columns): S two buffers at 0 and 64, O halves at 128 and 192, K operand at 256, V at 384.
+#define SPL_ATTN_CH 128               // tokens per chunk
+#define SPL_ATTN_PSCALE 4096.0f       // keeps small probabilities normal in fp16; removed at the end
+#define SPL_ATTN_THREADS 512
+
+__host__ __device__ constexpr int spl_attn_nq(int per_kv) { return (8 * per_kv + 15) / 16 * 16; }
+__host__ __device__ constexpr int spl_attn_stages(int hd) { return hd >= 256 ? 2 : 4; }
+__host__ __device__ constexpr size_t spl_attn_stage_bytes(int hd) { return size_t(2) * SPL_ATTN_CH * hd + 1024; }
+__host__ __device__ constexpr size_t spl_attn_smem_bytes(int hd, int nq) {
+    return 1024 + spl_attn_stages(hd) * spl_attn_stage_bytes(hd) + size_t(hd / 64) * nq * 128 /* Q */ + size_t(2) * 2 * nq * 128 /* P */
+           + size_t(2) * 4 * nq * 4 /* chunk maxima */ + size_t(4) * nq * 8 /* per-warp reference and factor */ + size_t(4) * nq * 4 /* sums */ + 512 /* barriers */;
 }
 
-#define SPL_ATTN_C 64                 // tokens per chunk
-#define SPL_ATTN_PS (SPL_ATTN_C + 4)  // row of the probability tile in shared memory (halves)
-#define SPL_ATTN_PSCALE 4096.0f       // keeps small probabilities normal in fp16; removed at the end
+__device__ __forceinline__ void spl_tc_st32(uint32_t taddr, const uint32_t *r) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+                   "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+                   "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+                   "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void spl_fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ float spl_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float spl_redux_max(float v) {
+    // Order-preserving map of a float onto a signed integer, reduced with redux.sync, mapped back.
+    int i = __float_as_int(v);
+    i ^= (i >> 31) & 0x7FFFFFFF;
+    int m;
+    asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;\n" : "=r"(m) : "r"(i));
+    m ^= (m >> 31) & 0x7FFFFFFF;
+    return __int_as_float(m);
+}
+// Sixteen int8 (a 16-byte piece) -> eight registers of fp16 pairs (exact): fp16 0x6400 | u is 1024 + u, u = x + 128.
+__device__ __forceinline__ void spl_s8x16_to_h2x8(const uint4 &piece, uint32_t *out) {
+    const __half2 off = __floats2half2_rn(1152.0f, 1152.0f);
+    const uint32_t w4[4] = {piece.x, piece.y, piece.z, piece.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t u = w4[i] ^ 0x80808080u;
+        uint32_t a = __byte_perm(u, 0x64646464u, 0x4140), b = __byte_perm(u, 0x64646464u, 0x4342);
+        const __half2 ha = __hsub2(*reinterpret_cast<__half2 *>(&a), off), hb = __hsub2(*reinterpret_cast<__half2 *>(&b), off);
+        out[2 * i] = *reinterpret_cast<const uint32_t *>(&ha); out[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&hb);
+    }
+}
+// Byte offset of element (row, k) in a K-major operand tile of 128-byte rows with the 128-byte swizzle; k < 64.
+__device__ __forceinline__ uint32_t spl_sw128_offset(int row, int k) {
+    return uint32_t((row >> 3) * 1024 + (row & 7) * 128 + ((((k >> 3) ^ (row & 7)) & 7) << 4) + (k & 7) * 2);
+}
 
-// The span scan. One block per (kv head, span of pages, attention block of <= 8 rows). The
-// block's queries (rows x the heads sharing the kv head) are M <= 16 MT rows of both products:
-//   scores[M x 64 tokens] = Q[M x head_dim] K^T      fp16 x int8 (as fp16), fp32 accumulate
-//   out[M x head_dim]    += P[M x 64] V               P = bf16(p * vScale) held as fp16 x 4096
-// with an online softmax across chunks of 64 tokens: s = acc * kScale[token] * scale, visible when
-// token < position + 1 of the query's row (attn_scan_r.metal:107-160). Each block leaves a partial
-// [reference, sum p, out[head_dim]] per query and span; spl_attn_merge_kernel combines the spans.
-// Warp w takes tokens 16w..16w+15 of a chunk in the score product and channels
-// w * head_dim / 4 ... in the value product; probabilities cross warps through shared memory.
-// The reduction (head) dimension and the token dimension are each fed to the tensor cores in a
-// permuted order that lets a lane load 16 consecutive bytes of K (or of transposed V) and use
-// them for four k16 steps; the query / probability fragments are read with the same permutation.
-// Grid (kv_heads * spans, blocks), 128 threads.
-template <int MT, int HD>
-__global__ void __launch_bounds__(128)
+template <int HD, int PER_KV>
+__global__ void __launch_bounds__(SPL_ATTN_THREADS, 1)
 spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ blocks, const uint32_t *__restrict__ row_slot,
                      const uint32_t *__restrict__ row_pos, const uint32_t *__restrict__ page_table, const int8_t *__restrict__ k_codes,
                      const float *__restrict__ k_scale, const int8_t *__restrict__ v_codes, const float *__restrict__ v_scale,
-                     float *partials, SplAttnParams p) {
-    constexpr int M = 16 * MT, QS = HD + 4, NQ = HD / 64, NVW = HD / 32;   // NVW: n8 tiles of this warp's HD / 4 channels
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    __half *Qs = reinterpret_cast<__half *>(smem_raw);                        // [M][QS]
-    __half *Ps = Qs + M * QS;                                                 // [M][SPL_ATTN_PS]
-    float *smax = reinterpret_cast<float *>(Ps + M * SPL_ATTN_PS);            // [4][M]
-    float *ssum = smax + 4 * M;                                               // [4][M]
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, g8 = lane >> 2, t = lane & 3;
+                     float *partials, SplAttnParams p, int *error_flag) {
+    constexpr int NQ = spl_attn_nq(PER_KV), CH = SPL_ATTN_CH, NST = spl_attn_stages(HD), HALVES = HD / 128, QGROUPS = HD / 64;
+    constexpr int CHUNK_BYTES = CH * HD, STAGE = int(spl_attn_stage_bytes(HD)), QTILE = NQ * 128, PTILE = 2 * NQ * 128;
+    constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+    extern __shared__ unsigned char spl_attn_smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(spl_attn_smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char *q_tile = smem;                                   // [QGROUPS][NQ rows x 128 B]   B operand of the score product
+    unsigned char *p_tile = q_tile + QGROUPS * QTILE;               // [2][2 token groups][NQ x 128 B] B operand of the value product
+    unsigned char *ring = p_tile + 2 * PTILE;                       // [NST][K chunk | V chunk | k scales | v scales]
+    float *xmax = reinterpret_cast<float *>(ring + size_t(NST) * STAGE);   // [2][4][NQ]
+    float2 *refs = reinterpret_cast<float2 *>(xmax + 2 * 4 * NQ);          // [4][NQ] (reference, factor), one copy per softmax warp
+    float *xsum = reinterpret_cast<float *>(refs + 4 * NQ);                // [4][NQ]
+    uint64_t *bars = reinterpret_cast<uint64_t *>(xsum + 4 * NQ);
+    uint64_t *full_kv = bars, *empty_kv = full_kv + NST, *ka_full = empty_kv + NST, *ka_free = ka_full + 2, *va_full = ka_free + 2,
+             *va_free = va_full + 2, *s_full = va_free + 2, *s_free = s_full + 2, *p_full = s_free + 2, *p_free = p_full + 2, *o_done = p_free + 2, *x_full = o_done + 2, *sum_full = x_full + 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sum_full + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kv_head = blockIdx.x % p.kv_heads, span = blockIdx.x / p.kv_heads, block = blockIdx.y;
-    const int per_kv = p.heads / p.kv_heads;
     const uint32_t r0 = blocks[block * 2], count = blocks[block * 2 + 1];
     const uint32_t first_pos = row_pos[r0], max_visible = first_pos + count;
+    const int valid_rows = min(int(count), p.live - int(r0));                   // rows of the block that are computed
     const int pages = int((max_visible + SPL_PAGE_TOKENS - 1) / SPL_PAGE_TOKENS);
     const int first_page = span * p.pages_per_span, last_page = min(pages, first_page + p.pages_per_span);
+    const uint32_t token_begin = uint32_t(first_page) * SPL_PAGE_TOKENS;
+    const uint32_t token_end = last_page > first_page ? min(uint32_t(last_page) * SPL_PAGE_TOKENS, max_visible) : token_begin;
+    const int chunks = int((token_end - token_begin + CH - 1) / CH);
     const size_t table_base = size_t(row_slot[r0]) * p.max_pages;
 
-    // Queries into shared memory, zero for padding rows.
-    for (int idx = tid; idx < M * (HD / 4); idx += 128) {
-        const int m = idx / (HD / 4), c4 = idx % (HD / 4);
-        const int rb = m / per_kv, hq = m % per_kv;
-        uint2 v = make_uint2(0, 0);
-        if (rb < int(count) && int(r0) + rb < p.live)
-            v = *reinterpret_cast<const uint2 *>(q + (size_t(r0 + rb) * p.heads + kv_head * per_kv + hq) * HD + c4 * 4);
-        *reinterpret_cast<uint2 *>(Qs + m * QS + c4 * 4) = v;
-    }
-    // Per-thread view of its query rows: m = 16 mt + g8 + 8 hr.
-    uint32_t limit[MT][2];
-    float ref[MT][2], total[MT][2];
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int hr = 0; hr < 2; ++hr) {
-            const int m = 16 * mt + g8 + 8 * hr, rb = m / per_kv;
-            limit[mt][hr] = (rb < int(count) && int(r0) + rb < p.live) ? first_pos + rb + 1 : 0u;
-            ref[mt][hr] = -INFINITY; total[mt][hr] = 0.0f;
+    if (tid == 0) {
+        for (int i = 0; i < NST; ++i) { spl_mbar_init(&full_kv[i], 1); spl_mbar_init(&empty_kv[i], 12); }
+        for (int i = 0; i < 2; ++i) {
+            spl_mbar_init(&ka_full[i], 4); spl_mbar_init(&ka_free[i], 1); spl_mbar_init(&va_full[i], 4); spl_mbar_init(&va_free[i], 1);
+            spl_mbar_init(&s_full[i], 1); spl_mbar_init(&s_free[i], 4); spl_mbar_init(&p_full[i], 4); spl_mbar_init(&p_free[i], 1);
+            spl_mbar_init(&o_done[i], 1); spl_mbar_init(&x_full[i], 4);
         }
-    float acc[MT][NVW][4] = {};               // value product: this warp's HD / 4 channels
+        spl_mbar_init(sum_full, 4);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(spl_smem_addr(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    // Queries into the swizzled operand tile, zero for padding rows: 16-byte pieces of eight channels.
+    for (int idx = tid; idx < NQ * (HD / 8); idx += SPL_ATTN_THREADS) {
+        const int m = idx / (HD / 8), piece = idx % (HD / 8);
+        const int rb = m / PER_KV, hq = m % PER_KV, g = piece >> 3, k8 = piece & 7;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (rb < valid_rows)
+            v = *reinterpret_cast<const uint4 *>(q + (size_t(r0 + rb) * p.heads + kv_head * PER_KV + hq) * HD + piece * 8);
+        *reinterpret_cast<uint4 *>(q_tile + g * QTILE + spl_sw128_offset(m, k8 * 8)) = v;
+    }
+    spl_fence_proxy_async();
+    spl_tc_fence_before();
     __syncthreads();
+    spl_tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 128, tmem_ka = tmem + 256, tmem_va = tmem + 384;
+    bool ok = true;
 
-    for (int pg = first_page; pg < last_page; ++pg) {
-        const size_t vec = size_t(page_table[table_base + pg]) * p.kv_heads + kv_head;
-        for (int chunk = 0; chunk < SPL_PAGE_TOKENS / SPL_ATTN_C; ++chunk) {
-            const uint32_t t0 = pg * SPL_PAGE_TOKENS + chunk * SPL_ATTN_C;
-            if (t0 >= max_visible) break;
-            const size_t token_base = vec * SPL_PAGE_TOKENS + chunk * SPL_ATTN_C;
-            // ---- scores for this warp's 16 tokens
-            float s[MT][2][4];
+    if (warp == 0) {
+        // ---- copies: one chunk = 128 tokens of one kv head = K, V and their scales, each contiguous in the pool.
+        if (lane == 0) {
+            for (int i = 0; i < chunks && ok; ++i) {
+                const int st = i % NST;
+                ok = spl_mbar_wait(&empty_kv[st], ((i / NST) & 1) ^ 1);
+                if (!ok) break;
+                const uint32_t token0 = token_begin + uint32_t(i) * CH;
+                const size_t vec = size_t(page_table[table_base + token0 / SPL_PAGE_TOKENS]) * p.kv_heads + kv_head;
+                const int sub = int(token0 % SPL_PAGE_TOKENS) / CH;
+                unsigned char *dst = ring + size_t(st) * STAGE;
+                spl_mbar_expect_tx(&full_kv[st], 2 * CHUNK_BYTES + 1024);
+                spl_bulk_g2s(dst, k_codes + vec * (SPL_PAGE_TOKENS * HD) + size_t(sub) * CHUNK_BYTES, CHUNK_BYTES, &full_kv[st]);
+                spl_bulk_g2s(dst + CHUNK_BYTES, v_codes + vec * (SPL_PAGE_TOKENS * HD) + size_t(sub) * CHUNK_BYTES, CHUNK_BYTES, &full_kv[st]);
+                spl_bulk_g2s(dst + 2 * CHUNK_BYTES, k_scale + vec * SPL_PAGE_TOKENS + sub * CH, 512, &full_kv[st]);
+                spl_bulk_g2s(dst + 2 * CHUNK_BYTES + 512, v_scale + vec * SPL_PAGE_TOKENS + sub * CH, 512, &full_kv[st]);
+            }
+        }
+    } else if (warp == 1) {
+        // ---- tensor-core issue.
+        if (lane == 0) {
+            constexpr uint32_t idesc = spl_tc_idesc(NQ);
+            auto scores = [&](int i) {
+                const int buf = i & 1;
+                ok = ok && spl_mbar_wait(&s_free[buf], ((i >> 1) & 1) ^ 1);
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
+                for (int h = 0; h < HALVES; ++h) {
+                    ok = ok && spl_mbar_wait(&ka_full[h], i & 1);
+                    if (!ok) return;
+                    spl_tc_fence_after();
 #pragma unroll
-                for (int jn = 0; jn < 2; ++jn)
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) s[mt][jn][e] = 0.0f;
-#pragma unroll
-            for (int ci = 0; ci < NQ; ++ci) {
-                uint4 kc[2];
-#pragma unroll
-                for (int jn = 0; jn < 2; ++jn)
-                    kc[jn] = __ldg(reinterpret_cast<const uint4 *>(k_codes + (token_base + 16 * warp + 8 * jn + g8) * HD + (t + 4 * ci) * 16));
-#pragma unroll
-                for (int sx = 0; sx < 4; ++sx) {
-                    uint32_t b[2][2];
-#pragma unroll
-                    for (int jn = 0; jn < 2; ++jn) {
-                        const uint32_t w = sx == 0 ? kc[jn].x : sx == 1 ? kc[jn].y : sx == 2 ? kc[jn].z : kc[jn].w;
-                        spl_s8x4_to_h2x2(w, b[jn][0], b[jn][1]);
+                    for (int ks = 0; ks < 8; ++ks) {
+                        const int step = h * 8 + ks;
+                        spl_tc_mma_ts(tmem_s + buf * 64, tmem_ka + h * 64 + ks * 8,
+                                      spl_tc_desc_sw128(spl_smem_addr(q_tile + (step >> 2) * QTILE) + (step & 3) * 32), idesc, step > 0 ? 1u : 0u);
                     }
+                    spl_tc_commit(&ka_free[h]);
+                }
+                spl_tc_commit(&s_full[buf]);
+            };
+            if (chunks > 0) scores(0);
+            for (int i = 0; i < chunks && ok; ++i) {
+                if (i + 1 < chunks) scores(i + 1);
+                const int pb = i & 1;
+                ok = ok && spl_mbar_wait(&p_full[pb], (i >> 1) & 1);
 #pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const __half *qa = Qs + (16 * mt + g8) * QS + (t + 4 * ci) * 16 + 4 * sx;
-                        const uint2 lo = *reinterpret_cast<const uint2 *>(qa), hi = *reinterpret_cast<const uint2 *>(qa + 8 * QS);
-                        const uint32_t a[4] = {lo.x, hi.x, lo.y, hi.y};
-                        spl_mma_f16(s[mt][0], a, b[0][0], b[0][1]);
-                        spl_mma_f16(s[mt][1], a, b[1][0], b[1][1]);
-                    }
+                for (int h = 0; h < HALVES; ++h) {
+                    ok = ok && spl_mbar_wait(&va_full[h], i & 1);
+                    if (!ok) break;
+                    spl_tc_fence_after();
+#pragma unroll
+                    for (int ks = 0; ks < 8; ++ks)
+                        spl_tc_mma_ts(tmem_o + h * 64, tmem_va + h * 64 + ks * 8,
+                                      spl_tc_desc_sw128(spl_smem_addr(p_tile + pb * PTILE + (ks >> 2) * QTILE) + (ks & 3) * 32), idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                    spl_tc_commit(&va_free[h]);
+                }
+                if (!ok) break;
+                spl_tc_commit(&p_free[pb]);
+                spl_tc_commit(&o_done[pb]);
+            }
+        }
+    } else if (warp >= 4 && warp < 8) {
+        // ---- K: thread = token. Its head_dim int8 -> fp16 pairs -> tensor memory, 128 channels (64 columns) at a time.
+        const int token = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+        for (int i = 0; i < chunks && ok; ++i) {
+            const int st = i % NST;
+            ok = spl_mbar_wait(&full_kv[st], (i / NST) & 1);
+            if (!ok) break;
+            const unsigned char *src = ring + size_t(st) * STAGE + token * 16;
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) {
+                uint32_t a[64];
+#pragma unroll
+                for (int pc = 0; pc < 8; ++pc)
+                    spl_s8x16_to_h2x8(*reinterpret_cast<const uint4 *>(src + (h * 8 + pc) * (CH * 16)), a + pc * 8);
+                if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_kv[st]); }
+                ok = spl_mbar_wait(&ka_free[h], (i & 1) ^ 1);
+                if (!ok) break;
+                spl_tc_fence_after();
+                spl_tc_st32(tmem_ka + lane_base + h * 64, a);
+                spl_tc_st32(tmem_ka + lane_base + h * 64 + 32, a + 32);
+                spl_tc_st_wait();
+                spl_tc_fence_before();
+                __syncwarp();
+                if (lane == 0) spl_mbar_arrive(&ka_full[h]);
+            }
+        }
+    } else if (warp >= 8 && warp < 12) {
+        // ---- V: thread = channel of a half. Its 128 tokens int8 -> fp16 pairs -> tensor memory.
+        const int channel = (warp & 3) * 32 + lane;
+        const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
+        for (int i = 0; i < chunks && ok; ++i) {
+            const int st = i % NST;
+            ok = spl_mbar_wait(&full_kv[st], (i / NST) & 1);
+            if (!ok) break;
+            const unsigned char *src = ring + size_t(st) * STAGE + CHUNK_BYTES;
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) {
+                uint32_t a[64];
+#pragma unroll
+                for (int tb = 0; tb < 8; ++tb)
+                    spl_s8x16_to_h2x8(*reinterpret_cast<const uint4 *>(src + tb * (HD * 16) + (h * 128 + channel) * 16), a + tb * 8);
+                if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_kv[st]); }
+                ok = spl_mbar_wait(&va_free[h], (i & 1) ^ 1);
+                if (!ok) break;
+                spl_tc_fence_after();
+                spl_tc_st32(tmem_va + lane_base + h * 64, a);
+                spl_tc_st32(tmem_va + lane_base + h * 64 + 32, a + 32);
+                spl_tc_st_wait();
+                spl_tc_fence_before();
+                __syncwarp();
+                if (lane == 0) spl_mbar_arrive(&va_full[h]);
+            }
+        }
+    } else if (warp >= 12) {
+        // ---- softmax: thread = token of the chunk (scores), = channel of a half (rescale and output).
+        const int w4 = warp & 3, token = w4 * 32 + lane;
+        const uint32_t lane_base = uint32_t(w4 * 32) << 16;
+        float sum[NQ];
+#pragma unroll
+        for (int n = 0; n < NQ; ++n) sum[n] = 0.0f;
+        for (int n = lane; n < NQ; n += 32) refs[w4 * NQ + n] = make_float2(-INFINITY, 1.0f);
+        __syncwarp();
+        for (int i = 0; i < chunks && ok; ++i) {
+            const int st = i % NST, buf = i & 1, par = i & 1;
+            ok = spl_mbar_wait(&full_kv[st], (i / NST) & 1);
+            if (!ok) break;
+            const float *scales = reinterpret_cast<const float *>(ring + size_t(st) * STAGE + 2 * CHUNK_BYTES);
+            const float ksl = scales[token] * p.scale * LOG2E, vsc = scales[CH + token];
+            __syncwarp();
+            if (lane == 0) spl_mbar_arrive(&empty_kv[st]);
+            const uint32_t token_index = token_begin + uint32_t(i) * CH + token;
+            // Rows rb >= first_hidden do not see this token; a chunk below every row's position needs no mask.
+            const bool whole = token_begin + uint32_t(i + 1) * CH <= first_pos + 1;
+            const int first_seen = whole ? 0 : max(0, int(token_index) - int(first_pos));     // visible to rows rb >= first_seen
+            ok = spl_mbar_wait(&s_full[buf], (i >> 1) & 1);
+            if (!ok) break;
+            spl_tc_fence_after();
+            // Pass 1: the chunk's maximum per query.
+#pragma unroll
+            for (int c0 = 0; c0 < NQ; c0 += 16) {
+                uint32_t v[16];
+                spl_tc_ld16(v, tmem_s + lane_base + buf * 64 + c0);
+                spl_tc_ld_wait();
+#pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    const int n = c0 + r, rb = n / PER_KV;
+                    const bool seen = whole || (rb >= first_seen && rb < valid_rows);
+                    const float s = seen ? __uint_as_float(v[r]) * ksl : -INFINITY;
+                    const float top = spl_redux_max(s);
+                    if (lane == (n & 31)) xmax[(par * 4 + w4) * NQ + n] = top;
                 }
             }
-            // ---- softmax bookkeeping. Element (jn, e): token 16 warp + 8 jn + 2 t + (e & 1), row hr = e >> 1.
-            float ksc[2][2], vsc[2][2];
-#pragma unroll
-            for (int jn = 0; jn < 2; ++jn) {
-                const float2 k2 = __ldg(reinterpret_cast<const float2 *>(k_scale + token_base + 16 * warp + 8 * jn + 2 * t));
-                const float2 v2 = __ldg(reinterpret_cast<const float2 *>(v_scale + token_base + 16 * warp + 8 * jn + 2 * t));
-                ksc[jn][0] = k2.x; ksc[jn][1] = k2.y; vsc[jn][0] = v2.x; vsc[jn][1] = v2.y;
+            // The four warps exchange their maxima through shared memory; the wait is bounded like every other.
+            __syncwarp();
+            if (lane == 0) spl_mbar_arrive(&x_full[par]);
+            ok = spl_mbar_wait(&x_full[par], (i >> 1) & 1);
+            if (!ok) break;
+            bool moved = false;
+            for (int n = lane; n < NQ; n += 32) {
+                const float top = fmaxf(fmaxf(xmax[(par * 4 + 0) * NQ + n], xmax[(par * 4 + 1) * NQ + n]),
+                                        fmaxf(xmax[(par * 4 + 2) * NQ + n], xmax[(par * 4 + 3) * NQ + n]));
+                const float old = refs[w4 * NQ + n].x, next = fmaxf(old, top);
+                const bool same = old == -INFINITY || next == old;
+                refs[w4 * NQ + n] = make_float2(next, same ? 1.0f : spl_ex2(old - next));
+                moved = moved || !same;
             }
-            const uint32_t tok = t0 + 16 * warp + 2 * t;
+            moved = __any_sync(0xffffffffu, moved);
+            __syncwarp();
+            // The probability tile of two chunks ago has been read (and with it that chunk's value product has finished,
+            // so the wait below on the previous chunk's completion cannot see a stale phase).
+            ok = spl_mbar_wait(&p_free[buf], ((i >> 1) & 1) ^ 1);
+            if (!ok) break;
+            if (moved && i > 0) {
+                // Rescale O^T (this warp's 32 channels of each half) once the previous value product has finished.
+                ok = spl_mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1);
+                if (!ok) break;
+                spl_tc_fence_after();
 #pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
+                for (int h = 0; h < HALVES; ++h)
 #pragma unroll
-                for (int hr = 0; hr < 2; ++hr) {
-                    float top = -INFINITY;
+                    for (int c0 = 0; c0 < NQ; c0 += 16) {
+                        uint32_t v[16];
+                        spl_tc_ld16(v, tmem_o + lane_base + h * 64 + c0);
+                        spl_tc_ld_wait();
 #pragma unroll
-                    for (int jn = 0; jn < 2; ++jn)
+                        for (int r = 0; r < 16; ++r) v[r] = __float_as_uint(__uint_as_float(v[r]) * refs[w4 * NQ + c0 + r].y);
+                        spl_tc_st16(tmem_o + lane_base + h * 64 + c0, v);
+                    }
+                spl_tc_st_wait();
+                spl_tc_fence_before();
+            }
+            // Pass 2: probabilities into the operand tile of the value product.
+            unsigned char *pt = p_tile + buf * PTILE + (token >> 6) * QTILE;
+            const int tk = token & 63;
 #pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const bool seen = tok + 8 * jn + e < limit[mt][hr];
-                            const float v = seen ? s[mt][jn][2 * hr + e] * ksc[jn][e] * p.scale : -INFINITY;
-                            s[mt][jn][2 * hr + e] = v;
-                            top = fmaxf(top, v);
+            for (int c0 = 0; c0 < NQ; c0 += 16) {
+                uint32_t v[16];
+                spl_tc_ld16(v, tmem_s + lane_base + buf * 64 + c0);
+                spl_tc_ld_wait();
+#pragma unroll
+                for (int r = 0; r < 16; ++r) {
+                    const int n = c0 + r, rb = n / PER_KV;
+                    const bool seen = whole || (rb >= first_seen && rb < valid_rows);
+                    const float2 rf = refs[w4 * NQ + n];
+                    const float prob = seen ? spl_ex2(__uint_as_float(v[r]) * ksl - rf.x) : 0.0f;
+                    sum[n] = moved ? fmaf(sum[n], rf.y, prob) : sum[n] + prob;
+                    const float pw = seen ? __bfloat162float(__float2bfloat16_rn(prob * vsc)) * SPL_ATTN_PSCALE : 0.0f;
+                    *reinterpret_cast<__half *>(pt + spl_sw128_offset(n, tk)) = __float2half_rn(pw);
+                }
+            }
+            spl_tc_fence_before();
+            spl_fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) { spl_mbar_arrive(&s_free[buf]); spl_mbar_arrive(&p_full[buf]); }
+        }
+        // ---- the span's partial: [reference, sum p, out[head_dim]] per query (row, head).
+        if (ok && chunks > 0) ok = spl_mbar_wait(&o_done[(chunks - 1) & 1], ((chunks - 1) >> 1) & 1);
+        if (ok) {
+            spl_tc_fence_after();
+#pragma unroll
+            for (int n = 0; n < NQ; ++n) {
+                const float total = spl_warp_sum(sum[n]);
+                if (lane == (n & 31)) xsum[w4 * NQ + n] = total;
+            }
+            __syncwarp();
+            if (lane == 0) spl_mbar_arrive(sum_full);
+            ok = spl_mbar_wait(sum_full, 0);
+        }
+        if (ok) {
+            const int record = HD + 2;
+            if (token < NQ && token / PER_KV < valid_rows) {
+                const int rb = token / PER_KV, hq = token % PER_KV;
+                float *partial = partials + ((size_t(r0 + rb) * p.heads + kv_head * PER_KV + hq) * p.spans + span) * record;
+                partial[0] = chunks > 0 ? refs[w4 * NQ + token].x * LN2 : -INFINITY;
+                partial[1] = ((xsum[token] + xsum[NQ + token]) + xsum[2 * NQ + token]) + xsum[3 * NQ + token];
+            }
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h)
+#pragma unroll
+                for (int c0 = 0; c0 < NQ; c0 += 16) {
+                    uint32_t v[16];
+                    if (chunks > 0) { spl_tc_ld16(v, tmem_o + lane_base + h * 64 + c0); spl_tc_ld_wait(); }
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        const int n = c0 + r, rb = n / PER_KV, hq = n % PER_KV;
+                        if (rb < valid_rows && n < 8 * PER_KV) {
+                            float *partial = partials + ((size_t(r0 + rb) * p.heads + kv_head * PER_KV + hq) * p.spans + span) * record;
+                            partial[2 + h * 128 + token] = chunks > 0 ? __uint_as_float(v[r]) * (1.0f / SPL_ATTN_PSCALE) : 0.0f;
                         }
-                    top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 1));
-                    top = fmaxf(top, __shfl_xor_sync(0xffffffffu, top, 2));
-                    if (t == 0) smax[warp * M + 16 * mt + g8 + 8 * hr] = top;
-                }
-            __syncthreads();
-            float factor[MT][2];
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                for (int hr = 0; hr < 2; ++hr) {
-                    const int m = 16 * mt + g8 + 8 * hr;
-                    const float top = fmaxf(fmaxf(smax[m], smax[M + m]), fmaxf(smax[2 * M + m], smax[3 * M + m]));
-                    const float next = fmaxf(ref[mt][hr], top);
-                    float sum = 0.0f;
-#pragma unroll
-                    for (int jn = 0; jn < 2; ++jn) {
-                        float pw[2];
-#pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const float v = s[mt][jn][2 * hr + e];
-                            const bool seen = v != -INFINITY;
-                            const float prob = seen ? expf(v - next) : 0.0f;
-                            sum += prob;
-                            pw[e] = seen ? spl_round_bf16(prob * vsc[jn][e]) * SPL_ATTN_PSCALE : 0.0f;
-                        }
-                        *reinterpret_cast<__half2 *>(Ps + m * SPL_ATTN_PS + 16 * warp + 8 * jn + 2 * t) = __floats2half2_rn(pw[0], pw[1]);
-                    }
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-                    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-                    if (t == 0) ssum[warp * M + m] = sum;
-                    factor[mt][hr] = (ref[mt][hr] == -INFINITY || next == ref[mt][hr]) ? 1.0f : expf(ref[mt][hr] - next);
-                    ref[mt][hr] = next;
-                }
-            __syncthreads();
-#pragma unroll
-            for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-                for (int hr = 0; hr < 2; ++hr) {
-                    const int m = 16 * mt + g8 + 8 * hr;
-                    total[mt][hr] = total[mt][hr] * factor[mt][hr] + (((ssum[m] + ssum[M + m]) + ssum[2 * M + m]) + ssum[3 * M + m]);
-#pragma unroll
-                    for (int nj = 0; nj < NVW; ++nj) { acc[mt][nj][2 * hr] *= factor[mt][hr]; acc[mt][nj][2 * hr + 1] *= factor[mt][hr]; }
-                }
-            // ---- value product for this warp's channels
-#pragma unroll
-            for (int nj = 0; nj < NVW; ++nj) {
-                const int d = warp * (HD / 4) + 8 * nj + g8;
-                const uint4 vc = __ldg(reinterpret_cast<const uint4 *>(v_codes + (vec * HD + d) * SPL_PAGE_TOKENS + chunk * SPL_ATTN_C + t * 16));
-#pragma unroll
-                for (int sx = 0; sx < 4; ++sx) {
-                    const uint32_t w = sx == 0 ? vc.x : sx == 1 ? vc.y : sx == 2 ? vc.z : vc.w;
-                    uint32_t b0, b1;
-                    spl_s8x4_to_h2x2(w, b0, b1);
-#pragma unroll
-                    for (int mt = 0; mt < MT; ++mt) {
-                        const __half *pa = Ps + (16 * mt + g8) * SPL_ATTN_PS + t * 16 + 4 * sx;
-                        const uint2 lo = *reinterpret_cast<const uint2 *>(pa), hi = *reinterpret_cast<const uint2 *>(pa + 8 * SPL_ATTN_PS);
-                        const uint32_t a[4] = {lo.x, hi.x, lo.y, hi.y};
-                        spl_mma_f16(acc[mt][nj], a, b0, b1);
                     }
                 }
-            }
-            // The next chunk's probabilities must not overwrite the tile while a warp still reads it;
-            // the barrier after its score product covers smax, this one covers Ps and ssum.
-            __syncthreads();
         }
     }
-
-    // Partials. acc element e of (mt, nj): row hr = e >> 1, channel warp * HD/4 + 8 nj + 2 t + (e & 1).
-    const int record = HD + 2;
-#pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int hr = 0; hr < 2; ++hr) {
-            const int m = 16 * mt + g8 + 8 * hr, rb = m / per_kv, hq = m % per_kv;
-            if (rb >= int(count) || int(r0) + rb >= p.live) continue;
-            float *partial = partials + ((size_t(r0 + rb) * p.heads + kv_head * per_kv + hq) * p.spans + span) * record;
-            if (warp == 0 && t == 0) { partial[0] = ref[mt][hr]; partial[1] = total[mt][hr]; }
-#pragma unroll
-            for (int nj = 0; nj < NVW; ++nj) {
-                float2 v = make_float2(acc[mt][nj][2 * hr] * (1.0f / SPL_ATTN_PSCALE), acc[mt][nj][2 * hr + 1] * (1.0f / SPL_ATTN_PSCALE));
-                *reinterpret_cast<float2 *>(partial + 2 + warp * (HD / 4) + 8 * nj + 2 * t) = v;
-            }
-        }
+    if (!ok) atomicExch(error_flag, 100 + warp);
+    spl_tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        spl_tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
+    }
 }
 
 // Merge span partials by log-sum-exp, apply the sigmoid output gate, round to the bf16 operand of

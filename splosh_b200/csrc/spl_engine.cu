@@ -213,20 +213,22 @@ void launch_gemm(spl_engine *e, const SplQ4Dev &w, const GemmOperand &op, float 
     profile_end(e);
 }
 
-template <int HD>
-void launch_scan(spl_engine *e, int mt, dim3 grid, const SplAttnParams &p, int layer) {
-    const int8_t *kc = e->k_codes[layer], *vc = e->v_codes[layer];
-    const float *ks = e->k_scale[layer], *vs = e->v_scale[layer];
-#define SPL_SCAN(MT)                                                                                                   \
-    {                                                                                                                  \
-        const size_t smem = size_t(16 * MT) * (HD + 4) * 2 + size_t(16 * MT) * SPL_ATTN_PS * 2 + size_t(8) * 16 * MT * 4; \
-        static bool configured = false;                                                                                \
-        if (!configured) { cudaFuncSetAttribute(spl_attn_scan_kernel<MT, HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); configured = true; } \
-        spl_attn_scan_kernel<MT, HD><<<grid, 128, smem, e->stream>>>(e->q, e->d_blocks, e->d_row_slot, e->d_row_pos, e->d_page_table, \
-                                                                     kc, ks, vc, vs, e->attn_partials, p);              \
-    }
-    if (mt <= 1) SPL_SCAN(1) else if (mt == 2) SPL_SCAN(2) else if (mt == 3) SPL_SCAN(3) else SPL_SCAN(4)
-#undef SPL_SCAN
+template <int HD, int PER_KV>
+void launch_scan_tc(spl_engine *e, dim3 grid, const SplAttnParams &p, int layer) {
+    const size_t smem = spl_attn_smem_bytes(HD, spl_attn_nq(PER_KV));
+    static bool configured = false;
+    if (!configured) { cudaFuncSetAttribute(spl_attn_scan_kernel<HD, PER_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); configured = true; }
+    spl_attn_scan_kernel<HD, PER_KV><<<grid, SPL_ATTN_THREADS, smem, e->stream>>>(e->q, e->d_blocks, e->d_row_slot, e->d_row_pos, e->d_page_table,
+        e->k_codes[layer], e->k_scale[layer], e->v_codes[layer], e->v_scale[layer], e->attn_partials, p, e->tc_error);
+}
+// The scan is built for the head shapes in use: head_dim 256 with six query heads per kv head, and head_dim 128 with four.
+bool scan_supported(const spl_geometry &g) {
+    const int per_kv = g.kv_heads > 0 ? g.heads / g.kv_heads : 0;
+    return (g.head_dim == 256 && per_kv == 6) || (g.head_dim == 128 && per_kv == 4);
+}
+void launch_scan(spl_engine *e, dim3 grid, const SplAttnParams &p, int layer) {
+    if (e->g.head_dim == 256) launch_scan_tc<256, 6>(e, grid, p, layer);
+    else launch_scan_tc<128, 4>(e, grid, p, layer);
 }
 
 spl_status check_launch(spl_engine *e, const char *what) {
@@ -307,17 +309,13 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
             profile_end(e);
             if (live > 0) {
                 // Blocks are in row order: those that begin below `live` hold the computed rows.
-                int blocks = 0, max_count = 1;
-                for (; blocks < int(t->attn_block_count); ++blocks) {
+                int blocks = 0;
+                for (; blocks < int(t->attn_block_count); ++blocks)
                     if (int(t->attn_blocks[blocks * 2]) >= live) break;
-                    max_count = std::max(max_count, int(t->attn_blocks[blocks * 2 + 1]));
-                }
                 if (size_t(live) * g.heads * t->spans * (g.head_dim + 2) > e->attn_partial_floats)
                     return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: attention partials exceed the engine's buffers");
-                const int mt = (max_count * (g.heads / g.kv_heads) + 15) / 16;
                 profile_begin(e, KLASS_ATTENTION, 0);
-                if (g.head_dim == 256) launch_scan<256>(e, mt, dim3(g.kv_heads * t->spans, blocks), p, full_index);
-                else launch_scan<128>(e, mt, dim3(g.kv_heads * t->spans, blocks), p, full_index);
+                launch_scan(e, dim3(g.kv_heads * t->spans, blocks), p, full_index);
                 profile_end(e);
                 profile_begin(e, KLASS_ATTENTION, 0);
                 spl_attn_merge_kernel<<<dim3(g.heads, live), g.head_dim, 0, e->stream>>>(e->attn_partials, e->proj, core, p);
@@ -441,7 +439,7 @@ spl_status create(const spl_geometry *gp, const spl_config *cp, spl_engine *e) {
     const Shapes sh(g);
     if (g.layers <= 0 || g.hidden % 256 || g.inter % 256 || sh.VD % 256 || sh.AD % 256 || g.gdn_head_dim != 128 ||
         (g.head_dim != 128 && g.head_dim != 256) || g.heads % g.kv_heads || g.gdn_value_heads % g.gdn_key_heads || g.vocab % 16 ||
-        g.inter % 16 || sh.C % 16 || g.rotary_dim > g.head_dim || g.rotary_dim % 2 || 8 * (g.heads / g.kv_heads) > 64)
+        g.inter % 16 || sh.C % 16 || g.rotary_dim > g.head_dim || g.rotary_dim % 2 || !scan_supported(g))
         return e->fail(SPL_ERR_INVALID_ARGUMENT, "unsupported geometry");
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || count == 0) return e->fail(SPL_ERR_UNSUPPORTED_DEVICE, "unsupported device: no CUDA device");
@@ -831,6 +829,19 @@ spl_status spl_debug_read(spl_engine *e, int32_t which, int32_t index, void *dst
     case 8: if (e->taps && index >= 0 && index < e->g.layers) { src = e->taps + size_t(index) * e->c.max_rows * e->g.hidden; have = size_t(e->last_rows) * e->g.hidden * 4; } break;
     }
     if (!src || bytes > have) return e->fail(SPL_ERR_INVALID_ARGUMENT, "debug read outside the buffer");
+    if (which == 3 || which == 4) {
+        // The code arrays are read out in the plain order [page][kv head][token][channel], whatever the pool's own order is.
+        const int hd = e->g.head_dim;
+        std::vector<int8_t> raw(have);
+        SPL_CUDA(cudaMemcpy(raw.data(), src, have, cudaMemcpyDeviceToHost));
+        int8_t *out = static_cast<int8_t *>(dst);
+        for (size_t i = 0; i < bytes; ++i) {
+            const size_t vec = i / (size_t(SPL_PAGE_TOKENS) * hd), rest = i % (size_t(SPL_PAGE_TOKENS) * hd);
+            const uint32_t token = uint32_t(rest / hd); const int d = int(rest % hd);
+            out[i] = raw[which == 3 ? spl_k_code_index(vec, token, d, hd) : spl_v_code_index(vec, token, d, hd)];
+        }
+        return SPL_OK;
+    }
     SPL_CUDA(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost));
     return SPL_OK;
 }

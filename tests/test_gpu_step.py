@@ -233,8 +233,6 @@ def test_long_context_attention_and_span_split(toks):
         for which in ("k_codes", "v_codes", "k_scale", "v_scale"):
             ob = pair.oengine.buffer(which, 0)
             gb = pair.engine.debug_read(which, 0, ob.size, ob.dtype)
-            if which == "v_codes":      # the library keeps V transposed inside a page
-                gb = gb.reshape(pages, kvh, hd, 256).transpose(0, 1, 3, 2).reshape(-1)
             ob[:] = gb
         rows = [S.EngineRow(0, toks[i], ctx[0] + i, True, True) for i in range(13)] + [S.EngineRow(1, toks[50 + i], ctx[1] + i, True) for i in range(11)]
         rows = rows[:13] + [S.EngineRow(1, toks[50 + i], ctx[1] + i, i >= 9) for i in range(11)]
