@@ -112,7 +112,10 @@ spl_attn_prepare_kernel(const float *__restrict__ proj, const uint16_t *__restri
 // memory, 8-11 V -> tensor memory, 12-15 softmax, rescale and the partial's output. Every wait is bounded.
 // Tensor memory (512 columns): S two buffers at 0 and 64, O halves at 128 and 192, K operand at 256, V at 384.
 #define SPL_ATTN_CH 128               // tokens per chunk
-#define SPL_ATTN_PSCALE 4096.0f       // keeps small probabilities normal in fp16; removed at the end
+#define SPL_ATTN_HEADROOM 6.0f        // a score may exceed its query's reference by this much (log2) before the reference is raised
+#define SPL_ATTN_PSCALE 64.0f         // 4096 / 2^headroom: keeps small probabilities normal in fp16 and large ones finite; removed at the end
+struct SplTrue { static constexpr bool value = true; };
+struct SplFalse { static constexpr bool value = false; };
 #define SPL_ATTN_THREADS 512
 
 __host__ __device__ constexpr int spl_attn_nq(int per_kv) { return (8 * per_kv + 15) / 16 * 16; }
@@ -134,13 +137,9 @@ __device__ __forceinline__ void spl_tc_st32(uint32_t taddr, const uint32_t *r) {
 __device__ __forceinline__ void spl_fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ float spl_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ float spl_redux_max(float v) {
-    // Order-preserving map of a float onto a signed integer, reduced with redux.sync, mapped back.
-    int i = __float_as_int(v);
-    i ^= (i >> 31) & 0x7FFFFFFF;
-    int m;
-    asm volatile("redux.sync.max.s32 %0, %1, 0xffffffff;\n" : "=r"(m) : "r"(i));
-    m ^= (m >> 31) & 0x7FFFFFFF;
-    return __int_as_float(m);
+    float m;
+    asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;\n" : "=f"(m) : "f"(v));
+    return m;
 }
 // Sixteen int8 (a 16-byte piece) -> eight registers of fp16 pairs (exact): fp16 0x6400 | u is 1024 + u, u = x + 128.
 __device__ __forceinline__ void spl_s8x16_to_h2x8(const uint4 &piece, uint32_t *out) {
@@ -174,12 +173,13 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
     unsigned char *p_tile = q_tile + QGROUPS * QTILE;               // [2][2 token groups][NQ x 128 B] B operand of the value product
     unsigned char *ring = p_tile + 2 * PTILE;                       // [NST][K chunk | V chunk | k scales | v scales]
     float *xmax = reinterpret_cast<float *>(ring + size_t(NST) * STAGE);   // [2][4][NQ]
-    float2 *refs = reinterpret_cast<float2 *>(xmax + 2 * 4 * NQ);          // [4][NQ] (reference, factor), one copy per softmax warp
-    float *xsum = reinterpret_cast<float *>(refs + 4 * NQ);                // [4][NQ]
+    float *ref_next = xmax + 2 * 4 * NQ, *ref_factor = ref_next + 4 * NQ;  // [4][NQ] each: running reference (log2 domain) and the chunk's rescale factor, one copy per softmax warp
+    float *xsum = ref_factor + 4 * NQ;                                     // [4][NQ]
     uint64_t *bars = reinterpret_cast<uint64_t *>(xsum + 4 * NQ);
     uint64_t *full_kv = bars, *empty_kv = full_kv + NST, *ka_full = empty_kv + NST, *ka_free = ka_full + 2, *va_full = ka_free + 2,
-             *va_free = va_full + 2, *s_full = va_free + 2, *s_free = s_full + 2, *p_full = s_free + 2, *p_free = p_full + 2, *o_done = p_free + 2, *x_full = o_done + 2, *sum_full = x_full + 2;
+             *va_free = va_full + 2, *s_full = va_free + 2, *s_free = s_full + 2, *p_full = s_free + 2, *p_free = p_full + 2, *o_done = p_free + 2, *x_full = o_done + 2, *y_full = x_full + 2, *sum_full = y_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sum_full + 1);
+    int *xflag = reinterpret_cast<int *>(tmem_slot + 1);          // [2] last chunk (+1) of each parity whose scores called for a raise
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kv_head = blockIdx.x % p.kv_heads, span = blockIdx.x / p.kv_heads, block = blockIdx.y;
@@ -198,7 +198,8 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
         for (int i = 0; i < 2; ++i) {
             spl_mbar_init(&ka_full[i], 4); spl_mbar_init(&ka_free[i], 1); spl_mbar_init(&va_full[i], 4); spl_mbar_init(&va_free[i], 1);
             spl_mbar_init(&s_full[i], 1); spl_mbar_init(&s_free[i], 4); spl_mbar_init(&p_full[i], 4); spl_mbar_init(&p_free[i], 1);
-            spl_mbar_init(&o_done[i], 1); spl_mbar_init(&x_full[i], 4);
+            spl_mbar_init(&o_done[i], 1); spl_mbar_init(&x_full[i], 4); spl_mbar_init(&y_full[i], 4);
+            xflag[i] = 0;
         }
         spl_mbar_init(sum_full, 4);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -223,13 +224,21 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_s = tmem, tmem_o = tmem + 128, tmem_ka = tmem + 256, tmem_va = tmem + 384;
     bool ok = true;
+    // Debug trace: cycles per chunk that one thread of each role of block (0, 0) spends in its waits and its work.
+    const bool trace = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && error_flag[1] == 0x7ACE && (error_flag[2] & 0x200);
+    long long tt[8] = {0, 0, 0, 0, 0, 0, 0, 0}, t_mark = 0;
+#define SPL_A0() do { if (trace) t_mark = clock64(); } while (0)
+#define SPL_A1(k) do { if (trace) { const long long now__ = clock64(); tt[k] += now__ - t_mark; t_mark = now__; } } while (0)
+#define SPL_AOUT(base, n) do { if (trace && chunks > 0) for (int k__ = 0; k__ < n; ++k__) error_flag[base + k__] = int(tt[k__] / chunks); } while (0)
 
     if (warp == 0) {
         // ---- copies: one chunk = 128 tokens of one kv head = K, V and their scales, each contiguous in the pool.
         if (lane == 0) {
             for (int i = 0; i < chunks && ok; ++i) {
                 const int st = i % NST;
+                SPL_A0();
                 ok = spl_mbar_wait(&empty_kv[st], ((i / NST) & 1) ^ 1);
+                SPL_A1(0);
                 if (!ok) break;
                 const uint32_t token0 = token_begin + uint32_t(i) * CH;
                 const size_t vec = size_t(page_table[table_base + token0 / SPL_PAGE_TOKENS]) * p.kv_heads + kv_head;
@@ -240,50 +249,69 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                 spl_bulk_g2s(dst + CHUNK_BYTES, v_codes + vec * (SPL_PAGE_TOKENS * HD) + size_t(sub) * CHUNK_BYTES, CHUNK_BYTES, &full_kv[st]);
                 spl_bulk_g2s(dst + 2 * CHUNK_BYTES, k_scale + vec * SPL_PAGE_TOKENS + sub * CH, 512, &full_kv[st]);
                 spl_bulk_g2s(dst + 2 * CHUNK_BYTES + 512, v_scale + vec * SPL_PAGE_TOKENS + sub * CH, 512, &full_kv[st]);
+                SPL_A1(1);
             }
+            SPL_AOUT(32, 2);
         }
     } else if (warp == 1) {
-        // ---- tensor-core issue.
+        // ---- tensor-core issue, score product: S^T[buffer] = K (tensor memory) x Q (shared memory), sixteen channels per instruction.
+        // (Issuing an instruction costs its thread on the order of a hundred cycles, so the two products have a thread each.)
         if (lane == 0) {
             constexpr uint32_t idesc = spl_tc_idesc(NQ);
-            auto scores = [&](int i) {
+            const uint64_t q_desc = spl_tc_desc_sw128(spl_smem_addr(q_tile));
+            for (int i = 0; i < chunks && ok; ++i) {
                 const int buf = i & 1;
-                ok = ok && spl_mbar_wait(&s_free[buf], ((i >> 1) & 1) ^ 1);
+                SPL_A0();
+                ok = spl_mbar_wait(&s_free[buf], ((i >> 1) & 1) ^ 1);
+                SPL_A1(0);
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) {
                     ok = ok && spl_mbar_wait(&ka_full[h], i & 1);
-                    if (!ok) return;
+                    SPL_A1(1);
+                    if (!ok) break;
                     spl_tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks) {
                         const int step = h * 8 + ks;
-                        spl_tc_mma_ts(tmem_s + buf * 64, tmem_ka + h * 64 + ks * 8,
-                                      spl_tc_desc_sw128(spl_smem_addr(q_tile + (step >> 2) * QTILE) + (step & 3) * 32), idesc, step > 0 ? 1u : 0u);
+                        spl_tc_mma_ts(tmem_s + buf * 64, tmem_ka + h * 64 + ks * 8, q_desc + uint64_t(((step >> 2) * QTILE + (step & 3) * 32) >> 4), idesc, step > 0 ? 1u : 0u);
                     }
                     spl_tc_commit(&ka_free[h]);
+                    SPL_A1(2);
                 }
+                if (!ok) break;
                 spl_tc_commit(&s_full[buf]);
-            };
-            if (chunks > 0) scores(0);
+                SPL_A1(2);
+            }
+            SPL_AOUT(34, 3);
+        }
+    } else if (warp == 2) {
+        // ---- tensor-core issue, value product: O^T[half] += V^T (tensor memory) x P (shared memory), sixteen tokens per instruction.
+        if (lane == 0) {
+            constexpr uint32_t idesc = spl_tc_idesc(NQ);
+            const uint64_t p_desc = spl_tc_desc_sw128(spl_smem_addr(p_tile));
             for (int i = 0; i < chunks && ok; ++i) {
-                if (i + 1 < chunks) scores(i + 1);
                 const int pb = i & 1;
-                ok = ok && spl_mbar_wait(&p_full[pb], (i >> 1) & 1);
+                SPL_A0();
+                ok = spl_mbar_wait(&p_full[pb], (i >> 1) & 1);
+                SPL_A1(0);
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) {
                     ok = ok && spl_mbar_wait(&va_full[h], i & 1);
+                    SPL_A1(1);
                     if (!ok) break;
                     spl_tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks)
-                        spl_tc_mma_ts(tmem_o + h * 64, tmem_va + h * 64 + ks * 8,
-                                      spl_tc_desc_sw128(spl_smem_addr(p_tile + pb * PTILE + (ks >> 2) * QTILE) + (ks & 3) * 32), idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                        spl_tc_mma_ts(tmem_o + h * 64, tmem_va + h * 64 + ks * 8, p_desc + uint64_t((pb * PTILE + (ks >> 2) * QTILE + (ks & 3) * 32) >> 4), idesc, (i > 0 || ks > 0) ? 1u : 0u);
                     spl_tc_commit(&va_free[h]);
+                    SPL_A1(2);
                 }
                 if (!ok) break;
                 spl_tc_commit(&p_free[pb]);
                 spl_tc_commit(&o_done[pb]);
+                SPL_A1(2);
             }
+            SPL_AOUT(37, 3);
         }
     } else if (warp >= 4 && warp < 8) {
         // ---- K: thread = token. Its head_dim int8 -> fp16 pairs -> tensor memory, 128 channels (64 columns) at a time.
@@ -291,7 +319,9 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
         const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
         for (int i = 0; i < chunks && ok; ++i) {
             const int st = i % NST;
+            SPL_A0();
             ok = spl_mbar_wait(&full_kv[st], (i / NST) & 1);
+            SPL_A1(0);
             if (!ok) break;
             const unsigned char *src = ring + size_t(st) * STAGE + token * 16;
 #pragma unroll
@@ -301,7 +331,9 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                 for (int pc = 0; pc < 8; ++pc)
                     spl_s8x16_to_h2x8(*reinterpret_cast<const uint4 *>(src + (h * 8 + pc) * (CH * 16)), a + pc * 8);
                 if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_kv[st]); }
+                SPL_A1(1);
                 ok = spl_mbar_wait(&ka_free[h], (i & 1) ^ 1);
+                SPL_A1(2);
                 if (!ok) break;
                 spl_tc_fence_after();
                 spl_tc_st32(tmem_ka + lane_base + h * 64, a);
@@ -310,15 +342,19 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                 spl_tc_fence_before();
                 __syncwarp();
                 if (lane == 0) spl_mbar_arrive(&ka_full[h]);
+                SPL_A1(3);
             }
         }
+        if (warp == 4) SPL_AOUT(40, 4);
     } else if (warp >= 8 && warp < 12) {
         // ---- V: thread = channel of a half. Its 128 tokens int8 -> fp16 pairs -> tensor memory.
         const int channel = (warp & 3) * 32 + lane;
         const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
         for (int i = 0; i < chunks && ok; ++i) {
             const int st = i % NST;
+            SPL_A0();
             ok = spl_mbar_wait(&full_kv[st], (i / NST) & 1);
+            SPL_A1(0);
             if (!ok) break;
             const unsigned char *src = ring + size_t(st) * STAGE + CHUNK_BYTES;
 #pragma unroll
@@ -328,7 +364,9 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                 for (int tb = 0; tb < 8; ++tb)
                     spl_s8x16_to_h2x8(*reinterpret_cast<const uint4 *>(src + tb * (HD * 16) + (h * 128 + channel) * 16), a + tb * 8);
                 if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_kv[st]); }
+                SPL_A1(1);
                 ok = spl_mbar_wait(&va_free[h], (i & 1) ^ 1);
+                SPL_A1(2);
                 if (!ok) break;
                 spl_tc_fence_after();
                 spl_tc_st32(tmem_va + lane_base + h * 64, a);
@@ -337,110 +375,168 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                 spl_tc_fence_before();
                 __syncwarp();
                 if (lane == 0) spl_mbar_arrive(&va_full[h]);
+                SPL_A1(3);
             }
         }
+        if (warp == 8) SPL_AOUT(44, 4);
     } else if (warp >= 12) {
         // ---- softmax: thread = token of the chunk (scores), = channel of a half (rescale and output).
         const int w4 = warp & 3, token = w4 * 32 + lane;
         const uint32_t lane_base = uint32_t(w4 * 32) << 16;
+        float *my_next = ref_next + w4 * NQ, *my_factor = ref_factor + w4 * NQ;       // this warp's copy: no cross-warp hazards
         float sum[NQ];
 #pragma unroll
         for (int n = 0; n < NQ; ++n) sum[n] = 0.0f;
-        for (int n = lane; n < NQ; n += 32) refs[w4 * NQ + n] = make_float2(-INFINITY, 1.0f);
+        for (int n = lane; n < NQ; n += 32) { my_next[n] = -INFINITY; my_factor[n] = 1.0f; }
         __syncwarp();
+        // The thread's byte offsets inside an operand row for each of the eight swizzle phases of a row.
+        uint32_t phase_offset[8];
+        int raises[2] = {0, 0};            // completed exchanges of maxima, per chunk parity
+#pragma unroll
+        for (int j = 0; j < 8; ++j) phase_offset[j] = uint32_t((token >> 6) * QTILE) + spl_sw128_offset(j, token & 63);
         for (int i = 0; i < chunks && ok; ++i) {
             const int st = i % NST, buf = i & 1, par = i & 1;
+            SPL_A0();
             ok = spl_mbar_wait(&full_kv[st], (i / NST) & 1);
+            SPL_A1(0);
             if (!ok) break;
             const float *scales = reinterpret_cast<const float *>(ring + size_t(st) * STAGE + 2 * CHUNK_BYTES);
-            const float ksl = scales[token] * p.scale * LOG2E, vsc = scales[CH + token];
+            const uint32_t token_index = token_begin + uint32_t(i) * CH + token;
+            // Tokens past the last visible one were never written: their scales are whatever the pool held.
+            const bool written = token_index < max_visible;
+            const float ksl = written ? scales[token] * p.scale * LOG2E : 0.0f, vsc = written ? scales[CH + token] * SPL_ATTN_PSCALE : 0.0f;
             __syncwarp();
             if (lane == 0) spl_mbar_arrive(&empty_kv[st]);
-            const uint32_t token_index = token_begin + uint32_t(i) * CH + token;
-            // Rows rb >= first_hidden do not see this token; a chunk below every row's position needs no mask.
+            // A token is visible to rows rb >= first_seen; a chunk wholly below the first row's position needs no mask
+            // (padding queries are zero there and their columns are never written out).
             const bool whole = token_begin + uint32_t(i + 1) * CH <= first_pos + 1;
-            const int first_seen = whole ? 0 : max(0, int(token_index) - int(first_pos));     // visible to rows rb >= first_seen
+            const int first_seen = max(0, int(token_index) - int(first_pos));
             ok = spl_mbar_wait(&s_full[buf], (i >> 1) & 1);
+            SPL_A1(1);
             if (!ok) break;
             spl_tc_fence_after();
-            // Pass 1: the chunk's maximum per query.
+            const uint32_t s_addr = tmem_s + lane_base + buf * 64, p_base = spl_smem_addr(p_tile + buf * PTILE);
+            auto chunk_body = [&](auto masked_tag) -> bool {
+                constexpr bool MASKED = decltype(masked_tag)::value;
+                // Pass 1: does any score of the chunk exceed its query's reference by more than the head-room?
+                float over = -INFINITY;
 #pragma unroll
-            for (int c0 = 0; c0 < NQ; c0 += 16) {
-                uint32_t v[16];
-                spl_tc_ld16(v, tmem_s + lane_base + buf * 64 + c0);
-                spl_tc_ld_wait();
+                for (int c0 = 0; c0 < NQ; c0 += 16) {
+                    uint32_t v[16];
+                    float nx[16];
 #pragma unroll
-                for (int r = 0; r < 16; ++r) {
-                    const int n = c0 + r, rb = n / PER_KV;
-                    const bool seen = whole || (rb >= first_seen && rb < valid_rows);
-                    const float s = seen ? __uint_as_float(v[r]) * ksl : -INFINITY;
-                    const float top = spl_redux_max(s);
-                    if (lane == (n & 31)) xmax[(par * 4 + w4) * NQ + n] = top;
+                    for (int r4 = 0; r4 < 4; ++r4) *reinterpret_cast<float4 *>(nx + 4 * r4) = *reinterpret_cast<const float4 *>(my_next + c0 + 4 * r4);
+                    spl_tc_ld16(v, s_addr + c0);
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        float t = fmaf(__uint_as_float(v[r]), ksl, -nx[r]);
+                        if (MASKED) { const int rb = (c0 + r) / PER_KV; t = (rb >= first_seen && rb < valid_rows) ? t : -INFINITY; }
+                        over = fmaxf(over, t);
+                    }
                 }
-            }
-            // The four warps exchange their maxima through shared memory; the wait is bounded like every other.
-            __syncwarp();
-            if (lane == 0) spl_mbar_arrive(&x_full[par]);
-            ok = spl_mbar_wait(&x_full[par], (i >> 1) & 1);
-            if (!ok) break;
-            bool moved = false;
-            for (int n = lane; n < NQ; n += 32) {
-                const float top = fmaxf(fmaxf(xmax[(par * 4 + 0) * NQ + n], xmax[(par * 4 + 1) * NQ + n]),
-                                        fmaxf(xmax[(par * 4 + 2) * NQ + n], xmax[(par * 4 + 3) * NQ + n]));
-                const float old = refs[w4 * NQ + n].x, next = fmaxf(old, top);
-                const bool same = old == -INFINITY || next == old;
-                refs[w4 * NQ + n] = make_float2(next, same ? 1.0f : spl_ex2(old - next));
-                moved = moved || !same;
-            }
-            moved = __any_sync(0xffffffffu, moved);
-            __syncwarp();
-            // The probability tile of two chunks ago has been read (and with it that chunk's value product has finished,
-            // so the wait below on the previous chunk's completion cannot see a stale phase).
-            ok = spl_mbar_wait(&p_free[buf], ((i >> 1) & 1) ^ 1);
-            if (!ok) break;
-            if (moved && i > 0) {
-                // Rescale O^T (this warp's 32 channels of each half) once the previous value product has finished.
-                ok = spl_mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1);
-                if (!ok) break;
-                spl_tc_fence_after();
-#pragma unroll
-                for (int h = 0; h < HALVES; ++h)
+                const bool any_over = __any_sync(0xffffffffu, over > SPL_ATTN_HEADROOM);
+                SPL_A1(2);
+                if (lane == 0) {
+                    if (any_over) atomicMax(xflag + par, i + 1);
+                    spl_mbar_arrive(&x_full[par]);
+                }
+                if (!spl_mbar_wait(&x_full[par], (i >> 1) & 1)) return false;
+                const bool raise = *reinterpret_cast<volatile int *>(xflag + par) == i + 1;
+                SPL_A1(3);
+                // The probability tile of two chunks ago has been read (and with it that chunk's value product has finished,
+                // so a wait on the previous chunk's completion cannot see a stale phase).
+                if (!spl_mbar_wait(&p_free[buf], ((i >> 1) & 1) ^ 1)) return false;
+                SPL_A1(4);
+                if (raise) {
+                    // Some score is far above its reference (always so in a span's first chunk): raise every reference to its
+                    // query's maximum so far, and rescale the sums and O^T by exp2(old - new).
 #pragma unroll
                     for (int c0 = 0; c0 < NQ; c0 += 16) {
                         uint32_t v[16];
-                        spl_tc_ld16(v, tmem_o + lane_base + h * 64 + c0);
-                        spl_tc_ld_wait();
+                        spl_tc_ld16(v, s_addr + c0);
 #pragma unroll
-                        for (int r = 0; r < 16; ++r) v[r] = __float_as_uint(__uint_as_float(v[r]) * refs[w4 * NQ + c0 + r].y);
-                        spl_tc_st16(tmem_o + lane_base + h * 64 + c0, v);
+                        for (int r = 0; r < 16; ++r) {
+                            const int n = c0 + r;
+                            float sc = __uint_as_float(v[r]) * ksl;
+                            if (MASKED) { const int rb = n / PER_KV; sc = (rb >= first_seen && rb < valid_rows) ? sc : -INFINITY; }
+                            const float top = spl_redux_max(sc);
+                            if (lane == (n & 31)) xmax[(par * 4 + w4) * NQ + n] = top;
+                        }
                     }
-                spl_tc_st_wait();
-                spl_tc_fence_before();
-            }
-            // Pass 2: probabilities into the operand tile of the value product.
-            unsigned char *pt = p_tile + buf * PTILE + (token >> 6) * QTILE;
-            const int tk = token & 63;
+                    __syncwarp();
+                    if (lane == 0) spl_mbar_arrive(&y_full[par]);
+                    if (!spl_mbar_wait(&y_full[par], raises[par] & 1)) return false;
+                    ++raises[par];
+                    for (int n = lane; n < NQ; n += 32) {
+                        const float top = fmaxf(fmaxf(xmax[(par * 4 + 0) * NQ + n], xmax[(par * 4 + 1) * NQ + n]),
+                                                fmaxf(xmax[(par * 4 + 2) * NQ + n], xmax[(par * 4 + 3) * NQ + n]));
+                        const float old = my_next[n], next = fmaxf(old, top);
+                        my_next[n] = next; my_factor[n] = (old == -INFINITY || next == old) ? 1.0f : spl_ex2(old - next);
+                    }
+                    __syncwarp();
+                    if (i > 0) {
+                        if (!spl_mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1)) return false;
+                        spl_tc_fence_after();
 #pragma unroll
-            for (int c0 = 0; c0 < NQ; c0 += 16) {
-                uint32_t v[16];
-                spl_tc_ld16(v, tmem_s + lane_base + buf * 64 + c0);
-                spl_tc_ld_wait();
+                        for (int c0 = 0; c0 < NQ; c0 += 16) {
+                            float f[16];
 #pragma unroll
-                for (int r = 0; r < 16; ++r) {
-                    const int n = c0 + r, rb = n / PER_KV;
-                    const bool seen = whole || (rb >= first_seen && rb < valid_rows);
-                    const float2 rf = refs[w4 * NQ + n];
-                    const float prob = seen ? spl_ex2(__uint_as_float(v[r]) * ksl - rf.x) : 0.0f;
-                    sum[n] = moved ? fmaf(sum[n], rf.y, prob) : sum[n] + prob;
-                    const float pw = seen ? __bfloat162float(__float2bfloat16_rn(prob * vsc)) * SPL_ATTN_PSCALE : 0.0f;
-                    *reinterpret_cast<__half *>(pt + spl_sw128_offset(n, tk)) = __float2half_rn(pw);
+                            for (int r4 = 0; r4 < 4; ++r4) *reinterpret_cast<float4 *>(f + 4 * r4) = *reinterpret_cast<const float4 *>(my_factor + c0 + 4 * r4);
+#pragma unroll
+                            for (int h = 0; h < HALVES; ++h) {
+                                uint32_t v[16];
+                                spl_tc_ld16(v, tmem_o + lane_base + h * 64 + c0);
+#pragma unroll
+                                for (int r = 0; r < 16; ++r) v[r] = __float_as_uint(__uint_as_float(v[r]) * f[r]);
+                                spl_tc_st16(tmem_o + lane_base + h * 64 + c0, v);
+                            }
+#pragma unroll
+                            for (int r = 0; r < 16; ++r) sum[c0 + r] *= f[r];
+                        }
+                        spl_tc_st_wait();
+                        spl_tc_fence_before();
+                    }
                 }
-            }
+                SPL_A1(5);
+                // Pass 2: probabilities into the operand tile of the value product, two queries at a time:
+                // P = bf16(p * vScale), held as fp16 of SPL_ATTN_PSCALE * P (both roundings of a pair are single instructions).
+#pragma unroll
+                for (int c0 = 0; c0 < NQ; c0 += 16) {
+                    uint32_t v[16];
+                    float nx[16];
+#pragma unroll
+                    for (int r4 = 0; r4 < 4; ++r4) *reinterpret_cast<float4 *>(nx + 4 * r4) = *reinterpret_cast<const float4 *>(my_next + c0 + 4 * r4);
+                    spl_tc_ld16(v, s_addr + c0);
+#pragma unroll
+                    for (int r = 0; r < 16; r += 2) {
+                        float pr[2];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int n = c0 + r + e;
+                            pr[e] = spl_ex2(fmaf(__uint_as_float(v[r + e]), ksl, -nx[r + e]));
+                            if (MASKED) { const int rb = n / PER_KV; pr[e] = (rb >= first_seen && rb < valid_rows) ? pr[e] : 0.0f; }
+                            sum[n] += pr[e];
+                        }
+                        uint32_t packed_bf16, packed_f16;
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(packed_bf16) : "f"(pr[1] * vsc), "f"(pr[0] * vsc));
+                        asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(packed_f16) : "f"(__uint_as_float(packed_bf16 & 0xFFFF0000u)), "f"(__uint_as_float(packed_bf16 << 16)));
+                        const int n0 = c0 + r, n1 = n0 + 1;
+                        asm volatile("{\n .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n st.shared.b16 [%0], lo;\n st.shared.b16 [%1], hi;\n}\n"
+                                     ::"r"(p_base + uint32_t((n0 >> 3) * 1024) + phase_offset[n0 & 7]),
+                                       "r"(p_base + uint32_t((n1 >> 3) * 1024) + phase_offset[n1 & 7]), "r"(packed_f16) : "memory");
+                    }
+                }
+                return true;
+            };
+            ok = whole ? chunk_body(SplFalse{}) : chunk_body(SplTrue{});
+            if (!ok) break;
             spl_tc_fence_before();
             spl_fence_proxy_async();
             __syncwarp();
             if (lane == 0) { spl_mbar_arrive(&s_free[buf]); spl_mbar_arrive(&p_full[buf]); }
+            SPL_A1(6);
         }
+        if (warp == 12) { SPL_AOUT(48, 7); if (trace) error_flag[55] = chunks; }
         // ---- the span's partial: [reference, sum p, out[head_dim]] per query (row, head).
         if (ok && chunks > 0) ok = spl_mbar_wait(&o_done[(chunks - 1) & 1], ((chunks - 1) >> 1) & 1);
         if (ok) {
@@ -459,7 +555,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
             if (token < NQ && token / PER_KV < valid_rows) {
                 const int rb = token / PER_KV, hq = token % PER_KV;
                 float *partial = partials + ((size_t(r0 + rb) * p.heads + kv_head * PER_KV + hq) * p.spans + span) * record;
-                partial[0] = chunks > 0 ? refs[w4 * NQ + token].x * LN2 : -INFINITY;
+                partial[0] = chunks > 0 ? my_next[token] * LN2 : -INFINITY;
                 partial[1] = ((xsum[token] + xsum[NQ + token]) + xsum[2 * NQ + token]) + xsum[3 * NQ + token];
             }
 #pragma unroll

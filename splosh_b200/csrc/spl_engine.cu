@@ -353,6 +353,13 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
         SPL_CUDA(cudaMemcpy(&flag, e->tc_error, sizeof flag, cudaMemcpyDeviceToHost));
         if (flag) { cudaMemset(e->tc_error, 0, sizeof flag); return e->fail(SPL_ERR_TIMEOUT, "a GEMM block gave up waiting (role " + std::to_string(flag - 1) + ")"); }
     }
+    if (getenv("SPL_ATTN_TRACE")) {
+        int t[64]; cudaMemcpy(t, e->tc_error, sizeof t, cudaMemcpyDeviceToHost);
+        fprintf(stderr, "attention trace, cycles per chunk: copy [wait %d, issue %d] mma [wait S slot %d, wait K %d, issue S %d, wait P %d, wait V %d, issue PV %d] "
+                        "K [wait %d, convert %d, wait slot %d, store %d] V [wait %d, convert %d, wait slot %d, store %d] "
+                        "softmax [wait kv %d, wait S %d, pass1 %d, exchange %d, wait P slot %d, rescale %d, pass2 %d] chunks %d\n",
+                t[32], t[33], t[34], t[35], t[36], t[37], t[38], t[39], t[40], t[41], t[42], t[43], t[44], t[45], t[46], t[47], t[48], t[49], t[50], t[51], t[52], t[53], t[54], t[55]);
+    }
     profile_collect(e);
     e->last_rows = R; e->last_logit_rows = int(t->logit_rows);
     if (stats) {
@@ -520,6 +527,7 @@ spl_status create(const spl_geometry *gp, const spl_config *cp, spl_engine *e) {
     if ((s = device_alloc(e, &e->hsn_sums, size_t(LP) * H / 64, &e->scratch_bytes)) != SPL_OK) return s;
     if ((s = device_alloc(e, &e->tc_error, 64)) != SPL_OK) return s;
     SPL_CUDA(cudaMemsetAsync(e->tc_error, 0, 64 * sizeof(int), e->stream));
+    if (getenv("SPL_ATTN_TRACE")) { const int magic[2] = {0x7ACE, 0x200}; SPL_CUDA(cudaMemcpyAsync(e->tc_error + 1, magic, sizeof magic, cudaMemcpyHostToDevice, e->stream)); }
     SPL_CUDA(cudaMemsetAsync(e->xn, 0, size_t(RP) * H * 2, e->stream));
     SPL_CUDA(cudaMemsetAsync(e->xn_sums, 0, size_t(RP) * H / 64 * 4, e->stream));
     SPL_CUDA(cudaMemsetAsync(e->core_sums, 0, size_t(RP) * e->core_ld / 64 * 4, e->stream));

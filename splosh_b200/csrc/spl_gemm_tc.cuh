@@ -185,7 +185,10 @@ __host__ __device__ constexpr uint32_t spl_tc_idesc(int n) {
 
 #define SPL_TC_LD(N, regs, addr) spl_tc_ld##N(regs, addr)
 __device__ __forceinline__ void spl_tc_ld16(uint32_t (&r)[16], uint32_t taddr) {
+    // The load and its wait are one statement: the registers are defined only after the wait, and a separate
+    // wait statement would not stop the compiler from scheduling their readers before it.
     asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+                 "tcgen05.wait::ld.sync.aligned;\n"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
                    "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]) : "r"(taddr));
 }
