@@ -28,6 +28,7 @@ sys.path.insert(0, ROOT)
 
 SESSIONS, BLOCK = 8, 8
 CONTEXT_LOW, CONTEXT_HIGH = 36 * 1024, 42 * 1024
+SPAN_TARGET = 576      # scan blocks per step the table builder aims for (engine configuration)
 WEIGHT_SEED, TOKEN_SEED = 0x5EED6D17, 0xC0FFEE00
 
 
@@ -206,7 +207,10 @@ def main():
     ctx = [int(c * args.context_scale) for c in contexts(rank)]
     steps_total = args.warmup + 2 * args.steps + 2
     pages = sum((c + BLOCK * steps_total) // 256 + 2 for c in ctx)
-    cfg = S.EngineConfig(max_slots=SESSIONS, max_rows=SESSIONS * BLOCK, kv_pages=pages, max_context=max(ctx) + BLOCK * steps_total + 256, device=local)
+    # The engine's span target (how many scan blocks a step should make; the reference tunes it to its GPU, 592 there): one
+    # scan block fills an SM here, so 576 = 4 blocks on each of 144 SMs keeps the 18 x 32 blocks of this workload in four full waves.
+    cfg = S.EngineConfig(max_slots=SESSIONS, max_rows=SESSIONS * BLOCK, kv_pages=pages, max_context=max(ctx) + BLOCK * steps_total + 256, device=local,
+                         span_target=SPAN_TARGET)
     engine = S.Engine(g, cfg)
     from splosh_b200 import synthetic
     synthetic.load_vectors(engine, WEIGHT_SEED)
@@ -279,7 +283,7 @@ def main():
             "dtype": "bf16 x int4 -> fp32 (int8 KV, fp32 state)", "data": "synthetic",
             "config": {"workload": f"27B-shape ({g.layers} blocks) MLX 4-bit g64, 8 sessions x 8-row verify blocks = 64 rows per step, contexts "
                                    f"{min(ctx)}-{max(ctx)} tokens, int8 paged KV, all rows accepted each step", "sessions_per_gpu": SESSIONS,
-                       "rows_per_step": rows_per_step, "parallelism": f"sessions sharded, {world} replica(s)",
+                       "rows_per_step": rows_per_step, "span_target": SPAN_TARGET, "parallelism": f"sessions sharded, {world} replica(s)",
                        "l2": "inputs larger than L2: 14.4 GB of weights and the KV pool stream every step"},
             "e2e": {"value": total_rows / wall_max, "unit": "tok/s", "h2d_bytes_per_step": tables_bytes, "d2h_bytes_per_step": rows_per_step * 4},
             "gpu_launches": launches,

@@ -108,22 +108,23 @@ spl_attn_prepare_kernel(const float *__restrict__ proj, const uint16_t *__restri
 // warp reduction (redux) plus a four-way exchange; sums stay per thread until the end of the span.
 // When a maximum moves, the softmax warps rescale O^T in tensor memory before the next value product.
 //
-// Warps: 0 copies (bulk copies of whole 128-token chunks into a ring), 1 tensor-core issue, 4-7 K -> tensor
-// memory, 8-11 V -> tensor memory, 12-15 softmax, rescale and the partial's output. Every wait is bounded.
+// Warps: 0-3 softmax, rescale and the partial's output, 4-7 K -> tensor memory, 8-11 V -> tensor memory, 12 copies (bulk
+// copies of whole 128-token chunks into a ring), 13 and 14 tensor-core issue of the score and the value product.
+// Every wait is bounded.
 // Tensor memory (512 columns): S two buffers at 0 and 64, O halves at 128 and 192, K operand at 256, V at 384.
 #define SPL_ATTN_CH 128               // tokens per chunk
 #define SPL_ATTN_HEADROOM 6.0f        // a score may exceed its query's reference by this much (log2) before the reference is raised
 #define SPL_ATTN_PSCALE 64.0f         // 4096 / 2^headroom: keeps small probabilities normal in fp16 and large ones finite; removed at the end
 struct SplTrue { static constexpr bool value = true; };
 struct SplFalse { static constexpr bool value = false; };
-#define SPL_ATTN_THREADS 512
+#define SPL_ATTN_THREADS 480
 
 __host__ __device__ constexpr int spl_attn_nq(int per_kv) { return (8 * per_kv + 15) / 16 * 16; }
 __host__ __device__ constexpr int spl_attn_stages(int hd) { return hd >= 256 ? 2 : 4; }
 __host__ __device__ constexpr size_t spl_attn_stage_bytes(int hd) { return size_t(2) * SPL_ATTN_CH * hd + 1024; }
 __host__ __device__ constexpr size_t spl_attn_smem_bytes(int hd, int nq) {
     return 1024 + spl_attn_stages(hd) * spl_attn_stage_bytes(hd) + size_t(hd / 64) * nq * 128 /* Q */ + size_t(2) * 2 * nq * 128 /* P */
-           + size_t(2) * 4 * nq * 4 /* chunk maxima */ + size_t(4) * nq * 8 /* per-warp reference and factor */ + size_t(4) * nq * 4 /* sums */ + 512 /* barriers */;
+           + size_t(2) * 4 * nq * 4 /* chunk maxima */ + size_t(4) * nq * 8 /* per-warp reference and factor */ + size_t(4) * nq * 4 + size_t(nq) * SPL_ATTN_CH * 4 /* sums */ + 512 /* barriers */;
 }
 
 __device__ __forceinline__ void spl_tc_st32(uint32_t taddr, const uint32_t *r) {
@@ -175,7 +176,8 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
     float *xmax = reinterpret_cast<float *>(ring + size_t(NST) * STAGE);   // [2][4][NQ]
     float *ref_next = xmax + 2 * 4 * NQ, *ref_factor = ref_next + 4 * NQ;  // [4][NQ] each: running reference (log2 domain) and the chunk's rescale factor, one copy per softmax warp
     float *xsum = ref_factor + 4 * NQ;                                     // [4][NQ]
-    uint64_t *bars = reinterpret_cast<uint64_t *>(xsum + 4 * NQ);
+    float *tsum = xsum + 4 * NQ;                                           // [NQ][128] sums of p per (query, token lane)
+    uint64_t *bars = reinterpret_cast<uint64_t *>(tsum + NQ * CH);
     uint64_t *full_kv = bars, *empty_kv = full_kv + NST, *ka_full = empty_kv + NST, *ka_free = ka_full + 2, *va_full = ka_free + 2,
              *va_free = va_full + 2, *s_full = va_free + 2, *s_free = s_full + 2, *p_full = s_free + 2, *p_free = p_full + 2, *o_done = p_free + 2, *x_full = o_done + 2, *y_full = x_full + 2, *sum_full = y_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sum_full + 1);
@@ -204,7 +206,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
         spl_mbar_init(sum_full, 4);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 1) {
+    if (warp == 13) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(spl_smem_addr(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
@@ -224,14 +226,23 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_s = tmem, tmem_o = tmem + 128, tmem_ka = tmem + 256, tmem_va = tmem + 384;
     bool ok = true;
-    // Debug trace: cycles per chunk that one thread of each role of block (0, 0) spends in its waits and its work.
+    // Debug trace (builds with -DSPL_TRACE only): cycles per chunk that one thread of each role of block (0, 0) spends in
+    // its waits and its work.
+#ifdef SPL_TRACE
     const bool trace = blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && error_flag[1] == 0x7ACE && (error_flag[2] & 0x200);
     long long tt[8] = {0, 0, 0, 0, 0, 0, 0, 0}, t_mark = 0;
 #define SPL_A0() do { if (trace) t_mark = clock64(); } while (0)
 #define SPL_A1(k) do { if (trace) { const long long now__ = clock64(); tt[k] += now__ - t_mark; t_mark = now__; } } while (0)
 #define SPL_AOUT(base, n) do { if (trace && chunks > 0) for (int k__ = 0; k__ < n; ++k__) error_flag[base + k__] = int(tt[k__] / chunks); } while (0)
+#define SPL_ACHUNKS() do { if (trace) error_flag[55] = chunks; } while (0)
+#else
+#define SPL_A0() do { } while (0)
+#define SPL_A1(k) do { } while (0)
+#define SPL_AOUT(base, n) do { } while (0)
+#define SPL_ACHUNKS() do { } while (0)
+#endif
 
-    if (warp == 0) {
+    if (warp == 12) {
         // ---- copies: one chunk = 128 tokens of one kv head = K, V and their scales, each contiguous in the pool.
         if (lane == 0) {
             for (int i = 0; i < chunks && ok; ++i) {
@@ -253,7 +264,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
             }
             SPL_AOUT(32, 2);
         }
-    } else if (warp == 1) {
+    } else if (warp == 13) {
         // ---- tensor-core issue, score product: S^T[buffer] = K (tensor memory) x Q (shared memory), sixteen channels per instruction.
         // (Issuing an instruction costs its thread on the order of a hundred cycles, so the two products have a thread each.)
         if (lane == 0) {
@@ -284,7 +295,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
             }
             SPL_AOUT(34, 3);
         }
-    } else if (warp == 2) {
+    } else if (warp == 14) {
         // ---- tensor-core issue, value product: O^T[half] += V^T (tensor memory) x P (shared memory), sixteen tokens per instruction.
         if (lane == 0) {
             constexpr uint32_t idesc = spl_tc_idesc(NQ);
@@ -324,20 +335,22 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
             SPL_A1(0);
             if (!ok) break;
             const unsigned char *src = ring + size_t(st) * STAGE + token * 16;
-#pragma unroll
+#pragma unroll 1
             for (int h = 0; h < HALVES; ++h) {
-                uint32_t a[64];
-#pragma unroll
-                for (int pc = 0; pc < 8; ++pc)
-                    spl_s8x16_to_h2x8(*reinterpret_cast<const uint4 *>(src + (h * 8 + pc) * (CH * 16)), a + pc * 8);
-                if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_kv[st]); }
                 SPL_A1(1);
                 ok = spl_mbar_wait(&ka_free[h], (i & 1) ^ 1);
                 SPL_A1(2);
                 if (!ok) break;
                 spl_tc_fence_after();
-                spl_tc_st32(tmem_ka + lane_base + h * 64, a);
-                spl_tc_st32(tmem_ka + lane_base + h * 64 + 32, a + 32);
+#pragma unroll 1
+                for (int b = 0; b < 2; ++b) {
+                    uint32_t a[32];
+#pragma unroll
+                    for (int pc = 0; pc < 4; ++pc)
+                        spl_s8x16_to_h2x8(*reinterpret_cast<const uint4 *>(src + (h * 8 + 4 * b + pc) * (CH * 16)), a + pc * 8);
+                    spl_tc_st32(tmem_ka + lane_base + h * 64 + 32 * b, a);
+                }
+                if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_kv[st]); }
                 spl_tc_st_wait();
                 spl_tc_fence_before();
                 __syncwarp();
@@ -357,20 +370,22 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
             SPL_A1(0);
             if (!ok) break;
             const unsigned char *src = ring + size_t(st) * STAGE + CHUNK_BYTES;
-#pragma unroll
+#pragma unroll 1
             for (int h = 0; h < HALVES; ++h) {
-                uint32_t a[64];
-#pragma unroll
-                for (int tb = 0; tb < 8; ++tb)
-                    spl_s8x16_to_h2x8(*reinterpret_cast<const uint4 *>(src + tb * (HD * 16) + (h * 128 + channel) * 16), a + tb * 8);
-                if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_kv[st]); }
                 SPL_A1(1);
                 ok = spl_mbar_wait(&va_free[h], (i & 1) ^ 1);
                 SPL_A1(2);
                 if (!ok) break;
                 spl_tc_fence_after();
-                spl_tc_st32(tmem_va + lane_base + h * 64, a);
-                spl_tc_st32(tmem_va + lane_base + h * 64 + 32, a + 32);
+#pragma unroll 1
+                for (int b = 0; b < 2; ++b) {
+                    uint32_t a[32];
+#pragma unroll
+                    for (int tb = 0; tb < 4; ++tb)
+                        spl_s8x16_to_h2x8(*reinterpret_cast<const uint4 *>(src + (4 * b + tb) * (HD * 16) + (h * 128 + channel) * 16), a + tb * 8);
+                    spl_tc_st32(tmem_va + lane_base + h * 64 + 32 * b, a);
+                }
+                if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_kv[st]); }
                 spl_tc_st_wait();
                 spl_tc_fence_before();
                 __syncwarp();
@@ -379,14 +394,16 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
             }
         }
         if (warp == 8) SPL_AOUT(44, 4);
-    } else if (warp >= 12) {
+    } else if (warp < 4) {
         // ---- softmax: thread = token of the chunk (scores), = channel of a half (rescale and output).
         const int w4 = warp & 3, token = w4 * 32 + lane;
         const uint32_t lane_base = uint32_t(w4 * 32) << 16;
         float *my_next = ref_next + w4 * NQ, *my_factor = ref_factor + w4 * NQ;       // this warp's copy: no cross-warp hazards
-        float sum[NQ];
-#pragma unroll
-        for (int n = 0; n < NQ; ++n) sum[n] = 0.0f;
+        // Sum of p per (query, token lane), reduced over the lanes at the end of the span. They live in shared memory so that
+        // the passes below can be loops over blocks of sixteen queries (small code: five roles share the instruction caches).
+        float *my_sum = tsum + token;
+#pragma unroll 1
+        for (int n = 0; n < NQ; ++n) my_sum[n * CH] = 0.0f;
         for (int n = lane; n < NQ; n += 32) { my_next[n] = -INFINITY; my_factor[n] = 1.0f; }
         __syncwarp();
         // The thread's byte offsets inside an operand row for each of the eight swizzle phases of a row.
@@ -420,18 +437,21 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                 constexpr bool MASKED = decltype(masked_tag)::value;
                 // Pass 1: does any score of the chunk exceed its query's reference by more than the head-room?
                 float over = -INFINITY;
-#pragma unroll
+#pragma unroll 1
                 for (int c0 = 0; c0 < NQ; c0 += 16) {
                     uint32_t v[16];
-                    float nx[16];
-#pragma unroll
-                    for (int r4 = 0; r4 < 4; ++r4) *reinterpret_cast<float4 *>(nx + 4 * r4) = *reinterpret_cast<const float4 *>(my_next + c0 + 4 * r4);
                     spl_tc_ld16(v, s_addr + c0);
 #pragma unroll
-                    for (int r = 0; r < 16; ++r) {
-                        float t = fmaf(__uint_as_float(v[r]), ksl, -nx[r]);
-                        if (MASKED) { const int rb = (c0 + r) / PER_KV; t = (rb >= first_seen && rb < valid_rows) ? t : -INFINITY; }
-                        over = fmaxf(over, t);
+                    for (int r4 = 0; r4 < 4; ++r4) {
+                        const float4 nx4 = *reinterpret_cast<const float4 *>(my_next + c0 + 4 * r4);
+                        const float nx[4] = {nx4.x, nx4.y, nx4.z, nx4.w};
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const int r = 4 * r4 + e;
+                            float t = fmaf(__uint_as_float(v[r]), ksl, -nx[e]);
+                            if (MASKED) { const int rb = (c0 + r) / PER_KV; t = (rb >= first_seen && rb < valid_rows) ? t : -INFINITY; }
+                            over = fmaxf(over, t);
+                        }
                     }
                 }
                 const bool any_over = __any_sync(0xffffffffu, over > SPL_ATTN_HEADROOM);
@@ -450,7 +470,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                 if (raise) {
                     // Some score is far above its reference (always so in a span's first chunk): raise every reference to its
                     // query's maximum so far, and rescale the sums and O^T by exp2(old - new).
-#pragma unroll
+#pragma unroll 1
                     for (int c0 = 0; c0 < NQ; c0 += 16) {
                         uint32_t v[16];
                         spl_tc_ld16(v, s_addr + c0);
@@ -477,7 +497,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                     if (i > 0) {
                         if (!spl_mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1)) return false;
                         spl_tc_fence_after();
-#pragma unroll
+#pragma unroll 1
                         for (int c0 = 0; c0 < NQ; c0 += 16) {
                             float f[16];
 #pragma unroll
@@ -491,7 +511,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                                 spl_tc_st16(tmem_o + lane_base + h * 64 + c0, v);
                             }
 #pragma unroll
-                            for (int r = 0; r < 16; ++r) sum[c0 + r] *= f[r];
+                            for (int r = 0; r < 16; ++r) my_sum[(c0 + r) * CH] *= f[r];
                         }
                         spl_tc_st_wait();
                         spl_tc_fence_before();
@@ -500,30 +520,35 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                 SPL_A1(5);
                 // Pass 2: probabilities into the operand tile of the value product, two queries at a time:
                 // P = bf16(p * vScale), held as fp16 of SPL_ATTN_PSCALE * P (both roundings of a pair are single instructions).
-#pragma unroll
+#pragma unroll 1
                 for (int c0 = 0; c0 < NQ; c0 += 16) {
                     uint32_t v[16];
-                    float nx[16];
-#pragma unroll
-                    for (int r4 = 0; r4 < 4; ++r4) *reinterpret_cast<float4 *>(nx + 4 * r4) = *reinterpret_cast<const float4 *>(my_next + c0 + 4 * r4);
                     spl_tc_ld16(v, s_addr + c0);
 #pragma unroll
-                    for (int r = 0; r < 16; r += 2) {
-                        float pr[2];
+                    for (int r4 = 0; r4 < 16; r4 += 4) {
+                        const float4 nx4 = *reinterpret_cast<const float4 *>(my_next + c0 + r4);
+                        const float nx[4] = {nx4.x, nx4.y, nx4.z, nx4.w};
 #pragma unroll
-                        for (int e = 0; e < 2; ++e) {
-                            const int n = c0 + r + e;
-                            pr[e] = spl_ex2(fmaf(__uint_as_float(v[r + e]), ksl, -nx[r + e]));
-                            if (MASKED) { const int rb = n / PER_KV; pr[e] = (rb >= first_seen && rb < valid_rows) ? pr[e] : 0.0f; }
-                            sum[n] += pr[e];
+                        for (int r2 = 0; r2 < 4; r2 += 2) {
+                            const int r = r4 + r2;
+                            float pr[2];
+#pragma unroll
+                            for (int e = 0; e < 2; ++e) {
+                                const int n = c0 + r + e;
+                                pr[e] = spl_ex2(fmaf(__uint_as_float(v[r + e]), ksl, -nx[r2 + e]));
+                                if (MASKED) { const int rb = n / PER_KV; pr[e] = (rb >= first_seen && rb < valid_rows) ? pr[e] : 0.0f; }
+                                my_sum[n * CH] += pr[e];
+                            }
+                            uint32_t packed_bf16, packed_f16;
+                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(packed_bf16) : "f"(pr[1] * vsc), "f"(pr[0] * vsc));
+                            asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(packed_f16) : "f"(__uint_as_float(packed_bf16 & 0xFFFF0000u)), "f"(__uint_as_float(packed_bf16 << 16)));
+                            const int n0 = c0 + r, n1 = n0 + 1;
+                            // No memory clobber: the stores need no order against this thread's loads, and the fences that
+                            // follow the pass order them against everything later.
+                            asm volatile("{\n .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n st.shared.b16 [%0], lo;\n st.shared.b16 [%1], hi;\n}\n"
+                                         ::"r"(p_base + uint32_t((n0 >> 3) * 1024) + phase_offset[r & 7]),
+                                           "r"(p_base + uint32_t((n1 >> 3) * 1024) + phase_offset[(r + 1) & 7]), "r"(packed_f16));
                         }
-                        uint32_t packed_bf16, packed_f16;
-                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(packed_bf16) : "f"(pr[1] * vsc), "f"(pr[0] * vsc));
-                        asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(packed_f16) : "f"(__uint_as_float(packed_bf16 & 0xFFFF0000u)), "f"(__uint_as_float(packed_bf16 << 16)));
-                        const int n0 = c0 + r, n1 = n0 + 1;
-                        asm volatile("{\n .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n st.shared.b16 [%0], lo;\n st.shared.b16 [%1], hi;\n}\n"
-                                     ::"r"(p_base + uint32_t((n0 >> 3) * 1024) + phase_offset[n0 & 7]),
-                                       "r"(p_base + uint32_t((n1 >> 3) * 1024) + phase_offset[n1 & 7]), "r"(packed_f16) : "memory");
                     }
                 }
                 return true;
@@ -536,14 +561,14 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
             if (lane == 0) { spl_mbar_arrive(&s_free[buf]); spl_mbar_arrive(&p_full[buf]); }
             SPL_A1(6);
         }
-        if (warp == 12) { SPL_AOUT(48, 7); if (trace) error_flag[55] = chunks; }
+        if (warp == 0) { SPL_AOUT(48, 7); SPL_ACHUNKS(); }
         // ---- the span's partial: [reference, sum p, out[head_dim]] per query (row, head).
         if (ok && chunks > 0) ok = spl_mbar_wait(&o_done[(chunks - 1) & 1], ((chunks - 1) >> 1) & 1);
         if (ok) {
             spl_tc_fence_after();
-#pragma unroll
+#pragma unroll 1
             for (int n = 0; n < NQ; ++n) {
-                const float total = spl_warp_sum(sum[n]);
+                const float total = spl_warp_sum(my_sum[n * CH]);
                 if (lane == (n & 31)) xsum[w4 * NQ + n] = total;
             }
             __syncwarp();
@@ -578,7 +603,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
     if (!ok) atomicExch(error_flag, 100 + warp);
     spl_tc_fence_before();
     __syncthreads();
-    if (warp == 1) {
+    if (warp == 13) {
         spl_tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
     }

@@ -132,6 +132,7 @@ __global__ void spl_synth_q4_kernel(uint64_t seed, float factor, int rows, int k
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
 #define SPL_WAIT_LIMIT (1u << 22)     // polls before a wait gives up
+#define SPL_WAIT_HINT_NS 4000u        // suspend-time hint of one poll
 
 __device__ __forceinline__ uint32_t spl_smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
 __device__ __forceinline__ void spl_mbar_init(uint64_t *bar, uint32_t count) {
@@ -148,8 +149,10 @@ __device__ __forceinline__ bool spl_mbar_wait(uint64_t *bar, uint32_t parity) {
     const uint32_t addr = spl_smem_addr(bar);
     for (uint32_t spin = 0; spin < SPL_WAIT_LIMIT; ++spin) {
         uint32_t done;
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(done) : "r"(addr), "r"(parity) : "memory");
+        // The hint lets the hardware keep the thread suspended (off the issue slots its neighbours need) for up to that many
+        // nanoseconds per poll; completion of the phase wakes it at once.
+        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+                     : "=r"(done) : "r"(addr), "r"(parity), "r"(SPL_WAIT_HINT_NS) : "memory");
         if (done) return true;
     }
     return false;
@@ -287,11 +290,19 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     constexpr int NACC = RN <= 32 ? 4 : 2;
     const uint32_t tmem_d = tmem, tmem_a = tmem + 128;
     bool ok = true;
-    // Debug trace: cycles per group that one thread of each role of block (0, 0, 0) spends in its waits and its work.
+    // Debug trace (builds with -DSPL_TRACE only): cycles per group that one thread of each role of block (0, 0, 0) spends
+    // in its waits and its work.
+#ifdef SPL_TRACE
     const bool trace = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && error_flag[1] == 0x7ACE && (error_flag[2] & 0x100);
     long long t0 = 0, t1 = 0, t2 = 0, t3 = 0, t_mark = 0;
 #define SPL_T0() do { if (trace) t_mark = clock64(); } while (0)
 #define SPL_T1(acc) do { if (trace) { const long long now__ = clock64(); acc += now__ - t_mark; t_mark = now__; } } while (0)
+#define SPL_TOUT(statement) do { statement; } while (0)
+#else
+#define SPL_T0() do { } while (0)
+#define SPL_T1(acc) do { } while (0)
+#define SPL_TOUT(statement) do { } while (0)
+#endif
 
     if (warp == 12) {
         // ---- copies. Codes have their own ring; activations, their sums and the scale/bias words share the other.
@@ -332,7 +343,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                 }
                 SPL_T1(t2);
             }
-            if (trace) { error_flag[8] = int(t0 / g_count); error_flag[9] = int(t1 / g_count); error_flag[10] = int(t2 / g_count); }
+            SPL_TOUT(if (trace) { error_flag[8] = int(t0 / g_count); error_flag[9] = int(t1 / g_count); error_flag[10] = int(t2 / g_count); });
         }
     } else if (warp >= 13) {
         // ---- tensor-core issue: D[128 x RN] += A[128 x 64] (fp16, tensor memory) * B[RN x 64]^T (fp16, shared memory).
@@ -371,7 +382,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                 }
                 SPL_T1(t2);
             }
-            if (trace && m == 0) { error_flag[11] = int(t0 / g_count); error_flag[12] = int(t1 / g_count); error_flag[13] = int(t2 / g_count); }
+            SPL_TOUT(if (trace && m == 0) { error_flag[11] = int(t0 / g_count); error_flag[12] = int(t1 / g_count); error_flag[13] = int(t2 / g_count); });
             if (ok) spl_tc_commit(finished);
         }
     } else if (warp < 4 || warp >= 8) {
@@ -437,7 +448,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             if (lane == 0) spl_mbar_arrive(&full_a[un % (AST / 2)]);
             SPL_T1(t3);
         }
-        if (trace && warp == 0 && lane == 0) { error_flag[14] = int(t0 / g_count); error_flag[15] = int(t1 / g_count); error_flag[16] = int(t2 / g_count); error_flag[17] = int(t3 / g_count); }
+        SPL_TOUT(if (trace && warp == 0 && lane == 0) { error_flag[14] = int(t0 / g_count); error_flag[15] = int(t1 / g_count); error_flag[16] = int(t2 / g_count); error_flag[17] = int(t3 / g_count); });
     } else {
         // ---- epilogue: thread = output column. Per group acc[r] += (bias + 8 scale) * sum[r]; at the end the
         // tensor cores' accumulator is added.
@@ -471,7 +482,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         SPL_T0();
         if (ok) ok = spl_mbar_wait(finished, 0);
         SPL_T1(t2);
-        if (trace && warp == 4 && lane == 0) { error_flag[18] = int(t0 / g_count); error_flag[19] = int(t1 / g_count); error_flag[20] = int(t2 / g_count); error_flag[21] = g_count; }
+        SPL_TOUT(if (trace && warp == 4 && lane == 0) { error_flag[18] = int(t0 / g_count); error_flag[19] = int(t1 / g_count); error_flag[20] = int(t2 / g_count); error_flag[21] = g_count; });
         if (ok) {
             spl_tc_fence_after();
             const int n = tile * 128 + col;
