@@ -292,7 +292,7 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
                 e->proj, L.vec[SPL_VEC_CONV], e->conv[linear_index], e->d_runs, e->d_row_read, e->d_row_write, e->gdn_act, p);
             profile_end(e);
             profile_begin(e, KLASS_GDN, 0);
-            spl_gdn_recurrence_kernel<<<dim3(g.gdn_value_heads, t->run_count), 256, 0, e->stream>>>(
+            spl_gdn_recurrence_kernel<<<dim3(g.gdn_value_heads, t->run_count), SPL_GDN_THREADS, 0, e->stream>>>(
                 e->gdn_act, e->proj, L.vec[SPL_VEC_A_LOG], L.vec[SPL_VEC_DT_BIAS], L.vec[SPL_VEC_GDN_NORM], e->state[linear_index],
                 e->journal[linear_index], e->d_runs, e->d_run_info, core, p);
             profile_end(e);

@@ -46,126 +46,169 @@ spl_gdn_conv_kernel(const float *__restrict__ proj, const uint16_t *__restrict__
     }
 }
 
+// Packed pairs of fp32 (Blackwell's two-wide fp32 instructions): each half is an IEEE single operation, so the
+// results are bit for bit those of the scalar code.
+__device__ __forceinline__ float2 spl_fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(reinterpret_cast<unsigned long long &>(d))
+        : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)), "l"(reinterpret_cast<unsigned long long &>(c)));
+    return d;
+}
+__device__ __forceinline__ float2 spl_mul2(float2 a, float2 b) {
+    float2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(reinterpret_cast<unsigned long long &>(d))
+        : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)));
+    return d;
+}
 // The state update S' = S * decay + k * delta with the product rounded on its own, so that the
 // replay of a journal entry reproduces the original update bit for bit (engine.metal:654-659).
-__device__ __forceinline__ float spl_gdn_update(float s, float decay, float k, float delta) {
-    return __fmaf_rn(s, decay, __fmul_rn(k, delta));
+__device__ __forceinline__ float2 spl_gdn_update2(float2 s, float2 decay, float2 k, float2 delta) {
+    return spl_fma2(s, decay, spl_mul2(k, delta));
 }
 
 #define SPL_GDN_TC 16          // tokens prepared per pass
 #define SPL_GDN_D 128          // head dim (key and value)
+#define SPL_GDN_THREADS 1024
 
-// One thread block per (value head, run). Thread (j = tid / 2, half = tid % 2) keeps 64 elements
-// of state row j in registers: i = 8 m + 4 half + e. Per token (engine.metal:763-805):
+// One thread block per (value head, run): the head's whole 128 x 128 state in the registers of 1,024 threads.
+// Thread (j = tid / 8, part = tid % 8) keeps 16 elements of state row j: i = 32 m + 4 part + e. Rows are
+// independent, so a token costs each thread two short dot products (combined over the row's eight threads with
+// three shuffles) and no block barrier. Per token (engine.metal:763-805):
 //   mem = S k;  delta = (v - mem * decay * invK) * beta * invK;  S = S * decay + k (x) delta;
 //   o = (S q) * invQ
 // then the gated RMSNorm w * o * rsqrt(mean o^2 + eps) * silu(z) rounded to bf16, with its per-64
 // sums (engine.metal:812-833). A speculative run leaves a journal entry per row instead of writing
 // the state; entries accepted from the previous run are replayed first (engine.metal:744-761).
-// Grid (value_heads, runs), 256 threads.
-__global__ void __launch_bounds__(256)
+// Grid (value_heads, runs), 1,024 threads.
+__global__ void __launch_bounds__(SPL_GDN_THREADS, 1)
 spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict__ proj, const uint16_t *__restrict__ a_log,
                           const uint16_t *__restrict__ dt_bias, const uint16_t *__restrict__ norm_weight, float *state, float *journal,
                           const uint32_t *__restrict__ runs, const uint32_t *__restrict__ run_info, SplOperand core, SplGdnParams p) {
-    constexpr int D = SPL_GDN_D, TC = SPL_GDN_TC;
-    __shared__ __align__(16) float q_s[TC][D], k_s[TC][D], v_s[TC][D], o_s[TC][D];
-    __shared__ float scal[TC][4];        // invQ, invK, decay, beta
+    constexpr int D = SPL_GDN_D, TC = SPL_GDN_TC, NT = SPL_GDN_THREADS;
+    __shared__ __align__(16) float q_s[TC][D], k_s[TC][D], v_s[TC][D], o_s[TC][D], jk_s[TC][D];
+    __shared__ float scal[TC][4], jdecay[TC];        // invQ, invK, decay, beta per token; decay per replayed entry
     const int h = blockIdx.x, run = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int j = tid >> 1, half = tid & 1;
+    const int j = tid >> 3, part = tid & 7;
     const uint32_t slot = runs[run * 3], start = runs[run * 3 + 1], length = runs[run * 3 + 2];
     const bool speculative = run_info[run * 2] != 0;
     const uint32_t pending = run_info[run * 2 + 1];
     const int VH = p.value_heads, KH = p.key_heads, hk = h / (VH / KH);
-
-    float4 S[16];
-    float4 *stored = reinterpret_cast<float4 *>(state + ((size_t(slot) * VH + h) * D + j) * D) + half;
-#pragma unroll
-    for (int m = 0; m < 16; ++m) S[m] = stored[2 * m];
-
     float *jhead = journal + (size_t(slot) * SPL_JOURNAL_ROWS * VH + h) * SPL_JOURNAL_WIDTH;
-    // Replay accepted entries. The entry's k goes through shared memory.
-    for (uint32_t e = 0; e < pending; ++e) {
-        const float *entry = jhead + size_t(e) * VH * SPL_JOURNAL_WIDTH;
-        __syncthreads();
-        if (tid < D) k_s[0][tid] = entry[tid];
-        __syncthreads();
-        const float delta = entry[D + j], decay = entry[2 * D];
-#pragma unroll
-        for (int m = 0; m < 16; ++m) {
-            const float4 kv = *reinterpret_cast<const float4 *>(&k_s[0][8 * m + 4 * half]);
-            S[m].x = spl_gdn_update(S[m].x, decay, kv.x, delta); S[m].y = spl_gdn_update(S[m].y, decay, kv.y, delta);
-            S[m].z = spl_gdn_update(S[m].z, decay, kv.z, delta); S[m].w = spl_gdn_update(S[m].w, decay, kv.w, delta);
-        }
-    }
-    if (speculative && pending != 0) {
-#pragma unroll
-        for (int m = 0; m < 16; ++m) stored[2 * m] = S[m];
-    }
 
+    // Everything the block needs from memory is asked for before anything is waited for: the state, the journal entries
+    // to replay (k into jk_s, delta into o_s, which is free until the first token), and the first tokens' q, k, v.
+    float4 S[4];
+    float4 *stored = reinterpret_cast<float4 *>(state + ((size_t(slot) * VH + h) * D + j) * D) + part;
+#pragma unroll
+    for (int m = 0; m < 4; ++m) S[m] = stored[8 * m];
+    for (int idx = tid; idx < int(pending) * (2 * D / 4); idx += NT) {
+        const int e = idx / (2 * D / 4), i4 = idx % (2 * D / 4);
+        const float4 v = *reinterpret_cast<const float4 *>(jhead + size_t(e) * VH * SPL_JOURNAL_WIDTH + i4 * 4);
+        float *dst = i4 < D / 4 ? &jk_s[e][i4 * 4] : &o_s[e][i4 * 4 - D];
+        *reinterpret_cast<float4 *>(dst) = v;
+    }
+    if (tid < int(pending)) jdecay[tid] = jhead[size_t(tid) * VH * SPL_JOURNAL_WIDTH + 2 * D];
     const float neg_a = -expf(spl_bf16_to_float(a_log[h])), bias = spl_bf16_to_float(dt_bias[h]);
+
     for (uint32_t base = 0; base < length; base += TC) {
         const int count = min(uint32_t(TC), length - base);
-        __syncthreads();
-        // q, k, v of up to TC tokens; one warp a token for the norms.
-        for (int idx = tid; idx < count * 3 * (D / 4); idx += 256) {
+        if (base != 0) __syncthreads();
+        // q, k, v of up to TC tokens; one warp a token for the norms and the gates.
+        for (int idx = tid; idx < count * 3 * (D / 4); idx += NT) {
             const int tt = idx / (3 * (D / 4)), rest = idx % (3 * (D / 4)), kind = rest / (D / 4), i4 = rest % (D / 4);
             const int channel = kind == 0 ? hk * D : kind == 1 ? KH * D + hk * D : 2 * KH * D + h * D;
             const float4 v = *reinterpret_cast<const float4 *>(act + size_t(start + base + tt) * p.channels + channel + i4 * 4);
             float *dst = kind == 0 ? q_s[tt] : kind == 1 ? k_s[tt] : v_s[tt];
             *reinterpret_cast<float4 *>(dst + i4 * 4) = v;
         }
+        // The gate input of this warp's token, for the norm at the end of the pass.
+        float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float gate_a = 0.0f, gate_b = 0.0f;
+        if (warp < count) {
+            const size_t row = start + base + warp;
+            z = *reinterpret_cast<const float4 *>(proj + row * p.proj_ld + p.z_offset + h * D + lane * 4);
+            if (lane == 0) { gate_a = proj[row * p.proj_ld + p.a_offset + h]; gate_b = proj[row * p.proj_ld + p.b_offset + h]; }
+        }
         __syncthreads();
-        for (int tt = warp; tt < count; tt += 8) {
+        if (warp < count) {
+            const int tt = warp;
             const float4 qv = *reinterpret_cast<const float4 *>(&q_s[tt][lane * 4]);
             const float4 kv = *reinterpret_cast<const float4 *>(&k_s[tt][lane * 4]);
             const float qq = spl_warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
             const float kk = spl_warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
             if (lane == 0) {
-                const size_t row = start + base + tt;
                 scal[tt][0] = (1.0f / sqrtf(qq + 1e-6f)) * (1.0f / sqrtf(float(D)));
                 scal[tt][1] = 1.0f / sqrtf(kk + 1e-6f);
-                const float x = proj[row * p.proj_ld + p.a_offset + h] + bias;
+                const float x = gate_a + bias;
                 const float softplus = x > 20.0f ? x : logf(1.0f + expf(x));
                 scal[tt][2] = expf(neg_a * softplus);
-                scal[tt][3] = spl_sigmoid(proj[row * p.proj_ld + p.b_offset + h]);
+                scal[tt][3] = spl_sigmoid(gate_b);
             }
         }
-        __syncthreads();
+        if (base == 0 && pending != 0) {
+            // Replay the accepted entries; a speculative run then stores the state it starts from.
+            for (uint32_t e = 0; e < pending; ++e) {
+                const float delta = o_s[e][j], decay = jdecay[e];
+                const float2 d2 = make_float2(delta, delta), c2 = make_float2(decay, decay);
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    const float4 kv = *reinterpret_cast<const float4 *>(&jk_s[e][32 * m + 4 * part]);
+                    const float2 lo = spl_gdn_update2(make_float2(S[m].x, S[m].y), c2, make_float2(kv.x, kv.y), d2);
+                    const float2 hi = spl_gdn_update2(make_float2(S[m].z, S[m].w), c2, make_float2(kv.z, kv.w), d2);
+                    S[m] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                }
+            }
+            if (speculative) {
+#pragma unroll
+                for (int m = 0; m < 4; ++m) stored[8 * m] = S[m];
+            }
+        }
+        __syncthreads();      // the tokens' scalars are written; the replay has finished with o_s
         for (int tt = 0; tt < count; ++tt) {
             const float inv_q = scal[tt][0], inv_k = scal[tt][1], decay = scal[tt][2], beta = scal[tt][3];
-            float mem = 0.0f;
+            float4 kv[4];
+            float2 ma = make_float2(0.0f, 0.0f), mb = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int m = 0; m < 16; ++m) {
-                const float4 kv = *reinterpret_cast<const float4 *>(&k_s[tt][8 * m + 4 * half]);
-                mem += S[m].x * kv.x + S[m].y * kv.y + S[m].z * kv.z + S[m].w * kv.w;
+            for (int m = 0; m < 4; ++m) {
+                kv[m] = *reinterpret_cast<const float4 *>(&k_s[tt][32 * m + 4 * part]);
+                ma = spl_fma2(make_float2(S[m].x, S[m].y), make_float2(kv[m].x, kv[m].y), ma);
+                mb = spl_fma2(make_float2(S[m].z, S[m].w), make_float2(kv[m].z, kv[m].w), mb);
             }
+            float mem = (ma.x + ma.y) + (mb.x + mb.y);
             mem += __shfl_xor_sync(0xffffffffu, mem, 1);
+            mem += __shfl_xor_sync(0xffffffffu, mem, 2);
+            mem += __shfl_xor_sync(0xffffffffu, mem, 4);
             const float delta = (v_s[tt][j] - mem * decay * inv_k) * beta * inv_k;
-            float o = 0.0f;
+            const float2 d2 = make_float2(delta, delta), c2 = make_float2(decay, decay);
+            float2 oa = make_float2(0.0f, 0.0f), ob = make_float2(0.0f, 0.0f);
 #pragma unroll
-            for (int m = 0; m < 16; ++m) {
-                const float4 kv = *reinterpret_cast<const float4 *>(&k_s[tt][8 * m + 4 * half]);
-                const float4 qv = *reinterpret_cast<const float4 *>(&q_s[tt][8 * m + 4 * half]);
-                S[m].x = spl_gdn_update(S[m].x, decay, kv.x, delta); S[m].y = spl_gdn_update(S[m].y, decay, kv.y, delta);
-                S[m].z = spl_gdn_update(S[m].z, decay, kv.z, delta); S[m].w = spl_gdn_update(S[m].w, decay, kv.w, delta);
-                o += S[m].x * qv.x + S[m].y * qv.y + S[m].z * qv.z + S[m].w * qv.w;
+            for (int m = 0; m < 4; ++m) {
+                const float4 qv = *reinterpret_cast<const float4 *>(&q_s[tt][32 * m + 4 * part]);
+                const float2 lo = spl_gdn_update2(make_float2(S[m].x, S[m].y), c2, make_float2(kv[m].x, kv[m].y), d2);
+                const float2 hi = spl_gdn_update2(make_float2(S[m].z, S[m].w), c2, make_float2(kv[m].z, kv[m].w), d2);
+                S[m] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                oa = spl_fma2(lo, make_float2(qv.x, qv.y), oa);
+                ob = spl_fma2(hi, make_float2(qv.z, qv.w), ob);
             }
+            float o = (oa.x + oa.y) + (ob.x + ob.y);
             o += __shfl_xor_sync(0xffffffffu, o, 1);
-            if (half == 0) o_s[tt][j] = o * inv_q;
+            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            o += __shfl_xor_sync(0xffffffffu, o, 4);
+            if (part == 0) o_s[tt][j] = o * inv_q;
             if (speculative) {
                 float *entry = jhead + size_t(base + tt) * VH * SPL_JOURNAL_WIDTH;
                 if (tid < D) entry[tid] = k_s[tt][tid];
-                if (half == 0) entry[D + j] = delta;
+                if (part == 0) entry[D + j] = delta;
                 if (tid == 0) entry[2 * D] = decay;
             }
         }
         __syncthreads();
         // Gated RMSNorm and the bf16 operand, one warp a token.
-        for (int tt = warp; tt < count; tt += 8) {
+        if (warp < count) {
+            const int tt = warp;
             const size_t row = start + base + tt;
             const float4 ov = *reinterpret_cast<const float4 *>(&o_s[tt][lane * 4]);
             const float inv = 1.0f / sqrtf(spl_warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w) / float(D) + p.eps);
-            const float4 z = *reinterpret_cast<const float4 *>(proj + row * p.proj_ld + p.z_offset + h * D + lane * 4);
             const uint2 w = *reinterpret_cast<const uint2 *>(norm_weight + lane * 4);
             const float r0 = spl_bf16_to_float(uint16_t(w.x)) * ov.x * inv * spl_silu_exact(z.x);
             const float r1 = spl_bf16_to_float(uint16_t(w.x >> 16)) * ov.y * inv * spl_silu_exact(z.y);
@@ -183,6 +226,6 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
     }
     if (!speculative) {
 #pragma unroll
-        for (int m = 0; m < 16; ++m) stored[2 * m] = S[m];
+        for (int m = 0; m < 4; ++m) stored[8 * m] = S[m];
     }
 }
