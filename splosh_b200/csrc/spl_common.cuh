@@ -48,6 +48,21 @@ __device__ __forceinline__ void spl_mma_bf16_dc(float (&d)[4], const uint32_t (&
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1), "f"(c[0]), "f"(c[1]), "f"(c[2]), "f"(c[3]));
 }
 
+// Packed pairs of fp32 (Blackwell's two-wide fp32 instructions): each half is an IEEE single operation, so the
+// results are bit for bit those of the scalar code.
+__device__ __forceinline__ float2 spl_fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(reinterpret_cast<unsigned long long &>(d))
+        : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)), "l"(reinterpret_cast<unsigned long long &>(c)));
+    return d;
+}
+__device__ __forceinline__ float2 spl_mul2(float2 a, float2 b) {
+    float2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(reinterpret_cast<unsigned long long &>(d))
+        : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)));
+    return d;
+}
+
 // SplitMix64 at an index: output n of the stream that starts at `seed`.
 __host__ __device__ __forceinline__ uint64_t spl_splitmix_at(uint64_t seed, uint64_t n) {
     uint64_t z = seed + (n + 1) * 0x9E3779B97F4A7C15ull;

@@ -395,7 +395,7 @@ spl_status upload_q4_into(spl_engine *e, SplQ4Dev &w, int n0, int rows, int inne
     cudaMemcpy(&flag, bad, sizeof flag, cudaMemcpyDeviceToHost);
     cudaFree(bad);
     if (sp) { cudaFree(sp); cudaFree(ss); cudaFree(sbias); }
-    if (launched == SPL_OK && flag) launched = e->fail(SPL_ERR_INVALID_ARGUMENT, "a quantisation scale is outside [2^-14, 8188]: scale * (code - 8) would not be exact in fp16");
+    if (launched == SPL_OK && flag) launched = e->fail(SPL_ERR_INVALID_ARGUMENT, "a quantisation scale is outside [2^-13, 8188]: scale * (code - 8) would not be exact in fp16");
     return launched;
 }
 
@@ -989,6 +989,7 @@ spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t
                 fprintf(stderr, "tc trace, cycles per group: copy [wait codes %d, wait act %d, issue %d] mma [wait act %d, wait A %d, issue %d] "
                                 "dequant(1 of 2 sets) [wait stage %d, convert %d, wait slot %d, store %d] epilogue [wait %d, work %d, final wait %d] groups %d\n",
                         t[8], t[9], t[10], t[11], t[12], t[13], t[14], t[15], t[16], t[17], t[18], t[19], t[20], t[21]);
+            fprintf(stderr, "tc timeline of block 0, cycles from entry: set-up done %d, first stage landed %d, last instruction issued %d, accumulators complete %d, output written %d\n", t[22], t[23], t[24], t[25], t[26]);
         }
         if (s == SPL_OK) cudaMemcpy2D(out, size_t(n) * 4, d_out, size_t(ld) * 4, size_t(n) * 4, rows, cudaMemcpyDeviceToHost);
     }

@@ -46,20 +46,6 @@ spl_gdn_conv_kernel(const float *__restrict__ proj, const uint16_t *__restrict__
     }
 }
 
-// Packed pairs of fp32 (Blackwell's two-wide fp32 instructions): each half is an IEEE single operation, so the
-// results are bit for bit those of the scalar code.
-__device__ __forceinline__ float2 spl_fma2(float2 a, float2 b, float2 c) {
-    float2 d;
-    asm("fma.rn.f32x2 %0, %1, %2, %3;\n" : "=l"(reinterpret_cast<unsigned long long &>(d))
-        : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)), "l"(reinterpret_cast<unsigned long long &>(c)));
-    return d;
-}
-__device__ __forceinline__ float2 spl_mul2(float2 a, float2 b) {
-    float2 d;
-    asm("mul.rn.f32x2 %0, %1, %2;\n" : "=l"(reinterpret_cast<unsigned long long &>(d))
-        : "l"(reinterpret_cast<unsigned long long &>(a)), "l"(reinterpret_cast<unsigned long long &>(b)));
-    return d;
-}
 // The state update S' = S * decay + k * delta with the product rounded on its own, so that the
 // replay of a journal entry reproduces the original update bit for bit (engine.metal:654-659).
 __device__ __forceinline__ float2 spl_gdn_update2(float2 s, float2 decay, float2 k, float2 delta) {

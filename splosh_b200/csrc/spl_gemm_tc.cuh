@@ -88,9 +88,10 @@ __global__ void spl_repack_q4_kernel(const uint32_t *__restrict__ packed, const 
         if ((w & 7) == 0) {
             const uint16_t sbits = scales[size_t(row) * groups + g];
             sb[(size_t(tile) * groups + g) * 128 + col] = uint32_t(sbits) | (uint32_t(biases[size_t(row) * groups + g]) << 16);
-            // The GEMM holds scale * (code - 8) in fp16: the scale must be zero or a normal fp16 number with room for a factor 8.
+            // The GEMM holds scale * (code - 8) in fp16 and forms it also from scale / 16: the scale must be zero, or at least
+            // 2^-13 (scale / 16 keeps its eight bits) with room for a factor 8.
             const float sc = fabsf(spl_bf16_to_float(sbits));
-            if (!(sc == 0.0f || (sc >= 6.103515625e-05f && sc <= 8188.0f))) atomicExch(out_of_range, 1);
+            if (!(sc == 0.0f || (sc >= 1.220703125e-04f && sc <= 8188.0f))) atomicExch(out_of_range, 1);
         }
     }
 }
@@ -262,6 +263,9 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     uint64_t *full_a = empty_b + BST, *done = full_a + AST, *finished = done + AST;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(finished + 1);
 
+#ifdef SPL_TRACE
+    const long long t_entry = clock64();
+#endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x, split = blockIdx.y, rb = blockIdx.z, row_blocks = op_blocks;   // the operand's row blocks (>= gridDim.z)
     const int rows_padded = op_blocks * RN;
@@ -285,6 +289,9 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     __syncthreads();
     spl_tc_fence_after();
     const uint32_t tmem = *tmem_slot;                 // lane 0, first allocated column
+#ifdef SPL_TRACE
+    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && error_flag[1] == 0x7ACE) error_flag[22] = int(clock64() - t_entry);   // set-up
+#endif
     // Consecutive instructions into one accumulator wait for each other (the pipeline's latency is longer than
     // so small an instruction), so the k16 steps rotate over NACC accumulators; the epilogue adds them in order.
     constexpr int NACC = RN <= 32 ? 4 : 2;
@@ -383,6 +390,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                 SPL_T1(t2);
             }
             SPL_TOUT(if (trace && m == 0) { error_flag[11] = int(t0 / g_count); error_flag[12] = int(t1 / g_count); error_flag[13] = int(t2 / g_count); });
+            SPL_TOUT(if (trace && m == 0) error_flag[24] = int(clock64() - t_entry));     // last instruction issued
             if (ok) spl_tc_commit(finished);
         }
     } else if (warp < 4 || warp >= 8) {
@@ -390,18 +398,19 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         // take the even groups, warps 8-11 the odd ones; both sets write the lanes of their warp index mod 4.
         const int quarter = warp & 3, col = quarter * 32 + lane, parity = warp >> 3;
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-        const __half2 c1032 = __floats2half2_rn(1032.0f, 1032.0f);
+        const __half2 c1032 = __floats2half2_rn(1032.0f, 1032.0f), c1152 = __floats2half2_rn(1152.0f, 1152.0f);
         for (int j = 0; j < supers && ok; ++j) {
             const int sc = j % CST, sbq = j % BST;
             SPL_T0();
             ok = spl_mbar_wait(&full_c[sc], (j / CST) & 1) && spl_mbar_wait(&full_b[sbq], (j / BST) & 1);
             SPL_T1(t0);
+            SPL_TOUT(if (trace && warp == 0 && lane == 0 && j == 0) error_flag[23] = int(clock64() - t_entry));     // first stage has landed
             if (!ok) break;
             const int n = min(SPL_TC_SUPER, g_count - j * SPL_TC_SUPER);
             // This warp's unit of the stage: groups 2 * parity and 2 * parity + 1, read before either is converted so
             // that the codes can be handed back at once.
             uint4 lo[2], hi[2];
-            __half2 s2[2];
+            __half2 s2[2], s16[2];
 #pragma unroll
             for (int v = 0; v < 2; ++v) {
                 const int u = 2 * parity + v;
@@ -409,24 +418,30 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                     lo[v] = *reinterpret_cast<const uint4 *>(w_ring + size_t(sc) * WSTAGE + u * 4096 + col * 16);
                     hi[v] = *reinterpret_cast<const uint4 *>(w_ring + size_t(sc) * WSTAGE + u * 4096 + 2048 + col * 16);
                     const float sf = __uint_as_float(q_ring[sbq * QSTAGE + u * 128 + col] << 16);
-                    s2[v] = __float2half2_rn(sf);
+                    s2[v] = __float2half2_rn(sf); s16[v] = __float2half2_rn(sf * 0.0625f);
                 }
             }
             __syncwarp();
             if (lane == 0) spl_mbar_arrive(&empty_c[sc]);
             if (2 * parity >= n) continue;                       // a short last stage may leave the second set nothing
+            // Nibbles in place: 0x6400 | c is 1024 + c and 0x6400 | (c << 4) is 1024 + 16 c in fp16, so that
+            // (q - 1032) * s and (q - 1152) * (s / 16) are both scale * (c - 8), exactly; one shift serves four nibbles.
             uint32_t a[2][32];
 #pragma unroll
             for (int v = 0; v < 2; ++v) {
                 const uint32_t w8[8] = {lo[v].x, lo[v].y, lo[v].z, lo[v].w, hi[v].x, hi[v].y, hi[v].z, hi[v].w};
 #pragma unroll
-                for (int w = 0; w < 8; ++w)
-#pragma unroll
-                    for (int p = 0; p < 4; ++p) {
-                        uint32_t q = ((w8[w] >> (4 * p)) & 0x000F000Fu) | 0x64006400u;       // fp16 1024 + code, twice
-                        const __half2 h = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&q), c1032), s2[v]);
-                        a[v][4 * w + p] = *reinterpret_cast<const uint32_t *>(&h);
-                    }
+                for (int w = 0; w < 8; ++w) {
+                    const uint32_t x0 = w8[w], x1 = w8[w] >> 8;
+                    uint32_t q0 = (x0 & 0x000F000Fu) | 0x64006400u, q1 = (x0 & 0x00F000F0u) | 0x64006400u;
+                    uint32_t q2 = (x1 & 0x000F000Fu) | 0x64006400u, q3 = (x1 & 0x00F000F0u) | 0x64006400u;
+                    const __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&q0), c1032), s2[v]);
+                    const __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&q1), c1152), s16[v]);
+                    const __half2 h2 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&q2), c1032), s2[v]);
+                    const __half2 h3 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&q3), c1152), s16[v]);
+                    a[v][4 * w + 0] = *reinterpret_cast<const uint32_t *>(&h0); a[v][4 * w + 1] = *reinterpret_cast<const uint32_t *>(&h1);
+                    a[v][4 * w + 2] = *reinterpret_cast<const uint32_t *>(&h2); a[v][4 * w + 3] = *reinterpret_cast<const uint32_t *>(&h3);
+                }
             }
             SPL_T1(t1);
             if (j >= SPL_TC_ASUPERS) ok = spl_mbar_wait(&done[j % SPL_TC_ASUPERS], ((j / SPL_TC_ASUPERS) & 1) ^ 1);
@@ -454,9 +469,9 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         // tensor cores' accumulator is added.
         const int q = warp - 4, col = q * 32 + lane;
         const uint32_t lane_base = uint32_t(q * 32) << 16;
-        float acc[RN];
+        float2 acc[RN / 2];           // packed pairs of rows: two-wide fp32 multiply-adds
 #pragma unroll
-        for (int r = 0; r < RN; ++r) acc[r] = 0.0f;
+        for (int r = 0; r < RN / 2; ++r) acc[r] = make_float2(0.0f, 0.0f);
         for (int j = 0; j < supers && ok; ++j) {
             const int sbq = j % BST;
             SPL_T0();
@@ -467,12 +482,13 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             for (int u = 0; u < n; ++u) {
                 const uint32_t x = q_ring[sbq * QSTAGE + u * 128 + col];
                 const float bias8 = fmaf(8.0f, __uint_as_float(x << 16), __uint_as_float(x & 0xFFFF0000u));
+                const float2 bb = make_float2(bias8, bias8);
                 const float *sums = s_ring + sbq * SSTAGE + u * RN;
 #pragma unroll
                 for (int r4 = 0; r4 < RN / 4; ++r4) {
                     const float4 sm = *reinterpret_cast<const float4 *>(sums + 4 * r4);
-                    acc[4 * r4 + 0] = fmaf(sm.x, bias8, acc[4 * r4 + 0]); acc[4 * r4 + 1] = fmaf(sm.y, bias8, acc[4 * r4 + 1]);
-                    acc[4 * r4 + 2] = fmaf(sm.z, bias8, acc[4 * r4 + 2]); acc[4 * r4 + 3] = fmaf(sm.w, bias8, acc[4 * r4 + 3]);
+                    acc[2 * r4] = spl_fma2(make_float2(sm.x, sm.y), bb, acc[2 * r4]);
+                    acc[2 * r4 + 1] = spl_fma2(make_float2(sm.z, sm.w), bb, acc[2 * r4 + 1]);
                 }
             }
             __syncwarp();
@@ -482,6 +498,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         SPL_T0();
         if (ok) ok = spl_mbar_wait(finished, 0);
         SPL_T1(t2);
+        SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[25] = int(clock64() - t_entry));     // accumulators complete
         SPL_TOUT(if (trace && warp == 4 && lane == 0) { error_flag[18] = int(t0 / g_count); error_flag[19] = int(t1 / g_count); error_flag[20] = int(t2 / g_count); error_flag[21] = g_count; });
         if (ok) {
             spl_tc_fence_after();
@@ -505,7 +522,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                         const int row = rb * RN + c0 + r;
                         if (row < rows) {
                             const size_t index = size_t(row) * out_ld + n;
-                            const float value = acc[c0 + r] + total[r];
+                            const float value = ((r & 1) ? acc[(c0 + r) >> 1].y : acc[(c0 + r) >> 1].x) + total[r];
                             dst[index] = (!is_split && residual) ? value + residual[index] : value;
                         }
                     }
@@ -513,6 +530,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             }
         }
     }
+    SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[26] = int(clock64() - t_entry));     // output written
     if (!ok) atomicExch(error_flag, 1 + warp);
     spl_tc_fence_before();
     __syncthreads();
