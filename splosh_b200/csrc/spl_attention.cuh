@@ -43,6 +43,7 @@ spl_attn_prepare_kernel(const float *__restrict__ proj, const uint16_t *__restri
                         const float *__restrict__ inv_freq, const uint32_t *__restrict__ row_slot, const uint32_t *__restrict__ row_pos,
                         const uint32_t *__restrict__ page_table, __half *q_out, int8_t *k_codes, float *k_scale, int8_t *v_codes,
                         float *v_scale, SplAttnParams p) {
+    spl_grid_begin();
     __shared__ float xs[256], red[4], red2[4];
     const int row = blockIdx.y, hd = p.head_dim, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const bool is_q = int(blockIdx.x) < p.heads;
@@ -165,6 +166,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                      const uint32_t *__restrict__ row_pos, const uint32_t *__restrict__ page_table, const int8_t *__restrict__ k_codes,
                      const float *__restrict__ k_scale, const int8_t *__restrict__ v_codes, const float *__restrict__ v_scale,
                      float *partials, SplAttnParams p, int *error_flag) {
+    spl_grid_begin();
     constexpr int NQ = spl_attn_nq(PER_KV), CH = SPL_ATTN_CH, NST = spl_attn_stages(HD), HALVES = HD / 128, QGROUPS = HD / 64;
     constexpr int CHUNK_BYTES = CH * HD, STAGE = int(spl_attn_stage_bytes(HD)), QTILE = NQ * 128, PTILE = 2 * NQ * 128;
     constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
@@ -612,6 +614,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
 // Merge span partials by log-sum-exp, apply the sigmoid output gate, round to the bf16 operand of
 // the output projection and emit its per-64 sums (engine.metal:2218-2255). Grid (heads, live rows), head_dim threads.
 __global__ void spl_attn_merge_kernel(const float *__restrict__ partials, const float *__restrict__ proj, SplOperand core, SplAttnParams p) {
+    spl_grid_begin();
     __shared__ float warp_sums[8];
     const int head = blockIdx.x, row = blockIdx.y, j = threadIdx.x, hd = p.head_dim, record = hd + 2;
     const float *base = partials + (size_t(row) * p.heads + head) * p.spans * record;

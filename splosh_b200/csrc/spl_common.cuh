@@ -63,6 +63,14 @@ __device__ __forceinline__ float2 spl_mul2(float2 a, float2 b) {
     return d;
 }
 
+// Programmatic dependent launch. A step's kernels are launched with programmatic stream serialisation: a kernel may be
+// scheduled while its predecessor still runs, so each one waits here (for the predecessor to have completed and its
+// writes to be visible) before it touches anything a predecessor wrote, and then lets its own successor be scheduled.
+// Without the launch attribute both instructions do nothing.
+__device__ __forceinline__ void spl_grid_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+__device__ __forceinline__ void spl_grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
+__device__ __forceinline__ void spl_grid_begin() { spl_grid_wait(); spl_grid_launch_dependents(); }
+
 // SplitMix64 at an index: output n of the stream that starts at `seed`.
 __host__ __device__ __forceinline__ uint64_t spl_splitmix_at(uint64_t seed, uint64_t n) {
     uint64_t z = seed + (n + 1) * 0x9E3779B97F4A7C15ull;

@@ -8,6 +8,7 @@
 // Grid (rows), any block size.
 __global__ void spl_embed_q4_kernel(const uint32_t *__restrict__ packed, const uint16_t *__restrict__ scales,
                                     const uint16_t *__restrict__ biases, const uint32_t *__restrict__ tokens, float *out, int hidden) {
+    spl_grid_begin();
     const int row = blockIdx.x;
     const uint32_t token = tokens[row];
     const int words = hidden / 8, groups = hidden / 64;
@@ -32,6 +33,7 @@ __global__ void spl_embed_q4_kernel(const uint32_t *__restrict__ packed, const u
 __global__ void __launch_bounds__(256)
 spl_rmsnorm_kernel(const float *__restrict__ input, int in_ld, const uint16_t *__restrict__ weight, const uint32_t *__restrict__ index,
                    SplOperand out, int dim, float eps) {
+    spl_grid_begin();
     __shared__ float part[8];
     const int row = blockIdx.x;
     const float *x = input + size_t(index ? index[row] : row) * in_ld;
@@ -71,6 +73,7 @@ spl_rmsnorm_kernel(const float *__restrict__ input, int in_ld, const uint16_t *_
 // act = bf16(silu(gate) * up) and its per-64 sums from the fused gate|up projection (engine.metal:200-219).
 // gate_up: [rows][ld] with gate at column 0 and up at column `inter`.
 __global__ void spl_silu_mul_kernel(const float *__restrict__ gate_up, int ld, int inter, int rows, SplOperand out) {
+    spl_grid_begin();
     const size_t total = size_t(rows) * inter / 4;
     const size_t stride = size_t(gridDim.x) * blockDim.x;
     const size_t bound = (total + 31) / 32 * 32;

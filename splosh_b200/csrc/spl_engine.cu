@@ -152,6 +152,20 @@ void profile_collect(spl_engine *e) {
     e->profile_used = 0;
 }
 
+// Launch of one of a step's kernels with programmatic stream serialisation: the kernel may be scheduled while its
+// predecessor in the stream still runs; each kernel itself waits for that predecessor (spl_grid_wait) before it reads
+// or writes anything a predecessor touched.
+template <typename... KArgs, typename... Args>
+void launch_step(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...);
+}
+
 // ---- GEMM launch ------------------------------------------------------------------------------
 // Rows per operand block for a step of `rows` rows.
 int operand_rn(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : 64; }
@@ -187,13 +201,13 @@ void launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &o
         cudaFuncSetAttribute(spl_gemm_q4_tc_kernel<RN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         configured = true;
     }
-    spl_gemm_q4_tc_kernel<RN><<<dim3(w.tiles, splits, row_blocks), SPL_TC_THREADS, smem, stream>>>(
+    launch_step(spl_gemm_q4_tc_kernel<RN>, dim3(dim3(w.tiles, splits, row_blocks)), dim3(SPL_TC_THREADS), smem, stream, 
         w.codes, w.sb, op.values, op.sums, out, w.ld, residual, partials, rows, op.blocks, groups, gps, error_flag);
     if (launches) ++*launches;
     if (splits > 1) {
         const size_t total = size_t(rows) * w.ld / 4;
         const int blocks = int(std::min<size_t>((total + 255) / 256, 2048));
-        spl_gemm_reduce_kernel<<<blocks, 256, 0, stream>>>(partials, splits, rows_padded, rows, w.ld, residual, out);
+        launch_step(spl_gemm_reduce_kernel, dim3(blocks), dim3(256), 0, stream, partials, splits, rows_padded, rows, w.ld, residual, out);
         if (launches) ++*launches;
     }
 }
@@ -218,7 +232,7 @@ void launch_scan_tc(spl_engine *e, dim3 grid, const SplAttnParams &p, int layer)
     const size_t smem = spl_attn_smem_bytes(HD, spl_attn_nq(PER_KV));
     static bool configured = false;
     if (!configured) { cudaFuncSetAttribute(spl_attn_scan_kernel<HD, PER_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); configured = true; }
-    spl_attn_scan_kernel<HD, PER_KV><<<grid, SPL_ATTN_THREADS, smem, e->stream>>>(e->q, e->d_blocks, e->d_row_slot, e->d_row_pos, e->d_page_table,
+    launch_step(spl_attn_scan_kernel<HD, PER_KV>, dim3(grid), dim3(SPL_ATTN_THREADS), smem, e->stream, e->q, e->d_blocks, e->d_row_slot, e->d_row_pos, e->d_page_table,
         e->k_codes[layer], e->k_scale[layer], e->v_codes[layer], e->v_scale[layer], e->attn_partials, p, e->tc_error);
 }
 // The scan is built for the head shapes in use: head_dim 256 with six query heads per kv head, and head_dim 128 with four.
@@ -270,7 +284,7 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
     const SplOperand xn{e->xn, e->xn_sums, rn, blocks}, core{e->core, e->core_sums, rn, blocks}, act{e->act, e->act_sums, rn, blocks};
     const GemmOperand gxn{e->xn, e->xn_sums, rn, blocks}, gcore{e->core, e->core_sums, rn, blocks}, gact{e->act, e->act_sums, rn, blocks};
     profile_begin(e, KLASS_ELEMENTWISE, 0);
-    spl_embed_q4_kernel<<<R, 128, 0, e->stream>>>(e->embed_packed, e->embed_scales, e->embed_biases, e->d_tokens, e->h, H);
+    launch_step(spl_embed_q4_kernel, dim3(R), dim3(128), 0, e->stream, e->embed_packed, e->embed_scales, e->embed_biases, e->d_tokens, e->h, H);
     profile_end(e);
 
     int linear_index = 0, full_index = 0;
@@ -280,7 +294,7 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
         const LayerWeights &L = e->layers[l];
         const int live = (l + 1 == g.layers) ? int(t->live_rows) : R;
         profile_begin(e, KLASS_ELEMENTWISE, 0);
-        spl_rmsnorm_kernel<<<R, 256, 0, e->stream>>>(e->h, H, L.vec[SPL_VEC_INPUT_NORM], nullptr, xn, H, g.eps);
+        launch_step(spl_rmsnorm_kernel, dim3(R), dim3(256), 0, e->stream, e->h, H, L.vec[SPL_VEC_INPUT_NORM], nullptr, xn, H, g.eps);
         profile_end(e);
         launch_gemm(e, L.in_proj, gxn, e->proj, nullptr, R);
         if (!L.full) {
@@ -288,11 +302,11 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
             p.rows = R; p.runs = int(t->run_count); p.channels = sh.C; p.key_heads = g.gdn_key_heads; p.value_heads = g.gdn_value_heads;
             p.head_dim = g.gdn_head_dim; p.proj_ld = L.in_proj.ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps;
             profile_begin(e, KLASS_GDN, 0);
-            spl_gdn_conv_kernel<<<dim3((sh.C + 255) / 256, t->run_count), 256, 0, e->stream>>>(
+            launch_step(spl_gdn_conv_kernel, dim3(dim3((sh.C + 255) / 256, t->run_count)), dim3(256), 0, e->stream, 
                 e->proj, L.vec[SPL_VEC_CONV], e->conv[linear_index], e->d_runs, e->d_row_read, e->d_row_write, e->gdn_act, p);
             profile_end(e);
             profile_begin(e, KLASS_GDN, 0);
-            spl_gdn_recurrence_kernel<<<dim3(g.gdn_value_heads, t->run_count), SPL_GDN_THREADS, 0, e->stream>>>(
+            launch_step(spl_gdn_recurrence_kernel, dim3(dim3(g.gdn_value_heads, t->run_count)), dim3(SPL_GDN_THREADS), 0, e->stream, 
                 e->gdn_act, e->proj, L.vec[SPL_VEC_A_LOG], L.vec[SPL_VEC_DT_BIAS], L.vec[SPL_VEC_GDN_NORM], e->state[linear_index],
                 e->journal[linear_index], e->d_runs, e->d_run_info, core, p);
             profile_end(e);
@@ -303,7 +317,7 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
             p.max_pages = e->host->max_pages; p.proj_ld = L.in_proj.ld; p.k_offset = sh.att_k; p.v_offset = sh.att_v;
             p.spans = int(t->spans); p.pages_per_span = int(t->pages_per_span); p.eps = g.eps; p.scale = 1.0f / sqrtf(float(g.head_dim));
             profile_begin(e, KLASS_ATTENTION, 0);
-            spl_attn_prepare_kernel<<<dim3(g.heads + g.kv_heads, R), 128, 0, e->stream>>>(
+            launch_step(spl_attn_prepare_kernel, dim3(dim3(g.heads + g.kv_heads, R)), dim3(128), 0, e->stream, 
                 e->proj, L.vec[SPL_VEC_Q_NORM], L.vec[SPL_VEC_K_NORM], e->inv_freq, e->d_row_slot, e->d_row_pos, e->d_page_table, e->q,
                 e->k_codes[full_index], e->k_scale[full_index], e->v_codes[full_index], e->v_scale[full_index], p);
             profile_end(e);
@@ -318,7 +332,7 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
                 launch_scan(e, dim3(g.kv_heads * t->spans, blocks), p, full_index);
                 profile_end(e);
                 profile_begin(e, KLASS_ATTENTION, 0);
-                spl_attn_merge_kernel<<<dim3(g.heads, live), g.head_dim, 0, e->stream>>>(e->attn_partials, e->proj, core, p);
+                launch_step(spl_attn_merge_kernel, dim3(dim3(g.heads, live)), dim3(g.head_dim), 0, e->stream, e->attn_partials, e->proj, core, p);
                 profile_end(e);
             }
             ++full_index;
@@ -326,12 +340,12 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
         if (live > 0) {
             launch_gemm(e, L.out_proj, gcore, e->h, e->h, live);
             profile_begin(e, KLASS_ELEMENTWISE, 0);
-            spl_rmsnorm_kernel<<<live, 256, 0, e->stream>>>(e->h, H, L.vec[SPL_VEC_POST_NORM], nullptr, xn, H, g.eps);
+            launch_step(spl_rmsnorm_kernel, dim3(live), dim3(256), 0, e->stream, e->h, H, L.vec[SPL_VEC_POST_NORM], nullptr, xn, H, g.eps);
             profile_end(e);
             launch_gemm(e, L.gate_up, gxn, e->gate_up, nullptr, live);
             profile_begin(e, KLASS_ELEMENTWISE, 0);
             const size_t total = size_t(live) * g.inter / 4;
-            spl_silu_mul_kernel<<<int(std::min<size_t>((total + 255) / 256, 4096)), 256, 0, e->stream>>>(e->gate_up, e->gate_up_ld, g.inter, live, act);
+            launch_step(spl_silu_mul_kernel, dim3(int(std::min<size_t>((total + 255) / 256, 4096))), dim3(256), 0, e->stream, e->gate_up, e->gate_up_ld, g.inter, live, act);
             profile_end(e);
             launch_gemm(e, L.down, gact, e->h, e->h, live);
         }
@@ -340,7 +354,7 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
     if (t->logit_rows > 0) {
         profile_begin(e, KLASS_OTHER, 0);
         const int lrn = operand_rn(int(t->logit_rows)), lblocks = (int(t->logit_rows) + lrn - 1) / lrn;
-        spl_rmsnorm_kernel<<<t->logit_rows, 256, 0, e->stream>>>(e->h, H, e->final_norm, e->d_gather, SplOperand{e->hsn, e->hsn_sums, lrn, lblocks}, H, g.eps);
+        launch_step(spl_rmsnorm_kernel, dim3(t->logit_rows), dim3(256), 0, e->stream, e->h, H, e->final_norm, e->d_gather, SplOperand{e->hsn, e->hsn_sums, lrn, lblocks}, H, g.eps);
         profile_end(e);
         launch_gemm(e, e->head, GemmOperand{e->hsn, e->hsn_sums, operand_rn(int(t->logit_rows)), (int(t->logit_rows) + operand_rn(int(t->logit_rows)) - 1) / operand_rn(int(t->logit_rows))}, e->logits, nullptr, int(t->logit_rows));
     }

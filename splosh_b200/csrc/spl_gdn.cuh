@@ -26,6 +26,7 @@ __global__ void __launch_bounds__(256)
 spl_gdn_conv_kernel(const float *__restrict__ proj, const uint16_t *__restrict__ conv_weight, float *conv_state,
                     const uint32_t *__restrict__ runs, const uint32_t *__restrict__ row_read, const uint32_t *__restrict__ row_write,
                     float *act, SplGdnParams p) {
+    spl_grid_begin();
     const int c = blockIdx.x * 256 + threadIdx.x;
     if (c >= p.channels) return;
     const uint32_t start = runs[blockIdx.y * 3 + 1], length = runs[blockIdx.y * 3 + 2];
@@ -70,6 +71,7 @@ __global__ void __launch_bounds__(SPL_GDN_THREADS, 1)
 spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict__ proj, const uint16_t *__restrict__ a_log,
                           const uint16_t *__restrict__ dt_bias, const uint16_t *__restrict__ norm_weight, float *state, float *journal,
                           const uint32_t *__restrict__ runs, const uint32_t *__restrict__ run_info, SplOperand core, SplGdnParams p) {
+    spl_grid_begin();
     constexpr int D = SPL_GDN_D, TC = SPL_GDN_TC, NT = SPL_GDN_THREADS;
     __shared__ __align__(16) float q_s[TC][D], k_s[TC][D], v_s[TC][D], o_s[TC][D], jk_s[TC][D];
     __shared__ float scal[TC][4], jdecay[TC];        // invQ, invK, decay, beta per token; decay per replayed entry

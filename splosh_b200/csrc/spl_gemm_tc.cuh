@@ -311,6 +311,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
 #define SPL_TOUT(statement) do { } while (0)
 #endif
 
+    if (!(warp == 12 && lane == 0)) spl_grid_begin();     // the copying thread first asks for weights (below)
     if (warp == 12) {
         // ---- copies. Codes have their own ring; activations, their sums and the scale/bias words share the other.
         if (lane == 0) {
@@ -322,16 +323,28 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             // different starting points (the order of a sum of groups does not matter beyond fp32 rounding, and it
             // is a fixed function of the tile), so that at any moment they ask L2 for different lines.
             const int rot = (g_count % SPL_TC_SUPER == 0 && supers > 1) ? int((uint32_t(tile) * 2654435761u >> 12) % uint32_t(supers)) : 0;
+            // The weights are nobody's output: the first stages of codes are asked for before this kernel waits for its
+            // predecessor in the stream, so they arrive while that one is still finishing.
+            const int ahead = min(CST, supers);
+            for (int j0 = 0; j0 < ahead; ++j0) {
+                const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
+                const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);
+                spl_mbar_expect_tx(&full_c[j0], uint32_t(n) * 4096);
+                spl_bulk_g2s(w_ring + size_t(j0) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[j0]);
+            }
+            spl_grid_begin();
             for (int j0 = 0; j0 < supers && ok; ++j0) {
                 const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;      // the stage's source; j0 is its place in the pipeline
                 const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);         // with a rotation every stage is full
                 const int sc = j0 % CST, sbq = j0 % BST;
                 SPL_T0();
-                ok = spl_mbar_wait(&empty_c[sc], ((j0 / CST) & 1) ^ 1);
-                SPL_T1(t0);
-                if (!ok) break;
-                spl_mbar_expect_tx(&full_c[sc], uint32_t(n) * 4096);
-                spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[sc]);
+                if (j0 >= ahead) {
+                    ok = spl_mbar_wait(&empty_c[sc], ((j0 / CST) & 1) ^ 1);
+                    SPL_T1(t0);
+                    if (!ok) break;
+                    spl_mbar_expect_tx(&full_c[sc], uint32_t(n) * 4096);
+                    spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[sc]);
+                }
                 SPL_T1(t2);
                 ok = spl_mbar_wait(&empty_b[sbq], ((j0 / BST) & 1) ^ 1);
                 SPL_T1(t1);
@@ -543,6 +556,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
 // out[r][n] = sum over splits, in split order, of partials[s][r][n] (+ residual[r][n]).
 __global__ void spl_gemm_reduce_kernel(const float *__restrict__ partials, int splits, int rows_padded, int rows, int ld,
                                        const float *residual, float *out) {
+    spl_grid_begin();
     const size_t total = size_t(rows) * ld / 4;
     for (size_t idx = blockIdx.x * size_t(blockDim.x) + threadIdx.x; idx < total; idx += size_t(gridDim.x) * blockDim.x) {
         float4 sum = reinterpret_cast<const float4 *>(partials)[idx];
