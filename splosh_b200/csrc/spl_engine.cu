@@ -300,7 +300,7 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
         if (!L.full) {
             SplGdnParams p;
             p.rows = R; p.runs = int(t->run_count); p.channels = sh.C; p.key_heads = g.gdn_key_heads; p.value_heads = g.gdn_value_heads;
-            p.head_dim = g.gdn_head_dim; p.proj_ld = L.in_proj.ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps;
+            p.head_dim = g.gdn_head_dim; p.proj_ld = L.in_proj.ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps; p.trace = e->tc_error;
             profile_begin(e, KLASS_GDN, 0);
             launch_step(spl_gdn_conv_kernel, dim3(dim3((sh.C + 255) / 256, t->run_count)), dim3(256), 0, e->stream, 
                 e->proj, L.vec[SPL_VEC_CONV], e->conv[linear_index], e->d_runs, e->d_row_read, e->d_row_write, e->gdn_act, p);
@@ -366,6 +366,10 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
         int flag = 0;
         SPL_CUDA(cudaMemcpy(&flag, e->tc_error, sizeof flag, cudaMemcpyDeviceToHost));
         if (flag) { cudaMemset(e->tc_error, 0, sizeof flag); return e->fail(SPL_ERR_TIMEOUT, "a GEMM block gave up waiting (role " + std::to_string(flag - 1) + ")"); }
+    }
+    if (getenv("SPL_GDN_TRACE")) {
+        int t[64]; cudaMemcpy(t, e->tc_error, sizeof t, cudaMemcpyDeviceToHost);
+        fprintf(stderr, "gdn timeline of block 0, cycles from entry: loads landed %d, scalars %d, replay %d, barrier %d, tokens %d, barrier %d, norm %d\n", t[56], t[57], t[58], t[59], t[60], t[61], t[62]);
     }
     if (getenv("SPL_ATTN_TRACE")) {
         int t[64]; cudaMemcpy(t, e->tc_error, sizeof t, cudaMemcpyDeviceToHost);

@@ -17,6 +17,7 @@ struct SplGdnParams {
     int rows, runs, channels, key_heads, value_heads, head_dim;
     int proj_ld, z_offset, a_offset, b_offset;     // columns of the fused input projection
     float eps;
+    int *trace;        // builds with -DSPL_TRACE: cycle stamps of block (0, 0)
 };
 
 // Conv (k = 4, depthwise, no bias) + SiLU over every channel of every run; then the conv history
@@ -55,28 +56,37 @@ __device__ __forceinline__ float2 spl_gdn_update2(float2 s, float2 decay, float2
 
 #define SPL_GDN_TC 16          // tokens prepared per pass
 #define SPL_GDN_D 128          // head dim (key and value)
-#define SPL_GDN_THREADS 1024
+#define SPL_GDN_THREADS 256
 
-// One thread block per (value head, run): the head's whole 128 x 128 state in the registers of 1,024 threads.
-// Thread (j = tid / 8, part = tid % 8) keeps 16 elements of state row j: i = 32 m + 4 part + e. Rows are
-// independent, so a token costs each thread two short dot products (combined over the row's eight threads with
-// three shuffles) and no block barrier. Per token (engine.metal:763-805):
+// One thread block per (value head, run): the head's whole 128 x 128 state in registers, a 4 x 16 tile a thread:
+// thread (rg = tid / 8, cg = tid % 8) keeps rows j = 4 rg + r (r < 4) at columns i = 32 c + 4 cg + e (c < 4, e < 4).
+// A token's k and q then cost a thread eight 16-byte loads from shared memory for 64 state elements (a thread that
+// held one row would load as much for 16 elements, and the kernel would be bound by shared-memory bandwidth); row
+// sums are combined over the eight threads of a row group by shuffles; there is no block barrier inside a pass.
+// Per token (engine.metal:763-805):
 //   mem = S k;  delta = (v - mem * decay * invK) * beta * invK;  S = S * decay + k (x) delta;
 //   o = (S q) * invQ
 // then the gated RMSNorm w * o * rsqrt(mean o^2 + eps) * silu(z) rounded to bf16, with its per-64
 // sums (engine.metal:812-833). A speculative run leaves a journal entry per row instead of writing
 // the state; entries accepted from the previous run are replayed first (engine.metal:744-761).
-// Grid (value_heads, runs), 1,024 threads.
-__global__ void __launch_bounds__(SPL_GDN_THREADS, 1)
+// Grid (value_heads, runs), 256 threads, two blocks to an SM.
+__global__ void __launch_bounds__(SPL_GDN_THREADS, 2)
 spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict__ proj, const uint16_t *__restrict__ a_log,
                           const uint16_t *__restrict__ dt_bias, const uint16_t *__restrict__ norm_weight, float *state, float *journal,
                           const uint32_t *__restrict__ runs, const uint32_t *__restrict__ run_info, SplOperand core, SplGdnParams p) {
     spl_grid_begin();
-    constexpr int D = SPL_GDN_D, TC = SPL_GDN_TC, NT = SPL_GDN_THREADS;
+#ifdef SPL_TRACE
+    const long long t_entry = clock64();
+#define SPL_G(k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && p.trace) p.trace[k] = int(clock64() - t_entry); } while (0)
+#else
+#define SPL_G(k) do { } while (0)
+#endif
+    constexpr int D = SPL_GDN_D, TC = SPL_GDN_TC, NT = SPL_GDN_THREADS, WARPS = NT / 32;
+    constexpr int ZT = (TC + WARPS - 1) / WARPS;      // tokens per warp in the norm passes
     __shared__ __align__(16) float q_s[TC][D], k_s[TC][D], v_s[TC][D], o_s[TC][D], jk_s[TC][D];
     __shared__ float scal[TC][4], jdecay[TC];        // invQ, invK, decay, beta per token; decay per replayed entry
     const int h = blockIdx.x, run = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int j = tid >> 3, part = tid & 7;
+    const int rg = tid >> 3, cg = tid & 7;
     const uint32_t slot = runs[run * 3], start = runs[run * 3 + 1], length = runs[run * 3 + 2];
     const bool speculative = run_info[run * 2] != 0;
     const uint32_t pending = run_info[run * 2 + 1];
@@ -85,10 +95,15 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
 
     // Everything the block needs from memory is asked for before anything is waited for: the state, the journal entries
     // to replay (k into jk_s, delta into o_s, which is free until the first token), and the first tokens' q, k, v.
-    float4 S[4];
-    float4 *stored = reinterpret_cast<float4 *>(state + ((size_t(slot) * VH + h) * D + j) * D) + part;
+    float2 S[4][4][2];          // [row r][column chunk c][pair]
+    float4 *stored = reinterpret_cast<float4 *>(state + ((size_t(slot) * VH + h) * D + 4 * rg) * D) + cg;
 #pragma unroll
-    for (int m = 0; m < 4; ++m) S[m] = stored[8 * m];
+    for (int r = 0; r < 4; ++r)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float4 v = stored[r * (D / 4) + 8 * c];
+            S[r][c][0] = make_float2(v.x, v.y); S[r][c][1] = make_float2(v.z, v.w);
+        }
     for (int idx = tid; idx < int(pending) * (2 * D / 4); idx += NT) {
         const int e = idx / (2 * D / 4), i4 = idx % (2 * D / 4);
         const float4 v = *reinterpret_cast<const float4 *>(jhead + size_t(e) * VH * SPL_JOURNAL_WIDTH + i4 * 4);
@@ -109,111 +124,152 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
             float *dst = kind == 0 ? q_s[tt] : kind == 1 ? k_s[tt] : v_s[tt];
             *reinterpret_cast<float4 *>(dst + i4 * 4) = v;
         }
-        // The gate input of this warp's token, for the norm at the end of the pass.
-        float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        float gate_a = 0.0f, gate_b = 0.0f;
-        if (warp < count) {
-            const size_t row = start + base + warp;
-            z = *reinterpret_cast<const float4 *>(proj + row * p.proj_ld + p.z_offset + h * D + lane * 4);
-            if (lane == 0) { gate_a = proj[row * p.proj_ld + p.a_offset + h]; gate_b = proj[row * p.proj_ld + p.b_offset + h]; }
-        }
-        __syncthreads();
-        if (warp < count) {
-            const int tt = warp;
-            const float4 qv = *reinterpret_cast<const float4 *>(&q_s[tt][lane * 4]);
-            const float4 kv = *reinterpret_cast<const float4 *>(&k_s[tt][lane * 4]);
-            const float qq = spl_warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
-            const float kk = spl_warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
-            if (lane == 0) {
-                scal[tt][0] = (1.0f / sqrtf(qq + 1e-6f)) * (1.0f / sqrtf(float(D)));
-                scal[tt][1] = 1.0f / sqrtf(kk + 1e-6f);
-                const float x = gate_a + bias;
-                const float softplus = x > 20.0f ? x : logf(1.0f + expf(x));
-                scal[tt][2] = expf(neg_a * softplus);
-                scal[tt][3] = spl_sigmoid(gate_b);
+        // The gate inputs of this warp's tokens, for the scalars below.
+        float gate_a[ZT], gate_b[ZT];
+#pragma unroll
+        for (int n = 0; n < ZT; ++n) {
+            const int tt = warp + n * WARPS;
+            gate_a[n] = 0.0f; gate_b[n] = 0.0f;
+            if (tt < count && lane == 0) {
+                const size_t row = start + base + tt;
+                gate_a[n] = proj[row * p.proj_ld + p.a_offset + h]; gate_b[n] = proj[row * p.proj_ld + p.b_offset + h];
             }
         }
+        __syncthreads();
+        SPL_G(56);
+#pragma unroll
+        for (int n = 0; n < ZT; ++n) {
+            const int tt = warp + n * WARPS;
+            if (tt < count) {
+                const float4 qv = *reinterpret_cast<const float4 *>(&q_s[tt][lane * 4]);
+                const float4 kv = *reinterpret_cast<const float4 *>(&k_s[tt][lane * 4]);
+                const float qq = spl_warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
+                const float kk = spl_warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
+                if (lane == 0) {
+                    scal[tt][0] = (1.0f / sqrtf(qq + 1e-6f)) * (1.0f / sqrtf(float(D)));
+                    scal[tt][1] = 1.0f / sqrtf(kk + 1e-6f);
+                    const float x = gate_a[n] + bias;
+                    const float softplus = x > 20.0f ? x : logf(1.0f + expf(x));
+                    scal[tt][2] = expf(neg_a * softplus);
+                    scal[tt][3] = spl_sigmoid(gate_b[n]);
+                }
+            }
+        }
+        SPL_G(57);
         if (base == 0 && pending != 0) {
             // Replay the accepted entries; a speculative run then stores the state it starts from.
             for (uint32_t e = 0; e < pending; ++e) {
-                const float delta = o_s[e][j], decay = jdecay[e];
-                const float2 d2 = make_float2(delta, delta), c2 = make_float2(decay, decay);
+                const float4 d4 = *reinterpret_cast<const float4 *>(&o_s[e][4 * rg]);
+                const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+                const float decay = jdecay[e];
+                const float2 c2 = make_float2(decay, decay);
 #pragma unroll
-                for (int m = 0; m < 4; ++m) {
-                    const float4 kv = *reinterpret_cast<const float4 *>(&jk_s[e][32 * m + 4 * part]);
-                    const float2 lo = spl_gdn_update2(make_float2(S[m].x, S[m].y), c2, make_float2(kv.x, kv.y), d2);
-                    const float2 hi = spl_gdn_update2(make_float2(S[m].z, S[m].w), c2, make_float2(kv.z, kv.w), d2);
-                    S[m] = make_float4(lo.x, lo.y, hi.x, hi.y);
+                for (int c = 0; c < 4; ++c) {
+                    const float4 kv = *reinterpret_cast<const float4 *>(&jk_s[e][32 * c + 4 * cg]);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        const float2 d2 = make_float2(dl[r], dl[r]);
+                        S[r][c][0] = spl_gdn_update2(S[r][c][0], c2, make_float2(kv.x, kv.y), d2);
+                        S[r][c][1] = spl_gdn_update2(S[r][c][1], c2, make_float2(kv.z, kv.w), d2);
+                    }
                 }
             }
             if (speculative) {
 #pragma unroll
-                for (int m = 0; m < 4; ++m) stored[8 * m] = S[m];
+                for (int r = 0; r < 4; ++r)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) stored[r * (D / 4) + 8 * c] = make_float4(S[r][c][0].x, S[r][c][0].y, S[r][c][1].x, S[r][c][1].y);
             }
         }
+        SPL_G(58);
         __syncthreads();      // the tokens' scalars are written; the replay has finished with o_s
+        SPL_G(59);
         for (int tt = 0; tt < count; ++tt) {
             const float inv_q = scal[tt][0], inv_k = scal[tt][1], decay = scal[tt][2], beta = scal[tt][3];
-            float4 kv[4];
-            float2 ma = make_float2(0.0f, 0.0f), mb = make_float2(0.0f, 0.0f);
+            float4 kv[4], qv[4];
 #pragma unroll
-            for (int m = 0; m < 4; ++m) {
-                kv[m] = *reinterpret_cast<const float4 *>(&k_s[tt][32 * m + 4 * part]);
-                ma = spl_fma2(make_float2(S[m].x, S[m].y), make_float2(kv[m].x, kv[m].y), ma);
-                mb = spl_fma2(make_float2(S[m].z, S[m].w), make_float2(kv[m].z, kv[m].w), mb);
+            for (int c = 0; c < 4; ++c) {
+                kv[c] = *reinterpret_cast<const float4 *>(&k_s[tt][32 * c + 4 * cg]);
+                qv[c] = *reinterpret_cast<const float4 *>(&q_s[tt][32 * c + 4 * cg]);
             }
-            float mem = (ma.x + ma.y) + (mb.x + mb.y);
-            mem += __shfl_xor_sync(0xffffffffu, mem, 1);
-            mem += __shfl_xor_sync(0xffffffffu, mem, 2);
-            mem += __shfl_xor_sync(0xffffffffu, mem, 4);
-            const float delta = (v_s[tt][j] - mem * decay * inv_k) * beta * inv_k;
-            const float2 d2 = make_float2(delta, delta), c2 = make_float2(decay, decay);
-            float2 oa = make_float2(0.0f, 0.0f), ob = make_float2(0.0f, 0.0f);
+            float mem[4];
 #pragma unroll
-            for (int m = 0; m < 4; ++m) {
-                const float4 qv = *reinterpret_cast<const float4 *>(&q_s[tt][32 * m + 4 * part]);
-                const float2 lo = spl_gdn_update2(make_float2(S[m].x, S[m].y), c2, make_float2(kv[m].x, kv[m].y), d2);
-                const float2 hi = spl_gdn_update2(make_float2(S[m].z, S[m].w), c2, make_float2(kv[m].z, kv[m].w), d2);
-                S[m] = make_float4(lo.x, lo.y, hi.x, hi.y);
-                oa = spl_fma2(lo, make_float2(qv.x, qv.y), oa);
-                ob = spl_fma2(hi, make_float2(qv.z, qv.w), ob);
+            for (int r = 0; r < 4; ++r) {
+                float2 ma = make_float2(0.0f, 0.0f), mb = make_float2(0.0f, 0.0f);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    ma = spl_fma2(S[r][c][0], make_float2(kv[c].x, kv[c].y), ma);
+                    mb = spl_fma2(S[r][c][1], make_float2(kv[c].z, kv[c].w), mb);
+                }
+                mem[r] = (ma.x + ma.y) + (mb.x + mb.y);
             }
-            float o = (oa.x + oa.y) + (ob.x + ob.y);
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            o += __shfl_xor_sync(0xffffffffu, o, 4);
-            if (part == 0) o_s[tt][j] = o * inv_q;
+#pragma unroll
+            for (int w = 1; w < 8; w <<= 1)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) mem[r] += __shfl_xor_sync(0xffffffffu, mem[r], w);
+            const float4 v4 = *reinterpret_cast<const float4 *>(&v_s[tt][4 * rg]);
+            const float vl[4] = {v4.x, v4.y, v4.z, v4.w};
+            float delta[4], o[4];
+            const float2 c2 = make_float2(decay, decay);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                delta[r] = (vl[r] - mem[r] * decay * inv_k) * beta * inv_k;
+                const float2 d2 = make_float2(delta[r], delta[r]);
+                float2 oa = make_float2(0.0f, 0.0f), ob = make_float2(0.0f, 0.0f);
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    S[r][c][0] = spl_gdn_update2(S[r][c][0], c2, make_float2(kv[c].x, kv[c].y), d2);
+                    S[r][c][1] = spl_gdn_update2(S[r][c][1], c2, make_float2(kv[c].z, kv[c].w), d2);
+                    oa = spl_fma2(S[r][c][0], make_float2(qv[c].x, qv[c].y), oa);
+                    ob = spl_fma2(S[r][c][1], make_float2(qv[c].z, qv[c].w), ob);
+                }
+                o[r] = (oa.x + oa.y) + (ob.x + ob.y);
+            }
+#pragma unroll
+            for (int w = 1; w < 8; w <<= 1)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) o[r] += __shfl_xor_sync(0xffffffffu, o[r], w);
+            if (cg == 0) *reinterpret_cast<float4 *>(&o_s[tt][4 * rg]) = make_float4(o[0] * inv_q, o[1] * inv_q, o[2] * inv_q, o[3] * inv_q);
             if (speculative) {
                 float *entry = jhead + size_t(base + tt) * VH * SPL_JOURNAL_WIDTH;
-                if (tid < D) entry[tid] = k_s[tt][tid];
-                if (part == 0) entry[D + j] = delta;
+                if (tid < D / 4) *reinterpret_cast<float4 *>(entry + 4 * tid) = *reinterpret_cast<const float4 *>(&k_s[tt][4 * tid]);
+                if (cg == 0) *reinterpret_cast<float4 *>(entry + D + 4 * rg) = make_float4(delta[0], delta[1], delta[2], delta[3]);
                 if (tid == 0) entry[2 * D] = decay;
             }
         }
+        SPL_G(60);
         __syncthreads();
+        SPL_G(61);
         // Gated RMSNorm and the bf16 operand, one warp a token.
-        if (warp < count) {
-            const int tt = warp;
-            const size_t row = start + base + tt;
-            const float4 ov = *reinterpret_cast<const float4 *>(&o_s[tt][lane * 4]);
-            const float inv = 1.0f / sqrtf(spl_warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w) / float(D) + p.eps);
-            const uint2 w = *reinterpret_cast<const uint2 *>(norm_weight + lane * 4);
-            const float r0 = spl_bf16_to_float(uint16_t(w.x)) * ov.x * inv * spl_silu_exact(z.x);
-            const float r1 = spl_bf16_to_float(uint16_t(w.x >> 16)) * ov.y * inv * spl_silu_exact(z.y);
-            const float r2 = spl_bf16_to_float(uint16_t(w.y)) * ov.z * inv * spl_silu_exact(z.z);
-            const float r3 = spl_bf16_to_float(uint16_t(w.y >> 16)) * ov.w * inv * spl_silu_exact(z.w);
-            const uint16_t b0 = spl_float_to_bf16(r0), b1 = spl_float_to_bf16(r1), b2 = spl_float_to_bf16(r2), b3 = spl_float_to_bf16(r3);
-            *reinterpret_cast<uint2 *>(core.values + core.at(int(row), h * D + lane * 4)) =
-                spl_operand_pack4(spl_bf16_to_float(b0), spl_bf16_to_float(b1), spl_bf16_to_float(b2), spl_bf16_to_float(b3));
-            // The following GEMM's per-64 sums: a 128-wide head is two quant groups, sixteen lanes each.
-            float gsum = (spl_bf16_to_float(b0) + spl_bf16_to_float(b1)) + (spl_bf16_to_float(b2) + spl_bf16_to_float(b3));
 #pragma unroll
-            for (int o = 8; o > 0; o >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o);
-            if ((lane & 15) == 0) core.put_sum(int(row), h * 2 + (lane >> 4), gsum);
+        for (int n = 0; n < ZT; ++n) {
+            const int tt = warp + n * WARPS;
+            if (tt < count) {
+                const size_t row = start + base + tt;
+                const float4 z = *reinterpret_cast<const float4 *>(proj + row * p.proj_ld + p.z_offset + h * D + lane * 4);
+                const float4 ov = *reinterpret_cast<const float4 *>(&o_s[tt][lane * 4]);
+                const float inv = 1.0f / sqrtf(spl_warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w) / float(D) + p.eps);
+                const uint2 w = *reinterpret_cast<const uint2 *>(norm_weight + lane * 4);
+                const float r0 = spl_bf16_to_float(uint16_t(w.x)) * ov.x * inv * spl_silu_exact(z.x);
+                const float r1 = spl_bf16_to_float(uint16_t(w.x >> 16)) * ov.y * inv * spl_silu_exact(z.y);
+                const float r2 = spl_bf16_to_float(uint16_t(w.y)) * ov.z * inv * spl_silu_exact(z.z);
+                const float r3 = spl_bf16_to_float(uint16_t(w.y >> 16)) * ov.w * inv * spl_silu_exact(z.w);
+                const uint16_t b0 = spl_float_to_bf16(r0), b1 = spl_float_to_bf16(r1), b2 = spl_float_to_bf16(r2), b3 = spl_float_to_bf16(r3);
+                *reinterpret_cast<uint2 *>(core.values + core.at(int(row), h * D + lane * 4)) =
+                    spl_operand_pack4(spl_bf16_to_float(b0), spl_bf16_to_float(b1), spl_bf16_to_float(b2), spl_bf16_to_float(b3));
+                // The following GEMM's per-64 sums: a 128-wide head is two quant groups, sixteen lanes each.
+                float gsum = (spl_bf16_to_float(b0) + spl_bf16_to_float(b1)) + (spl_bf16_to_float(b2) + spl_bf16_to_float(b3));
+#pragma unroll
+                for (int o2 = 8; o2 > 0; o2 >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o2);
+                if ((lane & 15) == 0) core.put_sum(int(row), h * 2 + (lane >> 4), gsum);
+            }
         }
     }
+    SPL_G(62);
     if (!speculative) {
 #pragma unroll
-        for (int m = 0; m < 4; ++m) stored[8 * m] = S[m];
+        for (int r = 0; r < 4; ++r)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) stored[r * (D / 4) + 8 * c] = make_float4(S[r][c][0].x, S[r][c][0].y, S[r][c][1].x, S[r][c][1].y);
     }
 }
