@@ -109,23 +109,24 @@ spl_attn_prepare_kernel(const float *__restrict__ proj, const uint16_t *__restri
 // warp reduction (redux) plus a four-way exchange; sums stay per thread until the end of the span.
 // When a maximum moves, the softmax warps rescale O^T in tensor memory before the next value product.
 //
-// Warps: 0-3 softmax, rescale and the partial's output, 4-7 K -> tensor memory, 8-11 V -> tensor memory, 12 copies (bulk
-// copies of whole 128-token chunks into a ring), 13 and 14 tensor-core issue of the score and the value product.
-// Every wait is bounded.
-// Tensor memory (512 columns): S two buffers at 0 and 64, O halves at 128 and 192, K operand at 256, V at 384.
+// Warps: 0-3 and 16-19 softmax (the first half and the second half of the queries), rescale and the partial's output,
+// 4-7 K -> tensor memory, 8-11 V -> tensor memory, 12 copies (bulk copies of whole 128-token chunks into a ring),
+// 13 and 14 tensor-core issue of the score and the value product. Every wait is bounded.
+// Tensor memory (512 columns): S two buffers of NQ columns at 0, O two halves of NQ columns at 96, K operand a ring
+// of three 64-column slots (128 channels each) at 192, V operand two 64-column halves at 384.
 #define SPL_ATTN_CH 128               // tokens per chunk
 #define SPL_ATTN_HEADROOM 6.0f        // a score may exceed its query's reference by this much (log2) before the reference is raised
 #define SPL_ATTN_PSCALE 64.0f         // 4096 / 2^headroom: keeps small probabilities normal in fp16 and large ones finite; removed at the end
 struct SplTrue { static constexpr bool value = true; };
 struct SplFalse { static constexpr bool value = false; };
-#define SPL_ATTN_THREADS 480
+#define SPL_ATTN_THREADS 640
 
 __host__ __device__ constexpr int spl_attn_nq(int per_kv) { return (8 * per_kv + 15) / 16 * 16; }
 __host__ __device__ constexpr int spl_attn_stages(int hd) { return hd >= 256 ? 2 : 4; }
 __host__ __device__ constexpr size_t spl_attn_stage_bytes(int hd) { return size_t(2) * SPL_ATTN_CH * hd + 1024; }
 __host__ __device__ constexpr size_t spl_attn_smem_bytes(int hd, int nq) {
     return 1024 + spl_attn_stages(hd) * spl_attn_stage_bytes(hd) + size_t(hd / 64) * nq * 128 /* Q */ + size_t(2) * 2 * nq * 128 /* P */
-           + size_t(2) * 4 * nq * 4 /* chunk maxima */ + size_t(4) * nq * 8 /* per-warp reference and factor */ + size_t(4) * nq * 4 + size_t(nq) * SPL_ATTN_CH * 4 /* sums */ + 512 /* barriers */;
+           + size_t(2) * 4 * nq * 4 /* chunk maxima */ + size_t(4) * nq * 8 /* per-warp reference and factor */ + size_t(4) * nq * 4 /* sums */ + 512 /* barriers */;
 }
 
 __device__ __forceinline__ void spl_tc_st32(uint32_t taddr, const uint32_t *r) {
@@ -135,6 +136,16 @@ __device__ __forceinline__ void spl_tc_st32(uint32_t taddr, const uint32_t *r) {
                    "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
                    "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
                    "r"(r[30]), "r"(r[31]) : "memory");
+}
+// Eight columns of this warp's 32 lanes; the load and its wait are one statement (see spl_tc_ld16).
+__device__ __forceinline__ void spl_tc_ld8(uint32_t (&r)[8], uint32_t taddr) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];\n"
+                 "tcgen05.wait::ld.sync.aligned;\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr));
+}
+__device__ __forceinline__ void spl_tc_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};\n"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]) : "memory");
 }
 __device__ __forceinline__ void spl_fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
 __device__ __forceinline__ float spl_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x)); return y; }
@@ -167,20 +178,20 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                      const float *__restrict__ k_scale, const int8_t *__restrict__ v_codes, const float *__restrict__ v_scale,
                      float *partials, SplAttnParams p, int *error_flag) {
     spl_grid_begin();
-    constexpr int NQ = spl_attn_nq(PER_KV), CH = SPL_ATTN_CH, NST = spl_attn_stages(HD), HALVES = HD / 128, QGROUPS = HD / 64;
+    constexpr int NQ = spl_attn_nq(PER_KV), NH = NQ / 2, CH = SPL_ATTN_CH, NST = spl_attn_stages(HD), HALVES = HD / 128, QGROUPS = HD / 64;
     constexpr int CHUNK_BYTES = CH * HD, STAGE = int(spl_attn_stage_bytes(HD)), QTILE = NQ * 128, PTILE = 2 * NQ * 128;
     constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
+    static_assert(NH % 8 == 0 && NQ <= 48, "two softmax groups of NQ / 2 queries, eight at a time; tensor memory holds two S and two O of NQ columns below column 192");
     extern __shared__ unsigned char spl_attn_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(spl_attn_smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char *q_tile = smem;                                   // [QGROUPS][NQ rows x 128 B]   B operand of the score product
     unsigned char *p_tile = q_tile + QGROUPS * QTILE;               // [2][2 token groups][NQ x 128 B] B operand of the value product
     unsigned char *ring = p_tile + 2 * PTILE;                       // [NST][K chunk | V chunk | k scales | v scales]
-    float *xmax = reinterpret_cast<float *>(ring + size_t(NST) * STAGE);   // [2][4][NQ]
-    float *ref_next = xmax + 2 * 4 * NQ, *ref_factor = ref_next + 4 * NQ;  // [4][NQ] each: running reference (log2 domain) and the chunk's rescale factor, one copy per softmax warp
+    float *xmax = reinterpret_cast<float *>(ring + size_t(NST) * STAGE);   // [2][4 token quarters][NQ]
+    float *ref_next = xmax + 2 * 4 * NQ, *ref_factor = ref_next + 4 * NQ;  // [4][NQ] each: running reference (log2 domain) and the chunk's rescale factor, a copy per softmax warp
     float *xsum = ref_factor + 4 * NQ;                                     // [4][NQ]
-    float *tsum = xsum + 4 * NQ;                                           // [NQ][128] sums of p per (query, token lane)
-    uint64_t *bars = reinterpret_cast<uint64_t *>(tsum + NQ * CH);
-    uint64_t *full_kv = bars, *empty_kv = full_kv + NST, *ka_full = empty_kv + NST, *ka_free = ka_full + 2, *va_full = ka_free + 2,
+    uint64_t *bars = reinterpret_cast<uint64_t *>(xsum + 4 * NQ);
+    uint64_t *full_kv = bars, *empty_kv = full_kv + NST, *ka_full = empty_kv + NST, *ka_free = ka_full + 3, *va_full = ka_free + 3,
              *va_free = va_full + 2, *s_full = va_free + 2, *s_free = s_full + 2, *p_full = s_free + 2, *p_free = p_full + 2, *o_done = p_free + 2, *x_full = o_done + 2, *y_full = x_full + 2, *sum_full = y_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sum_full + 1);
     int *xflag = reinterpret_cast<int *>(tmem_slot + 1);          // [2] last chunk (+1) of each parity whose scores called for a raise
@@ -198,14 +209,15 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
     const size_t table_base = size_t(row_slot[r0]) * p.max_pages;
 
     if (tid == 0) {
-        for (int i = 0; i < NST; ++i) { spl_mbar_init(&full_kv[i], 1); spl_mbar_init(&empty_kv[i], 12); }
+        for (int i = 0; i < NST; ++i) { spl_mbar_init(&full_kv[i], 1); spl_mbar_init(&empty_kv[i], 16); }      // K, V and softmax warps
+        for (int i = 0; i < 3; ++i) { spl_mbar_init(&ka_full[i], 4); spl_mbar_init(&ka_free[i], 1); }
         for (int i = 0; i < 2; ++i) {
-            spl_mbar_init(&ka_full[i], 4); spl_mbar_init(&ka_free[i], 1); spl_mbar_init(&va_full[i], 4); spl_mbar_init(&va_free[i], 1);
-            spl_mbar_init(&s_full[i], 1); spl_mbar_init(&s_free[i], 4); spl_mbar_init(&p_full[i], 4); spl_mbar_init(&p_free[i], 1);
-            spl_mbar_init(&o_done[i], 1); spl_mbar_init(&x_full[i], 4); spl_mbar_init(&y_full[i], 4);
+            spl_mbar_init(&va_full[i], 4); spl_mbar_init(&va_free[i], 1);
+            spl_mbar_init(&s_full[i], 1); spl_mbar_init(&s_free[i], 8); spl_mbar_init(&p_full[i], 8); spl_mbar_init(&p_free[i], 1);
+            spl_mbar_init(&o_done[i], 1); spl_mbar_init(&x_full[i], 8); spl_mbar_init(&y_full[i], 8);
             xflag[i] = 0;
         }
-        spl_mbar_init(sum_full, 4);
+        spl_mbar_init(sum_full, 8);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 13) {
@@ -226,7 +238,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
     __syncthreads();
     spl_tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem, tmem_o = tmem + 128, tmem_ka = tmem + 256, tmem_va = tmem + 384;
+    const uint32_t tmem_s = tmem, tmem_o = tmem + 96, tmem_ka = tmem + 192, tmem_va = tmem + 384;
     bool ok = true;
     // Debug trace (builds with -DSPL_TRACE only): cycles per chunk that one thread of each role of block (0, 0) spends in
     // its waits and its work.
@@ -279,16 +291,17 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                 SPL_A1(0);
 #pragma unroll
                 for (int h = 0; h < HALVES; ++h) {
-                    ok = ok && spl_mbar_wait(&ka_full[h], i & 1);
+                    const int piece = i * HALVES + h, slot = piece % 3;
+                    ok = ok && spl_mbar_wait(&ka_full[slot], (piece / 3) & 1);
                     SPL_A1(1);
                     if (!ok) break;
                     spl_tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks) {
                         const int step = h * 8 + ks;
-                        spl_tc_mma_ts(tmem_s + buf * 64, tmem_ka + h * 64 + ks * 8, q_desc + uint64_t(((step >> 2) * QTILE + (step & 3) * 32) >> 4), idesc, step > 0 ? 1u : 0u);
+                        spl_tc_mma_ts(tmem_s + buf * NQ, tmem_ka + slot * 64 + ks * 8, q_desc + uint64_t(((step >> 2) * QTILE + (step & 3) * 32) >> 4), idesc, step > 0 ? 1u : 0u);
                     }
-                    spl_tc_commit(&ka_free[h]);
+                    spl_tc_commit(&ka_free[slot]);
                     SPL_A1(2);
                 }
                 if (!ok) break;
@@ -315,7 +328,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                     spl_tc_fence_after();
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks)
-                        spl_tc_mma_ts(tmem_o + h * 64, tmem_va + h * 64 + ks * 8, p_desc + uint64_t((pb * PTILE + (ks >> 2) * QTILE + (ks & 3) * 32) >> 4), idesc, (i > 0 || ks > 0) ? 1u : 0u);
+                        spl_tc_mma_ts(tmem_o + h * NQ, tmem_va + h * 64 + ks * 8, p_desc + uint64_t((pb * PTILE + (ks >> 2) * QTILE + (ks & 3) * 32) >> 4), idesc, (i > 0 || ks > 0) ? 1u : 0u);
                     spl_tc_commit(&va_free[h]);
                     SPL_A1(2);
                 }
@@ -327,7 +340,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
             SPL_AOUT(37, 3);
         }
     } else if (warp >= 4 && warp < 8) {
-        // ---- K: thread = token. Its head_dim int8 -> fp16 pairs -> tensor memory, 128 channels (64 columns) at a time.
+        // ---- K: thread = token. Its head_dim int8 -> fp16 pairs -> tensor memory, 128 channels (a 64-column slot of the ring) at a time.
         const int token = (warp & 3) * 32 + lane;
         const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
         for (int i = 0; i < chunks && ok; ++i) {
@@ -339,8 +352,9 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
             const unsigned char *src = ring + size_t(st) * STAGE + token * 16;
 #pragma unroll 1
             for (int h = 0; h < HALVES; ++h) {
+                const int piece = i * HALVES + h, slot = piece % 3;
                 SPL_A1(1);
-                ok = spl_mbar_wait(&ka_free[h], (i & 1) ^ 1);
+                ok = spl_mbar_wait(&ka_free[slot], ((piece / 3) & 1) ^ 1);
                 SPL_A1(2);
                 if (!ok) break;
                 spl_tc_fence_after();
@@ -350,13 +364,13 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
 #pragma unroll
                     for (int pc = 0; pc < 4; ++pc)
                         spl_s8x16_to_h2x8(*reinterpret_cast<const uint4 *>(src + (h * 8 + 4 * b + pc) * (CH * 16)), a + pc * 8);
-                    spl_tc_st32(tmem_ka + lane_base + h * 64 + 32 * b, a);
+                    spl_tc_st32(tmem_ka + lane_base + slot * 64 + 32 * b, a);
                 }
                 if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_kv[st]); }
                 spl_tc_st_wait();
                 spl_tc_fence_before();
                 __syncwarp();
-                if (lane == 0) spl_mbar_arrive(&ka_full[h]);
+                if (lane == 0) spl_mbar_arrive(&ka_full[slot]);
                 SPL_A1(3);
             }
         }
@@ -396,17 +410,16 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
             }
         }
         if (warp == 8) SPL_AOUT(44, 4);
-    } else if (warp < 4) {
-        // ---- softmax: thread = token of the chunk (scores), = channel of a half (rescale and output).
-        const int w4 = warp & 3, token = w4 * 32 + lane;
+    } else if (warp < 4 || warp >= 16) {
+        // ---- softmax: thread = token of the chunk (scores), = channel of a half (rescale and output); the warp group
+        // (0-3 or 16-19) has the first or the second half of the queries.
+        const int w4 = warp & 3, token = w4 * 32 + lane, sg = warp >= 16 ? 1 : 0, cb = sg * NH;       // cb: first query column of the group
         const uint32_t lane_base = uint32_t(w4 * 32) << 16;
-        float *my_next = ref_next + w4 * NQ, *my_factor = ref_factor + w4 * NQ;       // this warp's copy: no cross-warp hazards
-        // Sum of p per (query, token lane), reduced over the lanes at the end of the span. They live in shared memory so that
-        // the passes below can be loops over blocks of sixteen queries (small code: five roles share the instruction caches).
-        float *my_sum = tsum + token;
-#pragma unroll 1
-        for (int n = 0; n < NQ; ++n) my_sum[n * CH] = 0.0f;
-        for (int n = lane; n < NQ; n += 32) { my_next[n] = -INFINITY; my_factor[n] = 1.0f; }
+        float *my_next = ref_next + w4 * NQ + cb, *my_factor = ref_factor + w4 * NQ + cb;      // this warp's copy: no cross-warp hazards
+        float sum[NH];              // sum of p per query over this thread's tokens; reduced over lanes and warps at the end of the span
+#pragma unroll
+        for (int n = 0; n < NH; ++n) sum[n] = 0.0f;
+        if (lane < NH) { my_next[lane] = -INFINITY; my_factor[lane] = 1.0f; }
         __syncwarp();
         // The thread's byte offsets inside an operand row for each of the eight swizzle phases of a row.
         uint32_t phase_offset[8];
@@ -434,26 +447,23 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
             SPL_A1(1);
             if (!ok) break;
             spl_tc_fence_after();
-            const uint32_t s_addr = tmem_s + lane_base + buf * 64, p_base = spl_smem_addr(p_tile + buf * PTILE);
+            const uint32_t s_addr = tmem_s + lane_base + buf * NQ + cb, p_base = spl_smem_addr(p_tile + buf * PTILE);
             auto chunk_body = [&](auto masked_tag) -> bool {
                 constexpr bool MASKED = decltype(masked_tag)::value;
                 // Pass 1: does any score of the chunk exceed its query's reference by more than the head-room?
                 float over = -INFINITY;
-#pragma unroll 1
-                for (int c0 = 0; c0 < NQ; c0 += 16) {
-                    uint32_t v[16];
-                    spl_tc_ld16(v, s_addr + c0);
 #pragma unroll
-                    for (int r4 = 0; r4 < 4; ++r4) {
-                        const float4 nx4 = *reinterpret_cast<const float4 *>(my_next + c0 + 4 * r4);
-                        const float nx[4] = {nx4.x, nx4.y, nx4.z, nx4.w};
+                for (int c0 = 0; c0 < NH; c0 += 8) {
+                    uint32_t v[8];
+                    float nx[8];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int r = 4 * r4 + e;
-                            float t = fmaf(__uint_as_float(v[r]), ksl, -nx[e]);
-                            if (MASKED) { const int rb = (c0 + r) / PER_KV; t = (rb >= first_seen && rb < valid_rows) ? t : -INFINITY; }
-                            over = fmaxf(over, t);
-                        }
+                    for (int r4 = 0; r4 < 2; ++r4) *reinterpret_cast<float4 *>(nx + 4 * r4) = *reinterpret_cast<const float4 *>(my_next + c0 + 4 * r4);
+                    spl_tc_ld8(v, s_addr + c0);
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) {
+                        float t = fmaf(__uint_as_float(v[r]), ksl, -nx[r]);
+                        if (MASKED) { const int rb = (cb + c0 + r) / PER_KV; t = (rb >= first_seen && rb < valid_rows) ? t : -INFINITY; }
+                        over = fmaxf(over, t);
                     }
                 }
                 const bool any_over = __any_sync(0xffffffffu, over > SPL_ATTN_HEADROOM);
@@ -473,48 +483,48 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                     // Some score is far above its reference (always so in a span's first chunk): raise every reference to its
                     // query's maximum so far, and rescale the sums and O^T by exp2(old - new).
 #pragma unroll 1
-                    for (int c0 = 0; c0 < NQ; c0 += 16) {
-                        uint32_t v[16];
-                        spl_tc_ld16(v, s_addr + c0);
+                    for (int c0 = 0; c0 < NH; c0 += 8) {
+                        uint32_t v[8];
+                        spl_tc_ld8(v, s_addr + c0);
 #pragma unroll
-                        for (int r = 0; r < 16; ++r) {
-                            const int n = c0 + r;
+                        for (int r = 0; r < 8; ++r) {
+                            const int n = cb + c0 + r;
                             float sc = __uint_as_float(v[r]) * ksl;
                             if (MASKED) { const int rb = n / PER_KV; sc = (rb >= first_seen && rb < valid_rows) ? sc : -INFINITY; }
                             const float top = spl_redux_max(sc);
-                            if (lane == (n & 31)) xmax[(par * 4 + w4) * NQ + n] = top;
+                            if (lane == r) xmax[(par * 4 + w4) * NQ + n] = top;
                         }
                     }
                     __syncwarp();
                     if (lane == 0) spl_mbar_arrive(&y_full[par]);
                     if (!spl_mbar_wait(&y_full[par], raises[par] & 1)) return false;
                     ++raises[par];
-                    for (int n = lane; n < NQ; n += 32) {
+                    if (lane < NH) {
+                        const int n = cb + lane;
                         const float top = fmaxf(fmaxf(xmax[(par * 4 + 0) * NQ + n], xmax[(par * 4 + 1) * NQ + n]),
                                                 fmaxf(xmax[(par * 4 + 2) * NQ + n], xmax[(par * 4 + 3) * NQ + n]));
-                        const float old = my_next[n], next = fmaxf(old, top);
-                        my_next[n] = next; my_factor[n] = (old == -INFINITY || next == old) ? 1.0f : spl_ex2(old - next);
+                        const float old = my_next[lane], next = fmaxf(old, top);
+                        my_next[lane] = next; my_factor[lane] = (old == -INFINITY || next == old) ? 1.0f : spl_ex2(old - next);
                     }
                     __syncwarp();
+                    float f[NH];
+#pragma unroll
+                    for (int r4 = 0; r4 < NH / 4; ++r4) *reinterpret_cast<float4 *>(f + 4 * r4) = *reinterpret_cast<const float4 *>(my_factor + 4 * r4);
+#pragma unroll
+                    for (int n = 0; n < NH; ++n) sum[n] *= f[n];
                     if (i > 0) {
                         if (!spl_mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1)) return false;
                         spl_tc_fence_after();
-#pragma unroll 1
-                        for (int c0 = 0; c0 < NQ; c0 += 16) {
-                            float f[16];
 #pragma unroll
-                            for (int r4 = 0; r4 < 4; ++r4) *reinterpret_cast<float4 *>(f + 4 * r4) = *reinterpret_cast<const float4 *>(my_factor + c0 + 4 * r4);
+                        for (int c0 = 0; c0 < NH; c0 += 8)
 #pragma unroll
                             for (int h = 0; h < HALVES; ++h) {
-                                uint32_t v[16];
-                                spl_tc_ld16(v, tmem_o + lane_base + h * 64 + c0);
+                                uint32_t v[8];
+                                spl_tc_ld8(v, tmem_o + lane_base + h * NQ + cb + c0);
 #pragma unroll
-                                for (int r = 0; r < 16; ++r) v[r] = __float_as_uint(__uint_as_float(v[r]) * f[r]);
-                                spl_tc_st16(tmem_o + lane_base + h * 64 + c0, v);
+                                for (int r = 0; r < 8; ++r) v[r] = __float_as_uint(__uint_as_float(v[r]) * f[c0 + r]);
+                                spl_tc_st8(tmem_o + lane_base + h * NQ + cb + c0, v);
                             }
-#pragma unroll
-                            for (int r = 0; r < 16; ++r) my_sum[(c0 + r) * CH] *= f[r];
-                        }
                         spl_tc_st_wait();
                         spl_tc_fence_before();
                     }
@@ -522,35 +532,31 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                 SPL_A1(5);
                 // Pass 2: probabilities into the operand tile of the value product, two queries at a time:
                 // P = bf16(p * vScale), held as fp16 of SPL_ATTN_PSCALE * P (both roundings of a pair are single instructions).
-#pragma unroll 1
-                for (int c0 = 0; c0 < NQ; c0 += 16) {
-                    uint32_t v[16];
-                    spl_tc_ld16(v, s_addr + c0);
 #pragma unroll
-                    for (int r4 = 0; r4 < 16; r4 += 4) {
-                        const float4 nx4 = *reinterpret_cast<const float4 *>(my_next + c0 + r4);
-                        const float nx[4] = {nx4.x, nx4.y, nx4.z, nx4.w};
+                for (int c0 = 0; c0 < NH; c0 += 8) {
+                    uint32_t v[8];
+                    float nx[8];
 #pragma unroll
-                        for (int r2 = 0; r2 < 4; r2 += 2) {
-                            const int r = r4 + r2;
-                            float pr[2];
+                    for (int r4 = 0; r4 < 2; ++r4) *reinterpret_cast<float4 *>(nx + 4 * r4) = *reinterpret_cast<const float4 *>(my_next + c0 + 4 * r4);
+                    spl_tc_ld8(v, s_addr + c0);
 #pragma unroll
-                            for (int e = 0; e < 2; ++e) {
-                                const int n = c0 + r + e;
-                                pr[e] = spl_ex2(fmaf(__uint_as_float(v[r + e]), ksl, -nx[r2 + e]));
-                                if (MASKED) { const int rb = n / PER_KV; pr[e] = (rb >= first_seen && rb < valid_rows) ? pr[e] : 0.0f; }
-                                my_sum[n * CH] += pr[e];
-                            }
-                            uint32_t packed_bf16, packed_f16;
-                            asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(packed_bf16) : "f"(pr[1] * vsc), "f"(pr[0] * vsc));
-                            asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(packed_f16) : "f"(__uint_as_float(packed_bf16 & 0xFFFF0000u)), "f"(__uint_as_float(packed_bf16 << 16)));
-                            const int n0 = c0 + r, n1 = n0 + 1;
-                            // No memory clobber: the stores need no order against this thread's loads, and the fences that
-                            // follow the pass order them against everything later.
-                            asm volatile("{\n .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n st.shared.b16 [%0], lo;\n st.shared.b16 [%1], hi;\n}\n"
-                                         ::"r"(p_base + uint32_t((n0 >> 3) * 1024) + phase_offset[r & 7]),
-                                           "r"(p_base + uint32_t((n1 >> 3) * 1024) + phase_offset[(r + 1) & 7]), "r"(packed_f16));
+                    for (int r = 0; r < 8; r += 2) {
+                        float pr[2];
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            pr[e] = spl_ex2(fmaf(__uint_as_float(v[r + e]), ksl, -nx[r + e]));
+                            if (MASKED) { const int rb = (cb + c0 + r + e) / PER_KV; pr[e] = (rb >= first_seen && rb < valid_rows) ? pr[e] : 0.0f; }
+                            sum[c0 + r + e] += pr[e];
                         }
+                        uint32_t packed_bf16, packed_f16;
+                        asm("cvt.rn.bf16x2.f32 %0, %1, %2;\n" : "=r"(packed_bf16) : "f"(pr[1] * vsc), "f"(pr[0] * vsc));
+                        asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(packed_f16) : "f"(__uint_as_float(packed_bf16 & 0xFFFF0000u)), "f"(__uint_as_float(packed_bf16 << 16)));
+                        const int n0 = cb + c0 + r, n1 = n0 + 1;
+                        // No memory clobber: the stores need no order against this thread's loads, and the fences that
+                        // follow the pass order them against everything later.
+                        asm volatile("{\n .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n st.shared.b16 [%0], lo;\n st.shared.b16 [%1], hi;\n}\n"
+                                     ::"r"(p_base + uint32_t((n0 >> 3) * 1024) + phase_offset[r & 7]),          // cb and c0 are multiples of 8
+                                       "r"(p_base + uint32_t((n1 >> 3) * 1024) + phase_offset[(r + 1) & 7]), "r"(packed_f16));
                     }
                 }
                 return true;
@@ -568,10 +574,10 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
         if (ok && chunks > 0) ok = spl_mbar_wait(&o_done[(chunks - 1) & 1], ((chunks - 1) >> 1) & 1);
         if (ok) {
             spl_tc_fence_after();
-#pragma unroll 1
-            for (int n = 0; n < NQ; ++n) {
-                const float total = spl_warp_sum(my_sum[n * CH]);
-                if (lane == (n & 31)) xsum[w4 * NQ + n] = total;
+#pragma unroll
+            for (int n = 0; n < NH; ++n) {
+                const float total = spl_warp_sum(sum[n]);
+                if (lane == n) xsum[w4 * NQ + cb + n] = total;
             }
             __syncwarp();
             if (lane == 0) spl_mbar_arrive(sum_full);
@@ -579,21 +585,21 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
         }
         if (ok) {
             const int record = HD + 2;
-            if (token < NQ && token / PER_KV < valid_rows) {
-                const int rb = token / PER_KV, hq = token % PER_KV;
+            if (w4 == 0 && lane < NH && (cb + lane) / PER_KV < valid_rows && cb + lane < 8 * PER_KV) {
+                const int n = cb + lane, rb = n / PER_KV, hq = n % PER_KV;
                 float *partial = partials + ((size_t(r0 + rb) * p.heads + kv_head * PER_KV + hq) * p.spans + span) * record;
-                partial[0] = chunks > 0 ? my_next[token] * LN2 : -INFINITY;
-                partial[1] = ((xsum[token] + xsum[NQ + token]) + xsum[2 * NQ + token]) + xsum[3 * NQ + token];
+                partial[0] = chunks > 0 ? my_next[lane] * LN2 : -INFINITY;
+                partial[1] = ((xsum[n] + xsum[NQ + n]) + xsum[2 * NQ + n]) + xsum[3 * NQ + n];
             }
 #pragma unroll
             for (int h = 0; h < HALVES; ++h)
 #pragma unroll
-                for (int c0 = 0; c0 < NQ; c0 += 16) {
-                    uint32_t v[16];
-                    if (chunks > 0) { spl_tc_ld16(v, tmem_o + lane_base + h * 64 + c0); spl_tc_ld_wait(); }
+                for (int c0 = 0; c0 < NH; c0 += 8) {
+                    uint32_t v[8];
+                    if (chunks > 0) spl_tc_ld8(v, tmem_o + lane_base + h * NQ + cb + c0);
 #pragma unroll
-                    for (int r = 0; r < 16; ++r) {
-                        const int n = c0 + r, rb = n / PER_KV, hq = n % PER_KV;
+                    for (int r = 0; r < 8; ++r) {
+                        const int n = cb + c0 + r, rb = n / PER_KV, hq = n % PER_KV;
                         if (rb < valid_rows && n < 8 * PER_KV) {
                             float *partial = partials + ((size_t(r0 + rb) * p.heads + kv_head * PER_KV + hq) * p.spans + span) * record;
                             partial[2 + h * 128 + token] = chunks > 0 ? __uint_as_float(v[r]) * (1.0f / SPL_ATTN_PSCALE) : 0.0f;
