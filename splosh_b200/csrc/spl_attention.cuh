@@ -110,7 +110,7 @@ spl_attn_prepare_kernel(const float *__restrict__ proj, const uint16_t *__restri
 // When a maximum moves, the softmax warps rescale O^T in tensor memory before the next value product.
 //
 // Warps: 0-3 and 16-19 softmax (the first half and the second half of the queries), rescale and the partial's output,
-// 4-7 K -> tensor memory, 8-11 V -> tensor memory, 12 copies (bulk copies of whole 128-token chunks into a ring),
+// 4-7 K -> tensor memory, 8-11 V -> tensor memory, 12 and 15 copies (bulk copies of whole 128-token chunks into rings),
 // 13 and 14 tensor-core issue of the score and the value product. Every wait is bounded.
 // Tensor memory (512 columns): S two buffers of NQ columns at 0, O two halves of NQ columns at 96, K operand a ring
 // of three 64-column slots (128 channels each) at 192, V operand two 64-column halves at 384.
@@ -122,10 +122,13 @@ struct SplFalse { static constexpr bool value = false; };
 #define SPL_ATTN_THREADS 640
 
 __host__ __device__ constexpr int spl_attn_nq(int per_kv) { return (8 * per_kv + 15) / 16 * 16; }
-__host__ __device__ constexpr int spl_attn_stages(int hd) { return hd >= 256 ? 2 : 4; }
-__host__ __device__ constexpr size_t spl_attn_stage_bytes(int hd) { return size_t(2) * SPL_ATTN_CH * hd + 1024; }
+// Shared-memory rings of 128-token chunks. K is converted as soon as it lands, so two stages do; V waits for the
+// probabilities of its chunk, so it has three and the copies still run two chunks ahead; scales are small.
+__host__ __device__ constexpr int spl_attn_k_stages(int hd) { return hd >= 256 ? 2 : 3; }
+__host__ __device__ constexpr int spl_attn_v_stages(int hd) { return hd >= 256 ? 3 : 4; }
+#define SPL_ATTN_S_STAGES 4
 __host__ __device__ constexpr size_t spl_attn_smem_bytes(int hd, int nq) {
-    return 1024 + spl_attn_stages(hd) * spl_attn_stage_bytes(hd) + size_t(hd / 64) * nq * 128 /* Q */ + size_t(2) * 2 * nq * 128 /* P */
+    return 1024 + size_t(spl_attn_k_stages(hd) + spl_attn_v_stages(hd)) * SPL_ATTN_CH * hd + SPL_ATTN_S_STAGES * 1024 + size_t(hd / 64) * nq * 128 /* Q */ + size_t(2) * 2 * nq * 128 /* P */
            + size_t(2) * 4 * nq * 4 /* chunk maxima */ + size_t(4) * nq * 8 /* per-warp reference and factor */ + size_t(4) * nq * 4 /* sums */ + 512 /* barriers */;
 }
 
@@ -178,20 +181,23 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                      const float *__restrict__ k_scale, const int8_t *__restrict__ v_codes, const float *__restrict__ v_scale,
                      float *partials, SplAttnParams p, int *error_flag) {
     spl_grid_begin();
-    constexpr int NQ = spl_attn_nq(PER_KV), NH = NQ / 2, CH = SPL_ATTN_CH, NST = spl_attn_stages(HD), HALVES = HD / 128, QGROUPS = HD / 64;
-    constexpr int CHUNK_BYTES = CH * HD, STAGE = int(spl_attn_stage_bytes(HD)), QTILE = NQ * 128, PTILE = 2 * NQ * 128;
+    constexpr int NQ = spl_attn_nq(PER_KV), NH = NQ / 2, CH = SPL_ATTN_CH, NKS = spl_attn_k_stages(HD), NVS = spl_attn_v_stages(HD), NSS = SPL_ATTN_S_STAGES;
+    constexpr int HALVES = HD / 128, QGROUPS = HD / 64, CHUNK_BYTES = CH * HD, QTILE = NQ * 128, PTILE = 2 * NQ * 128;
     constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
     static_assert(NH % 8 == 0 && NQ <= 48, "two softmax groups of NQ / 2 queries, eight at a time; tensor memory holds two S and two O of NQ columns below column 192");
     extern __shared__ unsigned char spl_attn_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(spl_attn_smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char *q_tile = smem;                                   // [QGROUPS][NQ rows x 128 B]   B operand of the score product
     unsigned char *p_tile = q_tile + QGROUPS * QTILE;               // [2][2 token groups][NQ x 128 B] B operand of the value product
-    unsigned char *ring = p_tile + 2 * PTILE;                       // [NST][K chunk | V chunk | k scales | v scales]
-    float *xmax = reinterpret_cast<float *>(ring + size_t(NST) * STAGE);   // [2][4 token quarters][NQ]
+    unsigned char *k_ring = p_tile + 2 * PTILE;                     // [NKS][K chunk]
+    unsigned char *v_ring = k_ring + size_t(NKS) * CHUNK_BYTES;     // [NVS][V chunk]
+    unsigned char *s_ring = v_ring + size_t(NVS) * CHUNK_BYTES;     // [NSS][k scales 512 B | v scales 512 B]
+    float *xmax = reinterpret_cast<float *>(s_ring + NSS * 1024);          // [2][4 token quarters][NQ]
     float *ref_next = xmax + 2 * 4 * NQ, *ref_factor = ref_next + 4 * NQ;  // [4][NQ] each: running reference (log2 domain) and the chunk's rescale factor, a copy per softmax warp
     float *xsum = ref_factor + 4 * NQ;                                     // [4][NQ]
     uint64_t *bars = reinterpret_cast<uint64_t *>(xsum + 4 * NQ);
-    uint64_t *full_kv = bars, *empty_kv = full_kv + NST, *ka_full = empty_kv + NST, *ka_free = ka_full + 3, *va_full = ka_free + 3,
+    uint64_t *full_k = bars, *empty_k = full_k + NKS, *full_v = empty_k + NKS, *empty_v = full_v + NVS, *full_sc = empty_v + NVS, *empty_sc = full_sc + NSS,
+             *ka_full = empty_sc + NSS, *ka_free = ka_full + 3, *va_full = ka_free + 3,
              *va_free = va_full + 2, *s_full = va_free + 2, *s_free = s_full + 2, *p_full = s_free + 2, *p_free = p_full + 2, *o_done = p_free + 2, *x_full = o_done + 2, *y_full = x_full + 2, *sum_full = y_full + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sum_full + 1);
     int *xflag = reinterpret_cast<int *>(tmem_slot + 1);          // [2] last chunk (+1) of each parity whose scores called for a raise
@@ -209,7 +215,9 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
     const size_t table_base = size_t(row_slot[r0]) * p.max_pages;
 
     if (tid == 0) {
-        for (int i = 0; i < NST; ++i) { spl_mbar_init(&full_kv[i], 1); spl_mbar_init(&empty_kv[i], 16); }      // K, V and softmax warps
+        for (int i = 0; i < NKS; ++i) { spl_mbar_init(&full_k[i], 1); spl_mbar_init(&empty_k[i], 4); }        // the K warps
+        for (int i = 0; i < NVS; ++i) { spl_mbar_init(&full_v[i], 1); spl_mbar_init(&empty_v[i], 4); }        // the V warps
+        for (int i = 0; i < NSS; ++i) { spl_mbar_init(&full_sc[i], 1); spl_mbar_init(&empty_sc[i], 8); }      // the softmax warps
         for (int i = 0; i < 3; ++i) { spl_mbar_init(&ka_full[i], 4); spl_mbar_init(&ka_free[i], 1); }
         for (int i = 0; i < 2; ++i) {
             spl_mbar_init(&va_full[i], 4); spl_mbar_init(&va_free[i], 1);
@@ -256,27 +264,36 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
 #define SPL_ACHUNKS() do { } while (0)
 #endif
 
-    if (warp == 12) {
-        // ---- copies: one chunk = 128 tokens of one kv head = K, V and their scales, each contiguous in the pool.
+    if (warp == 12 || warp == 15) {
+        // ---- copies: a chunk = 128 tokens of one kv head = K, V and their scales, each contiguous in the pool. Warp 12 brings
+        // K and the scales, warp 15 brings V, so that a full V ring does not hold back the K that the score product needs next.
         if (lane == 0) {
             for (int i = 0; i < chunks && ok; ++i) {
-                const int st = i % NST;
-                SPL_A0();
-                ok = spl_mbar_wait(&empty_kv[st], ((i / NST) & 1) ^ 1);
-                SPL_A1(0);
-                if (!ok) break;
                 const uint32_t token0 = token_begin + uint32_t(i) * CH;
                 const size_t vec = size_t(page_table[table_base + token0 / SPL_PAGE_TOKENS]) * p.kv_heads + kv_head;
                 const int sub = int(token0 % SPL_PAGE_TOKENS) / CH;
-                unsigned char *dst = ring + size_t(st) * STAGE;
-                spl_mbar_expect_tx(&full_kv[st], 2 * CHUNK_BYTES + 1024);
-                spl_bulk_g2s(dst, k_codes + vec * (SPL_PAGE_TOKENS * HD) + size_t(sub) * CHUNK_BYTES, CHUNK_BYTES, &full_kv[st]);
-                spl_bulk_g2s(dst + CHUNK_BYTES, v_codes + vec * (SPL_PAGE_TOKENS * HD) + size_t(sub) * CHUNK_BYTES, CHUNK_BYTES, &full_kv[st]);
-                spl_bulk_g2s(dst + 2 * CHUNK_BYTES, k_scale + vec * SPL_PAGE_TOKENS + sub * CH, 512, &full_kv[st]);
-                spl_bulk_g2s(dst + 2 * CHUNK_BYTES + 512, v_scale + vec * SPL_PAGE_TOKENS + sub * CH, 512, &full_kv[st]);
+                SPL_A0();
+                if (warp == 12) {
+                    const int st = i % NKS, ss = i % NSS;
+                    ok = spl_mbar_wait(&empty_k[st], ((i / NKS) & 1) ^ 1) && spl_mbar_wait(&empty_sc[ss], ((i / NSS) & 1) ^ 1);
+                    SPL_A1(0);
+                    if (!ok) break;
+                    spl_mbar_expect_tx(&full_k[st], CHUNK_BYTES);
+                    spl_bulk_g2s(k_ring + size_t(st) * CHUNK_BYTES, k_codes + vec * (SPL_PAGE_TOKENS * HD) + size_t(sub) * CHUNK_BYTES, CHUNK_BYTES, &full_k[st]);
+                    spl_mbar_expect_tx(&full_sc[ss], 1024);
+                    spl_bulk_g2s(s_ring + ss * 1024, k_scale + vec * SPL_PAGE_TOKENS + sub * CH, 512, &full_sc[ss]);
+                    spl_bulk_g2s(s_ring + ss * 1024 + 512, v_scale + vec * SPL_PAGE_TOKENS + sub * CH, 512, &full_sc[ss]);
+                } else {
+                    const int st = i % NVS;
+                    ok = spl_mbar_wait(&empty_v[st], ((i / NVS) & 1) ^ 1);
+                    SPL_A1(0);
+                    if (!ok) break;
+                    spl_mbar_expect_tx(&full_v[st], CHUNK_BYTES);
+                    spl_bulk_g2s(v_ring + size_t(st) * CHUNK_BYTES, v_codes + vec * (SPL_PAGE_TOKENS * HD) + size_t(sub) * CHUNK_BYTES, CHUNK_BYTES, &full_v[st]);
+                }
                 SPL_A1(1);
             }
-            SPL_AOUT(32, 2);
+            if (warp == 12) SPL_AOUT(32, 2);
         }
     } else if (warp == 13) {
         // ---- tensor-core issue, score product: S^T[buffer] = K (tensor memory) x Q (shared memory), sixteen channels per instruction.
@@ -344,12 +361,12 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
         const int token = (warp & 3) * 32 + lane;
         const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
         for (int i = 0; i < chunks && ok; ++i) {
-            const int st = i % NST;
+            const int st = i % NKS;
             SPL_A0();
-            ok = spl_mbar_wait(&full_kv[st], (i / NST) & 1);
+            ok = spl_mbar_wait(&full_k[st], (i / NKS) & 1);
             SPL_A1(0);
             if (!ok) break;
-            const unsigned char *src = ring + size_t(st) * STAGE + token * 16;
+            const unsigned char *src = k_ring + size_t(st) * CHUNK_BYTES + token * 16;
 #pragma unroll 1
             for (int h = 0; h < HALVES; ++h) {
                 const int piece = i * HALVES + h, slot = piece % 3;
@@ -366,7 +383,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                         spl_s8x16_to_h2x8(*reinterpret_cast<const uint4 *>(src + (h * 8 + 4 * b + pc) * (CH * 16)), a + pc * 8);
                     spl_tc_st32(tmem_ka + lane_base + slot * 64 + 32 * b, a);
                 }
-                if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_kv[st]); }
+                if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_k[st]); }
                 spl_tc_st_wait();
                 spl_tc_fence_before();
                 __syncwarp();
@@ -380,12 +397,12 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
         const int channel = (warp & 3) * 32 + lane;
         const uint32_t lane_base = uint32_t((warp & 3) * 32) << 16;
         for (int i = 0; i < chunks && ok; ++i) {
-            const int st = i % NST;
+            const int st = i % NVS;
             SPL_A0();
-            ok = spl_mbar_wait(&full_kv[st], (i / NST) & 1);
+            ok = spl_mbar_wait(&full_v[st], (i / NVS) & 1);
             SPL_A1(0);
             if (!ok) break;
-            const unsigned char *src = ring + size_t(st) * STAGE + CHUNK_BYTES;
+            const unsigned char *src = v_ring + size_t(st) * CHUNK_BYTES;
 #pragma unroll 1
             for (int h = 0; h < HALVES; ++h) {
                 SPL_A1(1);
@@ -401,7 +418,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                         spl_s8x16_to_h2x8(*reinterpret_cast<const uint4 *>(src + (4 * b + tb) * (HD * 16) + (h * 128 + channel) * 16), a + tb * 8);
                     spl_tc_st32(tmem_va + lane_base + h * 64 + 32 * b, a);
                 }
-                if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_kv[st]); }
+                if (h == HALVES - 1) { __syncwarp(); if (lane == 0) spl_mbar_arrive(&empty_v[st]); }
                 spl_tc_st_wait();
                 spl_tc_fence_before();
                 __syncwarp();
@@ -427,18 +444,18 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
 #pragma unroll
         for (int j = 0; j < 8; ++j) phase_offset[j] = uint32_t((token >> 6) * QTILE) + spl_sw128_offset(j, token & 63);
         for (int i = 0; i < chunks && ok; ++i) {
-            const int st = i % NST, buf = i & 1, par = i & 1;
+            const int ss = i % NSS, buf = i & 1, par = i & 1;
             SPL_A0();
-            ok = spl_mbar_wait(&full_kv[st], (i / NST) & 1);
+            ok = spl_mbar_wait(&full_sc[ss], (i / NSS) & 1);
             SPL_A1(0);
             if (!ok) break;
-            const float *scales = reinterpret_cast<const float *>(ring + size_t(st) * STAGE + 2 * CHUNK_BYTES);
+            const float *scales = reinterpret_cast<const float *>(s_ring + ss * 1024);
             const uint32_t token_index = token_begin + uint32_t(i) * CH + token;
             // Tokens past the last visible one were never written: their scales are whatever the pool held.
             const bool written = token_index < max_visible;
             const float ksl = written ? scales[token] * p.scale * LOG2E : 0.0f, vsc = written ? scales[CH + token] * SPL_ATTN_PSCALE : 0.0f;
             __syncwarp();
-            if (lane == 0) spl_mbar_arrive(&empty_kv[st]);
+            if (lane == 0) spl_mbar_arrive(&empty_sc[ss]);
             // A token is visible to rows rb >= first_seen; a chunk wholly below the first row's position needs no mask
             // (padding queries are zero there and their columns are never written out).
             const bool whole = token_begin + uint32_t(i + 1) * CH <= first_pos + 1;
