@@ -192,7 +192,7 @@ spl_status spl_debug_profile_read(spl_engine *engine, int32_t klass, double *mil
  * This entry point runs out[r][:] = GEMM(weights, activations[r][:]) (+ residual) on one of the
  * engine's resident weights and calls no cudaMalloc, cudaFree or other allocating routine: the
  * bf16 operand, its per-64 sums and the split-K partial sums live in a static device array of
- * about 10.2 MiB that every GPU loading the library holds until exit.
+ * about 10.3 MiB that every GPU loading the library holds until exit.
  *   - all three buffers are DEVICE pointers: activations fp32 [rows][inner], residual (may be
  *     null, may alias out) and out fp32 [rows][ld], ld = the tensor's columns rounded up to 16;
  *   - rows must be 1..64 and the tensor's inner dimension at most 17408, else SPL_ERR_INVALID_ROWS

@@ -176,7 +176,7 @@ int operand_rn(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : 64; }
 int choose_splits(int blocks, int groups, int sms, size_t partial_capacity, size_t partial_per_split) {
     int best = 1; double best_cost = 1e30;
     for (int s = 1; s <= groups / 8 && s <= 32; ++s) {
-        const int gps = (groups + s - 1) / s, eff = (groups + gps - 1) / gps;
+        const int gps = ((groups + s - 1) / s + 3) / 4 * 4, eff = (groups + gps - 1) / gps;      // a split starts on a multiple of four groups
         if (eff != s) continue;
         if (s > 1 && size_t(s) * partial_per_split > partial_capacity) break;
         const int waves = (blocks * s + sms - 1) / sms;
@@ -194,7 +194,7 @@ void launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &o
     const int groups = w.k / 64;
     const int row_blocks = (rows + RN - 1) / RN, rows_padded = op.blocks * RN;
     const int splits = choose_splits(w.tiles * row_blocks, groups, 148, partial_floats, size_t(rows_padded) * w.ld);
-    const int gps = (groups + splits - 1) / splits;
+    const int gps = ((groups + splits - 1) / splits + 3) / 4 * 4;
     const size_t smem = spl_tc_smem_bytes(RN);
     static bool configured = false;
     if (!configured) {
@@ -413,7 +413,7 @@ spl_status upload_q4_into(spl_engine *e, SplQ4Dev &w, int n0, int rows, int inne
     cudaMemcpy(&flag, bad, sizeof flag, cudaMemcpyDeviceToHost);
     cudaFree(bad);
     if (sp) { cudaFree(sp); cudaFree(ss); cudaFree(sbias); }
-    if (launched == SPL_OK && flag) launched = e->fail(SPL_ERR_INVALID_ARGUMENT, "a quantisation scale is outside [2^-13, 8188]: scale * (code - 8) would not be exact in fp16");
+    if (launched == SPL_OK && flag) launched = e->fail(SPL_ERR_INVALID_ARGUMENT, "a quantisation scale is outside [2^-13, 127] or a bias beyond 1023 in magnitude: the weight would not be exact in fp16");
     return launched;
 }
 
@@ -539,18 +539,18 @@ spl_status create(const spl_geometry *gp, const spl_config *cp, spl_engine *e) {
     e->rows_padded = (R + 63) / 64 * 64; e->logit_rows_padded = (e->c.max_logit_rows + 63) / 64 * 64;
     const int RP = e->rows_padded, LP = e->logit_rows_padded;
     if ((s = device_alloc(e, &e->xn, size_t(RP) * H, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->xn_sums, size_t(RP) * H / 64, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->core_sums, size_t(RP) * e->core_ld / 64, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->act_sums, size_t(RP) * g.inter / 64, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->hsn_sums, size_t(LP) * H / 64, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->xn_sums, spl_operand_sums_floats(RP, H), &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->core_sums, spl_operand_sums_floats(RP, e->core_ld), &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->act_sums, spl_operand_sums_floats(RP, g.inter), &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->hsn_sums, spl_operand_sums_floats(LP, H), &e->scratch_bytes)) != SPL_OK) return s;
     if ((s = device_alloc(e, &e->tc_error, 64)) != SPL_OK) return s;
     SPL_CUDA(cudaMemsetAsync(e->tc_error, 0, 64 * sizeof(int), e->stream));
     if (getenv("SPL_ATTN_TRACE")) { const int magic[2] = {0x7ACE, 0x200}; SPL_CUDA(cudaMemcpyAsync(e->tc_error + 1, magic, sizeof magic, cudaMemcpyHostToDevice, e->stream)); }
     SPL_CUDA(cudaMemsetAsync(e->xn, 0, size_t(RP) * H * 2, e->stream));
-    SPL_CUDA(cudaMemsetAsync(e->xn_sums, 0, size_t(RP) * H / 64 * 4, e->stream));
-    SPL_CUDA(cudaMemsetAsync(e->core_sums, 0, size_t(RP) * e->core_ld / 64 * 4, e->stream));
-    SPL_CUDA(cudaMemsetAsync(e->act_sums, 0, size_t(RP) * g.inter / 64 * 4, e->stream));
-    SPL_CUDA(cudaMemsetAsync(e->hsn_sums, 0, size_t(LP) * H / 64 * 4, e->stream));
+    SPL_CUDA(cudaMemsetAsync(e->xn_sums, 0, spl_operand_sums_floats(RP, H) * 4, e->stream));
+    SPL_CUDA(cudaMemsetAsync(e->core_sums, 0, spl_operand_sums_floats(RP, e->core_ld) * 4, e->stream));
+    SPL_CUDA(cudaMemsetAsync(e->act_sums, 0, spl_operand_sums_floats(RP, g.inter) * 4, e->stream));
+    SPL_CUDA(cudaMemsetAsync(e->hsn_sums, 0, spl_operand_sums_floats(LP, H) * 4, e->stream));
     if ((s = device_alloc(e, &e->proj, size_t(R) * e->proj_ld, &e->scratch_bytes)) != SPL_OK) return s;
     if ((s = device_alloc(e, &e->gdn_act, size_t(R) * sh.C, &e->scratch_bytes)) != SPL_OK) return s;
     if ((s = device_alloc(e, &e->core, size_t(RP) * e->core_ld, &e->scratch_bytes)) != SPL_OK) return s;
@@ -880,11 +880,11 @@ spl_status spl_debug_read(spl_engine *e, int32_t which, int32_t index, void *dst
 // pool at start-up, or a serving loop that bans allocator calls on its hot path because
 // cudaMalloc and cudaFree synchronise the whole device. The scratch the ordinary path takes from the engine's buffers (the bf16 operand with its
 // per-64 sums, and the split-K partial sums) lives here in one file-scope device array, so every
-// GPU that loads the library holds SPL_STATIC_BYTES (about 10.2 MiB) until the process exits.
+// GPU that loads the library holds SPL_STATIC_BYTES (about 10.3 MiB) until the process exits.
 #define SPL_STATIC_ROWS 64
 #define SPL_STATIC_INNER 17408
 #define SPL_STATIC_OPERAND_BYTES (SPL_STATIC_ROWS * SPL_STATIC_INNER * 2)
-#define SPL_STATIC_SUMS_BYTES (SPL_STATIC_ROWS * (SPL_STATIC_INNER / 64) * 4)
+#define SPL_STATIC_SUMS_BYTES (SPL_STATIC_ROWS * ((SPL_STATIC_INNER / 64 + 15) / 16) * 128)      // tiles of split means
 #define SPL_STATIC_FLAG_BYTES 256      // the error word and the kernel's debug words
 #define SPL_STATIC_PARTIAL_BYTES (8u << 20)
 #define SPL_STATIC_BYTES (SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES + SPL_STATIC_FLAG_BYTES + SPL_STATIC_PARTIAL_BYTES)
@@ -974,14 +974,14 @@ spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t
     e->partial_floats = size_t(16) * blocks * rn * ld;
     if (s == SPL_OK) s = device_alloc(e, &d_act32, size_t(rows) * k);
     if (s == SPL_OK) s = device_alloc(e, &d_act, size_t(blocks) * rn * k);
-    if (s == SPL_OK) s = device_alloc(e, &d_sums, size_t(blocks) * rn * k / 64);
+    if (s == SPL_OK) s = device_alloc(e, &d_sums, spl_operand_sums_floats(size_t(blocks) * rn, k));
     if (s == SPL_OK) s = device_alloc(e, &d_out, size_t(rows) * ld);
     if (s == SPL_OK) s = device_alloc(e, &d_flag, 64);
     if (s == SPL_OK) s = device_alloc(e, &e->partials, e->partial_floats);
     if (s == SPL_OK) s = upload_q4_into(e, w, 0, n, k, packed, scales, biases, false);
     if (s == SPL_OK) {
         cudaMemsetAsync(d_act, 0, size_t(blocks) * rn * k * 2, e->stream);
-        cudaMemsetAsync(d_sums, 0, size_t(blocks) * rn * k / 64 * 4, e->stream);
+        cudaMemsetAsync(d_sums, 0, spl_operand_sums_floats(size_t(blocks) * rn, k) * 4, e->stream);
         cudaMemsetAsync(d_flag, 0, 64 * sizeof(int), e->stream);
         if (getenv("SPL_TC_TRACE")) { const int magic[2] = {0x7ACE, int(strtol(getenv("SPL_TC_TRACE"), nullptr, 0))}; cudaMemcpyAsync(d_flag + 1, magic, sizeof magic, cudaMemcpyHostToDevice, e->stream); cudaStreamSynchronize(e->stream); }
         cudaMemcpyAsync(d_act32, activations, size_t(rows) * k * 4, cudaMemcpyHostToDevice, e->stream);

@@ -12,16 +12,17 @@
 // that 128 output columns are the M dimension of one tcgen05.mma and the step's rows (16..64 per
 // tile) are its N dimension. Per quant group (K = 64, four k16 instructions):
 //   * TMA bulk copies bring four groups at a time into shared memory: 16 KiB of codes, and the
-//     activations' slice with its per-64 sums and the scale/bias words;
-//   * dequant warps (one thread per output column, two sets taking alternate groups) turn the codes
+//     activations' slice with the scale/bias words; a tile of split means serves sixteen groups;
+//   * dequant warps (one thread per output column, three sets taking units of two groups in turn) turn the codes
 //     into exact fp16 values scale * (code - 8) and write them into tensor memory as the A operand
 //     (tcgen05.st), so weights never pass through shared memory expanded and are never re-read;
 //   * the activations' producer already wrote them (bf16-rounded, held as fp16) in the
 //     128-byte-swizzled K-major image the tensor core reads as the B operand;
-//   * one thread issues the four tcgen05.mma; the accumulator stays in tensor memory for the
+//   * two threads issue the four tcgen05.mma of a group; the accumulators stay in tensor memory for the
 //     whole contraction;
-//   * epilogue warps (again one thread per output column) add (bias + 8 scale) * sum per group in
-//     fp32 registers and, at the end, the accumulator (tcgen05.ld).
+//   * the bias term, (bias + 8 scale) * sum(a) per group, is a fifth instruction per four groups, from
+//     exact fp16 pairs of (64 bias, 512 scale) and the group means split in two fp16 numbers;
+//   * at the end every dequant warp reads its share of the accumulators (tcgen05.ld) and writes the output.
 // Everything is ordered by mbarriers. Every wait is bounded: a wait that runs out sets an error
 // word and the block unwinds, still releasing its tensor memory.
 //
@@ -50,22 +51,36 @@ struct SplQ4Dev {
 // rounding for activations of order one. The per-64 sums are taken from the bf16 values themselves.
 // The operand is cut in 64-wide groups and in row blocks of RN rows (RN = 16, 32 or 64, fixed per step). Block (g, rb) is RN * 128 bytes: row r at (r / 8) * 1024 + (r % 8) * 128,
 // its eight 16-byte units XOR-swizzled by r % 8: the canonical K-major SWIZZLE_128B image. The
-// per-64 sums sit beside it as fp32 [g][rb][RN].
+// per-64 sums sit beside it as tiles of the same shape, sixteen groups to a tile (SplOperand::put_sum).
 // Four bf16-rounded values (as floats) -> four fp16 in two words.
 __device__ __forceinline__ uint2 spl_operand_pack4(float r0, float r1, float r2, float r3) {
     const __half2 lo = __floats2half2_rn(r0, r1), hi = __floats2half2_rn(r2, r3);
     return make_uint2(*reinterpret_cast<const uint32_t *>(&lo), *reinterpret_cast<const uint32_t *>(&hi));
 }
 
+// Floats (4-byte cells) of the split-means array of an operand of `rows_padded` rows and contraction k.
+__host__ __device__ constexpr size_t spl_operand_sums_floats(size_t rows_padded, size_t k) { return ((k / 64 + 15) / 16) * rows_padded * 32; }
+
 struct SplOperand {
     __nv_bfloat16 *values;      // 16-bit cells (fp16 bits of the bf16-rounded values)
-    float *sums;
+    float *sums;               // tiles of split means, see put_sum
     int rn, blocks;            // rows per block, row blocks
     __device__ __forceinline__ size_t at(int row, int k) const {
         const int g = k >> 6, kk = k & 63, rb = row / rn, r = row % rn;
         return (size_t(g) * blocks + rb) * (size_t(rn) * 64) + size_t(r >> 3) * 512 + (r & 7) * 64 + (((kk >> 3) ^ (r & 7)) << 3) + (kk & 7);
     }
-    __device__ __forceinline__ void put_sum(int row, int g, float sum) const { sums[(size_t(g) * blocks + row / rn) * rn + row % rn] = sum; }
+    // The group's sum as the B operand of the GEMM's second term: (hi, lo, hi, lo) with hi + lo = sum / 64 in two fp16
+    // numbers, at contraction index 4 (g % 16) of row `row` of tile (g / 16, row block), the tiles laid out as `at` lays out
+    // the values. (`sums` is that array; the name is kept from the fp32 sums it replaces.)
+    __device__ __forceinline__ void put_sum(int row, int g, float sum) const {
+        const float mean = sum * 0.015625f;
+        const __half hi = __float2half_rn(mean), lo = __float2half_rn(mean - __half2float(hi));
+        const __half2 pair = __halves2half2(hi, lo);
+        const uint32_t bits = *reinterpret_cast<const uint32_t *>(&pair);
+        const int rb = row / rn, r = row % rn, kk = 4 * (g & 15);
+        __half *tile = reinterpret_cast<__half *>(sums) + (size_t(g >> 4) * blocks + rb) * (size_t(rn) * 64);
+        *reinterpret_cast<uint2 *>(tile + size_t(r >> 3) * 512 + (r & 7) * 64 + (((kk >> 3) ^ (r & 7)) << 3) + (kk & 7)) = make_uint2(bits, bits);
+    }
 };
 
 // ---- repack: MLX row-major -> tile layout, rows [n0, n0 + rows) of a fused tensor ------------
@@ -89,9 +104,10 @@ __global__ void spl_repack_q4_kernel(const uint32_t *__restrict__ packed, const 
             const uint16_t sbits = scales[size_t(row) * groups + g];
             sb[(size_t(tile) * groups + g) * 128 + col] = uint32_t(sbits) | (uint32_t(biases[size_t(row) * groups + g]) << 16);
             // The GEMM holds scale * (code - 8) in fp16 and forms it also from scale / 16: the scale must be zero, or at least
-            // 2^-13 (scale / 16 keeps its eight bits) with room for a factor 8.
+            // 2^-13 (scale / 16 keeps its eight bits); it also holds 512 scale and 64 bias in fp16.
             const float sc = fabsf(spl_bf16_to_float(sbits));
-            if (!(sc == 0.0f || (sc >= 1.220703125e-04f && sc <= 8188.0f))) atomicExch(out_of_range, 1);
+            const float bi = fabsf(spl_bf16_to_float(biases[size_t(row) * groups + g]));
+            if (!((sc == 0.0f || (sc >= 1.220703125e-04f && sc <= 127.0f)) && bi <= 1023.0f)) atomicExch(out_of_range, 1);
         }
     }
 }
@@ -220,47 +236,54 @@ __device__ __forceinline__ void spl_codes4(uint32_t w, uint32_t *a) {
 }
 
 // ---- the kernel -------------------------------------------------------------------------------
-// How the contract is kept without draining the accumulator after every group. With c the 4-bit code,
+// How the contract is kept with everything on the tensor cores. With c the 4-bit code,
 //   scale * c + bias = scale * (c - 8) + (bias + 8 * scale).
-// scale is bf16 (8 significant bits) and |c - 8| <= 8, so scale * (c - 8) has at most 11 significant bits:
-// it is EXACT in fp16 (for scales in fp16's normal range, checked when a weight is loaded). The tensor cores
-// therefore multiply exact fp16 weights by the bf16-rounded activations (held as fp16) and accumulate every group of the
-// contraction in one fp32 accumulator; the other term, (bias + 8 scale) * sum(a), is an fp32 multiply-add
-// per group in the epilogue warps, which have nothing else to do until the end. The result is the
-// reference's sum of exact per-group terms up to the order of fp32 additions.
+// First term. scale is bf16 (8 significant bits) and |c - 8| <= 8, so scale * (c - 8) has at most 11 significant
+// bits: it is EXACT in fp16 (for scales in the range checked when a weight is loaded). The tensor cores multiply
+// these exact weights by the bf16-rounded activations (held as fp16) and accumulate every group in fp32.
+// Second term, (bias + 8 scale) * sum(a) per group: one more k16 instruction per four groups. Its A operand holds,
+// per group, the pairs (64 bias, 64 bias) and (512 scale, 512 scale) (exact in fp16 for |bias| <= 1023 and
+// scale <= 127, checked at load); its B operand holds, per row and group, (hi, lo, hi, lo) with hi + lo the
+// group's mean sum(a) / 64 split in two fp16 numbers by the operand's producer (SplOperand::put_sum). The four
+// products add up to (bias + 8 scale) * sum(a) to within 2^-22 of the term, beside the fp32 accumulator's own 2^-24.
+// The result is the reference's sum of per-group terms up to the order of fp32 additions.
 #define SPL_TC_SUPER 4           // groups per shared-memory stage: one bulk copy brings 256 of the contraction
 #define SPL_TC_CSTAGES 4         // stages of codes (16 KiB each), handed back as soon as they are in registers
-#define SPL_TC_ASUPERS 3         // A operand stages in tensor memory: three times four groups of 32 columns; accumulators take the first 128 columns
+#define SPL_TC_ASUPERS 2         // A operand stages in tensor memory: twice four groups of 32 columns, and twice 8 columns for the second term
 #define SPL_TC_ASTAGES (SPL_TC_ASUPERS * SPL_TC_SUPER)
-#define SPL_TC_THREADS 480       // warps 0-3 and 8-11 dequant (even / odd groups), 4-7 epilogue, 12 copies, 13-14 tensor-core issue
+#define SPL_TC_THREADS 480       // warps 0-3, 8-11 and 4-7: three dequant sets (units of two groups in turn); 12 copies; 13-14 tensor-core issue
 
-// Stages of activations, sums and scale/bias words: they are held until the tensor core has finished with them.
+// Stages of activations and scale/bias words: they are held until the tensor core has finished with them.
 __host__ __device__ constexpr int spl_tc_bstages(int rn) { return rn >= 64 ? 4 : 6; }
-__host__ __device__ constexpr size_t spl_tc_bstage_bytes(int rn) { return size_t(SPL_TC_SUPER) * (size_t(rn) * 128 + size_t(rn) * 4 + 512); }
+__host__ __device__ constexpr size_t spl_tc_bstage_bytes(int rn) { return size_t(SPL_TC_SUPER) * (size_t(rn) * 128 + 512); }
 __host__ __device__ constexpr size_t spl_tc_smem_bytes(int rn) {
-    return 1024 /* alignment slack */ + size_t(SPL_TC_CSTAGES) * SPL_TC_SUPER * 4096 + size_t(spl_tc_bstages(rn)) * spl_tc_bstage_bytes(rn) + 1024 /* barriers */;
+    return 1024 /* alignment slack */ + size_t(SPL_TC_CSTAGES) * SPL_TC_SUPER * 4096 + size_t(spl_tc_bstages(rn)) * spl_tc_bstage_bytes(rn)
+           + size_t(2) * rn * 128 /* tiles of split means */ + 1024 /* barriers */;
+}
+__device__ __forceinline__ void spl_tc_st4(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
 }
 
 // Grid (tiles, splits, row blocks in use). Block (t, s, rb) computes columns [128 t, 128 t + 128) of rows
-// [RN rb, RN rb + RN) over groups [s * gps, (s + 1) * gps) and writes them to `out`, or, when the
-// contraction is split, to partials[s][row][column] for spl_gemm_reduce_kernel.
+// [RN rb, RN rb + RN) over groups [s * gps, (s + 1) * gps) (gps a multiple of four) and writes them to `out`, or,
+// when the contraction is split, to partials[s][row][column] for spl_gemm_reduce_kernel.
 template <int RN>
 __global__ void __launch_bounds__(SPL_TC_THREADS, 1)
 spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__restrict__ sb, const __nv_bfloat16 *__restrict__ act,
                       const float *__restrict__ act_sums, float *out, int out_ld, const float *residual, float *partials,
                       int rows, int op_blocks, int groups, int groups_per_split, int *error_flag) {
-    constexpr int BST = spl_tc_bstages(RN), CST = SPL_TC_CSTAGES, AST = SPL_TC_ASTAGES;
-    constexpr int BTILE = SPL_TC_SUPER * RN * 128, WSTAGE = SPL_TC_SUPER * 4096, SSTAGE = SPL_TC_SUPER * RN, QSTAGE = SPL_TC_SUPER * 128;
+    constexpr int BST = spl_tc_bstages(RN), CST = SPL_TC_CSTAGES, AST = SPL_TC_ASTAGES, ASUP = SPL_TC_ASUPERS;
+    constexpr int BTILE = SPL_TC_SUPER * RN * 128, WSTAGE = SPL_TC_SUPER * 4096, QSTAGE = SPL_TC_SUPER * 128, TTILE = RN * 128;
     extern __shared__ unsigned char spl_tc_smem_raw[];
     // The swizzled activation tiles must sit on 1,024-byte boundaries.
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(spl_tc_smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char *b_ring = smem;                                                       // [BST][SUPER][RN * 128] activations
-    unsigned char *w_ring = b_ring + size_t(BST) * BTILE;                               // [CST][SUPER][4096] codes
+    unsigned char *t_ring = b_ring + size_t(BST) * BTILE;                               // [2][RN * 128] split means of sixteen groups
+    unsigned char *w_ring = t_ring + 2 * TTILE;                                         // [CST][SUPER][4096] codes
     uint32_t *q_ring = reinterpret_cast<uint32_t *>(w_ring + size_t(CST) * WSTAGE);     // [BST][SUPER][128] scale | bias << 16
-    float *s_ring = reinterpret_cast<float *>(q_ring + BST * QSTAGE);                   // [BST][SUPER][RN] per-64 sums
-    uint64_t *bars = reinterpret_cast<uint64_t *>(s_ring + BST * SSTAGE);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(q_ring + BST * QSTAGE);
     uint64_t *full_c = bars, *empty_c = full_c + CST, *full_b = empty_c + CST, *empty_b = full_b + BST;
-    uint64_t *full_a = empty_b + BST, *done = full_a + AST, *finished = done + AST;
+    uint64_t *full_a = empty_b + BST, *done = full_a + AST / 2, *full_t = done + ASUP, *empty_t = full_t + 2, *finished = empty_t + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(finished + 1);
 
 #ifdef SPL_TRACE
@@ -272,12 +295,18 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     const int g_first = split * groups_per_split;
     const int g_count = min(groups_per_split, groups - g_first);
     const int supers = (g_count + SPL_TC_SUPER - 1) / SPL_TC_SUPER;
+    const int units = (g_count + 1) / 2;            // a unit = two groups = one hand-over from a dequant set
+    // Every block of a GEMM reads the same activation lines. Blocks therefore walk the contraction from
+    // different starting points (the order of a sum of groups does not matter beyond fp32 rounding, and it
+    // is a fixed function of the tile), so that at any moment they ask L2 for different lines.
+    const int rot = (g_count % SPL_TC_SUPER == 0 && supers > 1) ? int((uint32_t(tile) * 2654435761u >> 12) % uint32_t(supers)) : 0;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < CST; ++i) { spl_mbar_init(&full_c[i], 1); spl_mbar_init(&empty_c[i], 8); }       // the eight dequant warps
-        for (int i = 0; i < BST; ++i) { spl_mbar_init(&full_b[i], 1); spl_mbar_init(&empty_b[i], 6); }       // the two issuing threads and the four epilogue warps
+        for (int i = 0; i < CST; ++i) { spl_mbar_init(&full_c[i], 1); spl_mbar_init(&empty_c[i], 8); }       // the two sets (four warps each) that take the stage's units
+        for (int i = 0; i < BST; ++i) { spl_mbar_init(&full_b[i], 1); spl_mbar_init(&empty_b[i], 2); }       // the two issuing threads
         for (int i = 0; i < AST / 2; ++i) spl_mbar_init(&full_a[i], 4);      // one per unit of two groups
-        for (int i = 0; i < SPL_TC_ASUPERS; ++i) spl_mbar_init(&done[i], 2);      // one completion per four groups from each issuing thread
+        for (int i = 0; i < ASUP; ++i) spl_mbar_init(&done[i], 2);           // one completion per four groups from each issuing thread
+        for (int i = 0; i < 2; ++i) { spl_mbar_init(&full_t[i], 1); spl_mbar_init(&empty_t[i], 1); }
         spl_mbar_init(finished, 2);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -292,10 +321,10 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
 #ifdef SPL_TRACE
     if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && error_flag[1] == 0x7ACE) error_flag[22] = int(clock64() - t_entry);   // set-up
 #endif
-    // Consecutive instructions into one accumulator wait for each other (the pipeline's latency is longer than
-    // so small an instruction), so the k16 steps rotate over NACC accumulators; the epilogue adds them in order.
+    // Each issuing thread has accumulators of its own (consecutive instructions into one accumulator wait for each other);
+    // the output adds them in order.
     constexpr int NACC = RN <= 32 ? 4 : 2;
-    const uint32_t tmem_d = tmem, tmem_a = tmem + 128;
+    const uint32_t tmem_d = tmem, tmem_a = tmem + 128, tmem_aq = tmem + 128 + AST * 32;       // second-term operand: ASUP slots of 8 columns
     bool ok = true;
     // Debug trace (builds with -DSPL_TRACE only): cycles per group that one thread of each role of block (0, 0, 0) spends
     // in its waits and its work.
@@ -313,16 +342,12 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
 
     if (!(warp == 12 && lane == 0)) spl_grid_begin();     // the copying thread first asks for weights (below)
     if (warp == 12) {
-        // ---- copies. Codes have their own ring; activations, their sums and the scale/bias words share the other.
+        // ---- copies. Codes have their own ring; activations and the scale/bias words share another; the split means a third.
         if (lane == 0) {
             const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(codes) + (size_t(tile) * groups + g_first) * 4096;
             const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(act) + ((size_t(g_first) * row_blocks + rb) * RN) * 128;
-            const float *ssrc = act_sums + (size_t(g_first) * row_blocks + rb) * RN;
+            const unsigned char *tsrc = reinterpret_cast<const unsigned char *>(act_sums);
             const uint32_t *qsrc = sb + (size_t(tile) * groups + g_first) * 128;
-            // Every block of a GEMM reads the same activation lines. Blocks therefore walk the contraction from
-            // different starting points (the order of a sum of groups does not matter beyond fp32 rounding, and it
-            // is a fixed function of the tile), so that at any moment they ask L2 for different lines.
-            const int rot = (g_count % SPL_TC_SUPER == 0 && supers > 1) ? int((uint32_t(tile) * 2654435761u >> 12) % uint32_t(supers)) : 0;
             // The weights are nobody's output: the first stages of codes are asked for before this kernel waits for its
             // predecessor in the stream, so they arrive while that one is still finishing.
             const int ahead = min(CST, supers);
@@ -333,6 +358,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                 spl_bulk_g2s(w_ring + size_t(j0) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[j0]);
             }
             spl_grid_begin();
+            int mean_tile = -1, mean_loads = 0;
             for (int j0 = 0; j0 < supers && ok; ++j0) {
                 const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;      // the stage's source; j0 is its place in the pipeline
                 const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);         // with a rotation every stage is full
@@ -346,19 +372,27 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                     spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[sc]);
                 }
                 SPL_T1(t2);
+                // The tile of split means that holds this stage's groups (sixteen groups to a tile).
+                const int want = (g_first / SPL_TC_SUPER + j) >> 2;
+                if (want != mean_tile) {
+                    const int slot = mean_loads & 1;
+                    ok = spl_mbar_wait(&empty_t[slot], ((mean_loads >> 1) & 1) ^ 1);
+                    if (!ok) break;
+                    spl_mbar_expect_tx(&full_t[slot], TTILE);
+                    spl_bulk_g2s(t_ring + slot * TTILE, tsrc + (size_t(want) * row_blocks + rb) * TTILE, TTILE, &full_t[slot]);
+                    mean_tile = want; ++mean_loads;
+                }
                 ok = spl_mbar_wait(&empty_b[sbq], ((j0 / BST) & 1) ^ 1);
                 SPL_T1(t1);
                 if (!ok) break;
-                spl_mbar_expect_tx(&full_b[sbq], uint32_t(n) * (RN * 128 + RN * 4 + 512));
+                spl_mbar_expect_tx(&full_b[sbq], uint32_t(n) * (RN * 128 + 512));
                 spl_bulk_g2s(q_ring + sbq * QSTAGE, qsrc + size_t(j) * QSTAGE, uint32_t(n) * 512, &full_b[sbq]);
                 if (row_blocks == 1) {
                     spl_bulk_g2s(b_ring + size_t(sbq) * BTILE, bsrc + size_t(j) * BTILE, uint32_t(n) * RN * 128, &full_b[sbq]);
-                    spl_bulk_g2s(s_ring + sbq * SSTAGE, ssrc + size_t(j) * SSTAGE, uint32_t(n) * RN * 4, &full_b[sbq]);
                 } else {
                     for (int u = 0; u < n; ++u) {
                         const size_t g = size_t(j) * SPL_TC_SUPER + u;
                         spl_bulk_g2s(b_ring + size_t(sbq) * BTILE + u * RN * 128, bsrc + g * row_blocks * RN * 128, RN * 128, &full_b[sbq]);
-                        spl_bulk_g2s(s_ring + sbq * SSTAGE + u * RN, ssrc + g * row_blocks * RN, RN * 4, &full_b[sbq]);
                     }
                 }
                 SPL_T1(t2);
@@ -368,16 +402,16 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     } else if (warp >= 13) {
         // ---- tensor-core issue: D[128 x RN] += A[128 x 64] (fp16, tensor memory) * B[RN x 64]^T (fp16, shared memory).
         // Issuing one tcgen05.mma costs its thread about ninety cycles, so two threads share the work: warp 13 issues
-        // the first two k16 steps of every group and warp 14 the last two, each into accumulators of its own.
+        // the first two k16 steps of every group and warp 14 the last two, each into accumulators of its own; warp 13
+        // also issues each stage's second-term instruction.
         const int m = warp - 13;
         if (lane == 0) {
             constexpr uint32_t idesc = spl_tc_idesc(RN);
-            // Two groups (a "unit", K = 128) share one hand-over from the dequant warps.
-            const int units = (g_count + 1) / 2;
+            int mean_tile = -1, mean_loads = 0, mean_slot = 0;
             for (int un = 0; un < units && ok; ++un) {
-                const int j = un / 2, sbq = j % BST, au = un % (AST / 2);
+                const int j0 = un / 2, sbq = j0 % BST, au = un % (AST / 2);
                 SPL_T0();
-                if ((un & 1) == 0) ok = spl_mbar_wait(&full_b[sbq], (j / BST) & 1);
+                if ((un & 1) == 0) ok = spl_mbar_wait(&full_b[sbq], (j0 / BST) & 1);
                 SPL_T1(t0);
                 ok = ok && spl_mbar_wait(&full_a[au], (un / (AST / 2)) & 1);
                 SPL_T1(t1);
@@ -397,7 +431,20 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                     }
                 }
                 if ((un & 1) == 1 || un == units - 1) {
-                    spl_tc_commit(&done[j % SPL_TC_ASUPERS]);     // the stage's A slots may be rewritten
+                    if (m == 0) {
+                        // The stage's second term: its 16 values of the contraction are a quarter of a 128-byte row of the tile.
+                        const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
+                        const int quarter = g_first / SPL_TC_SUPER + j, want = quarter >> 2;
+                        if (want != mean_tile) {
+                            if (mean_tile >= 0) spl_tc_commit(&empty_t[mean_slot]);      // every instruction that read the old tile has been issued
+                            mean_slot = mean_loads & 1;
+                            ok = spl_mbar_wait(&full_t[mean_slot], (mean_loads >> 1) & 1);
+                            if (!ok) break;
+                            mean_tile = want; ++mean_loads;
+                        }
+                        spl_tc_mma_ts(tmem_d, tmem_aq + (j0 % ASUP) * 8, spl_tc_desc_sw128(spl_smem_addr(t_ring + mean_slot * TTILE) + (quarter & 3) * 32), idesc, 1u);
+                    }
+                    spl_tc_commit(&done[j0 % ASUP]);              // the stage's A slots may be rewritten
                     spl_tc_commit(&empty_b[sbq]);                 // its activations have been read
                 }
                 SPL_T1(t2);
@@ -406,144 +453,118 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             SPL_TOUT(if (trace && m == 0) error_flag[24] = int(clock64() - t_entry));     // last instruction issued
             if (ok) spl_tc_commit(finished);
         }
-    } else if (warp < 4 || warp >= 8) {
-        // ---- dequant: thread = output column; codes -> scale * (code - 8), exact in fp16 -> tensor memory. Warps 0-3
-        // take the even groups, warps 8-11 the odd ones; both sets write the lanes of their warp index mod 4.
-        const int quarter = warp & 3, col = quarter * 32 + lane, parity = warp >> 3;
+    } else {
+        // ---- dequant: thread = output column; codes -> scale * (code - 8), exact in fp16 -> tensor memory. Three sets
+        // of four warps (0-3, 8-11, 4-7) take the units of two groups in turn; a set's warps write the lanes of their
+        // warp index mod 4. A unit also carries its two groups' pairs of the second-term operand.
+        const int quarter = warp & 3, col = quarter * 32 + lane, set = warp < 4 ? 0 : warp >= 8 ? 1 : 2;
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
         const __half2 c1032 = __floats2half2_rn(1032.0f, 1032.0f), c1152 = __floats2half2_rn(1152.0f, 1152.0f);
-        for (int j = 0; j < supers && ok; ++j) {
-            const int sc = j % CST, sbq = j % BST;
+        for (int un = set; un < units && ok; un += 3) {
+            const int j = un >> 1, half = un & 1, sc = j % CST, sbq = j % BST;
             SPL_T0();
             ok = spl_mbar_wait(&full_c[sc], (j / CST) & 1) && spl_mbar_wait(&full_b[sbq], (j / BST) & 1);
+            SPL_TOUT(if (trace && warp == 0 && lane == 0 && un == 0) error_flag[23] = int(clock64() - t_entry));     // first stage has landed
             SPL_T1(t0);
-            SPL_TOUT(if (trace && warp == 0 && lane == 0 && j == 0) error_flag[23] = int(clock64() - t_entry));     // first stage has landed
             if (!ok) break;
-            const int n = min(SPL_TC_SUPER, g_count - j * SPL_TC_SUPER);
-            // This warp's unit of the stage: groups 2 * parity and 2 * parity + 1, read before either is converted so
-            // that the codes can be handed back at once.
-            uint4 lo[2], hi[2];
-            __half2 s2[2], s16[2];
+            const int n = min(SPL_TC_SUPER, g_count - j * SPL_TC_SUPER);      // groups of the stage; this unit has those from 2 * half
+            // The unit's codes and scale/bias words are read before anything is converted, so the codes can be handed back at once.
+            uint4 lo[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)}, hi[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+            uint32_t sbw[2] = {0u, 0u};
 #pragma unroll
             for (int v = 0; v < 2; ++v) {
-                const int u = 2 * parity + v;
+                const int u = 2 * half + v;
                 if (u < n) {
                     lo[v] = *reinterpret_cast<const uint4 *>(w_ring + size_t(sc) * WSTAGE + u * 4096 + col * 16);
                     hi[v] = *reinterpret_cast<const uint4 *>(w_ring + size_t(sc) * WSTAGE + u * 4096 + 2048 + col * 16);
-                    const float sf = __uint_as_float(q_ring[sbq * QSTAGE + u * 128 + col] << 16);
-                    s2[v] = __float2half2_rn(sf); s16[v] = __float2half2_rn(sf * 0.0625f);
+                    sbw[v] = q_ring[sbq * QSTAGE + u * 128 + col];
                 }
             }
             __syncwarp();
             if (lane == 0) spl_mbar_arrive(&empty_c[sc]);
-            if (2 * parity >= n) continue;                       // a short last stage may leave the second set nothing
             // Nibbles in place: 0x6400 | c is 1024 + c and 0x6400 | (c << 4) is 1024 + 16 c in fp16, so that
             // (q - 1032) * s and (q - 1152) * (s / 16) are both scale * (c - 8), exactly; one shift serves four nibbles.
-            uint32_t a[2][32];
+            uint32_t a[2][32], aq[4];
 #pragma unroll
             for (int v = 0; v < 2; ++v) {
+                const float sf = __uint_as_float(sbw[v] << 16), bf = __uint_as_float(sbw[v] & 0xFFFF0000u);
+                const __half2 s2 = __float2half2_rn(sf), s16 = __float2half2_rn(sf * 0.0625f);
+                const __half2 q1 = __float2half2_rn(bf * 64.0f), q2 = __float2half2_rn(sf * 512.0f);      // zero for a group past the end
+                aq[2 * v] = *reinterpret_cast<const uint32_t *>(&q1); aq[2 * v + 1] = *reinterpret_cast<const uint32_t *>(&q2);
                 const uint32_t w8[8] = {lo[v].x, lo[v].y, lo[v].z, lo[v].w, hi[v].x, hi[v].y, hi[v].z, hi[v].w};
 #pragma unroll
                 for (int w = 0; w < 8; ++w) {
                     const uint32_t x0 = w8[w], x1 = w8[w] >> 8;
-                    uint32_t q0 = (x0 & 0x000F000Fu) | 0x64006400u, q1 = (x0 & 0x00F000F0u) | 0x64006400u;
-                    uint32_t q2 = (x1 & 0x000F000Fu) | 0x64006400u, q3 = (x1 & 0x00F000F0u) | 0x64006400u;
-                    const __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&q0), c1032), s2[v]);
-                    const __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&q1), c1152), s16[v]);
-                    const __half2 h2 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&q2), c1032), s2[v]);
-                    const __half2 h3 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&q3), c1152), s16[v]);
+                    uint32_t p0 = (x0 & 0x000F000Fu) | 0x64006400u, p1 = (x0 & 0x00F000F0u) | 0x64006400u;
+                    uint32_t p2 = (x1 & 0x000F000Fu) | 0x64006400u, p3 = (x1 & 0x00F000F0u) | 0x64006400u;
+                    const __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p0), c1032), s2);
+                    const __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p1), c1152), s16);
+                    const __half2 h2 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p2), c1032), s2);
+                    const __half2 h3 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p3), c1152), s16);
                     a[v][4 * w + 0] = *reinterpret_cast<const uint32_t *>(&h0); a[v][4 * w + 1] = *reinterpret_cast<const uint32_t *>(&h1);
                     a[v][4 * w + 2] = *reinterpret_cast<const uint32_t *>(&h2); a[v][4 * w + 3] = *reinterpret_cast<const uint32_t *>(&h3);
                 }
             }
             SPL_T1(t1);
-            if (j >= SPL_TC_ASUPERS) ok = spl_mbar_wait(&done[j % SPL_TC_ASUPERS], ((j / SPL_TC_ASUPERS) & 1) ^ 1);
+            if (j >= ASUP) ok = spl_mbar_wait(&done[j % ASUP], ((j / ASUP) & 1) ^ 1);
             SPL_T1(t2);
             if (!ok) break;
             spl_tc_fence_after();
-            const int un = 2 * j + parity;                       // the unit's index and its A slots
 #pragma unroll
             for (int v = 0; v < 2; ++v) {
-                const int i = j * SPL_TC_SUPER + 2 * parity + v, sa = i % AST;
-                if (2 * parity + v < n) {
+                const int i = j * SPL_TC_SUPER + 2 * half + v, sa = i % AST;
+                if (2 * half + v < n) {
                     spl_tc_st16(tmem_a + lane_base + sa * 32, *reinterpret_cast<uint32_t (*)[16]>(&a[v][0]));
                     spl_tc_st16(tmem_a + lane_base + sa * 32 + 16, *reinterpret_cast<uint32_t (*)[16]>(&a[v][16]));
                 }
             }
+            spl_tc_st4(tmem_aq + lane_base + (j % ASUP) * 8 + half * 4, aq[0], aq[1], aq[2], aq[3]);
+            if (n <= 2) spl_tc_st4(tmem_aq + lane_base + (j % ASUP) * 8 + 4, 0u, 0u, 0u, 0u);       // a short last stage has no second unit
             spl_tc_st_wait();
             spl_tc_fence_before();
             __syncwarp();
             if (lane == 0) spl_mbar_arrive(&full_a[un % (AST / 2)]);
             SPL_T1(t3);
         }
-        SPL_TOUT(if (trace && warp == 0 && lane == 0) { error_flag[14] = int(t0 / g_count); error_flag[15] = int(t1 / g_count); error_flag[16] = int(t2 / g_count); error_flag[17] = int(t3 / g_count); });
-    } else {
-        // ---- epilogue: thread = output column. Per group acc[r] += (bias + 8 scale) * sum[r]; at the end the
-        // tensor cores' accumulator is added.
-        const int q = warp - 4, col = q * 32 + lane;
-        const uint32_t lane_base = uint32_t(q * 32) << 16;
-        float2 acc[RN / 2];           // packed pairs of rows: two-wide fp32 multiply-adds
-#pragma unroll
-        for (int r = 0; r < RN / 2; ++r) acc[r] = make_float2(0.0f, 0.0f);
-        for (int j = 0; j < supers && ok; ++j) {
-            const int sbq = j % BST;
-            SPL_T0();
-            ok = spl_mbar_wait(&full_b[sbq], (j / BST) & 1);
-            SPL_T1(t0);
-            if (!ok) break;
-            const int n = min(SPL_TC_SUPER, g_count - j * SPL_TC_SUPER);
-            for (int u = 0; u < n; ++u) {
-                const uint32_t x = q_ring[sbq * QSTAGE + u * 128 + col];
-                const float bias8 = fmaf(8.0f, __uint_as_float(x << 16), __uint_as_float(x & 0xFFFF0000u));
-                const float2 bb = make_float2(bias8, bias8);
-                const float *sums = s_ring + sbq * SSTAGE + u * RN;
-#pragma unroll
-                for (int r4 = 0; r4 < RN / 4; ++r4) {
-                    const float4 sm = *reinterpret_cast<const float4 *>(sums + 4 * r4);
-                    acc[2 * r4] = spl_fma2(make_float2(sm.x, sm.y), bb, acc[2 * r4]);
-                    acc[2 * r4 + 1] = spl_fma2(make_float2(sm.z, sm.w), bb, acc[2 * r4 + 1]);
-                }
-            }
-            __syncwarp();
-            if (lane == 0) spl_mbar_arrive(&empty_b[sbq]);
-            SPL_T1(t1);
-        }
+        SPL_TOUT(if (trace && warp == 0 && lane == 0) { error_flag[14] = int(t0 / g_count); error_flag[15] = int(t1 / g_count); error_flag[16] = int(t2 / g_count); error_flag[17] = int(t3 / g_count); error_flag[21] = g_count; });
+        // ---- output: the sets share the accumulators' columns, sixteen rows of the step at a time.
         SPL_T0();
         if (ok) ok = spl_mbar_wait(finished, 0);
-        SPL_T1(t2);
         SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[25] = int(clock64() - t_entry));     // accumulators complete
-        SPL_TOUT(if (trace && warp == 4 && lane == 0) { error_flag[18] = int(t0 / g_count); error_flag[19] = int(t1 / g_count); error_flag[20] = int(t2 / g_count); error_flag[21] = g_count; });
         if (ok) {
             spl_tc_fence_after();
             const int n = tile * 128 + col;
             const bool is_split = gridDim.y > 1;
             float *dst = is_split ? partials + size_t(split) * rows_padded * out_ld : out;
 #pragma unroll
-            for (int c0 = 0; c0 < RN; c0 += 16) {
+            for (int cb = 0; cb < RN / 16; ++cb) {
+                if (cb % 3 != set) continue;
+                const int c0 = cb * 16;
                 float total[16];
 #pragma unroll
                 for (int a = 0; a < NACC; ++a) {
                     uint32_t v[16];
                     spl_tc_ld16(v, tmem_d + lane_base + a * RN + c0);
-                    spl_tc_ld_wait();
 #pragma unroll
                     for (int r = 0; r < 16; ++r) total[r] = a == 0 ? __uint_as_float(v[r]) : total[r] + __uint_as_float(v[r]);
                 }
                 if (n < out_ld) {
+                    float res[16];
 #pragma unroll
                     for (int r = 0; r < 16; ++r) {
                         const int row = rb * RN + c0 + r;
-                        if (row < rows) {
-                            const size_t index = size_t(row) * out_ld + n;
-                            const float value = ((r & 1) ? acc[(c0 + r) >> 1].y : acc[(c0 + r) >> 1].x) + total[r];
-                            dst[index] = (!is_split && residual) ? value + residual[index] : value;
-                        }
+                        res[r] = (!is_split && residual && row < rows) ? residual[size_t(row) * out_ld + n] : 0.0f;
+                    }
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        const int row = rb * RN + c0 + r;
+                        if (row < rows) dst[size_t(row) * out_ld + n] = total[r] + res[r];
                     }
                 }
             }
         }
+        SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[26] = int(clock64() - t_entry));     // output written
     }
-    SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[26] = int(clock64() - t_entry));     // output written
     if (!ok) atomicExch(error_flag, 1 + warp);
     spl_tc_fence_before();
     __syncthreads();
