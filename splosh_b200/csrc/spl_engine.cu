@@ -187,10 +187,12 @@ int choose_splits(int blocks, int groups, int sms, size_t partial_capacity, size
 }
 
 struct GemmOperand { const __nv_bfloat16 *values; const float *sums; int rn, blocks; };
+// A split GEMM whose reduction (partials in split order + residual) is left to the kernel that reads its output next.
+struct PendingReduce { int splits = 1; size_t stride = 0; int ld = 0; };
 
 template <int RN>
 void launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows,
-                    float *partials, size_t partial_floats, int *error_flag, int *launches) {
+                    float *partials, size_t partial_floats, int *error_flag, int *launches, PendingReduce *defer) {
     const int groups = w.k / 64;
     const int row_blocks = (rows + RN - 1) / RN, rows_padded = op.blocks * RN;
     const int splits = choose_splits(w.tiles * row_blocks, groups, 148, partial_floats, size_t(rows_padded) * w.ld);
@@ -204,7 +206,8 @@ void launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &o
     launch_step(spl_gemm_q4_tc_kernel<RN>, dim3(dim3(w.tiles, splits, row_blocks)), dim3(SPL_TC_THREADS), smem, stream, 
         w.codes, w.sb, op.values, op.sums, out, w.ld, residual, partials, rows, op.blocks, groups, gps, error_flag);
     if (launches) ++*launches;
-    if (splits > 1) {
+    if (defer) { defer->splits = splits; defer->stride = size_t(rows_padded) * w.ld; defer->ld = w.ld; }
+    if (splits > 1 && !defer) {
         const size_t total = size_t(rows) * w.ld / 4;
         const int blocks = int(std::min<size_t>((total + 255) / 256, 2048));
         launch_step(spl_gemm_reduce_kernel, dim3(blocks), dim3(256), 0, stream, partials, splits, rows_padded, rows, w.ld, residual, out);
@@ -214,16 +217,16 @@ void launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &o
 
 // out[r][:] = GEMM(w, operand[r][:]) (+ residual) for the first `rows` rows of the operand.
 void launch_gemm_rows(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows,
-                      float *partials, size_t partial_floats, int *error_flag, int *launches) {
-    if (op.rn == 16) launch_gemm_tc<16>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches);
-    else if (op.rn == 32) launch_gemm_tc<32>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches);
-    else launch_gemm_tc<64>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches);
+                      float *partials, size_t partial_floats, int *error_flag, int *launches, PendingReduce *defer = nullptr) {
+    if (op.rn == 16) launch_gemm_tc<16>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer);
+    else if (op.rn == 32) launch_gemm_tc<32>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer);
+    else launch_gemm_tc<64>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer);
 }
 
-void launch_gemm(spl_engine *e, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows) {
+void launch_gemm(spl_engine *e, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows, PendingReduce *defer = nullptr) {
     profile_begin(e, KLASS_GEMM, double(w.bytes()) * ((rows + op.rn - 1) / op.rn));
     --e->launches;      // profile_begin counted one; the launcher counts the kernels it really starts
-    launch_gemm_rows(e->stream, w, op, out, residual, rows, e->partials, e->partial_floats, e->tc_error, &e->launches);
+    launch_gemm_rows(e->stream, w, op, out, residual, rows, e->partials, e->partial_floats, e->tc_error, &e->launches, defer);
     profile_end(e);
 }
 
@@ -287,6 +290,13 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
     launch_step(spl_embed_q4_kernel, dim3(R), dim3(128), 0, e->stream, e->embed_packed, e->embed_scales, e->embed_biases, e->d_tokens, e->h, H);
     profile_end(e);
 
+    // RMSNorm into an operand; `pending` names a split GEMM into `e->h` whose reduction this kernel performs first.
+    auto norm = [&](int rows, const uint16_t *weight, const uint32_t *gather, const SplOperand &dst, const PendingReduce &pending) {
+        const bool fused = pending.splits > 1;
+        launch_step(spl_rmsnorm_kernel, dim3(rows), dim3(fused ? 1024 : 256), 0, e->stream, e->h, H, weight, gather, dst, H, g.eps,
+                    fused ? e->partials : nullptr, pending.splits, pending.stride, pending.ld);
+    };
+    PendingReduce carried;      // the previous block's down projection, when its reduction is left to this block's input norm
     int linear_index = 0, full_index = 0;
     const int span_rows_needed = int(t->spans);
     (void)span_rows_needed;
@@ -294,7 +304,8 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
         const LayerWeights &L = e->layers[l];
         const int live = (l + 1 == g.layers) ? int(t->live_rows) : R;
         profile_begin(e, KLASS_ELEMENTWISE, 0);
-        launch_step(spl_rmsnorm_kernel, dim3(R), dim3(256), 0, e->stream, e->h, H, L.vec[SPL_VEC_INPUT_NORM], nullptr, xn, H, g.eps);
+        norm(R, L.vec[SPL_VEC_INPUT_NORM], nullptr, xn, carried);
+        carried = PendingReduce();
         profile_end(e);
         launch_gemm(e, L.in_proj, gxn, e->proj, nullptr, R);
         if (!L.full) {
@@ -338,23 +349,27 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
             ++full_index;
         }
         if (live > 0) {
-            launch_gemm(e, L.out_proj, gcore, e->h, e->h, live);
+            PendingReduce mixer;
+            launch_gemm(e, L.out_proj, gcore, e->h, e->h, live, &mixer);
             profile_begin(e, KLASS_ELEMENTWISE, 0);
-            launch_step(spl_rmsnorm_kernel, dim3(live), dim3(256), 0, e->stream, e->h, H, L.vec[SPL_VEC_POST_NORM], nullptr, xn, H, g.eps);
+            norm(live, L.vec[SPL_VEC_POST_NORM], nullptr, xn, mixer);
             profile_end(e);
             launch_gemm(e, L.gate_up, gxn, e->gate_up, nullptr, live);
             profile_begin(e, KLASS_ELEMENTWISE, 0);
             const size_t total = size_t(live) * g.inter / 4;
             launch_step(spl_silu_mul_kernel, dim3(int(std::min<size_t>((total + 255) / 256, 4096))), dim3(256), 0, e->stream, e->gate_up, e->gate_up_ld, g.inter, live, act);
             profile_end(e);
-            launch_gemm(e, L.down, gact, e->h, e->h, live);
+            // The down projection's reduction is left to the next block's input norm, except after the last block (the final
+            // norm gathers rows) and when the residual stream is tapped after every block.
+            const bool leave = l + 1 < g.layers && !e->taps_enabled && live == R;
+            launch_gemm(e, L.down, gact, e->h, e->h, live, leave ? &carried : nullptr);
         }
         if (e->taps_enabled) SPL_CUDA(cudaMemcpyAsync(e->taps + size_t(l) * e->c.max_rows * H, e->h, size_t(R) * H * 4, cudaMemcpyDeviceToDevice, e->stream));
     }
     if (t->logit_rows > 0) {
         profile_begin(e, KLASS_OTHER, 0);
         const int lrn = operand_rn(int(t->logit_rows)), lblocks = (int(t->logit_rows) + lrn - 1) / lrn;
-        launch_step(spl_rmsnorm_kernel, dim3(t->logit_rows), dim3(256), 0, e->stream, e->h, H, e->final_norm, e->d_gather, SplOperand{e->hsn, e->hsn_sums, lrn, lblocks}, H, g.eps);
+        norm(int(t->logit_rows), e->final_norm, e->d_gather, SplOperand{e->hsn, e->hsn_sums, lrn, lblocks}, PendingReduce());
         profile_end(e);
         launch_gemm(e, e->head, GemmOperand{e->hsn, e->hsn_sums, operand_rn(int(t->logit_rows)), (int(t->logit_rows) + operand_rn(int(t->logit_rows)) - 1) / operand_rn(int(t->logit_rows))}, e->logits, nullptr, int(t->logit_rows));
     }
