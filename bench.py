@@ -28,6 +28,9 @@ sys.path.insert(0, ROOT)
 
 SESSIONS, BLOCK = 8, 8
 CONTEXT_LOW, CONTEXT_HIGH = 36 * 1024, 42 * 1024
+# DRAM bytes the GEMM kernel moves per algorithmic byte: measured per tensor shape with ncu (reads + writes), 14.81 GB
+# for the 14.41 GB of a full step's 257 launches.
+GEMM_DRAM_PER_ALGORITHMIC_BYTE = 1.027
 SPAN_TARGET = 576      # scan blocks per step the table builder aims for (engine configuration)
 WEIGHT_SEED, TOKEN_SEED = 0x5EED6D17, 0xC0FFEE00
 
@@ -293,7 +296,9 @@ def main():
                      "class_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
                      "class_launches_per_step": {k: v["launches"] / args.steps for k, v in prof.items()}},
             "roofline": {"kernel": "spl_gemm_q4_tc_kernel", "bound": "hbm", "achieved": gemm_gbs, "peak": peak, "unit": "GB/s",
-                         "frac": gemm_gbs / peak, "traffic": None, "peak_source": peak_source,
+                         "frac": gemm_gbs / peak, "traffic": GEMM_DRAM_PER_ALGORITHMIC_BYTE * gemm["bytes"] / max(gemm["launches"], 1),
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of the 4-block case, per tensor shape, scaled by launches (profiles/gemm_q4_tc_kernel_27b_64rows.md)",
+                         "peak_source": peak_source,
                          "per_launch": {"algorithmic_bytes": gemm["bytes"] / max(gemm["launches"], 1), "ms": gemm["ms"] / max(gemm["launches"], 1)}},
         }
         if not args.no_cpu_baseline and world == 1:
