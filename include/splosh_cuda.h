@@ -133,7 +133,10 @@ void spl_engine_destroy(spl_engine *engine);
 const char *spl_last_error_string(const spl_engine *engine);
 /* Q4Handle (Sources/SploshCore/Allocator.swift:34-88): MLX affine-4, group 64, row-major packed
  * u32 [rows][inner/8] with bf16 scales and biases [rows][inner/64]. The caller keeps ownership of
- * the host arrays; the engine copies them into its own device layout before returning. */
+ * the host arrays; the engine copies them into its own device layout before returning.
+ * The tensor cores hold scale * (code - 8), 512 * scale and 64 * bias exactly in fp16: a tensor with a
+ * non-zero scale outside [2^-13, 127] or a bias beyond 1023 in magnitude is refused
+ * (SPL_ERR_INVALID_ARGUMENT), not approximated. */
 spl_status spl_weights_set_q4(spl_engine *engine, int32_t layer, int32_t kind, int32_t rows, int32_t inner,
                               const uint32_t *packed, const uint16_t *scales, const uint16_t *biases);
 /* TensorHandle for the bf16 vectors (norm weights, conv1d, A_log, dt_bias). */
@@ -191,7 +194,7 @@ spl_status spl_debug_profile_read(spl_engine *engine, int32_t klass, double *mil
  * path because cudaMalloc and cudaFree synchronise the whole device.
  * This entry point runs out[r][:] = GEMM(weights, activations[r][:]) (+ residual) on one of the
  * engine's resident weights and calls no cudaMalloc, cudaFree or other allocating routine: the
- * bf16 operand, its per-64 sums and the split-K partial sums live in a static device array of
+ * GEMM operand, its per-64 sums and the split-K partial sums live in a static device array of
  * about 10.3 MiB that every GPU loading the library holds until exit.
  *   - all three buffers are DEVICE pointers: activations fp32 [rows][inner], residual (may be
  *     null, may alias out) and out fp32 [rows][ld], ld = the tensor's columns rounded up to 16;

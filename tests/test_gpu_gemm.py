@@ -59,3 +59,18 @@ def test_zero_rows_and_bad_shapes_are_rejected():
         S.gemm_q4(z16, s, s, np.zeros((0, 256), np.float32))
     with pytest.raises(S.EngineError):
         S.gemm_q4(np.zeros((16, 8), np.uint32), np.zeros((16, 1), np.uint16), np.zeros((16, 1), np.uint16), np.zeros((1, 64), np.float32))
+
+
+def test_weights_the_tensor_cores_cannot_hold_exactly_are_refused():
+    """scale * (code - 8), 512 * scale and 64 * bias must be exact in fp16: a scale of 200, a scale of 2^-20 or a bias of
+    2,048 is refused when the weight is loaded, never approximated; zero scales and the largest allowed values pass."""
+    packed = np.zeros((128, 32), np.uint32); a = np.ones((4, 256), np.float32)
+    def run(scale_bits, bias_bits):
+        return S.gemm_q4(packed, np.full((128, 4), scale_bits, np.uint16), np.full((128, 4), bias_bits, np.uint16), a)
+    for scale_bits, bias_bits in ((0x4348, 0x0000), (0x3580, 0x0000), (0x3C00, 0x4500)):      # 200.0; 2^-20; bias 2,048
+        with pytest.raises(S.EngineError) as caught:
+            run(scale_bits, bias_bits)
+        assert caught.value.case == "invalidArgument"
+    out = run(0x42FE, 0xC47F)            # scale 127, bias -1,020: codes are 0, so every output is 256 * bias
+    assert np.array_equal(out, np.full((4, 128), -1020.0 * 256, np.float32))
+    assert np.array_equal(run(0x0000, 0x3F80), np.full((4, 128), 256.0, np.float32))      # zero scale, bias 1
