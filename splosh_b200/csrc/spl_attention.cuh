@@ -13,7 +13,7 @@
 //   v codes  [page][kv head][chunk 2][token block 8][channel head_dim][16 tokens]          int8
 //   k scale, v scale  [page][kv head][token 256]   fp32, value = scale * code
 // A K or V vector is symmetric int8: scale = max|x| / 127 (1 when all zero),
-// code = clamp(rint(x / scale), -127, 127) (engine_na.metal:2084-2093).
+// code = clamp(rint(x / scale), -127, 127) (engine_na.metal:2084-2093), stored as the byte code + 128.
 #pragma once
 #include "spl_common.cuh"
 #include "spl_gemm_tc.cuh"
@@ -25,6 +25,11 @@ __host__ __device__ __forceinline__ size_t spl_k_code_index(size_t vec, uint32_t
 __host__ __device__ __forceinline__ size_t spl_v_code_index(size_t vec, uint32_t in_page, int d, int hd) {
     return vec * (SPL_PAGE_TOKENS * size_t(hd)) + size_t(in_page >> 7) * (128 * size_t(hd)) + size_t((in_page & 127) >> 4) * (16 * size_t(hd)) + size_t(d) * 16 + (in_page & 15);
 }
+
+// A code is stored as code + 128 in a byte (offset binary): the scan turns four bytes into fp16 with two byte
+// permutes and two subtractions, without a sign fix.
+__host__ __device__ __forceinline__ int8_t spl_code_byte(float code) { return int8_t(uint8_t(int(code) + 128)); }
+__host__ __device__ __forceinline__ int8_t spl_code_value(int8_t byte) { return int8_t(int(uint8_t(byte)) - 128); }
 
 struct SplAttnParams {
     int rows, live, heads, kv_heads, head_dim, rotary, max_pages;
@@ -90,8 +95,8 @@ spl_attn_prepare_kernel(const float *__restrict__ proj, const uint16_t *__restri
     const size_t vec = size_t(page) * p.kv_heads + head;
     const uint32_t in_page = position % SPL_PAGE_TOKENS;
     for (int n = 0, i = tid; i < hd; i += 128, ++n) {
-        k_codes[spl_k_code_index(vec, in_page, i, hd)] = int8_t(fminf(127.0f, fmaxf(-127.0f, rintf(__fdiv_rn(vals[n], ks)))));
-        v_codes[spl_v_code_index(vec, in_page, i, hd)] = int8_t(fminf(127.0f, fmaxf(-127.0f, rintf(__fdiv_rn(vv[n], vs)))));
+        k_codes[spl_k_code_index(vec, in_page, i, hd)] = spl_code_byte(fminf(127.0f, fmaxf(-127.0f, rintf(__fdiv_rn(vals[n], ks)))));
+        v_codes[spl_v_code_index(vec, in_page, i, hd)] = spl_code_byte(fminf(127.0f, fmaxf(-127.0f, rintf(__fdiv_rn(vv[n], vs)))));
     }
     if (tid == 0) { k_scale[vec * SPL_PAGE_TOKENS + in_page] = ks; v_scale[vec * SPL_PAGE_TOKENS + in_page] = vs; }
 }
@@ -157,13 +162,13 @@ __device__ __forceinline__ float spl_redux_max(float v) {
     asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;\n" : "=f"(m) : "f"(v));
     return m;
 }
-// Sixteen int8 (a 16-byte piece) -> eight registers of fp16 pairs (exact): fp16 0x6400 | u is 1024 + u, u = x + 128.
+// Sixteen stored codes (a 16-byte piece, each byte u = code + 128) -> eight registers of fp16 pairs (exact): fp16 0x6400 | u is 1024 + u.
 __device__ __forceinline__ void spl_s8x16_to_h2x8(const uint4 &piece, uint32_t *out) {
     const __half2 off = __floats2half2_rn(1152.0f, 1152.0f);
     const uint32_t w4[4] = {piece.x, piece.y, piece.z, piece.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-        const uint32_t u = w4[i] ^ 0x80808080u;
+        const uint32_t u = w4[i];
         uint32_t a = __byte_perm(u, 0x64646464u, 0x4140), b = __byte_perm(u, 0x64646464u, 0x4342);
         const __half2 ha = __hsub2(*reinterpret_cast<__half2 *>(&a), off), hb = __hsub2(*reinterpret_cast<__half2 *>(&b), off);
         out[2 * i] = *reinterpret_cast<const uint32_t *>(&ha); out[2 * i + 1] = *reinterpret_cast<const uint32_t *>(&hb);

@@ -871,7 +871,7 @@ spl_status spl_debug_read(spl_engine *e, int32_t which, int32_t index, void *dst
     }
     if (!src || bytes > have) return e->fail(SPL_ERR_INVALID_ARGUMENT, "debug read outside the buffer");
     if (which == 3 || which == 4) {
-        // The code arrays are read out in the plain order [page][kv head][token][channel], whatever the pool's own order is.
+        // The code arrays are read out as signed codes in the plain order [page][kv head][token][channel], whatever the pool's own order and byte form are.
         const int hd = e->g.head_dim;
         std::vector<int8_t> raw(have);
         SPL_CUDA(cudaMemcpy(raw.data(), src, have, cudaMemcpyDeviceToHost));
@@ -879,7 +879,7 @@ spl_status spl_debug_read(spl_engine *e, int32_t which, int32_t index, void *dst
         for (size_t i = 0; i < bytes; ++i) {
             const size_t vec = i / (size_t(SPL_PAGE_TOKENS) * hd), rest = i % (size_t(SPL_PAGE_TOKENS) * hd);
             const uint32_t token = uint32_t(rest / hd); const int d = int(rest % hd);
-            out[i] = raw[which == 3 ? spl_k_code_index(vec, token, d, hd) : spl_v_code_index(vec, token, d, hd)];
+            out[i] = spl_code_value(raw[which == 3 ? spl_k_code_index(vec, token, d, hd) : spl_v_code_index(vec, token, d, hd)]);
         }
         return SPL_OK;
     }

@@ -283,7 +283,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     uint32_t *q_ring = reinterpret_cast<uint32_t *>(w_ring + size_t(CST) * WSTAGE);     // [BST][SUPER][128] scale | bias << 16
     uint64_t *bars = reinterpret_cast<uint64_t *>(q_ring + BST * QSTAGE);
     uint64_t *full_c = bars, *empty_c = full_c + CST, *full_b = empty_c + CST, *empty_b = full_b + BST;
-    uint64_t *full_a = empty_b + BST, *done = full_a + AST / 2, *full_t = done + ASUP, *empty_t = full_t + 2, *finished = empty_t + 2;
+    uint64_t *full_a = empty_b + BST, *full_t = full_a + AST / 2, *empty_t = full_t + 2, *finished = empty_t + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(finished + 1);
 
 #ifdef SPL_TRACE
@@ -305,7 +305,6 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         for (int i = 0; i < CST; ++i) { spl_mbar_init(&full_c[i], 1); spl_mbar_init(&empty_c[i], 8); }       // the two sets (four warps each) that take the stage's units
         for (int i = 0; i < BST; ++i) { spl_mbar_init(&full_b[i], 1); spl_mbar_init(&empty_b[i], 2); }       // the two issuing threads
         for (int i = 0; i < AST / 2; ++i) spl_mbar_init(&full_a[i], 4);      // one per unit of two groups
-        for (int i = 0; i < ASUP; ++i) spl_mbar_init(&done[i], 2);           // one completion per four groups from each issuing thread
         for (int i = 0; i < 2; ++i) { spl_mbar_init(&full_t[i], 1); spl_mbar_init(&empty_t[i], 1); }
         spl_mbar_init(finished, 2);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -408,45 +407,55 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         if (lane == 0) {
             constexpr uint32_t idesc = spl_tc_idesc(RN);
             int mean_tile = -1, mean_loads = 0, mean_slot = 0;
-            for (int un = 0; un < units && ok; ++un) {
-                const int j0 = un / 2, sbq = j0 % BST, au = un % (AST / 2);
+            // The issuing thread is one lane running scalar code, so its instruction count matters: descriptors and
+            // tensor-memory addresses are a base per stage plus compile-time offsets.
+            const uint64_t b_desc0 = spl_tc_desc_sw128(spl_smem_addr(b_ring)), t_desc0 = spl_tc_desc_sw128(spl_smem_addr(t_ring));
+            uint32_t accumulate = 0u;          // the thread's first instructions overwrite its accumulators
+            for (int j0 = 0; j0 < supers && ok; ++j0) {
+                const int sbq = j0 % BST, n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);
+                const uint64_t b_desc = b_desc0 + uint64_t((sbq * BTILE) >> 4);
+                const uint32_t a_base = tmem_a + (j0 % ASUP) * (SPL_TC_SUPER * 32);
                 SPL_T0();
-                if ((un & 1) == 0) ok = spl_mbar_wait(&full_b[sbq], (j0 / BST) & 1);
+                ok = spl_mbar_wait(&full_b[sbq], (j0 / BST) & 1);
                 SPL_T1(t0);
-                ok = ok && spl_mbar_wait(&full_a[au], (un / (AST / 2)) & 1);
-                SPL_T1(t1);
-                if (!ok) break;
-                spl_tc_fence_after();
 #pragma unroll
-                for (int v = 0; v < 2; ++v) {
-                    const int i = 2 * un + v, u = i % SPL_TC_SUPER, sa = i % AST;
-                    if (i >= g_count) break;
-                    const uint32_t b_addr = spl_smem_addr(b_ring + size_t(sbq) * BTILE + u * RN * 128);
+                for (int half = 0; half < 2; ++half) {
+                    if (2 * half >= n) break;
+                    const int un = 2 * j0 + half;
+                    ok = ok && spl_mbar_wait(&full_a[un % (AST / 2)], (un / (AST / 2)) & 1);
+                    SPL_T1(t1);
+                    if (!ok) break;
+                    spl_tc_fence_after();
 #pragma unroll
-                    for (int l = 0; l < 2; ++l) {
-                        const int ks = 2 * m + l;
-                        const int a = NACC == 4 ? ks : m;                       // this thread's accumulator for the step
-                        const uint32_t accumulate = (i > 0 || (NACC == 2 && l > 0)) ? 1u : 0u;
-                        spl_tc_mma_ts(tmem_d + a * RN, tmem_a + sa * 32 + ks * 8, spl_tc_desc_sw128(b_addr + ks * 32), idesc, accumulate);
-                    }
-                }
-                if ((un & 1) == 1 || un == units - 1) {
-                    if (m == 0) {
-                        // The stage's second term: its 16 values of the contraction are a quarter of a 128-byte row of the tile.
-                        const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
-                        const int quarter = g_first / SPL_TC_SUPER + j, want = quarter >> 2;
-                        if (want != mean_tile) {
-                            if (mean_tile >= 0) spl_tc_commit(&empty_t[mean_slot]);      // every instruction that read the old tile has been issued
-                            mean_slot = mean_loads & 1;
-                            ok = spl_mbar_wait(&full_t[mean_slot], (mean_loads >> 1) & 1);
-                            if (!ok) break;
-                            mean_tile = want; ++mean_loads;
+                    for (int v = 0; v < 2; ++v) {
+                        const int u = 2 * half + v;
+                        if (u >= n) break;
+#pragma unroll
+                        for (int l = 0; l < 2; ++l) {
+                            const int ks = 2 * m + l;
+                            const int acc = NACC == 4 ? ks : m;                       // this thread's accumulator for the step
+                            spl_tc_mma_ts(tmem_d + acc * RN, a_base + u * 32 + ks * 8, b_desc + uint64_t((u * RN * 128 + ks * 32) >> 4), idesc,
+                                          (NACC == 2 && l > 0) ? 1u : accumulate);
                         }
-                        spl_tc_mma_ts(tmem_d, tmem_aq + (j0 % ASUP) * 8, spl_tc_desc_sw128(spl_smem_addr(t_ring + mean_slot * TTILE) + (quarter & 3) * 32), idesc, 1u);
+                        accumulate = 1u;
                     }
-                    spl_tc_commit(&done[j0 % ASUP]);              // the stage's A slots may be rewritten
-                    spl_tc_commit(&empty_b[sbq]);                 // its activations have been read
+                    SPL_T1(t2);
                 }
+                if (!ok) break;
+                if (m == 0) {
+                    // The stage's second term: its 16 values of the contraction are a quarter of a 128-byte row of the tile.
+                    const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
+                    const int quarter = g_first / SPL_TC_SUPER + j, want = quarter >> 2;
+                    if (want != mean_tile) {
+                        if (mean_tile >= 0) spl_tc_commit(&empty_t[mean_slot]);      // every instruction that read the old tile has been issued
+                        mean_slot = mean_loads & 1;
+                        ok = spl_mbar_wait(&full_t[mean_slot], (mean_loads >> 1) & 1);
+                        if (!ok) break;
+                        mean_tile = want; ++mean_loads;
+                    }
+                    spl_tc_mma_ts(tmem_d, tmem_aq + (j0 % ASUP) * 8, t_desc0 + uint64_t((mean_slot * TTILE + (quarter & 3) * 32) >> 4), idesc, 1u);
+                }
+                spl_tc_commit(&empty_b[sbq]);                 // the stage's instructions have completed: its activations and its A slots are free
                 SPL_T1(t2);
             }
             SPL_TOUT(if (trace && m == 0) { error_flag[11] = int(t0 / g_count); error_flag[12] = int(t1 / g_count); error_flag[13] = int(t2 / g_count); });
@@ -506,7 +515,8 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                 }
             }
             SPL_T1(t1);
-            if (j >= ASUP) ok = spl_mbar_wait(&done[j % ASUP], ((j / ASUP) & 1) ^ 1);
+            // The A slots were last used ASUP stages ago; that stage's completion is the one its activation stage is freed by.
+            if (j >= ASUP) ok = spl_mbar_wait(&empty_b[(j - ASUP) % BST], ((j - ASUP) / BST) & 1);
             SPL_T1(t2);
             if (!ok) break;
             spl_tc_fence_after();
