@@ -124,6 +124,41 @@ const char *spl_host_last_error(const spl_host *host);
 /* BatchScheduler.accept, greedy branch (Sources/SploshRuntime/BatchScheduler.swift:1583-1587):
  * the agreeing prefix of `drafts` against the block's arg-max ids, and the bonus token. */
 int32_t spl_greedy_accept(const int32_t *argmax_ids, const int32_t *drafts, int32_t draft_count, int32_t *bonus);
+/* ---- Width planner (Sources/SploshRuntime/BatchScheduler.swift:646-669, 735-789) ---------------
+ * How many rows a mixed step may hold (prefillCap) and which speculating sessions get a double block
+ * (planBlocks). The arithmetic is the reference's; its cost table (tierMilliseconds :740, cycleMilliseconds
+ * :743-745, attentionMilliseconds :750, 0.022 :659, 0.88 :779) is an argument: spl_plan_costs_reference fills
+ * in the reference's (M5) figures, spl_plan_costs_b200 this library's measured ones. */
+typedef struct spl_plan_costs {
+    double tier_ms[5];          /* a decode step of up to 16, 32, 64, 96, 128 rows */
+    double beyond_ms_per_row;   /* per row past the last tier */
+    double per_row_ms, fixed_ms;/* the rest of a cycle: per row, and fixed */
+    double attention_first, attention_second;   /* ms per thousand context tokens: a block's first and second eight rows */
+    double prefill_attention;   /* ms per prefill row and thousand tokens of its prompt's context */
+    double tier_margin;         /* a plan that crosses a tier keeps this fraction of its rate */
+} spl_plan_costs;
+void spl_plan_costs_reference(spl_plan_costs *costs);
+void spl_plan_costs_b200(spl_plan_costs *costs);
+int32_t spl_plan_tier(int32_t rows);
+double spl_plan_cycle_ms(const spl_plan_costs *costs, int32_t rows);
+int32_t spl_plan_prefill_cap(const spl_plan_costs *costs, int32_t max_rows, int32_t decode_rows, double decode_tokens, double decode_attention_ms,
+                             double decode_weight, int32_t backlog, int32_t first_fed, int32_t prefill_rows_while_decoding);
+int32_t spl_plan_blocks(const spl_plan_costs *costs, int32_t sessions, const double *tail, const double *block_yield, const int32_t *context_tokens,
+                        int32_t other_rows, int32_t block, int32_t max_rows, int32_t max_logit_rows, int32_t max_verify_rows, int32_t max_context,
+                        int32_t *blocks_out);
+/* Sampler (Sources/SploshRuntime/Sampler.swift:68-156), the part after the k largest logits are known
+ * (spl_topk gives them): `state` is the sampler's SplitMix64 state, advanced by every draw.
+ *   spl_sampler_uniform     Sampler.uniform01 (:79-90)
+ *   spl_sample_topk         Sampler.sample (:128-156): temperature softmax over the k values, the smallest
+ *                           prefix reaching top_p, one draw; temperature <= 0 returns ids[0]
+ *   spl_sampler_distribution Sampler.distribution (:100-116): writes the kept candidates' renormalised
+ *                           probabilities, returns how many are kept
+ *   spl_speculative_resolve SpeculativeSampling.resolve (:163-179): -1 when the draft is kept, else its replacement */
+float spl_sampler_uniform(uint64_t *state);
+int32_t spl_sample_topk(const int32_t *ids, const float *values, int32_t k, float temperature, float top_p, uint64_t *state);
+int32_t spl_sampler_distribution(const float *values, int32_t k, float temperature, float top_p, float *probabilities);
+int32_t spl_speculative_resolve(int32_t draft, const int32_t *candidates, const float *draft_probabilities, int32_t candidate_count,
+                                const int32_t *target_ids, const float *target_probabilities, int32_t target_count, uint64_t *state);
 
 /* ---- Engine ------------------------------------------------------------------------------- */
 typedef struct spl_engine spl_engine;
@@ -156,6 +191,10 @@ spl_status spl_logits_row(spl_engine *engine, int32_t index, float *dst);
 /* Sampler.argmax over [0, vocab_limit) for every logit row of the last step, on the device
  * (Sources/SploshRuntime/Sampler.swift:11-16, 94-96): the first index of the maximum. */
 spl_status spl_argmax(spl_engine *engine, int32_t vocab_limit, int32_t *ids);
+/* TopK.select (Sampler.swift:19-52) for every logit row of the last step: the k <= 64 largest of [0, vocab_limit) in
+ * descending order, the lower index first among equal values; ids and values [logit rows][k] on the host. Rows with
+ * fewer than k values above -inf end in (0, -inf) entries, as the reference's untouched slots do. */
+spl_status spl_topk(spl_engine *engine, int32_t vocab_limit, int32_t k, int32_t *ids, float *values);
 spl_status spl_slot_reset(spl_engine *engine, int32_t slot);                                  /* Engine.resetSlot */
 spl_status spl_verify_discard(spl_engine *engine, int32_t slot);                              /* Engine.discardVerify */
 spl_status spl_verify_accept(spl_engine *engine, int32_t slot, int32_t rows, int32_t token_count); /* Engine.acceptVerify */
@@ -181,6 +220,19 @@ spl_status spl_debug_fill_state(spl_engine *engine, int32_t slot, uint64_t seed)
  * codes [page][kv head][256][head_dim] (V codes are stored [page][kv head][head_dim][256]). */
 spl_status spl_debug_read(spl_engine *engine, int32_t which, int32_t index, void *dst, size_t bytes);
 spl_status spl_debug_taps(spl_engine *engine, int32_t enabled);
+
+/* ---- Drafter feature taps ------------------------------------------------------------------
+ * step(_:captureFeatures:) and featureRow(_:) (Engine.swift:1316, 1309-1313; taps at
+ * Engine.featureLayers = [5, 19, 33, 47, 61], Engine.swift:331, copied by sp_copy_rows :1488-1497):
+ * while enabled, every step leaves the residual stream after each listed block as
+ * [row][tap][hidden] fp32. `layers` null with count > 0 selects the reference's list; blocks the
+ * geometry does not have are left out; count 0 disables. The last block is computed for the rows
+ * that want logits only, so a tap on it holds those rows (the reference keeps every row there). */
+spl_status spl_features_enable(spl_engine *engine, const int32_t *layers, int32_t count);
+/* Floats of one row: taps in use x hidden. */
+int32_t spl_feature_width(const spl_engine *engine);
+/* Engine.featureRow: the taps of row `row` of the last step, copied to the host. */
+spl_status spl_feature_row(spl_engine *engine, int32_t row, float *dst);
 /* Per-kernel-class device time of the last step when enabled (events around every launch; slow). */
 spl_status spl_debug_profile(spl_engine *engine, int32_t enabled);
 /* class: 0 q4 gemm, 1 norms and elementwise, 2 gated-delta, 3 attention, 4 head/argmax/other.

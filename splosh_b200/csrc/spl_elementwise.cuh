@@ -148,6 +148,54 @@ spl_argmax_kernel(const float *__restrict__ logits, int ld, int limit, int32_t *
     }
 }
 
+// The k largest of [0, limit) per logit row in descending order, the lower index first among equal values
+// (TopK.select, Sampler.swift:19-52). k rounds of a block-wide selection: round r takes the best element that comes
+// strictly after the previous pick in the order (value descending, index ascending); the row stays in L2 between rounds.
+// Grid (rows), 1024 threads; ids and values [rows][k].
+__global__ void __launch_bounds__(1024)
+spl_topk_kernel(const float *__restrict__ logits, int ld, int limit, int k, int32_t *ids, float *values) {
+    __shared__ float best_v[32];
+    __shared__ int best_i[32];
+    __shared__ float pick_v;
+    __shared__ int pick_i;
+    const float *x = logits + size_t(blockIdx.x) * ld;
+    float last_v = INFINITY; int last_i = -1;
+    for (int round = 0; round < k; ++round) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int i = threadIdx.x; i < limit; i += blockDim.x) {
+            const float v = x[i];
+            const bool after = v < last_v || (v == last_v && i > last_i);          // not taken in an earlier round (NaNs never qualify)
+            if (after && v > -INFINITY && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if ((threadIdx.x & 31) == 0) { best_v[threadIdx.x >> 5] = bv; best_i[threadIdx.x >> 5] = bi; }
+        __syncthreads();
+        if (threadIdx.x < 32) {
+            bv = best_v[threadIdx.x]; bi = best_i[threadIdx.x];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            if (threadIdx.x == 0) {
+                // Fewer than k selectable values (a short row, NaNs, -inf): the reference's untouched slots, id 0 at -inf.
+                const bool none = bi == 0x7fffffff;
+                pick_v = none ? -INFINITY : bv; pick_i = none ? -1 : bi;
+                ids[size_t(blockIdx.x) * k + round] = none ? 0 : bi; values[size_t(blockIdx.x) * k + round] = pick_v;
+            }
+        }
+        __syncthreads();
+        if (pick_i < 0) { last_v = -INFINITY; last_i = 0x7ffffffe; } else { last_v = pick_v; last_i = pick_i; }
+        __syncthreads();
+    }
+}
+
 // Fill helpers for synthetic contexts.
 __global__ void spl_fill_codes_kernel(uint64_t *words, size_t count, uint64_t seed) {
     for (size_t idx = blockIdx.x * size_t(blockDim.x) + threadIdx.x; idx < count; idx += size_t(gridDim.x) * blockDim.x)

@@ -58,6 +58,10 @@ struct spl_engine {
     float *xn_sums = nullptr, *core_sums = nullptr, *act_sums = nullptr, *hsn_sums = nullptr;
     int rows_padded = 0, logit_rows_padded = 0;
     int *tc_error = nullptr;
+    // Drafter feature taps (Engine.swift:330-331, 1488-1497): the residual stream after the listed blocks, [row][tap][hidden].
+    float *features = nullptr;
+    std::vector<int> feature_layers;
+    int32_t *topk_ids = nullptr; float *topk_values = nullptr;      // allocated by the first spl_topk
     __half *q = nullptr;
     int32_t *argmax_ids = nullptr;
     int proj_ld = 0, gate_up_ld = 0, core_ld = 0, logits_ld = 0;
@@ -303,6 +307,8 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
     for (int l = 0; l < g.layers; ++l) {
         const LayerWeights &L = e->layers[l];
         const int live = (l + 1 == g.layers) ? int(t->live_rows) : R;
+        int feature_tap = -1;
+        for (size_t f = 0; f < e->feature_layers.size(); ++f) if (e->feature_layers[f] == l) feature_tap = int(f);
         profile_begin(e, KLASS_ELEMENTWISE, 0);
         norm(R, L.vec[SPL_VEC_INPUT_NORM], nullptr, xn, carried);
         carried = PendingReduce();
@@ -361,10 +367,15 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
             profile_end(e);
             // The down projection's reduction is left to the next block's input norm, except after the last block (the final
             // norm gathers rows) and when the residual stream is tapped after every block.
-            const bool leave = l + 1 < g.layers && !e->taps_enabled && live == R;
+            const bool leave = l + 1 < g.layers && !e->taps_enabled && feature_tap < 0 && live == R;
             launch_gemm(e, L.down, gact, e->h, e->h, live, leave ? &carried : nullptr);
         }
         if (e->taps_enabled) SPL_CUDA(cudaMemcpyAsync(e->taps + size_t(l) * e->c.max_rows * H, e->h, size_t(R) * H * 4, cudaMemcpyDeviceToDevice, e->stream));
+        if (feature_tap >= 0) {
+            const size_t width = e->feature_layers.size() * size_t(H);
+            SPL_CUDA(cudaMemcpy2DAsync(e->features + size_t(feature_tap) * H, width * 4, e->h, size_t(H) * 4, size_t(H) * 4, live,
+                                       cudaMemcpyDeviceToDevice, e->stream));
+        }
     }
     if (t->logit_rows > 0) {
         profile_begin(e, KLASS_OTHER, 0);
@@ -616,7 +627,7 @@ void spl_engine_destroy(spl_engine *e) {
     for (auto p : e->state) cudaFree(p); for (auto p : e->conv) cudaFree(p); for (auto p : e->journal) cudaFree(p);
     cudaFree(e->h); cudaFree(e->xn); cudaFree(e->proj); cudaFree(e->gdn_act); cudaFree(e->core); cudaFree(e->gate_up); cudaFree(e->act);
     cudaFree(e->q); cudaFree(e->hsn); cudaFree(e->logits); cudaFree(e->argmax_ids); cudaFree(e->partials); cudaFree(e->attn_partials);
-    cudaFree(e->taps); cudaFree(e->tables_dev); cudaFree(e->xn_sums); cudaFree(e->core_sums); cudaFree(e->act_sums); cudaFree(e->hsn_sums); cudaFree(e->tc_error);
+    cudaFree(e->taps); cudaFree(e->features); cudaFree(e->topk_ids); cudaFree(e->topk_values); cudaFree(e->tables_dev); cudaFree(e->xn_sums); cudaFree(e->core_sums); cudaFree(e->act_sums); cudaFree(e->hsn_sums); cudaFree(e->tc_error);
     if (e->tables_host) cudaFreeHost(e->tables_host);
     for (ProfileSlot &s : e->profile_slots) { cudaEventDestroy(s.begin); cudaEventDestroy(s.end); }
     if (e->ev_begin) cudaEventDestroy(e->ev_begin);
@@ -750,6 +761,24 @@ spl_status spl_argmax(spl_engine *e, int32_t vocab_limit, int32_t *ids) {
     return SPL_OK;
 }
 
+spl_status spl_topk(spl_engine *e, int32_t vocab_limit, int32_t k, int32_t *ids, float *values) {
+    if (!e || !ids || !values || vocab_limit <= 0 || vocab_limit > e->g.vocab || k < 1 || k > 64 || k > vocab_limit) return SPL_ERR_INVALID_ARGUMENT;
+    if (e->last_logit_rows == 0) return SPL_OK;
+    SPL_CUDA(cudaSetDevice(e->device));
+    const size_t cells = size_t(e->host->config.max_logit_rows) * 64;
+    if (!e->topk_ids) {
+        SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&e->topk_ids), cells * 4));
+        SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&e->topk_values), cells * 4));
+    }
+    spl_topk_kernel<<<e->last_logit_rows, 1024, 0, e->stream>>>(e->logits, e->logits_ld, vocab_limit, k, e->topk_ids, e->topk_values);
+    const spl_status launched = check_launch(e, "top-k");
+    if (launched != SPL_OK) return launched;
+    SPL_CUDA(cudaMemcpyAsync(ids, e->topk_ids, size_t(e->last_logit_rows) * k * 4, cudaMemcpyDeviceToHost, e->stream));
+    SPL_CUDA(cudaMemcpyAsync(values, e->topk_values, size_t(e->last_logit_rows) * k * 4, cudaMemcpyDeviceToHost, e->stream));
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    return SPL_OK;
+}
+
 spl_status spl_slot_reset(spl_engine *e, int32_t slot) {
     if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
     SPL_CUDA(cudaSetDevice(e->device));
@@ -831,6 +860,39 @@ spl_status spl_debug_taps(spl_engine *e, int32_t enabled) {
     SPL_CUDA(cudaSetDevice(e->device));
     if (enabled && !e->taps) SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&e->taps), size_t(e->g.layers) * e->c.max_rows * e->g.hidden * 4));
     e->taps_enabled = enabled != 0;
+    return SPL_OK;
+}
+
+spl_status spl_features_enable(spl_engine *e, const int32_t *layers, int32_t count) {
+    if (!e || count < 0 || count > 16) return SPL_ERR_INVALID_ARGUMENT;
+    static const int32_t reference_layers[5] = {5, 19, 33, 47, 61};
+    if (count > 0 && !layers) { layers = reference_layers; count = 5; }
+    std::vector<int> wanted;
+    for (int i = 0; i < count; ++i) {
+        if (layers[i] < 0) return e->fail(SPL_ERR_INVALID_ARGUMENT, "feature layer below zero");
+        if (layers[i] < e->g.layers) wanted.push_back(layers[i]);      // taps of blocks this geometry does not have are left out
+    }
+    SPL_CUDA(cudaSetDevice(e->device));
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    if (e->features) { cudaFree(e->features); e->features = nullptr; }
+    e->feature_layers = wanted;
+    if (!wanted.empty()) {
+        const size_t bytes = size_t(e->c.max_rows) * wanted.size() * e->g.hidden * 4;
+        SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&e->features), bytes));
+        SPL_CUDA(cudaMemsetAsync(e->features, 0, bytes, e->stream));
+    }
+    return SPL_OK;
+}
+
+int32_t spl_feature_width(const spl_engine *e) { return e ? int32_t(e->feature_layers.size()) * e->g.hidden : 0; }
+
+spl_status spl_feature_row(spl_engine *e, int32_t row, float *dst) {
+    if (!e || !dst) return SPL_ERR_INVALID_ARGUMENT;
+    if (!e->features) return e->fail(SPL_ERR_INVALID_ARGUMENT, "feature taps are not enabled");
+    if (row < 0 || row >= e->last_rows) return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: no such row in the last step");
+    SPL_CUDA(cudaSetDevice(e->device));
+    const size_t width = e->feature_layers.size() * size_t(e->g.hidden);
+    SPL_CUDA(cudaMemcpy(dst, e->features + size_t(row) * width, width * 4, cudaMemcpyDeviceToHost));
     return SPL_OK;
 }
 

@@ -7,6 +7,8 @@
 // pages are reused last-in first-out; slot i starts on state unit i and speculative rows take
 // fresh units from max_slots upward.
 #include "spl_host.h"
+#include <cmath>
+#include <algorithm>
 
 #include <algorithm>
 #include <cstdio>
@@ -213,6 +215,156 @@ int32_t spl_greedy_accept(const int32_t *argmax_ids, const int32_t *drafts, int3
     while (agreed < draft_count && argmax_ids[agreed] == drafts[agreed]) ++agreed;
     if (bonus) *bonus = argmax_ids[agreed];
     return agreed;
+}
+
+// ---- width planner (BatchScheduler.swift:646-669, 735-789) -----------------------------------------
+// The algorithm is the reference's; its cost table is a property of the machine, so it is an argument.
+void spl_plan_costs_reference(spl_plan_costs *c) {
+    if (!c) return;
+    const double tiers[5] = {62, 86, 165, 230, 295};                    // tierMilliseconds, BatchScheduler.swift:740
+    for (int i = 0; i < 5; ++i) c->tier_ms[i] = tiers[i];
+    c->beyond_ms_per_row = 2.3; c->per_row_ms = 0.45; c->fixed_ms = 10;  // cycleMilliseconds, :743-745
+    c->attention_first = 0.29; c->attention_second = 0.22;              // attentionMilliseconds, :750
+    c->prefill_attention = 0.022;                                       // per row and thousand tokens, :659
+    c->tier_margin = 0.88;                                              // :779
+}
+// The same table measured with this library on a B200 (27B shape, MLX 4-bit): steps of 16..128 rows at short context
+// for the tiers, 64-row steps at 1K and 40K context for attention. Draft pass and CPU work are the caller's to add.
+void spl_plan_costs_b200(spl_plan_costs *c) {
+    if (!c) return;
+    const double tiers[5] = {11.0, 11.6, 12.9, 23.0, 25.0};
+    for (int i = 0; i < 5; ++i) c->tier_ms[i] = tiers[i];
+    c->beyond_ms_per_row = 0.2; c->per_row_ms = 0.0; c->fixed_ms = 0.5;
+    c->attention_first = 0.0078; c->attention_second = 0.0078;
+    c->prefill_attention = 0.001;
+    c->tier_margin = 0.88;
+}
+int32_t spl_plan_tier(int32_t rows) { return rows <= 16 ? 16 : ((rows + 31) / 32) * 32; }
+double spl_plan_cycle_ms(const spl_plan_costs *c, int32_t rows) {
+    const int tier = spl_plan_tier(rows);
+    const int index = tier == 16 ? 0 : tier / 32;
+    const double step = index <= 4 ? c->tier_ms[index] : double(rows) * c->beyond_ms_per_row;
+    return step + c->per_row_ms * double(rows) + c->fixed_ms;
+}
+// prefillCap: the width (16, 32, 64, 96, 128) that makes the most progress per millisecond, a generated token counting
+// as `decode_weight` prompt tokens. backlog = prompt tokens still to feed; first_fed = tokens already fed of the prompt
+// with least left.
+int32_t spl_plan_prefill_cap(const spl_plan_costs *c, int32_t max_rows, int32_t decode_rows, double decode_tokens, double decode_attention_ms,
+                             double decode_weight, int32_t backlog, int32_t first_fed, int32_t prefill_rows_while_decoding) {
+    if (backlog <= 0) return decode_rows;
+    const double per_row = c->prefill_attention * double(first_fed) / 1000.0;
+    int32_t best_cap = std::min(max_rows, spl_plan_tier(decode_rows + prefill_rows_while_decoding));
+    double best_rate = 0.0;
+    const int widths[5] = {16, 32, 64, 96, 128};
+    for (int width : widths) {
+        if (!(width <= max_rows && width > decode_rows)) continue;
+        const int prefill = std::min(backlog, width - decode_rows);
+        const double ms = spl_plan_cycle_ms(c, decode_rows + prefill) + decode_attention_ms + per_row * double(prefill);
+        const double rate = (decode_weight * decode_tokens + double(prefill)) / ms;
+        if (rate > best_rate) { best_cap = width; best_rate = rate; }
+    }
+    return best_cap;
+}
+// planBlocks: which speculating sessions get a double block. Per session: tail = wholeRate * tailYield and block_yield
+// (SpeculationState.BlockStats, LookupIndex.swift:175-183), context_tokens. blocks_out[i] = block or 2 * block; returns
+// how many were doubled.
+int32_t spl_plan_blocks(const spl_plan_costs *c, int32_t sessions, const double *tail, const double *block_yield, const int32_t *context_tokens,
+                        int32_t other_rows, int32_t block, int32_t max_rows, int32_t max_logit_rows, int32_t max_verify_rows, int32_t max_context,
+                        int32_t *blocks_out) {
+    for (int i = 0; i < sessions; ++i) blocks_out[i] = block;
+    const int base = sessions * block + other_rows;
+    auto thousands = [&](int i) { return double(context_tokens[i]) / 1000.0; };
+    auto tail_cost = [&](int i) { return c->per_row_ms * double(block) + c->attention_second * thousands(i); };      // 0.45 per row in the reference, its cycle's per-row cost
+    std::vector<int> candidates;
+    for (int i = 0; i < sessions; ++i) if (context_tokens[i] + 2 * block < max_context) candidates.push_back(i);
+    std::stable_sort(candidates.begin(), candidates.end(), [&](int a, int b) { return tail[a] / tail_cost(a) > tail[b] / tail_cost(b); });
+    double tokens = double(other_rows), attention = 0.0;
+    for (int i = 0; i < sessions; ++i) { tokens += block_yield[i]; attention += c->attention_first * thousands(i); }
+    int best_count = 0;
+    double best_rate = tokens / (spl_plan_cycle_ms(c, base) + attention);
+    for (size_t index = 0; index < candidates.size(); ++index) {
+        const int rows = base + int(index + 1) * block;
+        if (!(rows <= max_rows && rows <= max_logit_rows && (sessions + int(index) + 1) * block <= max_verify_rows)) break;
+        tokens += tail[candidates[index]];
+        attention += c->attention_second * thousands(candidates[index]);
+        const double rate = tokens / (spl_plan_cycle_ms(c, rows) + attention) * (spl_plan_tier(rows) == spl_plan_tier(base) ? 1.0 : c->tier_margin);
+        if (rate > best_rate) { best_count = int(index) + 1; best_rate = rate; }
+    }
+    for (int i = 0; i < best_count; ++i) blocks_out[candidates[i]] = 2 * block;
+    return best_count;
+}
+
+// ---- sampling from the k largest logits (Sampler.swift:68-156) -----------------------------------
+// The generator is SplitMix64 kept in `*state`; one uniform = the top 24 bits of an output over 2^24.
+static float sampler_uniform(uint64_t *state) {
+    *state += 0x9E3779B97F4A7C15ull;
+    uint64_t z = *state;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    z ^= z >> 31;
+    return float(z >> 40) / float(1 << 24);
+}
+
+float spl_sampler_uniform(uint64_t *state) { return state ? sampler_uniform(state) : 0.0f; }
+
+// Sampler.sample after TopK.select: ids/values are the k largest logits in descending order. Temperature softmax over
+// them, the smallest prefix whose mass reaches top_p, one uniform draw scaled by the kept mass (Sampler.swift:128-156).
+int32_t spl_sample_topk(const int32_t *ids, const float *values, int32_t k, float temperature, float top_p, uint64_t *state) {
+    if (!ids || !values || k < 1 || !state) return -1;
+    if (temperature <= 0.0f) return ids[0];
+    std::vector<float> probabilities(k);
+    const float top = values[0];
+    float total = 0.0f;
+    for (int i = 0; i < k; ++i) { probabilities[i] = expf((values[i] - top) / temperature); total += probabilities[i]; }
+    for (int i = 0; i < k; ++i) probabilities[i] /= total;
+    int kept = k;
+    if (top_p < 1.0f) {
+        float mass = 0.0f;
+        for (int i = 0; i < k; ++i) { mass += probabilities[i]; if (mass >= top_p) { kept = i + 1; break; } }
+    }
+    float kept_mass = 0.0f;
+    for (int i = 0; i < kept; ++i) kept_mass += probabilities[i];
+    float draw = sampler_uniform(state) * kept_mass;
+    for (int i = 0; i < kept; ++i) { draw -= probabilities[i]; if (draw <= 0.0f) return ids[i]; }
+    return ids[kept - 1];
+}
+
+// Sampler.distribution (Sampler.swift:100-116): probabilities over the kept candidates, renormalised; returns how many are kept.
+int32_t spl_sampler_distribution(const float *values, int32_t k, float temperature, float top_p, float *probabilities) {
+    if (!values || !probabilities || k < 1) return 0;
+    const float top = values[0], t = temperature > 1e-6f ? temperature : 1e-6f;
+    float total = 0.0f;
+    for (int i = 0; i < k; ++i) { probabilities[i] = expf((values[i] - top) / t); total += probabilities[i]; }
+    for (int i = 0; i < k; ++i) probabilities[i] /= total;
+    int kept = k;
+    if (top_p < 1.0f) {
+        float mass = 0.0f;
+        for (int i = 0; i < k; ++i) { mass += probabilities[i]; if (mass >= top_p) { kept = i + 1; break; } }
+    }
+    total = 0.0f;
+    for (int i = 0; i < kept; ++i) total += probabilities[i];
+    for (int i = 0; i < kept; ++i) probabilities[i] /= total;
+    return kept;
+}
+
+// SpeculativeSampling.resolve (Sampler.swift:163-179): -1 when the draft token is kept, else the token that replaces it.
+int32_t spl_speculative_resolve(int32_t draft, const int32_t *candidates, const float *draft_probabilities, int32_t candidate_count,
+                                const int32_t *target_ids, const float *target_probabilities, int32_t target_count, uint64_t *state) {
+    if (!candidates || !draft_probabilities || !target_ids || !target_probabilities || !state || target_count < 1) return -2;
+    float q = 0.0f, p = 0.0f;
+    for (int i = 0; i < candidate_count; ++i) if (candidates[i] == draft) { q = draft_probabilities[i]; break; }
+    for (int i = 0; i < target_count; ++i) if (target_ids[i] == draft) { p = target_probabilities[i]; break; }
+    if (sampler_uniform(state) * q < p) return -1;
+    std::vector<float> residual(target_probabilities, target_probabilities + target_count);
+    for (int slot = 0; slot < target_count; ++slot)
+        for (int c = 0; c < candidate_count; ++c)
+            if (candidates[c] == target_ids[slot]) { residual[slot] = std::max(0.0f, residual[slot] - draft_probabilities[c]); break; }
+    float total = 0.0f;
+    for (float r : residual) total += r;
+    if (total > 0.0f) { for (float &r : residual) r /= total; } else { residual.assign(target_probabilities, target_probabilities + target_count); }
+    float remaining = sampler_uniform(state);
+    for (int i = 0; i < target_count; ++i) { remaining -= residual[i]; if (remaining <= 0.0f) return target_ids[i]; }
+    return target_ids[target_count - 1];
 }
 
 }  // extern "C"

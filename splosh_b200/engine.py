@@ -161,6 +161,20 @@ def lib():
             "spl_debug_fill_state": (i32, [vp, i32, u64]),
             "spl_debug_read": (i32, [vp, i32, i32, vp, C.c_size_t]),
             "spl_debug_taps": (i32, [vp, i32]),
+            "spl_plan_costs_reference": (None, [vp]),
+            "spl_plan_costs_b200": (None, [vp]),
+            "spl_plan_tier": (i32, [i32]),
+            "spl_plan_cycle_ms": (C.c_double, [vp, i32]),
+            "spl_plan_prefill_cap": (i32, [vp, i32, i32, C.c_double, C.c_double, C.c_double, i32, i32, i32]),
+            "spl_plan_blocks": (i32, [vp, i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp]),
+            "spl_topk": (i32, [vp, i32, i32, vp, vp]),
+            "spl_sampler_uniform": (C.c_float, [vp]),
+            "spl_sample_topk": (i32, [vp, vp, i32, C.c_float, C.c_float, vp]),
+            "spl_sampler_distribution": (i32, [vp, i32, C.c_float, C.c_float, vp]),
+            "spl_speculative_resolve": (i32, [i32, vp, vp, i32, vp, vp, i32, vp]),
+            "spl_features_enable": (i32, [vp, vp, i32]),
+            "spl_feature_width": (i32, [vp]),
+            "spl_feature_row": (i32, [vp, i32, vp]),
             "spl_debug_profile": (i32, [vp, i32]),
             "spl_debug_profile_read": (i32, [vp, i32, C.POINTER(C.c_double), C.POINTER(C.c_int64), C.POINTER(C.c_double)]),
             "spl_op_gemm_q4": (i32, [i32, vp, vp, vp, i32, i32, vp, i32, vp, vp]),
@@ -261,6 +275,67 @@ class Host:
 
     def journal_pending(self, slot):
         return lib().spl_host_journal_pending(self.handle, slot)
+
+
+class PlanCosts(C.Structure):
+    """spl_plan_costs: the width planner's cost table (BatchScheduler.swift:740-750)."""
+    _fields_ = [("tier_ms", C.c_double * 5), ("beyond_ms_per_row", C.c_double), ("per_row_ms", C.c_double), ("fixed_ms", C.c_double),
+                ("attention_first", C.c_double), ("attention_second", C.c_double), ("prefill_attention", C.c_double), ("tier_margin", C.c_double)]
+
+
+class Planner:
+    """prefillCap and planBlocks (BatchScheduler.swift:646-669, 751-789) over a cost table: the reference's or this
+    library's measured one."""
+
+    def __init__(self, costs="b200"):
+        self.costs = PlanCosts()
+        (lib().spl_plan_costs_reference if costs == "reference" else lib().spl_plan_costs_b200)(C.byref(self.costs))
+
+    @staticmethod
+    def tier(rows):
+        return lib().spl_plan_tier(rows)
+
+    def cycle_ms(self, rows):
+        return lib().spl_plan_cycle_ms(C.byref(self.costs), rows)
+
+    def prefill_cap(self, max_rows, decode_rows, decode_tokens, decode_attention_ms, backlog, first_fed, decode_weight=1.0, prefill_rows_while_decoding=8):
+        return lib().spl_plan_prefill_cap(C.byref(self.costs), max_rows, decode_rows, decode_tokens, decode_attention_ms, decode_weight,
+                                          backlog, first_fed, prefill_rows_while_decoding)
+
+    def blocks(self, tail, block_yield, context_tokens, other_rows=0, block=8, max_rows=128, max_logit_rows=128, max_verify_rows=64, max_context=262144):
+        t = np.ascontiguousarray(tail, np.float64); y = np.ascontiguousarray(block_yield, np.float64); c = np.ascontiguousarray(context_tokens, np.int32)
+        out = np.zeros(len(t), np.int32)
+        lib().spl_plan_blocks(C.byref(self.costs), len(t), _ptr(t), _ptr(y), _ptr(c), other_rows, block, max_rows, max_logit_rows, max_verify_rows,
+                              max_context, _ptr(out))
+        return [int(x) for x in out]
+
+
+class Sampler:
+    """Sampler (Sampler.swift:68-156) over the k largest logits that `Engine.topk` returns; the state is SplitMix64."""
+
+    def __init__(self, temperature=1.0, top_p=0.95, top_k=20, seed=1):
+        self.temperature, self.top_p, self.top_k = float(temperature), float(top_p), int(top_k)
+        self.state = C.c_uint64(seed)
+
+    def uniform01(self):
+        return float(lib().spl_sampler_uniform(C.byref(self.state)))
+
+    def sample(self, ids, values):
+        ids = np.ascontiguousarray(ids, np.int32); values = np.ascontiguousarray(values, np.float32)
+        return int(lib().spl_sample_topk(_ptr(ids), _ptr(values), len(ids), self.temperature, self.top_p, C.byref(self.state)))
+
+    def distribution(self, ids, values):
+        values = np.ascontiguousarray(values, np.float32)
+        out = np.empty(len(values), np.float32)
+        kept = lib().spl_sampler_distribution(_ptr(values), len(values), self.temperature, self.top_p, _ptr(out))
+        return list(np.asarray(ids)[:kept]), out[:kept]
+
+    def resolve(self, draft, candidates, draft_probabilities, target_ids, target_probabilities):
+        """SpeculativeSampling.resolve (Sampler.swift:163-179): None when the draft is kept, else its replacement."""
+        c = np.ascontiguousarray(candidates, np.int32); q = np.ascontiguousarray(draft_probabilities, np.float32)
+        t = np.ascontiguousarray(target_ids, np.int32); pr = np.ascontiguousarray(target_probabilities, np.float32)
+        out = lib().spl_speculative_resolve(int(draft), _ptr(c), _ptr(q), len(c), _ptr(t), _ptr(pr), len(t), C.byref(self.state))
+        return None if out == -1 else int(out)
 
 
 def greedy_accept(argmax_ids, drafts):
@@ -383,6 +458,30 @@ class Engine:
 
     def debug_fill_state(self, slot, seed):
         self._check(lib().spl_debug_fill_state(self.handle, slot, seed))
+
+    def topk(self, k=20, vocab_limit=None):
+        """TopK.select (Sampler.swift:19-52) over every logit row of the last step: (ids, values), each [rows][k]."""
+        n = max(self.last_logit_rows, 1)
+        ids = np.zeros((n, k), np.int32); values = np.zeros((n, k), np.float32)
+        self._check(lib().spl_topk(self.handle, vocab_limit or self.g.vocab, k, _ptr(ids), _ptr(values)))
+        return ids[:self.last_logit_rows], values[:self.last_logit_rows]
+
+    def enable_features(self, layers=None, enabled=True):
+        """Engine.step(captureFeatures:) (Engine.swift:1316): keep the residual stream after the listed blocks
+        (default Engine.featureLayers, Engine.swift:331) for `feature_row`."""
+        if not enabled:
+            self._check(lib().spl_features_enable(self.handle, None, 0))
+        elif layers is None:
+            self._check(lib().spl_features_enable(self.handle, None, 5))
+        else:
+            arr = np.ascontiguousarray(layers, np.int32)
+            self._check(lib().spl_features_enable(self.handle, _ptr(arr), len(arr)))
+
+    def feature_row(self, row):
+        """Engine.featureRow (Engine.swift:1309-1313): taps x hidden floats of one row of the last step."""
+        out = np.empty(lib().spl_feature_width(self.handle), np.float32)
+        self._check(lib().spl_feature_row(self.handle, row, _ptr(out)))
+        return out
 
     def debug_taps(self, enabled=True):
         self._check(lib().spl_debug_taps(self.handle, int(enabled)))

@@ -286,3 +286,54 @@ def test_27b_shape_slice_and_device_generated_weights(toks):
     # Contractions of 5,120 to 17,408 instead of 1,024 to 2,816 and wider logits: the same kind of
     # bound is 1e-1 here.
     check(gl, ol, g.vocab, "27B-shape slice", tol=1e-1)
+
+
+def test_drafter_feature_taps_against_the_oracles_residual_stream(toks):
+    """Engine.step(captureFeatures:) / featureRow (Engine.swift:1309-1316, 1488-1497): the residual stream after the tapped
+    blocks, [row][tap][hidden]. Tiny model, taps after blocks 0 and 2 (the reference's list 5, 19, ... needs 62 blocks:
+    asking for it here leaves every tap out); a packed step of a verify block and a prompt chunk."""
+    g = S.tiny_geometry()
+    pair = Pair(g, S.EngineConfig(max_slots=2, max_rows=64, kv_pages=8, max_context=1024))
+    pair.engine.enable_features([0, 2, 77])          # block 77 does not exist and is left out
+    rows = [S.EngineRow(0, toks[i], i, True, True) for i in range(5)] + [S.EngineRow(1, toks[100 + i], i, i == 19) for i in range(20)]
+    pair.step(rows)
+    _, _, _, otaps = Pair.step(pair, [S.EngineRow(0, toks[5 + i], 5 + i, True, True) for i in range(4)], taps=True)
+    width = 2 * g.hidden
+    for r in range(4):
+        row = pair.engine.feature_row(r)
+        assert row.shape == (width,) and not np.isnan(row).any()
+        for tap, layer in enumerate((0, 2)):
+            want = otaps[layer][r]
+            assert np.abs(row[tap * g.hidden:(tap + 1) * g.hidden] - want).max() <= 2e-2 * max(1.0, np.abs(want).max()), (r, layer)
+    with pytest.raises(S.EngineError):
+        pair.engine.feature_row(4)
+    pair.engine.enable_features(None)               # the reference's taps: none of them exists in a 4-block model
+    assert pair.engine.feature_row.__self__ is pair.engine
+    with pytest.raises(S.EngineError):
+        pair.engine.feature_row(0)
+    pair.engine.enable_features(enabled=False)
+
+
+def test_topk_on_the_device_and_sampling_from_it(toks):
+    """TopK.select (Sampler.swift:19-52) on the device for every logit row, bit for bit against the restated selection over
+    the same logits (values and ids, ties by lower index, the vocabulary limit); then Sampler.sample over those
+    candidates draws the tokens the restated sampler draws."""
+    from oracle import sampler as OS
+    g = S.tiny_geometry()
+    engine = S.Engine(g, S.EngineConfig(max_slots=2, max_rows=32, kv_pages=4, max_context=512))
+    engine.load_model(O.Model(O.tiny_geometry()))
+    engine.step([S.EngineRow(0, toks[i], i, i >= 4) for i in range(12)] + [S.EngineRow(1, toks[40 + i], i, True, True) for i in range(5)])
+    logits = engine.all_logits()
+    assert logits.shape[0] == 13
+    for k, limit in ((20, g.vocab), (1, g.vocab), (64, 31000), (7, 100)):
+        ids, values = engine.topk(k, limit)
+        for r in range(logits.shape[0]):
+            rid, rvalues = OS.topk_select(logits[r], limit, k)
+            assert list(ids[r]) == rid and np.array_equal(values[r], rvalues), (k, limit, r)
+    assert np.array_equal(engine.topk(1)[0][:, 0], engine.argmax())
+    ids, values = engine.topk(20)
+    mine, ref = S.Sampler(0.8, 0.9, 20, seed=2024), OS.Sampler(0.8, 0.9, 20, seed=2024)
+    for r in range(logits.shape[0]):
+        assert mine.sample(ids[r], values[r]) == ref.sample(ids[r], values[r])
+    with pytest.raises(S.EngineError):
+        engine.topk(65)
