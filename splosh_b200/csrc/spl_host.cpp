@@ -228,14 +228,16 @@ void spl_plan_costs_reference(spl_plan_costs *c) {
     c->prefill_attention = 0.022;                                       // per row and thousand tokens, :659
     c->tier_margin = 0.88;                                              // :779
 }
-// The same table measured with this library on a B200 (27B shape, MLX 4-bit): steps of 16..128 rows at short context
-// for the tiers, 64-row steps at 1K and 40K context for attention. Draft pass and CPU work are the caller's to add.
+// The same table measured with this library on a B200 (27B shape, MLX 4-bit, 8 sessions): steps of 16, 32, 64, 96 and
+// 128 rows at 1K context took 10.7, 11.3, 12.7, 21.2 and 22.2 ms; 64 rows at 40K took 15.2 ms and 128 rows 27.2 ms,
+// i.e. 0.0082 ms per thousand context tokens and block of eight rows, first or second; the host's share of a step
+// (tables, launches, ids back) was 0.3 ms. A draft pass is the caller's to add.
 void spl_plan_costs_b200(spl_plan_costs *c) {
     if (!c) return;
-    const double tiers[5] = {11.0, 11.6, 12.9, 23.0, 25.0};
+    const double tiers[5] = {10.7, 11.3, 12.7, 21.2, 22.2};
     for (int i = 0; i < 5; ++i) c->tier_ms[i] = tiers[i];
-    c->beyond_ms_per_row = 0.2; c->per_row_ms = 0.0; c->fixed_ms = 0.5;
-    c->attention_first = 0.0078; c->attention_second = 0.0078;
+    c->beyond_ms_per_row = 0.17; c->per_row_ms = 0.0; c->fixed_ms = 0.3;
+    c->attention_first = 0.0082; c->attention_second = 0.0082;
     c->prefill_attention = 0.001;
     c->tier_margin = 0.88;
 }
