@@ -221,6 +221,21 @@ spl_status spl_debug_fill_state(spl_engine *engine, int32_t slot, uint64_t seed)
 spl_status spl_debug_read(spl_engine *engine, int32_t which, int32_t index, void *dst, size_t bytes);
 spl_status spl_debug_taps(spl_engine *engine, int32_t enabled);
 
+/* ---- Slot snapshots ------------------------------------------------------------------------
+ * exportState / importState (Engine.swift:871-939) and exportKV / kvPrefix / importSlot's KV part (:953-1042), as two
+ * opaque, versioned blobs on host memory. The state blob is the slot's recurrent state of every gated-delta block,
+ * accepted journal entries folded in first (Engine.commitJournal, :889-903), with the conv history of its current
+ * unit. The KV blob is the pages covering the slot's first `token_count` tokens in every attention block; KV is
+ * append-only, so it is valid for any prefix of what the slot has evaluated, and importing fewer tokens than a blob
+ * holds takes the prefix (kvPrefix). A blob of another geometry or layout is refused with SPL_ERR_SNAPSHOT_MISMATCH
+ * (EngineError.snapshotMismatch). Import leaves the slot holding exactly the imported pages and no pending journal. */
+size_t spl_state_bytes(const spl_engine *engine);
+spl_status spl_state_export(spl_engine *engine, int32_t slot, void *dst, size_t capacity);
+spl_status spl_state_import(spl_engine *engine, int32_t slot, const void *src, size_t bytes);
+size_t spl_kv_bytes(const spl_engine *engine, int32_t token_count);
+spl_status spl_kv_export(spl_engine *engine, int32_t slot, int32_t token_count, void *dst, size_t capacity);
+spl_status spl_kv_import(spl_engine *engine, int32_t slot, int32_t token_count, const void *src, size_t bytes);
+
 /* ---- Drafter feature taps ------------------------------------------------------------------
  * step(_:captureFeatures:) and featureRow(_:) (Engine.swift:1316, 1309-1313; taps at
  * Engine.featureLayers = [5, 19, 33, 47, 61], Engine.swift:331, copied by sp_copy_rows :1488-1497):

@@ -951,6 +951,168 @@ spl_status spl_debug_read(spl_engine *e, int32_t which, int32_t index, void *dst
 
 }  // extern "C"
 
+// ---- slot snapshots (Engine.swift:870-1042) -----------------------------------------------------
+// Two opaque, versioned blobs. State: the slot's recurrent state of every gated-delta block with the journal folded
+// in, and the conv history of its current unit. KV: the pages that cover the slot's first `token_count` tokens,
+// every attention block, in the pool's own byte order. A blob is valid for engines of the same geometry only.
+namespace {
+struct SnapshotHeader { uint32_t magic, version; uint64_t identity; uint32_t blocks, tokens; uint64_t payload; };
+constexpr uint32_t kStateMagic = 0x53504C53u, kKvMagic = 0x4B504C53u, kSnapshotVersion = 2u;      // "SLPS", "SLPK"
+
+uint64_t snapshot_identity(const spl_engine *e) {
+    const spl_geometry &g = e->g;
+    const int fields[] = {g.layers, g.hidden, g.heads, g.kv_heads, g.head_dim, g.rotary_dim, g.gdn_key_heads, g.gdn_value_heads, g.gdn_head_dim, SPL_PAGE_TOKENS};
+    uint64_t h = 1469598103934665603ull;
+    for (int f : fields) for (int b = 0; b < 4; ++b) { h ^= uint64_t((f >> (8 * b)) & 0xFF); h *= 1099511628211ull; }
+    return h;
+}
+size_t state_payload(const spl_engine *e) { return e->state.size() * (e->state_layer_bytes + e->conv_unit_bytes); }
+size_t kv_page_payload(const spl_engine *e) {       // one page of one attention block: K codes, V codes, K scales, V scales
+    const size_t vecs = size_t(e->g.kv_heads) * SPL_PAGE_TOKENS;
+    return 2 * vecs * e->g.head_dim + 2 * vecs * 4;
+}
+// Engine.commitJournal (Engine.swift:889-903): fold the slot's accepted journal entries into its stored state. The
+// recurrence kernel does it when given a run of no rows.
+spl_status commit_journal(spl_engine *e, int slot) {
+    const uint32_t pending = e->host->journal_pending[slot];
+    if (pending == 0) return SPL_OK;
+    const uint32_t table[5] = {uint32_t(slot), 0u, 0u, /* run_info: */ 0u, pending};
+    memcpy(e->tables_host, table, sizeof table);
+    SPL_CUDA(cudaMemcpyAsync(e->tables_dev, e->tables_host, sizeof table, cudaMemcpyHostToDevice, e->stream));
+    const Shapes sh(e->g);
+    SplGdnParams p;
+    p.rows = 0; p.runs = 1; p.channels = sh.C; p.key_heads = e->g.gdn_key_heads; p.value_heads = e->g.gdn_value_heads; p.head_dim = e->g.gdn_head_dim;
+    p.proj_ld = e->proj_ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = e->g.eps; p.trace = nullptr;
+    const int rn = 16;
+    const SplOperand core{e->core, e->core_sums, rn, 1};
+    int linear = 0;
+    for (size_t l = 0; l < e->layers.size(); ++l) {
+        if (e->layers[l].full) continue;
+        spl_gdn_recurrence_kernel<<<dim3(e->g.gdn_value_heads, 1), SPL_GDN_THREADS, 0, e->stream>>>(
+            e->gdn_act, e->proj, e->layers[l].vec[SPL_VEC_A_LOG], e->layers[l].vec[SPL_VEC_DT_BIAS], e->layers[l].vec[SPL_VEC_GDN_NORM],
+            e->state[linear], e->journal[linear], e->tables_dev, e->tables_dev + 3, core, p);
+        ++linear;
+    }
+    const spl_status launched = check_launch(e, "journal commit");
+    if (launched != SPL_OK) return launched;
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    e->host->journal_pending[slot] = 0;
+    return SPL_OK;
+}
+}  // namespace
+
+extern "C" {
+
+size_t spl_state_bytes(const spl_engine *e) { return e ? sizeof(SnapshotHeader) + state_payload(e) : 0; }
+
+spl_status spl_state_export(spl_engine *e, int32_t slot, void *dst, size_t capacity) {
+    if (!e || !dst || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    if (capacity < spl_state_bytes(e)) return e->fail(SPL_ERR_INVALID_ARGUMENT, "state export: the buffer is smaller than spl_state_bytes");
+    SPL_CUDA(cudaSetDevice(e->device));
+    const spl_status committed = commit_journal(e, slot);
+    if (committed != SPL_OK) return committed;
+    SnapshotHeader header = {kStateMagic, kSnapshotVersion, snapshot_identity(e), uint32_t(e->state.size()), 0u, uint64_t(state_payload(e))};
+    memcpy(dst, &header, sizeof header);
+    unsigned char *out = static_cast<unsigned char *>(dst) + sizeof header;
+    const uint32_t unit = e->host->slot_unit[slot];
+    for (size_t l = 0; l < e->state.size(); ++l) {
+        SPL_CUDA(cudaMemcpyAsync(out, reinterpret_cast<const char *>(e->state[l]) + size_t(slot) * e->state_layer_bytes, e->state_layer_bytes, cudaMemcpyDeviceToHost, e->stream));
+        out += e->state_layer_bytes;
+        SPL_CUDA(cudaMemcpyAsync(out, reinterpret_cast<const char *>(e->conv[l]) + size_t(unit) * e->conv_unit_bytes, e->conv_unit_bytes, cudaMemcpyDeviceToHost, e->stream));
+        out += e->conv_unit_bytes;
+    }
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    return SPL_OK;
+}
+
+spl_status spl_state_import(spl_engine *e, int32_t slot, const void *src, size_t bytes) {
+    if (!e || !src || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    SnapshotHeader header;
+    if (bytes < sizeof header) return e->fail(SPL_ERR_SNAPSHOT_MISMATCH, "snapshot mismatch: truncated state blob");
+    memcpy(&header, src, sizeof header);
+    if (header.magic != kStateMagic || header.version != kSnapshotVersion || header.identity != snapshot_identity(e) ||
+        header.payload != state_payload(e) || bytes < sizeof header + header.payload)
+        return e->fail(SPL_ERR_SNAPSHOT_MISMATCH, "snapshot mismatch: the state blob is not one of this engine's geometry and layout");
+    SPL_CUDA(cudaSetDevice(e->device));
+    spl_host_discard_verify(e->host, slot);
+    e->host->journal_pending[slot] = 0;
+    const unsigned char *in = static_cast<const unsigned char *>(src) + sizeof header;
+    const uint32_t unit = e->host->slot_unit[slot];
+    for (size_t l = 0; l < e->state.size(); ++l) {
+        SPL_CUDA(cudaMemcpyAsync(reinterpret_cast<char *>(e->state[l]) + size_t(slot) * e->state_layer_bytes, in, e->state_layer_bytes, cudaMemcpyHostToDevice, e->stream));
+        in += e->state_layer_bytes;
+        SPL_CUDA(cudaMemcpyAsync(reinterpret_cast<char *>(e->conv[l]) + size_t(unit) * e->conv_unit_bytes, in, e->conv_unit_bytes, cudaMemcpyHostToDevice, e->stream));
+        in += e->conv_unit_bytes;
+    }
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    return SPL_OK;
+}
+
+size_t spl_kv_bytes(const spl_engine *e, int32_t token_count) {
+    if (!e || token_count < 0) return 0;
+    const size_t pages = size_t(token_count + SPL_PAGE_TOKENS - 1) / SPL_PAGE_TOKENS;
+    return sizeof(SnapshotHeader) + pages * e->k_codes.size() * kv_page_payload(e);
+}
+
+spl_status spl_kv_export(spl_engine *e, int32_t slot, int32_t token_count, void *dst, size_t capacity) {
+    if (!e || !dst || slot < 0 || slot >= e->c.max_slots || token_count < 0) return SPL_ERR_INVALID_ARGUMENT;
+    const size_t pages = size_t(token_count + SPL_PAGE_TOKENS - 1) / SPL_PAGE_TOKENS;
+    if (pages > e->host->slot_pages[slot].size()) return e->fail(SPL_ERR_INVALID_ARGUMENT, "kv export: the slot holds fewer tokens than asked for");
+    if (capacity < spl_kv_bytes(e, token_count)) return e->fail(SPL_ERR_INVALID_ARGUMENT, "kv export: the buffer is smaller than spl_kv_bytes");
+    SPL_CUDA(cudaSetDevice(e->device));
+    SnapshotHeader header = {kKvMagic, kSnapshotVersion, snapshot_identity(e), uint32_t(e->k_codes.size()), uint32_t(token_count),
+                             uint64_t(pages * e->k_codes.size() * kv_page_payload(e))};
+    memcpy(dst, &header, sizeof header);
+    unsigned char *out = static_cast<unsigned char *>(dst) + sizeof header;
+    const size_t vecs = size_t(e->g.kv_heads) * SPL_PAGE_TOKENS, codes = vecs * e->g.head_dim;
+    for (size_t l = 0; l < e->k_codes.size(); ++l)
+        for (size_t pg = 0; pg < pages; ++pg) {
+            const size_t page = e->host->slot_pages[slot][pg];
+            SPL_CUDA(cudaMemcpyAsync(out, e->k_codes[l] + page * codes, codes, cudaMemcpyDeviceToHost, e->stream)); out += codes;
+            SPL_CUDA(cudaMemcpyAsync(out, e->v_codes[l] + page * codes, codes, cudaMemcpyDeviceToHost, e->stream)); out += codes;
+            SPL_CUDA(cudaMemcpyAsync(out, e->k_scale[l] + page * vecs, vecs * 4, cudaMemcpyDeviceToHost, e->stream)); out += vecs * 4;
+            SPL_CUDA(cudaMemcpyAsync(out, e->v_scale[l] + page * vecs, vecs * 4, cudaMemcpyDeviceToHost, e->stream)); out += vecs * 4;
+        }
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    return SPL_OK;
+}
+
+spl_status spl_kv_import(spl_engine *e, int32_t slot, int32_t token_count, const void *src, size_t bytes) {
+    if (!e || !src || slot < 0 || slot >= e->c.max_slots || token_count < 0) return SPL_ERR_INVALID_ARGUMENT;
+    SnapshotHeader header;
+    if (bytes < sizeof header) return e->fail(SPL_ERR_SNAPSHOT_MISMATCH, "snapshot mismatch: truncated KV blob");
+    memcpy(&header, src, sizeof header);
+    const size_t pages = size_t(token_count + SPL_PAGE_TOKENS - 1) / SPL_PAGE_TOKENS;
+    const size_t stored_pages = size_t(header.tokens + SPL_PAGE_TOKENS - 1) / SPL_PAGE_TOKENS;
+    if (header.magic != kKvMagic || header.version != kSnapshotVersion || header.identity != snapshot_identity(e) || header.blocks != e->k_codes.size() ||
+        uint32_t(token_count) > header.tokens || header.payload != stored_pages * e->k_codes.size() * kv_page_payload(e) || bytes < sizeof header + header.payload)
+        return e->fail(SPL_ERR_SNAPSHOT_MISMATCH, "snapshot mismatch: the KV blob is not one of this engine's geometry and layout, or holds fewer tokens");
+    SPL_CUDA(cudaSetDevice(e->device));
+    // The slot keeps exactly the pages of the imported prefix (Engine.kvPrefix, Engine.swift:974-991: a prefix of a stored KV is valid as it is).
+    spl_host_truncate(e->host, slot, 0);
+    if (token_count > 0) {
+        const spl_status paged = e->host->ensure_page(slot, token_count - 1);
+        if (paged != SPL_OK) return e->fail(paged, e->host->error);
+    }
+    const unsigned char *in = static_cast<const unsigned char *>(src) + sizeof header;
+    const size_t vecs = size_t(e->g.kv_heads) * SPL_PAGE_TOKENS, codes = vecs * e->g.head_dim;
+    for (size_t l = 0; l < e->k_codes.size(); ++l)
+        for (size_t pg = 0; pg < stored_pages; ++pg) {
+            if (pg < pages) {
+                const size_t page = e->host->slot_pages[slot][pg];
+                SPL_CUDA(cudaMemcpyAsync(e->k_codes[l] + page * codes, in, codes, cudaMemcpyHostToDevice, e->stream));
+                SPL_CUDA(cudaMemcpyAsync(e->v_codes[l] + page * codes, in + codes, codes, cudaMemcpyHostToDevice, e->stream));
+                SPL_CUDA(cudaMemcpyAsync(e->k_scale[l] + page * vecs, in + 2 * codes, vecs * 4, cudaMemcpyHostToDevice, e->stream));
+                SPL_CUDA(cudaMemcpyAsync(e->v_scale[l] + page * vecs, in + 2 * codes + vecs * 4, vecs * 4, cudaMemcpyHostToDevice, e->stream));
+            }
+            in += kv_page_payload(e);
+        }
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    return SPL_OK;
+}
+
+}  // extern "C"
+
 // ---- A GEMM that allocates nothing ---------------------------------------------------------
 //
 // For callers that may not allocate device memory: a host that handed the whole GPU to its own

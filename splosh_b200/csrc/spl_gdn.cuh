@@ -113,7 +113,8 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
     if (tid < int(pending)) jdecay[tid] = jhead[size_t(tid) * VH * SPL_JOURNAL_WIDTH + 2 * D];
     const float neg_a = -expf(spl_bf16_to_float(a_log[h])), bias = spl_bf16_to_float(dt_bias[h]);
 
-    for (uint32_t base = 0; base < length; base += TC) {
+    // A run of no rows with entries to replay is a journal commit (Engine.commitJournal, Engine.swift:889-903): one pass, no tokens.
+    for (uint32_t base = 0; base < length || (base == 0 && pending != 0); base += TC) {
         const int count = min(uint32_t(TC), length - base);
         if (base != 0) __syncthreads();
         // q, k, v of up to TC tokens; one warp a token for the norms and the gates.

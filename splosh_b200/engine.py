@@ -161,6 +161,12 @@ def lib():
             "spl_debug_fill_state": (i32, [vp, i32, u64]),
             "spl_debug_read": (i32, [vp, i32, i32, vp, C.c_size_t]),
             "spl_debug_taps": (i32, [vp, i32]),
+            "spl_state_bytes": (C.c_size_t, [vp]),
+            "spl_state_export": (i32, [vp, i32, vp, C.c_size_t]),
+            "spl_state_import": (i32, [vp, i32, vp, C.c_size_t]),
+            "spl_kv_bytes": (C.c_size_t, [vp, i32]),
+            "spl_kv_export": (i32, [vp, i32, i32, vp, C.c_size_t]),
+            "spl_kv_import": (i32, [vp, i32, i32, vp, C.c_size_t]),
             "spl_plan_costs_reference": (None, [vp]),
             "spl_plan_costs_b200": (None, [vp]),
             "spl_plan_tier": (i32, [i32]),
@@ -458,6 +464,27 @@ class Engine:
 
     def debug_fill_state(self, slot, seed):
         self._check(lib().spl_debug_fill_state(self.handle, slot, seed))
+
+    # ---- snapshots
+    def export_state(self, slot):
+        """Engine.exportState (Engine.swift:871-887): the slot's recurrent and conv state, journal folded in."""
+        blob = np.empty(lib().spl_state_bytes(self.handle), np.uint8)
+        self._check(lib().spl_state_export(self.handle, slot, _ptr(blob), blob.size))
+        return blob
+
+    def import_state(self, slot, blob):
+        blob = np.ascontiguousarray(blob, np.uint8)
+        self._check(lib().spl_state_import(self.handle, slot, _ptr(blob), blob.size))
+
+    def export_kv(self, slot, token_count):
+        """Engine.exportKV (Engine.swift:953-970): the pages covering the slot's first `token_count` tokens."""
+        blob = np.empty(lib().spl_kv_bytes(self.handle, token_count), np.uint8)
+        self._check(lib().spl_kv_export(self.handle, slot, token_count, _ptr(blob), blob.size))
+        return blob
+
+    def import_kv(self, slot, token_count, blob):
+        blob = np.ascontiguousarray(blob, np.uint8)
+        self._check(lib().spl_kv_import(self.handle, slot, token_count, _ptr(blob), blob.size))
 
     def topk(self, k=20, vocab_limit=None):
         """TopK.select (Sampler.swift:19-52) over every logit row of the last step: (ids, values), each [rows][k]."""

@@ -337,3 +337,50 @@ def test_topk_on_the_device_and_sampling_from_it(toks):
         assert mine.sample(ids[r], values[r]) == ref.sample(ids[r], values[r])
     with pytest.raises(S.EngineError):
         engine.topk(65)
+
+
+def test_a_slot_moves_to_another_engine_through_state_and_kv_snapshots(toks):
+    """exportState / exportKV / importState / importSlot (Engine.swift:870-1042). A conversation of 300 tokens plus one
+    accepted 6-row speculative block (so the export has journal entries to fold in) moves from slot 0 of engine A to
+    slot 1 of engine B; both then decode the same tokens and must give the same logits bit for bit. A prefix of the KV
+    blob (Engine.kvPrefix) imports too; a blob of another geometry is refused."""
+    g = S.tiny_geometry()
+    cfg = S.EngineConfig(max_slots=2, max_rows=64, kv_pages=8, max_context=1024)
+    model = O.Model(O.tiny_geometry())
+    a = S.Engine(g, cfg); b = S.Engine(g, cfg)
+    a.load_model(model); b.load_model(model)
+    for start in (0, 64, 128, 192, 256):
+        n = min(64, 300 - start)
+        a.step([S.EngineRow(0, toks[start + i], start + i, False) for i in range(n)])
+    a.step([S.EngineRow(0, toks[300 + i], 300 + i, True, True) for i in range(6)])
+    a.accept_verify(0, 4, 304)                       # four of the six rows are kept: four journal entries pending
+    b.step([S.EngineRow(1, toks[900 + i], i, False) for i in range(5)])       # slot 1 of B holds something else first
+    state, kv = a.export_state(0), a.export_kv(0, 304)
+    assert state.size == lib_state_bytes(a) and kv.size > 0
+    b.reset_slot(1)
+    b.import_kv(1, 304, kv); b.import_state(1, state)
+    assert b.pages_held(1) == 2 and a.host.journal_pending(0) == 0
+    for i in range(4):
+        a.step([S.EngineRow(0, toks[304 + i], 304 + i, True)])
+        b.step([S.EngineRow(1, toks[304 + i], 304 + i, True)])
+        assert np.array_equal(a.all_logits(), b.all_logits()), i
+    # A prefix of the blob: 256 tokens = one page; positions 256.. are then re-evaluated by the importer.
+    c = S.Engine(g, cfg); c.load_model(model)
+    c.import_kv(0, 256, kv)
+    assert c.pages_held(0) == 1
+    with pytest.raises(S.EngineError) as caught:
+        c.import_kv(0, 400, kv)                      # more tokens than the blob holds
+    assert caught.value.case == "snapshotMismatch"
+    deeper = S.tiny_geometry(); deeper.layers = 8
+    other = S.Engine(deeper, cfg)
+    for blob, load in ((state, other.import_state), (kv, lambda slot, data: other.import_kv(slot, 256, data))):
+        with pytest.raises(S.EngineError) as caught:
+            load(0, blob)
+        assert caught.value.case == "snapshotMismatch"
+    with pytest.raises(S.EngineError):
+        b.import_state(1, state[:100])
+
+
+def lib_state_bytes(engine):
+    from splosh_b200.engine import lib
+    return lib().spl_state_bytes(engine.handle)
