@@ -282,6 +282,14 @@ spl_status spl_gemm_q4_static(spl_engine *engine, int32_t layer, int32_t which, 
 spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t *scales, const uint16_t *biases,
                           int32_t n, int32_t k, const float *activations, int32_t rows, const float *residual, float *out);
 
+/* Engine.gemm's GGUF branch (Engine.swift:1666-1695; kernels Sources/Shaders/engine_gguf.metal:82-273) for one K-quant
+ * tensor: blocks = native GGUF super-blocks of 256, row-major [n][k / 256][144 | 176 | 210 bytes], format = the GGUF
+ * type number (12 Q4_K, 13 Q5_K, 14 Q6_K). out[r][n] = sum_k bf16(a[r][k]) * w16[n][k] (+ residual[r][n]) with each
+ * weight rounded once to fp16 from fma(code, d * scale, -dmin * minimum) (Q4_K, Q5_K) or (code - 32) * (d * scale)
+ * (Q6_K), as the reference's tile kernels form it (Sources/Shaders/gguf_formats.h:390-438). */
+spl_status spl_op_gemm_gguf(int32_t device, int32_t format, const uint8_t *blocks, int32_t n, int32_t k, const float *activations,
+                            int32_t rows, const float *residual, float *out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -131,6 +131,84 @@ def decode_gguf(kind, raw):
     return out
 
 
+GGUF_TYPE = {"Q4_K": 12, "Q5_K": 13, "Q6_K": 14}
+GGUF_BLOCK_BYTES = {"Q4_K": 144, "Q5_K": 176, "Q6_K": 210}
+
+
+def gguf_tile_weights(kind, raw):
+    """The weights as the GGUF tile kernels form them (gguf_formats.h:390-438): raw uint8 [blocks, bytes] -> float32 [blocks, 256]
+    of fp16-representable values."""
+    raw = np.ascontiguousarray(raw, np.uint8)
+    assert raw.shape[1] == GGUF_BLOCK_BYTES[kind]
+    out = np.zeros((raw.shape[0], 256), np.float32)
+    lib().orc_gguf_tile_weights(GGUF_TYPE[kind], _ptr(raw), raw.shape[0], _ptr(out))
+    return out
+
+
+def gemm_gguf(kind, blocks, activations, residual=None):
+    """blocks: uint8 [n, k / 256, block bytes] native GGUF super-blocks, row-major; activations fp32 [rows, k]."""
+    blocks = np.ascontiguousarray(blocks, np.uint8)
+    n, per_row = blocks.shape[0], blocks.shape[1]
+    a = np.ascontiguousarray(activations, np.float32)
+    out = np.zeros((a.shape[0], n), np.float32)
+    res = None if residual is None else np.ascontiguousarray(residual, np.float32)
+    lib().orc_gemm_gguf(GGUF_TYPE[kind], _ptr(blocks), n, per_row * 256, _ptr(a), a.shape[0], None if res is None else _ptr(res), _ptr(out))
+    return out
+
+
+def quantize_gguf(kind, weights, seed=0):
+    """A build-owned K-quant encoder, good enough to make valid blocks (parity is defined on the DECODED values, so any
+    valid encoding serves): per 32 (Q4_K, Q5_K) or 16 (Q6_K) elements a min/max scale against per-256 fp16 d / dmin.
+    weights: fp32 [n, k] -> uint8 [n, k / 256, block bytes]."""
+    w = np.ascontiguousarray(weights, np.float32)
+    n, k = w.shape
+    assert k % 256 == 0
+    blocks = w.reshape(n * (k // 256), 256)
+    nb = blocks.shape[0]
+    out = np.zeros((nb, GGUF_BLOCK_BYTES[kind]), np.uint8)
+    if kind == "Q6_K":
+        sub = blocks.reshape(nb, 16, 16)
+        amax = np.abs(sub).max(axis=2)                          # [nb, 16]
+        d = (amax.max(axis=1) / (127.0 * 31.0)).astype(np.float16)
+        d32 = np.where(d.astype(np.float32) == 0, 1.0, d.astype(np.float32))
+        sc = np.clip(np.rint(amax / 31.0 / d32[:, None]), -128, 127).astype(np.int8)
+        step = d32[:, None] * sc.astype(np.float32)
+        step = np.where(step == 0, 1.0, step)
+        q = np.clip(np.rint(sub / step[:, :, None]) + 32, 0, 63).astype(np.uint8).reshape(nb, 256)
+        for half in range(2):
+            for quarter in range(4):
+                e = q[:, 128 * half + 32 * quarter: 128 * half + 32 * quarter + 32]
+                low, high = e & 15, e >> 4
+                ql = out[:, 64 * half + 32 * (quarter & 1): 64 * half + 32 * (quarter & 1) + 32]
+                ql |= (low << (4 * (quarter >> 1))).astype(np.uint8)
+                qh = out[:, 128 + 32 * half: 128 + 32 * half + 32]
+                qh |= (high << (2 * quarter)).astype(np.uint8)
+        out[:, 192:208] = sc.view(np.uint8)
+        out[:, 208:210] = d.view(np.uint8).reshape(nb, 2)
+        return out.reshape(n, k // 256, 210)
+    levels = 31 if kind == "Q5_K" else 15
+    sub = blocks.reshape(nb, 8, 32)
+    lo = np.minimum(sub.min(axis=2), 0.0); hi = sub.max(axis=2)
+    step = (hi - lo) / levels                                   # [nb, 8]
+    d = (step.max(axis=1) / 63.0).astype(np.float16); dmin = ((-lo).max(axis=1) / 63.0).astype(np.float16)
+    d32 = np.where(d.astype(np.float32) == 0, 1.0, d.astype(np.float32)); m32 = np.where(dmin.astype(np.float32) == 0, 1.0, dmin.astype(np.float32))
+    sc = np.clip(np.rint(step / d32[:, None]), 0, 63).astype(np.uint8); mn = np.clip(np.rint(-lo / m32[:, None]), 0, 63).astype(np.uint8)
+    s = d.astype(np.float32)[:, None] * sc; m = dmin.astype(np.float32)[:, None] * mn
+    q = np.clip(np.rint((sub + m[:, :, None]) / np.where(s == 0, 1.0, s)[:, :, None]), 0, levels).astype(np.uint8)      # [nb, 8, 32]
+    out[:, 0:2] = d.view(np.uint8).reshape(nb, 2); out[:, 2:4] = dmin.view(np.uint8).reshape(nb, 2)
+    for j in range(4):
+        out[:, 4 + j] = (sc[:, j] & 63) | ((sc[:, j + 4] >> 4) << 6)
+        out[:, 8 + j] = (mn[:, j] & 63) | ((mn[:, j + 4] >> 4) << 6)
+        out[:, 12 + j] = (sc[:, j + 4] & 15) | ((mn[:, j + 4] & 15) << 4)
+    codes = 48 if kind == "Q5_K" else 16
+    for j in range(8):
+        nib = (q[:, j] & 15).astype(np.uint8)
+        out[:, codes + 32 * (j // 2): codes + 32 * (j // 2) + 32] |= (nib << (4 * (j % 2))).astype(np.uint8)
+        if kind == "Q5_K":
+            out[:, 16:48] |= ((q[:, j] >> 4) << j).astype(np.uint8)
+    return out.reshape(n, k // 256, GGUF_BLOCK_BYTES[kind])
+
+
 def gemm_q4(packed, scales, biases, activations, residual=None):
     n, k = packed.shape[0], packed.shape[1] * 8
     a = np.ascontiguousarray(activations, np.float32)

@@ -669,6 +669,65 @@ void orc_decode_q6k(const uint8_t *data, int blocks, float *out) {
     }
 }
 
+// The GGUF GEMM's weights as its tile kernels form them (Sources/Shaders/gguf_formats.h:390-438): one fp32
+// multiply-add (Q4_K, Q5_K: fma(code, d * scale, -dmin * minimum)) or multiply (Q6_K: (code - 32) * (d * scale)),
+// rounded once to fp16. format: 12 = Q4_K, 13 = Q5_K, 14 = Q6_K (the GGUF type numbers).
+static float round_half(float v) { _Float16 h = _Float16(v); return float(h); }
+void orc_gguf_tile_weights(int format, const uint8_t *data, int blocks, float *out) {
+    for (int n = 0; n < blocks; ++n) {
+        if (format == 14) {
+            const uint8_t *b = data + size_t(n) * 210;
+            const float d = half_at(b, 208);
+            for (int j = 0; j < 8; ++j) {
+                const int half = j / 4, quarter = j % 4;
+                for (int e = 0; e < 32; ++e) {
+                    const int low = (b[64 * half + 32 * (quarter & 1) + e] >> (4 * (quarter >> 1))) & 15;
+                    const int high = (b[128 + 32 * half + e] >> (2 * quarter)) & 3;
+                    const float code = float((low | (high << 4)) - 32);
+                    const float s = d * float(int8_t(b[192 + 2 * j + e / 16]));
+                    out[size_t(n) * 256 + 32 * j + e] = round_half(code * s);
+                }
+            }
+        } else {
+            const bool fifth = format == 13;
+            const uint8_t *b = data + size_t(n) * (fifth ? 176 : 144);
+            const int codes = fifth ? 48 : 16;
+            const float d = half_at(b, 0), dmin = half_at(b, 2);
+            for (int j = 0; j < 8; ++j) {
+                uint8_t scale, minimum;
+                if (j < 4) { scale = b[4 + j] & 63; minimum = b[4 + j + 4] & 63; }
+                else { scale = (b[4 + j + 4] & 0xF) | ((b[4 + j - 4] >> 6) << 4); minimum = (b[4 + j + 4] >> 4) | ((b[4 + j] >> 6) << 4); }
+                const float s = d * float(scale), m = -dmin * float(minimum);
+                for (int e = 0; e < 32; ++e) {
+                    const uint8_t byte = b[codes + 32 * (j / 2) + e];
+                    int code = j % 2 == 0 ? byte & 15 : byte >> 4;
+                    if (fifth) code += 16 * ((b[16 + e] >> j) & 1);
+                    out[size_t(n) * 256 + 32 * j + e] = round_half(fmaf(float(code), s, m));
+                }
+            }
+        }
+    }
+}
+
+// GGUF GEMM (Sources/Shaders/engine_gguf.metal:82-273): out[r][n] = sum_k bf16(a[r][k]) * w16[n][k] (+ residual), fp32 sums;
+// data: row-major native blocks [n][k / 256].
+void orc_gemm_gguf(int format, const uint8_t *data, int n, int k, const float *a, int rows, const float *residual, float *out) {
+    const int per_row = k / 256, bytes = format == 14 ? 210 : format == 13 ? 176 : 144;
+    std::vector<float> rounded(size_t(rows) * k);
+    for (size_t i = 0; i < rounded.size(); ++i) rounded[i] = round_bf16(a[i]);
+#pragma omp parallel for schedule(static)
+    for (int col = 0; col < n; ++col) {
+        std::vector<float> w(k);
+        orc_gguf_tile_weights(format, data + size_t(col) * per_row * bytes, per_row, w.data());
+        for (int r = 0; r < rows; ++r) {
+            float acc = 0.0f;
+            const float *x = rounded.data() + size_t(r) * k;
+            for (int i = 0; i < k; ++i) acc += x[i] * w[i];
+            out[size_t(r) * n + col] = acc + (residual ? residual[size_t(r) * n + col] : 0.0f);
+        }
+    }
+}
+
 // One fp32 gated-delta update, state [head][key][value] and log-space decay: the per-op oracle of
 // Sources/SploshOracle/GdnOracle.swift:44-64, kept to pin against Tests/SploshOracleTests/GdnOracleTests.swift.
 void orc_gdn_decode(const float *query, const float *key, const float *value, const float *beta, const float *log_decay,

@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "spl_attention.cuh"
+#include "spl_gemm_gguf.cuh"
 #include "spl_elementwise.cuh"
 #include "spl_gdn.cuh"
 #include "spl_gemm_tc.cuh"
@@ -225,6 +226,38 @@ void launch_gemm_rows(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand 
     if (op.rn == 16) launch_gemm_tc<16>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer);
     else if (op.rn == 32) launch_gemm_tc<32>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer);
     else launch_gemm_tc<64>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer);
+}
+
+template <int RN, int FMT>
+void launch_gemm_gguf_tc(cudaStream_t stream, const SplGgufDev &w, const GemmOperand &op, float *out, const float *residual, int rows,
+                         float *partials, size_t partial_floats, int *error_flag) {
+    const int supers = w.k / 256;
+    const int row_blocks = (rows + RN - 1) / RN, rows_padded = op.blocks * RN;
+    // The q4 rule in units of four groups: a split is a whole number of super-blocks.
+    const int splits4 = choose_splits(w.tiles * row_blocks, supers * 4, 148, partial_floats, size_t(rows_padded) * w.ld);
+    const int sps = (supers + splits4 - 1) / splits4, splits = (supers + sps - 1) / sps;
+    const size_t smem = spl_gguf_smem_bytes(RN, FMT);
+    static bool configured = false;
+    if (!configured) { cudaFuncSetAttribute(spl_gemm_gguf_tc_kernel<RN, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); configured = true; }
+    launch_step(spl_gemm_gguf_tc_kernel<RN, FMT>, dim3(w.tiles, splits, row_blocks), dim3(SPL_GG_THREADS), smem, stream,
+                w.blocks, op.values, out, w.ld, residual, partials, rows, op.blocks, supers, sps, error_flag);
+    if (splits > 1) {
+        const size_t total = size_t(rows) * w.ld / 4;
+        launch_step(spl_gemm_reduce_kernel, dim3(int(std::min<size_t>((total + 255) / 256, 2048))), dim3(256), 0, stream, partials, splits, rows_padded, rows, w.ld, residual, out);
+    }
+}
+template <int FMT>
+void launch_gemm_gguf_rows(cudaStream_t stream, const SplGgufDev &w, const GemmOperand &op, float *out, const float *residual, int rows,
+                           float *partials, size_t partial_floats, int *error_flag) {
+    if (op.rn == 16) launch_gemm_gguf_tc<16, FMT>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag);
+    else if (op.rn == 32) launch_gemm_gguf_tc<32, FMT>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag);
+    else launch_gemm_gguf_tc<64, FMT>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag);
+}
+void launch_gemm_gguf(cudaStream_t stream, const SplGgufDev &w, const GemmOperand &op, float *out, const float *residual, int rows,
+                      float *partials, size_t partial_floats, int *error_flag) {
+    if (w.format == SPL_GGUF_Q6K) launch_gemm_gguf_rows<SPL_GGUF_Q6K>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag);
+    else if (w.format == SPL_GGUF_Q5K) launch_gemm_gguf_rows<SPL_GGUF_Q5K>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag);
+    else launch_gemm_gguf_rows<SPL_GGUF_Q4K>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag);
 }
 
 void launch_gemm(spl_engine *e, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows, PendingReduce *defer = nullptr) {
@@ -1252,6 +1285,70 @@ spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t
     }
     cudaFree(d_sums); cudaFree(d_flag);
     cudaFree(w.codes); cudaFree(w.sb); cudaFree(d_act32); cudaFree(d_act); cudaFree(d_out); cudaFree(e->partials);
+    cudaStreamDestroy(e->stream);
+    e->stream = nullptr; e->partials = nullptr;
+    return s;
+}
+
+// Engine.gemm's GGUF branch for one K-quant tensor on host buffers (tests, micro-benchmarks): native super-blocks
+// [n][k / 256][block bytes] of GGUF type `format` (12 Q4_K, 13 Q5_K, 14 Q6_K).
+spl_status spl_op_gemm_gguf(int32_t device, int32_t format, const uint8_t *blocks, int32_t n, int32_t k, const float *activations, int32_t rows,
+                            const float *residual, float *out) {
+    if (!blocks || !activations || !out || n <= 0 || k <= 0 || k % 256 || rows <= 0 ||
+        (format != SPL_GGUF_Q4K && format != SPL_GGUF_Q5K && format != SPL_GGUF_Q6K)) return SPL_ERR_INVALID_ARGUMENT;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return SPL_ERR_UNSUPPORTED_DEVICE;
+    spl_engine local;
+    spl_engine *e = &local;
+    e->device = device;
+    SPL_CUDA(cudaSetDevice(device));
+    SPL_CUDA(cudaStreamCreate(&e->stream));
+    SplGgufDev w;
+    w.n = n; w.ld = round16(n); w.tiles = (n + 127) / 128; w.k = k; w.format = format;
+    const int ld = w.ld, rn = operand_rn(rows), row_blocks = (rows + rn - 1) / rn;
+    float *d_act32 = nullptr, *d_out = nullptr, *d_sums = nullptr; __nv_bfloat16 *d_act = nullptr; int *d_flag = nullptr; unsigned char *d_native = nullptr;
+    e->partial_floats = size_t(16) * row_blocks * rn * ld;
+    spl_status s = SPL_OK;
+    if (cudaMalloc(reinterpret_cast<void **>(&w.blocks), w.device_bytes()) != cudaSuccess || cudaMalloc(reinterpret_cast<void **>(&d_native), w.bytes()) != cudaSuccess)
+        s = SPL_ERR_ALLOCATION_FAILED;
+    if (s == SPL_OK) s = device_alloc(e, &d_act32, size_t(rows) * k);
+    if (s == SPL_OK) s = device_alloc(e, &d_act, size_t(row_blocks) * rn * k);
+    if (s == SPL_OK) s = device_alloc(e, &d_sums, spl_operand_sums_floats(size_t(row_blocks) * rn, k));
+    if (s == SPL_OK) s = device_alloc(e, &d_out, size_t(rows) * ld);
+    if (s == SPL_OK) s = device_alloc(e, &d_flag, 64);
+    if (s == SPL_OK) s = device_alloc(e, &e->partials, e->partial_floats);
+    if (s == SPL_OK) {
+        cudaMemsetAsync(w.blocks, 0, w.device_bytes(), e->stream);           // columns past n are zero blocks: weights 0
+        cudaMemcpyAsync(d_native, blocks, w.bytes(), cudaMemcpyHostToDevice, e->stream);
+        const size_t items = size_t(n) * (k / 256) * spl_gguf_pieces(format);
+        spl_repack_gguf_kernel<<<int(std::min<size_t>((items + 255) / 256, 16384)), 256, 0, e->stream>>>(d_native, n, k / 256, format, w.blocks);
+        cudaMemsetAsync(d_act, 0, size_t(row_blocks) * rn * k * 2, e->stream);
+        cudaMemsetAsync(d_sums, 0, spl_operand_sums_floats(size_t(row_blocks) * rn, k) * 4, e->stream);
+        cudaMemsetAsync(d_flag, 0, 64 * sizeof(int), e->stream);
+        cudaMemcpyAsync(d_act32, activations, size_t(rows) * k * 4, cudaMemcpyHostToDevice, e->stream);
+        spl_operand_kernel<<<rows, 256, 0, e->stream>>>(d_act32, SplOperand{d_act, d_sums, rn, row_blocks}, k);
+        if (residual) cudaMemcpy2DAsync(d_out, size_t(ld) * 4, residual, size_t(n) * 4, size_t(n) * 4, rows, cudaMemcpyHostToDevice, e->stream);
+        cudaEvent_t ev0, ev1; cudaEventCreate(&ev0); cudaEventCreate(&ev1);
+        const bool timed = getenv("SPL_TC_TRACE") != nullptr;
+        if (timed)
+            for (int warm = 0; warm < 3; ++warm)
+                launch_gemm_gguf(e->stream, w, GemmOperand{d_act, d_sums, rn, row_blocks}, d_out, nullptr, rows, e->partials, e->partial_floats, d_flag);
+        if (timed && residual) cudaMemcpy2DAsync(d_out, size_t(ld) * 4, residual, size_t(n) * 4, size_t(n) * 4, rows, cudaMemcpyHostToDevice, e->stream);
+        cudaEventRecord(ev0, e->stream);
+        launch_gemm_gguf(e->stream, w, GemmOperand{d_act, d_sums, rn, row_blocks}, d_out, residual ? d_out : nullptr, rows, e->partials, e->partial_floats, d_flag);
+        cudaEventRecord(ev1, e->stream);
+        s = check_launch(e, "gguf gemm");
+        if (cudaStreamSynchronize(e->stream) != cudaSuccess) s = SPL_ERR_DEVICE;
+        int flag = 0;
+        if (s == SPL_OK) { cudaMemcpy(&flag, d_flag, sizeof flag, cudaMemcpyDeviceToHost); if (flag) s = SPL_ERR_TIMEOUT; }
+        if (timed) {
+            float ms = 0; cudaEventElapsedTime(&ms, ev0, ev1);
+            fprintf(stderr, "gguf gemm type %d n %d k %d rows %d: %.1f us, %.0f GB/s\n", format, n, k, rows, ms * 1e3, double(w.bytes()) * row_blocks / (ms * 1e-3) / 1e9);
+        }
+        if (s == SPL_OK) cudaMemcpy2D(out, size_t(n) * 4, d_out, size_t(ld) * 4, size_t(n) * 4, rows, cudaMemcpyDeviceToHost);
+    }
+    cudaFree(d_sums); cudaFree(d_flag); cudaFree(d_native);
+    cudaFree(w.blocks); cudaFree(d_act32); cudaFree(d_act); cudaFree(d_out); cudaFree(e->partials);
     cudaStreamDestroy(e->stream);
     e->stream = nullptr; e->partials = nullptr;
     return s;

