@@ -188,6 +188,26 @@ __device__ __forceinline__ void spl_tc_mma_ts(uint32_t d_tmem, uint32_t a_tmem, 
     asm volatile("{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
                  ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the accumulate flag fixed at one (no predicate to compute in the issuing loop).
+__device__ __forceinline__ void spl_tc_mma_ts_acc(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc) {
+    asm volatile("{\n .reg .pred p;\n setp.eq.u32 p, 1, 1;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc) : "memory");
+}
+// One lane of a converged warp. The tensor-core instructions of a kernel are issued from loops that the WHOLE warp runs
+// (waits included), with only the instruction itself under this predicate: with warp-uniform control flow the
+// descriptors stay in uniform registers and one warp issues a k16 instruction every 32 cycles (the tensor pipe's own
+// rate at N = 64); the same loop under `if (lane == 0)` measured 51-57 cycles an instruction at best and 140-150 with a
+// few run-time conditions between the instructions.
+__device__ __forceinline__ bool spl_elect_one() {
+    uint32_t pred;
+    asm volatile("{\n .reg .pred p;\n elect.sync _|p, 0xffffffff;\n selp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+    return pred != 0;
+}
+// A bounded wait by every lane of a converged warp, with one answer for the warp (a lane that gave up alone would leave
+// the warp's later elect.sync waiting for it).
+__device__ __forceinline__ bool spl_mbar_wait_warp(uint64_t *bar, uint32_t parity) {
+    return __all_sync(0xffffffffu, spl_mbar_wait(bar, parity));
+}
 // K-major, 128-byte swizzle, rows of 128 bytes, eight-row groups 1,024 bytes apart.
 __device__ __forceinline__ uint64_t spl_tc_desc_sw128(uint32_t smem_byte_addr) {
     uint64_t d = 0;
@@ -248,16 +268,16 @@ __device__ __forceinline__ void spl_codes4(uint32_t w, uint32_t *a) {
 // products add up to (bias + 8 scale) * sum(a) to within 2^-22 of the term, beside the fp32 accumulator's own 2^-24.
 // The result is the reference's sum of per-group terms up to the order of fp32 additions.
 #define SPL_TC_SUPER 4           // groups per shared-memory stage: one bulk copy brings 256 of the contraction
-#define SPL_TC_CSTAGES 4         // stages of codes (16 KiB each), handed back as soon as they are in registers
-#define SPL_TC_ASUPERS 2         // A operand stages in tensor memory: twice four groups of 32 columns, and twice 8 columns for the second term
-#define SPL_TC_ASTAGES (SPL_TC_ASUPERS * SPL_TC_SUPER)
-#define SPL_TC_THREADS 480       // warps 0-3, 8-11 and 4-7: three dequant sets (units of two groups in turn); 12 copies; 13-14 tensor-core issue
+#define SPL_TC_AUNITS 5          // A operand slots in tensor memory, a unit (two groups, 64 columns) each, with 8 columns each for the second term
+#define SPL_TC_THREADS 512       // warps 0-3, 8-11 and 4-7: three dequant sets (units of two groups in turn); 12 copies weights; 14 copies activations; 13, 15 tensor-core issue
 
-// Stages of activations and scale/bias words: they are held until the tensor core has finished with them.
+// Stages of activations: held until the tensor core has finished with them. Stages of codes with their scale/bias
+// words (18 KiB each): handed back as soon as they are in registers.
 __host__ __device__ constexpr int spl_tc_bstages(int rn) { return rn >= 64 ? 4 : 6; }
-__host__ __device__ constexpr size_t spl_tc_bstage_bytes(int rn) { return size_t(SPL_TC_SUPER) * (size_t(rn) * 128 + 512); }
+__host__ __device__ constexpr int spl_tc_cstages(int rn) { return rn >= 64 ? 4 : 6; }
+__host__ __device__ constexpr size_t spl_tc_bstage_bytes(int rn) { return size_t(SPL_TC_SUPER) * size_t(rn) * 128; }
 __host__ __device__ constexpr size_t spl_tc_smem_bytes(int rn) {
-    return 1024 /* alignment slack */ + size_t(SPL_TC_CSTAGES) * SPL_TC_SUPER * 4096 + size_t(spl_tc_bstages(rn)) * spl_tc_bstage_bytes(rn)
+    return 1024 /* alignment slack */ + size_t(spl_tc_cstages(rn)) * SPL_TC_SUPER * (4096 + 512) + size_t(spl_tc_bstages(rn)) * spl_tc_bstage_bytes(rn)
            + size_t(2) * rn * 128 /* tiles of split means */ + 1024 /* barriers */;
 }
 __device__ __forceinline__ void spl_tc_st4(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
@@ -272,7 +292,7 @@ __global__ void __launch_bounds__(SPL_TC_THREADS, 1)
 spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__restrict__ sb, const __nv_bfloat16 *__restrict__ act,
                       const float *__restrict__ act_sums, float *out, int out_ld, const float *residual, float *partials,
                       int rows, int op_blocks, int groups, int groups_per_split, int *error_flag) {
-    constexpr int BST = spl_tc_bstages(RN), CST = SPL_TC_CSTAGES, AST = SPL_TC_ASTAGES, ASUP = SPL_TC_ASUPERS;
+    constexpr int BST = spl_tc_bstages(RN), CST = spl_tc_cstages(RN), AUN = SPL_TC_AUNITS;
     constexpr int BTILE = SPL_TC_SUPER * RN * 128, WSTAGE = SPL_TC_SUPER * 4096, QSTAGE = SPL_TC_SUPER * 128, TTILE = RN * 128;
     extern __shared__ unsigned char spl_tc_smem_raw[];
     // The swizzled activation tiles must sit on 1,024-byte boundaries.
@@ -280,10 +300,10 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     unsigned char *b_ring = smem;                                                       // [BST][SUPER][RN * 128] activations
     unsigned char *t_ring = b_ring + size_t(BST) * BTILE;                               // [2][RN * 128] split means of sixteen groups
     unsigned char *w_ring = t_ring + 2 * TTILE;                                         // [CST][SUPER][4096] codes
-    uint32_t *q_ring = reinterpret_cast<uint32_t *>(w_ring + size_t(CST) * WSTAGE);     // [BST][SUPER][128] scale | bias << 16
-    uint64_t *bars = reinterpret_cast<uint64_t *>(q_ring + BST * QSTAGE);
+    uint32_t *q_ring = reinterpret_cast<uint32_t *>(w_ring + size_t(CST) * WSTAGE);     // [CST][SUPER][128] scale | bias << 16
+    uint64_t *bars = reinterpret_cast<uint64_t *>(q_ring + CST * QSTAGE);
     uint64_t *full_c = bars, *empty_c = full_c + CST, *full_b = empty_c + CST, *empty_b = full_b + BST;
-    uint64_t *full_a = empty_b + BST, *full_t = full_a + AST / 2, *empty_t = full_t + 2, *finished = empty_t + 2;
+    uint64_t *full_a = empty_b + BST, *full_t = full_a + AUN, *empty_t = full_t + 2, *finished = empty_t + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(finished + 1);
 
 #ifdef SPL_TRACE
@@ -303,9 +323,9 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < CST; ++i) { spl_mbar_init(&full_c[i], 1); spl_mbar_init(&empty_c[i], 8); }       // the two sets (four warps each) that take the stage's units
-        for (int i = 0; i < BST; ++i) { spl_mbar_init(&full_b[i], 1); spl_mbar_init(&empty_b[i], 2); }       // the two issuing threads
-        for (int i = 0; i < AST / 2; ++i) spl_mbar_init(&full_a[i], 4);      // one per unit of two groups
-        for (int i = 0; i < 2; ++i) { spl_mbar_init(&full_t[i], 1); spl_mbar_init(&empty_t[i], 1); }
+        for (int i = 0; i < BST; ++i) { spl_mbar_init(&full_b[i], 1); spl_mbar_init(&empty_b[i], 2); }       // the two issuing warps' commits
+        for (int i = 0; i < AUN; ++i) spl_mbar_init(&full_a[i], 4);      // one per unit of two groups
+        for (int i = 0; i < 2; ++i) { spl_mbar_init(&full_t[i], 1); spl_mbar_init(&empty_t[i], 2); }
         spl_mbar_init(finished, 2);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -320,10 +340,9 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
 #ifdef SPL_TRACE
     if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && error_flag[1] == 0x7ACE) error_flag[22] = int(clock64() - t_entry);   // set-up
 #endif
-    // Each issuing thread has accumulators of its own (consecutive instructions into one accumulator wait for each other);
-    // the output adds them in order.
-    constexpr int NACC = RN <= 32 ? 4 : 2;
-    const uint32_t tmem_d = tmem, tmem_a = tmem + 128, tmem_aq = tmem + 128 + AST * 32;       // second-term operand: ASUP slots of 8 columns
+    // Two accumulators, one per issuing warp (instructions of different warps are not ordered against each other);
+    // the A ring, 64 columns a unit; the second-term operand, 8 columns a unit.
+    const uint32_t tmem_d = tmem, tmem_a = tmem + 128, tmem_aq = tmem + 128 + AUN * 64;
     bool ok = true;
     // Debug trace (builds with -DSPL_TRACE only): cycles per group that one thread of each role of block (0, 0, 0) spends
     // in its waits and its work.
@@ -339,38 +358,44 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
 #define SPL_TOUT(statement) do { } while (0)
 #endif
 
-    if (!(warp == 12 && lane == 0)) spl_grid_begin();     // the copying thread first asks for weights (below)
+    if (!(warp == 12 && lane == 0)) spl_grid_begin();     // the thread that copies weights first asks for some (below)
     if (warp == 12) {
-        // ---- copies. Codes have their own ring; activations and the scale/bias words share another; the split means a third.
+        // ---- copies of weights: codes and their scale/bias words, one ring.
         if (lane == 0) {
             const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(codes) + (size_t(tile) * groups + g_first) * 4096;
-            const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(act) + ((size_t(g_first) * row_blocks + rb) * RN) * 128;
-            const unsigned char *tsrc = reinterpret_cast<const unsigned char *>(act_sums);
             const uint32_t *qsrc = sb + (size_t(tile) * groups + g_first) * 128;
-            // The weights are nobody's output: the first stages of codes are asked for before this kernel waits for its
+            // The weights are nobody's output: the first stages are asked for before this kernel waits for its
             // predecessor in the stream, so they arrive while that one is still finishing.
             const int ahead = min(CST, supers);
-            for (int j0 = 0; j0 < ahead; ++j0) {
-                const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
-                const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);
-                spl_mbar_expect_tx(&full_c[j0], uint32_t(n) * 4096);
-                spl_bulk_g2s(w_ring + size_t(j0) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[j0]);
-            }
-            spl_grid_begin();
-            int mean_tile = -1, mean_loads = 0;
             for (int j0 = 0; j0 < supers && ok; ++j0) {
+                if (j0 == ahead) spl_grid_begin();
                 const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;      // the stage's source; j0 is its place in the pipeline
                 const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);         // with a rotation every stage is full
-                const int sc = j0 % CST, sbq = j0 % BST;
+                const int sc = j0 % CST;
                 SPL_T0();
                 if (j0 >= ahead) {
                     ok = spl_mbar_wait(&empty_c[sc], ((j0 / CST) & 1) ^ 1);
                     SPL_T1(t0);
                     if (!ok) break;
-                    spl_mbar_expect_tx(&full_c[sc], uint32_t(n) * 4096);
-                    spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[sc]);
                 }
+                spl_mbar_expect_tx(&full_c[sc], uint32_t(n) * (4096 + 512));
+                spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[sc]);
+                spl_bulk_g2s(q_ring + sc * QSTAGE, qsrc + size_t(j) * QSTAGE, uint32_t(n) * 512, &full_c[sc]);
                 SPL_T1(t2);
+            }
+            if (supers <= ahead) spl_grid_begin();
+            SPL_TOUT(if (trace) { error_flag[8] = int(t0 / g_count); error_flag[10] = int(t2 / g_count); });
+        }
+    } else if (warp == 14) {
+        // ---- copies of activations and of the tiles of split means.
+        if (lane == 0) {
+            const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(act) + ((size_t(g_first) * row_blocks + rb) * RN) * 128;
+            const unsigned char *tsrc = reinterpret_cast<const unsigned char *>(act_sums);
+            int mean_tile = -1, mean_loads = 0;
+            for (int j0 = 0; j0 < supers && ok; ++j0) {
+                const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
+                const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);
+                const int sbq = j0 % BST;
                 // The tile of split means that holds this stage's groups (sixteen groups to a tile).
                 const int want = (g_first / SPL_TC_SUPER + j) >> 2;
                 if (want != mean_tile) {
@@ -381,11 +406,11 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                     spl_bulk_g2s(t_ring + slot * TTILE, tsrc + (size_t(want) * row_blocks + rb) * TTILE, TTILE, &full_t[slot]);
                     mean_tile = want; ++mean_loads;
                 }
+                SPL_T0();
                 ok = spl_mbar_wait(&empty_b[sbq], ((j0 / BST) & 1) ^ 1);
                 SPL_T1(t1);
                 if (!ok) break;
-                spl_mbar_expect_tx(&full_b[sbq], uint32_t(n) * (RN * 128 + 512));
-                spl_bulk_g2s(q_ring + sbq * QSTAGE, qsrc + size_t(j) * QSTAGE, uint32_t(n) * 512, &full_b[sbq]);
+                spl_mbar_expect_tx(&full_b[sbq], uint32_t(n) * RN * 128);
                 if (row_blocks == 1) {
                     spl_bulk_g2s(b_ring + size_t(sbq) * BTILE, bsrc + size_t(j) * BTILE, uint32_t(n) * RN * 128, &full_b[sbq]);
                 } else {
@@ -394,74 +419,71 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                         spl_bulk_g2s(b_ring + size_t(sbq) * BTILE + u * RN * 128, bsrc + g * row_blocks * RN * 128, RN * 128, &full_b[sbq]);
                     }
                 }
-                SPL_T1(t2);
             }
-            SPL_TOUT(if (trace) { error_flag[8] = int(t0 / g_count); error_flag[9] = int(t1 / g_count); error_flag[10] = int(t2 / g_count); });
+            SPL_TOUT(if (trace) { error_flag[9] = int(t1 / g_count); });
         }
-    } else if (warp >= 13) {
+    } else if (warp == 13 || warp == 15) {
         // ---- tensor-core issue: D[128 x RN] += A[128 x 64] (fp16, tensor memory) * B[RN x 64]^T (fp16, shared memory).
-        // Issuing one tcgen05.mma costs its thread about ninety cycles, so two threads share the work: warp 13 issues
-        // the first two k16 steps of every group and warp 14 the last two, each into accumulators of its own; warp 13
-        // also issues each stage's second-term instruction.
-        const int m = warp - 13;
-        if (lane == 0) {
-            constexpr uint32_t idesc = spl_tc_idesc(RN);
-            int mean_tile = -1, mean_loads = 0, mean_slot = 0;
-            // The issuing thread is one lane running scalar code, so its instruction count matters: descriptors and
-            // tensor-memory addresses are a base per stage plus compile-time offsets.
-            const uint64_t b_desc0 = spl_tc_desc_sw128(spl_smem_addr(b_ring)), t_desc0 = spl_tc_desc_sw128(spl_smem_addr(t_ring));
-            uint32_t accumulate = 0u;          // the thread's first instructions overwrite its accumulators
-            for (int j0 = 0; j0 < supers && ok; ++j0) {
-                const int sbq = j0 % BST, n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);
-                const uint64_t b_desc = b_desc0 + uint64_t((sbq * BTILE) >> 4);
-                const uint32_t a_base = tmem_a + (j0 % ASUP) * (SPL_TC_SUPER * 32);
-                SPL_T0();
-                ok = spl_mbar_wait(&full_b[sbq], (j0 / BST) & 1);
-                SPL_T1(t0);
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    if (2 * half >= n) break;
-                    const int un = 2 * j0 + half;
-                    ok = ok && spl_mbar_wait(&full_a[un % (AST / 2)], (un / (AST / 2)) & 1);
-                    SPL_T1(t1);
-                    if (!ok) break;
-                    spl_tc_fence_after();
-#pragma unroll
-                    for (int v = 0; v < 2; ++v) {
-                        const int u = 2 * half + v;
-                        if (u >= n) break;
-#pragma unroll
-                        for (int l = 0; l < 2; ++l) {
-                            const int ks = 2 * m + l;
-                            const int acc = NACC == 4 ? ks : m;                       // this thread's accumulator for the step
-                            spl_tc_mma_ts(tmem_d + acc * RN, a_base + u * 32 + ks * 8, b_desc + uint64_t((u * RN * 128 + ks * 32) >> 4), idesc,
-                                          (NACC == 2 && l > 0) ? 1u : accumulate);
-                        }
-                        accumulate = 1u;
-                    }
-                    SPL_T1(t2);
-                }
+        // The whole warp runs the loop and its waits; one elected lane issues (spl_elect_one). An elected lane is held
+        // while the tensor pipe works through its instructions, and a wait on a barrier costs its latency even when the
+        // phase is complete, so two warps take the units in turn (warp 13 the first unit of every stage, warp 15 the
+        // second), each into an accumulator of its own: one warp's waits run under the other's instructions. A unit is
+        // eight k16 instructions at fixed offsets from the unit's bases and a ninth for its share of the second term
+        // (the unit's 8 values of that contraction; the other 8 columns of its operand slot are zero).
+        const int m = warp == 13 ? 0 : 1;
+        constexpr uint32_t idesc = spl_tc_idesc(RN);
+        int mean_tile = -1, mean_loads = 0, mean_slot = 0;
+        const uint64_t b_desc0 = spl_tc_desc_sw128(spl_smem_addr(b_ring)), t_desc0 = spl_tc_desc_sw128(spl_smem_addr(t_ring));
+        const uint32_t d_mine = tmem_d + m * RN;
+        int slot = m;                                      // un % AUN
+        uint32_t a_parity = 0;                             // (un / AUN) & 1
+        for (int un = m; un < units && ok; un += 2) {
+            const int j0 = un >> 1, sbq = j0 % BST, n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER) - 2 * m;     // groups of this unit: 1 or 2
+            const uint64_t b_desc = b_desc0 + uint64_t((sbq * BTILE + m * 2 * RN * 128) >> 4);
+            const uint32_t a_base = tmem_a + slot * 64;
+            // The stage's share of the second term: its 16 values of the contraction are a quarter of a 128-byte row of the tile.
+            const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
+            const int quarter = g_first / SPL_TC_SUPER + j, want = quarter >> 2;
+            SPL_T0();
+            if (want != mean_tile) {
+                if (mean_tile >= 0 && spl_elect_one()) spl_tc_commit(&empty_t[mean_slot]);      // every instruction of this warp that read the old tile has been issued
+                __syncwarp();
+                mean_slot = mean_loads & 1;
+                ok = spl_mbar_wait_warp(&full_t[mean_slot], (mean_loads >> 1) & 1);
                 if (!ok) break;
-                if (m == 0) {
-                    // The stage's second term: its 16 values of the contraction are a quarter of a 128-byte row of the tile.
-                    const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
-                    const int quarter = g_first / SPL_TC_SUPER + j, want = quarter >> 2;
-                    if (want != mean_tile) {
-                        if (mean_tile >= 0) spl_tc_commit(&empty_t[mean_slot]);      // every instruction that read the old tile has been issued
-                        mean_slot = mean_loads & 1;
-                        ok = spl_mbar_wait(&full_t[mean_slot], (mean_loads >> 1) & 1);
-                        if (!ok) break;
-                        mean_tile = want; ++mean_loads;
-                    }
-                    spl_tc_mma_ts(tmem_d, tmem_aq + (j0 % ASUP) * 8, t_desc0 + uint64_t((mean_slot * TTILE + (quarter & 3) * 32) >> 4), idesc, 1u);
-                }
-                spl_tc_commit(&empty_b[sbq]);                 // the stage's instructions have completed: its activations and its A slots are free
-                SPL_T1(t2);
+                mean_tile = want; ++mean_loads;
             }
-            SPL_TOUT(if (trace && m == 0) { error_flag[11] = int(t0 / g_count); error_flag[12] = int(t1 / g_count); error_flag[13] = int(t2 / g_count); });
-            SPL_TOUT(if (trace && m == 0) error_flag[24] = int(clock64() - t_entry));     // last instruction issued
-            if (ok) spl_tc_commit(finished);
+            ok = spl_mbar_wait_warp(&full_b[sbq], (j0 / BST) & 1);
+            SPL_T1(t0);
+            if (!ok) break;
+            ok = spl_mbar_wait_warp(&full_a[slot], a_parity);
+            SPL_T1(t1);
+            if (!ok) break;
+            spl_tc_fence_after();
+            const uint64_t t_desc = t_desc0 + uint64_t((mean_slot * TTILE + (quarter & 3) * 32) >> 4);
+            if (n >= 2 && un >= 2) {                             // the common case: nothing to decide between the instructions
+                if (spl_elect_one()) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q)
+                        spl_tc_mma_ts_acc(d_mine, a_base + q * 8, b_desc + uint64_t(((q >> 2) * RN * 128 + (q & 3) * 32) >> 4), idesc);
+                    spl_tc_mma_ts_acc(d_mine, tmem_aq + slot * 8, t_desc, idesc);
+                    spl_tc_commit(&empty_b[sbq]);             // with the other warp's commit: the stage's activations are free
+                }
+            } else if (spl_elect_one()) {                        // the warp's first unit (it overwrites the accumulator) and a unit of one group
+                for (int q = 0; q < 8; ++q)
+                    if ((q >> 2) < n)
+                        spl_tc_mma_ts(d_mine, a_base + q * 8, b_desc + uint64_t(((q >> 2) * RN * 128 + (q & 3) * 32) >> 4), idesc, (un >= 2 || q) ? 1u : 0u);
+                spl_tc_mma_ts_acc(d_mine, tmem_aq + slot * 8, t_desc, idesc);
+                spl_tc_commit(&empty_b[sbq]);
+            }
+            __syncwarp();
+            SPL_T1(t2);
+            slot += 2; if (slot >= AUN) { slot -= AUN; a_parity ^= 1u; }
         }
+        SPL_TOUT(if (trace && lane == 0 && m == 0) { error_flag[11] = int(t0 / g_count); error_flag[12] = int(t1 / g_count); error_flag[13] = int(t2 / g_count); });
+        SPL_TOUT(if (trace && lane == 0 && m == 0) error_flag[24] = int(clock64() - t_entry));     // last instruction issued
+        if (ok && spl_elect_one()) spl_tc_commit(finished);
+        __syncwarp();
     } else {
         // ---- dequant: thread = output column; codes -> scale * (code - 8), exact in fp16 -> tensor memory. Three sets
         // of four warps (0-3, 8-11, 4-7) take the units of two groups in turn; a set's warps write the lanes of their
@@ -470,9 +492,9 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
         const __half2 c1032 = __floats2half2_rn(1032.0f, 1032.0f), c1152 = __floats2half2_rn(1152.0f, 1152.0f);
         for (int un = set; un < units && ok; un += 3) {
-            const int j = un >> 1, half = un & 1, sc = j % CST, sbq = j % BST;
+            const int j = un >> 1, half = un & 1, sc = j % CST;
             SPL_T0();
-            ok = spl_mbar_wait(&full_c[sc], (j / CST) & 1) && spl_mbar_wait(&full_b[sbq], (j / BST) & 1);
+            ok = spl_mbar_wait(&full_c[sc], (j / CST) & 1);
             SPL_TOUT(if (trace && warp == 0 && lane == 0 && un == 0) error_flag[23] = int(clock64() - t_entry));     // first stage has landed
             SPL_T1(t0);
             if (!ok) break;
@@ -486,54 +508,57 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                 if (u < n) {
                     lo[v] = *reinterpret_cast<const uint4 *>(w_ring + size_t(sc) * WSTAGE + u * 4096 + col * 16);
                     hi[v] = *reinterpret_cast<const uint4 *>(w_ring + size_t(sc) * WSTAGE + u * 4096 + 2048 + col * 16);
-                    sbw[v] = q_ring[sbq * QSTAGE + u * 128 + col];
+                    sbw[v] = q_ring[sc * QSTAGE + u * 128 + col];
                 }
             }
             __syncwarp();
             if (lane == 0) spl_mbar_arrive(&empty_c[sc]);
+            SPL_T1(t1);
+            // The unit's slot was last used by unit un - AUN: the stage that unit belongs to has to have completed.
+            const int slot = un % AUN;
+            if (un >= AUN) { const int jr = (un - AUN) >> 1; ok = spl_mbar_wait(&empty_b[jr % BST], (jr / BST) & 1); }
+            SPL_T1(t2);
+            if (!ok) break;
+            spl_tc_fence_after();
             // Nibbles in place: 0x6400 | c is 1024 + c and 0x6400 | (c << 4) is 1024 + 16 c in fp16, so that
             // (q - 1032) * s and (q - 1152) * (s / 16) are both scale * (c - 8), exactly; one shift serves four nibbles.
-            uint32_t a[2][32], aq[4];
+            // Sixteen registers (32 weights) are converted and stored at a time.
+            uint32_t aq[4];
 #pragma unroll
             for (int v = 0; v < 2; ++v) {
                 const float sf = __uint_as_float(sbw[v] << 16), bf = __uint_as_float(sbw[v] & 0xFFFF0000u);
                 const __half2 s2 = __float2half2_rn(sf), s16 = __float2half2_rn(sf * 0.0625f);
                 const __half2 q1 = __float2half2_rn(bf * 64.0f), q2 = __float2half2_rn(sf * 512.0f);      // zero for a group past the end
                 aq[2 * v] = *reinterpret_cast<const uint32_t *>(&q1); aq[2 * v + 1] = *reinterpret_cast<const uint32_t *>(&q2);
-                const uint32_t w8[8] = {lo[v].x, lo[v].y, lo[v].z, lo[v].w, hi[v].x, hi[v].y, hi[v].z, hi[v].w};
-#pragma unroll
-                for (int w = 0; w < 8; ++w) {
-                    const uint32_t x0 = w8[w], x1 = w8[w] >> 8;
-                    uint32_t p0 = (x0 & 0x000F000Fu) | 0x64006400u, p1 = (x0 & 0x00F000F0u) | 0x64006400u;
-                    uint32_t p2 = (x1 & 0x000F000Fu) | 0x64006400u, p3 = (x1 & 0x00F000F0u) | 0x64006400u;
-                    const __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p0), c1032), s2);
-                    const __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p1), c1152), s16);
-                    const __half2 h2 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p2), c1032), s2);
-                    const __half2 h3 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p3), c1152), s16);
-                    a[v][4 * w + 0] = *reinterpret_cast<const uint32_t *>(&h0); a[v][4 * w + 1] = *reinterpret_cast<const uint32_t *>(&h1);
-                    a[v][4 * w + 2] = *reinterpret_cast<const uint32_t *>(&h2); a[v][4 * w + 3] = *reinterpret_cast<const uint32_t *>(&h3);
-                }
-            }
-            SPL_T1(t1);
-            // The A slots were last used ASUP stages ago; that stage's completion is the one its activation stage is freed by.
-            if (j >= ASUP) ok = spl_mbar_wait(&empty_b[(j - ASUP) % BST], ((j - ASUP) / BST) & 1);
-            SPL_T1(t2);
-            if (!ok) break;
-            spl_tc_fence_after();
-#pragma unroll
-            for (int v = 0; v < 2; ++v) {
-                const int i = j * SPL_TC_SUPER + 2 * half + v, sa = i % AST;
                 if (2 * half + v < n) {
-                    spl_tc_st16(tmem_a + lane_base + sa * 32, *reinterpret_cast<uint32_t (*)[16]>(&a[v][0]));
-                    spl_tc_st16(tmem_a + lane_base + sa * 32 + 16, *reinterpret_cast<uint32_t (*)[16]>(&a[v][16]));
+#pragma unroll
+                    for (int part = 0; part < 2; ++part) {
+                        const uint4 src = part == 0 ? lo[v] : hi[v];
+                        const uint32_t w4[4] = {src.x, src.y, src.z, src.w};
+                        uint32_t a[16];
+#pragma unroll
+                        for (int w = 0; w < 4; ++w) {
+                            const uint32_t x0 = w4[w], x1 = w4[w] >> 8;
+                            uint32_t p0 = (x0 & 0x000F000Fu) | 0x64006400u, p1 = (x0 & 0x00F000F0u) | 0x64006400u;
+                            uint32_t p2 = (x1 & 0x000F000Fu) | 0x64006400u, p3 = (x1 & 0x00F000F0u) | 0x64006400u;
+                            const __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p0), c1032), s2);
+                            const __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p1), c1152), s16);
+                            const __half2 h2 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p2), c1032), s2);
+                            const __half2 h3 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p3), c1152), s16);
+                            a[4 * w + 0] = *reinterpret_cast<const uint32_t *>(&h0); a[4 * w + 1] = *reinterpret_cast<const uint32_t *>(&h1);
+                            a[4 * w + 2] = *reinterpret_cast<const uint32_t *>(&h2); a[4 * w + 3] = *reinterpret_cast<const uint32_t *>(&h3);
+                        }
+                        spl_tc_st16(tmem_a + lane_base + slot * 64 + v * 32 + part * 16, a);
+                    }
                 }
             }
-            spl_tc_st4(tmem_aq + lane_base + (j % ASUP) * 8 + half * 4, aq[0], aq[1], aq[2], aq[3]);
-            if (n <= 2) spl_tc_st4(tmem_aq + lane_base + (j % ASUP) * 8 + 4, 0u, 0u, 0u, 0u);       // a short last stage has no second unit
+            // The unit's share of the second-term operand sits at its place among the stage's sixteen values; the rest is zero.
+            if (half == 0) { spl_tc_st4(tmem_aq + lane_base + slot * 8, aq[0], aq[1], aq[2], aq[3]); spl_tc_st4(tmem_aq + lane_base + slot * 8 + 4, 0u, 0u, 0u, 0u); }
+            else { spl_tc_st4(tmem_aq + lane_base + slot * 8, 0u, 0u, 0u, 0u); spl_tc_st4(tmem_aq + lane_base + slot * 8 + 4, aq[0], aq[1], aq[2], aq[3]); }
             spl_tc_st_wait();
             spl_tc_fence_before();
             __syncwarp();
-            if (lane == 0) spl_mbar_arrive(&full_a[un % (AST / 2)]);
+            if (lane == 0) spl_mbar_arrive(&full_a[slot]);
             SPL_T1(t3);
         }
         SPL_TOUT(if (trace && warp == 0 && lane == 0) { error_flag[14] = int(t0 / g_count); error_flag[15] = int(t1 / g_count); error_flag[16] = int(t2 / g_count); error_flag[17] = int(t3 / g_count); error_flag[21] = g_count; });
@@ -552,7 +577,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                 const int c0 = cb * 16;
                 float total[16];
 #pragma unroll
-                for (int a = 0; a < NACC; ++a) {
+                for (int a = 0; a < (units > 1 ? 2 : 1); ++a) {
                     uint32_t v[16];
                     spl_tc_ld16(v, tmem_d + lane_base + a * RN + c0);
 #pragma unroll
