@@ -490,7 +490,6 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         // warp index mod 4. A unit also carries its two groups' pairs of the second-term operand.
         const int quarter = warp & 3, col = quarter * 32 + lane, set = warp < 4 ? 0 : warp >= 8 ? 1 : 2;
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-        const __half2 c1032 = __floats2half2_rn(1032.0f, 1032.0f), c1152 = __floats2half2_rn(1152.0f, 1152.0f);
         for (int un = set; un < units && ok; un += 3) {
             const int j = un >> 1, half = un & 1, sc = j % CST;
             SPL_T0();
@@ -520,14 +519,16 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             SPL_T1(t2);
             if (!ok) break;
             spl_tc_fence_after();
-            // Nibbles in place: 0x6400 | c is 1024 + c and 0x6400 | (c << 4) is 1024 + 16 c in fp16, so that
-            // (q - 1032) * s and (q - 1152) * (s / 16) are both scale * (c - 8), exactly; one shift serves four nibbles.
-            // Sixteen registers (32 weights) are converted and stored at a time.
+            // A nibble moved to mantissa bits 6-9 under the exponent of 16 (0x4C00) is the fp16 number 16 + c, and
+            // fma(16 + c, s, -24 s) = s * (c - 8) with one rounding of a result that fp16 holds exactly; -24 s is exact in
+            // fp16 too (3 * 8 significant bits). One shift and one logic operation place the nibbles of both halves of a
+            // word, one fused multiply-add converts the pair. Sixteen registers (32 weights) are converted and stored at a time.
             uint32_t aq[4];
 #pragma unroll
             for (int v = 0; v < 2; ++v) {
                 const float sf = __uint_as_float(sbw[v] << 16), bf = __uint_as_float(sbw[v] & 0xFFFF0000u);
-                const __half2 s2 = __float2half2_rn(sf), s16 = __float2half2_rn(sf * 0.0625f);
+                const __half2 s2h = __float2half2_rn(sf), m24h = __float2half2_rn(sf * -24.0f);
+                const uint32_t s2 = *reinterpret_cast<const uint32_t *>(&s2h), m24 = *reinterpret_cast<const uint32_t *>(&m24h);
                 const __half2 q1 = __float2half2_rn(bf * 64.0f), q2 = __float2half2_rn(sf * 512.0f);      // zero for a group past the end
                 aq[2 * v] = *reinterpret_cast<const uint32_t *>(&q1); aq[2 * v + 1] = *reinterpret_cast<const uint32_t *>(&q2);
                 if (2 * half + v < n) {
@@ -537,17 +538,17 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                         const uint32_t w4[4] = {src.x, src.y, src.z, src.w};
                         uint32_t a[16];
 #pragma unroll
-                        for (int w = 0; w < 4; ++w) {
-                            const uint32_t x0 = w4[w], x1 = w4[w] >> 8;
-                            uint32_t p0 = (x0 & 0x000F000Fu) | 0x64006400u, p1 = (x0 & 0x00F000F0u) | 0x64006400u;
-                            uint32_t p2 = (x1 & 0x000F000Fu) | 0x64006400u, p3 = (x1 & 0x00F000F0u) | 0x64006400u;
-                            const __half2 h0 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p0), c1032), s2);
-                            const __half2 h1 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p1), c1152), s16);
-                            const __half2 h2 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p2), c1032), s2);
-                            const __half2 h3 = __hmul2(__hsub2(*reinterpret_cast<__half2 *>(&p3), c1152), s16);
-                            a[4 * w + 0] = *reinterpret_cast<const uint32_t *>(&h0); a[4 * w + 1] = *reinterpret_cast<const uint32_t *>(&h1);
-                            a[4 * w + 2] = *reinterpret_cast<const uint32_t *>(&h2); a[4 * w + 3] = *reinterpret_cast<const uint32_t *>(&h3);
-                        }
+                        for (int w = 0; w < 4; ++w)
+                            asm("{\n .reg .b32 xa, xb, xc, xd;\n"
+                                " shl.b32 xa, %4, 6;\n shl.b32 xb, %4, 2;\n shr.b32 xc, %4, 2;\n shr.b32 xd, %4, 6;\n"
+                                " lop3.b32 xa, xa, 0x03C003C0, 0x4C004C00, 0xEA;\n"
+                                " lop3.b32 xb, xb, 0x03C003C0, 0x4C004C00, 0xEA;\n"
+                                " lop3.b32 xc, xc, 0x03C003C0, 0x4C004C00, 0xEA;\n"
+                                " lop3.b32 xd, xd, 0x03C003C0, 0x4C004C00, 0xEA;\n"
+                                " fma.rn.f16x2 %0, xa, %5, %6;\n fma.rn.f16x2 %1, xb, %5, %6;\n"
+                                " fma.rn.f16x2 %2, xc, %5, %6;\n fma.rn.f16x2 %3, xd, %5, %6;\n}\n"
+                                : "=r"(a[4 * w]), "=r"(a[4 * w + 1]), "=r"(a[4 * w + 2]), "=r"(a[4 * w + 3])
+                                : "r"(w4[w]), "r"(s2), "r"(m24));
                         spl_tc_st16(tmem_a + lane_base + slot * 64 + v * 32 + part * 16, a);
                     }
                 }
