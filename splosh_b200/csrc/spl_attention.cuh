@@ -302,65 +302,67 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
         }
     } else if (warp == 13) {
         // ---- tensor-core issue, score product: S^T[buffer] = K (tensor memory) x Q (shared memory), sixteen channels per instruction.
-        // (Issuing an instruction costs its thread on the order of a hundred cycles, so the two products have a thread each.)
-        if (lane == 0) {
-            constexpr uint32_t idesc = spl_tc_idesc(NQ);
-            const uint64_t q_desc = spl_tc_desc_sw128(spl_smem_addr(q_tile));
-            for (int i = 0; i < chunks && ok; ++i) {
-                const int buf = i & 1;
-                SPL_A0();
-                ok = spl_mbar_wait(&s_free[buf], ((i >> 1) & 1) ^ 1);
-                SPL_A1(0);
+        // The whole warp runs the loop and its waits and one elected lane issues (spl_elect_one); the two products have
+        // a warp each, so that one's waits run under the other's instructions.
+        constexpr uint32_t idesc = spl_tc_idesc(NQ);
+        const uint64_t q_desc = spl_tc_desc_sw128(spl_smem_addr(q_tile));
+        for (int i = 0; i < chunks && ok; ++i) {
+            const int buf = i & 1;
+            SPL_A0();
+            ok = spl_mbar_wait_warp(&s_free[buf], ((i >> 1) & 1) ^ 1);
+            SPL_A1(0);
+            if (!ok) break;
 #pragma unroll
-                for (int h = 0; h < HALVES; ++h) {
-                    const int piece = i * HALVES + h, slot = piece % 3;
-                    ok = ok && spl_mbar_wait(&ka_full[slot], (piece / 3) & 1);
-                    SPL_A1(1);
-                    if (!ok) break;
-                    spl_tc_fence_after();
+            for (int h = 0; h < HALVES; ++h) {
+                const int piece = i * HALVES + h, slot = piece % 3;
+                ok = spl_mbar_wait_warp(&ka_full[slot], (piece / 3) & 1);
+                SPL_A1(1);
+                if (!ok) break;
+                spl_tc_fence_after();
+                if (spl_elect_one()) {
 #pragma unroll
                     for (int ks = 0; ks < 8; ++ks) {
                         const int step = h * 8 + ks;
-                        spl_tc_mma_ts(tmem_s + buf * NQ, tmem_ka + slot * 64 + ks * 8, q_desc + uint64_t(((step >> 2) * QTILE + (step & 3) * 32) >> 4), idesc, step > 0 ? 1u : 0u);
+                        if (step == 0) spl_tc_mma_ts(tmem_s + buf * NQ, tmem_ka + slot * 64 + ks * 8, q_desc + uint64_t(((step >> 2) * QTILE + (step & 3) * 32) >> 4), idesc, 0u);
+                        else spl_tc_mma_ts_acc(tmem_s + buf * NQ, tmem_ka + slot * 64 + ks * 8, q_desc + uint64_t(((step >> 2) * QTILE + (step & 3) * 32) >> 4), idesc);
                     }
                     spl_tc_commit(&ka_free[slot]);
-                    SPL_A1(2);
+                    if (h == HALVES - 1) spl_tc_commit(&s_full[buf]);
                 }
-                if (!ok) break;
-                spl_tc_commit(&s_full[buf]);
+                __syncwarp();
                 SPL_A1(2);
             }
-            SPL_AOUT(34, 3);
         }
+        if (lane == 0) SPL_AOUT(34, 3);
     } else if (warp == 14) {
         // ---- tensor-core issue, value product: O^T[half] += V^T (tensor memory) x P (shared memory), sixteen tokens per instruction.
-        if (lane == 0) {
-            constexpr uint32_t idesc = spl_tc_idesc(NQ);
-            const uint64_t p_desc = spl_tc_desc_sw128(spl_smem_addr(p_tile));
-            for (int i = 0; i < chunks && ok; ++i) {
-                const int pb = i & 1;
-                SPL_A0();
-                ok = spl_mbar_wait(&p_full[pb], (i >> 1) & 1);
-                SPL_A1(0);
+        constexpr uint32_t idesc = spl_tc_idesc(NQ);
+        const uint64_t p_desc = spl_tc_desc_sw128(spl_smem_addr(p_tile));
+        for (int i = 0; i < chunks && ok; ++i) {
+            const int pb = i & 1;
+            SPL_A0();
+            ok = spl_mbar_wait_warp(&p_full[pb], (i >> 1) & 1);
+            SPL_A1(0);
+            if (!ok) break;
 #pragma unroll
-                for (int h = 0; h < HALVES; ++h) {
-                    ok = ok && spl_mbar_wait(&va_full[h], i & 1);
-                    SPL_A1(1);
-                    if (!ok) break;
-                    spl_tc_fence_after();
-#pragma unroll
-                    for (int ks = 0; ks < 8; ++ks)
-                        spl_tc_mma_ts(tmem_o + h * NQ, tmem_va + h * 64 + ks * 8, p_desc + uint64_t((pb * PTILE + (ks >> 2) * QTILE + (ks & 3) * 32) >> 4), idesc, (i > 0 || ks > 0) ? 1u : 0u);
-                    spl_tc_commit(&va_free[h]);
-                    SPL_A1(2);
-                }
+            for (int h = 0; h < HALVES; ++h) {
+                ok = spl_mbar_wait_warp(&va_full[h], i & 1);
+                SPL_A1(1);
                 if (!ok) break;
-                spl_tc_commit(&p_free[pb]);
-                spl_tc_commit(&o_done[pb]);
+                spl_tc_fence_after();
+                if (spl_elect_one()) {
+                    spl_tc_mma_ts(tmem_o + h * NQ, tmem_va + h * 64, p_desc + uint64_t((pb * PTILE) >> 4), idesc, i > 0 ? 1u : 0u);
+#pragma unroll
+                    for (int ks = 1; ks < 8; ++ks)
+                        spl_tc_mma_ts_acc(tmem_o + h * NQ, tmem_va + h * 64 + ks * 8, p_desc + uint64_t((pb * PTILE + (ks >> 2) * QTILE + (ks & 3) * 32) >> 4), idesc);
+                    spl_tc_commit(&va_free[h]);
+                    if (h == HALVES - 1) { spl_tc_commit(&p_free[pb]); spl_tc_commit(&o_done[pb]); }
+                }
+                __syncwarp();
                 SPL_A1(2);
             }
-            SPL_AOUT(37, 3);
         }
+        if (lane == 0) SPL_AOUT(37, 3);
     } else if (warp >= 4 && warp < 8) {
         // ---- K: thread = token. Its head_dim int8 -> fp16 pairs -> tensor memory, 128 channels (a 64-column slot of the ring) at a time.
         const int token = (warp & 3) * 32 + lane;

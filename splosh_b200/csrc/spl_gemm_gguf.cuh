@@ -215,39 +215,44 @@ spl_gemm_gguf_tc_kernel(const unsigned char *__restrict__ blocks, const __nv_bfl
             }
         }
     } else if (warp >= 13) {
+        // The whole warp runs the loop and its waits; one elected lane issues (spl_elect_one). Warp 13 issues the first
+        // two k16 steps of every group and warp 14 the last two, each into accumulators of its own.
         const int m = warp - 13;
-        if (lane == 0) {
-            constexpr uint32_t idesc = spl_tc_idesc(RN);
-            const uint64_t b_desc0 = spl_tc_desc_sw128(spl_smem_addr(b_ring));
-            uint32_t accumulate = 0u;
-            for (int j = 0; j < supers && ok; ++j) {
-                const int sbq = j % BST;
-                const uint64_t b_desc = b_desc0 + uint64_t((sbq * BTILE) >> 4);
-                const uint32_t a_base = tmem_a + (j % ASUP) * (SPL_TC_SUPER * 32);
-                ok = spl_mbar_wait(&full_b[sbq], (j / BST) & 1);
+        constexpr uint32_t idesc = spl_tc_idesc(RN);
+        const uint64_t b_desc0 = spl_tc_desc_sw128(spl_smem_addr(b_ring));
+        for (int j = 0; j < supers && ok; ++j) {
+            const int sbq = j % BST;
+            const uint64_t b_desc = b_desc0 + uint64_t((sbq * BTILE) >> 4);
+            const uint32_t a_base = tmem_a + (j % ASUP) * (SPL_TC_SUPER * 32);
+            ok = spl_mbar_wait_warp(&full_b[sbq], (j / BST) & 1);
+            if (!ok) break;
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    const int un = 2 * j + half;
-                    ok = ok && spl_mbar_wait(&full_a[un % (AST / 2)], (un / (AST / 2)) & 1);
-                    if (!ok) break;
-                    spl_tc_fence_after();
+            for (int half = 0; half < 2; ++half) {
+                const int un = 2 * j + half;
+                ok = spl_mbar_wait_warp(&full_a[un % (AST / 2)], (un / (AST / 2)) & 1);
+                if (!ok) break;
+                spl_tc_fence_after();
+                if (spl_elect_one()) {
 #pragma unroll
                     for (int v = 0; v < 2; ++v) {
                         const int u = 2 * half + v;
 #pragma unroll
                         for (int l = 0; l < 2; ++l) {
                             const int ks = 2 * m + l, acc = NACC == 4 ? ks : m;
-                            spl_tc_mma_ts(tmem_d + acc * RN, a_base + u * 32 + ks * 8, b_desc + uint64_t((u * RN * 128 + ks * 32) >> 4), idesc,
-                                          (NACC == 2 && l > 0) ? 1u : accumulate);
+                            const uint32_t d = tmem_d + acc * RN, a = a_base + u * 32 + ks * 8;
+                            const uint64_t b = b_desc + uint64_t((u * RN * 128 + ks * 32) >> 4);
+                            if (NACC == 2 && l > 0) spl_tc_mma_ts_acc(d, a, b, idesc);
+                            else if (j > 0 || u > 0) spl_tc_mma_ts_acc(d, a, b, idesc);
+                            else spl_tc_mma_ts(d, a, b, idesc, 0u);
                         }
-                        accumulate = 1u;
                     }
+                    if (half == 1) spl_tc_commit(&empty_b[sbq]);
                 }
-                if (!ok) break;
-                spl_tc_commit(&empty_b[sbq]);
+                __syncwarp();
             }
-            if (ok) spl_tc_commit(finished);
         }
+        if (ok && spl_elect_one()) spl_tc_commit(finished);
+        __syncwarp();
     } else {
         const int quarter = warp & 3, col = quarter * 32 + lane, set = warp < 4 ? 0 : warp >= 8 ? 1 : 2;
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
