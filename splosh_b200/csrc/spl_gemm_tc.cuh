@@ -11,17 +11,21 @@
 // Shape of the computation. The product is taken transposed, D[n][r] = w[n][k] * a[r][k]^T, so
 // that 128 output columns are the M dimension of one tcgen05.mma and the step's rows (16..64 per
 // tile) are its N dimension. Per quant group (K = 64, four k16 instructions):
-//   * TMA bulk copies bring four groups at a time into shared memory: 16 KiB of codes, and the
-//     activations' slice with the scale/bias words; a tile of split means serves sixteen groups;
-//   * dequant warps (one thread per output column, three sets taking units of two groups in turn) turn the codes
-//     into exact fp16 values scale * (code - 8) and write them into tensor memory as the A operand
-//     (tcgen05.st), so weights never pass through shared memory expanded and are never re-read;
+//   * TMA bulk copies bring four groups at a time into shared memory, from two warps that run independently: one
+//     copies the weights (16 KiB of codes and 2 KiB of scale/bias words, a ring handed back as soon as the codes are
+//     in registers), the other the activations' slice (held until the tensor core has finished with it) and the
+//     tiles of split means, each of which serves sixteen groups;
+//   * dequant warps (one thread per output column, four sets of four warps taking units of two groups in turn)
+//     turn the codes into exact fp16 values scale * (code - 8), sixteen registers at a time, and write them into
+//     tensor memory as the A operand (tcgen05.st): weights never pass through shared memory expanded and are
+//     never re-read. A pair of weights costs one shift, one logic operation and one fused multiply-add;
 //   * the activations' producer already wrote them (bf16-rounded, held as fp16) in the
 //     128-byte-swizzled K-major image the tensor core reads as the B operand;
-//   * two threads issue the four tcgen05.mma of a group; the accumulators stay in tensor memory for the
-//     whole contraction;
-//   * the bias term, (bias + 8 scale) * sum(a) per group, is a fifth instruction per four groups, from
-//     exact fp16 pairs of (64 bias, 512 scale) and the group means split in two fp16 numbers;
+//   * two warps issue the tcgen05.mma, a unit each in turn (eight k16 instructions and a ninth for the unit's
+//     share of the bias term), into an accumulator each; the accumulators stay in tensor memory for the whole
+//     contraction. The warps run their loops and waits whole, with one elected lane issuing;
+//   * the bias term, (bias + 8 scale) * sum(a) per group, comes from exact fp16 pairs of (64 bias, 512 scale)
+//     in tensor memory and the group means split in two fp16 numbers;
 //   * at the end every dequant warp reads its share of the accumulators (tcgen05.ld) and writes the output.
 // Everything is ordered by mbarriers. Every wait is bounded: a wait that runs out sets an error
 // word and the block unwinds, still releasing its tensor memory.
@@ -29,7 +33,7 @@
 // Device layout of a weight (private to this library): for each tile of 128 output columns and each
 // group, 4,096 bytes of codes [half h][column n][16 bytes] holding k = 64 g + 32 h + 0..31, each
 // 32-bit word's nibbles in the order [k0 k2 k4 k6 k1 k3 k5 k7] so that (word >> 4j) & 0x000F000F is
-// the bf16 pair (k_2j, k_2j+1); and 128 words (scale | bias << 16) per (tile, group).
+// the pair of codes (k_2j, k_2j+1); and 128 words (scale | bias << 16) per (tile, group).
 #pragma once
 #include "spl_common.cuh"
 
@@ -269,7 +273,8 @@ __device__ __forceinline__ void spl_codes4(uint32_t w, uint32_t *a) {
 // The result is the reference's sum of per-group terms up to the order of fp32 additions.
 #define SPL_TC_SUPER 4           // groups per shared-memory stage: one bulk copy brings 256 of the contraction
 #define SPL_TC_AUNITS 5          // A operand slots in tensor memory, a unit (two groups, 64 columns) each, with 8 columns each for the second term
-#define SPL_TC_THREADS 512       // warps 0-3, 8-11 and 4-7: three dequant sets (units of two groups in turn); 12 copies weights; 14 copies activations; 13, 15 tensor-core issue
+#define SPL_TC_SETS 4            // dequant sets of four warps (a warp writes the tensor-memory lanes of its index mod 4); they take the units in turn
+#define SPL_TC_THREADS (SPL_TC_SETS * 128 + 128)       // the sets; then a warp that copies weights, a tensor-core issue warp, a warp that copies activations, the other issue warp
 
 // Stages of activations: held until the tensor core has finished with them. Stages of codes with their scale/bias
 // words (18 KiB each): handed back as soon as they are in registers.
@@ -310,6 +315,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     const long long t_entry = clock64();
 #endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int W_COPY = SPL_TC_SETS * 4, W_MMA0 = W_COPY + 1, W_COPYB = W_COPY + 2, W_MMA1 = W_COPY + 3;
     const int tile = blockIdx.x, split = blockIdx.y, rb = blockIdx.z, row_blocks = op_blocks;   // the operand's row blocks (>= gridDim.z)
     const int rows_padded = op_blocks * RN;
     const int g_first = split * groups_per_split;
@@ -329,7 +335,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         spl_mbar_init(finished, 2);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
-    if (warp == 13) {
+    if (warp == W_MMA0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(spl_smem_addr(tmem_slot)), "r"(512) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
@@ -348,7 +354,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     // in its waits and its work.
 #ifdef SPL_TRACE
     const bool trace = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && error_flag[1] == 0x7ACE && (error_flag[2] & 0x100);
-    long long t0 = 0, t1 = 0, t2 = 0, t3 = 0, t_mark = 0;
+    long long t0 = 0, t1 = 0, t2 = 0, t3 = 0, t4 = 0, t5 = 0, t_mark = 0;
 #define SPL_T0() do { if (trace) t_mark = clock64(); } while (0)
 #define SPL_T1(acc) do { if (trace) { const long long now__ = clock64(); acc += now__ - t_mark; t_mark = now__; } } while (0)
 #define SPL_TOUT(statement) do { statement; } while (0)
@@ -358,8 +364,8 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
 #define SPL_TOUT(statement) do { } while (0)
 #endif
 
-    if (!(warp == 12 && lane == 0)) spl_grid_begin();     // the thread that copies weights first asks for some (below)
-    if (warp == 12) {
+    if (!(warp == W_COPY && lane == 0)) spl_grid_begin();     // the thread that copies weights first asks for some (below)
+    if (warp == W_COPY) {
         // ---- copies of weights: codes and their scale/bias words, one ring.
         if (lane == 0) {
             const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(codes) + (size_t(tile) * groups + g_first) * 4096;
@@ -386,7 +392,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             if (supers <= ahead) spl_grid_begin();
             SPL_TOUT(if (trace) { error_flag[8] = int(t0 / g_count); error_flag[10] = int(t2 / g_count); });
         }
-    } else if (warp == 14) {
+    } else if (warp == W_COPYB) {
         // ---- copies of activations and of the tiles of split means.
         if (lane == 0) {
             const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(act) + ((size_t(g_first) * row_blocks + rb) * RN) * 128;
@@ -422,15 +428,15 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             }
             SPL_TOUT(if (trace) { error_flag[9] = int(t1 / g_count); });
         }
-    } else if (warp == 13 || warp == 15) {
+    } else if (warp == W_MMA0 || warp == W_MMA1) {
         // ---- tensor-core issue: D[128 x RN] += A[128 x 64] (fp16, tensor memory) * B[RN x 64]^T (fp16, shared memory).
         // The whole warp runs the loop and its waits; one elected lane issues (spl_elect_one). An elected lane is held
         // while the tensor pipe works through its instructions, and a wait on a barrier costs its latency even when the
-        // phase is complete, so two warps take the units in turn (warp 13 the first unit of every stage, warp 15 the
+        // phase is complete, so two warps take the units in turn (one the first unit of every stage, the other the
         // second), each into an accumulator of its own: one warp's waits run under the other's instructions. A unit is
         // eight k16 instructions at fixed offsets from the unit's bases and a ninth for its share of the second term
         // (the unit's 8 values of that contraction; the other 8 columns of its operand slot are zero).
-        const int m = warp == 13 ? 0 : 1;
+        const int m = warp == W_MMA0 ? 0 : 1;
         constexpr uint32_t idesc = spl_tc_idesc(RN);
         int mean_tile = -1, mean_loads = 0, mean_slot = 0;
         const uint64_t b_desc0 = spl_tc_desc_sw128(spl_smem_addr(b_ring)), t_desc0 = spl_tc_desc_sw128(spl_smem_addr(t_ring));
@@ -485,12 +491,12 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         if (ok && spl_elect_one()) spl_tc_commit(finished);
         __syncwarp();
     } else {
-        // ---- dequant: thread = output column; codes -> scale * (code - 8), exact in fp16 -> tensor memory. Three sets
-        // of four warps (0-3, 8-11, 4-7) take the units of two groups in turn; a set's warps write the lanes of their
+        // ---- dequant: thread = output column; codes -> scale * (code - 8), exact in fp16 -> tensor memory. The sets
+        // of four warps take the units of two groups in turn; a set's warps write the lanes of their
         // warp index mod 4. A unit also carries its two groups' pairs of the second-term operand.
-        const int quarter = warp & 3, col = quarter * 32 + lane, set = warp < 4 ? 0 : warp >= 8 ? 1 : 2;
+        const int quarter = warp & 3, col = quarter * 32 + lane, set = warp >> 2;
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-        for (int un = set; un < units && ok; un += 3) {
+        for (int un = set; un < units && ok; un += SPL_TC_SETS) {
             const int j = un >> 1, half = un & 1, sc = j % CST;
             SPL_T0();
             ok = spl_mbar_wait(&full_c[sc], (j / CST) & 1);
@@ -556,13 +562,15 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             // The unit's share of the second-term operand sits at its place among the stage's sixteen values; the rest is zero.
             if (half == 0) { spl_tc_st4(tmem_aq + lane_base + slot * 8, aq[0], aq[1], aq[2], aq[3]); spl_tc_st4(tmem_aq + lane_base + slot * 8 + 4, 0u, 0u, 0u, 0u); }
             else { spl_tc_st4(tmem_aq + lane_base + slot * 8, 0u, 0u, 0u, 0u); spl_tc_st4(tmem_aq + lane_base + slot * 8 + 4, aq[0], aq[1], aq[2], aq[3]); }
+            SPL_T1(t3);
             spl_tc_st_wait();
+            SPL_T1(t4);
             spl_tc_fence_before();
             __syncwarp();
             if (lane == 0) spl_mbar_arrive(&full_a[slot]);
-            SPL_T1(t3);
+            SPL_T1(t5);
         }
-        SPL_TOUT(if (trace && warp == 0 && lane == 0) { error_flag[14] = int(t0 / g_count); error_flag[15] = int(t1 / g_count); error_flag[16] = int(t2 / g_count); error_flag[17] = int(t3 / g_count); error_flag[21] = g_count; });
+        SPL_TOUT(if (trace && warp == 0 && lane == 0) { error_flag[14] = int(t0 / g_count); error_flag[15] = int(t1 / g_count); error_flag[16] = int(t2 / g_count); error_flag[17] = int(t3 / g_count); error_flag[18] = int(t4 / g_count); error_flag[19] = int(t5 / g_count); error_flag[21] = g_count; });
         // ---- output: the sets share the accumulators' columns, sixteen rows of the step at a time.
         SPL_T0();
         if (ok) ok = spl_mbar_wait(finished, 0);
@@ -574,7 +582,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             float *dst = is_split ? partials + size_t(split) * rows_padded * out_ld : out;
 #pragma unroll
             for (int cb = 0; cb < RN / 16; ++cb) {
-                if (cb % 3 != set) continue;
+                if (cb % SPL_TC_SETS != set) continue;
                 const int c0 = cb * 16;
                 float total[16];
 #pragma unroll
@@ -604,7 +612,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     if (!ok) atomicExch(error_flag, 1 + warp);
     spl_tc_fence_before();
     __syncthreads();
-    if (warp == 13) {
+    if (warp == W_MMA0) {
         spl_tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
     }
