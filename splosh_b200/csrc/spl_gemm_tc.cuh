@@ -310,6 +310,9 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     uint64_t *full_c = bars, *empty_c = full_c + CST, *full_b = empty_c + CST, *empty_b = full_b + BST;
     uint64_t *full_a = empty_b + BST, *full_t = full_a + AUN, *empty_t = full_t + 2, *finished = empty_t + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(finished + 1);
+#ifdef SPL_TRACE
+    volatile long long *trace_clock = reinterpret_cast<volatile long long *>(bars + 64);      // issue times of the code stages
+#endif
 
 #ifdef SPL_TRACE
     const long long t_entry = clock64();
@@ -354,7 +357,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     // in its waits and its work.
 #ifdef SPL_TRACE
     const bool trace = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && error_flag[1] == 0x7ACE && (error_flag[2] & 0x100);
-    long long t0 = 0, t1 = 0, t2 = 0, t3 = 0, t4 = 0, t5 = 0, t_mark = 0;
+    long long t0 = 0, t1 = 0, t2 = 0, t3 = 0, t4 = 0, t5 = 0, t_mark = 0, age_all = 0, age_waited = 0; int age_n = 0; int age_wn = 0;
 #define SPL_T0() do { if (trace) t_mark = clock64(); } while (0)
 #define SPL_T1(acc) do { if (trace) { const long long now__ = clock64(); acc += now__ - t_mark; t_mark = now__; } } while (0)
 #define SPL_TOUT(statement) do { statement; } while (0)
@@ -384,6 +387,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                     SPL_T1(t0);
                     if (!ok) break;
                 }
+                SPL_TOUT(if (trace) trace_clock[sc] = clock64());
                 spl_mbar_expect_tx(&full_c[sc], uint32_t(n) * (4096 + 512));
                 spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[sc]);
                 spl_bulk_g2s(q_ring + sc * QSTAGE, qsrc + size_t(j) * QSTAGE, uint32_t(n) * 512, &full_c[sc]);
@@ -501,6 +505,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             SPL_T0();
             ok = spl_mbar_wait(&full_c[sc], (j / CST) & 1);
             SPL_TOUT(if (trace && warp == 0 && lane == 0 && un == 0) error_flag[23] = int(clock64() - t_entry));     // first stage has landed
+            SPL_TOUT(if (trace && warp == 0 && lane == 0) { const long long now = clock64(); const long long age = now - trace_clock[sc]; age_all += age; ++age_n; if (now - t_mark > 200) { age_waited += age; ++age_wn; } });
             SPL_T1(t0);
             if (!ok) break;
             const int n = min(SPL_TC_SUPER, g_count - j * SPL_TC_SUPER);      // groups of the stage; this unit has those from 2 * half
@@ -570,7 +575,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             if (lane == 0) spl_mbar_arrive(&full_a[slot]);
             SPL_T1(t5);
         }
-        SPL_TOUT(if (trace && warp == 0 && lane == 0) { error_flag[14] = int(t0 / g_count); error_flag[15] = int(t1 / g_count); error_flag[16] = int(t2 / g_count); error_flag[17] = int(t3 / g_count); error_flag[18] = int(t4 / g_count); error_flag[19] = int(t5 / g_count); error_flag[21] = g_count; });
+        SPL_TOUT(if (trace && warp == 0 && lane == 0) { error_flag[14] = int(t0 / g_count); error_flag[15] = int(t1 / g_count); error_flag[16] = int(t2 / g_count); error_flag[17] = int(t3 / g_count); error_flag[18] = int(t4 / g_count); error_flag[19] = int(t5 / g_count); error_flag[21] = g_count; error_flag[27] = int(age_all / max(age_n, 1)); error_flag[28] = int(age_waited / max(age_wn, 1)); error_flag[29] = age_wn; error_flag[30] = age_n; });
         // ---- output: the sets share the accumulators' columns, sixteen rows of the step at a time.
         SPL_T0();
         if (ok) ok = spl_mbar_wait(finished, 0);
