@@ -185,7 +185,7 @@ int choose_splits(int blocks, int groups, int sms, size_t partial_capacity, size
         if (eff != s) continue;
         if (s > 1 && size_t(s) * partial_per_split > partial_capacity) break;
         const int waves = (blocks * s + sms - 1) / sms;
-        const double cost = double(waves) * (gps + 6.0) + (s > 1 ? 4.0 : 0.0);
+        const double cost = double(waves) * (gps + 20.0) + (s > 1 ? 4.0 : 0.0);     // a block costs about twenty groups of time besides its groups (measured: fill, first loads, output)
         if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
     }
     return best;
