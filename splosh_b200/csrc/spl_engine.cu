@@ -1280,7 +1280,7 @@ spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t
                                 "dequant(1 of 2 sets) [wait stage %d, convert %d, wait slot %d, store %d] epilogue [wait %d, work %d, final wait %d] groups %d\n",
                         t[8], t[9], t[10], t[11], t[12], t[13], t[14], t[15], t[16], t[17], t[18], t[19], t[20], t[21]);
             fprintf(stderr, "tc code stages: age at pick-up %d cycles (all %d units), %d when the set had to wait (%d units)\n", t[27], t[30], t[28], t[29]);
-            fprintf(stderr, "tc timeline of block 0, cycles from entry: set-up done %d, first stage landed %d, last instruction issued %d, accumulators complete %d, output written %d\n", t[22], t[23], t[24], t[25], t[26]);
+            fprintf(stderr, "tc timeline of block 0, cycles from entry: set-up done %d, first stage landed %d, last instruction issued %d, accumulators complete %d (read %d, residual read %d), output written %d\n", t[22], t[23], t[24], t[25], t[31], t[32], t[26]);
         }
         if (s == SPL_OK) cudaMemcpy2D(out, size_t(n) * 4, d_out, size_t(ld) * 4, size_t(n) * 4, rows, cudaMemcpyDeviceToHost);
     }

@@ -597,6 +597,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
 #pragma unroll
                     for (int r = 0; r < 16; ++r) total[r] = a == 0 ? __uint_as_float(v[r]) : total[r] + __uint_as_float(v[r]);
                 }
+                SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[31] = int(clock64() - t_entry));     // accumulators read
                 if (n < out_ld) {
                     float res[16];
 #pragma unroll
@@ -604,6 +605,7 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                         const int row = rb * RN + c0 + r;
                         res[r] = (!is_split && residual && row < rows) ? residual[size_t(row) * out_ld + n] : 0.0f;
                     }
+                    SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[32] = int(clock64() - t_entry));     // residual read
 #pragma unroll
                     for (int r = 0; r < 16; ++r) {
                         const int row = rb * RN + c0 + r;
