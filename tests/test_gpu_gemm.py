@@ -2,7 +2,8 @@
 against the CPU oracle on the same seeded inputs.
 
 Tolerance: both sides form, per 64-group, the exact dot of bf16 activations with 4-bit codes and
-add dot * scale + sum * bias; they differ only in fp32 summation order, so |diff| <= 4e-6 of the
+add dot * scale + sum * bias; they differ only in fp32 summation order (the kernel keeps one running
+accumulator per issuing warp over all of a split's groups), so |diff| <= 8e-6 of the
 largest output (the reference allows relErr 1e-2 for its kernel, GemmOracleTests.swift:165)."""
 import numpy as np
 import pytest
