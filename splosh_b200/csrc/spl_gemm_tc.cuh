@@ -307,8 +307,8 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     unsigned char *w_ring = t_ring + 2 * TTILE;                                         // [CST][SUPER][4096] codes
     uint32_t *q_ring = reinterpret_cast<uint32_t *>(w_ring + size_t(CST) * WSTAGE);     // [CST][SUPER][128] scale | bias << 16
     uint64_t *bars = reinterpret_cast<uint64_t *>(q_ring + CST * QSTAGE);
-    uint64_t *full_c = bars, *empty_c = full_c + CST, *full_b = empty_c + CST, *empty_b = full_b + BST;
-    uint64_t *full_a = empty_b + BST, *full_t = full_a + AUN, *empty_t = full_t + 2, *finished = empty_t + 2;
+    uint64_t *full_c = bars, *empty_c = full_c + CST, *full_b = empty_c + CST, *done = full_b + BST;      // done[un % 16]: the instructions that read unit un have completed
+    uint64_t *full_a = done + 16, *full_t = full_a + AUN, *empty_t = full_t + 2, *finished = empty_t + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(finished + 1);
 #ifdef SPL_TRACE
     volatile long long *trace_clock = reinterpret_cast<volatile long long *>(bars + 64);      // issue times of the code stages
@@ -332,7 +332,8 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < CST; ++i) { spl_mbar_init(&full_c[i], 1); spl_mbar_init(&empty_c[i], 8); }       // the two sets (four warps each) that take the stage's units
-        for (int i = 0; i < BST; ++i) { spl_mbar_init(&full_b[i], 1); spl_mbar_init(&empty_b[i], 2); }       // the two issuing warps' commits
+        for (int i = 0; i < BST; ++i) spl_mbar_init(&full_b[i], 1);
+        for (int i = 0; i < 16; ++i) spl_mbar_init(&done[i], 1);            // the commit of the issuing warp that took the unit
         for (int i = 0; i < AUN; ++i) spl_mbar_init(&full_a[i], 4);      // one per unit of two groups
         for (int i = 0; i < 2; ++i) { spl_mbar_init(&full_t[i], 1); spl_mbar_init(&empty_t[i], 2); }
         spl_mbar_init(finished, 2);
@@ -417,7 +418,10 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                     mean_tile = want; ++mean_loads;
                 }
                 SPL_T0();
-                ok = spl_mbar_wait(&empty_b[sbq], ((j0 / BST) & 1) ^ 1);
+                if (j0 >= BST) {            // the stage's last tenant: both of its units have to have completed
+                    const int u0 = 2 * (j0 - BST);
+                    ok = spl_mbar_wait(&done[u0 & 15], (u0 >> 4) & 1) && spl_mbar_wait(&done[(u0 + 1) & 15], ((u0 + 1) >> 4) & 1);
+                }
                 SPL_T1(t1);
                 if (!ok) break;
                 spl_mbar_expect_tx(&full_b[sbq], uint32_t(n) * RN * 128);
@@ -477,14 +481,14 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                     for (int q = 0; q < 8; ++q)
                         spl_tc_mma_ts_acc(d_mine, a_base + q * 8, b_desc + uint64_t(((q >> 2) * RN * 128 + (q & 3) * 32) >> 4), idesc);
                     spl_tc_mma_ts_acc(d_mine, tmem_aq + slot * 8, t_desc, idesc);
-                    spl_tc_commit(&empty_b[sbq]);             // with the other warp's commit: the stage's activations are free
+                    spl_tc_commit(&done[un & 15]);            // the unit's A slot is free, and with the stage's other unit its activations
                 }
             } else if (spl_elect_one()) {                        // the warp's first unit (it overwrites the accumulator) and a unit of one group
                 for (int q = 0; q < 8; ++q)
                     if ((q >> 2) < n)
                         spl_tc_mma_ts(d_mine, a_base + q * 8, b_desc + uint64_t(((q >> 2) * RN * 128 + (q & 3) * 32) >> 4), idesc, (un >= 2 || q) ? 1u : 0u);
                 spl_tc_mma_ts_acc(d_mine, tmem_aq + slot * 8, t_desc, idesc);
-                spl_tc_commit(&empty_b[sbq]);
+                spl_tc_commit(&done[un & 15]);
             }
             __syncwarp();
             SPL_T1(t2);
@@ -524,9 +528,9 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             __syncwarp();
             if (lane == 0) spl_mbar_arrive(&empty_c[sc]);
             SPL_T1(t1);
-            // The unit's slot was last used by unit un - AUN: the stage that unit belongs to has to have completed.
+            // The unit's slot was last used by unit un - AUN, which has to have completed.
             const int slot = un % AUN;
-            if (un >= AUN) { const int jr = (un - AUN) >> 1; ok = spl_mbar_wait(&empty_b[jr % BST], (jr / BST) & 1); }
+            if (un >= AUN) ok = spl_mbar_wait(&done[(un - AUN) & 15], ((un - AUN) >> 4) & 1);
             SPL_T1(t2);
             if (!ok) break;
             spl_tc_fence_after();
