@@ -330,8 +330,24 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     // is a fixed function of the tile), so that at any moment they ask L2 for different lines.
     const int rot = (g_count % SPL_TC_SUPER == 0 && supers > 1) ? int((uint32_t(tile) * 2654435761u >> 12) % uint32_t(supers)) : 0;
 
+    // The thread that copies weights sets up its own barriers and asks for the first stages at once: they are nobody's
+    // output (no wait for the predecessor in the stream), and they travel while the block is still being set up.
+    const int ahead = min(CST, supers);
+    if (warp == W_COPY && lane == 0) {
+        const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(codes) + (size_t(tile) * groups + g_first) * 4096;
+        const uint32_t *qsrc = sb + (size_t(tile) * groups + g_first) * 128;
+        for (int i = 0; i < CST; ++i) spl_mbar_init(&full_c[i], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        for (int j0 = 0; j0 < ahead; ++j0) {
+            const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
+            const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);
+            spl_mbar_expect_tx(&full_c[j0], uint32_t(n) * (4096 + 512));
+            spl_bulk_g2s(w_ring + size_t(j0) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[j0]);
+            spl_bulk_g2s(q_ring + j0 * QSTAGE, qsrc + size_t(j) * QSTAGE, uint32_t(n) * 512, &full_c[j0]);
+        }
+    }
     if (threadIdx.x == 0) {
-        for (int i = 0; i < CST; ++i) { spl_mbar_init(&full_c[i], 1); spl_mbar_init(&empty_c[i], 8); }       // the two sets (four warps each) that take the stage's units
+        for (int i = 0; i < CST; ++i) spl_mbar_init(&empty_c[i], 8);       // the two sets (four warps each) that take the stage's units
         for (int i = 0; i < BST; ++i) spl_mbar_init(&full_b[i], 1);
         for (int i = 0; i < 16; ++i) spl_mbar_init(&done[i], 1);            // the commit of the issuing warp that took the unit
         for (int i = 0; i < AUN; ++i) spl_mbar_init(&full_a[i], 4);      // one per unit of two groups
@@ -374,27 +390,21 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         if (lane == 0) {
             const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(codes) + (size_t(tile) * groups + g_first) * 4096;
             const uint32_t *qsrc = sb + (size_t(tile) * groups + g_first) * 128;
-            // The weights are nobody's output: the first stages are asked for before this kernel waits for its
-            // predecessor in the stream, so they arrive while that one is still finishing.
-            const int ahead = min(CST, supers);
-            for (int j0 = 0; j0 < supers && ok; ++j0) {
-                if (j0 == ahead) spl_grid_begin();
+            spl_grid_begin();
+            for (int j0 = ahead; j0 < supers && ok; ++j0) {
                 const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;      // the stage's source; j0 is its place in the pipeline
                 const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);         // with a rotation every stage is full
                 const int sc = j0 % CST;
                 SPL_T0();
-                if (j0 >= ahead) {
-                    ok = spl_mbar_wait(&empty_c[sc], ((j0 / CST) & 1) ^ 1);
-                    SPL_T1(t0);
-                    if (!ok) break;
-                }
+                ok = spl_mbar_wait(&empty_c[sc], ((j0 / CST) & 1) ^ 1);
+                SPL_T1(t0);
+                if (!ok) break;
                 SPL_TOUT(if (trace) trace_clock[sc] = clock64());
                 spl_mbar_expect_tx(&full_c[sc], uint32_t(n) * (4096 + 512));
                 spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[sc]);
                 spl_bulk_g2s(q_ring + sc * QSTAGE, qsrc + size_t(j) * QSTAGE, uint32_t(n) * 512, &full_c[sc]);
                 SPL_T1(t2);
             }
-            if (supers <= ahead) spl_grid_begin();
             SPL_TOUT(if (trace) { error_flag[8] = int(t0 / g_count); error_flag[10] = int(t2 / g_count); });
         }
     } else if (warp == W_COPYB) {
