@@ -599,9 +599,9 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             const int n = tile * 128 + col;
             const bool is_split = gridDim.y > 1;
             float *dst = is_split ? partials + size_t(split) * rows_padded * out_ld : out;
-#pragma unroll
-            for (int cb = 0; cb < RN / 16; ++cb) {
-                if (cb % SPL_TC_SETS != set) continue;
+            // (one copy of the body: code that runs once a block is paid for in instruction fetches)
+#pragma unroll 1
+            for (int cb = set; cb < RN / 16; cb += SPL_TC_SETS) {
                 const int c0 = cb * 16;
                 float total[16];
 #pragma unroll
