@@ -346,13 +346,20 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             spl_bulk_g2s(q_ring + j0 * QSTAGE, qsrc + size_t(j) * QSTAGE, uint32_t(n) * 512, &full_c[j0]);
         }
     }
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < CST; ++i) spl_mbar_init(&empty_c[i], 8);       // the two sets (four warps each) that take the stage's units
-        for (int i = 0; i < BST; ++i) spl_mbar_init(&full_b[i], 1);
-        for (int i = 0; i < 16; ++i) spl_mbar_init(&done[i], 1);            // the commit of the issuing warp that took the unit
-        for (int i = 0; i < AUN; ++i) spl_mbar_init(&full_a[i], 4);      // one per unit of two groups
-        for (int i = 0; i < 2; ++i) { spl_mbar_init(&full_t[i], 1); spl_mbar_init(&empty_t[i], 2); }
-        spl_mbar_init(finished, 2);
+    if (warp == 0) {
+        // One barrier a lane: the arrival count of barrier i (in the order of the pointers above, after full_c).
+        const int i = lane + CST;
+        const int total = int(finished + 1 - bars);
+        for (int b = i; b < total; b += 32) {
+            uint64_t *bar = bars + b;
+            const uint32_t count = bar < full_b ? 8u              // empty_c: the two sets (four warps each) that take the stage's units
+                                 : bar < done ? 1u                // full_b: the copy's bytes
+                                 : bar < full_a ? 1u              // done: the commit of the issuing warp that took the unit
+                                 : bar < full_t ? 4u              // full_a: the four warps of a set
+                                 : bar < empty_t ? 1u             // full_t
+                                 : 2u;                            // empty_t and finished: the two issuing warps
+            spl_mbar_init(bar, count);
+        }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == W_MMA0) {
