@@ -186,6 +186,15 @@ spl_status spl_step(spl_engine *engine, const spl_row *rows, int32_t count, spl_
 /* The same pass from tables the caller built (the north star's split: packer and allocator stay
  * with the host language). */
 spl_status spl_step_tables(spl_engine *engine, const spl_tables *tables, spl_step_stats *stats);
+
+/* Engine.step in two halves (Sources/SploshRuntime/Engine.swift:1316 commits its command graph and waits for it in
+ * one call; a host that wants to pack the next step's rows or sample while the GPU runs uses the halves). spl_step_launch
+ * validates and packs the rows, copies the tables and enqueues every kernel of the step, then returns;
+ * spl_step_wait waits for them and returns the step's status and statistics, after which logits, arg-max and the
+ * slot calls see the step. Exactly one spl_step_wait per successful spl_step_launch; no other call on the engine
+ * in between (SPL_ERR_INVALID_ARGUMENT otherwise). spl_step is the two in a row. */
+spl_status spl_step_launch(spl_engine *engine, const spl_row *rows, int32_t count);
+spl_status spl_step_wait(spl_engine *engine, spl_step_stats *stats);
 /* Engine.logits(_:) (Engine.swift:1202-1205): row i of the last step's logits, vocab floats. */
 spl_status spl_logits_row(spl_engine *engine, int32_t index, float *dst);
 /* Sampler.argmax over [0, vocab_limit) for every logit row of the last step, on the device

@@ -39,6 +39,11 @@ struct spl_engine {
     int device = 0;
     cudaStream_t stream = nullptr;
     std::string error;
+    // A step between spl_step_launch and spl_step_wait: its tables (the host object's arrays) and its start on the wall clock.
+    bool in_flight = false;
+    spl_tables flying{};
+    int flying_rows = 0, flying_logit_rows = 0;
+    std::chrono::steady_clock::time_point wall0;
 
     std::vector<LayerWeights> layers;
     SplQ4Dev head;
@@ -291,8 +296,9 @@ spl_status check_launch(spl_engine *e, const char *what) {
     return SPL_OK;
 }
 
-spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
-    const auto wall0 = std::chrono::steady_clock::now();
+// Everything of a step up to its last launch; finish_step waits for it.
+spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
+    e->wall0 = std::chrono::steady_clock::now();
     const spl_geometry &g = e->g;
     const Shapes sh(g);
     const int R = int(t->rows);
@@ -418,8 +424,13 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
         launch_gemm(e, e->head, GemmOperand{e->hsn, e->hsn_sums, operand_rn(int(t->logit_rows)), (int(t->logit_rows) + operand_rn(int(t->logit_rows)) - 1) / operand_rn(int(t->logit_rows))}, e->logits, nullptr, int(t->logit_rows));
     }
     SPL_CUDA(cudaEventRecord(e->ev_end, e->stream));
-    const spl_status launched = check_launch(e, "step launch");
-    if (launched != SPL_OK) return launched;
+    e->flying_rows = R; e->flying_logit_rows = int(t->logit_rows);
+    return check_launch(e, "step launch");
+}
+
+spl_status finish_step(spl_engine *e, spl_step_stats *stats) {
+    const int R = e->flying_rows;
+    SPL_CUDA(cudaSetDevice(e->device));
     SPL_CUDA(cudaStreamSynchronize(e->stream));
     {
         int flag = 0;
@@ -438,14 +449,20 @@ spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
                 t[32], t[33], t[34], t[35], t[36], t[37], t[38], t[39], t[40], t[41], t[42], t[43], t[44], t[45], t[46], t[47], t[48], t[49], t[50], t[51], t[52], t[53], t[54], t[55]);
     }
     profile_collect(e);
-    e->last_rows = R; e->last_logit_rows = int(t->logit_rows);
+    e->last_rows = R; e->last_logit_rows = e->flying_logit_rows;
     if (stats) {
         float ms = 0;
         cudaEventElapsedTime(&ms, e->ev_begin, e->ev_end);
         stats->rows = R; stats->launches = e->launches; stats->gpu_seconds = ms / 1000.0;
-        stats->wall_seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - wall0).count();
+        stats->wall_seconds = std::chrono::duration<double>(std::chrono::steady_clock::now() - e->wall0).count();
     }
     return SPL_OK;
+}
+
+spl_status run_step(spl_engine *e, const spl_tables *t, spl_step_stats *stats) {
+    if (e->in_flight) return e->fail(SPL_ERR_INVALID_ARGUMENT, "a step is in flight: call spl_step_wait first");
+    const spl_status queued = enqueue_step(e, t);
+    return queued == SPL_OK ? finish_step(e, stats) : queued;
 }
 
 spl_status upload_q4_into(spl_engine *e, SplQ4Dev &w, int n0, int rows, int inner, const uint32_t *packed, const uint16_t *scales,
@@ -771,6 +788,29 @@ spl_status spl_step(spl_engine *e, const spl_row *rows, int32_t count, spl_step_
     if (built != SPL_OK) return e->fail(built, e->host->error);
     const spl_status ran = run_step(e, &t, stats);
     if (ran == SPL_OK) spl_host_finish_step(e->host, &t);
+    return ran;
+}
+
+// The asynchronous pair (Engine.step split in two: the host may pack the next step's rows, or sample from the last
+// step's logits on another engine, while this one runs). Between the two calls the engine accepts no other call that
+// touches slots, logits or weights; spl_step_wait returns the step's status and statistics.
+spl_status spl_step_launch(spl_engine *e, const spl_row *rows, int32_t count) {
+    if (!e || !rows) return SPL_ERR_INVALID_ARGUMENT;
+    if (e->in_flight) return e->fail(SPL_ERR_INVALID_ARGUMENT, "a step is in flight: call spl_step_wait first");
+    e->error.clear();
+    const spl_status built = spl_host_build_tables(e->host, rows, count, &e->flying);
+    if (built != SPL_OK) return e->fail(built, e->host->error);
+    const spl_status queued = enqueue_step(e, &e->flying);
+    if (queued == SPL_OK) e->in_flight = true;
+    return queued;
+}
+
+spl_status spl_step_wait(spl_engine *e, spl_step_stats *stats) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    if (!e->in_flight) return e->fail(SPL_ERR_INVALID_ARGUMENT, "no step is in flight");
+    e->in_flight = false;
+    const spl_status ran = finish_step(e, stats);
+    if (ran == SPL_OK) spl_host_finish_step(e->host, &e->flying);
     return ran;
 }
 

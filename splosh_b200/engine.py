@@ -145,6 +145,8 @@ def lib():
             "spl_weights_set_vector": (i32, [vp, i32, i32, vp, i32]),
             "spl_weights_synthesize_q4": (i32, [vp, u64]),
             "spl_step": (i32, [vp, C.POINTER(_Row), i32, C.POINTER(_Stats)]),
+            "spl_step_launch": (i32, [vp, C.POINTER(_Row), i32]),
+            "spl_step_wait": (i32, [vp, C.POINTER(_Stats)]),
             "spl_step_tables": (i32, [vp, C.POINTER(_Tables), C.POINTER(_Stats)]),
             "spl_logits_row": (i32, [vp, i32, vp]),
             "spl_argmax": (i32, [vp, i32, vp]),
@@ -412,6 +414,19 @@ class Engine:
         arr = _rows_array(rows)
         self._check(lib().spl_step(self.handle, arr, len(rows), C.byref(stats)))
         self.last_logit_rows = sum(1 for r in rows if r.want_logits)
+        return StepStats(stats.rows, stats.launches, stats.gpu_seconds, stats.wall_seconds)
+
+    def step_launch(self, rows):
+        """The first half of step: everything is enqueued when this returns; nothing else may be asked of the engine
+        until step_wait."""
+        self._flying_rows = _rows_array(rows)          # kept alive until the wait
+        self._check(lib().spl_step_launch(self.handle, self._flying_rows, len(rows)))
+        self._flying_logit_rows = sum(1 for r in rows if r.want_logits)
+
+    def step_wait(self):
+        stats = _Stats()
+        self._check(lib().spl_step_wait(self.handle, C.byref(stats)))
+        self.last_logit_rows = self._flying_logit_rows
         return StepStats(stats.rows, stats.launches, stats.gpu_seconds, stats.wall_seconds)
 
     def step_tables(self, tables: _Tables, logit_rows):

@@ -37,6 +37,14 @@ def test_output_widths_that_do_not_fill_a_tile(oracle, n, k):
     case(oracle, n, k, 20, n + k, residual=n % 2 == 0)
 
 
+@pytest.mark.parametrize("k", [256, 768, 1280, 2304])
+@pytest.mark.parametrize("rows", [5, 64])
+def test_short_contractions_with_odd_stage_counts(oracle, k, rows):
+    """One, three, five and nine shared-memory stages of four groups (inner dimensions are multiples of 256): fewer
+    stages than the rings hold, and counts that leave the rings' slots at every phase."""
+    case(oracle, 384, k, rows, 100 + k)
+
+
 @pytest.mark.parametrize("n,k", [(17408, 5120), (5120, 17408), (10240, 5120), (5120, 6144)])
 def test_27b_shapes_at_64_rows(oracle, n, k):
     case(oracle, n, k, 64, 7)

@@ -384,3 +384,26 @@ def test_a_slot_moves_to_another_engine_through_state_and_kv_snapshots(toks):
 def lib_state_bytes(engine):
     from splosh_b200.engine import lib
     return lib().spl_state_bytes(engine.handle)
+
+
+def test_a_step_in_two_halves_is_the_step():
+    """spl_step_launch + spl_step_wait against spl_step on a second engine with the same weights: same tokens, bit for
+    bit the same logits; a second launch before the wait, and a wait with nothing in flight, are refused."""
+    g = S.tiny_geometry()
+    cfg = S.EngineConfig(max_slots=2, max_rows=64, kv_pages=16, max_context=1024)
+    a, b = Pair(g, cfg), Pair(g, cfg)
+    toks = tokens_for(0xA5A5, 40, g.vocab)
+    rows = [S.EngineRow(0, toks[p], p, p == 23) for p in range(24)]
+    a.engine.step(rows)
+    b.engine.step_launch(rows)
+    with pytest.raises(S.EngineError):
+        b.engine.step_launch(rows)
+    b.engine.step_wait()
+    with pytest.raises(S.EngineError):
+        b.engine.step_wait()
+    assert np.array_equal(a.engine.all_logits(), b.engine.all_logits())
+    nxt = [S.EngineRow(0, toks[24], 24, True)]
+    a.engine.step(nxt)
+    b.engine.step_launch(nxt); b.engine.step_wait()
+    assert np.array_equal(a.engine.all_logits(), b.engine.all_logits())
+    assert a.engine.pages_held(0) == b.engine.pages_held(0)
