@@ -202,10 +202,11 @@ struct PendingReduce { int splits = 1; size_t stride = 0; int ld = 0; };
 
 template <int RN>
 void launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows,
-                    float *partials, size_t partial_floats, int *error_flag, int *launches, PendingReduce *defer) {
+                    float *partials, size_t partial_floats, int *error_flag, int *launches, PendingReduce *defer, const SplOperand *fuse_act) {
     const int groups = w.k / 64;
     const int row_blocks = (rows + RN - 1) / RN, rows_padded = op.blocks * RN;
-    const int splits = choose_splits(w.tiles * row_blocks, groups, 148, partial_floats, size_t(rows_padded) * w.ld);
+    // A block that writes the activation needs the whole contraction (silu is not linear).
+    const int splits = fuse_act ? 1 : choose_splits(w.tiles * row_blocks, groups, 148, partial_floats, size_t(rows_padded) * w.ld);
     const int gps = ((groups + splits - 1) / splits + 3) / 4 * 4;
     const size_t smem = spl_tc_smem_bytes(RN);
     static bool configured = false;
@@ -214,7 +215,8 @@ void launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &o
         configured = true;
     }
     launch_step(spl_gemm_q4_tc_kernel<RN>, dim3(dim3(w.tiles, splits, row_blocks)), dim3(SPL_TC_THREADS), smem, stream, 
-        w.codes, w.sb, op.values, op.sums, out, w.ld, residual, partials, rows, op.blocks, groups, gps, error_flag);
+        w.codes, w.sb, op.values, op.sums, out, w.ld, residual, partials, rows, op.blocks, groups, gps, error_flag,
+        w.interleave, fuse_act ? *fuse_act : SplOperand{nullptr, nullptr, RN, 1}, fuse_act ? 1 : 0);
     if (launches) ++*launches;
     if (defer) { defer->splits = splits; defer->stride = size_t(rows_padded) * w.ld; defer->ld = w.ld; }
     if (splits > 1 && !defer) {
@@ -227,10 +229,10 @@ void launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &o
 
 // out[r][:] = GEMM(w, operand[r][:]) (+ residual) for the first `rows` rows of the operand.
 void launch_gemm_rows(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows,
-                      float *partials, size_t partial_floats, int *error_flag, int *launches, PendingReduce *defer = nullptr) {
-    if (op.rn == 16) launch_gemm_tc<16>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer);
-    else if (op.rn == 32) launch_gemm_tc<32>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer);
-    else launch_gemm_tc<64>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer);
+                      float *partials, size_t partial_floats, int *error_flag, int *launches, PendingReduce *defer = nullptr, const SplOperand *fuse_act = nullptr) {
+    if (op.rn == 16) launch_gemm_tc<16>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer, fuse_act);
+    else if (op.rn == 32) launch_gemm_tc<32>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer, fuse_act);
+    else launch_gemm_tc<64>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer, fuse_act);
 }
 
 template <int RN, int FMT>
@@ -265,10 +267,10 @@ void launch_gemm_gguf(cudaStream_t stream, const SplGgufDev &w, const GemmOperan
     else launch_gemm_gguf_rows<SPL_GGUF_Q4K>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag);
 }
 
-void launch_gemm(spl_engine *e, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows, PendingReduce *defer = nullptr) {
+void launch_gemm(spl_engine *e, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows, PendingReduce *defer = nullptr, const SplOperand *fuse_act = nullptr) {
     profile_begin(e, KLASS_GEMM, double(w.bytes()) * ((rows + op.rn - 1) / op.rn));
     --e->launches;      // profile_begin counted one; the launcher counts the kernels it really starts
-    launch_gemm_rows(e->stream, w, op, out, residual, rows, e->partials, e->partial_floats, e->tc_error, &e->launches, defer);
+    launch_gemm_rows(e->stream, w, op, out, residual, rows, e->partials, e->partial_floats, e->tc_error, &e->launches, defer, fuse_act);
     profile_end(e);
 }
 
@@ -399,11 +401,8 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
             profile_begin(e, KLASS_ELEMENTWISE, 0);
             norm(live, L.vec[SPL_VEC_POST_NORM], nullptr, xn, mixer);
             profile_end(e);
-            launch_gemm(e, L.gate_up, gxn, e->gate_up, nullptr, live);
-            profile_begin(e, KLASS_ELEMENTWISE, 0);
-            const size_t total = size_t(live) * g.inter / 4;
-            launch_step(spl_silu_mul_kernel, dim3(int(std::min<size_t>((total + 255) / 256, 4096))), dim3(256), 0, e->stream, e->gate_up, e->gate_up_ld, g.inter, live, act);
-            profile_end(e);
+            // gate|up and the SiLU gate in one kernel: the GEMM's blocks write act = bf16(silu(gate) * up) and its sums.
+            launch_gemm(e, L.gate_up, gxn, e->gate_up, nullptr, live, nullptr, &act);
             // The down projection's reduction is left to the next block's input norm, except after the last block (the final
             // norm gathers rows) and when the residual stream is tapped after every block.
             const bool leave = l + 1 < g.layers && !e->taps_enabled && feature_tap < 0 && live == R;
@@ -482,7 +481,7 @@ spl_status upload_q4_into(spl_engine *e, SplQ4Dev &w, int n0, int rows, int inne
     int *bad = nullptr;
     SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&bad), sizeof(int)));
     SPL_CUDA(cudaMemsetAsync(bad, 0, sizeof(int), e->stream));
-    spl_repack_q4_kernel<<<int(std::min<size_t>((words + 255) / 256, 16384)), 256, 0, e->stream>>>(dp, ds, db, rows, inner, w.codes, w.sb, n0, bad);
+    spl_repack_q4_kernel<<<int(std::min<size_t>((words + 255) / 256, 16384)), 256, 0, e->stream>>>(dp, ds, db, rows, inner, w.codes, w.sb, n0, bad, w.interleave);
     spl_status launched = check_launch(e, "repack");
     SPL_CUDA(cudaStreamSynchronize(e->stream));
     int flag = 0;
@@ -566,6 +565,7 @@ spl_status create(const spl_geometry *gp, const spl_config *cp, spl_engine *e) {
         if ((s = alloc_q4(e, L.in_proj, L.full ? sh.att_n : sh.gdn_n, H)) != SPL_OK) return s;
         if ((s = alloc_q4(e, L.out_proj, H, L.full ? sh.AD : sh.VD)) != SPL_OK) return s;
         if ((s = alloc_q4(e, L.gate_up, 2 * g.inter, H)) != SPL_OK) return s;
+        L.gate_up.interleave = g.inter;
         if ((s = alloc_q4(e, L.down, H, g.inter)) != SPL_OK) return s;
     }
     spl_status s;

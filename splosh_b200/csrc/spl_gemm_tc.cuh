@@ -42,6 +42,7 @@ struct SplQ4Dev {
     int ld = 0;           // columns rounded up to 16: the width of an output row
     int tiles = 0;        // 128-column tiles
     int k = 0;            // contraction length, a multiple of 64
+    int interleave = 0;   // > 0 for a fused gate|up tensor of 2 x interleave columns: tile t holds gate columns [64 t, 64 t + 64) then the up columns of the same range
     uint32_t *codes = nullptr;      // [tiles][k/64][2][128][4] words
     uint32_t *sb = nullptr;         // [tiles][k/64][128] words
     size_t bytes() const { return size_t(ld) * (k / 64) * 36; }   // algorithmic: 32 B of codes + 4 B of scale and bias per (column, group)
@@ -89,7 +90,7 @@ struct SplOperand {
 
 // ---- repack: MLX row-major -> tile layout, rows [n0, n0 + rows) of a fused tensor ------------
 __global__ void spl_repack_q4_kernel(const uint32_t *__restrict__ packed, const uint16_t *__restrict__ scales,
-                                     const uint16_t *__restrict__ biases, int rows, int k, uint32_t *codes, uint32_t *sb, int n0, int *out_of_range) {
+                                     const uint16_t *__restrict__ biases, int rows, int k, uint32_t *codes, uint32_t *sb, int n0, int *out_of_range, int interleave) {
     const int groups = k / 64, words = k / 8;
     const size_t total = size_t(rows) * words;
     for (size_t idx = blockIdx.x * size_t(blockDim.x) + threadIdx.x; idx < total; idx += size_t(gridDim.x) * blockDim.x) {
@@ -102,7 +103,9 @@ __global__ void spl_repack_q4_kernel(const uint32_t *__restrict__ packed, const 
             dst |= ((src >> (8 * j)) & 0xFu) << (4 * j);
             dst |= ((src >> (8 * j + 4)) & 0xFu) << (4 * j + 16);
         }
-        const int n = n0 + row, tile = n >> 7, col = n & 127, g = w >> 3, h = (w >> 2) & 1, j = w & 3;
+        int n = n0 + row;
+        if (interleave > 0) { const int c = n < interleave ? n : n - interleave; n = (c >> 6) * 128 + (n < interleave ? 0 : 64) + (c & 63); }
+        const int tile = n >> 7, col = n & 127, g = w >> 3, h = (w >> 2) & 1, j = w & 3;
         codes[(((size_t(tile) * groups + g) * 2 + h) * 128 + col) * 4 + j] = dst;
         if ((w & 7) == 0) {
             const uint16_t sbits = scales[size_t(row) * groups + g];
@@ -296,7 +299,7 @@ template <int RN>
 __global__ void __launch_bounds__(SPL_TC_THREADS, 1)
 spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__restrict__ sb, const __nv_bfloat16 *__restrict__ act,
                       const float *__restrict__ act_sums, float *out, int out_ld, const float *residual, float *partials,
-                      int rows, int op_blocks, int groups, int groups_per_split, int *error_flag) {
+                      int rows, int op_blocks, int groups, int groups_per_split, int *error_flag, int interleave, SplOperand act_out, int fuse) {
     constexpr int BST = spl_tc_bstages(RN), CST = spl_tc_cstages(RN), AUN = SPL_TC_AUNITS;
     constexpr int BTILE = SPL_TC_SUPER * RN * 128, WSTAGE = SPL_TC_SUPER * 4096, QSTAGE = SPL_TC_SUPER * 128, TTILE = RN * 128;
     extern __shared__ unsigned char spl_tc_smem_raw[];
@@ -601,9 +604,16 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         SPL_T0();
         if (ok) ok = spl_mbar_wait(finished, 0);
         SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[25] = int(clock64() - t_entry));     // accumulators complete
+        // A fused gate|up tensor (interleave > 0) holds, in tile t, the gate columns [64 t, 64 t + 64) and then the up columns of
+        // the same range. Without `fuse` the output goes to the columns of the plain layout; with it the block writes
+        // act = bf16(silu(gate) * up) and its per-64 sums (engine.metal:200-219) straight into the next GEMM's operand:
+        // the accumulators pass through shared memory (the activation ring is idle by now) so that a thread holds the
+        // gate and the up value of the same element.
+        float *stage = reinterpret_cast<float *>(b_ring);       // [RN][128] fp32
         if (ok) {
             spl_tc_fence_after();
             const int n = tile * 128 + col;
+            const int n_out = interleave > 0 ? ((col < 64 ? 0 : interleave) + tile * 64 + (col & 63)) : n;
             const bool is_split = gridDim.y > 1;
             float *dst = is_split ? partials + size_t(split) * rows_padded * out_ld : out;
             // (one copy of the body: code that runs once a block is paid for in instruction fetches)
@@ -619,19 +629,48 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                     for (int r = 0; r < 16; ++r) total[r] = a == 0 ? __uint_as_float(v[r]) : total[r] + __uint_as_float(v[r]);
                 }
                 SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[31] = int(clock64() - t_entry));     // accumulators read
-                if (n < out_ld) {
+                if (fuse) {
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) stage[(c0 + r) * 128 + col] = total[r];
+                } else if (n < out_ld) {
                     float res[16];
 #pragma unroll
                     for (int r = 0; r < 16; ++r) {
                         const int row = rb * RN + c0 + r;
-                        res[r] = (!is_split && residual && row < rows) ? residual[size_t(row) * out_ld + n] : 0.0f;
+                        res[r] = (!is_split && residual && row < rows) ? residual[size_t(row) * out_ld + n_out] : 0.0f;
                     }
                     SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[32] = int(clock64() - t_entry));     // residual read
 #pragma unroll
                     for (int r = 0; r < 16; ++r) {
                         const int row = rb * RN + c0 + r;
-                        if (row < rows) dst[size_t(row) * out_ld + n] = total[r] + res[r];
+                        if (row < rows) dst[size_t(row) * out_ld + n_out] = total[r] + res[r];
                     }
+                }
+            }
+        }
+        if (fuse) {
+            // Every dequant thread comes here, whatever happened to it before: the barrier cannot be left waiting.
+            asm volatile("bar.sync 1, %0;\n" ::"n"(SPL_TC_SETS * 128) : "memory");
+            const int t = threadIdx.x, c8 = (t & 7) * 8;
+            for (int rr = t >> 3; rr < RN; rr += SPL_TC_SETS * 16) {
+                const int row = rb * RN + rr;
+                float r[8];
+                {
+                    const float4 g0 = *reinterpret_cast<const float4 *>(stage + rr * 128 + c8), g1 = *reinterpret_cast<const float4 *>(stage + rr * 128 + c8 + 4);
+                    const float4 u0 = *reinterpret_cast<const float4 *>(stage + rr * 128 + 64 + c8), u1 = *reinterpret_cast<const float4 *>(stage + rr * 128 + 64 + c8 + 4);
+                    const float gs[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, us[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) r[i] = (ok && row < rows) ? spl_bf16_to_float(spl_float_to_bf16(spl_silu_exact(gs[i]) * us[i])) : 0.0f;
+                }
+                // The sums in the order of the stand-alone kernel (spl_silu_mul_kernel): fours, then a butterfly over sixteen
+                // holders of four; a thread here holds two of those fours.
+                float sa = (r[0] + r[1]) + (r[2] + r[3]), sb2 = (r[4] + r[5]) + (r[6] + r[7]);
+#pragma unroll
+                for (int o = 4; o > 0; o >>= 1) { sa += __shfl_xor_sync(0xffffffffu, sa, o); sb2 += __shfl_xor_sync(0xffffffffu, sb2, o); }
+                if (ok && row < rows) {
+                    const uint2 lo8 = spl_operand_pack4(r[0], r[1], r[2], r[3]), hi8 = spl_operand_pack4(r[4], r[5], r[6], r[7]);
+                    *reinterpret_cast<uint4 *>(act_out.values + act_out.at(row, tile * 64 + c8)) = make_uint4(lo8.x, lo8.y, hi8.x, hi8.y);
+                    if ((t & 7) == 0) act_out.put_sum(row, tile, sa + sb2);
                 }
             }
         }
