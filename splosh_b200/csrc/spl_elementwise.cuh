@@ -88,32 +88,6 @@ for (int i = 0; i < warps; ++i) total += part[i];
     }
 }
 
-// act = bf16(silu(gate) * up) and its per-64 sums from the fused gate|up projection (engine.metal:200-219).
-// gate_up: [rows][ld] with gate at column 0 and up at column `inter`.
-__global__ void spl_silu_mul_kernel(const float *__restrict__ gate_up, int ld, int inter, int rows, SplOperand out) {
-    spl_grid_begin();
-    const size_t total = size_t(rows) * inter / 4;
-    const size_t stride = size_t(gridDim.x) * blockDim.x;
-    const size_t bound = (total + 31) / 32 * 32;
-    for (size_t idx = blockIdx.x * size_t(blockDim.x) + threadIdx.x; idx < bound; idx += stride) {
-        float r0 = 0.f, r1 = 0.f, r2 = 0.f, r3 = 0.f;
-        int row = 0, col = 0;
-        if (idx < total) {
-            row = int(idx / (inter / 4)); col = int(idx % (inter / 4)) * 4;
-            const float4 g = *reinterpret_cast<const float4 *>(gate_up + size_t(row) * ld + col);
-            const float4 u = *reinterpret_cast<const float4 *>(gate_up + size_t(row) * ld + inter + col);
-            const uint16_t b0 = spl_float_to_bf16(spl_silu_exact(g.x) * u.x), b1 = spl_float_to_bf16(spl_silu_exact(g.y) * u.y);
-            const uint16_t b2 = spl_float_to_bf16(spl_silu_exact(g.z) * u.z), b3 = spl_float_to_bf16(spl_silu_exact(g.w) * u.w);
-            r0 = spl_bf16_to_float(b0); r1 = spl_bf16_to_float(b1); r2 = spl_bf16_to_float(b2); r3 = spl_bf16_to_float(b3);
-            *reinterpret_cast<uint2 *>(out.values + out.at(row, col)) = spl_operand_pack4(r0, r1, r2, r3);
-        }
-        float gsum = (r0 + r1) + (r2 + r3);
-#pragma unroll
-        for (int o = 8; o > 0; o >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o);
-        if (idx < total && (threadIdx.x & 15) == 0) out.put_sum(row, col / 64, gsum);
-    }
-}
-
 // Arg-max over [0, limit) per logit row, first index on ties (vDSP_maxvi, Sampler.swift:11-16;
 // the vocabulary limit Sampler.swift:94-96). Grid (rows), 1024 threads.
 __global__ void __launch_bounds__(1024)

@@ -662,8 +662,8 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
 #pragma unroll
                     for (int i = 0; i < 8; ++i) r[i] = (ok && row < rows) ? spl_bf16_to_float(spl_float_to_bf16(spl_silu_exact(gs[i]) * us[i])) : 0.0f;
                 }
-                // The sums in the order of the stand-alone kernel (spl_silu_mul_kernel): fours, then a butterfly over sixteen
-                // holders of four; a thread here holds two of those fours.
+                // The sums in one fixed order: fours, then a butterfly over the sixteen fours of a group (8, 4, 2, 1 apart);
+                // a thread here holds two neighbouring fours, so the last level is its own addition.
                 float sa = (r[0] + r[1]) + (r[2] + r[3]), sb2 = (r[4] + r[5]) + (r[6] + r[7]);
 #pragma unroll
                 for (int o = 4; o > 0; o >>= 1) { sa += __shfl_xor_sync(0xffffffffu, sa, o); sb2 += __shfl_xor_sync(0xffffffffu, sb2, o); }
