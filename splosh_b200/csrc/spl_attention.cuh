@@ -648,13 +648,30 @@ __global__ void spl_attn_merge_kernel(const float *__restrict__ partials, const 
     __shared__ float warp_sums[8];
     const int head = blockIdx.x, row = blockIdx.y, j = threadIdx.x, hd = p.head_dim, record = hd + 2;
     const float *base = partials + (size_t(row) * p.heads + head) * p.spans * record;
-    float top = -INFINITY;
-    for (int s = 0; s < p.spans; ++s) top = fmaxf(top, base[s * record]);
-    float sum = 0.0f, acc = 0.0f;
-    for (int s = 0; s < p.spans; ++s) {
-        const float weight = expf(base[s * record] - top);
-        if (weight > 0.0f) { sum += base[s * record + 1] * weight; acc += base[s * record + 2 + j] * weight; }
+    // The spans' weights once for the block (the first warp; at most 64 spans), then every thread walks its channel with
+    // the loads of four spans in flight and the additions in span order.
+    __shared__ float weights[64];
+    if (j < 32) {
+        float top = -INFINITY;
+        for (int s = j; s < p.spans; s += 32) top = fmaxf(top, base[s * record]);
+        top = spl_warp_max(top);
+        for (int s = j; s < p.spans; s += 32) {
+            const float weight = expf(base[s * record] - top);
+            weights[s] = weight;
+        }
     }
+    __syncthreads();
+    float sum = 0.0f, acc = 0.0f;
+    for (int s = 0; s < p.spans; ++s) if (weights[s] > 0.0f) sum += base[s * record + 1] * weights[s];
+    int s = 0;
+    for (; s + 4 <= p.spans; s += 4) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = base[(s + u) * record + 2 + j];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) if (weights[s + u] > 0.0f) acc += v[u] * weights[s + u];
+    }
+    for (; s < p.spans; ++s) if (weights[s] > 0.0f) acc += base[s * record + 2 + j] * weights[s];
     const float gate = proj[size_t(row) * p.proj_ld + head * 2 * hd + hd + j];
     const uint16_t bits = spl_float_to_bf16((acc / sum) * spl_sigmoid(gate));
     reinterpret_cast<__half *>(core.values)[core.at(row, head * hd + j)] = __float2half_rn(spl_bf16_to_float(bits));
