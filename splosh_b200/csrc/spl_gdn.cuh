@@ -35,16 +35,28 @@ spl_gdn_conv_kernel(const float *__restrict__ proj, const uint16_t *__restrict__
     float x3 = hist[0], x2 = hist[1], x1 = hist[2];
     const float w0 = spl_bf16_to_float(conv_weight[c * 4]), w1 = spl_bf16_to_float(conv_weight[c * 4 + 1]);
     const float w2 = spl_bf16_to_float(conv_weight[c * 4 + 2]), w3 = spl_bf16_to_float(conv_weight[c * 4 + 3]);
-    for (uint32_t t = 0; t < length; ++t) {
-        const uint32_t row = start + t;
-        const float x0 = proj[size_t(row) * p.proj_ld + c];
-        const float y = ((w0 * x3 + w1 * x2) + w2 * x1) + w3 * x0;
-        act[size_t(row) * p.channels + c] = spl_silu_exact(y);
-        if (t + 1 == length || row_write[row + 1] != row_write[row]) {
-            float *dst = conv_state + (size_t(row_write[row]) * p.channels + c) * 3;
-            dst[0] = x2; dst[1] = x1; dst[2] = x0;
+    // Eight rows at a time: their inputs and the units they write are asked for together, then the rows are taken in order.
+    for (uint32_t base = 0; base < length; base += 8) {
+        float xs[8];
+        uint32_t unit[9];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) xs[u] = base + u < length ? proj[size_t(start + base + u) * p.proj_ld + c] : 0.0f;
+#pragma unroll
+        for (int u = 0; u < 9; ++u) unit[u] = base + u < length ? row_write[start + base + u] : 0xFFFFFFFFu;      // past the run: "another unit"
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            if (base + u < length) {
+                const uint32_t row = start + base + u;
+                const float x0 = xs[u];
+                const float y = ((w0 * x3 + w1 * x2) + w2 * x1) + w3 * x0;
+                act[size_t(row) * p.channels + c] = spl_silu_exact(y);
+                if (unit[u + 1] != unit[u]) {
+                    float *dst = conv_state + (size_t(unit[u]) * p.channels + c) * 3;
+                    dst[0] = x2; dst[1] = x1; dst[2] = x0;
+                }
+                x3 = x2; x2 = x1; x1 = x0;
+            }
         }
-        x3 = x2; x2 = x1; x1 = x0;
     }
 }
 
