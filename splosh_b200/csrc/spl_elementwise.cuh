@@ -96,9 +96,34 @@ spl_argmax_kernel(const float *__restrict__ logits, int ld, int limit, int32_t *
     __shared__ int best_i[32];
     const float *x = logits + size_t(blockIdx.x) * ld;
     float bv = -INFINITY; int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < limit; i += blockDim.x) {
+    // Sixteen-byte loads, four of them in flight a thread (rows start on 16-byte boundaries: the vocabulary is a multiple
+    // of 16); ascending i per thread, so strict > keeps the first.
+    const int quads = limit / 4;
+    int q = threadIdx.x;
+    for (; q + 3 * int(blockDim.x) < quads; q += 4 * blockDim.x) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = reinterpret_cast<const float4 *>(x)[q + u * blockDim.x];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int i = 4 * (q + u * int(blockDim.x));
+            if (v[u].x > bv) { bv = v[u].x; bi = i; }
+            if (v[u].y > bv) { bv = v[u].y; bi = i + 1; }
+            if (v[u].z > bv) { bv = v[u].z; bi = i + 2; }
+            if (v[u].w > bv) { bv = v[u].w; bi = i + 3; }
+        }
+    }
+    for (; q < quads; q += blockDim.x) {
+        const float4 v = reinterpret_cast<const float4 *>(x)[q];
+        const int i = 4 * q;
+        if (v.x > bv) { bv = v.x; bi = i; }
+        if (v.y > bv) { bv = v.y; bi = i + 1; }
+        if (v.z > bv) { bv = v.z; bi = i + 2; }
+        if (v.w > bv) { bv = v.w; bi = i + 3; }
+    }
+    for (int i = 4 * quads + threadIdx.x; i < limit; i += blockDim.x) {
         const float v = x[i];
-        if (v > bv) { bv = v; bi = i; }      // ascending i per thread: strict > keeps the first
+        if (v > bv) { bv = v; bi = i; }
     }
     if (bi == 0x7fffffff) { bv = -INFINITY; }
 #pragma unroll
