@@ -31,7 +31,7 @@ CONTEXT_LOW, CONTEXT_HIGH = 36 * 1024, 42 * 1024
 # DRAM bytes the GEMM kernel moves per algorithmic byte: measured per tensor shape with ncu (reads + writes), 14.81 GB
 # for the 14.41 GB of a full step's 257 launches.
 GEMM_DRAM_PER_ALGORITHMIC_BYTE = 1.025
-SPAN_TARGET = 576      # scan blocks per step the table builder aims for (engine configuration)
+SPAN_TARGET = 608      # scan blocks per step the table builder aims for (engine configuration)
 WEIGHT_SEED, TOKEN_SEED = 0x5EED6D17, 0xC0FFEE00
 
 
