@@ -53,7 +53,9 @@ def check_vectors(reference):
 
 
 if __name__ == "__main__":
-    reference = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py <path of the reference checkout>")
+    reference = sys.argv[1]
     with open(os.path.join(HERE, "gguf_golden_blocks.json"), "w") as f:
         json.dump(golden_blocks(reference), f)
     np.savez_compressed(os.path.join(HERE, "gguf_check_vectors.npz"), **check_vectors(reference))
