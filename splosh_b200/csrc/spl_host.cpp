@@ -229,15 +229,15 @@ void spl_plan_costs_reference(spl_plan_costs *c) {
     c->tier_margin = 0.88;                                              // :779
 }
 // The same table measured with this library on a B200 (27B shape, MLX 4-bit, 8 sessions): steps of 16, 32, 64, 96 and
-// 128 rows at 1K context took 10.7, 11.3, 12.7, 21.2 and 22.2 ms; 64 rows at 40K took 15.2 ms and 128 rows 27.2 ms,
-// i.e. 0.0082 ms per thousand context tokens and block of eight rows, first or second; the host's share of a step
+// 128 rows at 1K context took 7.5, 8.1, 9.1, 15.6 and 16.4 ms; 64 rows at 40K took 11.3 ms and 128 rows 20.8 ms,
+// i.e. 0.0072 ms per thousand context tokens for a session's first block of eight rows and 0.0070 for its second; the host's share of a step
 // (tables, launches, ids back) was 0.3 ms. A draft pass is the caller's to add.
 void spl_plan_costs_b200(spl_plan_costs *c) {
     if (!c) return;
-    const double tiers[5] = {10.7, 11.3, 12.7, 21.2, 22.2};
+    const double tiers[5] = {7.5, 8.1, 9.1, 15.6, 16.4};       // steps of 16, 32, 64, 96, 128 rows over 8 sessions at 1K context
     for (int i = 0; i < 5; ++i) c->tier_ms[i] = tiers[i];
-    c->beyond_ms_per_row = 0.17; c->per_row_ms = 0.0; c->fixed_ms = 0.3;
-    c->attention_first = 0.0082; c->attention_second = 0.0082;
+    c->beyond_ms_per_row = 0.13; c->per_row_ms = 0.0; c->fixed_ms = 0.3;
+    c->attention_first = 0.0072; c->attention_second = 0.0070;      // (64 rows at 40K - at 1K) / (8 x 39K tokens); the same for the second block of 8 rows
     c->prefill_attention = 0.001;
     c->tier_margin = 0.88;
 }
