@@ -229,6 +229,10 @@ spl_status spl_debug_fill_state(spl_engine *engine, int32_t slot, uint64_t seed)
  * codes [page][kv head][256][head_dim] (V codes are stored [page][kv head][head_dim][256]). */
 spl_status spl_debug_read(spl_engine *engine, int32_t which, int32_t index, void *dst, size_t bytes);
 spl_status spl_debug_taps(spl_engine *engine, int32_t enabled);
+/* Test switch: with `enabled` 0 the following steps do not store their rows' keys and values, so the attention scan
+ * reads the pool exactly as a test wrote it, the rows' own positions included (the scenes of
+ * Tests/SploshOracleTests/AttentionScanCandidateTests.swift:85-200 place large keys there). 1 restores the store. */
+spl_status spl_debug_kv_store(spl_engine *engine, int32_t enabled);
 
 /* ---- Slot snapshots ------------------------------------------------------------------------
  * exportState / importState (Engine.swift:871-939) and exportKV / kvPrefix / importSlot's KV part (:953-1042), as two

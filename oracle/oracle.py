@@ -75,6 +75,8 @@ def lib():
         L.orc_engine_reset_slot.argtypes = [C.c_void_p, C.c_int, C.c_int]
         L.orc_engine_buffer.restype = C.c_void_p; L.orc_engine_buffer.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_size_t)]
         L.orc_step.restype = C.c_int; L.orc_step.argtypes = [C.c_void_p, C.POINTER(_CTables), C.c_void_p, C.c_void_p, C.c_int]
+        L.orc_attention_scan.restype = C.c_int
+        L.orc_attention_scan.argtypes = [C.c_void_p, C.c_int, C.POINTER(_CTables), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
         L.orc_model_q4.restype = C.c_int
         L.orc_model_q4.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_int), C.POINTER(C.c_int)] + [C.POINTER(C.c_void_p)] * 3
         L.orc_model_vec.restype = C.c_int
@@ -276,12 +278,29 @@ class Engine:
         count = n.value // np.dtype(dtype).itemsize
         return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_int8 if dtype == np.int8 else C.c_float)), (count,))
 
-    def step(self, t: Tables, taps=False, max_layers=-1):
-        g = self.model.g
+    @staticmethod
+    def _ctables(t):
         keep = [np.ascontiguousarray(getattr(t, n), np.uint32) for n in
                 ("tokens", "row_slot", "row_pos", "runs", "run_info", "row_read", "row_write", "gather_index", "attn_blocks", "page_table")]
         ct = _CTables(t.rows, t.run_count, t.logit_rows, t.attn_block_count, t.step_pages, t.live_rows, t.spans, t.pages_per_span,
                       *[a.ctypes.data_as(C.POINTER(C.c_uint32)) for a in keep])
+        return ct, keep
+
+    def attention_scan(self, t: Tables, full_index, live, q, qproj):
+        """The span scan and merge of one attention layer over the pool as it stands: q [live, heads, head_dim] prepared
+        queries, qproj [rows, heads, 2 head_dim]. Returns (partials [live, heads, spans, head_dim + 2], merged [live, heads * head_dim])."""
+        g = self.model.g
+        ct, keep = self._ctables(t)
+        q = np.ascontiguousarray(q, np.float32); qproj = np.ascontiguousarray(qproj, np.float32)
+        partials = np.zeros((live, g.heads, t.spans, g.head_dim + 2), np.float32)
+        merged = np.zeros((live, g.heads * g.head_dim), np.float32)
+        rc = lib().orc_attention_scan(self.handle, full_index, C.byref(ct), live, _ptr(q), _ptr(qproj), _ptr(partials), _ptr(merged))
+        assert rc == 0
+        return partials, merged
+
+    def step(self, t: Tables, taps=False, max_layers=-1):
+        g = self.model.g
+        ct, keep = self._ctables(t)
         logits = np.zeros((t.logit_rows, g.vocab), np.float32)
         hidden = np.zeros((g.layers, t.rows, g.hidden), np.float32) if taps else None
         rc = lib().orc_step(self.handle, C.byref(ct), _ptr(logits), None if hidden is None else _ptr(hidden), max_layers)

@@ -455,13 +455,15 @@ void gdn_layer(Engine &e, int linear_index, const Layer &L, const Tables &t, con
     }
 }
 
+void attention_scan(Engine &e, int full_index, const Tables &t, int live, const float *q, const float *qproj, float *partials_out, Operand &core);
+
 // One gated GQA layer: q prepare (engine_na.metal:1222-1266), int8 KV store (:2044-2094), the
 // span scan (candidates/attn_scan_r.metal:46-202), the merge (engine.metal:2218-2255). The CPU
 // statement of the scan and merge is Tests/SploshOracleTests/AttentionScanCandidateTests.swift:313-420.
 void attention_layer(Engine &e, int full_index, const Layer &L, const Tables &t, int live, const float *qproj,
                      const float *kproj, const float *vproj, Operand &core) {
     const Geometry &g = e.m->g;
-    const int hd = g.head_dim, heads = g.heads, kvh = g.kv_heads, perKV = heads / kvh, rows = t.rows;
+    const int hd = g.head_dim, heads = g.heads, kvh = g.kv_heads, rows = t.rows;
     std::vector<int8_t> &kc = e.k_codes[full_index], &vc = e.v_codes[full_index];
     std::vector<float> &ks = e.k_scale[full_index], &vs = e.v_scale[full_index];
     // Keys and values of every row of the step go in first, so rows of a block see each other.
@@ -493,6 +495,17 @@ void attention_layer(Engine &e, int full_index, const Layer &L, const Tables &t,
             norm_rope(qproj + (size_t(r) * heads + h) * 2 * hd, L.vec[V_Q_NORM], hd, g.rotary_dim, t.row_pos[r], g.eps, g.rope_theta, out);
             for (int i = 0; i < hd; ++i) out[i] = round_f16(out[i]);
         }
+    attention_scan(e, full_index, t, live, q.data(), qproj, nullptr, core);
+}
+
+// The span scan and the merge on their own, over the pool as it stands: q [live][heads][head_dim] holds the prepared
+// (fp16-representable) queries, qproj [rows][heads][2 head_dim] the projection whose second halves are the output gates.
+// `partials_out`, when given, receives the span records [live][heads][spans][head_dim + 2].
+void attention_scan(Engine &e, int full_index, const Tables &t, int live, const float *q, const float *qproj, float *partials_out, Operand &core) {
+    const Geometry &g = e.m->g;
+    const int hd = g.head_dim, heads = g.heads, kvh = g.kv_heads, perKV = heads / kvh;
+    std::vector<int8_t> &kc = e.k_codes[full_index], &vc = e.v_codes[full_index];
+    std::vector<float> &ks = e.k_scale[full_index], &vs = e.v_scale[full_index];
     const float scale = 1.0f / sqrtf(float(hd));
     const int spans = t.spans, pps = t.pages_per_span;
     const int record = hd + 2;
@@ -582,6 +595,7 @@ void attention_layer(Engine &e, int full_index, const Layer &L, const Tables &t,
         }
         core.finish_row(r);
     }
+    if (partials_out) memcpy(partials_out, partials.data(), partials.size() * sizeof(float));
 }
 
 }  // namespace
@@ -899,6 +913,20 @@ void *orc_engine_buffer(void *engine, int which, int index, size_t *bytes) {
     }
     *bytes = 0; return nullptr;
 }
+
+// The attention scan and merge of one layer over the engine's pool as it stands (test entry): q [live][heads][head_dim]
+// prepared queries, qproj [rows][heads][2 head_dim]; writes partials [live][heads][spans][head_dim + 2] and the merged,
+// gated, bf16-rounded output [live][heads * head_dim].
+int orc_attention_scan(void *engine, int full_index, const Tables *tp, int live, const float *q, const float *qproj, float *partials_out, float *core_out) {
+    Engine &e = *static_cast<Engine *>(engine);
+    if (full_index < 0 || full_index >= int(e.k_codes.size()) || live <= 0) return 1;
+    const Geometry &g = e.m->g;
+    Operand core(int(tp->rows), g.heads * g.head_dim);
+    attention_scan(e, full_index, *tp, live, q, qproj, partials_out, core);
+    memcpy(core_out, core.values.data(), size_t(live) * g.heads * g.head_dim * sizeof(float));
+    return 0;
+}
+
 
 // One step (Engine.swift:1400-1512). logits: [logit_rows][vocab]. hidden_taps, when not null:
 // [layers][rows][hidden], the residual stream after each block. max_layers < 0 runs all blocks.

@@ -81,6 +81,7 @@ struct spl_engine {
     int last_rows = 0, last_logit_rows = 0;
 
     bool taps_enabled = false, profile = false;
+    bool kv_store = true;            // false: test switch, the step's rows leave the KV pool as it is (spl_debug_kv_store)
     std::vector<ProfileSlot> profile_slots;
     size_t profile_used = 0;
     double klass_ms[KLASS_COUNT] = {}, klass_bytes[KLASS_COUNT] = {};
@@ -375,7 +376,7 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
             p.max_pages = e->host->max_pages; p.proj_ld = L.in_proj.ld; p.k_offset = sh.att_k; p.v_offset = sh.att_v;
             p.spans = int(t->spans); p.pages_per_span = int(t->pages_per_span); p.eps = g.eps; p.scale = 1.0f / sqrtf(float(g.head_dim));
             profile_begin(e, KLASS_ATTENTION, 0);
-            launch_step(spl_attn_prepare_kernel, dim3(dim3(g.heads + g.kv_heads, R)), dim3(128), 0, e->stream, 
+            launch_step(spl_attn_prepare_kernel, dim3(dim3(g.heads + (e->kv_store ? g.kv_heads : 0), R)), dim3(128), 0, e->stream, 
                 e->proj, L.vec[SPL_VEC_Q_NORM], L.vec[SPL_VEC_K_NORM], e->inv_freq, e->d_row_slot, e->d_row_pos, e->d_page_table, e->q,
                 e->k_codes[full_index], e->k_scale[full_index], e->v_codes[full_index], e->v_scale[full_index], p);
             profile_end(e);
@@ -933,6 +934,12 @@ spl_status spl_debug_taps(spl_engine *e, int32_t enabled) {
     SPL_CUDA(cudaSetDevice(e->device));
     if (enabled && !e->taps) SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&e->taps), size_t(e->g.layers) * e->c.max_rows * e->g.hidden * 4));
     e->taps_enabled = enabled != 0;
+    return SPL_OK;
+}
+
+spl_status spl_debug_kv_store(spl_engine *e, int32_t enabled) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    e->kv_store = enabled != 0;
     return SPL_OK;
 }
 

@@ -163,6 +163,7 @@ def lib():
             "spl_debug_fill_state": (i32, [vp, i32, u64]),
             "spl_debug_read": (i32, [vp, i32, i32, vp, C.c_size_t]),
             "spl_debug_taps": (i32, [vp, i32]),
+            "spl_debug_kv_store": (i32, [vp, i32]),
             "spl_op_gemm_gguf": (i32, [i32, i32, vp, i32, i32, vp, i32, vp, vp]),
             "spl_state_bytes": (C.c_size_t, [vp]),
             "spl_state_export": (i32, [vp, i32, vp, C.c_size_t]),
@@ -528,6 +529,9 @@ class Engine:
 
     def debug_taps(self, enabled=True):
         self._check(lib().spl_debug_taps(self.handle, int(enabled)))
+
+    def debug_kv_store(self, enabled=True):
+        self._check(lib().spl_debug_kv_store(self.handle, int(enabled)))
 
     def debug_profile(self, enabled=True):
         self._check(lib().spl_debug_profile(self.handle, int(enabled)))

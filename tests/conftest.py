@@ -12,6 +12,18 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a B200 (run with -m gpu on the GPU box)")
 
 
+def pytest_terminal_summary(terminalreporter):
+    """The differences the parity tests observed (helpers.observed), one line each."""
+    try:
+        from helpers import OBSERVED
+    except ImportError:
+        return
+    if OBSERVED:
+        terminalreporter.section("observed differences")
+        for line in OBSERVED:
+            terminalreporter.write_line(line)
+
+
 @pytest.fixture(scope="session")
 def oracle():
     from oracle import oracle as O

@@ -6,6 +6,15 @@ import splosh_b200 as S
 from oracle import oracle as O
 from oracle import tables as T
 
+OBSERVED = []
+
+
+def observed(text):
+    """Record a measured difference; conftest prints every line at the end of the run."""
+    OBSERVED.append(text)
+    print(text)
+
+
 TABLE_FIELDS = ["tokens", "row_slot", "row_pos", "runs", "run_info", "row_read", "row_write", "gather_index", "attn_blocks"]
 SCALARS = ["rows", "step_pages", "live_rows", "spans", "pages_per_span"]
 
