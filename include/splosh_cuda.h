@@ -146,6 +146,39 @@ int32_t spl_plan_prefill_cap(const spl_plan_costs *costs, int32_t max_rows, int3
 int32_t spl_plan_blocks(const spl_plan_costs *costs, int32_t sessions, const double *tail, const double *block_yield, const int32_t *context_tokens,
                         int32_t other_rows, int32_t block, int32_t max_rows, int32_t max_logit_rows, int32_t max_verify_rows, int32_t max_context,
                         int32_t *blocks_out);
+/* ---- Row packer (BatchScheduler.buildRows, Sources/SploshRuntime/BatchScheduler.swift:1323-1442) -----------
+ * Which rows the next step holds and in which order: verify blocks of the speculating sessions (anchor + proposal, every
+ * row wanting logits), then one row for each plainly decoding session, then prompt chunks shortest backlog first under
+ * the width prefillCap allows; KV pages are reserved against the host's free pages as rows are taken (:1336-1343), a
+ * chunk ends where the session's state is to be kept (:1420-1422) and shrinks to the pages its slot already holds when
+ * the pool cannot give more (:1423-1428). What stays with the caller: where proposals come from (the draft model, the
+ * lookup index) and which idle slot to evict when memory is short (sessions that sat out are listed in `waiting`). */
+typedef struct spl_session {
+    int32_t slot, evaluated;            /* tokens already in the slot (slotTokens[slot].count) */
+    int32_t pending;                    /* the token waiting to be evaluated; -1 while the prompt is being fed */
+    const int32_t *proposal;            /* drafted continuation of a speculating session (BatchScheduler.swift:1395) */
+    int32_t proposal_count;
+    const int32_t *prompt;              /* request.promptTokens */
+    int32_t prompt_count, fed;
+    const int32_t *marks;               /* positions where a prefill step must end (stateMarks, diskMarks, turnMark) */
+    int32_t mark_count;
+    double block_yield;                 /* expected tokens of its verify block (SpeculationState.BlockStats.blockYield) */
+} spl_session;
+typedef struct spl_pack_config {
+    int32_t block;                      /* DraftModel.blockSize */
+    int32_t max_verify_rows;            /* BatchScheduler.maxVerifyRows */
+    int32_t speculate;                  /* a draft source exists (draft != nil) */
+    int32_t prefill_rows_while_decoding;
+    double decode_weight;
+    const spl_plan_costs *costs;        /* the cost table prefillCap reads */
+} spl_pack_config;
+enum { SPL_PLAN_VERIFY = 0, SPL_PLAN_DECODE = 1, SPL_PLAN_PREFILL = 2 };
+typedef struct spl_planned { int32_t kind, session, count, complete; } spl_planned;   /* count: proposal tokens, or prefill rows */
+/* Returns the number of rows written to `rows` (capacity: the engine's max_rows), or -1 on a bad argument. `plan`
+ * (capacity: sessions) receives what each packed session does, `waiting` (capacity: sessions) the indices of sessions
+ * that sat the step out for want of KV pages. Sessions are given in the scheduler's order (active). */
+int32_t spl_host_pack_rows(const spl_host *host, const spl_session *sessions, int32_t session_count, const spl_pack_config *config,
+                           spl_row *rows, spl_planned *plan, int32_t *plan_count, int32_t *waiting, int32_t *waiting_count);
 /* Sampler (Sources/SploshRuntime/Sampler.swift:68-156), the part after the k largest logits are known
  * (spl_topk gives them): `state` is the sampler's SplitMix64 state, advanced by every draw.
  *   spl_sampler_uniform     Sampler.uniform01 (:79-90)
@@ -233,6 +266,13 @@ spl_status spl_debug_taps(spl_engine *engine, int32_t enabled);
  * reads the pool exactly as a test wrote it, the rows' own positions included (the scenes of
  * Tests/SploshOracleTests/AttentionScanCandidateTests.swift:85-200 place large keys there). 1 restores the store. */
 spl_status spl_debug_kv_store(spl_engine *engine, int32_t enabled);
+/* Every wait inside a kernel (a role of a block waiting for another role of the same block) gives up after a time
+ * budget, 250 ms unless changed here, and the step then returns SPL_ERR_TIMEOUT with the engine still usable.
+ * spl_debug_drop_weight_stage is the test of that path: the q4 GEMM's weight-copy role leaves out stage `stage` of
+ * every block's piece (a stage nothing delivers), -1 switches it off. Both settings hold for every engine on the
+ * engine's device until changed. */
+spl_status spl_debug_wait_budget(spl_engine *engine, int64_t nanoseconds);
+spl_status spl_debug_drop_weight_stage(spl_engine *engine, int32_t stage);
 
 /* ---- Slot snapshots ------------------------------------------------------------------------
  * exportState / importState (Engine.swift:871-939) and exportKV / kvPrefix / importSlot's KV part (:953-1042), as two
@@ -274,8 +314,9 @@ spl_status spl_debug_profile_read(spl_engine *engine, int32_t klass, double *mil
  * path because cudaMalloc and cudaFree synchronise the whole device.
  * This entry point runs out[r][:] = GEMM(weights, activations[r][:]) (+ residual) on one of the
  * engine's resident weights and calls no cudaMalloc, cudaFree or other allocating routine: the
- * GEMM operand, its per-64 sums and the split-K partial sums live in a static device array of
- * about 10.3 MiB that every GPU loading the library holds until exit.
+ * GEMM operand, its per-64 sums, the slots where blocks that share an output tile leave their partial sums
+ * and the tiles' tickets live in a static device array of about 12.9 MiB that every GPU loading the library
+ * holds until exit.
  *   - all three buffers are DEVICE pointers: activations fp32 [rows][inner], residual (may be
  *     null, may alias out) and out fp32 [rows][ld], ld = the tensor's columns rounded up to 16;
  *   - rows must be 1..64 and the tensor's inner dimension at most 17408, else SPL_ERR_INVALID_ROWS
@@ -288,6 +329,10 @@ spl_status spl_debug_profile_read(spl_engine *engine, int32_t klass, double *mil
 enum { SPL_RESIDENT_IN_PROJ = 0, SPL_RESIDENT_OUT_PROJ, SPL_RESIDENT_GATE_UP, SPL_RESIDENT_DOWN, SPL_RESIDENT_HEAD };
 spl_status spl_gemm_q4_static(spl_engine *engine, int32_t layer, int32_t which, const float *device_activations, int32_t rows,
                               const float *device_residual, float *device_out, void *stream);
+/* The static array also holds the error word of those calls. After the caller has synchronised the stream they were
+ * queued on, this returns SPL_ERR_TIMEOUT when a block of one of them gave up a wait (its output is then incomplete),
+ * SPL_OK otherwise. It allocates nothing. No counterpart in the reference. */
+spl_status spl_gemm_q4_static_status(spl_engine *engine);
 
 /* ---- Single operators on host buffers (tests, micro-benchmarks) --------------------------- */
 /* Engine.gemm (Engine.swift:1651-1806) for one MLX affine-4 tensor: out[r][n] = sum_k

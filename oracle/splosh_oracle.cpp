@@ -66,6 +66,7 @@ inline float bf16_fma_once(float code, float scale, float bias) {
     return round_bf16(f);
 }
 int g_weight_contract = 0;
+int g_norm_contract = 1;      // 1: a norm fed by a residual GEMM takes the deferred form (the shipped contract); 0: every norm plain
 inline float silu(float x) { return x / (1.0f + expf(-x)); }
 inline float sigmoidf(float x) { return 1.0f / (1.0f + expf(-x)); }
 
@@ -239,7 +240,7 @@ struct Operand {                       // a GEMM's activation input: bf16-rounde
 };
 
 // out[r][n] = sum_k a[r][k] * w[n][k] (+ residual), under the weight contract in force.
-void gemm(const Q4 &w, const Operand &a, int rows, float *out, int out_stride, const float *residual) {
+void gemm(const Q4 &w, const Operand &a, int rows, float *out, int out_stride, const float *residual, const float *row_scale = nullptr) {
     const int K = w.inner, groups = K / 64;
     const bool rounded = g_weight_contract == 1;
 #pragma omp parallel
@@ -278,7 +279,9 @@ void gemm(const Q4 &w, const Operand &a, int rows, float *out, int out_stride, c
                     }
                 }
                 const size_t index = size_t(r) * out_stride + n;
-                out[index] = residual ? float(acc + double(residual[index])) : float(acc);
+                // A deferred norm's per-row factor multiplies the finished sum (one fp32 multiply), as the consumers of the
+                // reference's deferred path apply rowInv to the GEMM's output.
+                out[index] = residual ? float(acc + double(residual[index])) : row_scale ? float(acc) * row_scale[r] : float(acc);
             }
         }
     }
@@ -293,6 +296,22 @@ void rmsnorm_operand(const float *x, int stride, const std::vector<uint16_t> &w,
         for (int i = 0; i < dim; ++i) ss += double(v[i]) * v[i];
         const float inv = 1.0f / sqrtf(float(ss / dim) + eps);
         for (int i = 0; i < dim; ++i) out.values[size_t(r) * dim + i] = round_bf16(v[i] * inv * bf16_to_float(w[i]));
+        out.finish_row(r);
+    }
+}
+
+// The deferred form of the same norm (Sources/Shaders/engine_na.metal:365-415, Sources/SploshRuntime/Engine.swift:1439-1451):
+// the residual GEMM that produced x emits bf16(x * w) with its per-64 sums and the squares of x; the GEMMs that read the
+// operand multiply their sums by inv[r] = rsqrt(mean x^2 + eps). The rounding point moves from x * inv * w to x * w.
+void rmsnorm_operand_deferred(const float *x, int stride, const std::vector<uint16_t> &w, int rows, int dim, float eps, Operand &out, std::vector<float> &inv) {
+    inv.assign(rows, 1.0f);
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const float *v = x + size_t(r) * stride;
+        double ss = 0;
+        for (int i = 0; i < dim; ++i) ss += double(v[i]) * v[i];
+        inv[r] = 1.0f / sqrtf(float(ss / dim) + eps);
+        for (int i = 0; i < dim; ++i) out.values[size_t(r) * dim + i] = round_bf16(v[i] * bf16_to_float(w[i]));
         out.finish_row(r);
     }
 }
@@ -613,6 +632,7 @@ uint16_t orc_bf16(float v) { return float_to_bf16(v); }
 float orc_f16_round(float v) { return round_f16(v); }
 // 0: exact codes with per-group scale and bias (default); 1: weights rounded to bf16 once.
 void orc_set_weight_contract(int contract) { g_weight_contract = contract; }
+void orc_set_norm_contract(int contract) { g_norm_contract = contract; }
 int orc_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();
@@ -953,14 +973,20 @@ int orc_step(void *engine, const Tables *tp, float *logits, float *hidden_taps, 
         // Rows the last block is computed for (Engine.swift:1419-1429); keys and values are stored for all.
         const int live = (l + 1 == g.layers) ? int(t.live_rows) : R;
         Operand xn(R, H);
-        rmsnorm_operand(h.data(), H, L.vec[V_IN_NORM], R, H, g.eps, xn);
+        // The first block's input comes from the embedding: a plain norm. Every later input norm reads what the previous
+        // block's down projection left, and takes the deferred form.
+        std::vector<float> inv_in;
+        const bool deferred_in = g_norm_contract == 1 && l > 0;
+        if (deferred_in) rmsnorm_operand_deferred(h.data(), H, L.vec[V_IN_NORM], R, H, g.eps, xn, inv_in);
+        else rmsnorm_operand(h.data(), H, L.vec[V_IN_NORM], R, H, g.eps, xn);
+        const float *scale_in = deferred_in ? inv_in.data() : nullptr;
         if (!L.full) {
             const int C = g.channels(), VD = g.value_dim(), VH = g.gdn_value_heads;
             std::vector<float> mixed(size_t(R) * C), z(size_t(R) * VD), a(size_t(R) * VH), b(size_t(R) * VH);
-            gemm(L.q4[Q_QKV], xn, R, mixed.data(), C, nullptr);
-            gemm(L.q4[Q_Z], xn, R, z.data(), VD, nullptr);
-            gemm(L.q4[Q_A], xn, R, a.data(), VH, nullptr);
-            gemm(L.q4[Q_B], xn, R, b.data(), VH, nullptr);
+            gemm(L.q4[Q_QKV], xn, R, mixed.data(), C, nullptr, scale_in);
+            gemm(L.q4[Q_Z], xn, R, z.data(), VD, nullptr, scale_in);
+            gemm(L.q4[Q_A], xn, R, a.data(), VH, nullptr, scale_in);
+            gemm(L.q4[Q_B], xn, R, b.data(), VH, nullptr, scale_in);
             Operand core(R, VD);
             gdn_layer(e, linear_index, L, t, mixed.data(), z.data(), a.data(), b.data(), core);
             if (live > 0) gemm(L.q4[Q_OUT], core, live, h.data(), H, h.data());
@@ -968,9 +994,9 @@ int orc_step(void *engine, const Tables *tp, float *logits, float *hidden_taps, 
         } else {
             const int AD = g.heads * g.head_dim, KV = g.kv_heads * g.head_dim;
             std::vector<float> qp(size_t(R) * 2 * AD), kp(size_t(R) * KV), vp(size_t(R) * KV);
-            if (live > 0) gemm(L.q4[Q_Q], xn, live, qp.data(), 2 * AD, nullptr);
-            gemm(L.q4[Q_K], xn, R, kp.data(), KV, nullptr);
-            gemm(L.q4[Q_V], xn, R, vp.data(), KV, nullptr);
+            if (live > 0) gemm(L.q4[Q_Q], xn, live, qp.data(), 2 * AD, nullptr, scale_in);
+            gemm(L.q4[Q_K], xn, R, kp.data(), KV, nullptr, scale_in);
+            gemm(L.q4[Q_V], xn, R, vp.data(), KV, nullptr, scale_in);
             Operand core(R, AD);
             attention_layer(e, full_index, L, t, live, qp.data(), kp.data(), vp.data(), core);
             if (live > 0) gemm(L.q4[Q_O], core, live, h.data(), H, h.data());
@@ -978,10 +1004,13 @@ int orc_step(void *engine, const Tables *tp, float *logits, float *hidden_taps, 
         }
         if (live > 0) {
             Operand pn(live, H);
-            rmsnorm_operand(h.data(), H, L.vec[V_POST_NORM], live, H, g.eps, pn);
+            std::vector<float> inv_post;
+            if (g_norm_contract == 1) rmsnorm_operand_deferred(h.data(), H, L.vec[V_POST_NORM], live, H, g.eps, pn, inv_post);
+            else rmsnorm_operand(h.data(), H, L.vec[V_POST_NORM], live, H, g.eps, pn);
+            const float *scale_post = g_norm_contract == 1 ? inv_post.data() : nullptr;
             std::vector<float> gate(size_t(live) * g.inter), up(size_t(live) * g.inter);
-            gemm(L.q4[Q_GATE], pn, live, gate.data(), g.inter, nullptr);
-            gemm(L.q4[Q_UP], pn, live, up.data(), g.inter, nullptr);
+            gemm(L.q4[Q_GATE], pn, live, gate.data(), g.inter, nullptr, scale_post);
+            gemm(L.q4[Q_UP], pn, live, up.data(), g.inter, nullptr, scale_post);
             Operand act(live, g.inter);      // engine.metal:200-219
 #pragma omp parallel for schedule(static)
             for (int r = 0; r < live; ++r) {

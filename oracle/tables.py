@@ -259,6 +259,86 @@ def pack_rows(sessions, max_rows, max_logit_rows=None, prefill_cap=None):
     return rows, plan
 
 
+def build_rows(host, sessions, planner_cap, block=8, max_verify_rows=64, speculate=True, attention_first=0.29, yields=None, marks=None):
+    """BatchScheduler.buildRows in full (BatchScheduler.swift:1323-1442) over a Host's allocator state: the `fits` rule for
+    speculating sessions (:1351-1353), KV-page reservation without eviction (:1336-1343), the prefill cap from
+    `planner_cap(decode_rows, decode_tokens, decode_attention, backlog, first_fed)` (:1408-1409), chunks that end at a
+    state mark (:1420-1422) or at the pages the slot already holds (:1423-1428).
+    sessions: Session objects in the scheduler's order; yields[i]: a speculating session's expected block yield;
+    marks[i]: positions where session i's prefill must stop. Returns (rows, plan, waiting) with plan entries
+    (kind, session index, count, complete) and kind 0 verify, 1 decode, 2 prefill."""
+    yields = yields or [0.0] * len(sessions); marks = marks or [[] for _ in sessions]
+    rows, plan, waiting = [], [], []
+    logit_rows, reserved = 0, 0
+    decode_tokens, decode_attention = 0.0, 0.0
+
+    def reserve(index, position):
+        nonlocal reserved
+        need = position // PAGE_TOKENS + 1 - len(host.slot_pages[sessions[index].slot])
+        if need <= 0:
+            return True
+        if need > len(host.free_pages) - reserved:
+            waiting.append(index)
+            return False
+        reserved += need
+        return True
+
+    decoders = [i for i, s in enumerate(sessions) if s.pending is not None][:host.max_slots]
+    speculative, plain = [], []
+    for i in decoders:
+        s = sessions[i]
+        ahead = len(speculative) + 1
+        fits = (ahead * block <= max_verify_rows and len(rows) + ahead * block + len(plain) <= host.max_rows
+                and logit_rows + ahead * block + len(plain) <= host.max_logit_rows)
+        if speculate and s.evaluated + block < host.max_context:
+            if fits and reserve(i, s.evaluated + 2 * block - 1):
+                speculative.append(i)
+        elif reserve(i, s.evaluated):
+            plain.append(i)
+    for i in speculative:
+        decode_tokens += yields[i]
+        decode_attention += attention_first * sessions[i].evaluated / 1000
+    for i in speculative:
+        s = sessions[i]
+        for offset, token in enumerate([s.pending] + list(s.drafts)):
+            rows.append(Row(s.slot, token, s.evaluated + offset, True, True))
+        logit_rows += len(s.drafts) + 1
+        plan.append((0, i, len(s.drafts), 0))
+    for i in plain:
+        s = sessions[i]
+        rows.append(Row(s.slot, s.pending, s.evaluated, True))
+        logit_rows += 1
+        plan.append((1, i, 0, 0))
+    prefillers = sorted((i for i, s in enumerate(sessions) if s.pending is None), key=lambda i: len(sessions[i].prompt) - sessions[i].fed)
+    cap = host.max_rows
+    if decoders:
+        backlog = sum(len(sessions[i].prompt) - sessions[i].fed for i in prefillers)
+        cap = planner_cap(len(rows), decode_tokens + len(plain), decode_attention, backlog, sessions[prefillers[0]].fed if prefillers else 0)
+    for i in prefillers:
+        s = sessions[i]
+        budget = cap - len(rows)
+        if budget <= 0:
+            break
+        count = min(len(s.prompt) - s.fed, budget)
+        later = [m for m in marks[i] if m > s.fed]
+        if later and min(later) < s.fed + count:
+            count = min(later) - s.fed
+        if not reserve(i, s.fed + count - 1):
+            count = min(count, len(host.slot_pages[s.slot]) * PAGE_TOKENS - s.fed)
+            if count <= 0:
+                continue
+            waiting.remove(i)
+        complete = s.fed + count == len(s.prompt)
+        if complete and logit_rows >= host.max_logit_rows:
+            continue
+        for offset in range(count):
+            rows.append(Row(s.slot, s.prompt[s.fed + offset], s.fed + offset, complete and offset == count - 1))
+        if complete:
+            logit_rows += 1
+        plan.append((2, i, count, 1 if complete else 0))
+    return rows, plan, waiting
+
+
 def greedy_accept(argmax_ids, drafts):
     """(agreed, bonus): the agreeing prefix of the drafts, then the target's own arg-max
     (BatchScheduler.swift:1583-1587). argmax_ids: the arg-max of the block's logit rows."""

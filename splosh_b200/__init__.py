@@ -5,7 +5,7 @@ host over it that mirrors the reference's Swift `Engine` interface
 (Sources/SploshRuntime/Engine.swift) for tests and benchmarks. There is no CPU fallback.
 """
 from .engine import (Engine, EngineConfig, EngineRow, EngineError, Geometry, Host, StepStats, tiny_geometry, b27_geometry,
-                     gemm_q4, gemm_gguf, greedy_accept, library_path, Sampler, Planner)
+                     gemm_q4, gemm_gguf, greedy_accept, library_path, Sampler, Planner, PackSession)
 
 __all__ = ["Engine", "EngineConfig", "EngineRow", "EngineError", "Geometry", "Host", "StepStats", "tiny_geometry",
-           "b27_geometry", "gemm_q4", "gemm_gguf", "greedy_accept", "library_path", "Sampler", "Planner"]
+           "b27_geometry", "gemm_q4", "gemm_gguf", "greedy_accept", "library_path", "Sampler", "Planner", "PackSession"]

@@ -30,42 +30,24 @@ __global__ void spl_embed_q4_kernel(const uint32_t *__restrict__ packed, const u
 // rounding engine_na.metal:42-57). When `index` is not
 // null row r of the output reads input row index[r] (the logit-row gather, engine.metal:273-281).
 // Grid (rows), a multiple of 32 threads up to 1,024.
-// When `partials` is given, the row is first formed from a split GEMM's partial sums (in split order) plus `input` as
-// the residual, and written back to `input`: the reduction pass of the preceding GEMM folded into this kernel
-// (spl_gemm_reduce_kernel is its stand-alone form).
 __global__ void __launch_bounds__(1024)
-spl_rmsnorm_kernel(float *input, int in_ld, const uint16_t *__restrict__ weight, const uint32_t *__restrict__ index,
-                   SplOperand out, int dim, float eps, const float *__restrict__ partials, int splits, size_t split_stride, int partial_ld) {
+spl_rmsnorm_kernel(const float *input, int in_ld, const uint16_t *__restrict__ weight, const uint32_t *__restrict__ index,
+                   SplOperand out, int dim, float eps) {
     spl_grid_begin();
     __shared__ float part[32];
     const int stride = blockDim.x * 4, warps = blockDim.x >> 5;
     const int row = blockIdx.x;
-    float *x = input + size_t(index ? index[row] : row) * in_ld;
+    const float *x = input + size_t(index ? index[row] : row) * in_ld;
     float ss = 0.0f;
-    if (partials) {
-        const float *pr = partials + size_t(row) * partial_ld;
-        for (int i = threadIdx.x * 4; i < dim; i += stride) {
-            float4 sum = *reinterpret_cast<const float4 *>(pr + i);
-            for (int sp = 1; sp < splits; ++sp) {
-                const float4 q = *reinterpret_cast<const float4 *>(pr + size_t(sp) * split_stride + i);
-                sum.x += q.x; sum.y += q.y; sum.z += q.z; sum.w += q.w;
-            }
-            const float4 r = *reinterpret_cast<const float4 *>(x + i);
-            sum.x += r.x; sum.y += r.y; sum.z += r.z; sum.w += r.w;
-            *reinterpret_cast<float4 *>(x + i) = sum;
-            ss += sum.x * sum.x + sum.y * sum.y + sum.z * sum.z + sum.w * sum.w;
-        }
-    } else {
-        for (int i = threadIdx.x * 4; i < dim; i += stride) {
-            const float4 v = *reinterpret_cast<const float4 *>(x + i);
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
+    for (int i = threadIdx.x * 4; i < dim; i += stride) {
+        const float4 v = *reinterpret_cast<const float4 *>(x + i);
+        ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
     ss = spl_warp_sum(ss);
     if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
     __syncthreads();
     float total = 0.0f;
-for (int i = 0; i < warps; ++i) total += part[i];
+    for (int i = 0; i < warps; ++i) total += part[i];
     const float inv = 1.0f / sqrtf(total / float(dim) + eps);
     for (int base = 0; base < dim; base += stride) {
         const int i = base + threadIdx.x * 4;

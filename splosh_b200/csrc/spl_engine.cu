@@ -62,6 +62,11 @@ struct spl_engine {
     float *taps = nullptr;
     __nv_bfloat16 *xn = nullptr, *core = nullptr, *act = nullptr, *hsn = nullptr;      // GEMM operands (tile layout)
     float *xn_sums = nullptr, *core_sums = nullptr, *act_sums = nullptr, *hsn_sums = nullptr;
+    float *xn_squares = nullptr;       // [row][hidden / 64] squares of the residual stream, left by the GEMM that feeds a deferred norm
+    float *slots = nullptr;            // partial sums of the GEMM tiles that several blocks share
+    int *tickets = nullptr;            // one per (row block, tile); zero between launches
+    size_t slot_floats = 0, ticket_count = 0;
+    int sms = 148;
     int rows_padded = 0, logit_rows_padded = 0;
     int *tc_error = nullptr;
     // Drafter feature taps (Engine.swift:330-331, 1488-1497): the residual stream after the listed blocks, [row][tap][hidden].
@@ -181,7 +186,7 @@ void launch_step(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, c
 // Rows per operand block for a step of `rows` rows.
 int operand_rn(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : 64; }
 
-// Splits of the contraction for a GEMM of `blocks` (tile, row block) pairs and `groups` quant
+// Splits of the contraction for a GGUF GEMM of `blocks` (tile, row block) pairs and `groups` quant
 // groups: the count that minimises waves x groups per block on `sms` single-block SMs, with a
 // fixed cost per block (pipeline fill) and a reduction pass counted in.
 int choose_splits(int blocks, int groups, int sms, size_t partial_capacity, size_t partial_per_split) {
@@ -198,42 +203,69 @@ int choose_splits(int blocks, int groups, int sms, size_t partial_capacity, size
 }
 
 struct GemmOperand { const __nv_bfloat16 *values; const float *sums; int rn, blocks; };
-// A split GEMM whose reduction (partials in split order + residual) is left to the kernel that reads its output next.
-struct PendingReduce { int splits = 1; size_t stride = 0; int ld = 0; };
+// What a GEMM does besides the product. `fuse_act`: a fused gate|up tensor writes the SiLU-gated activation as the next
+// operand. `in_squares`: the operand came from a deferred norm, the sums are scaled by the rows' factors. `emit_weight`:
+// the output feeds a deferred norm, whose operand and squares the GEMM leaves as well.
+struct GemmExtras {
+    const SplOperand *fuse_act = nullptr;
+    const float *in_squares = nullptr; int in_dim = 0; float eps = 0.0f;
+    const uint16_t *emit_weight = nullptr; const SplOperand *emit_out = nullptr; float *emit_squares = nullptr;
+};
+// Where the tiles that several blocks share meet: slots for partial sums and one ticket per (row block, tile).
+struct GemmScratch { float *slots; size_t slot_floats; int *tickets; size_t ticket_count; int *error_flag; int sms; };
 
-template <int RN>
-void launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows,
-                    float *partials, size_t partial_floats, int *error_flag, int *launches, PendingReduce *defer, const SplOperand *fuse_act) {
-    const int groups = w.k / 64;
-    const int row_blocks = (rows + RN - 1) / RN, rows_padded = op.blocks * RN;
-    // A block that writes the activation needs the whole contraction (silu is not linear).
-    const int splits = fuse_act ? 1 : choose_splits(w.tiles * row_blocks, groups, 148, partial_floats, size_t(rows_padded) * w.ld);
-    const int gps = ((groups + splits - 1) / splits + 3) / 4 * 4;
-    const size_t smem = spl_tc_smem_bytes(RN);
-    static bool configured = false;
-    if (!configured) {
-        cudaFuncSetAttribute(spl_gemm_q4_tc_kernel<RN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-        configured = true;
+// The kernels that need more than the default shared memory, opted in on the current device (the attribute is per device).
+template <int RN> void configure_gemm() { cudaFuncSetAttribute(spl_gemm_q4_tc_kernel<RN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_tc_smem_bytes(RN))); }
+template <int RN, int FMT> void configure_gguf() { cudaFuncSetAttribute(spl_gemm_gguf_tc_kernel<RN, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_gguf_smem_bytes(RN, FMT))); }
+template <int HD, int PER_KV> void configure_scan() { cudaFuncSetAttribute(spl_attn_scan_kernel<HD, PER_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_attn_smem_bytes(HD, spl_attn_nq(PER_KV)))); }
+// Once per device and process, with that device current. `sms` (may be null) receives its SM count.
+bool configure_device(int device, int *sms) {
+    static bool done[64] = {};
+    static int count[64] = {};
+    if (device < 0 || device >= 64) return false;
+    if (!done[device]) {
+        configure_gemm<16>(); configure_gemm<32>(); configure_gemm<64>();
+        configure_gguf<16, SPL_GGUF_Q4K>(); configure_gguf<32, SPL_GGUF_Q4K>(); configure_gguf<64, SPL_GGUF_Q4K>();
+        configure_gguf<16, SPL_GGUF_Q5K>(); configure_gguf<32, SPL_GGUF_Q5K>(); configure_gguf<64, SPL_GGUF_Q5K>();
+        configure_gguf<16, SPL_GGUF_Q6K>(); configure_gguf<32, SPL_GGUF_Q6K>(); configure_gguf<64, SPL_GGUF_Q6K>();
+        configure_scan<256, 6>(); configure_scan<128, 4>();
+        cudaDeviceProp prop;
+        if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return false;
+        count[device] = prop.multiProcessorCount;
+        if (cudaGetLastError() != cudaSuccess) return false;
+        done[device] = true;
     }
-    launch_step(spl_gemm_q4_tc_kernel<RN>, dim3(dim3(w.tiles, splits, row_blocks)), dim3(SPL_TC_THREADS), smem, stream, 
-        w.codes, w.sb, op.values, op.sums, out, w.ld, residual, partials, rows, op.blocks, groups, gps, error_flag,
-        w.interleave, fuse_act ? *fuse_act : SplOperand{nullptr, nullptr, RN, 1}, fuse_act ? 1 : 0);
-    if (launches) ++*launches;
-    if (defer) { defer->splits = splits; defer->stride = size_t(rows_padded) * w.ld; defer->ld = w.ld; }
-    if (splits > 1 && !defer) {
-        const size_t total = size_t(rows) * w.ld / 4;
-        const int blocks = int(std::min<size_t>((total + 255) / 256, 2048));
-        launch_step(spl_gemm_reduce_kernel, dim3(blocks), dim3(256), 0, stream, partials, splits, rows_padded, rows, w.ld, residual, out);
-        if (launches) ++*launches;
-    }
+    if (sms) *sms = count[device];
+    return true;
 }
 
-// out[r][:] = GEMM(w, operand[r][:]) (+ residual) for the first `rows` rows of the operand.
-void launch_gemm_rows(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows,
-                      float *partials, size_t partial_floats, int *error_flag, int *launches, PendingReduce *defer = nullptr, const SplOperand *fuse_act = nullptr) {
-    if (op.rn == 16) launch_gemm_tc<16>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer, fuse_act);
-    else if (op.rn == 32) launch_gemm_tc<32>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer, fuse_act);
-    else launch_gemm_tc<64>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag, launches, defer, fuse_act);
+// Blocks of a GEMM launch: one per SM, fewer when the tensor has fewer stages than that.
+int gemm_blocks(const SplQ4Dev &w, int sms) { return int(std::min<long long>(sms, (long long)w.tiles * (w.k / 256))); }
+
+template <int RN>
+bool launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows,
+                    const GemmScratch &scratch, const GemmExtras &x, int *launches) {
+    const int row_blocks = (rows + RN - 1) / RN, blocks = gemm_blocks(w, scratch.sms);
+    if (spl_tc_slot_floats(blocks, row_blocks, RN) > scratch.slot_floats || size_t(row_blocks) * w.tiles > scratch.ticket_count) return false;
+    SplGemmArgs a = {};
+    a.codes = w.codes; a.sb = w.sb; a.act = op.values; a.act_sums = op.sums; a.out = out; a.residual = residual;
+    a.slots = scratch.slots; a.tickets = scratch.tickets; a.error_flag = scratch.error_flag;
+    a.out_ld = w.ld; a.rows = rows; a.op_blocks = op.blocks; a.tiles = w.tiles; a.stages_per_tile = w.k / 256; a.interleave = w.interleave;
+    a.fuse = x.fuse_act ? 1 : 0;
+    a.act_out = x.fuse_act ? *x.fuse_act : SplOperand{nullptr, nullptr, RN, 1};
+    a.in_squares = x.in_squares; a.in_groups = x.in_dim / 64; a.in_dim = float(x.in_dim); a.eps = x.eps;
+    a.emit_weight = x.emit_weight; a.emit_out = x.emit_out ? *x.emit_out : SplOperand{nullptr, nullptr, RN, 1}; a.emit_squares = x.emit_squares;
+    launch_step(spl_gemm_q4_tc_kernel<RN>, dim3(blocks, 1, row_blocks), dim3(SPL_TC_THREADS), spl_tc_smem_bytes(RN), stream, a);
+    if (launches) ++*launches;
+    return true;
+}
+
+// out[r][:] = GEMM(w, operand[r][:]) (+ residual) for the first `rows` rows of the operand. False when the scratch is too small.
+bool launch_gemm_rows(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows,
+                      const GemmScratch &scratch, const GemmExtras &x, int *launches) {
+    if (op.rn == 16) return launch_gemm_tc<16>(stream, w, op, out, residual, rows, scratch, x, launches);
+    if (op.rn == 32) return launch_gemm_tc<32>(stream, w, op, out, residual, rows, scratch, x, launches);
+    return launch_gemm_tc<64>(stream, w, op, out, residual, rows, scratch, x, launches);
 }
 
 template <int RN, int FMT>
@@ -245,8 +277,6 @@ void launch_gemm_gguf_tc(cudaStream_t stream, const SplGgufDev &w, const GemmOpe
     const int splits4 = choose_splits(w.tiles * row_blocks, supers * 4, 148, partial_floats, size_t(rows_padded) * w.ld);
     const int sps = (supers + splits4 - 1) / splits4, splits = (supers + sps - 1) / sps;
     const size_t smem = spl_gguf_smem_bytes(RN, FMT);
-    static bool configured = false;
-    if (!configured) { cudaFuncSetAttribute(spl_gemm_gguf_tc_kernel<RN, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); configured = true; }
     launch_step(spl_gemm_gguf_tc_kernel<RN, FMT>, dim3(w.tiles, splits, row_blocks), dim3(SPL_GG_THREADS), smem, stream,
                 w.blocks, op.values, out, w.ld, residual, partials, rows, op.blocks, supers, sps, error_flag);
     if (splits > 1) {
@@ -268,18 +298,18 @@ void launch_gemm_gguf(cudaStream_t stream, const SplGgufDev &w, const GemmOperan
     else launch_gemm_gguf_rows<SPL_GGUF_Q4K>(stream, w, op, out, residual, rows, partials, partial_floats, error_flag);
 }
 
-void launch_gemm(spl_engine *e, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows, PendingReduce *defer = nullptr, const SplOperand *fuse_act = nullptr) {
+bool launch_gemm(spl_engine *e, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows, const GemmExtras &x = GemmExtras()) {
     profile_begin(e, KLASS_GEMM, double(w.bytes()) * ((rows + op.rn - 1) / op.rn));
     --e->launches;      // profile_begin counted one; the launcher counts the kernels it really starts
-    launch_gemm_rows(e->stream, w, op, out, residual, rows, e->partials, e->partial_floats, e->tc_error, &e->launches, defer, fuse_act);
+    const GemmScratch scratch{e->slots, e->slot_floats, e->tickets, e->ticket_count, e->tc_error, e->sms};
+    const bool fits = launch_gemm_rows(e->stream, w, op, out, residual, rows, scratch, x, &e->launches);
     profile_end(e);
+    return fits;
 }
 
 template <int HD, int PER_KV>
 void launch_scan_tc(spl_engine *e, dim3 grid, const SplAttnParams &p, int layer) {
     const size_t smem = spl_attn_smem_bytes(HD, spl_attn_nq(PER_KV));
-    static bool configured = false;
-    if (!configured) { cudaFuncSetAttribute(spl_attn_scan_kernel<HD, PER_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem)); configured = true; }
     launch_step(spl_attn_scan_kernel<HD, PER_KV>, dim3(grid), dim3(SPL_ATTN_THREADS), smem, e->stream, e->q, e->d_blocks, e->d_row_slot, e->d_row_pos, e->d_page_table,
         e->k_codes[layer], e->k_scale[layer], e->v_codes[layer], e->v_scale[layer], e->attn_partials, p, e->tc_error);
 }
@@ -336,26 +366,30 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
     launch_step(spl_embed_q4_kernel, dim3(R), dim3(128), 0, e->stream, e->embed_packed, e->embed_scales, e->embed_biases, e->d_tokens, e->h, H);
     profile_end(e);
 
-    // RMSNorm into an operand; `pending` names a split GEMM into `e->h` whose reduction this kernel performs first.
-    auto norm = [&](int rows, const uint16_t *weight, const uint32_t *gather, const SplOperand &dst, const PendingReduce &pending) {
-        const bool fused = pending.splits > 1;
-        launch_step(spl_rmsnorm_kernel, dim3(rows), dim3(fused ? 1024 : 256), 0, e->stream, e->h, H, weight, gather, dst, H, g.eps,
-                    fused ? e->partials : nullptr, pending.splits, pending.stride, pending.ld);
+    // The attention partials of the widest scan of the step have to fit (checked before anything is launched, so a
+    // refused step leaves no slot half-advanced).
+    if (!e->k_codes.empty() && size_t(R) * g.heads * t->spans * (g.head_dim + 2) > e->attn_partial_floats)
+        return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: attention partials exceed the engine's buffers");
+    // A plain RMSNorm into an operand: the first block's input (the embedding's output) and the final norm.
+    auto norm = [&](int rows, const uint16_t *weight, const uint32_t *gather, const SplOperand &dst) {
+        launch_step(spl_rmsnorm_kernel, dim3(rows), dim3(256), 0, e->stream, e->h, H, weight, gather, dst, H, g.eps);
     };
-    PendingReduce carried;      // the previous block's down projection, when its reduction is left to this block's input norm
+    // Every other norm is deferred (Sources/SploshRuntime/Engine.swift:1439-1451): the GEMM that adds into the residual
+    // stream leaves bf16(h * w) as the next operand with the squares of h, and the GEMM that reads it scales its sums.
+    GemmExtras scaled; scaled.in_squares = e->xn_squares; scaled.in_dim = H; scaled.eps = g.eps;
+    bool fits = true;
     int linear_index = 0, full_index = 0;
-    const int span_rows_needed = int(t->spans);
-    (void)span_rows_needed;
     for (int l = 0; l < g.layers; ++l) {
         const LayerWeights &L = e->layers[l];
         const int live = (l + 1 == g.layers) ? int(t->live_rows) : R;
         int feature_tap = -1;
         for (size_t f = 0; f < e->feature_layers.size(); ++f) if (e->feature_layers[f] == l) feature_tap = int(f);
-        profile_begin(e, KLASS_ELEMENTWISE, 0);
-        norm(R, L.vec[SPL_VEC_INPUT_NORM], nullptr, xn, carried);
-        carried = PendingReduce();
-        profile_end(e);
-        launch_gemm(e, L.in_proj, gxn, e->proj, nullptr, R);
+        if (l == 0) {
+            profile_begin(e, KLASS_ELEMENTWISE, 0);
+            norm(R, L.vec[SPL_VEC_INPUT_NORM], nullptr, xn);
+            profile_end(e);
+        }
+        fits &= launch_gemm(e, L.in_proj, gxn, e->proj, nullptr, R, l == 0 ? GemmExtras() : scaled);
         if (!L.full) {
             SplGdnParams p;
             p.rows = R; p.runs = int(t->run_count); p.channels = sh.C; p.key_heads = g.gdn_key_heads; p.value_heads = g.gdn_value_heads;
@@ -385,8 +419,6 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
                 int blocks = 0;
                 for (; blocks < int(t->attn_block_count); ++blocks)
                     if (int(t->attn_blocks[blocks * 2]) >= live) break;
-                if (size_t(live) * g.heads * t->spans * (g.head_dim + 2) > e->attn_partial_floats)
-                    return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: attention partials exceed the engine's buffers");
                 profile_begin(e, KLASS_ATTENTION, 0);
                 launch_scan(e, dim3(g.kv_heads * t->spans, blocks), p, full_index);
                 profile_end(e);
@@ -397,17 +429,16 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
             ++full_index;
         }
         if (live > 0) {
-            PendingReduce mixer;
-            launch_gemm(e, L.out_proj, gcore, e->h, e->h, live, &mixer);
-            profile_begin(e, KLASS_ELEMENTWISE, 0);
-            norm(live, L.vec[SPL_VEC_POST_NORM], nullptr, xn, mixer);
-            profile_end(e);
+            // The mixer's output projection adds into the residual stream and leaves the post norm's operand.
+            GemmExtras mixer; mixer.emit_weight = L.vec[SPL_VEC_POST_NORM]; mixer.emit_out = &xn; mixer.emit_squares = e->xn_squares;
+            fits &= launch_gemm(e, L.out_proj, gcore, e->h, e->h, live, mixer);
             // gate|up and the SiLU gate in one kernel: the GEMM's blocks write act = bf16(silu(gate) * up) and its sums.
-            launch_gemm(e, L.gate_up, gxn, e->gate_up, nullptr, live, nullptr, &act);
-            // The down projection's reduction is left to the next block's input norm, except after the last block (the final
-            // norm gathers rows) and when the residual stream is tapped after every block.
-            const bool leave = l + 1 < g.layers && !e->taps_enabled && feature_tap < 0 && live == R;
-            launch_gemm(e, L.down, gact, e->h, e->h, live, leave ? &carried : nullptr);
+            GemmExtras mlp = scaled; mlp.fuse_act = &act;
+            fits &= launch_gemm(e, L.gate_up, gxn, e->gate_up, nullptr, live, mlp);
+            // The down projection leaves the next block's input norm operand (the final norm gathers rows: it stays a kernel).
+            GemmExtras down;
+            if (l + 1 < g.layers) { down.emit_weight = e->layers[l + 1].vec[SPL_VEC_INPUT_NORM]; down.emit_out = &xn; down.emit_squares = e->xn_squares; }
+            fits &= launch_gemm(e, L.down, gact, e->h, e->h, live, down);
         }
         if (e->taps_enabled) SPL_CUDA(cudaMemcpyAsync(e->taps + size_t(l) * e->c.max_rows * H, e->h, size_t(R) * H * 4, cudaMemcpyDeviceToDevice, e->stream));
         if (feature_tap >= 0) {
@@ -419,10 +450,11 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
     if (t->logit_rows > 0) {
         profile_begin(e, KLASS_OTHER, 0);
         const int lrn = operand_rn(int(t->logit_rows)), lblocks = (int(t->logit_rows) + lrn - 1) / lrn;
-        norm(int(t->logit_rows), e->final_norm, e->d_gather, SplOperand{e->hsn, e->hsn_sums, lrn, lblocks}, PendingReduce());
+        norm(int(t->logit_rows), e->final_norm, e->d_gather, SplOperand{e->hsn, e->hsn_sums, lrn, lblocks});
         profile_end(e);
-        launch_gemm(e, e->head, GemmOperand{e->hsn, e->hsn_sums, operand_rn(int(t->logit_rows)), (int(t->logit_rows) + operand_rn(int(t->logit_rows)) - 1) / operand_rn(int(t->logit_rows))}, e->logits, nullptr, int(t->logit_rows));
+        fits &= launch_gemm(e, e->head, GemmOperand{e->hsn, e->hsn_sums, lrn, lblocks}, e->logits, nullptr, int(t->logit_rows));
     }
+    if (!fits) return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: the GEMM scratch is smaller than the step needs");
     SPL_CUDA(cudaEventRecord(e->ev_end, e->stream));
     e->flying_rows = R; e->flying_logit_rows = int(t->logit_rows);
     return check_launch(e, "step launch");
@@ -433,20 +465,19 @@ spl_status finish_step(spl_engine *e, spl_step_stats *stats) {
     SPL_CUDA(cudaSetDevice(e->device));
     SPL_CUDA(cudaStreamSynchronize(e->stream));
     {
-        int flag = 0;
-        SPL_CUDA(cudaMemcpy(&flag, e->tc_error, sizeof flag, cudaMemcpyDeviceToHost));
-        if (flag) { cudaMemset(e->tc_error, 0, sizeof flag); return e->fail(SPL_ERR_TIMEOUT, "a GEMM block gave up waiting (role " + std::to_string(flag - 1) + ")"); }
-    }
-    if (getenv("SPL_GDN_TRACE")) {
-        int t[64]; cudaMemcpy(t, e->tc_error, sizeof t, cudaMemcpyDeviceToHost);
-        fprintf(stderr, "gdn timeline of block 0, cycles from entry: loads landed %d, scalars %d, replay %d, barrier %d, tokens %d, barrier %d, norm %d\n", t[56], t[57], t[58], t[59], t[60], t[61], t[62]);
-    }
-    if (getenv("SPL_ATTN_TRACE")) {
-        int t[64]; cudaMemcpy(t, e->tc_error, sizeof t, cudaMemcpyDeviceToHost);
-        fprintf(stderr, "attention trace, cycles per chunk: copy [wait %d, issue %d] mma [wait S slot %d, wait K %d, issue S %d, wait P %d, wait V %d, issue PV %d] "
-                        "K [wait %d, convert %d, wait slot %d, store %d] V [wait %d, convert %d, wait slot %d, store %d] "
-                        "softmax [wait kv %d, wait S %d, pass1 %d, exchange %d, wait P slot %d, rescale %d, pass2 %d] chunks %d\n",
-                t[32], t[33], t[34], t[35], t[36], t[37], t[38], t[39], t[40], t[41], t[42], t[43], t[44], t[45], t[46], t[47], t[48], t[49], t[50], t[51], t[52], t[53], t[54], t[55]);
+        int flag[4] = {0, 0, 0, 0};
+        SPL_CUDA(cudaMemcpy(flag, e->tc_error, sizeof flag, cudaMemcpyDeviceToHost));
+        if (flag[0]) {
+            // A block gave up: its tile's ticket may be left half-taken, so the tickets start again from zero.
+            cudaMemset(e->tc_error, 0, sizeof flag);
+            cudaMemset(e->tickets, 0, e->ticket_count * sizeof(int));
+            if (flag[0] >= 100) return e->fail(SPL_ERR_TIMEOUT, "an attention scan block gave up waiting (warp " + std::to_string(flag[0] - 100) + ")");
+            // The wait that ran out first: 10 weight copy for a free stage; 20, 21 activation copy for a free tile of means, a free
+            // stage; 30-37 tensor-core issue (two warps) for a tile of means, the accumulators, activations, converted weights;
+            // 40-42 conversion for the accumulators' completion, a weight stage, a free operand slot.
+            return e->fail(SPL_ERR_TIMEOUT, "a GEMM block gave up waiting (warp " + std::to_string(flag[0] - 1) + "; first wait " + std::to_string(flag[1]) +
+                                            " at " + std::to_string(flag[2]) + ", block " + std::to_string(flag[3] & 0xFFFF) + ")");
+        }
     }
     profile_collect(e);
     e->last_rows = R; e->last_logit_rows = e->flying_logit_rows;
@@ -550,6 +581,7 @@ spl_status create(const spl_geometry *gp, const spl_config *cp, spl_engine *e) {
     if (prop.major != 10) return e->fail(SPL_ERR_UNSUPPORTED_DEVICE, "unsupported device: kernels are built for sm_100a only");
     e->device = cp->device;
     SPL_CUDA(cudaSetDevice(e->device));
+    if (!configure_device(e->device, &e->sms)) return e->fail(SPL_ERR_UNSUPPORTED_DEVICE, "unsupported device: the kernels' shared-memory opt-in failed");
     spl_status hs = spl_host_create(gp, cp, &e->host);
     if (hs != SPL_OK) return e->fail(hs, "invalid engine configuration");
     e->c = e->host->config;
@@ -622,7 +654,6 @@ spl_status create(const spl_geometry *gp, const spl_config *cp, spl_engine *e) {
     if ((s = device_alloc(e, &e->hsn_sums, spl_operand_sums_floats(LP, H), &e->scratch_bytes)) != SPL_OK) return s;
     if ((s = device_alloc(e, &e->tc_error, 64)) != SPL_OK) return s;
     SPL_CUDA(cudaMemsetAsync(e->tc_error, 0, 64 * sizeof(int), e->stream));
-    if (getenv("SPL_ATTN_TRACE")) { const int magic[2] = {0x7ACE, 0x200}; SPL_CUDA(cudaMemcpyAsync(e->tc_error + 1, magic, sizeof magic, cudaMemcpyHostToDevice, e->stream)); }
     SPL_CUDA(cudaMemsetAsync(e->xn, 0, size_t(RP) * H * 2, e->stream));
     SPL_CUDA(cudaMemsetAsync(e->xn_sums, 0, spl_operand_sums_floats(RP, H) * 4, e->stream));
     SPL_CUDA(cudaMemsetAsync(e->core_sums, 0, spl_operand_sums_floats(RP, e->core_ld) * 4, e->stream));
@@ -640,8 +671,18 @@ spl_status create(const spl_geometry *gp, const spl_config *cp, spl_engine *e) {
     SPL_CUDA(cudaMemsetAsync(e->hsn, 0, size_t(LP) * H * 2, e->stream));
     if ((s = device_alloc(e, &e->logits, size_t(LR) * e->logits_ld, &e->scratch_bytes)) != SPL_OK) return s;
     if ((s = device_alloc(e, &e->argmax_ids, size_t(LR), &e->scratch_bytes)) != SPL_OK) return s;
-    e->partial_floats = size_t(16) * RP * std::max(H, 4096);
+    e->partial_floats = size_t(16) * RP * std::max(H, 4096);      // split-K partial sums of the GGUF kernel
     if ((s = device_alloc(e, &e->partials, e->partial_floats, &e->scratch_bytes)) != SPL_OK) return s;
+    // The q4 GEMM's meeting place for tiles that several blocks share: two slots of 64 x 128 sums a block and row block,
+    // one ticket per (row block, tile) of the widest tensor.
+    const int row_blocks = std::max(RP, LP) / 64;
+    e->slot_floats = spl_tc_slot_floats(e->sms, row_blocks, 64);
+    e->ticket_count = size_t(row_blocks) * ((std::max(std::max(g.vocab, 2 * g.inter), std::max(sh.gdn_n, sh.att_n)) + 127) / 128);
+    if ((s = device_alloc(e, &e->slots, e->slot_floats, &e->scratch_bytes)) != SPL_OK) return s;
+    if ((s = device_alloc(e, &e->tickets, e->ticket_count, &e->scratch_bytes)) != SPL_OK) return s;
+    SPL_CUDA(cudaMemsetAsync(e->tickets, 0, e->ticket_count * sizeof(int), e->stream));
+    if ((s = device_alloc(e, &e->xn_squares, size_t(RP) * (H / 64), &e->scratch_bytes)) != SPL_OK) return s;
+    SPL_CUDA(cudaMemsetAsync(e->xn_squares, 0, size_t(RP) * (H / 64) * 4, e->stream));
     e->attn_partial_floats = size_t(std::max(16 * R, 64 * std::min(R, 128))) * g.heads * (g.head_dim + 2);
     if ((s = device_alloc(e, &e->attn_partials, e->attn_partial_floats, &e->scratch_bytes)) != SPL_OK) return s;
     e->tables_words = size_t(R) * 5 + size_t(e->c.max_slots) * 5 + size_t(LR) + size_t(R) * 2 + size_t(e->c.max_slots) * e->host->max_pages + 64;
@@ -678,7 +719,7 @@ void spl_engine_destroy(spl_engine *e) {
     for (auto p : e->state) cudaFree(p); for (auto p : e->conv) cudaFree(p); for (auto p : e->journal) cudaFree(p);
     cudaFree(e->h); cudaFree(e->xn); cudaFree(e->proj); cudaFree(e->gdn_act); cudaFree(e->core); cudaFree(e->gate_up); cudaFree(e->act);
     cudaFree(e->q); cudaFree(e->hsn); cudaFree(e->logits); cudaFree(e->argmax_ids); cudaFree(e->partials); cudaFree(e->attn_partials);
-    cudaFree(e->taps); cudaFree(e->features); cudaFree(e->topk_ids); cudaFree(e->topk_values); cudaFree(e->tables_dev); cudaFree(e->xn_sums); cudaFree(e->core_sums); cudaFree(e->act_sums); cudaFree(e->hsn_sums); cudaFree(e->tc_error);
+    cudaFree(e->taps); cudaFree(e->features); cudaFree(e->topk_ids); cudaFree(e->topk_values); cudaFree(e->tables_dev); cudaFree(e->slots); cudaFree(e->tickets); cudaFree(e->xn_squares); cudaFree(e->xn_sums); cudaFree(e->core_sums); cudaFree(e->act_sums); cudaFree(e->hsn_sums); cudaFree(e->tc_error);
     if (e->tables_host) cudaFreeHost(e->tables_host);
     for (ProfileSlot &s : e->profile_slots) { cudaEventDestroy(s.begin); cudaEventDestroy(s.end); }
     if (e->ev_begin) cudaEventDestroy(e->ev_begin);
@@ -934,6 +975,21 @@ spl_status spl_debug_taps(spl_engine *e, int32_t enabled) {
     SPL_CUDA(cudaSetDevice(e->device));
     if (enabled && !e->taps) SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&e->taps), size_t(e->g.layers) * e->c.max_rows * e->g.hidden * 4));
     e->taps_enabled = enabled != 0;
+    return SPL_OK;
+}
+
+spl_status spl_debug_wait_budget(spl_engine *e, int64_t nanoseconds) {
+    if (!e || nanoseconds <= 0) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_CUDA(cudaSetDevice(e->device));
+    const unsigned long long value = static_cast<unsigned long long>(nanoseconds);
+    SPL_CUDA(cudaMemcpyToSymbol(spl_wait_budget_ns, &value, sizeof value));
+    return SPL_OK;
+}
+
+spl_status spl_debug_drop_weight_stage(spl_engine *e, int32_t stage) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_CUDA(cudaSetDevice(e->device));
+    SPL_CUDA(cudaMemcpyToSymbol(spl_drop_weight_stage, &stage, sizeof stage));
     return SPL_OK;
 }
 
@@ -1198,22 +1254,26 @@ spl_status spl_kv_import(spl_engine *e, int32_t slot, int32_t token_count, const
 // For callers that may not allocate device memory: a host that handed the whole GPU to its own
 // pool at start-up, or a serving loop that bans allocator calls on its hot path because
 // cudaMalloc and cudaFree synchronise the whole device. The scratch the ordinary path takes from the engine's buffers (the bf16 operand with its
-// per-64 sums, and the split-K partial sums) lives here in one file-scope device array, so every
-// GPU that loads the library holds SPL_STATIC_BYTES (about 10.3 MiB) until the process exits.
+// per-64 sums, the slots where blocks that share a tile leave their partial sums, and the tiles' tickets) lives here in
+// one file-scope device array, so every GPU that loads the library holds SPL_STATIC_BYTES (about 12.9 MiB) until the
+// process exits.
 #define SPL_STATIC_ROWS 64
 #define SPL_STATIC_INNER 17408
 #define SPL_STATIC_OPERAND_BYTES (SPL_STATIC_ROWS * SPL_STATIC_INNER * 2)
 #define SPL_STATIC_SUMS_BYTES (SPL_STATIC_ROWS * ((SPL_STATIC_INNER / 64 + 15) / 16) * 128)      // tiles of split means
-#define SPL_STATIC_FLAG_BYTES 256      // the error word and the kernel's debug words
-#define SPL_STATIC_PARTIAL_BYTES (8u << 20)
-#define SPL_STATIC_BYTES (SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES + SPL_STATIC_FLAG_BYTES + SPL_STATIC_PARTIAL_BYTES)
+#define SPL_STATIC_CONTROL_BYTES 16384     // the error word (first 256 bytes), then one ticket per 128-column tile
+#define SPL_STATIC_TILES ((SPL_STATIC_CONTROL_BYTES - 256) / 4)
+#define SPL_STATIC_BLOCKS 160              // blocks a launch may use: two slots of 64 x 128 sums each
+#define SPL_STATIC_SLOT_BYTES (SPL_STATIC_BLOCKS * 2 * 64 * 128 * 4)
+#define SPL_STATIC_BYTES (SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES + SPL_STATIC_CONTROL_BYTES + SPL_STATIC_SLOT_BYTES)
 static __device__ __align__(256) unsigned char spl_static_scratch[SPL_STATIC_BYTES];
 // The array's address on each device, asked for once per device. The symbol itself is only a
 // host-side handle: a kernel must be given what cudaGetSymbolAddress returns.
 static void *spl_static_address[64] = {};
 
 // fp32 rows -> the bf16 GEMM operand and its per-64 sums (Sources/Shaders/engine_na.metal:42-57;
-// layout: SplOperand). Grid (rows), 256 threads.
+// layout: SplOperand). Groups past the contraction in the last tile of split means are written as zero, so nothing an
+// earlier call left there is ever multiplied. Grid (rows), 256 threads.
 __global__ void __launch_bounds__(256)
 spl_operand_kernel(const float *__restrict__ input, SplOperand out, int inner) {
     const int row = blockIdx.x;
@@ -1231,6 +1291,21 @@ spl_operand_kernel(const float *__restrict__ input, SplOperand out, int inner) {
         for (int o = 8; o > 0; o >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o);
         if (i < inner && (threadIdx.x & 15) == 0) out.put_sum(row, i / 64, gsum);
     }
+    const int groups = inner / 64;
+    for (int g = groups + int(threadIdx.x); g < (groups + 15) / 16 * 16; g += blockDim.x) out.put_sum(row, g, 0.0f);
+}
+
+static spl_status static_base(spl_engine *e, unsigned char **base) {
+    SPL_CUDA(cudaSetDevice(e->device));
+    if (e->device >= 64) return e->fail(SPL_ERR_UNSUPPORTED_DEVICE, "spl_gemm_q4_static: device ordinal beyond 63");
+    if (!spl_static_address[e->device]) {
+        // First call on this device: resolve the array's device address (this device is current).
+        void *address = nullptr;
+        SPL_CUDA(cudaGetSymbolAddress(&address, spl_static_scratch));
+        spl_static_address[e->device] = address;
+    }
+    *base = static_cast<unsigned char *>(spl_static_address[e->device]);
+    return SPL_OK;
 }
 
 extern "C" spl_status spl_gemm_q4_static(spl_engine *e, int32_t layer, int32_t which, const float *device_activations, int32_t rows,
@@ -1248,28 +1323,39 @@ extern "C" spl_status spl_gemm_q4_static(spl_engine *e, int32_t layer, int32_t w
         return e->fail(SPL_ERR_INVALID_ROWS, "spl_gemm_q4_static: rows must be 1..64 (the static scratch holds a 64-row operand)");
     if (w->k > SPL_STATIC_INNER)
         return e->fail(SPL_ERR_INVALID_ARGUMENT, "spl_gemm_q4_static: contraction longer than 17408 does not fit the static scratch");
-    SPL_CUDA(cudaSetDevice(e->device));
-    if (e->device >= 64) return e->fail(SPL_ERR_UNSUPPORTED_DEVICE, "spl_gemm_q4_static: device ordinal beyond 63");
-    if (!spl_static_address[e->device]) {
-        // First call on this device: resolve the array's device address (this device is current).
-        void *address = nullptr;
-        SPL_CUDA(cudaGetSymbolAddress(&address, spl_static_scratch));
-        spl_static_address[e->device] = address;
-    }
-    unsigned char *base = static_cast<unsigned char *>(spl_static_address[e->device]);
+    if (w->tiles > SPL_STATIC_TILES)
+        return e->fail(SPL_ERR_INVALID_ARGUMENT, "spl_gemm_q4_static: more output columns than the static scratch has tickets for");
+    unsigned char *base = nullptr;
+    const spl_status found = static_base(e, &base);
+    if (found != SPL_OK) return found;
     __nv_bfloat16 *operand = reinterpret_cast<__nv_bfloat16 *>(base);
     float *sums = reinterpret_cast<float *>(base + SPL_STATIC_OPERAND_BYTES);
-    int *flag = reinterpret_cast<int *>(base + SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES);
-    float *partials = reinterpret_cast<float *>(base + SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES + SPL_STATIC_FLAG_BYTES);
+    int *control = reinterpret_cast<int *>(base + SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES);
+    float *slots = reinterpret_cast<float *>(base + SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES + SPL_STATIC_CONTROL_BYTES);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
     const int rn = operand_rn(rows);
-    // The array keeps what the last call left. Only the error word has to start at zero; the
+    // The array keeps what the last call left. The error word and the tickets have to start at zero; the
     // operand and sums of the rows in use are rewritten here, the block's other rows feed outputs
-    // that are never stored, and every partial sum the reduction reads is written by this call.
-    SPL_CUDA(cudaMemsetAsync(flag, 0, SPL_STATIC_FLAG_BYTES, stream));
+    // that are never stored, and every slot the output stage reads is written by this call.
+    SPL_CUDA(cudaMemsetAsync(control, 0, SPL_STATIC_CONTROL_BYTES, stream));
     spl_operand_kernel<<<rows, 256, 0, stream>>>(device_activations, SplOperand{operand, sums, rn, 1}, w->k);
-    launch_gemm_rows(stream, *w, GemmOperand{operand, sums, rn, 1}, device_out, device_residual, rows, partials, SPL_STATIC_PARTIAL_BYTES / 4, flag, nullptr);
+    const GemmScratch scratch{slots, SPL_STATIC_SLOT_BYTES / 4, control + 64, SPL_STATIC_TILES, control, std::min(e->sms, SPL_STATIC_BLOCKS)};
+    if (!launch_gemm_rows(stream, *w, GemmOperand{operand, sums, rn, 1}, device_out, device_residual, rows, scratch, GemmExtras(), nullptr))
+        return e->fail(SPL_ERR_INVALID_ARGUMENT, "spl_gemm_q4_static: the tensor does not fit the static scratch");
     return check_launch(e, "spl_gemm_q4_static");
+}
+
+// Whether a block of the last spl_gemm_q4_static calls on this engine's device gave up a wait (its output is then
+// incomplete). Call it after the stream those calls were queued on has been synchronised; it allocates nothing.
+extern "C" spl_status spl_gemm_q4_static_status(spl_engine *e) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    unsigned char *base = nullptr;
+    const spl_status found = static_base(e, &base);
+    if (found != SPL_OK) return found;
+    int flag = 0;
+    SPL_CUDA(cudaMemcpy(&flag, base + SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES, sizeof flag, cudaMemcpyDeviceToHost));
+    if (flag) return e->fail(SPL_ERR_TIMEOUT, "spl_gemm_q4_static: a GEMM block gave up waiting (warp " + std::to_string(flag - 1) + "); the output is incomplete");
+    return SPL_OK;
 }
 
 extern "C" {
@@ -1280,61 +1366,46 @@ spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t
     if (!packed || !scales || !biases || !activations || !out || n <= 0 || k <= 0 || k % 256 || rows <= 0) return SPL_ERR_INVALID_ARGUMENT;   // inner dimensions are multiples of 256 in every geometry this library accepts
     int count = 0;
     if (cudaGetDeviceCount(&count) != cudaSuccess || device < 0 || device >= count) return SPL_ERR_UNSUPPORTED_DEVICE;
-    spl_engine local;                     // only stream, partial scratch and error text are used
+    spl_engine local;                     // only stream, scratch and error text are used
     spl_engine *e = &local;
     e->device = device;
     SPL_CUDA(cudaSetDevice(device));
+    if (!configure_device(device, &e->sms)) return SPL_ERR_UNSUPPORTED_DEVICE;
     SPL_CUDA(cudaStreamCreate(&e->stream));
     SplQ4Dev w;
     spl_status s = alloc_q4(e, w, n, k);
     const int ld = w.ld;
     const int rn = operand_rn(rows), blocks = (rows + rn - 1) / rn;
     float *d_act32 = nullptr, *d_out = nullptr, *d_sums = nullptr; __nv_bfloat16 *d_act = nullptr; int *d_flag = nullptr;
-    e->partial_floats = size_t(16) * blocks * rn * ld;
+    e->slot_floats = spl_tc_slot_floats(e->sms, blocks, rn); e->ticket_count = size_t(blocks) * w.tiles;
     if (s == SPL_OK) s = device_alloc(e, &d_act32, size_t(rows) * k);
     if (s == SPL_OK) s = device_alloc(e, &d_act, size_t(blocks) * rn * k);
     if (s == SPL_OK) s = device_alloc(e, &d_sums, spl_operand_sums_floats(size_t(blocks) * rn, k));
     if (s == SPL_OK) s = device_alloc(e, &d_out, size_t(rows) * ld);
     if (s == SPL_OK) s = device_alloc(e, &d_flag, 64);
-    if (s == SPL_OK) s = device_alloc(e, &e->partials, e->partial_floats);
+    if (s == SPL_OK) s = device_alloc(e, &e->slots, e->slot_floats);
+    if (s == SPL_OK) s = device_alloc(e, &e->tickets, e->ticket_count);
     if (s == SPL_OK) s = upload_q4_into(e, w, 0, n, k, packed, scales, biases, false);
     if (s == SPL_OK) {
         cudaMemsetAsync(d_act, 0, size_t(blocks) * rn * k * 2, e->stream);
         cudaMemsetAsync(d_sums, 0, spl_operand_sums_floats(size_t(blocks) * rn, k) * 4, e->stream);
         cudaMemsetAsync(d_flag, 0, 64 * sizeof(int), e->stream);
-        if (getenv("SPL_TC_TRACE")) { const int magic[2] = {0x7ACE, int(strtol(getenv("SPL_TC_TRACE"), nullptr, 0))}; cudaMemcpyAsync(d_flag + 1, magic, sizeof magic, cudaMemcpyHostToDevice, e->stream); cudaStreamSynchronize(e->stream); }
+        cudaMemsetAsync(e->tickets, 0, e->ticket_count * sizeof(int), e->stream);
         cudaMemcpyAsync(d_act32, activations, size_t(rows) * k * 4, cudaMemcpyHostToDevice, e->stream);
         spl_operand_kernel<<<rows, 256, 0, e->stream>>>(d_act32, SplOperand{d_act, d_sums, rn, blocks}, k);
         if (residual) cudaMemcpy2DAsync(d_out, size_t(ld) * 4, residual, size_t(n) * 4, size_t(n) * 4, rows, cudaMemcpyHostToDevice, e->stream);
-        cudaEvent_t ev0, ev1; cudaEventCreate(&ev0); cudaEventCreate(&ev1);     // destroyed with the context; a handful per process
-        if (getenv("SPL_TC_TRACE"))      // warm the kernel so the timed launch below is a steady-state one
-            for (int warm = 0; warm < 3; ++warm)
-                launch_gemm_rows(e->stream, w, GemmOperand{d_act, d_sums, rn, blocks}, d_out, nullptr, rows, e->partials, e->partial_floats, d_flag, nullptr);
-        if (residual) cudaMemcpy2DAsync(d_out, size_t(ld) * 4, residual, size_t(n) * 4, size_t(n) * 4, rows, cudaMemcpyHostToDevice, e->stream);
-        cudaEventRecord(ev0, e->stream);
-        launch_gemm_rows(e->stream, w, GemmOperand{d_act, d_sums, rn, blocks}, d_out, residual ? d_out : nullptr, rows, e->partials, e->partial_floats, d_flag, nullptr);
-        cudaEventRecord(ev1, e->stream);
-        s = check_launch(e, "gemm");
+        const GemmScratch scratch{e->slots, e->slot_floats, e->tickets, e->ticket_count, d_flag, e->sms};
+        if (!launch_gemm_rows(e->stream, w, GemmOperand{d_act, d_sums, rn, blocks}, d_out, residual ? d_out : nullptr, rows, scratch, GemmExtras(), nullptr)) s = SPL_ERR_INVALID_ARGUMENT;
+        if (s == SPL_OK) s = check_launch(e, "gemm");
         if (cudaStreamSynchronize(e->stream) != cudaSuccess) s = SPL_ERR_DEVICE;
         int flag = 0;
         if (s == SPL_OK) { cudaMemcpy(&flag, d_flag, sizeof flag, cudaMemcpyDeviceToHost); if (flag) s = SPL_ERR_TIMEOUT; }
-        if (getenv("SPL_TC_TRACE")) {
-            float ms = 0; cudaEventElapsedTime(&ms, ev0, ev1);
-            fprintf(stderr, "gemm n %d k %d rows %d: %.1f us, %.0f GB/s\n", n, k, rows, ms * 1e3, double(w.bytes()) * blocks / (ms * 1e-3) / 1e9);
-            int t[64]; cudaMemcpy(t, d_flag, sizeof t, cudaMemcpyDeviceToHost);
-            if (t[2] & 0x100)
-                fprintf(stderr, "tc trace, cycles per group: copy [wait codes %d, wait act %d, issue %d] mma [wait act %d, wait A %d, issue %d] "
-                                "dequant(1 of 2 sets) [wait stage %d, convert %d, wait slot %d, store %d] epilogue [wait %d, work %d, final wait %d] groups %d\n",
-                        t[8], t[9], t[10], t[11], t[12], t[13], t[14], t[15], t[16], t[17], t[18], t[19], t[20], t[21]);
-            fprintf(stderr, "tc code stages: age at pick-up %d cycles (all %d units), %d when the set had to wait (%d units)\n", t[27], t[30], t[28], t[29]);
-            fprintf(stderr, "tc timeline of block 0, cycles from entry: set-up done %d, first stage landed %d, last instruction issued %d, accumulators complete %d (read %d, residual read %d), output written %d\n", t[22], t[23], t[24], t[25], t[31], t[32], t[26]);
-        }
         if (s == SPL_OK) cudaMemcpy2D(out, size_t(n) * 4, d_out, size_t(ld) * 4, size_t(n) * 4, rows, cudaMemcpyDeviceToHost);
     }
     cudaFree(d_sums); cudaFree(d_flag);
-    cudaFree(w.codes); cudaFree(w.sb); cudaFree(d_act32); cudaFree(d_act); cudaFree(d_out); cudaFree(e->partials);
+    cudaFree(w.codes); cudaFree(w.sb); cudaFree(d_act32); cudaFree(d_act); cudaFree(d_out); cudaFree(e->slots); cudaFree(e->tickets);
     cudaStreamDestroy(e->stream);
-    e->stream = nullptr; e->partials = nullptr;
+    e->stream = nullptr; e->slots = nullptr; e->tickets = nullptr;
     return s;
 }
 
@@ -1350,6 +1421,7 @@ spl_status spl_op_gemm_gguf(int32_t device, int32_t format, const uint8_t *block
     spl_engine *e = &local;
     e->device = device;
     SPL_CUDA(cudaSetDevice(device));
+    if (!configure_device(device, &e->sms)) return SPL_ERR_UNSUPPORTED_DEVICE;
     SPL_CUDA(cudaStreamCreate(&e->stream));
     SplGgufDev w;
     w.n = n; w.ld = round16(n); w.tiles = (n + 127) / 128; w.k = k; w.format = format;
@@ -1376,23 +1448,11 @@ spl_status spl_op_gemm_gguf(int32_t device, int32_t format, const uint8_t *block
         cudaMemcpyAsync(d_act32, activations, size_t(rows) * k * 4, cudaMemcpyHostToDevice, e->stream);
         spl_operand_kernel<<<rows, 256, 0, e->stream>>>(d_act32, SplOperand{d_act, d_sums, rn, row_blocks}, k);
         if (residual) cudaMemcpy2DAsync(d_out, size_t(ld) * 4, residual, size_t(n) * 4, size_t(n) * 4, rows, cudaMemcpyHostToDevice, e->stream);
-        cudaEvent_t ev0, ev1; cudaEventCreate(&ev0); cudaEventCreate(&ev1);
-        const bool timed = getenv("SPL_TC_TRACE") != nullptr;
-        if (timed)
-            for (int warm = 0; warm < 3; ++warm)
-                launch_gemm_gguf(e->stream, w, GemmOperand{d_act, d_sums, rn, row_blocks}, d_out, nullptr, rows, e->partials, e->partial_floats, d_flag);
-        if (timed && residual) cudaMemcpy2DAsync(d_out, size_t(ld) * 4, residual, size_t(n) * 4, size_t(n) * 4, rows, cudaMemcpyHostToDevice, e->stream);
-        cudaEventRecord(ev0, e->stream);
         launch_gemm_gguf(e->stream, w, GemmOperand{d_act, d_sums, rn, row_blocks}, d_out, residual ? d_out : nullptr, rows, e->partials, e->partial_floats, d_flag);
-        cudaEventRecord(ev1, e->stream);
         s = check_launch(e, "gguf gemm");
         if (cudaStreamSynchronize(e->stream) != cudaSuccess) s = SPL_ERR_DEVICE;
         int flag = 0;
         if (s == SPL_OK) { cudaMemcpy(&flag, d_flag, sizeof flag, cudaMemcpyDeviceToHost); if (flag) s = SPL_ERR_TIMEOUT; }
-        if (timed) {
-            float ms = 0; cudaEventElapsedTime(&ms, ev0, ev1);
-            fprintf(stderr, "gguf gemm type %d n %d k %d rows %d: %.1f us, %.0f GB/s\n", format, n, k, rows, ms * 1e3, double(w.bytes()) * row_blocks / (ms * 1e-3) / 1e9);
-        }
         if (s == SPL_OK) cudaMemcpy2D(out, size_t(n) * 4, d_out, size_t(ld) * 4, size_t(n) * 4, rows, cudaMemcpyDeviceToHost);
     }
     cudaFree(d_sums); cudaFree(d_flag); cudaFree(d_native);

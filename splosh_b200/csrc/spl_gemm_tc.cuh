@@ -42,7 +42,7 @@ struct SplQ4Dev {
     int ld = 0;           // columns rounded up to 16: the width of an output row
     int tiles = 0;        // 128-column tiles
     int k = 0;            // contraction length, a multiple of 64
-    int interleave = 0;   // > 0 for a fused gate|up tensor of 2 x interleave columns: tile t holds gate columns [64 t, 64 t + 64) then the up columns of the same range
+    int interleave = 0;   // > 0 for a fused gate|up tensor of 2 x interleave columns: tile t holds elements [64 t, 64 t + 64), in runs of 32 columns = sixteen gate columns then the sixteen up columns of the same elements
     uint32_t *codes = nullptr;      // [tiles][k/64][2][128][4] words
     uint32_t *sb = nullptr;         // [tiles][k/64][128] words
     size_t bytes() const { return size_t(ld) * (k / 64) * 36; }   // algorithmic: 32 B of codes + 4 B of scale and bias per (column, group)
@@ -104,7 +104,7 @@ __global__ void spl_repack_q4_kernel(const uint32_t *__restrict__ packed, const 
             dst |= ((src >> (8 * j + 4)) & 0xFu) << (4 * j + 16);
         }
         int n = n0 + row;
-        if (interleave > 0) { const int c = n < interleave ? n : n - interleave; n = (c >> 6) * 128 + (n < interleave ? 0 : 64) + (c & 63); }
+        if (interleave > 0) { const int c = n < interleave ? n : n - interleave; n = (c >> 6) * 128 + ((c & 63) >> 4) * 32 + (n < interleave ? 0 : 16) + (c & 15); }
         const int tile = n >> 7, col = n & 127, g = w >> 3, h = (w >> 2) & 1, j = w & 3;
         codes[(((size_t(tile) * groups + g) * 2 + h) * 128 + col) * 4 + j] = dst;
         if ((w & 7) == 0) {
@@ -155,10 +155,20 @@ __global__ void spl_synth_q4_kernel(uint64_t seed, float factor, int rows, int k
 }
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
-#define SPL_WAIT_LIMIT (1u << 22)     // polls before a wait gives up
-#define SPL_WAIT_HINT_NS 4000u        // suspend-time hint of one poll
+// Every wait inside a kernel is bounded in time: a wait that outlasts the budget returns false, the kernel sets its error
+// word and unwinds. The budget is a device variable so that a test can shorten it (spl_debug_wait_budget).
+#define SPL_WAIT_HINT_NS 2000u        // suspend-time hint of one poll
+__device__ unsigned long long spl_wait_budget_ns = 250ull * 1000 * 1000;
+// Test switch (spl_debug_drop_weight_stage): the q4 GEMM's weight-copy role leaves out this stage of every block's piece, so
+// the roles that wait for it run out of time. -1: off.
+__device__ int spl_drop_weight_stage = -1;
 
 __device__ __forceinline__ uint32_t spl_smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ unsigned long long spl_global_timer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;\n" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ void spl_mbar_init(uint64_t *bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(spl_smem_addr(bar)), "r"(count));
 }
@@ -168,18 +178,27 @@ __device__ __forceinline__ void spl_mbar_arrive(uint64_t *bar) {
 __device__ __forceinline__ void spl_mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(spl_smem_addr(bar)), "r"(bytes) : "memory");
 }
-// Bounded wait on a phase parity. Returns false when the limit ran out.
-__device__ __forceinline__ bool spl_mbar_wait(uint64_t *bar, uint32_t parity) {
+__device__ __forceinline__ bool spl_mbar_try(uint32_t addr, uint32_t parity) {
+    uint32_t done;
+    // The hint lets the hardware keep the thread suspended (off the issue slots its neighbours need) for up to that many
+    // nanoseconds per poll; completion of the phase wakes it at once.
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
+                 : "=r"(done) : "r"(addr), "r"(parity), "r"(SPL_WAIT_HINT_NS) : "memory");
+    return done != 0;
+}
+// Bounded wait on a phase parity. Returns false when the time budget ran out, or when `abort` (a word of the block's
+// shared memory that any role sets when its own wait ran out) is set: one lost arrival then unwinds the whole block
+// within one budget instead of one budget per waiting role.
+__device__ __forceinline__ bool spl_mbar_wait(uint64_t *bar, uint32_t parity, const volatile int *abort = nullptr) {
     const uint32_t addr = spl_smem_addr(bar);
-    for (uint32_t spin = 0; spin < SPL_WAIT_LIMIT; ++spin) {
-        uint32_t done;
-        // The hint lets the hardware keep the thread suspended (off the issue slots its neighbours need) for up to that many
-        // nanoseconds per poll; completion of the phase wakes it at once.
-        asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n selp.u32 %0, 1, 0, p;\n}\n"
-                     : "=r"(done) : "r"(addr), "r"(parity), "r"(SPL_WAIT_HINT_NS) : "memory");
-        if (done) return true;
+    if (spl_mbar_try(addr, parity)) return true;
+    const unsigned long long t0 = spl_global_timer(), budget = spl_wait_budget_ns;
+    for (;;) {
+        for (int spin = 0; spin < 32; ++spin)
+            if (spl_mbar_try(addr, parity)) return true;
+        if (abort && *abort) return false;
+        if (spl_global_timer() - t0 > budget) return false;
     }
-    return false;
 }
 __device__ __forceinline__ void spl_bulk_g2s(void *smem, const void *gmem, uint32_t bytes, uint64_t *bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
@@ -211,9 +230,9 @@ __device__ __forceinline__ bool spl_elect_one() {
     return pred != 0;
 }
 // A bounded wait by every lane of a converged warp, with one answer for the warp (a lane that gave up alone would leave
-// the warp's later elect.sync waiting for it).
-__device__ __forceinline__ bool spl_mbar_wait_warp(uint64_t *bar, uint32_t parity) {
-    return __all_sync(0xffffffffu, spl_mbar_wait(bar, parity));
+// the warp's later warp-wide instructions waiting for it).
+__device__ __forceinline__ bool spl_mbar_wait_warp(uint64_t *bar, uint32_t parity, const volatile int *abort = nullptr) {
+    return __all_sync(0xffffffffu, spl_mbar_wait(bar, parity, abort));
 }
 // K-major, 128-byte swizzle, rows of 128 bytes, eight-row groups 1,024 bytes apart.
 __device__ __forceinline__ uint64_t spl_tc_desc_sw128(uint32_t smem_byte_addr) {
@@ -230,7 +249,6 @@ __host__ __device__ constexpr uint32_t spl_tc_idesc(int n) {
     return (1u << 4) | (0u << 7) | (0u << 10) | (uint32_t(n >> 3) << 17) | (uint32_t(128 >> 4) << 24);
 }
 
-#define SPL_TC_LD(N, regs, addr) spl_tc_ld##N(regs, addr)
 __device__ __forceinline__ void spl_tc_ld16(uint32_t (&r)[16], uint32_t taddr) {
     // The load and its wait are one statement: the registers are defined only after the wait, and a separate
     // wait statement would not stop the compiler from scheduling their readers before it.
@@ -239,28 +257,22 @@ __device__ __forceinline__ void spl_tc_ld16(uint32_t (&r)[16], uint32_t taddr) {
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]),
                    "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]) : "r"(taddr));
 }
-__device__ __forceinline__ void spl_tc_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void spl_tc_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
 __device__ __forceinline__ void spl_tc_st16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};\n"
                  ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
                    "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
-
-// Eight 4-bit codes of a word -> four bf16x2 registers of exact values: 0x4300 | c is 128 + c.
-__device__ __forceinline__ void spl_codes4(uint32_t w, uint32_t *a) {
-    const __nv_bfloat162 bias128 = __floats2bfloat162_rn(128.0f, 128.0f);
-    uint32_t q0 = (w & 0x000F000Fu) | 0x43004300u;
-    uint32_t q1 = ((w >> 4) & 0x000F000Fu) | 0x43004300u;
-    uint32_t q2 = ((w >> 8) & 0x000F000Fu) | 0x43004300u;
-    uint32_t q3 = ((w >> 12) & 0x000F000Fu) | 0x43004300u;
-    __nv_bfloat162 c0 = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&q0), bias128);
-    __nv_bfloat162 c1 = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&q1), bias128);
-    __nv_bfloat162 c2 = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&q2), bias128);
-    __nv_bfloat162 c3 = __hsub2(*reinterpret_cast<__nv_bfloat162 *>(&q3), bias128);
-    a[0] = *reinterpret_cast<uint32_t *>(&c0); a[1] = *reinterpret_cast<uint32_t *>(&c1);
-    a[2] = *reinterpret_cast<uint32_t *>(&c2); a[3] = *reinterpret_cast<uint32_t *>(&c3);
+__device__ __forceinline__ void spl_tc_st4(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
 }
+// The first wait of a launch that ran out leaves its place in the error words: [1] which wait (the codes are listed where
+// the engine turns them into text), [2] the stage or unit it was at, [3] the block.
+__device__ __forceinline__ void spl_note_wait(int *error_flag, int code, int where) {
+    if (atomicCAS(error_flag + 1, 0, code) == 0) { error_flag[2] = where; error_flag[3] = int(blockIdx.x) | (int(blockIdx.z) << 16); }
+}
+// A barrier among `count` threads of the block (a multiple of 32), id 1..15.
+__device__ __forceinline__ void spl_named_barrier(int id, int count) { asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(count) : "memory"); }
 
 // ---- the kernel -------------------------------------------------------------------------------
 // How the contract is kept with everything on the tensor cores. With c the 4-bit code,
@@ -274,32 +286,56 @@ __device__ __forceinline__ void spl_codes4(uint32_t w, uint32_t *a) {
 // group's mean sum(a) / 64 split in two fp16 numbers by the operand's producer (SplOperand::put_sum). The four
 // products add up to (bias + 8 scale) * sum(a) to within 2^-22 of the term, beside the fp32 accumulator's own 2^-24.
 // The result is the reference's sum of per-group terms up to the order of fp32 additions.
+//
+// How the work is cut. A launch has one block per SM (or fewer for a small tensor). The tensor's (tile, stage)
+// pairs, a stage = four groups, in tile-major order are one line of W stages; block c of P takes the stages
+// [c W / P, (c + 1) W / P): the same number for every block whatever the tile count, and one contiguous piece of the
+// weight array, which the block streams without a bubble at a tile's end. A piece covers the end of one tile, some
+// whole tiles and the beginning of another: each is a SEGMENT with an output stage of its own. A tile that one block
+// covers alone is written out directly. A tile shared by several blocks is finished by the block that arrives last:
+// every contributor stores its partial sums in a slot of its own, then takes a ticket (one atomic add per tile);
+// the holder of the last ticket adds the slots in the order of the contraction, whoever arrived when, so the sum's order
+// is fixed, and writes the output. Nobody waits for anybody.
 #define SPL_TC_SUPER 4           // groups per shared-memory stage: one bulk copy brings 256 of the contraction
 #define SPL_TC_AUNITS 5          // A operand slots in tensor memory, a unit (two groups, 64 columns) each, with 8 columns each for the second term
 #define SPL_TC_SETS 4            // dequant sets of four warps (a warp writes the tensor-memory lanes of its index mod 4); they take the units in turn
-#define SPL_TC_THREADS (SPL_TC_SETS * 128 + 128)       // the sets; then a warp that copies weights, a tensor-core issue warp, a warp that copies activations, the other issue warp
+#define SPL_TC_DEQUANT (SPL_TC_SETS * 128)
+#define SPL_TC_THREADS (SPL_TC_DEQUANT + 128)       // the sets; then a warp that copies weights, a tensor-core issue warp, a warp that copies activations, the other issue warp
 
 // Stages of activations: held until the tensor core has finished with them. Stages of codes with their scale/bias
 // words (18 KiB each): handed back as soon as they are in registers.
 __host__ __device__ constexpr int spl_tc_bstages(int rn) { return rn >= 64 ? 4 : 6; }
 __host__ __device__ constexpr int spl_tc_cstages(int rn) { return rn >= 64 ? 4 : 6; }
 __host__ __device__ constexpr size_t spl_tc_bstage_bytes(int rn) { return size_t(SPL_TC_SUPER) * size_t(rn) * 128; }
+#define SPL_TC_CONTROL_BYTES 4096       // barriers, row factors, the output stage's exchange cells
 __host__ __device__ constexpr size_t spl_tc_smem_bytes(int rn) {
     return 1024 /* alignment slack */ + size_t(spl_tc_cstages(rn)) * SPL_TC_SUPER * (4096 + 512) + size_t(spl_tc_bstages(rn)) * spl_tc_bstage_bytes(rn)
-           + size_t(2) * rn * 128 /* tiles of split means */ + 1024 /* barriers */;
+           + size_t(2) * rn * 128 /* tiles of split means */ + SPL_TC_CONTROL_BYTES;
 }
-__device__ __forceinline__ void spl_tc_st4(uint32_t taddr, uint32_t r0, uint32_t r1, uint32_t r2, uint32_t r3) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x4.b32 [%0], {%1,%2,%3,%4};\n" ::"r"(taddr), "r"(r0), "r"(r1), "r"(r2), "r"(r3) : "memory");
-}
+// Floats of the slot array a launch of `blocks` x `row_blocks` blocks may write: two slots of rn x 128 a block.
+__host__ __device__ constexpr size_t spl_tc_slot_floats(int blocks, int row_blocks, int rn) { return size_t(blocks) * row_blocks * 2 * rn * 128; }
 
-// Grid (tiles, splits, row blocks in use). Block (t, s, rb) computes columns [128 t, 128 t + 128) of rows
-// [RN rb, RN rb + RN) over groups [s * gps, (s + 1) * gps) (gps a multiple of four) and writes them to `out`, or,
-// when the contraction is split, to partials[s][row][column] for spl_gemm_reduce_kernel.
+struct SplGemmArgs {
+    const uint32_t *codes, *sb;            // the weight (SplQ4Dev)
+    const __nv_bfloat16 *act;              // the operand (SplOperand layout) and its tiles of split means
+    const float *act_sums;
+    float *out;                            // [rows][out_ld]
+    const float *residual;                 // null, or [rows][out_ld] added to the output (may be `out`)
+    float *slots;                          // partial sums of shared tiles: [row block][block][2][RN][128]
+    int *tickets;                          // [row block][tile], zero between launches
+    int *error_flag;
+    int out_ld, rows, op_blocks, tiles, stages_per_tile, interleave, fuse;
+    SplOperand act_out;                    // fuse: the SiLU-gated activation, written as the next GEMM's operand
+    // The operand came from a deferred norm: out = sum * rsqrt(mean of the row's squares + eps). [row][in_groups] squares.
+    const float *in_squares; int in_groups; float in_dim, eps;
+    // The output feeds a deferred norm: also write bf16(out * emit_weight) as an operand, with its sums and the squares of out.
+    const uint16_t *emit_weight; SplOperand emit_out; float *emit_squares;
+};
+
+// Grid (blocks, 1, row blocks in use). See "How the work is cut" above.
 template <int RN>
 __global__ void __launch_bounds__(SPL_TC_THREADS, 1)
-spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__restrict__ sb, const __nv_bfloat16 *__restrict__ act,
-                      const float *__restrict__ act_sums, float *out, int out_ld, const float *residual, float *partials,
-                      int rows, int op_blocks, int groups, int groups_per_split, int *error_flag, int interleave, SplOperand act_out, int fuse) {
+spl_gemm_q4_tc_kernel(const SplGemmArgs a) {
     constexpr int BST = spl_tc_bstages(RN), CST = spl_tc_cstages(RN), AUN = SPL_TC_AUNITS;
     constexpr int BTILE = SPL_TC_SUPER * RN * 128, WSTAGE = SPL_TC_SUPER * 4096, QSTAGE = SPL_TC_SUPER * 128, TTILE = RN * 128;
     extern __shared__ unsigned char spl_tc_smem_raw[];
@@ -311,58 +347,53 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     uint32_t *q_ring = reinterpret_cast<uint32_t *>(w_ring + size_t(CST) * WSTAGE);     // [CST][SUPER][128] scale | bias << 16
     uint64_t *bars = reinterpret_cast<uint64_t *>(q_ring + CST * QSTAGE);
     uint64_t *full_c = bars, *empty_c = full_c + CST, *full_b = empty_c + CST, *done = full_b + BST;      // done[un % 16]: the instructions that read unit un have completed
-    uint64_t *full_a = done + 16, *full_t = full_a + AUN, *empty_t = full_t + 2, *finished = empty_t + 2;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(finished + 1);
-#ifdef SPL_TRACE
-    volatile long long *trace_clock = reinterpret_cast<volatile long long *>(bars + 64);      // issue times of the code stages
-#endif
+    uint64_t *full_a = done + 16, *full_t = full_a + AUN, *empty_t = full_t + 2, *finished = empty_t + 2, *acc_free = finished + 1;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_free + 1);
+    int *abort_word = reinterpret_cast<int *>(tmem_slot + 1), *last_word = abort_word + 1;
+    float *row_factor = reinterpret_cast<float *>(bars) + 256;                          // [64] at byte 1,024 of the control area
+    float *cells = row_factor + 64;                                                     // [SETS][4 warps][16 rows][2] the output stage's exchange
 
-#ifdef SPL_TRACE
-    const long long t_entry = clock64();
-#endif
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int W_COPY = SPL_TC_SETS * 4, W_MMA0 = W_COPY + 1, W_COPYB = W_COPY + 2, W_MMA1 = W_COPY + 3;
-    const int tile = blockIdx.x, split = blockIdx.y, rb = blockIdx.z, row_blocks = op_blocks;   // the operand's row blocks (>= gridDim.z)
-    const int rows_padded = op_blocks * RN;
-    const int g_first = split * groups_per_split;
-    const int g_count = min(groups_per_split, groups - g_first);
-    const int supers = (g_count + SPL_TC_SUPER - 1) / SPL_TC_SUPER;
-    const int units = (g_count + 1) / 2;            // a unit = two groups = one hand-over from a dequant set
-    // Every block of a GEMM reads the same activation lines. Blocks therefore walk the contraction from
-    // different starting points (the order of a sum of groups does not matter beyond fp32 rounding, and it
-    // is a fixed function of the tile), so that at any moment they ask L2 for different lines.
-    const int rot = (g_count % SPL_TC_SUPER == 0 && supers > 1) ? int((uint32_t(tile) * 2654435761u >> 12) % uint32_t(supers)) : 0;
+    const int rb = blockIdx.z, row_blocks = a.op_blocks, S = a.stages_per_tile, P = gridDim.x, c = blockIdx.x;
+    const long long W = (long long)a.tiles * S;
+    const int w0 = int(W * c / P), w1 = int(W * (c + 1) / P), stages = w1 - w0;          // this block's piece of the line
+    const int tile0 = w0 / S, segments = stages > 0 ? (w1 - 1) / S - tile0 + 1 : 0;
+    const volatile int *abort = abort_word;
 
     // The thread that copies weights sets up its own barriers and asks for the first stages at once: they are nobody's
     // output (no wait for the predecessor in the stream), and they travel while the block is still being set up.
-    const int ahead = min(CST, supers);
+    const int ahead = min(CST, stages);
+    int issued_c = 0, issued_b = 0, issued_t = 0;       // stages and tiles of split means this thread has asked for (copy roles)
+    const int drop = spl_drop_weight_stage;
+    const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(a.codes) + size_t(w0) * WSTAGE;
+    const uint32_t *qsrc = a.sb + size_t(w0) * QSTAGE;
     if (warp == W_COPY && lane == 0) {
-        const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(codes) + (size_t(tile) * groups + g_first) * 4096;
-        const uint32_t *qsrc = sb + (size_t(tile) * groups + g_first) * 128;
         for (int i = 0; i < CST; ++i) spl_mbar_init(&full_c[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-        for (int j0 = 0; j0 < ahead; ++j0) {
-            const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
-            const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);
-            spl_mbar_expect_tx(&full_c[j0], uint32_t(n) * (4096 + 512));
-            spl_bulk_g2s(w_ring + size_t(j0) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[j0]);
-            spl_bulk_g2s(q_ring + j0 * QSTAGE, qsrc + size_t(j) * QSTAGE, uint32_t(n) * 512, &full_c[j0]);
+        issued_c = ahead;
+        for (int i = 0; i < ahead; ++i) {
+            if (i == drop) continue;
+            spl_mbar_expect_tx(&full_c[i], WSTAGE + QSTAGE * 4);
+            spl_bulk_g2s(w_ring + size_t(i) * WSTAGE, wsrc + size_t(i) * WSTAGE, WSTAGE, &full_c[i]);
+            spl_bulk_g2s(q_ring + i * QSTAGE, qsrc + size_t(i) * QSTAGE, QSTAGE * 4, &full_c[i]);
         }
     }
     if (warp == 0) {
         // One barrier a lane: the arrival count of barrier i (in the order of the pointers above, after full_c).
-        const int i = lane + CST;
-        const int total = int(finished + 1 - bars);
-        for (int b = i; b < total; b += 32) {
+        const int total = int(acc_free + 1 - bars);
+        for (int b = lane + CST; b < total; b += 32) {
             uint64_t *bar = bars + b;
             const uint32_t count = bar < full_b ? 8u              // empty_c: the two sets (four warps each) that take the stage's units
                                  : bar < done ? 1u                // full_b: the copy's bytes
                                  : bar < full_a ? 1u              // done: the commit of the issuing warp that took the unit
                                  : bar < full_t ? 4u              // full_a: the four warps of a set
                                  : bar < empty_t ? 1u             // full_t
-                                 : 2u;                            // empty_t and finished: the two issuing warps
+                                 : bar < acc_free ? 2u            // empty_t and finished: the two issuing warps
+                                 : 16u;                           // acc_free: every dequant warp has read its share of the accumulators
             spl_mbar_init(bar, count);
         }
+        if (lane == 0) { *abort_word = 0; *last_word = 0; }
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == W_MMA0) {
@@ -373,88 +404,56 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
     __syncthreads();
     spl_tc_fence_after();
     const uint32_t tmem = *tmem_slot;                 // lane 0, first allocated column
-#ifdef SPL_TRACE
-    if (threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && error_flag[1] == 0x7ACE) error_flag[22] = int(clock64() - t_entry);   // set-up
-#endif
     // Two accumulators, one per issuing warp (instructions of different warps are not ordered against each other);
     // the A ring, 64 columns a unit; the second-term operand, 8 columns a unit.
     const uint32_t tmem_d = tmem, tmem_a = tmem + 128, tmem_aq = tmem + 128 + AUN * 64;
     bool ok = true;
-    // Debug trace (builds with -DSPL_TRACE only): cycles per group that one thread of each role of block (0, 0, 0) spends
-    // in its waits and its work.
-#ifdef SPL_TRACE
-    const bool trace = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && error_flag[1] == 0x7ACE && (error_flag[2] & 0x100);
-    long long t0 = 0, t1 = 0, t2 = 0, t3 = 0, t4 = 0, t5 = 0, t_mark = 0, age_all = 0, age_waited = 0; int age_n = 0; int age_wn = 0;
-#define SPL_T0() do { if (trace) t_mark = clock64(); } while (0)
-#define SPL_T1(acc) do { if (trace) { const long long now__ = clock64(); acc += now__ - t_mark; t_mark = now__; } } while (0)
-#define SPL_TOUT(statement) do { statement; } while (0)
-#else
-#define SPL_T0() do { } while (0)
-#define SPL_T1(acc) do { } while (0)
-#define SPL_TOUT(statement) do { } while (0)
-#endif
 
-    if (!(warp == W_COPY && lane == 0)) spl_grid_begin();     // the thread that copies weights first asks for some (below)
+    spl_grid_begin();
     if (warp == W_COPY) {
-        // ---- copies of weights: codes and their scale/bias words, one ring.
+        // ---- copies of weights: codes and their scale/bias words, one ring, one contiguous piece of the arrays.
         if (lane == 0) {
-            const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(codes) + (size_t(tile) * groups + g_first) * 4096;
-            const uint32_t *qsrc = sb + (size_t(tile) * groups + g_first) * 128;
-            spl_grid_begin();
-            for (int j0 = ahead; j0 < supers && ok; ++j0) {
-                const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;      // the stage's source; j0 is its place in the pipeline
-                const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);         // with a rotation every stage is full
-                const int sc = j0 % CST;
-                SPL_T0();
-                ok = spl_mbar_wait(&empty_c[sc], ((j0 / CST) & 1) ^ 1);
-                SPL_T1(t0);
-                if (!ok) break;
-                SPL_TOUT(if (trace) trace_clock[sc] = clock64());
-                spl_mbar_expect_tx(&full_c[sc], uint32_t(n) * (4096 + 512));
-                spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[sc]);
-                spl_bulk_g2s(q_ring + sc * QSTAGE, qsrc + size_t(j) * QSTAGE, uint32_t(n) * 512, &full_c[sc]);
-                SPL_T1(t2);
+            for (int i = ahead; i < stages; ++i) {
+                const int sc = i % CST;
+                if (!spl_mbar_wait(&empty_c[sc], ((i / CST) & 1) ^ 1, abort)) { ok = false; if (!*abort) spl_note_wait(a.error_flag, 10, i); break; }
+                issued_c = i + 1;
+                if (i == drop) continue;
+                spl_mbar_expect_tx(&full_c[sc], WSTAGE + QSTAGE * 4);
+                spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, wsrc + size_t(i) * WSTAGE, WSTAGE, &full_c[sc]);
+                spl_bulk_g2s(q_ring + sc * QSTAGE, qsrc + size_t(i) * QSTAGE, QSTAGE * 4, &full_c[sc]);
             }
-            SPL_TOUT(if (trace) { error_flag[8] = int(t0 / g_count); error_flag[10] = int(t2 / g_count); });
         }
     } else if (warp == W_COPYB) {
         // ---- copies of activations and of the tiles of split means.
         if (lane == 0) {
-            const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(act) + ((size_t(g_first) * row_blocks + rb) * RN) * 128;
-            const unsigned char *tsrc = reinterpret_cast<const unsigned char *>(act_sums);
+            const unsigned char *bsrc = reinterpret_cast<const unsigned char *>(a.act) + size_t(rb) * RN * 128;
+            const unsigned char *tsrc = reinterpret_cast<const unsigned char *>(a.act_sums);
             int mean_tile = -1, mean_loads = 0;
-            for (int j0 = 0; j0 < supers && ok; ++j0) {
-                const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
-                const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);
-                const int sbq = j0 % BST;
-                // The tile of split means that holds this stage's groups (sixteen groups to a tile).
-                const int want = (g_first / SPL_TC_SUPER + j) >> 2;
+            for (int i = 0; i < stages; ++i) {
+                const int j = (w0 + i) % S, sbq = i % BST;         // the stage's place in the contraction
+                const int want = j >> 2;                           // the tile of split means that holds its groups (sixteen groups to a tile)
                 if (want != mean_tile) {
                     const int slot = mean_loads & 1;
-                    ok = spl_mbar_wait(&empty_t[slot], ((mean_loads >> 1) & 1) ^ 1);
-                    if (!ok) break;
+                    if (!spl_mbar_wait(&empty_t[slot], ((mean_loads >> 1) & 1) ^ 1, abort)) { ok = false; if (!*abort) spl_note_wait(a.error_flag, 20, i); break; }
                     spl_mbar_expect_tx(&full_t[slot], TTILE);
                     spl_bulk_g2s(t_ring + slot * TTILE, tsrc + (size_t(want) * row_blocks + rb) * TTILE, TTILE, &full_t[slot]);
-                    mean_tile = want; ++mean_loads;
+                    mean_tile = want; ++mean_loads; issued_t = mean_loads;
                 }
-                SPL_T0();
-                if (j0 >= BST) {            // the stage's last tenant: both of its units have to have completed
-                    const int u0 = 2 * (j0 - BST);
-                    ok = spl_mbar_wait(&done[u0 & 15], (u0 >> 4) & 1) && spl_mbar_wait(&done[(u0 + 1) & 15], ((u0 + 1) >> 4) & 1);
+                if (i >= BST) {            // the stage's last tenant: both of its units have to have completed
+                    const int u0 = 2 * (i - BST);
+                    if (!(spl_mbar_wait(&done[u0 & 15], (u0 >> 4) & 1, abort) && spl_mbar_wait(&done[(u0 + 1) & 15], ((u0 + 1) >> 4) & 1, abort))) { ok = false; if (!*abort) spl_note_wait(a.error_flag, 21, i); break; }
                 }
-                SPL_T1(t1);
-                if (!ok) break;
-                spl_mbar_expect_tx(&full_b[sbq], uint32_t(n) * RN * 128);
+                issued_b = i + 1;
+                spl_mbar_expect_tx(&full_b[sbq], BTILE);
                 if (row_blocks == 1) {
-                    spl_bulk_g2s(b_ring + size_t(sbq) * BTILE, bsrc + size_t(j) * BTILE, uint32_t(n) * RN * 128, &full_b[sbq]);
+                    spl_bulk_g2s(b_ring + size_t(sbq) * BTILE, bsrc + size_t(j) * BTILE, BTILE, &full_b[sbq]);
                 } else {
-                    for (int u = 0; u < n; ++u) {
+                    for (int u = 0; u < SPL_TC_SUPER; ++u) {
                         const size_t g = size_t(j) * SPL_TC_SUPER + u;
                         spl_bulk_g2s(b_ring + size_t(sbq) * BTILE + u * RN * 128, bsrc + g * row_blocks * RN * 128, RN * 128, &full_b[sbq]);
                     }
                 }
             }
-            SPL_TOUT(if (trace) { error_flag[9] = int(t1 / g_count); });
         }
     } else if (warp == W_MMA0 || warp == W_MMA1) {
         // ---- tensor-core issue: D[128 x RN] += A[128 x 64] (fp16, tensor memory) * B[RN x 64]^T (fp16, shared memory).
@@ -466,80 +465,237 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
         // (the unit's 8 values of that contraction; the other 8 columns of its operand slot are zero).
         const int m = warp == W_MMA0 ? 0 : 1;
         constexpr uint32_t idesc = spl_tc_idesc(RN);
-        int mean_tile = -1, mean_loads = 0, mean_slot = 0;
+        int mean_tile = -1, mean_loads = 0, mean_slot = 0, segment = 0;
         const uint64_t b_desc0 = spl_tc_desc_sw128(spl_smem_addr(b_ring)), t_desc0 = spl_tc_desc_sw128(spl_smem_addr(t_ring));
         const uint32_t d_mine = tmem_d + m * RN;
         int slot = m;                                      // un % AUN
         uint32_t a_parity = 0;                             // (un / AUN) & 1
-        for (int un = m; un < units && ok; un += 2) {
-            const int j0 = un >> 1, sbq = j0 % BST, n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER) - 2 * m;     // groups of this unit: 1 or 2
+        for (int i = 0; i < stages; ++i) {
+            const int un = 2 * i + m, j = (w0 + i) % S, sbq = i % BST;
+            const bool first = i == 0 || j == 0, last = i + 1 == stages || j + 1 == S;       // of its segment
             const uint64_t b_desc = b_desc0 + uint64_t((sbq * BTILE + m * 2 * RN * 128) >> 4);
             const uint32_t a_base = tmem_a + slot * 64;
-            // The stage's share of the second term: its 16 values of the contraction are a quarter of a 128-byte row of the tile.
-            const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
-            const int quarter = g_first / SPL_TC_SUPER + j, want = quarter >> 2;
-            SPL_T0();
+            const int want = j >> 2;
             if (want != mean_tile) {
                 if (mean_tile >= 0 && spl_elect_one()) spl_tc_commit(&empty_t[mean_slot]);      // every instruction of this warp that read the old tile has been issued
                 __syncwarp();
                 mean_slot = mean_loads & 1;
-                ok = spl_mbar_wait_warp(&full_t[mean_slot], (mean_loads >> 1) & 1);
-                if (!ok) break;
+                if (!spl_mbar_wait_warp(&full_t[mean_slot], (mean_loads >> 1) & 1, abort)) { ok = false; if (!*abort && lane == 0) spl_note_wait(a.error_flag, 30 + m, i); break; }
                 mean_tile = want; ++mean_loads;
             }
-            ok = spl_mbar_wait_warp(&full_b[sbq], (j0 / BST) & 1);
-            SPL_T1(t0);
-            if (!ok) break;
-            ok = spl_mbar_wait_warp(&full_a[slot], a_parity);
-            SPL_T1(t1);
-            if (!ok) break;
+            // A new segment overwrites the accumulators: the output stage of the one before has to have read them.
+            if (first && segment > 0 && !spl_mbar_wait_warp(acc_free, (segment - 1) & 1, abort)) { ok = false; if (!*abort && lane == 0) spl_note_wait(a.error_flag, 32 + m, i); break; }
+            if (!spl_mbar_wait_warp(&full_b[sbq], (i / BST) & 1, abort)) { ok = false; if (!*abort && lane == 0) spl_note_wait(a.error_flag, 34 + m, i); break; }
+            if (!spl_mbar_wait_warp(&full_a[slot], a_parity, abort)) { ok = false; if (!*abort && lane == 0) spl_note_wait(a.error_flag, 36 + m, i); break; }
             spl_tc_fence_after();
-            const uint64_t t_desc = t_desc0 + uint64_t((mean_slot * TTILE + (quarter & 3) * 32) >> 4);
-            if (n >= 2 && un >= 2) {                             // the common case: nothing to decide between the instructions
+            const uint64_t t_desc = t_desc0 + uint64_t((mean_slot * TTILE + (j & 3) * 32) >> 4);
+            if (!first) {                                        // the common case: nothing to decide between the instructions
                 if (spl_elect_one()) {
 #pragma unroll
                     for (int q = 0; q < 8; ++q)
                         spl_tc_mma_ts_acc(d_mine, a_base + q * 8, b_desc + uint64_t(((q >> 2) * RN * 128 + (q & 3) * 32) >> 4), idesc);
                     spl_tc_mma_ts_acc(d_mine, tmem_aq + slot * 8, t_desc, idesc);
                     spl_tc_commit(&done[un & 15]);            // the unit's A slot is free, and with the stage's other unit its activations
+                    if (last) spl_tc_commit(finished);
                 }
-            } else if (spl_elect_one()) {                        // the warp's first unit (it overwrites the accumulator) and a unit of one group
+            } else if (spl_elect_one()) {                        // the segment's first unit of this warp overwrites its accumulator
                 for (int q = 0; q < 8; ++q)
-                    if ((q >> 2) < n)
-                        spl_tc_mma_ts(d_mine, a_base + q * 8, b_desc + uint64_t(((q >> 2) * RN * 128 + (q & 3) * 32) >> 4), idesc, (un >= 2 || q) ? 1u : 0u);
+                    spl_tc_mma_ts(d_mine, a_base + q * 8, b_desc + uint64_t(((q >> 2) * RN * 128 + (q & 3) * 32) >> 4), idesc, q ? 1u : 0u);
                 spl_tc_mma_ts_acc(d_mine, tmem_aq + slot * 8, t_desc, idesc);
                 spl_tc_commit(&done[un & 15]);
+                if (last) spl_tc_commit(finished);
             }
             __syncwarp();
-            SPL_T1(t2);
+            if (last) ++segment;
             slot += 2; if (slot >= AUN) { slot -= AUN; a_parity ^= 1u; }
         }
-        SPL_TOUT(if (trace && lane == 0 && m == 0) { error_flag[11] = int(t0 / g_count); error_flag[12] = int(t1 / g_count); error_flag[13] = int(t2 / g_count); });
-        SPL_TOUT(if (trace && lane == 0 && m == 0) error_flag[24] = int(clock64() - t_entry));     // last instruction issued
-        if (ok && spl_elect_one()) spl_tc_commit(finished);
-        __syncwarp();
     } else {
         // ---- dequant: thread = output column; codes -> scale * (code - 8), exact in fp16 -> tensor memory. The sets
         // of four warps take the units of two groups in turn; a set's warps write the lanes of their
         // warp index mod 4. A unit also carries its two groups' pairs of the second-term operand.
+        // Every one of these 512 threads runs every segment's output stage and its barriers whatever its waits returned
+        // (a failed thread skips the work, never a barrier), and `ok` is the same in all lanes of a warp.
         const int quarter = warp & 3, col = quarter * 32 + lane, set = warp >> 2;
         const uint32_t lane_base = uint32_t(quarter * 32) << 16;
-        for (int un = set; un < units && ok; un += SPL_TC_SETS) {
-            const int j = un >> 1, half = un & 1, sc = j % CST;
-            SPL_T0();
-            ok = spl_mbar_wait(&full_c[sc], (j / CST) & 1);
-            SPL_TOUT(if (trace && warp == 0 && lane == 0 && un == 0) error_flag[23] = int(clock64() - t_entry));     // first stage has landed
-            SPL_TOUT(if (trace && warp == 0 && lane == 0) { const long long now = clock64(); const long long age = now - trace_clock[sc]; age_all += age; ++age_n; if (now - t_mark > 200) { age_waited += age; ++age_wn; } });
-            SPL_T1(t0);
-            if (!ok) break;
-            const int n = min(SPL_TC_SUPER, g_count - j * SPL_TC_SUPER);      // groups of the stage; this unit has those from 2 * half
+        // The rows' factors of a deferred norm, a warp a row: the squares in one fixed order.
+        if (a.in_squares) {
+            for (int r = warp; r < RN; r += SPL_TC_SETS * 4) {
+                const int row = rb * RN + r;
+                float ss = 0.0f;
+                if (row < a.rows)
+                    for (int g = lane; g < a.in_groups; g += 32) ss += a.in_squares[size_t(row) * a.in_groups + g];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (lane == 0) row_factor[r] = 1.0f / sqrtf(ss / a.in_dim + a.eps);
+            }
+            spl_named_barrier(1, SPL_TC_DEQUANT);
+        }
+        int outputs_done = 0;
+        auto output_stage = [&](int segment) {
+            // The segment: stages [s0, s1) of the block's piece, all of one tile.
+            const int tile = tile0 + segment;
+            const int s0 = max(w0, tile * S), s1 = min(w1, (tile + 1) * S);
+            const bool direct = s0 == tile * S && s1 == (tile + 1) * S;
+            const int cb = set, c0 = cb * 16;
+            const bool mine = cb < RN / 16;                  // sets beyond the rows in use only keep the barriers company
+            float total[16];
+#pragma unroll
+            for (int r = 0; r < 16; ++r) total[r] = 0.0f;
+            if (ok && !spl_mbar_wait_warp(finished, segment & 1, abort)) { ok = false; if (!*abort && lane == 0) spl_note_wait(a.error_flag, 40, segment); *abort_word = 1; }
+            if (ok && mine) {
+                spl_tc_fence_after();
+                uint32_t v0[16], v1[16];
+                spl_tc_ld16(v0, tmem_d + lane_base + c0);
+                spl_tc_ld16(v1, tmem_d + lane_base + RN + c0);
+#pragma unroll
+                for (int r = 0; r < 16; ++r) total[r] = __uint_as_float(v0[r]) + __uint_as_float(v1[r]);
+                spl_tc_fence_before();
+            }
+            __syncwarp();
+            if (lane == 0) spl_mbar_arrive(acc_free);
+            bool finish = true;
+            if (!direct) {
+                // A shared tile: leave the partial sums in this block's slot, take a ticket; the last of the tile's
+                // contributors adds all of their slots in the order of the contraction.
+                const long long t0 = (long long)tile * S;
+                const int c_first = int(((t0 + 1) * P + W - 1) / W) - 1, c_last = int(((t0 + S) * P + W - 1) / W) - 1;
+                float *slot_base = a.slots + (size_t(rb) * P) * (2 * RN * 128);
+                float *my_slot = slot_base + (size_t(c) * 2 + (s0 > tile * S ? 0 : 1)) * (RN * 128);
+                if (ok && mine)
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) my_slot[(c0 + r) * 128 + col] = total[r];
+                __threadfence();
+                spl_named_barrier(1, SPL_TC_DEQUANT);
+                if (threadIdx.x == 0) {
+                    int *ticket = a.tickets + size_t(rb) * a.tiles + tile;
+                    const int taken = (*abort) ? 0 : atomicAdd(ticket, 1);
+                    const int is_last = taken == c_last - c_first;
+                    if (is_last) *ticket = 0;
+                    *last_word = is_last;
+                }
+                spl_named_barrier(1, SPL_TC_DEQUANT);
+                finish = *reinterpret_cast<volatile int *>(last_word) != 0;
+                if (finish && ok && mine) {
+                    __threadfence();
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) total[r] = 0.0f;
+                    for (int cc = c_first; cc <= c_last; ++cc) {
+                        const long long start = W * cc / P;
+                        const float *src = slot_base + (size_t(cc) * 2 + (start > t0 ? 0 : 1)) * (RN * 128);
+#pragma unroll
+                        for (int r = 0; r < 16; ++r) total[r] += __ldcg(src + (c0 + r) * 128 + col);
+                    }
+                }
+            }
+            const bool write = finish && ok && mine;
+            if (write && a.in_squares)
+#pragma unroll
+                for (int r = 0; r < 16; ++r) total[r] *= row_factor[c0 + r];
+            if (a.fuse) {
+                // A fused gate|up tensor: in each run of 32 columns of a tile the first sixteen are gate columns and the
+                // next sixteen the up columns of the same elements, so a lane and the lane sixteen further hold a pair.
+                // They exchange halves of their rows; each then forms act = bf16(silu(gate) * up) for eight rows
+                // (Sources/Shaders/engine.metal:200-219) and writes it straight into the next GEMM's operand with its per-64 sums.
+                float other[8];
+#pragma unroll
+                for (int r = 0; r < 8; ++r) other[r] = __shfl_xor_sync(0xffffffffu, lane < 16 ? total[r + 8] : total[r], 16);
+                float sums[8];
+                const int element = tile * 64 + quarter * 16 + (lane & 15), r_first = lane < 16 ? 0 : 8;
+#pragma unroll
+                for (int r = 0; r < 8; ++r) {
+                    const float gate = lane < 16 ? total[r] : other[r], up = lane < 16 ? other[r] : total[r + 8];
+                    const int row = rb * RN + c0 + r_first + r;
+                    const float v = (write && row < a.rows && element < a.interleave) ? spl_bf16_to_float(spl_float_to_bf16(spl_silu_exact(gate) * up)) : 0.0f;
+                    if (write && row < a.rows && element < a.interleave)
+                        reinterpret_cast<__half *>(a.act_out.values)[a.act_out.at(row, element)] = __float2half_rn(v);
+                    sums[r] = v;
+                }
+#pragma unroll
+                for (int o = 8; o > 0; o >>= 1)
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) sums[r] += __shfl_xor_sync(0xffffffffu, sums[r], o);
+                if ((lane & 15) == 0)
+#pragma unroll
+                    for (int r = 0; r < 8; ++r) cells[((set * 4 + quarter) * 16 + r_first + r) * 2] = sums[r];
+                spl_named_barrier(2 + set, 128);
+                if (quarter == 0 && lane < 16) {
+                    const int row = rb * RN + c0 + lane;
+                    const float *cell = cells + (set * 4 * 16 + lane) * 2;
+                    if (write && row < a.rows) a.act_out.put_sum(row, tile, ((cell[0] + cell[32]) + cell[64]) + cell[96]);
+                }
+                spl_named_barrier(2 + set, 128);
+            } else {
+                const int n = tile * 128 + col;
+                int n_out = n;
+                if (a.interleave > 0) { const int e = tile * 64 + (col >> 5) * 16 + (col & 15); n_out = ((col & 16) ? a.interleave : 0) + e; }
+                const bool inside = a.interleave > 0 ? (tile * 64 + (col >> 5) * 16 + (col & 15)) < a.interleave : n < a.out_ld;
+                float x[16];
+#pragma unroll
+                for (int r = 0; r < 16; ++r) x[r] = 0.0f;
+                if (write && inside) {
+                    float res[16];
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        const int row = rb * RN + c0 + r;
+                        res[r] = (a.residual && row < a.rows) ? a.residual[size_t(row) * a.out_ld + n_out] : 0.0f;
+                    }
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        const int row = rb * RN + c0 + r;
+                        x[r] = total[r] + res[r];
+                        if (row < a.rows) a.out[size_t(row) * a.out_ld + n_out] = x[r];
+                        else x[r] = 0.0f;
+                    }
+                }
+                if (a.emit_weight) {
+                    // The output feeds a deferred norm (Sources/Shaders/engine_na.metal:365-415): bf16(x * w) as the next
+                    // operand, its per-64 sums, and the squares of x per 64 columns.
+                    const float w = (write && inside) ? spl_bf16_to_float(a.emit_weight[n]) : 0.0f;
+                    float sums[16], squares[16];
+#pragma unroll
+                    for (int r = 0; r < 16; ++r) {
+                        const int row = rb * RN + c0 + r;
+                        const float v = spl_bf16_to_float(spl_float_to_bf16(x[r] * w));
+                        if (write && inside && row < a.rows) reinterpret_cast<__half *>(a.emit_out.values)[a.emit_out.at(row, n)] = __float2half_rn(v);
+                        sums[r] = v; squares[r] = x[r] * x[r];
+                    }
+#pragma unroll
+                    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                        for (int r = 0; r < 16; ++r) { sums[r] += __shfl_xor_sync(0xffffffffu, sums[r], o); squares[r] += __shfl_xor_sync(0xffffffffu, squares[r], o); }
+                    if (lane < 16) {
+                        float s = sums[0], q = squares[0];
+#pragma unroll
+                        for (int r = 1; r < 16; ++r) if (lane == r) { s = sums[r]; q = squares[r]; }
+                        cells[((set * 4 + quarter) * 16 + lane) * 2] = s; cells[((set * 4 + quarter) * 16 + lane) * 2 + 1] = q;
+                    }
+                    spl_named_barrier(2 + set, 128);
+                    if (quarter < 2 && lane < 16) {            // warp 0 of the set: the tile's first 64 columns; warp 1: its last
+                        const int row = rb * RN + c0 + lane, group = tile * 2 + quarter;
+                        const float *cell = cells + ((set * 4 + 2 * quarter) * 16 + lane) * 2;
+                        if (write && row < a.rows && group * 64 < a.out_ld) {
+                            a.emit_out.put_sum(row, group, cell[0] + cell[32]);
+                            a.emit_squares[size_t(row) * (a.out_ld / 64) + group] = cell[1] + cell[33];
+                        }
+                    }
+                    spl_named_barrier(2 + set, 128);
+                }
+            }
+        };
+        const int units = 2 * stages;
+        for (int un = set; un < units; un += SPL_TC_SETS) {
+            const int i = un >> 1, half = un & 1, sc = i % CST;
+            // Segments that ended before this unit are written out first (every warp, every segment, in order).
+            const int segment_of = (w0 + i) / S - tile0;
+            while (outputs_done < segment_of) output_stage(outputs_done++);
+            if (ok && !spl_mbar_wait_warp(&full_c[sc], (i / CST) & 1, abort)) { ok = false; if (!*abort && lane == 0) spl_note_wait(a.error_flag, 41, un); *abort_word = 1; }
             // The unit's codes and scale/bias words are read before anything is converted, so the codes can be handed back at once.
             uint4 lo[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)}, hi[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
             uint32_t sbw[2] = {0u, 0u};
+            if (ok) {
 #pragma unroll
-            for (int v = 0; v < 2; ++v) {
-                const int u = 2 * half + v;
-                if (u < n) {
+                for (int v = 0; v < 2; ++v) {
+                    const int u = 2 * half + v;
                     lo[v] = *reinterpret_cast<const uint4 *>(w_ring + size_t(sc) * WSTAGE + u * 4096 + col * 16);
                     hi[v] = *reinterpret_cast<const uint4 *>(w_ring + size_t(sc) * WSTAGE + u * 4096 + 2048 + col * 16);
                     sbw[v] = q_ring[sc * QSTAGE + u * 128 + col];
@@ -547,31 +703,28 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
             }
             __syncwarp();
             if (lane == 0) spl_mbar_arrive(&empty_c[sc]);
-            SPL_T1(t1);
             // The unit's slot was last used by unit un - AUN, which has to have completed.
             const int slot = un % AUN;
-            if (un >= AUN) ok = spl_mbar_wait(&done[(un - AUN) & 15], ((un - AUN) >> 4) & 1);
-            SPL_T1(t2);
-            if (!ok) break;
-            spl_tc_fence_after();
-            // A nibble moved to mantissa bits 6-9 under the exponent of 16 (0x4C00) is the fp16 number 16 + c, and
-            // fma(16 + c, s, -24 s) = s * (c - 8) with one rounding of a result that fp16 holds exactly; -24 s is exact in
-            // fp16 too (3 * 8 significant bits). One shift and one logic operation place the nibbles of both halves of a
-            // word, one fused multiply-add converts the pair. Sixteen registers (32 weights) are converted and stored at a time.
-            uint32_t aq[4];
+            if (ok && un >= AUN && !spl_mbar_wait_warp(&done[(un - AUN) & 15], ((un - AUN) >> 4) & 1, abort)) { ok = false; if (!*abort && lane == 0) spl_note_wait(a.error_flag, 42, un); *abort_word = 1; }
+            if (ok) {
+                spl_tc_fence_after();
+                // A nibble moved to mantissa bits 6-9 under the exponent of 16 (0x4C00) is the fp16 number 16 + c, and
+                // fma(16 + c, s, -24 s) = s * (c - 8) with one rounding of a result that fp16 holds exactly; -24 s is exact in
+                // fp16 too (3 * 8 significant bits). One shift and one logic operation place the nibbles of both halves of a
+                // word, one fused multiply-add converts the pair. Sixteen registers (32 weights) are converted and stored at a time.
+                uint32_t aq[4];
 #pragma unroll
-            for (int v = 0; v < 2; ++v) {
-                const float sf = __uint_as_float(sbw[v] << 16), bf = __uint_as_float(sbw[v] & 0xFFFF0000u);
-                const __half2 s2h = __float2half2_rn(sf), m24h = __float2half2_rn(sf * -24.0f);
-                const uint32_t s2 = *reinterpret_cast<const uint32_t *>(&s2h), m24 = *reinterpret_cast<const uint32_t *>(&m24h);
-                const __half2 q1 = __float2half2_rn(bf * 64.0f), q2 = __float2half2_rn(sf * 512.0f);      // zero for a group past the end
-                aq[2 * v] = *reinterpret_cast<const uint32_t *>(&q1); aq[2 * v + 1] = *reinterpret_cast<const uint32_t *>(&q2);
-                if (2 * half + v < n) {
+                for (int v = 0; v < 2; ++v) {
+                    const float sf = __uint_as_float(sbw[v] << 16), bf = __uint_as_float(sbw[v] & 0xFFFF0000u);
+                    const __half2 s2h = __float2half2_rn(sf), m24h = __float2half2_rn(sf * -24.0f);
+                    const uint32_t s2 = *reinterpret_cast<const uint32_t *>(&s2h), m24 = *reinterpret_cast<const uint32_t *>(&m24h);
+                    const __half2 q1 = __float2half2_rn(bf * 64.0f), q2 = __float2half2_rn(sf * 512.0f);
+                    aq[2 * v] = *reinterpret_cast<const uint32_t *>(&q1); aq[2 * v + 1] = *reinterpret_cast<const uint32_t *>(&q2);
 #pragma unroll
                     for (int part = 0; part < 2; ++part) {
                         const uint4 src = part == 0 ? lo[v] : hi[v];
                         const uint32_t w4[4] = {src.x, src.y, src.z, src.w};
-                        uint32_t a[16];
+                        uint32_t regs[16];
 #pragma unroll
                         for (int w = 0; w < 4; ++w)
                             asm("{\n .reg .b32 xa, xb, xc, xd;\n"
@@ -582,110 +735,43 @@ spl_gemm_q4_tc_kernel(const uint32_t *__restrict__ codes, const uint32_t *__rest
                                 " lop3.b32 xd, xd, 0x03C003C0, 0x4C004C00, 0xEA;\n"
                                 " fma.rn.f16x2 %0, xa, %5, %6;\n fma.rn.f16x2 %1, xb, %5, %6;\n"
                                 " fma.rn.f16x2 %2, xc, %5, %6;\n fma.rn.f16x2 %3, xd, %5, %6;\n}\n"
-                                : "=r"(a[4 * w]), "=r"(a[4 * w + 1]), "=r"(a[4 * w + 2]), "=r"(a[4 * w + 3])
+                                : "=r"(regs[4 * w]), "=r"(regs[4 * w + 1]), "=r"(regs[4 * w + 2]), "=r"(regs[4 * w + 3])
                                 : "r"(w4[w]), "r"(s2), "r"(m24));
-                        spl_tc_st16(tmem_a + lane_base + slot * 64 + v * 32 + part * 16, a);
+                        spl_tc_st16(tmem_a + lane_base + slot * 64 + v * 32 + part * 16, regs);
                     }
                 }
+                // The unit's share of the second-term operand sits at its place among the stage's sixteen values; the rest is zero.
+                if (half == 0) { spl_tc_st4(tmem_aq + lane_base + slot * 8, aq[0], aq[1], aq[2], aq[3]); spl_tc_st4(tmem_aq + lane_base + slot * 8 + 4, 0u, 0u, 0u, 0u); }
+                else { spl_tc_st4(tmem_aq + lane_base + slot * 8, 0u, 0u, 0u, 0u); spl_tc_st4(tmem_aq + lane_base + slot * 8 + 4, aq[0], aq[1], aq[2], aq[3]); }
+                spl_tc_st_wait();
+                spl_tc_fence_before();
             }
-            // The unit's share of the second-term operand sits at its place among the stage's sixteen values; the rest is zero.
-            if (half == 0) { spl_tc_st4(tmem_aq + lane_base + slot * 8, aq[0], aq[1], aq[2], aq[3]); spl_tc_st4(tmem_aq + lane_base + slot * 8 + 4, 0u, 0u, 0u, 0u); }
-            else { spl_tc_st4(tmem_aq + lane_base + slot * 8, 0u, 0u, 0u, 0u); spl_tc_st4(tmem_aq + lane_base + slot * 8 + 4, aq[0], aq[1], aq[2], aq[3]); }
-            SPL_T1(t3);
-            spl_tc_st_wait();
-            SPL_T1(t4);
-            spl_tc_fence_before();
             __syncwarp();
             if (lane == 0) spl_mbar_arrive(&full_a[slot]);
-            SPL_T1(t5);
         }
-        SPL_TOUT(if (trace && warp == 0 && lane == 0) { error_flag[14] = int(t0 / g_count); error_flag[15] = int(t1 / g_count); error_flag[16] = int(t2 / g_count); error_flag[17] = int(t3 / g_count); error_flag[18] = int(t4 / g_count); error_flag[19] = int(t5 / g_count); error_flag[21] = g_count; error_flag[27] = int(age_all / max(age_n, 1)); error_flag[28] = int(age_waited / max(age_wn, 1)); error_flag[29] = age_wn; error_flag[30] = age_n; });
-        // ---- output: the sets share the accumulators' columns, sixteen rows of the step at a time.
-        SPL_T0();
-        if (ok) ok = spl_mbar_wait(finished, 0);
-        SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[25] = int(clock64() - t_entry));     // accumulators complete
-        // A fused gate|up tensor (interleave > 0) holds, in tile t, the gate columns [64 t, 64 t + 64) and then the up columns of
-        // the same range. Without `fuse` the output goes to the columns of the plain layout; with it the block writes
-        // act = bf16(silu(gate) * up) and its per-64 sums (engine.metal:200-219) straight into the next GEMM's operand:
-        // the accumulators pass through shared memory (the activation ring is idle by now) so that a thread holds the
-        // gate and the up value of the same element.
-        float *stage = reinterpret_cast<float *>(b_ring);       // [RN][128] fp32
-        if (ok) {
-            spl_tc_fence_after();
-            const int n = tile * 128 + col;
-            const int n_out = interleave > 0 ? ((col < 64 ? 0 : interleave) + tile * 64 + (col & 63)) : n;
-            const bool is_split = gridDim.y > 1;
-            float *dst = is_split ? partials + size_t(split) * rows_padded * out_ld : out;
-            // (one copy of the body: code that runs once a block is paid for in instruction fetches)
-#pragma unroll 1
-            for (int cb = set; cb < RN / 16; cb += SPL_TC_SETS) {
-                const int c0 = cb * 16;
-                float total[16];
-#pragma unroll
-                for (int a = 0; a < (units > 1 ? 2 : 1); ++a) {
-                    uint32_t v[16];
-                    spl_tc_ld16(v, tmem_d + lane_base + a * RN + c0);
-#pragma unroll
-                    for (int r = 0; r < 16; ++r) total[r] = a == 0 ? __uint_as_float(v[r]) : total[r] + __uint_as_float(v[r]);
-                }
-                SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[31] = int(clock64() - t_entry));     // accumulators read
-                if (fuse) {
-#pragma unroll
-                    for (int r = 0; r < 16; ++r) stage[(c0 + r) * 128 + col] = total[r];
-                } else if (n < out_ld) {
-                    float res[16];
-#pragma unroll
-                    for (int r = 0; r < 16; ++r) {
-                        const int row = rb * RN + c0 + r;
-                        res[r] = (!is_split && residual && row < rows) ? residual[size_t(row) * out_ld + n_out] : 0.0f;
-                    }
-                    SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[32] = int(clock64() - t_entry));     // residual read
-#pragma unroll
-                    for (int r = 0; r < 16; ++r) {
-                        const int row = rb * RN + c0 + r;
-                        if (row < rows) dst[size_t(row) * out_ld + n_out] = total[r] + res[r];
-                    }
-                }
-            }
-        }
-        if (fuse) {
-            // Every dequant thread comes here, whatever happened to it before: the barrier cannot be left waiting.
-            asm volatile("bar.sync 1, %0;\n" ::"n"(SPL_TC_SETS * 128) : "memory");
-            const int t = threadIdx.x, c8 = (t & 7) * 8;
-            for (int rr = t >> 3; rr < RN; rr += SPL_TC_SETS * 16) {
-                const int row = rb * RN + rr;
-                float r[8];
-                {
-                    const float4 g0 = *reinterpret_cast<const float4 *>(stage + rr * 128 + c8), g1 = *reinterpret_cast<const float4 *>(stage + rr * 128 + c8 + 4);
-                    const float4 u0 = *reinterpret_cast<const float4 *>(stage + rr * 128 + 64 + c8), u1 = *reinterpret_cast<const float4 *>(stage + rr * 128 + 64 + c8 + 4);
-                    const float gs[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w}, us[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) r[i] = (ok && row < rows) ? spl_bf16_to_float(spl_float_to_bf16(spl_silu_exact(gs[i]) * us[i])) : 0.0f;
-                }
-                // The sums in one fixed order: fours, then a butterfly over the sixteen fours of a group (8, 4, 2, 1 apart);
-                // a thread here holds two neighbouring fours, so the last level is its own addition.
-                float sa = (r[0] + r[1]) + (r[2] + r[3]), sb2 = (r[4] + r[5]) + (r[6] + r[7]);
-#pragma unroll
-                for (int o = 4; o > 0; o >>= 1) { sa += __shfl_xor_sync(0xffffffffu, sa, o); sb2 += __shfl_xor_sync(0xffffffffu, sb2, o); }
-                if (ok && row < rows) {
-                    const uint2 lo8 = spl_operand_pack4(r[0], r[1], r[2], r[3]), hi8 = spl_operand_pack4(r[4], r[5], r[6], r[7]);
-                    *reinterpret_cast<uint4 *>(act_out.values + act_out.at(row, tile * 64 + c8)) = make_uint4(lo8.x, lo8.y, hi8.x, hi8.y);
-                    if ((t & 7) == 0) act_out.put_sum(row, tile, sa + sb2);
-                }
-            }
-        }
-        SPL_TOUT(if (trace && warp == 4 && lane == 0) error_flag[26] = int(clock64() - t_entry));     // output written
+        while (outputs_done < segments) output_stage(outputs_done++);
     }
-    if (!ok) atomicExch(error_flag, 1 + warp);
+    if (!ok) { *abort_word = 1; atomicExch(a.error_flag, 1 + warp); }
     spl_tc_fence_before();
     __syncthreads();
     if (warp == W_MMA0) {
         spl_tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
     }
+    // A block that gave up may have copies in flight that nobody waited for: the copying threads wait (bounded) for the
+    // last one they asked for in every ring slot before the block's shared memory is handed on.
+    if (*abort_word && lane == 0) {
+        if (warp == W_COPY)
+            for (int sc = 0; sc < CST && sc < issued_c; ++sc) { const int i = sc + (issued_c - 1 - sc) / CST * CST; spl_mbar_wait(&full_c[sc], (i / CST) & 1); }
+        if (warp == W_COPYB) {
+            for (int sb = 0; sb < BST && sb < issued_b; ++sb) { const int i = sb + (issued_b - 1 - sb) / BST * BST; spl_mbar_wait(&full_b[sb], (i / BST) & 1); }
+            for (int st = 0; st < 2 && st < issued_t; ++st) { const int n = st + (issued_t - 1 - st) / 2 * 2; spl_mbar_wait(&full_t[st], (n >> 1) & 1); }
+        }
+    }
 }
 
-// out[r][n] = sum over splits, in split order, of partials[s][r][n] (+ residual[r][n]).
+// out[r][n] = sum over splits, in split order, of partials[s][r][n] (+ residual[r][n]): the reduction pass of the
+// GGUF kernel's split contraction.
 __global__ void spl_gemm_reduce_kernel(const float *__restrict__ partials, int splits, int rows_padded, int rows, int ld,
                                        const float *residual, float *out) {
     spl_grid_begin();

@@ -296,6 +296,101 @@ int32_t spl_plan_blocks(const spl_plan_costs *c, int32_t sessions, const double 
     return best_count;
 }
 
+// ---- row packer (BatchScheduler.buildRows, BatchScheduler.swift:1323-1442) ------------------------------------
+int32_t spl_host_pack_rows(const spl_host *host, const spl_session *sessions, int32_t session_count, const spl_pack_config *config,
+                           spl_row *rows, spl_planned *plan, int32_t *plan_count, int32_t *waiting, int32_t *waiting_count) {
+    if (!host || !sessions || session_count < 0 || !config || !config->costs || !rows || !plan || !plan_count || !waiting || !waiting_count ||
+        config->block < 1) return -1;
+    const spl_config &c = host->config;
+    const int block = config->block;
+    int row_count = 0, plans = 0, waits = 0, logit_rows = 0, reserved = 0;
+    double decode_tokens = 0.0, decode_attention = 0.0;
+    // KV pages this step's rows will take (:1336-1343); eviction of idle slots is the caller's policy.
+    auto reserve = [&](int index, int position) {
+        const spl_session &s = sessions[index];
+        const int need = position / kPageTokens + 1 - int(host->slot_pages[s.slot].size());
+        if (need <= 0) return true;
+        if (need > int(host->free_pages.size()) - reserved) { waiting[waits++] = index; return false; }
+        reserved += need;
+        return true;
+    };
+    auto put = [&](int slot, int token, int position, bool logits, bool verify) {
+        spl_row &r = rows[row_count++];
+        r.slot = slot; r.token = token; r.position = position; r.want_logits = logits ? 1 : 0; r.verify = verify ? 1 : 0; r.reserved[0] = r.reserved[1] = 0;
+    };
+    std::vector<int> decoders, speculative, plain, prefillers;
+    for (int i = 0; i < session_count; ++i) {
+        if (sessions[i].slot < 0 || sessions[i].slot >= c.max_slots) return -1;
+        if (sessions[i].pending >= 0 && int(decoders.size()) < c.max_slots) decoders.push_back(i);
+    }
+    // Speculative sessions verify a drafted block; the rest decode one token (:1347-1361).
+    for (int i : decoders) {
+        const spl_session &s = sessions[i];
+        const int position = s.evaluated, ahead = int(speculative.size()) + 1;
+        const bool fits = ahead * block <= config->max_verify_rows && row_count + ahead * block + int(plain.size()) <= c.max_rows &&
+                          logit_rows + ahead * block + int(plain.size()) <= c.max_logit_rows;
+        if (config->speculate && position + block < c.max_context) {
+            if (fits && reserve(i, position + 2 * block - 1)) speculative.push_back(i);      // otherwise it waits for the next step
+        } else if (reserve(i, position)) {
+            plain.push_back(i);
+        }
+    }
+    for (int i : speculative) {
+        const spl_session &s = sessions[i];
+        decode_tokens += s.block_yield;
+        decode_attention += config->costs->attention_first * double(s.evaluated) / 1000.0;
+    }
+    for (int i : speculative) {
+        const spl_session &s = sessions[i];
+        if (row_count + 1 + s.proposal_count > c.max_rows) return -1;
+        put(s.slot, s.pending, s.evaluated, true, true);
+        for (int k = 0; k < s.proposal_count; ++k) put(s.slot, s.proposal[k], s.evaluated + 1 + k, true, true);
+        logit_rows += s.proposal_count + 1;
+        plan[plans++] = {SPL_PLAN_VERIFY, i, s.proposal_count, 0};
+    }
+    for (int i : plain) {
+        const spl_session &s = sessions[i];
+        if (row_count + 1 > c.max_rows) return -1;
+        put(s.slot, s.pending, s.evaluated, true, false);
+        logit_rows += 1;
+        plan[plans++] = {SPL_PLAN_DECODE, i, 0, 0};
+    }
+    // Prompt chunks, the prompt with least left first (:1403-1440).
+    for (int i = 0; i < session_count; ++i) if (sessions[i].pending < 0) prefillers.push_back(i);
+    std::stable_sort(prefillers.begin(), prefillers.end(), [&](int a, int b) {
+        return sessions[a].prompt_count - sessions[a].fed < sessions[b].prompt_count - sessions[b].fed; });
+    int cap = c.max_rows;
+    if (!decoders.empty()) {
+        int backlog = 0;
+        for (int i : prefillers) backlog += sessions[i].prompt_count - sessions[i].fed;
+        cap = spl_plan_prefill_cap(config->costs, c.max_rows, row_count, decode_tokens + double(plain.size()), decode_attention, config->decode_weight,
+                                   backlog, prefillers.empty() ? 0 : sessions[prefillers[0]].fed, config->prefill_rows_while_decoding);
+    }
+    for (int i : prefillers) {
+        const spl_session &s = sessions[i];
+        const int budget = cap - row_count;
+        if (budget <= 0) break;
+        int count = std::min(s.prompt_count - s.fed, budget);
+        // A step ends exactly where the state is to be kept.
+        int mark = -1;
+        for (int k = 0; k < s.mark_count; ++k) if (s.marks[k] > s.fed && (mark < 0 || s.marks[k] < mark)) mark = s.marks[k];
+        if (mark >= 0 && mark < s.fed + count) count = mark - s.fed;
+        if (!reserve(i, s.fed + count - 1)) {
+            // Whatever still fits in the pages the slot has.
+            count = std::min(count, int(host->slot_pages[s.slot].size()) * kPageTokens - s.fed);
+            if (count <= 0) continue;
+            --waits;      // it takes part after all (the entry reserve() just made is the last one)
+        }
+        const bool complete = s.fed + count == s.prompt_count;
+        if (complete && logit_rows >= c.max_logit_rows) continue;
+        for (int offset = 0; offset < count; ++offset) put(s.slot, s.prompt[s.fed + offset], s.fed + offset, complete && offset == count - 1, false);
+        if (complete) logit_rows += 1;
+        plan[plans++] = {SPL_PLAN_PREFILL, i, count, complete ? 1 : 0};
+    }
+    *plan_count = plans; *waiting_count = waits;
+    return row_count;
+}
+
 // ---- sampling from the k largest logits (Sampler.swift:68-156) -----------------------------------
 // The generator is SplitMix64 kept in `*state`; one uniform = the top 24 bits of an output over 2^24.
 static float sampler_uniform(uint64_t *state) {

@@ -55,6 +55,34 @@ class _Tables(C.Structure):
                                                      "gather_index", "attn_blocks", "page_table")]
 
 
+class _Session(C.Structure):
+    _fields_ = [("slot", C.c_int32), ("evaluated", C.c_int32), ("pending", C.c_int32), ("proposal", C.POINTER(C.c_int32)), ("proposal_count", C.c_int32),
+                ("prompt", C.POINTER(C.c_int32)), ("prompt_count", C.c_int32), ("fed", C.c_int32), ("marks", C.POINTER(C.c_int32)),
+                ("mark_count", C.c_int32), ("block_yield", C.c_double)]
+
+
+class _PackConfig(C.Structure):
+    _fields_ = [("block", C.c_int32), ("max_verify_rows", C.c_int32), ("speculate", C.c_int32), ("prefill_rows_while_decoding", C.c_int32),
+                ("decode_weight", C.c_double), ("costs", C.c_void_p)]
+
+
+class _Planned(C.Structure):
+    _fields_ = [("kind", C.c_int32), ("session", C.c_int32), ("count", C.c_int32), ("complete", C.c_int32)]
+
+
+@dataclass
+class PackSession:
+    """What the row packer reads of a session (BatchScheduler.swift:1323-1442)."""
+    slot: int
+    evaluated: int
+    pending: int = None            # None while the prompt is being fed
+    proposal: tuple = ()
+    prompt: tuple = ()
+    fed: int = 0
+    marks: tuple = ()
+    block_yield: float = 0.0
+
+
 class _Stats(C.Structure):
     _fields_ = [("rows", C.c_int32), ("launches", C.c_int32), ("gpu_seconds", C.c_double), ("wall_seconds", C.c_double)]
 
@@ -138,6 +166,7 @@ def lib():
             "spl_host_max_pages": (i32, [vp]),
             "spl_host_last_error": (C.c_char_p, [vp]),
             "spl_greedy_accept": (i32, [vp, vp, i32, C.POINTER(i32)]),
+            "spl_host_pack_rows": (i32, [vp, vp, i32, vp, vp, vp, C.POINTER(i32), vp, C.POINTER(i32)]),
             "spl_engine_create": (i32, [C.POINTER(Geometry), C.POINTER(_Config), C.POINTER(vp)]),
             "spl_engine_destroy": (None, [vp]),
             "spl_last_error_string": (C.c_char_p, [vp]),
@@ -164,6 +193,9 @@ def lib():
             "spl_debug_read": (i32, [vp, i32, i32, vp, C.c_size_t]),
             "spl_debug_taps": (i32, [vp, i32]),
             "spl_debug_kv_store": (i32, [vp, i32]),
+            "spl_debug_wait_budget": (i32, [vp, C.c_int64]),
+            "spl_debug_drop_weight_stage": (i32, [vp, i32]),
+            "spl_gemm_q4_static_status": (i32, [vp]),
             "spl_op_gemm_gguf": (i32, [i32, i32, vp, i32, i32, vp, i32, vp, vp]),
             "spl_state_bytes": (C.c_size_t, [vp]),
             "spl_state_export": (i32, [vp, i32, vp, C.c_size_t]),
@@ -258,6 +290,29 @@ class Host:
 
     def finish_step(self):
         lib().spl_host_finish_step(self.handle, C.byref(self.last))
+
+    def pack_rows(self, sessions, planner, block=8, max_verify_rows=64, speculate=True, prefill_rows_while_decoding=8, decode_weight=1.0):
+        """BatchScheduler.buildRows: (rows, plan, waiting) for PackSession objects in the scheduler's order; plan entries are
+        (kind, session index, count, complete) with kind 0 verify, 1 decode, 2 prefill."""
+        n = len(sessions)
+        arr = (_Session * max(n, 1))()
+        keep = []
+        for i, s in enumerate(sessions):
+            bufs = [np.ascontiguousarray(x, np.int32) for x in (s.proposal, s.prompt, s.marks)]
+            keep.append(bufs)
+            arr[i].slot, arr[i].evaluated, arr[i].pending = s.slot, s.evaluated, -1 if s.pending is None else s.pending
+            arr[i].proposal, arr[i].proposal_count = bufs[0].ctypes.data_as(C.POINTER(C.c_int32)), len(bufs[0])
+            arr[i].prompt, arr[i].prompt_count, arr[i].fed = bufs[1].ctypes.data_as(C.POINTER(C.c_int32)), len(bufs[1]), s.fed
+            arr[i].marks, arr[i].mark_count = bufs[2].ctypes.data_as(C.POINTER(C.c_int32)), len(bufs[2])
+            arr[i].block_yield = s.block_yield
+        cfg = _PackConfig(block, max_verify_rows, int(speculate), prefill_rows_while_decoding, decode_weight, C.addressof(planner.costs))
+        rows = (_Row * self.config.max_rows)(); plan = (_Planned * max(n, 1))(); waiting = (C.c_int32 * max(n, 1))()
+        plan_count, waiting_count = C.c_int32(), C.c_int32()
+        count = lib().spl_host_pack_rows(self.handle, arr, n, C.byref(cfg), rows, plan, C.byref(plan_count), waiting, C.byref(waiting_count))
+        if count < 0:
+            raise EngineError(10, "spl_host_pack_rows: bad argument")
+        out = [EngineRow(rows[i].slot, rows[i].token, rows[i].position, bool(rows[i].want_logits), bool(rows[i].verify)) for i in range(count)]
+        return out, [(plan[i].kind, plan[i].session, plan[i].count, plan[i].complete) for i in range(plan_count.value)], list(waiting[:waiting_count.value])
 
     def reset_slot(self, slot):
         return lib().spl_host_reset_slot(self.handle, slot)
@@ -529,6 +584,16 @@ class Engine:
 
     def debug_taps(self, enabled=True):
         self._check(lib().spl_debug_taps(self.handle, int(enabled)))
+
+    def debug_wait_budget(self, nanoseconds):
+        self._check(lib().spl_debug_wait_budget(self.handle, int(nanoseconds)))
+
+    def debug_drop_weight_stage(self, stage):
+        self._check(lib().spl_debug_drop_weight_stage(self.handle, int(stage)))
+
+    def static_status(self):
+        """spl_gemm_q4_static_status: raises EngineError('timeout') when a block of the last static GEMMs gave up a wait."""
+        self._check(lib().spl_gemm_q4_static_status(self.handle))
 
     def debug_kv_store(self, enabled=True):
         self._check(lib().spl_debug_kv_store(self.handle, int(enabled)))
