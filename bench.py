@@ -28,6 +28,8 @@ sys.path.insert(0, ROOT)
 
 SESSIONS, BLOCK = 8, 8
 CONTEXT_LOW, CONTEXT_HIGH = 36 * 1024, 42 * 1024
+PREFILL_PROMPT, PREFILL_CHUNK = 54500, 2048        # BASELINE configuration 2: one 54.5K-token prompt in 2,048-row chunks
+RIDER_PROMPT, RIDER_ROWS = 21000, 64               # configuration 3's prefilling session: 64 prompt rows ride in every 64-row decode step
 # DRAM bytes the GEMM kernel moves per algorithmic byte: measured per tensor shape with ncu (reads + writes), 14.81 GB
 # for the 14.41 GB of a full step's 257 launches.
 GEMM_DRAM_PER_ALGORITHMIC_BYTE = 1.025
@@ -112,19 +114,20 @@ class CpuSample:
     """The oracle on a bounded sample of the same step: `layers` blocks of the 27B shape (3 gated-delta + 1 attention per 4)
     and a head of `vocab` columns, 64 rows at `context` tokens of synthetic KV; extrapolated to 64 blocks and the full head."""
 
-    def __init__(self, rows_per_session=BLOCK, sessions=SESSIONS, context=2048, layers=4, vocab=32768):
+    def __init__(self, rows_per_session=BLOCK, sessions=SESSIONS, layers=4, vocab=32768):
         from oracle import oracle as O
         from oracle import tables as T
         self.O, self.T = O, T
-        self.sessions, self.block, self.context, self.layers, self.vocab = sessions, rows_per_session, context, layers, vocab
+        self.sessions, self.block, self.layers, self.vocab = sessions, rows_per_session, layers, vocab
+        ctx = contexts(0)[:sessions]              # the benchmark's own contexts: the attention block sees what the GPU arm sees
         g = O.b27_geometry().with_(layers=layers, vocab=vocab)
         self.model = O.Model(g, WEIGHT_SEED)
-        pages = sessions * (context // 256 + 4)
-        self.host = T.Host(max_slots=sessions, max_rows=sessions * rows_per_session, kv_pages=pages, max_context=context + 1024,
+        pages = sum(c // 256 + 4 for c in ctx)
+        self.host = T.Host(max_slots=sessions, max_rows=sessions * rows_per_session, kv_pages=pages, max_context=max(ctx) + 1024,
                            vocab=vocab, kv_heads=g.kv_heads, last_layer_full=True)
         self.engine = O.Engine(self.model, sessions, pages, self.host.max_pages, self.host.state_units)
         # Allocate each slot's pages with a throwaway row at the end of its context, then fill KV and state.
-        tb = self.host.build([T.Row(s, 1000, context - 1, False) for s in range(sessions)])
+        tb = self.host.build([T.Row(s, 1000, ctx[s] - 1, False) for s in range(sessions)])
         self.engine.step(tb); self.host.finish_step(tb)
         rng = np.random.default_rng(1)
         for index in range(layers // 4):
@@ -134,22 +137,22 @@ class CpuSample:
                 self.engine.buffer(which, index)[:] = 0.01
         for index in range(layers - layers // 4):
             st = self.engine.buffer("state", index); st[:] = rng.uniform(-0.5, 0.5, st.size).astype(np.float32)
-        self.position = context
+        self.position = list(ctx)
         self.cores = O.lib().orc_threads()
         self.sample = (f"{layers} blocks (3 gated-delta : 1 attention) of the 27B shape + a {vocab}-column head, {sessions * rows_per_session} rows, "
-                       f"{sessions} sessions at {context} tokens of synthetic KV; time = blocks x{64 / layers:g} + head x{248320 / vocab:.2f}")
+                       f"{sessions} sessions at the benchmark's contexts ({min(ctx)}-{max(ctx)} tokens of synthetic KV); time = blocks x{64 / layers:g} + head x{248320 / vocab:.2f}")
 
     def step(self):
         """One 64-row verify step; returns the extrapolated seconds of a full 64-block step."""
         T = self.T
-        rows = [T.Row(s, int(splitmix_at(TOKEN_SEED, s * 100 + i + self.position) % self.vocab), self.position + i, True, True)
+        rows = [T.Row(s, int(splitmix_at(TOKEN_SEED, s * 100 + i + self.position[s]) % self.vocab), self.position[s] + i, True, True)
                 for s in range(self.sessions) for i in range(self.block)]
         tb = self.host.build(rows)
         t0 = time.perf_counter(); self.engine.step(tb, max_layers=self.layers); t_blocks = time.perf_counter() - t0
         self.host.finish_step(tb)
         for s in range(self.sessions):
-            self.host.accept_verify(s, self.block, self.position + self.block)
-        self.position += self.block
+            self.position[s] += self.block
+            self.host.accept_verify(s, self.block, self.position[s])
         # The head on the same rows: final norm + head GEMM = a step of zero blocks is not expressible, so time it as a bare GEMM.
         packed, scales, biases = self.model.q4(-1, "head")
         a = np.zeros((self.sessions * self.block, 5120), np.float32) + 0.5
@@ -167,6 +170,10 @@ def run_reference(args, rank, world):
     """The reference arm: the CPU restatement of the step on all host threads, rank 0 only."""
     if rank != 0:
         return
+    # A launcher that starts one process per GPU sets OMP_NUM_THREADS=1 for its workers; this arm is a CPU job and takes
+    # every host core (the OpenMP runtime reads the variable when the oracle's library loads, below).
+    if os.environ.get("OMP_NUM_THREADS") == "1" and ("TORCHELASTIC_RUN_ID" in os.environ or "LOCAL_RANK" in os.environ):
+        os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
     sample = CpuSample()
     for _ in range(max(args.warmup, 0)):
         sample.step()
@@ -192,6 +199,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64, help="blocks of the 27B shape (64 is the benchmark; fewer for ncu captures)")
     ap.add_argument("--context-scale", type=float, default=1.0, help="scales the session contexts (1.0 is the benchmark)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-prefill", action="store_true", help="leave out the prefill, rider and strong-scaling measurements that follow the timed region")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
@@ -208,12 +216,15 @@ def main():
 
     g = S.b27_geometry(layers=args.layers)
     ctx = [int(c * args.context_scale) for c in contexts(rank)]
-    steps_total = args.warmup + 2 * args.steps + 2
-    pages = sum((c + BLOCK * steps_total) // 256 + 2 for c in ctx)
+    steps_total = args.warmup + 4 * args.steps + 8
+    extras = not args.no_prefill
+    prompt_tokens = int(PREFILL_PROMPT * args.context_scale)
+    pages = sum((c + BLOCK * steps_total) // 256 + 2 for c in ctx) + (prompt_tokens // 256 + 4 if extras else 0)
     # The engine's span target (how many scan blocks a step should make; the reference tunes it to its GPU, 592 there): one
-    # scan block fills an SM here, so 576 = 4 blocks on each of 144 SMs keeps the 18 x 32 blocks of this workload in four full waves.
-    cfg = S.EngineConfig(max_slots=SESSIONS, max_rows=SESSIONS * BLOCK, kv_pages=pages, max_context=max(ctx) + BLOCK * steps_total + 256, device=local,
-                         span_target=SPAN_TARGET)
+    # scan block fills an SM here; 608 gives this workload 19 spans of 9 pages, which packs the 148 SMs best.
+    cfg = S.EngineConfig(max_slots=SESSIONS + 1, max_rows=max(SESSIONS * BLOCK + RIDER_ROWS, PREFILL_CHUNK) if extras else SESSIONS * BLOCK, kv_pages=pages,
+                         max_context=max(max(ctx) + BLOCK * steps_total, prompt_tokens if extras else 0) + 256, device=local, span_target=SPAN_TARGET,
+                         max_logit_rows=SESSIONS * BLOCK + 8)
     engine = S.Engine(g, cfg)
     from splosh_b200 import synthetic
     synthetic.load_vectors(engine, WEIGHT_SEED)
@@ -244,6 +255,20 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    # Every rank first runs the same seeded session (slot 8 is free of the timed work): the token ids it decodes have to be
+    # rank 0's, or the replicas are not replicas.
+    if dist is not None:
+        probe = []
+        engine.step([S.EngineRow(SESSIONS, int(splitmix_at(TOKEN_SEED, 7000 + i) % g.vocab), i, i == 23) for i in range(24)])
+        probe += [int(x) for x in engine.argmax(g.vocab)]
+        engine.step([S.EngineRow(SESSIONS, int(splitmix_at(TOKEN_SEED, 8000 + i) % g.vocab), 24 + i, True, True) for i in range(8)])
+        probe += [int(x) for x in engine.argmax(g.vocab)]
+        engine.reset_slot(SESSIONS)
+        gathered = [None] * world
+        dist.all_gather_object(gathered, probe)
+        if any(ids != gathered[0] for ids in gathered):
+            raise SystemExit(f"rank {rank}: the ranks decode different tokens from the same session: {gathered}")
+
     step_index = 0
     for _ in range(args.warmup):
         one_step(step_index, True); step_index += 1
@@ -263,6 +288,10 @@ def main():
     if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     wall_max, gpu_max = float(times[0]), float(times[1])
+    per_rank = [1000.0 * gpu_seconds / args.steps]
+    if dist is not None:
+        per_rank = [None] * world
+        dist.all_gather_object(per_rank, 1000.0 * gpu_seconds / args.steps)
     rows_per_step = SESSIONS * BLOCK
     total_rows = world * rows_per_step * args.steps
 
@@ -272,6 +301,85 @@ def main():
         one_step(step_index, False); step_index += 1
     prof = engine.profile_read()
     engine.debug_profile(False)
+
+    PREFILL_SLOT = SESSIONS
+
+    def prompt_token(i):
+        return int(splitmix_at(TOKEN_SEED ^ 0x9F1E, i) % g.vocab)
+
+    def prefill_pass(tokens, chunk):
+        """One prompt of `tokens` tokens through slot 8 in steps of `chunk` rows; returns (device seconds, launches)."""
+        engine.reset_slot(PREFILL_SLOT)
+        fed, seconds, count = 0, 0.0, 0
+        while fed < tokens:
+            n = min(chunk, tokens - fed)
+            stats = engine.step([S.EngineRow(PREFILL_SLOT, prompt_token(fed + i), fed + i, fed + i == tokens - 1) for i in range(n)])
+            seconds += stats.gpu_seconds; count += stats.launches; fed += n
+        return seconds, count
+
+    prefill = rider = strong = None
+    if extras and world == 1:
+        # Configuration 2: a 54.5K-token prompt in 2,048-row chunks. One chunk warms the wide kernels, one pass is timed,
+        # a third runs with events around every launch for the classes' shares.
+        prefill_pass(min(prompt_tokens, PREFILL_CHUNK), PREFILL_CHUNK)
+        seconds, count = prefill_pass(prompt_tokens, PREFILL_CHUNK)
+        engine.debug_profile(True)
+        prefill_pass(prompt_tokens, PREFILL_CHUNK)
+        shares = engine.profile_read()
+        engine.debug_profile(False)
+        weights, _ = weights_per_step(g)
+        gemm_flops = 2.0 * (weights - g.vocab * g.hidden) * prompt_tokens
+        peaks = {}
+        if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")):
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peaks = json.load(f)
+        tensor_peak = float(peaks.get("bf16_tflops_sustained", 1400.0))
+        gemm_tflops = gemm_flops / (shares["gemm_q4"]["ms"] * 1e-3) / 1e12 if shares["gemm_q4"]["ms"] > 0 else 0.0
+        prefill = {"workload": f"one session, {prompt_tokens}-token prompt in {PREFILL_CHUNK}-row chunks, {g.layers} blocks", "tok_per_s": prompt_tokens / seconds,
+                   "seconds": seconds, "steps": -(-prompt_tokens // PREFILL_CHUNK), "gpu_launches": count,
+                   "gemm": {"tflops": gemm_tflops, "peak_tflops": tensor_peak, "frac": gemm_tflops / tensor_peak,
+                            "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if peaks else "fallback (1.4 PFLOP/s sustained, an earlier measurement on this pool)",
+                            "flops": "2 x the blocks' weights per prompt token (the head runs for the prompt's last token only)"},
+                   "class_ms": {k: v["ms"] for k, v in shares.items()}}
+        # Configuration 3's rider: the 8 decoding sessions' 64 verify rows and 64 rows of a 21K-token prompt in every step,
+        # the prompt half fed (its pages hold synthetic KV, its state is seeded).
+        engine.reset_slot(PREFILL_SLOT)
+        start = RIDER_PROMPT // 2
+        engine.step([S.EngineRow(PREFILL_SLOT, 1000, start - 1, False)])
+        engine.debug_fill_kv(PREFILL_SLOT); engine.debug_fill_state(PREFILL_SLOT, 0x7777)
+        seconds = 0.0
+        for n in range(args.steps + 2):
+            rows = rows_for(step_index) + [S.EngineRow(PREFILL_SLOT, prompt_token(start + i), start + i, False) for i in range(RIDER_ROWS)]
+            stats = engine.step(rows)
+            engine.argmax(248077 if g.vocab == 248320 else g.vocab)
+            for s_ in range(SESSIONS):
+                position[s_] += BLOCK
+                engine.accept_verify(s_, BLOCK, position[s_])
+            start += RIDER_ROWS; step_index += 1
+            if n >= 2:
+                seconds += stats.gpu_seconds
+        rider = {"workload": f"64 verify rows of the 8 decoding sessions + {RIDER_ROWS} rows of a {RIDER_PROMPT}-token prompt (half fed) per step",
+                 "ms_per_step": 1000.0 * seconds / args.steps, "decode_tok_per_s": rows_per_step * args.steps / seconds,
+                 "prefill_tok_per_s": RIDER_ROWS * args.steps / seconds}
+    if extras:
+        # Strong scaling of configuration 3 as written: its 8 sessions split over the GPUs, 8 / N each, weights replicated.
+        share = [s_ for s_ in range(SESSIONS) if s_ % world == rank]
+        seconds = 0.0
+        for n in range(args.steps + 2):
+            rows = [r for r in rows_for(step_index) if r.slot in share]
+            stats = engine.step(rows)
+            engine.argmax(248077 if g.vocab == 248320 else g.vocab)
+            for s_ in share:
+                position[s_] += BLOCK
+                engine.accept_verify(s_, BLOCK, position[s_])
+            step_index += 1
+            if n >= 2:
+                seconds += stats.gpu_seconds
+        slowest = torch.tensor([seconds], dtype=torch.float64, device="cuda")
+        if dist is not None:
+            dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
+        strong = {"workload": f"the 8 sessions split over {world} GPU(s), {len(share)} per GPU, 8-row verify blocks", "ms_per_step": 1000.0 * float(slowest[0]) / args.steps,
+                  "tok_per_s": rows_per_step * args.steps / float(slowest[0])}
 
     if rank == 0:
         peak, peak_source = measured_peak_gbs()
@@ -290,6 +398,7 @@ def main():
                        "l2": "inputs larger than L2: 14.4 GB of weights and the KV pool stream every step"},
             "e2e": {"value": total_rows / wall_max, "unit": "tok/s", "h2d_bytes_per_step": tables_bytes, "d2h_bytes_per_step": rows_per_step * 4},
             "gpu_launches": launches,
+            "ms_per_step_by_rank": per_rank,
             "clocks": clocks,
             "step": {"algorithmic_gb": step_bytes / 1e9, "weights_gb": parts["weights"] / 1e9, "kv_gb": parts["kv"] / 1e9, "state_gb": parts["state"] / 1e9,
                      "hbm_gbs": step_bytes / (step_ms * 1e-3) / 1e9, "frac_of_peak": step_bytes / (step_ms * 1e-3) / 1e9 / peak,
@@ -301,6 +410,12 @@ def main():
                          "peak_source": peak_source,
                          "per_launch": {"algorithmic_bytes": gemm["bytes"] / max(gemm["launches"], 1), "ms": gemm["ms"] / max(gemm["launches"], 1)}},
         }
+        if prefill is not None:
+            line["prefill"] = prefill
+        if rider is not None:
+            line["rider"] = rider
+        if strong is not None:
+            line["strong"] = strong
         if not args.no_cpu_baseline and world == 1:
             value, cores, sample = cpu_baseline()
             line["cpu_baseline"] = {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}

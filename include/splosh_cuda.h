@@ -245,7 +245,8 @@ int32_t spl_pages_held(const spl_engine *engine, int32_t slot);                 
 int32_t spl_free_page_count(const spl_engine *engine);                                        /* Engine.freePageCount */
 spl_status spl_memory(const spl_engine *engine, spl_memory_info *out);                        /* Engine.memory */
 spl_host *spl_engine_host(spl_engine *engine);
-/* Engine.warmUp (Engine.swift:1191-1197): no-op placeholder for graph capture. */
+/* Engine.warmUp (Engine.swift:1191-1197): a full-width step and a one-row step on slot 0, so that the first real request
+ * does not pay for module loading and first touches; slot 0 is left empty. */
 spl_status spl_warmup(spl_engine *engine);
 /* Engine.debugFillKV (Engine.swift:1218-1236): pseudo-random codes and scale 0.01 in every page
  * the slot holds; and a U(-0.5, 0.5) recurrent state as the reference's tests draw it
@@ -315,7 +316,7 @@ spl_status spl_debug_profile_read(spl_engine *engine, int32_t klass, double *mil
  * This entry point runs out[r][:] = GEMM(weights, activations[r][:]) (+ residual) on one of the
  * engine's resident weights and calls no cudaMalloc, cudaFree or other allocating routine: the
  * GEMM operand, its per-64 sums, the slots where blocks that share an output tile leave their partial sums
- * and the tiles' tickets live in a static device array of about 12.9 MiB that every GPU loading the library
+ * and the tiles' tickets live in a static device array of about 12.3 MiB that every GPU loading the library
  * holds until exit.
  *   - all three buffers are DEVICE pointers: activations fp32 [rows][inner], residual (may be
  *     null, may alias out) and out fp32 [rows][ld], ld = the tensor's columns rounded up to 16;

@@ -15,6 +15,7 @@
 #include "spl_gemm_gguf.cuh"
 #include "spl_elementwise.cuh"
 #include "spl_gdn.cuh"
+#include "spl_gdn_chunk.cuh"
 #include "spl_gemm_tc.cuh"
 #include "spl_host.h"
 
@@ -62,10 +63,12 @@ struct spl_engine {
     float *taps = nullptr;
     __nv_bfloat16 *xn = nullptr, *core = nullptr, *act = nullptr, *hsn = nullptr;      // GEMM operands (tile layout)
     float *xn_sums = nullptr, *core_sums = nullptr, *act_sums = nullptr, *hsn_sums = nullptr;
+    float *gdn_records = nullptr, *gdn_o_raw = nullptr;      // the chunked gated-delta path: per (chunk, value head) records; raw outputs [row][value dim]
+    int gdn_chunks_max = 0;
+    uint32_t *d_chunk_runs = nullptr, *d_chunks = nullptr;
     float *xn_squares = nullptr;       // [row][hidden / 64] squares of the residual stream, left by the GEMM that feeds a deferred norm
     float *slots = nullptr;            // partial sums of the GEMM tiles that several blocks share
-    int *tickets = nullptr;            // one per (row block, tile); zero between launches
-    size_t slot_floats = 0, ticket_count = 0;
+    size_t slot_floats = 0;
     int sms = 148;
     int rows_padded = 0, logit_rows_padded = 0;
     int *tc_error = nullptr;
@@ -107,6 +110,10 @@ namespace {
                            std::string(#call) + ": " + cudaGetErrorString(err__));                      \
         }                                                                                               \
     } while (0)
+
+// Between spl_step_launch and spl_step_wait the step's tables, slots, logits and weights belong to the GPU.
+#define SPL_NOT_IN_FLIGHT(e)                                                                                        \
+    do { if ((e)->in_flight) return (e)->fail(SPL_ERR_INVALID_ARGUMENT, "a step is in flight: call spl_step_wait first"); } while (0)
 
 template <typename T>
 spl_status device_alloc(spl_engine *e, T **ptr, size_t count, size_t *account = nullptr) {
@@ -184,7 +191,7 @@ void launch_step(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, c
 
 // ---- GEMM launch ------------------------------------------------------------------------------
 // Rows per operand block for a step of `rows` rows.
-int operand_rn(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : 64; }
+int operand_rn(int rows) { return rows <= 16 ? 16 : rows <= 32 ? 32 : rows <= 64 ? 64 : 128; }
 
 // Splits of the contraction for a GGUF GEMM of `blocks` (tile, row block) pairs and `groups` quant
 // groups: the count that minimises waves x groups per block on `sms` single-block SMs, with a
@@ -211,11 +218,16 @@ struct GemmExtras {
     const float *in_squares = nullptr; int in_dim = 0; float eps = 0.0f;
     const uint16_t *emit_weight = nullptr; const SplOperand *emit_out = nullptr; float *emit_squares = nullptr;
 };
-// Where the tiles that several blocks share meet: slots for partial sums and one ticket per (row block, tile).
-struct GemmScratch { float *slots; size_t slot_floats; int *tickets; size_t ticket_count; int *error_flag; int sms; };
+// Where the blocks of a cut tile leave their partial sums, the launch's error words, the device's SM count.
+struct GemmScratch { float *slots; size_t slot_floats; int *error_flag; int sms; };
 
 // The kernels that need more than the default shared memory, opted in on the current device (the attribute is per device).
-template <int RN> void configure_gemm() { cudaFuncSetAttribute(spl_gemm_q4_tc_kernel<RN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_tc_smem_bytes(RN))); }
+template <int RN> void configure_gemm() {
+    cudaFuncSetAttribute(spl_gemm_q4_tc_kernel<RN, SPL_TC_PLAIN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_tc_smem_bytes(RN)));
+    cudaFuncSetAttribute(spl_gemm_q4_tc_kernel<RN, SPL_TC_EMIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_tc_smem_bytes(RN)));
+    cudaFuncSetAttribute(spl_gemm_q4_tc_kernel<RN, SPL_TC_FUSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_tc_smem_bytes(RN)));
+    if constexpr (RN < 128) cudaFuncSetAttribute(spl_gemm_q4_narrow_kernel<RN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_tc_smem_bytes(RN)));
+}
 template <int RN, int FMT> void configure_gguf() { cudaFuncSetAttribute(spl_gemm_gguf_tc_kernel<RN, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_gguf_smem_bytes(RN, FMT))); }
 template <int HD, int PER_KV> void configure_scan() { cudaFuncSetAttribute(spl_attn_scan_kernel<HD, PER_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_attn_smem_bytes(HD, spl_attn_nq(PER_KV)))); }
 // Once per device and process, with that device current. `sms` (may be null) receives its SM count.
@@ -224,11 +236,13 @@ bool configure_device(int device, int *sms) {
     static int count[64] = {};
     if (device < 0 || device >= 64) return false;
     if (!done[device]) {
-        configure_gemm<16>(); configure_gemm<32>(); configure_gemm<64>();
+        configure_gemm<16>(); configure_gemm<32>(); configure_gemm<64>(); configure_gemm<128>();
         configure_gguf<16, SPL_GGUF_Q4K>(); configure_gguf<32, SPL_GGUF_Q4K>(); configure_gguf<64, SPL_GGUF_Q4K>();
         configure_gguf<16, SPL_GGUF_Q5K>(); configure_gguf<32, SPL_GGUF_Q5K>(); configure_gguf<64, SPL_GGUF_Q5K>();
         configure_gguf<16, SPL_GGUF_Q6K>(); configure_gguf<32, SPL_GGUF_Q6K>(); configure_gguf<64, SPL_GGUF_Q6K>();
         configure_scan<256, 6>(); configure_scan<128, 4>();
+        cudaFuncSetAttribute(spl_gdn_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_gdn_chunk_prepare_smem()));
+        cudaFuncSetAttribute(spl_gdn_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_gdn_chunk_scan_smem()));
         cudaDeviceProp prop;
         if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return false;
         count[device] = prop.multiProcessorCount;
@@ -239,24 +253,85 @@ bool configure_device(int device, int *sms) {
     return true;
 }
 
-// Blocks of a GEMM launch: one per SM, fewer when the tensor has fewer stages than that.
-int gemm_blocks(const SplQ4Dev &w, int sms) { return int(std::min<long long>(sms, (long long)w.tiles * (w.k / 256))); }
+// How a GEMM's weight is cut in pieces, one block a piece and row block: every tile in `splits` pieces, the count that
+// minimises waves x stages per block with a fixed cost per block, and the second kernel of a cut GEMM, counted in.
+// `whole`: the block's output stage needs the whole sum (the fused SiLU gate), so tiles are not cut.
+// Test switch (spl_debug_drop_weight_stage): the q4 GEMM's weight-copy role leaves out this stage of every block's piece, so
+// the roles that wait for it run out of time. -1: off.
+static int g_drop_weight_stage = -1;
+
+struct GemmCut { int pieces, splits; };
+GemmCut gemm_cut(const SplQ4Dev &w, int sms, int rn, int row_blocks, bool whole) {
+    const int stages = w.k / (64 * spl_tc_super(rn));
+    int best = 1; double best_cost = 1e30;
+    for (int s = 1; s <= stages && s <= 16 && !(whole && s > 1); ++s) {
+        const int per = (stages + s - 1) / s;
+        if (s > 1 && per < 2) break;
+        const int waves = (w.tiles * s * row_blocks + sms - 1) / sms;
+        const double cost = double(waves) * (per * spl_tc_super(rn) + 20.0) + (s > 1 ? 12.0 : 0.0);      // in groups of time: a block's fill and output cost about twenty, the second kernel twelve
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
+    }
+    return {w.tiles * best, best};
+}
+
+// Floats of scratch a GEMM on `w` may leave for its second kernel: the wide block's slots, or the narrow block's
+// partials[split][row][column] (cut tiles, and every tile when the output feeds a deferred norm: `emit`).
+size_t gemm_slot_floats(const SplQ4Dev &w, int sms, int rn, int row_blocks, bool emit, bool whole) {
+    const GemmCut cut = gemm_cut(w, sms, rn, row_blocks, whole);
+    if (rn >= 128) return spl_tc_slot_floats(cut.pieces, cut.splits, row_blocks, rn);
+    const int stages = w.k / 256, per = (stages + cut.splits - 1) / cut.splits, splits = (stages + per - 1) / per;
+    return (splits > 1 || emit) ? size_t(splits) * row_blocks * rn * w.ld : 0;
+}
 
 template <int RN>
 bool launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows,
                     const GemmScratch &scratch, const GemmExtras &x, int *launches) {
-    const int row_blocks = (rows + RN - 1) / RN, blocks = gemm_blocks(w, scratch.sms);
-    if (spl_tc_slot_floats(blocks, row_blocks, RN) > scratch.slot_floats || size_t(row_blocks) * w.tiles > scratch.ticket_count) return false;
+    const int row_blocks = (rows + RN - 1) / RN;
+    const GemmCut cut = gemm_cut(w, scratch.sms, RN, row_blocks, x.fuse_act != nullptr);
+    if (RN >= 128 && spl_tc_slot_floats(cut.pieces, cut.splits, row_blocks, RN) > scratch.slot_floats) return false;
     SplGemmArgs a = {};
     a.codes = w.codes; a.sb = w.sb; a.act = op.values; a.act_sums = op.sums; a.out = out; a.residual = residual;
-    a.slots = scratch.slots; a.tickets = scratch.tickets; a.error_flag = scratch.error_flag;
-    a.out_ld = w.ld; a.rows = rows; a.op_blocks = op.blocks; a.tiles = w.tiles; a.stages_per_tile = w.k / 256; a.interleave = w.interleave;
+    a.slots = scratch.slots; a.error_flag = scratch.error_flag;
+    a.out_ld = w.ld; a.rows = rows; a.op_blocks = op.blocks; a.tiles = w.tiles; a.stages_per_tile = w.k / (64 * spl_tc_super(RN)); a.interleave = w.interleave;
+    a.pieces = cut.pieces; a.row_blocks = row_blocks; a.splits = cut.splits;
+    a.drop_stage = g_drop_weight_stage;
     a.fuse = x.fuse_act ? 1 : 0;
     a.act_out = x.fuse_act ? *x.fuse_act : SplOperand{nullptr, nullptr, RN, 1};
     a.in_squares = x.in_squares; a.in_groups = x.in_dim / 64; a.in_dim = float(x.in_dim); a.eps = x.eps;
-    a.emit_weight = x.emit_weight; a.emit_out = x.emit_out ? *x.emit_out : SplOperand{nullptr, nullptr, RN, 1}; a.emit_squares = x.emit_squares;
-    launch_step(spl_gemm_q4_tc_kernel<RN>, dim3(blocks, 1, row_blocks), dim3(SPL_TC_THREADS), spl_tc_smem_bytes(RN), stream, a);
+    const SplOperand emit_out = x.emit_out ? *x.emit_out : SplOperand{nullptr, nullptr, RN, 1};
+    a.emit_weight = x.emit_weight; a.emit_out = emit_out; a.emit_squares = x.emit_squares;
+    const dim3 grid(cut.pieces * row_blocks), block(SPL_TC_THREADS);
+    if constexpr (RN < 128) {
+        // The narrow block: a tile's contraction in `splits` runs of whole stages. A cut GEMM, and one whose output feeds a
+        // deferred norm, leave partial sums for the second kernel.
+        const int stages = w.k / 256, per = (stages + cut.splits - 1) / cut.splits, splits = (stages + per - 1) / per;
+        const bool second = splits > 1 || x.emit_weight != nullptr;
+        const size_t rows_padded = size_t(op.blocks) * RN;
+        if (second && size_t(splits) * rows_padded * w.ld > scratch.slot_floats) return false;
+        launch_step(spl_gemm_q4_narrow_kernel<RN>, dim3(w.tiles, splits, row_blocks), block, spl_tc_smem_bytes(RN), stream, (const uint32_t *)w.codes, (const uint32_t *)w.sb, op.values, op.sums,
+                    out, w.ld, second ? (const float *)nullptr : residual, second ? scratch.slots : (float *)nullptr, rows, op.blocks, w.k / 64, per * 4, scratch.error_flag, w.interleave,
+                    a.act_out, a.fuse, x.in_squares, x.in_dim / 64, float(x.in_dim), x.eps, g_drop_weight_stage);
+        if (launches) ++*launches;
+        if (second) {
+            const long long warps = (long long)rows * ((w.ld + 63) / 64);
+            launch_step(spl_gemm_fixup_rows_kernel, dim3(int(std::min<long long>((warps + 7) / 8, 8LL * scratch.sms))), dim3(256), 0, stream, (const float *)scratch.slots, splits, int(rows_padded), rows, w.ld,
+                        residual, out, x.emit_weight, emit_out, x.emit_squares);
+            if (launches) ++*launches;
+        }
+        return true;
+    }
+    if (x.fuse_act) launch_step(spl_gemm_q4_tc_kernel<RN, SPL_TC_FUSE>, grid, block, spl_tc_smem_bytes(RN), stream, a);
+    else if (x.emit_weight && cut.splits == 1) launch_step(spl_gemm_q4_tc_kernel<RN, SPL_TC_EMIT>, grid, block, spl_tc_smem_bytes(RN), stream, a);
+    else launch_step(spl_gemm_q4_tc_kernel<RN, SPL_TC_PLAIN>, grid, block, spl_tc_smem_bytes(RN), stream, a);
     if (launches) ++*launches;
+    if (cut.splits > 1) {
+        // The second kernel of a cut GEMM: the slots' sum in the order of the contraction, the residual, the output, the emitted operand.
+        const long long warps = (long long)rows * w.tiles * 2;
+        const int blocks = int(std::min<long long>((warps + 7) / 8, 8LL * scratch.sms));
+        launch_step(spl_gemm_fixup_kernel, dim3(blocks), dim3(256), 0, stream, (const float *)scratch.slots, cut.splits, cut.pieces, RN, rows, w.tiles, w.ld, w.interleave,
+                    residual, out, x.emit_weight, emit_out, x.emit_squares);
+        if (launches) ++*launches;
+    }
     return true;
 }
 
@@ -265,7 +340,8 @@ bool launch_gemm_rows(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand 
                       const GemmScratch &scratch, const GemmExtras &x, int *launches) {
     if (op.rn == 16) return launch_gemm_tc<16>(stream, w, op, out, residual, rows, scratch, x, launches);
     if (op.rn == 32) return launch_gemm_tc<32>(stream, w, op, out, residual, rows, scratch, x, launches);
-    return launch_gemm_tc<64>(stream, w, op, out, residual, rows, scratch, x, launches);
+    if (op.rn == 64) return launch_gemm_tc<64>(stream, w, op, out, residual, rows, scratch, x, launches);
+    return launch_gemm_tc<128>(stream, w, op, out, residual, rows, scratch, x, launches);
 }
 
 template <int RN, int FMT>
@@ -301,7 +377,7 @@ void launch_gemm_gguf(cudaStream_t stream, const SplGgufDev &w, const GemmOperan
 bool launch_gemm(spl_engine *e, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows, const GemmExtras &x = GemmExtras()) {
     profile_begin(e, KLASS_GEMM, double(w.bytes()) * ((rows + op.rn - 1) / op.rn));
     --e->launches;      // profile_begin counted one; the launcher counts the kernels it really starts
-    const GemmScratch scratch{e->slots, e->slot_floats, e->tickets, e->ticket_count, e->tc_error, e->sms};
+    const GemmScratch scratch{e->slots, e->slot_floats, e->tc_error, e->sms};
     const bool fits = launch_gemm_rows(e->stream, w, op, out, residual, rows, scratch, x, &e->launches);
     profile_end(e);
     return fits;
@@ -352,6 +428,19 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
     put(t->runs, size_t(t->run_count) * 3, &e->d_runs); put(t->run_info, size_t(t->run_count) * 2, &e->d_run_info);
     put(t->gather_index, t->logit_rows, &e->d_gather); put(t->attn_blocks, size_t(t->attn_block_count) * 2, &e->d_blocks);
     put(t->page_table, size_t(e->c.max_slots) * e->host->max_pages, &e->d_page_table);
+    // Long ordinary runs take the chunked gated-delta kernels: their list, and the list of their 64-token chunks.
+    std::vector<uint32_t> chunk_runs, chunks;
+    for (uint32_t r = 0; r < t->run_count; ++r) {
+        const uint32_t length = t->runs[r * 3 + 2];
+        if (t->run_info[r * 2] != 0 || length < SPL_GDN_CHUNK_MIN || e->state.empty()) continue;
+        const uint32_t index = uint32_t(chunk_runs.size() / 4);
+        chunk_runs.insert(chunk_runs.end(), {t->runs[r * 3], t->runs[r * 3 + 1], length, t->run_info[r * 2 + 1]});
+        for (uint32_t first = 0, n = 0; first < length; first += SPL_GDN_CHUNK, ++n)
+            chunks.insert(chunks.end(), {index, t->runs[r * 3 + 1] + first, std::min<uint32_t>(SPL_GDN_CHUNK, length - first), n});
+    }
+    const int chunked_runs = int(chunk_runs.size() / 4), chunk_count = int(chunks.size() / 4);
+    if (chunk_count > e->gdn_chunks_max) return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: more chunks than the engine's gated-delta scratch holds");
+    put(chunk_runs.data(), chunk_runs.size(), &e->d_chunk_runs); put(chunks.data(), chunks.size(), &e->d_chunks);
     if (off > e->tables_words) return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: tables exceed the engine's buffers");
     e->launches = 0;
     SPL_CUDA(cudaEventRecord(e->ev_begin, e->stream));
@@ -393,7 +482,7 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
         if (!L.full) {
             SplGdnParams p;
             p.rows = R; p.runs = int(t->run_count); p.channels = sh.C; p.key_heads = g.gdn_key_heads; p.value_heads = g.gdn_value_heads;
-            p.head_dim = g.gdn_head_dim; p.proj_ld = L.in_proj.ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps; p.trace = e->tc_error;
+            p.head_dim = g.gdn_head_dim; p.proj_ld = L.in_proj.ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps; p.chunk_min = chunked_runs > 0 ? SPL_GDN_CHUNK_MIN : 0;
             profile_begin(e, KLASS_GDN, 0);
             launch_step(spl_gdn_conv_kernel, dim3(dim3((sh.C + 255) / 256, t->run_count)), dim3(256), 0, e->stream, 
                 e->proj, L.vec[SPL_VEC_CONV], e->conv[linear_index], e->d_runs, e->d_row_read, e->d_row_write, e->gdn_act, p);
@@ -403,6 +492,21 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
                 e->gdn_act, e->proj, L.vec[SPL_VEC_A_LOG], L.vec[SPL_VEC_DT_BIAS], L.vec[SPL_VEC_GDN_NORM], e->state[linear_index],
                 e->journal[linear_index], e->d_runs, e->d_run_info, core, p);
             profile_end(e);
+            if (chunked_runs > 0) {
+                const SplGdnChunkTables ct{e->d_chunk_runs, e->d_chunks, chunked_runs, chunk_count};
+                profile_begin(e, KLASS_GDN, 0);
+                launch_step(spl_gdn_chunk_prepare_kernel, dim3(g.gdn_value_heads, chunk_count), dim3(256), spl_gdn_chunk_prepare_smem(), e->stream,
+                    e->gdn_act, e->proj, L.vec[SPL_VEC_A_LOG], L.vec[SPL_VEC_DT_BIAS], ct, e->gdn_records, p);
+                profile_end(e);
+                profile_begin(e, KLASS_GDN, 0);
+                launch_step(spl_gdn_chunk_scan_kernel, dim3(g.gdn_value_heads, chunked_runs, SPL_GDN_SLICES), dim3(256), spl_gdn_chunk_scan_smem(), e->stream,
+                    e->gdn_records, ct, e->state[linear_index], e->journal[linear_index], e->gdn_o_raw, p);
+                profile_end(e);
+                profile_begin(e, KLASS_GDN, 0);
+                launch_step(spl_gdn_chunk_finish_kernel, dim3(g.gdn_value_heads, chunk_count), dim3(256), 0, e->stream,
+                    e->gdn_o_raw, e->proj, L.vec[SPL_VEC_GDN_NORM], ct, core, p);
+                profile_end(e);
+            }
             ++linear_index;
         } else {
             SplAttnParams p;
@@ -468,12 +572,10 @@ spl_status finish_step(spl_engine *e, spl_step_stats *stats) {
         int flag[4] = {0, 0, 0, 0};
         SPL_CUDA(cudaMemcpy(flag, e->tc_error, sizeof flag, cudaMemcpyDeviceToHost));
         if (flag[0]) {
-            // A block gave up: its tile's ticket may be left half-taken, so the tickets start again from zero.
             cudaMemset(e->tc_error, 0, sizeof flag);
-            cudaMemset(e->tickets, 0, e->ticket_count * sizeof(int));
             if (flag[0] >= 100) return e->fail(SPL_ERR_TIMEOUT, "an attention scan block gave up waiting (warp " + std::to_string(flag[0] - 100) + ")");
             // The wait that ran out first: 10 weight copy for a free stage; 20, 21 activation copy for a free tile of means, a free
-            // stage; 30-37 tensor-core issue (two warps) for a tile of means, the accumulators, activations, converted weights;
+            // stage; 30-37 tensor-core issue (two warps) for a tile of means, activations, converted weights;
             // 40-42 conversion for the accumulators' completion, a weight stage, a free operand slot.
             return e->fail(SPL_ERR_TIMEOUT, "a GEMM block gave up waiting (warp " + std::to_string(flag[0] - 1) + "; first wait " + std::to_string(flag[1]) +
                                             " at " + std::to_string(flag[2]) + ", block " + std::to_string(flag[3] & 0xFFFF) + ")");
@@ -645,7 +747,7 @@ spl_status create(const spl_geometry *gp, const spl_config *cp, spl_engine *e) {
     e->proj_ld = std::max(sh.gdn_n, sh.att_n); e->gate_up_ld = 2 * g.inter; e->core_ld = std::max(sh.VD, sh.AD); e->logits_ld = g.vocab;
     const int LR = e->c.max_logit_rows;
     if ((s = device_alloc(e, &e->h, size_t(R) * H, &e->scratch_bytes)) != SPL_OK) return s;
-    e->rows_padded = (R + 63) / 64 * 64; e->logit_rows_padded = (e->c.max_logit_rows + 63) / 64 * 64;
+    e->rows_padded = (R + 127) / 128 * 128; e->logit_rows_padded = (e->c.max_logit_rows + 127) / 128 * 128;
     const int RP = e->rows_padded, LP = e->logit_rows_padded;
     if ((s = device_alloc(e, &e->xn, size_t(RP) * H, &e->scratch_bytes)) != SPL_OK) return s;
     if ((s = device_alloc(e, &e->xn_sums, spl_operand_sums_floats(RP, H), &e->scratch_bytes)) != SPL_OK) return s;
@@ -673,19 +775,31 @@ spl_status create(const spl_geometry *gp, const spl_config *cp, spl_engine *e) {
     if ((s = device_alloc(e, &e->argmax_ids, size_t(LR), &e->scratch_bytes)) != SPL_OK) return s;
     e->partial_floats = size_t(16) * RP * std::max(H, 4096);      // split-K partial sums of the GGUF kernel
     if ((s = device_alloc(e, &e->partials, e->partial_floats, &e->scratch_bytes)) != SPL_OK) return s;
-    // The q4 GEMM's meeting place for tiles that several blocks share: two slots of 64 x 128 sums a block and row block,
-    // one ticket per (row block, tile) of the widest tensor.
-    const int row_blocks = std::max(RP, LP) / 64;
-    e->slot_floats = spl_tc_slot_floats(e->sms, row_blocks, 64);
-    e->ticket_count = size_t(row_blocks) * ((std::max(std::max(g.vocab, 2 * g.inter), std::max(sh.gdn_n, sh.att_n)) + 127) / 128);
+    // Where the blocks of a cut tile of the q4 GEMM leave their partial sums: a slot of rn x 128 sums a block.
+    const int row_blocks = std::max(RP, LP) / 128;      // more than 64 rows go in blocks of 128
+    // The most slot space any of the engine's tensors takes, at any row count.
+    e->slot_floats = 0;
+    {
+        struct Use { const SplQ4Dev *w; bool emit, whole; };
+        std::vector<Use> all{{&e->head, false, false}};
+        for (const LayerWeights &L : e->layers) { all.push_back({&L.in_proj, false, false}); all.push_back({&L.out_proj, true, false}); all.push_back({&L.gate_up, false, true}); all.push_back({&L.down, true, false}); }
+        for (const Use &u : all)
+            for (int rn : {16, 32, 64, 128})
+                for (int rbs = 1; rbs <= (rn == 128 ? row_blocks : 1); ++rbs)
+                    e->slot_floats = std::max(e->slot_floats, gemm_slot_floats(*u.w, e->sms, rn, rbs, u.emit, u.whole));
+    }
     if ((s = device_alloc(e, &e->slots, e->slot_floats, &e->scratch_bytes)) != SPL_OK) return s;
-    if ((s = device_alloc(e, &e->tickets, e->ticket_count, &e->scratch_bytes)) != SPL_OK) return s;
-    SPL_CUDA(cudaMemsetAsync(e->tickets, 0, e->ticket_count * sizeof(int), e->stream));
+    if (R >= SPL_GDN_CHUNK_MIN && !e->state.empty()) {
+        e->gdn_chunks_max = R / SPL_GDN_CHUNK + e->c.max_slots;
+        if ((s = device_alloc(e, &e->gdn_records, size_t(e->gdn_chunks_max) * g.gdn_value_heads * SPL_GDN_REC_FLOATS, &e->scratch_bytes)) != SPL_OK) return s;
+        if ((s = device_alloc(e, &e->gdn_o_raw, size_t(R) * sh.VD, &e->scratch_bytes)) != SPL_OK) return s;
+    }
     if ((s = device_alloc(e, &e->xn_squares, size_t(RP) * (H / 64), &e->scratch_bytes)) != SPL_OK) return s;
     SPL_CUDA(cudaMemsetAsync(e->xn_squares, 0, size_t(RP) * (H / 64) * 4, e->stream));
     e->attn_partial_floats = size_t(std::max(16 * R, 64 * std::min(R, 128))) * g.heads * (g.head_dim + 2);
     if ((s = device_alloc(e, &e->attn_partials, e->attn_partial_floats, &e->scratch_bytes)) != SPL_OK) return s;
-    e->tables_words = size_t(R) * 5 + size_t(e->c.max_slots) * 5 + size_t(LR) + size_t(R) * 2 + size_t(e->c.max_slots) * e->host->max_pages + 64;
+    e->tables_words = size_t(R) * 5 + size_t(e->c.max_slots) * 5 + size_t(LR) + size_t(R) * 2 + size_t(e->c.max_slots) * e->host->max_pages + 64
+                      + size_t(e->c.max_slots) * 4 + (size_t(R) / SPL_GDN_CHUNK + e->c.max_slots) * 4 + 16;
     SPL_CUDA(cudaMallocHost(reinterpret_cast<void **>(&e->tables_host), e->tables_words * 4));
     if ((s = device_alloc(e, &e->tables_dev, e->tables_words)) != SPL_OK) return s;
     SPL_CUDA(cudaStreamSynchronize(e->stream));
@@ -719,7 +833,7 @@ void spl_engine_destroy(spl_engine *e) {
     for (auto p : e->state) cudaFree(p); for (auto p : e->conv) cudaFree(p); for (auto p : e->journal) cudaFree(p);
     cudaFree(e->h); cudaFree(e->xn); cudaFree(e->proj); cudaFree(e->gdn_act); cudaFree(e->core); cudaFree(e->gate_up); cudaFree(e->act);
     cudaFree(e->q); cudaFree(e->hsn); cudaFree(e->logits); cudaFree(e->argmax_ids); cudaFree(e->partials); cudaFree(e->attn_partials);
-    cudaFree(e->taps); cudaFree(e->features); cudaFree(e->topk_ids); cudaFree(e->topk_values); cudaFree(e->tables_dev); cudaFree(e->slots); cudaFree(e->tickets); cudaFree(e->xn_squares); cudaFree(e->xn_sums); cudaFree(e->core_sums); cudaFree(e->act_sums); cudaFree(e->hsn_sums); cudaFree(e->tc_error);
+    cudaFree(e->taps); cudaFree(e->features); cudaFree(e->topk_ids); cudaFree(e->topk_values); cudaFree(e->tables_dev); cudaFree(e->gdn_records); cudaFree(e->gdn_o_raw); cudaFree(e->slots); cudaFree(e->xn_squares); cudaFree(e->xn_sums); cudaFree(e->core_sums); cudaFree(e->act_sums); cudaFree(e->hsn_sums); cudaFree(e->tc_error);
     if (e->tables_host) cudaFreeHost(e->tables_host);
     for (ProfileSlot &s : e->profile_slots) { cudaEventDestroy(s.begin); cudaEventDestroy(s.end); }
     if (e->ev_begin) cudaEventDestroy(e->ev_begin);
@@ -738,6 +852,7 @@ const char *spl_last_error_string(const spl_engine *e) {
 spl_status spl_weights_set_q4(spl_engine *e, int32_t layer, int32_t kind, int32_t rows, int32_t inner,
                               const uint32_t *packed, const uint16_t *scales, const uint16_t *biases) {
     if (!e || !packed || !scales || !biases) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     SPL_CUDA(cudaSetDevice(e->device));
     if (layer < 0 && kind == SPL_Q4_EMBED) {
         if (rows != e->g.vocab || inner != e->g.hidden) return e->fail(SPL_ERR_INVALID_ARGUMENT, "embedding shape does not match the geometry");
@@ -755,6 +870,7 @@ spl_status spl_weights_set_q4(spl_engine *e, int32_t layer, int32_t kind, int32_
 
 spl_status spl_weights_set_vector(spl_engine *e, int32_t layer, int32_t kind, const uint16_t *bf16, int32_t count) {
     if (!e || !bf16 || kind < 0 || kind >= SPL_VEC_KINDS) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     if (count != vec_count(e->g, kind)) return e->fail(SPL_ERR_INVALID_ARGUMENT, "vector length does not match the geometry");
     SPL_CUDA(cudaSetDevice(e->device));
     uint16_t **slot = nullptr;
@@ -776,6 +892,7 @@ static uint64_t fnv1a64(const char *s) {
 
 spl_status spl_weights_synthesize_q4(spl_engine *e, uint64_t seed) {
     if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     SPL_CUDA(cudaSetDevice(e->device));
     static const char *names[SPL_Q4_KINDS] = {"linear_attn.in_proj_qkv", "linear_attn.in_proj_z", "linear_attn.in_proj_a", "linear_attn.in_proj_b",
                                               "linear_attn.out_proj", "self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj", "self_attn.o_proj",
@@ -816,9 +933,50 @@ spl_status spl_weights_synthesize_q4(spl_engine *e, uint64_t seed) {
     return result;
 }
 
+// Tables built outside the library are checked for range before anything is launched: the kernels index with them.
+static spl_status check_tables(spl_engine *e, const spl_tables *t) {
+    const int max_pages = e->host->max_pages;
+    auto bad = [&](const char *what) { return e->fail(SPL_ERR_INVALID_ROWS, std::string("invalid step rows: ") + what); };
+    if (t->rows == 0 || int(t->rows) > e->c.max_rows) return bad("row count outside the engine's limit");
+    if (!t->tokens || !t->row_slot || !t->row_pos || !t->runs || !t->run_info || !t->row_read || !t->row_write || !t->attn_blocks || !t->page_table ||
+        (t->logit_rows && !t->gather_index)) return bad("a table is missing");
+    if (t->live_rows > t->rows || t->spans == 0 || t->spans > 64 || t->pages_per_span == 0 || t->run_count == 0 || t->run_count > t->rows ||
+        t->attn_block_count == 0 || t->attn_block_count > t->rows) return bad("a count is out of range");
+    for (uint32_t r = 0; r < t->rows; ++r) {
+        if (int(t->tokens[r]) >= e->g.vocab || int(t->row_slot[r]) >= e->c.max_slots || int(t->row_pos[r]) >= e->c.max_context ||
+            int(t->row_read[r]) >= e->c.state_units || int(t->row_write[r]) >= e->c.state_units) return bad("a row's token, slot, position or state unit is out of range");
+        if (int(t->page_table[size_t(t->row_slot[r]) * max_pages + t->row_pos[r] / SPL_PAGE_TOKENS]) >= e->c.kv_pages) return bad("a page id is out of range");
+    }
+    uint32_t covered = 0;
+    for (uint32_t r = 0; r < t->run_count; ++r) {
+        if (int(t->runs[r * 3]) >= e->c.max_slots || t->runs[r * 3 + 1] != covered || t->runs[r * 3 + 2] == 0 || t->run_info[r * 2 + 1] > SPL_JOURNAL_ROWS ||
+            (t->run_info[r * 2] && t->runs[r * 3 + 2] > SPL_JOURNAL_ROWS)) return bad("a run is out of range");
+        covered += t->runs[r * 3 + 2];
+    }
+    if (covered != t->rows) return bad("the runs do not cover the rows");
+    covered = 0;
+    for (uint32_t b = 0; b < t->attn_block_count; ++b) {
+        if (t->attn_blocks[b * 2] != covered || t->attn_blocks[b * 2 + 1] == 0 || t->attn_blocks[b * 2 + 1] > 8) return bad("an attention block is out of range");
+        covered += t->attn_blocks[b * 2 + 1];
+    }
+    if (covered != t->rows) return bad("the attention blocks do not cover the rows");
+    for (uint32_t i = 0; i < t->logit_rows; ++i) if (t->gather_index[i] >= t->rows) return bad("a logit row is out of range");
+    // Every page a slot's rows can see has to be a valid id (the scan walks the table up to the last visible position).
+    for (uint32_t b = 0; b < t->attn_block_count; ++b) {
+        const uint32_t r0 = t->attn_blocks[b * 2], last = t->row_pos[r0] + t->attn_blocks[b * 2 + 1] - 1;
+        if (int(last) >= e->c.max_context) return bad("an attention block runs past the context limit");
+        for (uint32_t pg = 0; pg <= last / SPL_PAGE_TOKENS; ++pg)
+            if (int(t->page_table[size_t(t->row_slot[r0]) * max_pages + pg]) >= e->c.kv_pages) return bad("a page id is out of range");
+    }
+    return SPL_OK;
+}
+
 spl_status spl_step_tables(spl_engine *e, const spl_tables *tables, spl_step_stats *stats) {
     if (!e || !tables) return SPL_ERR_INVALID_ARGUMENT;
     e->error.clear();
+    SPL_NOT_IN_FLIGHT(e);
+    const spl_status checked = check_tables(e, tables);
+    if (checked != SPL_OK) return checked;
     return run_step(e, tables, stats);
 }
 
@@ -858,6 +1016,7 @@ spl_status spl_step_wait(spl_engine *e, spl_step_stats *stats) {
 
 spl_status spl_logits_row(spl_engine *e, int32_t index, float *dst) {
     if (!e || !dst || index < 0 || index >= e->last_logit_rows) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     SPL_CUDA(cudaSetDevice(e->device));
     SPL_CUDA(cudaMemcpyAsync(dst, e->logits + size_t(index) * e->logits_ld, size_t(e->g.vocab) * 4, cudaMemcpyDeviceToHost, e->stream));
     SPL_CUDA(cudaStreamSynchronize(e->stream));
@@ -866,6 +1025,7 @@ spl_status spl_logits_row(spl_engine *e, int32_t index, float *dst) {
 
 spl_status spl_argmax(spl_engine *e, int32_t vocab_limit, int32_t *ids) {
     if (!e || !ids || vocab_limit <= 0 || vocab_limit > e->g.vocab) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     if (e->last_logit_rows == 0) return SPL_OK;
     SPL_CUDA(cudaSetDevice(e->device));
     spl_argmax_kernel<<<e->last_logit_rows, 1024, 0, e->stream>>>(e->logits, e->logits_ld, vocab_limit, e->argmax_ids);
@@ -878,6 +1038,7 @@ spl_status spl_argmax(spl_engine *e, int32_t vocab_limit, int32_t *ids) {
 
 spl_status spl_topk(spl_engine *e, int32_t vocab_limit, int32_t k, int32_t *ids, float *values) {
     if (!e || !ids || !values || vocab_limit <= 0 || vocab_limit > e->g.vocab || k < 1 || k > 64 || k > vocab_limit) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     if (e->last_logit_rows == 0) return SPL_OK;
     SPL_CUDA(cudaSetDevice(e->device));
     const size_t cells = size_t(e->host->config.max_logit_rows) * 64;
@@ -896,6 +1057,7 @@ spl_status spl_topk(spl_engine *e, int32_t vocab_limit, int32_t k, int32_t *ids,
 
 spl_status spl_slot_reset(spl_engine *e, int32_t slot) {
     if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     SPL_CUDA(cudaSetDevice(e->device));
     const int unit = spl_host_reset_slot(e->host, slot);
     for (size_t l = 0; l < e->state.size(); ++l) {
@@ -907,22 +1069,39 @@ spl_status spl_slot_reset(spl_engine *e, int32_t slot) {
 }
 spl_status spl_verify_discard(spl_engine *e, int32_t slot) {
     if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     spl_host_discard_verify(e->host, slot); return SPL_OK;
 }
 spl_status spl_verify_accept(spl_engine *e, int32_t slot, int32_t rows, int32_t token_count) {
     if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     const spl_status s = spl_host_accept_verify(e->host, slot, rows, token_count);
     if (s != SPL_OK) e->error = e->host->error;
     return s;
 }
 spl_status spl_slot_truncate(spl_engine *e, int32_t slot, int32_t token_count) {
     if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     spl_host_truncate(e->host, slot, token_count); return SPL_OK;
 }
 int32_t spl_pages_held(const spl_engine *e, int32_t slot) { return spl_host_pages_held(e->host, slot); }
 int32_t spl_free_page_count(const spl_engine *e) { return spl_host_free_page_count(e->host); }
 spl_host *spl_engine_host(spl_engine *e) { return e ? e->host : nullptr; }
-spl_status spl_warmup(spl_engine *) { return SPL_OK; }
+// Engine.warmUp (Engine.swift:1191-1197): a full-width step and a one-row step on slot 0, which is left empty.
+spl_status spl_warmup(spl_engine *e) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    if (e->in_flight) return e->fail(SPL_ERR_INVALID_ARGUMENT, "a step is in flight: call spl_step_wait first");
+    const int width = std::min(e->c.max_rows, std::min(e->c.max_context - 1, e->c.kv_pages * SPL_PAGE_TOKENS - 1));
+    if (width < 1) return SPL_OK;
+    spl_status s = spl_slot_reset(e, 0);
+    std::vector<spl_row> rows(width);
+    for (int i = 0; i < width; ++i) { rows[i] = {}; rows[i].slot = 0; rows[i].token = 0; rows[i].position = i; rows[i].want_logits = i == width - 1; }
+    if (s == SPL_OK) s = spl_step(e, rows.data(), width, nullptr);
+    spl_row one = {}; one.slot = 0; one.token = 0; one.position = width; one.want_logits = 1;
+    if (s == SPL_OK) s = spl_step(e, &one, 1, nullptr);
+    const spl_status cleared = spl_slot_reset(e, 0);
+    return s == SPL_OK ? cleared : s;
+}
 
 spl_status spl_memory(const spl_engine *ce, spl_memory_info *out) {
     spl_engine *e = const_cast<spl_engine *>(ce);
@@ -944,6 +1123,7 @@ spl_status spl_memory(const spl_engine *ce, spl_memory_info *out) {
 
 spl_status spl_debug_fill_kv(spl_engine *e, int32_t slot) {
     if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     SPL_CUDA(cudaSetDevice(e->device));
     const size_t page_vecs = size_t(e->g.kv_heads) * SPL_PAGE_TOKENS, page_codes = page_vecs * e->g.head_dim;
     for (size_t l = 0; l < e->k_codes.size(); ++l)
@@ -961,6 +1141,7 @@ spl_status spl_debug_fill_kv(spl_engine *e, int32_t slot) {
 
 spl_status spl_debug_fill_state(spl_engine *e, int32_t slot, uint64_t seed) {
     if (!e || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     SPL_CUDA(cudaSetDevice(e->device));
     const size_t count = e->state_layer_bytes / 4;
     for (size_t l = 0; l < e->state.size(); ++l)
@@ -988,8 +1169,7 @@ spl_status spl_debug_wait_budget(spl_engine *e, int64_t nanoseconds) {
 
 spl_status spl_debug_drop_weight_stage(spl_engine *e, int32_t stage) {
     if (!e) return SPL_ERR_INVALID_ARGUMENT;
-    SPL_CUDA(cudaSetDevice(e->device));
-    SPL_CUDA(cudaMemcpyToSymbol(spl_drop_weight_stage, &stage, sizeof stage));
+    g_drop_weight_stage = stage;
     return SPL_OK;
 }
 
@@ -1001,6 +1181,7 @@ spl_status spl_debug_kv_store(spl_engine *e, int32_t enabled) {
 
 spl_status spl_features_enable(spl_engine *e, const int32_t *layers, int32_t count) {
     if (!e || count < 0 || count > 16) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     static const int32_t reference_layers[5] = {5, 19, 33, 47, 61};
     if (count > 0 && !layers) { layers = reference_layers; count = 5; }
     std::vector<int> wanted;
@@ -1024,6 +1205,7 @@ int32_t spl_feature_width(const spl_engine *e) { return e ? int32_t(e->feature_l
 
 spl_status spl_feature_row(spl_engine *e, int32_t row, float *dst) {
     if (!e || !dst) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     if (!e->features) return e->fail(SPL_ERR_INVALID_ARGUMENT, "feature taps are not enabled");
     if (row < 0 || row >= e->last_rows) return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: no such row in the last step");
     SPL_CUDA(cudaSetDevice(e->device));
@@ -1065,6 +1247,7 @@ spl_status spl_debug_read(spl_engine *e, int32_t which, int32_t index, void *dst
     case 10: src = e->core; have = size_t(e->rows_padded) * e->core_ld * 2; break;
     case 11: src = e->q; have = size_t(e->last_rows) * e->g.heads * e->g.head_dim * 2; break;
     case 12: src = e->attn_partials; have = e->attn_partial_floats * 4; break;
+    case 13: src = e->tc_error; have = 64 * sizeof(int); break;
     case 8: if (e->taps && index >= 0 && index < e->g.layers) { src = e->taps + size_t(index) * e->c.max_rows * e->g.hidden; have = size_t(e->last_rows) * e->g.hidden * 4; } break;
     }
     if (!src || bytes > have) return e->fail(SPL_ERR_INVALID_ARGUMENT, "debug read outside the buffer");
@@ -1118,7 +1301,7 @@ spl_status commit_journal(spl_engine *e, int slot) {
     const Shapes sh(e->g);
     SplGdnParams p;
     p.rows = 0; p.runs = 1; p.channels = sh.C; p.key_heads = e->g.gdn_key_heads; p.value_heads = e->g.gdn_value_heads; p.head_dim = e->g.gdn_head_dim;
-    p.proj_ld = e->proj_ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = e->g.eps; p.trace = nullptr;
+    p.proj_ld = e->proj_ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = e->g.eps; p.chunk_min = 0;
     const int rn = 16;
     const SplOperand core{e->core, e->core_sums, rn, 1};
     int linear = 0;
@@ -1143,6 +1326,7 @@ size_t spl_state_bytes(const spl_engine *e) { return e ? sizeof(SnapshotHeader) 
 
 spl_status spl_state_export(spl_engine *e, int32_t slot, void *dst, size_t capacity) {
     if (!e || !dst || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     if (capacity < spl_state_bytes(e)) return e->fail(SPL_ERR_INVALID_ARGUMENT, "state export: the buffer is smaller than spl_state_bytes");
     SPL_CUDA(cudaSetDevice(e->device));
     const spl_status committed = commit_journal(e, slot);
@@ -1163,6 +1347,7 @@ spl_status spl_state_export(spl_engine *e, int32_t slot, void *dst, size_t capac
 
 spl_status spl_state_import(spl_engine *e, int32_t slot, const void *src, size_t bytes) {
     if (!e || !src || slot < 0 || slot >= e->c.max_slots) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     SnapshotHeader header;
     if (bytes < sizeof header) return e->fail(SPL_ERR_SNAPSHOT_MISMATCH, "snapshot mismatch: truncated state blob");
     memcpy(&header, src, sizeof header);
@@ -1192,6 +1377,7 @@ size_t spl_kv_bytes(const spl_engine *e, int32_t token_count) {
 
 spl_status spl_kv_export(spl_engine *e, int32_t slot, int32_t token_count, void *dst, size_t capacity) {
     if (!e || !dst || slot < 0 || slot >= e->c.max_slots || token_count < 0) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     const size_t pages = size_t(token_count + SPL_PAGE_TOKENS - 1) / SPL_PAGE_TOKENS;
     if (pages > e->host->slot_pages[slot].size()) return e->fail(SPL_ERR_INVALID_ARGUMENT, "kv export: the slot holds fewer tokens than asked for");
     if (capacity < spl_kv_bytes(e, token_count)) return e->fail(SPL_ERR_INVALID_ARGUMENT, "kv export: the buffer is smaller than spl_kv_bytes");
@@ -1215,6 +1401,7 @@ spl_status spl_kv_export(spl_engine *e, int32_t slot, int32_t token_count, void 
 
 spl_status spl_kv_import(spl_engine *e, int32_t slot, int32_t token_count, const void *src, size_t bytes) {
     if (!e || !src || slot < 0 || slot >= e->c.max_slots || token_count < 0) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
     SnapshotHeader header;
     if (bytes < sizeof header) return e->fail(SPL_ERR_SNAPSHOT_MISMATCH, "snapshot mismatch: truncated KV blob");
     memcpy(&header, src, sizeof header);
@@ -1254,17 +1441,16 @@ spl_status spl_kv_import(spl_engine *e, int32_t slot, int32_t token_count, const
 // For callers that may not allocate device memory: a host that handed the whole GPU to its own
 // pool at start-up, or a serving loop that bans allocator calls on its hot path because
 // cudaMalloc and cudaFree synchronise the whole device. The scratch the ordinary path takes from the engine's buffers (the bf16 operand with its
-// per-64 sums, the slots where blocks that share a tile leave their partial sums, and the tiles' tickets) lives here in
-// one file-scope device array, so every GPU that loads the library holds SPL_STATIC_BYTES (about 12.9 MiB) until the
+// per-64 sums, and the slots where the blocks of a cut tile leave their partial sums) lives here in
+// one file-scope device array, so every GPU that loads the library holds SPL_STATIC_BYTES (about 12.3 MiB) until the
 // process exits.
 #define SPL_STATIC_ROWS 64
 #define SPL_STATIC_INNER 17408
 #define SPL_STATIC_OPERAND_BYTES (SPL_STATIC_ROWS * SPL_STATIC_INNER * 2)
 #define SPL_STATIC_SUMS_BYTES (SPL_STATIC_ROWS * ((SPL_STATIC_INNER / 64 + 15) / 16) * 128)      // tiles of split means
-#define SPL_STATIC_CONTROL_BYTES 16384     // the error word (first 256 bytes), then one ticket per 128-column tile
-#define SPL_STATIC_TILES ((SPL_STATIC_CONTROL_BYTES - 256) / 4)
-#define SPL_STATIC_BLOCKS 160              // blocks a launch may use: two slots of 64 x 128 sums each
-#define SPL_STATIC_SLOT_BYTES (SPL_STATIC_BLOCKS * 2 * 64 * 128 * 4)
+#define SPL_STATIC_CONTROL_BYTES 256       // the error words
+#define SPL_STATIC_SLOTS 320               // slots of 64 x 128 partial sums: a tensor cut in more pieces than that is refused
+#define SPL_STATIC_SLOT_BYTES (SPL_STATIC_SLOTS * 64 * 128 * 4)
 #define SPL_STATIC_BYTES (SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES + SPL_STATIC_CONTROL_BYTES + SPL_STATIC_SLOT_BYTES)
 static __device__ __align__(256) unsigned char spl_static_scratch[SPL_STATIC_BYTES];
 // The array's address on each device, asked for once per device. The symbol itself is only a
@@ -1323,8 +1509,6 @@ extern "C" spl_status spl_gemm_q4_static(spl_engine *e, int32_t layer, int32_t w
         return e->fail(SPL_ERR_INVALID_ROWS, "spl_gemm_q4_static: rows must be 1..64 (the static scratch holds a 64-row operand)");
     if (w->k > SPL_STATIC_INNER)
         return e->fail(SPL_ERR_INVALID_ARGUMENT, "spl_gemm_q4_static: contraction longer than 17408 does not fit the static scratch");
-    if (w->tiles > SPL_STATIC_TILES)
-        return e->fail(SPL_ERR_INVALID_ARGUMENT, "spl_gemm_q4_static: more output columns than the static scratch has tickets for");
     unsigned char *base = nullptr;
     const spl_status found = static_base(e, &base);
     if (found != SPL_OK) return found;
@@ -1334,12 +1518,12 @@ extern "C" spl_status spl_gemm_q4_static(spl_engine *e, int32_t layer, int32_t w
     float *slots = reinterpret_cast<float *>(base + SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES + SPL_STATIC_CONTROL_BYTES);
     cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
     const int rn = operand_rn(rows);
-    // The array keeps what the last call left. The error word and the tickets have to start at zero; the
+    // The array keeps what the last call left. The error words have to start at zero; the
     // operand and sums of the rows in use are rewritten here, the block's other rows feed outputs
-    // that are never stored, and every slot the output stage reads is written by this call.
+    // that are never stored, and every slot the second kernel reads is written by this call.
     SPL_CUDA(cudaMemsetAsync(control, 0, SPL_STATIC_CONTROL_BYTES, stream));
     spl_operand_kernel<<<rows, 256, 0, stream>>>(device_activations, SplOperand{operand, sums, rn, 1}, w->k);
-    const GemmScratch scratch{slots, SPL_STATIC_SLOT_BYTES / 4, control + 64, SPL_STATIC_TILES, control, std::min(e->sms, SPL_STATIC_BLOCKS)};
+    const GemmScratch scratch{slots, SPL_STATIC_SLOT_BYTES / 4, control, e->sms};
     if (!launch_gemm_rows(stream, *w, GemmOperand{operand, sums, rn, 1}, device_out, device_residual, rows, scratch, GemmExtras(), nullptr))
         return e->fail(SPL_ERR_INVALID_ARGUMENT, "spl_gemm_q4_static: the tensor does not fit the static scratch");
     return check_launch(e, "spl_gemm_q4_static");
@@ -1377,24 +1561,22 @@ spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t
     const int ld = w.ld;
     const int rn = operand_rn(rows), blocks = (rows + rn - 1) / rn;
     float *d_act32 = nullptr, *d_out = nullptr, *d_sums = nullptr; __nv_bfloat16 *d_act = nullptr; int *d_flag = nullptr;
-    e->slot_floats = spl_tc_slot_floats(e->sms, blocks, rn); e->ticket_count = size_t(blocks) * w.tiles;
+    e->slot_floats = gemm_slot_floats(w, e->sms, rn, blocks, false, false);
     if (s == SPL_OK) s = device_alloc(e, &d_act32, size_t(rows) * k);
     if (s == SPL_OK) s = device_alloc(e, &d_act, size_t(blocks) * rn * k);
     if (s == SPL_OK) s = device_alloc(e, &d_sums, spl_operand_sums_floats(size_t(blocks) * rn, k));
     if (s == SPL_OK) s = device_alloc(e, &d_out, size_t(rows) * ld);
     if (s == SPL_OK) s = device_alloc(e, &d_flag, 64);
     if (s == SPL_OK) s = device_alloc(e, &e->slots, e->slot_floats);
-    if (s == SPL_OK) s = device_alloc(e, &e->tickets, e->ticket_count);
     if (s == SPL_OK) s = upload_q4_into(e, w, 0, n, k, packed, scales, biases, false);
     if (s == SPL_OK) {
         cudaMemsetAsync(d_act, 0, size_t(blocks) * rn * k * 2, e->stream);
         cudaMemsetAsync(d_sums, 0, spl_operand_sums_floats(size_t(blocks) * rn, k) * 4, e->stream);
         cudaMemsetAsync(d_flag, 0, 64 * sizeof(int), e->stream);
-        cudaMemsetAsync(e->tickets, 0, e->ticket_count * sizeof(int), e->stream);
         cudaMemcpyAsync(d_act32, activations, size_t(rows) * k * 4, cudaMemcpyHostToDevice, e->stream);
         spl_operand_kernel<<<rows, 256, 0, e->stream>>>(d_act32, SplOperand{d_act, d_sums, rn, blocks}, k);
         if (residual) cudaMemcpy2DAsync(d_out, size_t(ld) * 4, residual, size_t(n) * 4, size_t(n) * 4, rows, cudaMemcpyHostToDevice, e->stream);
-        const GemmScratch scratch{e->slots, e->slot_floats, e->tickets, e->ticket_count, d_flag, e->sms};
+        const GemmScratch scratch{e->slots, e->slot_floats, d_flag, e->sms};
         if (!launch_gemm_rows(e->stream, w, GemmOperand{d_act, d_sums, rn, blocks}, d_out, residual ? d_out : nullptr, rows, scratch, GemmExtras(), nullptr)) s = SPL_ERR_INVALID_ARGUMENT;
         if (s == SPL_OK) s = check_launch(e, "gemm");
         if (cudaStreamSynchronize(e->stream) != cudaSuccess) s = SPL_ERR_DEVICE;
@@ -1403,9 +1585,9 @@ spl_status spl_op_gemm_q4(int32_t device, const uint32_t *packed, const uint16_t
         if (s == SPL_OK) cudaMemcpy2D(out, size_t(n) * 4, d_out, size_t(ld) * 4, size_t(n) * 4, rows, cudaMemcpyDeviceToHost);
     }
     cudaFree(d_sums); cudaFree(d_flag);
-    cudaFree(w.codes); cudaFree(w.sb); cudaFree(d_act32); cudaFree(d_act); cudaFree(d_out); cudaFree(e->slots); cudaFree(e->tickets);
+    cudaFree(w.codes); cudaFree(w.sb); cudaFree(d_act32); cudaFree(d_act); cudaFree(d_out); cudaFree(e->gdn_records); cudaFree(e->gdn_o_raw); cudaFree(e->slots);
     cudaStreamDestroy(e->stream);
-    e->stream = nullptr; e->slots = nullptr; e->tickets = nullptr;
+    e->stream = nullptr; e->slots = nullptr;
     return s;
 }
 
@@ -1425,7 +1607,7 @@ spl_status spl_op_gemm_gguf(int32_t device, int32_t format, const uint8_t *block
     SPL_CUDA(cudaStreamCreate(&e->stream));
     SplGgufDev w;
     w.n = n; w.ld = round16(n); w.tiles = (n + 127) / 128; w.k = k; w.format = format;
-    const int ld = w.ld, rn = operand_rn(rows), row_blocks = (rows + rn - 1) / rn;
+    const int ld = w.ld, rn = std::min(operand_rn(rows), 64), row_blocks = (rows + rn - 1) / rn;      // the GGUF kernel's blocks hold up to 64 rows
     float *d_act32 = nullptr, *d_out = nullptr, *d_sums = nullptr; __nv_bfloat16 *d_act = nullptr; int *d_flag = nullptr; unsigned char *d_native = nullptr;
     e->partial_floats = size_t(16) * row_blocks * rn * ld;
     spl_status s = SPL_OK;

@@ -17,7 +17,7 @@ struct SplGdnParams {
     int rows, runs, channels, key_heads, value_heads, head_dim;
     int proj_ld, z_offset, a_offset, b_offset;     // columns of the fused input projection
     float eps;
-    int *trace;        // builds with -DSPL_TRACE: cycle stamps of block (0, 0)
+    int chunk_min;     // > 0: ordinary runs of at least this many rows are left to the chunked kernels (spl_gdn_chunk.cuh)
 };
 
 // Conv (k = 4, depthwise, no bias) + SiLU over every channel of every run; then the conv history
@@ -87,12 +87,6 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
                           const uint16_t *__restrict__ dt_bias, const uint16_t *__restrict__ norm_weight, float *state, float *journal,
                           const uint32_t *__restrict__ runs, const uint32_t *__restrict__ run_info, SplOperand core, SplGdnParams p) {
     spl_grid_begin();
-#ifdef SPL_TRACE
-    const long long t_entry = clock64();
-#define SPL_G(k) do { if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0 && p.trace) p.trace[k] = int(clock64() - t_entry); } while (0)
-#else
-#define SPL_G(k) do { } while (0)
-#endif
     constexpr int D = SPL_GDN_D, TC = SPL_GDN_TC, NT = SPL_GDN_THREADS, WARPS = NT / 32;
     constexpr int ZT = (TC + WARPS - 1) / WARPS;      // tokens per warp in the norm passes
     __shared__ __align__(16) float q_s[TC][D], k_s[TC][D], v_s[TC][D], o_s[TC][D], jk_s[TC][D];
@@ -102,6 +96,7 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
     const uint32_t slot = runs[run * 3], start = runs[run * 3 + 1], length = runs[run * 3 + 2];
     const bool speculative = run_info[run * 2] != 0;
     const uint32_t pending = run_info[run * 2 + 1];
+    if (!speculative && p.chunk_min > 0 && length >= uint32_t(p.chunk_min)) return;      // a long ordinary run: the chunked kernels take it
     const int VH = p.value_heads, KH = p.key_heads, hk = h / (VH / KH);
     float *jhead = journal + (size_t(slot) * SPL_JOURNAL_ROWS * VH + h) * SPL_JOURNAL_WIDTH;
 
@@ -149,7 +144,6 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
             }
         }
         __syncthreads();
-        SPL_G(56);
 #pragma unroll
         for (int n = 0; n < ZT; ++n) {
             const int tt = warp + n * WARPS;
@@ -168,7 +162,6 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
                 }
             }
         }
-        SPL_G(57);
         if (base == 0 && pending != 0) {
             // Replay the accepted entries; a speculative run then stores the state it starts from.
             for (uint32_t e = 0; e < pending; ++e) {
@@ -194,9 +187,7 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
                     for (int c = 0; c < 4; ++c) stored[r * (D / 4) + 8 * c] = make_float4(S[r][c][0].x, S[r][c][0].y, S[r][c][1].x, S[r][c][1].y);
             }
         }
-        SPL_G(58);
         __syncthreads();      // the tokens' scalars are written; the replay has finished with o_s
-        SPL_G(59);
         for (int tt = 0; tt < count; ++tt) {
             const float inv_q = scal[tt][0], inv_k = scal[tt][1], decay = scal[tt][2], beta = scal[tt][3];
             float4 kv[4], qv[4];
@@ -250,9 +241,7 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
                 if (tid == 0) entry[2 * D] = decay;
             }
         }
-        SPL_G(60);
         __syncthreads();
-        SPL_G(61);
         // Gated RMSNorm and the bf16 operand, one warp a token.
 #pragma unroll
         for (int n = 0; n < ZT; ++n) {
@@ -278,7 +267,6 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
             }
         }
     }
-    SPL_G(62);
     if (!speculative) {
 #pragma unroll
         for (int r = 0; r < 4; ++r)

@@ -610,7 +610,7 @@ class Engine:
         return out
 
     def debug_read(self, which, index, count, dtype=np.float32):
-        names = ["state", "conv", "journal", "k_codes", "v_codes", "k_scale", "v_scale", "hidden", "tap", "proj", "core", "q", "attn_partials"]
+        names = ["state", "conv", "journal", "k_codes", "v_codes", "k_scale", "v_scale", "hidden", "tap", "proj", "core", "q", "attn_partials", "flags"]
         out = np.empty(count, dtype)
         self._check(lib().spl_debug_read(self.handle, names.index(which), index, _ptr(out), out.nbytes))
         return out

@@ -42,7 +42,7 @@ def test_static_gemm_reports_a_timeout_through_its_status_call():
     engine.load_model(O.Model(O.tiny_geometry()))
     d_a = torch.ones((4, 2816), device="cuda"); d_out = torch.zeros((4, 1024), device="cuda")
     engine.debug_wait_budget(20_000_000)
-    engine.debug_drop_weight_stage(1)
+    engine.debug_drop_weight_stage(0)          # every block's first stage: this tensor's blocks have one stage each
     try:
         gemm_q4_static(engine, 0, "down", d_a.data_ptr(), 4, 0, d_out.data_ptr())
         torch.cuda.synchronize()
