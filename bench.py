@@ -30,9 +30,9 @@ SESSIONS, BLOCK = 8, 8
 CONTEXT_LOW, CONTEXT_HIGH = 36 * 1024, 42 * 1024
 PREFILL_PROMPT, PREFILL_CHUNK = 54500, 2048        # BASELINE configuration 2: one 54.5K-token prompt in 2,048-row chunks
 RIDER_PROMPT, RIDER_ROWS = 21000, 64               # configuration 3's prefilling session: 64 prompt rows ride in every 64-row decode step
-# DRAM bytes the GEMM kernel moves per algorithmic byte: measured per tensor shape with ncu (reads + writes), 14.81 GB
+# DRAM bytes the GEMM kernel moves per algorithmic byte: measured per tensor shape with ncu (reads + writes), 15.06 GB
 # for the 14.41 GB of a full step's 257 launches.
-GEMM_DRAM_PER_ALGORITHMIC_BYTE = 1.025
+GEMM_DRAM_PER_ALGORITHMIC_BYTE = 1.044
 SPAN_TARGET = 608      # scan blocks per step the table builder aims for (engine configuration)
 WEIGHT_SEED, TOKEN_SEED = 0x5EED6D17, 0xC0FFEE00
 
@@ -199,7 +199,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64, help="blocks of the 27B shape (64 is the benchmark; fewer for ncu captures)")
     ap.add_argument("--context-scale", type=float, default=1.0, help="scales the session contexts (1.0 is the benchmark)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--no-prefill", action="store_true", help="leave out the prefill, rider and strong-scaling measurements that follow the timed region")
+    ap.add_argument("--no-prefill", action="store_true", help="leave out the prefill, rider, strong-scaling and GGUF measurements that follow the timed region")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
     if args.impl == "reference":
@@ -219,6 +219,7 @@ def main():
     steps_total = args.warmup + 4 * args.steps + 8
     extras = not args.no_prefill
     prompt_tokens = int(PREFILL_PROMPT * args.context_scale)
+    rider_prompt = int(RIDER_PROMPT * args.context_scale)
     pages = sum((c + BLOCK * steps_total) // 256 + 2 for c in ctx) + (prompt_tokens // 256 + 4 if extras else 0)
     # The engine's span target (how many scan blocks a step should make; the reference tunes it to its GPU, 592 there): one
     # scan block fills an SM here; 608 gives this workload 19 spans of 9 pages, which packs the 148 SMs best.
@@ -344,7 +345,7 @@ def main():
         # Configuration 3's rider: the 8 decoding sessions' 64 verify rows and 64 rows of a 21K-token prompt in every step,
         # the prompt half fed (its pages hold synthetic KV, its state is seeded).
         engine.reset_slot(PREFILL_SLOT)
-        start = RIDER_PROMPT // 2
+        start = rider_prompt // 2
         engine.step([S.EngineRow(PREFILL_SLOT, 1000, start - 1, False)])
         engine.debug_fill_kv(PREFILL_SLOT); engine.debug_fill_state(PREFILL_SLOT, 0x7777)
         seconds = 0.0
@@ -358,7 +359,7 @@ def main():
             start += RIDER_ROWS; step_index += 1
             if n >= 2:
                 seconds += stats.gpu_seconds
-        rider = {"workload": f"64 verify rows of the 8 decoding sessions + {RIDER_ROWS} rows of a {RIDER_PROMPT}-token prompt (half fed) per step",
+        rider = {"workload": f"64 verify rows of the 8 decoding sessions + {RIDER_ROWS} rows of a {rider_prompt}-token prompt (half fed) per step",
                  "ms_per_step": 1000.0 * seconds / args.steps, "decode_tok_per_s": rows_per_step * args.steps / seconds,
                  "prefill_tok_per_s": RIDER_ROWS * args.steps / seconds}
     if extras:
@@ -380,6 +381,23 @@ def main():
             dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
         strong = {"workload": f"the 8 sessions split over {world} GPU(s), {len(share)} per GPU, 8-row verify blocks", "ms_per_step": 1000.0 * float(slowest[0]) / args.steps,
                   "tok_per_s": rows_per_step * args.steps / float(slowest[0])}
+    gguf = None
+    if extras and world == 1 and g.hidden % 256 == 0:
+        # BASELINE's GGUF configuration: the same 64-row step on a Q5_K_M-style model (Q5_K blocks, Q6_K embedding and head,
+        # pseudo-random blocks made on the device). One way: the MLX tensors are freed as the GGUF ones arrive, so this
+        # comes last.
+        engine.synthesize_gguf(WEIGHT_SEED, "Q5_K", "Q6_K")
+        seconds = 0.0
+        for n in range(args.steps + 2):
+            stats, _ = one_step(step_index, True); step_index += 1
+            if n >= 2:
+                seconds += stats.gpu_seconds
+        wcount, _ = weights_per_step(g)
+        head_weights = g.vocab * g.hidden
+        gguf_bytes = (wcount - head_weights) * 176 / 256 + head_weights * 210 / 256
+        gguf = {"workload": "the same 64-row step, every block tensor Q5_K, embedding and head Q6_K (GGUF super-blocks), plain norms, unfused SiLU gate",
+                "ms_per_step": 1000.0 * seconds / args.steps, "tok_per_s": rows_per_step * args.steps / seconds, "weights_gb": gguf_bytes / 1e9,
+                "weights_gbs": gguf_bytes / (seconds / args.steps) / 1e9}
 
     if rank == 0:
         peak, peak_source = measured_peak_gbs()
@@ -404,9 +422,9 @@ def main():
                      "hbm_gbs": step_bytes / (step_ms * 1e-3) / 1e9, "frac_of_peak": step_bytes / (step_ms * 1e-3) / 1e9 / peak,
                      "class_ms_per_step": {k: v["ms"] / args.steps for k, v in prof.items()},
                      "class_launches_per_step": {k: v["launches"] / args.steps for k, v in prof.items()}},
-            "roofline": {"kernel": "spl_gemm_q4_tc_kernel", "bound": "hbm", "achieved": gemm_gbs, "peak": peak, "unit": "GB/s",
+            "roofline": {"kernel": "spl_gemm_q4_narrow_kernel", "bound": "hbm", "achieved": gemm_gbs, "peak": peak, "unit": "GB/s",
                          "frac": gemm_gbs / peak, "traffic": GEMM_DRAM_PER_ALGORITHMIC_BYTE * gemm["bytes"] / max(gemm["launches"], 1),
-                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of the 4-block case, per tensor shape, scaled by launches (profiles/gemm_q4_tc_kernel_27b_64rows.md)",
+                         "traffic_source": "dram__bytes_read.sum + dram__bytes_write.sum of an ncu capture of the 4-block case, per tensor shape, scaled by launches (profiles/gemm_q4_narrow_kernel_27b_64rows.md)",
                          "peak_source": peak_source,
                          "per_launch": {"algorithmic_bytes": gemm["bytes"] / max(gemm["launches"], 1), "ms": gemm["ms"] / max(gemm["launches"], 1)}},
         }
@@ -416,6 +434,8 @@ def main():
             line["rider"] = rider
         if strong is not None:
             line["strong"] = strong
+        if gguf is not None:
+            line["gguf"] = gguf
         if not args.no_cpu_baseline and world == 1:
             value, cores, sample = cpu_baseline()
             line["cpu_baseline"] = {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}

@@ -213,6 +213,18 @@ spl_status spl_weights_set_vector(spl_engine *engine, int32_t layer, int32_t kin
  * recipe defines (value n of tensor `name` = centred sum of the four 16-bit fields of
  * SplitMix64(seed ^ fnv1a64(name), n), scaled to deviation 0.02, then quantised group by group). */
 spl_status spl_weights_synthesize_q4(spl_engine *engine, uint64_t seed);
+/* A GGUF-weighted model (the GGUF branch of Engine.gemm, Sources/SploshRuntime/Engine.swift:1666-1695; tensors as
+ * Sources/SploshModel/GgufConvert.swift:1-33 leaves them): one tensor as native K-quant super-blocks
+ * [rows][inner / 256][144, 176 or 210 bytes], `type` the GGUF type number 12 (Q4_K), 13 (Q5_K) or 14 (Q6_K), `kind`
+ * and `layer` as for spl_weights_set_q4 (SPL_Q4_EMBED and SPL_Q4_HEAD with layer -1). The engine copies. Tensors that
+ * share a device tensor (qkv, z, a, b; q, k, v; gate, up) must share a type. Once the head is GGUF the engine steps as
+ * a GGUF-weighted model and wants every GEMM tensor and the embedding as GGUF: its GEMMs form weights as the
+ * reference's tile kernels do (one fp32 operation, rounded to fp16, Sources/Shaders/gguf_formats.h:390-438), the
+ * embedding gather decodes exactly (:463-501), norms are plain RMSNorms and the SiLU gate a kernel of its own. */
+spl_status spl_weights_set_gguf(spl_engine *engine, int32_t layer, int32_t kind, int32_t type, int32_t rows, int32_t inner, const uint8_t *blocks);
+/* Benchmarking: pseudo-random GGUF blocks for every tensor (`block_type`) and for the embedding and head
+ * (`head_type`), generated on the device. */
+spl_status spl_weights_synthesize_gguf(spl_engine *engine, uint64_t seed, int32_t block_type, int32_t head_type);
 /* Engine.step(_:) (Engine.swift:1316): validate, build tables with the engine's own host state,
  * run the pass, wait. */
 spl_status spl_step(spl_engine *engine, const spl_row *rows, int32_t count, spl_step_stats *stats);

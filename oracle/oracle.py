@@ -74,6 +74,8 @@ def lib():
         L.orc_engine_destroy.argtypes = [C.c_void_p]
         L.orc_engine_reset_slot.argtypes = [C.c_void_p, C.c_int, C.c_int]
         L.orc_engine_buffer.restype = C.c_void_p; L.orc_engine_buffer.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_size_t)]
+        L.orc_set_norm_contract.argtypes = [C.c_int]
+        L.orc_model_set_gguf.restype = C.c_int; L.orc_model_set_gguf.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
         L.orc_step.restype = C.c_int; L.orc_step.argtypes = [C.c_void_p, C.POINTER(_CTables), C.c_void_p, C.c_void_p, C.c_int]
         L.orc_attention_scan.restype = C.c_int
         L.orc_attention_scan.argtypes = [C.c_void_p, C.c_int, C.POINTER(_CTables), C.c_int, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
@@ -248,6 +250,33 @@ class Model:
         biases = np.ctypeslib.as_array(C.cast(b, C.POINTER(C.c_uint16)), (r, k // 64))
         return packed, scales, biases
 
+    def set_gguf(self, layer, kind, gguf_kind, blocks):
+        """The tensor as native GGUF super-blocks from now on (uint8 [rows, inner / 256, block bytes])."""
+        blocks = np.ascontiguousarray(blocks, np.uint8)
+        if lib().orc_model_set_gguf(self.handle, layer, Q4_KINDS.index(kind), GGUF_TYPE[gguf_kind], _ptr(blocks)):
+            raise ValueError(f"tensor {kind} of layer {layer} cannot hold {gguf_kind} blocks")
+        if not hasattr(self, "_gguf"):
+            self._gguf = {}
+        self._gguf[(layer, kind)] = (gguf_kind, blocks)
+
+    def gguf(self, layer, kind):
+        return self._gguf[(layer, kind)]
+
+    def to_gguf(self, block_kind="Q5_K", head_kind="Q6_K"):
+        """Re-quantise every tensor from its MLX affine-4 values to GGUF K-quants: the synthetic GGUF-weighted model
+        (all 2-D tensors `block_kind`, embedding and head `head_kind`). Parity is defined on the decoded blocks."""
+        def convert(layer, kind, gguf_kind):
+            packed, scales, biases = self.q4(layer, kind)
+            to_float = lambda bits: (bits.astype(np.uint32) << 16).view(np.float32)
+            values = dequant_mlx4(packed, to_float(scales), to_float(biases), packed.shape[1] * 8)
+            self.set_gguf(layer, kind, gguf_kind, quantize_gguf(gguf_kind, values))
+        for layer in range(self.g.layers):
+            for kind in (["q", "k", "v", "o"] if self.full(layer) else ["qkv", "z", "a", "b", "out"]) + ["gate", "up", "down"]:
+                convert(layer, kind, block_kind)
+        convert(-1, "embed", head_kind)
+        convert(-1, "head", head_kind)
+        return self
+
     def vec(self, layer, kind):
         p, n = C.c_void_p(), C.c_int()
         if lib().orc_model_vec(self.handle, layer, VEC_KINDS.index(kind), C.byref(p), C.byref(n)):
@@ -306,6 +335,13 @@ class Engine:
         rc = lib().orc_step(self.handle, C.byref(ct), _ptr(logits), None if hidden is None else _ptr(hidden), max_layers)
         assert rc == 0
         return (logits, hidden) if taps else logits
+
+
+def set_norm_contract(deferred):
+    """True (the default): norms after the first are the reference's deferred form (Sources/Shaders/engine_na.metal:365-415:
+    the operand is bf16(h w), the consumer multiplies its sums by the row's rsqrt). False: the plain RMSNorm before rounding
+    (Sources/Shaders/engine.metal:159-178)."""
+    lib().orc_set_norm_contract(1 if deferred else 0)
 
 
 def argmax(logits, limit):

@@ -111,6 +111,10 @@ struct Q4 {
     std::vector<uint32_t> packed;    // [rows][inner / 8], eight low-first nibbles per word
     std::vector<uint16_t> scales;    // [rows][inner / 64] bf16
     std::vector<uint16_t> biases;
+    // A GGUF-weighted model holds the tensor as native K-quant super-blocks instead ([rows][inner / 256], format = the
+    // GGUF type number 12, 13 or 14); the MLX arrays above are then ignored.
+    int gguf_format = 0;
+    std::vector<uint8_t> gguf;
 };
 
 // The quantiser of Sources/SploshRuntime/DraftModel.swift:634-670 with the "minmax" range rule.
@@ -240,7 +244,35 @@ struct Operand {                       // a GEMM's activation input: bf16-rounde
 };
 
 // out[r][n] = sum_k a[r][k] * w[n][k] (+ residual), under the weight contract in force.
+extern "C" {
+void orc_gguf_tile_weights(int format, const uint8_t *data, int blocks, float *out);
+void orc_decode_q45k(const uint8_t *data, int blocks, int fifth_bit, float *out);
+void orc_decode_q6k(const uint8_t *data, int blocks, float *out);
+}
+
+// The GGUF branch of the GEMM (Sources/SploshRuntime/Engine.swift:1666-1695, Sources/Shaders/engine_gguf.metal:82-273): the
+// bf16-rounded activations against weights formed as the tile kernels form them (one fp32 operation, rounded to fp16).
+void gemm_gguf_model(const Q4 &w, const Operand &a, int rows, float *out, int out_stride, const float *residual, const float *row_scale) {
+    const int K = w.inner, per_row = K / 256, bytes = w.gguf_format == 14 ? 210 : w.gguf_format == 13 ? 176 : 144;
+#pragma omp parallel
+    {
+        std::vector<float> weights(K);
+#pragma omp for schedule(static)
+        for (int n = 0; n < w.rows; ++n) {
+            orc_gguf_tile_weights(w.gguf_format, w.gguf.data() + size_t(n) * per_row * bytes, per_row, weights.data());
+            for (int r = 0; r < rows; ++r) {
+                const float *x = &a.values[size_t(r) * K];
+                double acc = 0;
+                for (int i = 0; i < K; ++i) acc += double(x[i] * weights[i]);
+                const size_t index = size_t(r) * out_stride + n;
+                out[index] = residual ? float(acc + double(residual[index])) : row_scale ? float(acc) * row_scale[r] : float(acc);
+            }
+        }
+    }
+}
+
 void gemm(const Q4 &w, const Operand &a, int rows, float *out, int out_stride, const float *residual, const float *row_scale = nullptr) {
+    if (w.gguf_format) { gemm_gguf_model(w, a, rows, out, out_stride, residual, row_scale); return; }
     const int K = w.inner, groups = K / 64;
     const bool rounded = g_weight_contract == 1;
 #pragma omp parallel
@@ -871,6 +903,17 @@ int orc_model_q4(void *model, int layer, int kind, int *rows, int *inner, const 
     *rows = t->rows; *inner = t->inner; *packed = t->packed.data(); *scales = t->scales.data(); *biases = t->biases.data();
     return 0;
 }
+// One tensor of the model as native GGUF blocks [rows][inner / 256] of `format` (12, 13, 14): the GEMMs and the embedding
+// gather use them from then on. The tensor keeps its shape.
+int orc_model_set_gguf(void *model, int layer, int kind, int format, const uint8_t *data) {
+    Model *m = static_cast<Model *>(model);
+    Q4 *t = kind == Q_EMBED ? &m->embed : kind == Q_HEAD ? &m->head : &m->layers[layer].q4[kind];
+    if (t->rows == 0 || t->inner % 256 || (format != 12 && format != 13 && format != 14)) return 1;
+    const size_t bytes = size_t(t->rows) * (t->inner / 256) * (format == 14 ? 210 : format == 13 ? 176 : 144);
+    t->gguf.assign(data, data + bytes);
+    t->gguf_format = format;
+    return 0;
+}
 int orc_model_vec(void *model, int layer, int kind, const uint16_t **data, int *count) {
     Model *m = static_cast<Model *>(model);
     const std::vector<uint16_t> *v = kind == V_FINAL_NORM ? &m->final_norm : &m->layers[layer].vec[kind];
@@ -960,6 +1003,14 @@ int orc_step(void *engine, const Tables *tp, float *logits, float *hidden_taps, 
     // Embedding (engine.metal:39-57).
     for (int r = 0; r < R; ++r) {
         const uint32_t token = t.tokens[r];
+        if (m.embed.gguf_format) {
+            // The embedding gather decodes its row exactly (Sources/Shaders/gguf_formats.h:463-501).
+            const int per_row = H / 256, bytes = m.embed.gguf_format == 14 ? 210 : m.embed.gguf_format == 13 ? 176 : 144;
+            const uint8_t *src = m.embed.gguf.data() + size_t(token) * per_row * bytes;
+            if (m.embed.gguf_format == 14) orc_decode_q6k(src, per_row, &h[size_t(r) * H]);
+            else orc_decode_q45k(src, per_row, m.embed.gguf_format == 13, &h[size_t(r) * H]);
+            continue;
+        }
         for (int c = 0; c < H; ++c) {
             const uint32_t nib = (m.embed.packed[size_t(token) * H / 8 + c / 8] >> (4 * (c % 8))) & 0xF;
             h[size_t(r) * H + c] = bf16_to_float(m.embed.scales[size_t(token) * H / 64 + c / 64]) * float(nib)

@@ -24,6 +24,7 @@ namespace {
 struct LayerWeights {
     bool full = false;
     SplQ4Dev in_proj, out_proj, gate_up, down;     // in_proj: qkv|z|a|b (gated-delta) or q|k|v (attention)
+    SplGgufDev g_in_proj, g_out_proj, g_gate_up, g_down;      // the same tensors of a GGUF-weighted model (gate|up: gate columns, then up columns)
     uint16_t *vec[SPL_VEC_KINDS] = {};
 };
 
@@ -48,6 +49,8 @@ struct spl_engine {
 
     std::vector<LayerWeights> layers;
     SplQ4Dev head;
+    SplGgufDev g_head;                  // a GGUF-weighted model's head, and its embedding table as native blocks [vocab][hidden / 256]
+    unsigned char *g_embed = nullptr; int g_embed_format = 0;
     uint32_t *embed_packed = nullptr; uint16_t *embed_scales = nullptr, *embed_biases = nullptr;
     uint16_t *final_norm = nullptr;
     float *inv_freq = nullptr;
@@ -219,7 +222,7 @@ struct GemmExtras {
     const uint16_t *emit_weight = nullptr; const SplOperand *emit_out = nullptr; float *emit_squares = nullptr;
 };
 // Where the blocks of a cut tile leave their partial sums, the launch's error words, the device's SM count.
-struct GemmScratch { float *slots; size_t slot_floats; int *error_flag; int sms; };
+struct GemmScratch { float *slots; size_t slot_floats; int *error_flag; int sms; spl_engine *timed = nullptr; };    // timed: the engine whose profile times the second kernel as elementwise work
 
 // The kernels that need more than the default shared memory, opted in on the current device (the attribute is per device).
 template <int RN> void configure_gemm() {
@@ -313,10 +316,11 @@ bool launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &o
                     a.act_out, a.fuse, x.in_squares, x.in_dim / 64, float(x.in_dim), x.eps, g_drop_weight_stage);
         if (launches) ++*launches;
         if (second) {
+            if (scratch.timed) { profile_end(scratch.timed); profile_begin(scratch.timed, KLASS_ELEMENTWISE, 0); }
+            else if (launches) ++*launches;
             const long long warps = (long long)rows * ((w.ld + 63) / 64);
             launch_step(spl_gemm_fixup_rows_kernel, dim3(int(std::min<long long>((warps + 7) / 8, 8LL * scratch.sms))), dim3(256), 0, stream, (const float *)scratch.slots, splits, int(rows_padded), rows, w.ld,
                         residual, out, x.emit_weight, emit_out, x.emit_squares);
-            if (launches) ++*launches;
         }
         return true;
     }
@@ -326,11 +330,12 @@ bool launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &o
     if (launches) ++*launches;
     if (cut.splits > 1) {
         // The second kernel of a cut GEMM: the slots' sum in the order of the contraction, the residual, the output, the emitted operand.
+        if (scratch.timed) { profile_end(scratch.timed); profile_begin(scratch.timed, KLASS_ELEMENTWISE, 0); }
+        else if (launches) ++*launches;
         const long long warps = (long long)rows * w.tiles * 2;
         const int blocks = int(std::min<long long>((warps + 7) / 8, 8LL * scratch.sms));
         launch_step(spl_gemm_fixup_kernel, dim3(blocks), dim3(256), 0, stream, (const float *)scratch.slots, cut.splits, cut.pieces, RN, rows, w.tiles, w.ld, w.interleave,
                     residual, out, x.emit_weight, emit_out, x.emit_squares);
-        if (launches) ++*launches;
     }
     return true;
 }
@@ -377,7 +382,7 @@ void launch_gemm_gguf(cudaStream_t stream, const SplGgufDev &w, const GemmOperan
 bool launch_gemm(spl_engine *e, const SplQ4Dev &w, const GemmOperand &op, float *out, const float *residual, int rows, const GemmExtras &x = GemmExtras()) {
     profile_begin(e, KLASS_GEMM, double(w.bytes()) * ((rows + op.rn - 1) / op.rn));
     --e->launches;      // profile_begin counted one; the launcher counts the kernels it really starts
-    const GemmScratch scratch{e->slots, e->slot_floats, e->tc_error, e->sms};
+    const GemmScratch scratch{e->slots, e->slot_floats, e->tc_error, e->sms, e};
     const bool fits = launch_gemm_rows(e->stream, w, op, out, residual, rows, scratch, x, &e->launches);
     profile_end(e);
     return fits;
@@ -413,11 +418,17 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
     const int R = int(t->rows);
     if (R <= 0 || R > e->c.max_rows) return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: row count outside the engine's limit");
     if (int(t->logit_rows) > e->host->config.max_logit_rows) return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: too many logit rows");
+    const bool gguf = e->g_head.blocks != nullptr;      // a GGUF-weighted model: every GEMM tensor and the embedding came through spl_weights_set_gguf
+    if (gguf) {
+        bool all = e->g_embed != nullptr;
+        for (const LayerWeights &L : e->layers) all = all && L.g_in_proj.blocks && L.g_out_proj.blocks && L.g_gate_up.blocks && L.g_down.blocks;
+        if (!all) return e->fail(SPL_ERR_INVALID_ARGUMENT, "a GGUF-weighted engine needs every tensor as GGUF blocks");
+    }
     for (size_t l = 0; l < e->layers.size(); ++l) {
         const LayerWeights &L = e->layers[l];
-        if (!L.in_proj.codes || !L.vec[SPL_VEC_INPUT_NORM]) return e->fail(SPL_ERR_INVALID_ARGUMENT, "weights of a block are not set");
+        if ((!gguf && !L.in_proj.codes) || !L.vec[SPL_VEC_INPUT_NORM]) return e->fail(SPL_ERR_INVALID_ARGUMENT, "weights of a block are not set");
     }
-    if (!e->head.codes || !e->embed_packed || !e->final_norm) return e->fail(SPL_ERR_INVALID_ARGUMENT, "model-level weights are not set");
+    if ((!gguf && (!e->head.codes || !e->embed_packed)) || !e->final_norm) return e->fail(SPL_ERR_INVALID_ARGUMENT, "model-level weights are not set");
     SPL_CUDA(cudaSetDevice(e->device));
     // Tables: pack into the pinned blob, one copy.
     uint32_t *hb = e->tables_host;
@@ -448,12 +459,20 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
 
     const int H = g.hidden;
     // GEMM operands of this step: row blocks of rn rows, in the tile layout the tensor cores read.
-    const int rn = operand_rn(R), blocks = (R + rn - 1) / rn;
+    const int rn = gguf ? std::min(operand_rn(R), 64) : operand_rn(R), blocks = (R + rn - 1) / rn;      // the GGUF kernel's blocks hold up to 64 rows
     const SplOperand xn{e->xn, e->xn_sums, rn, blocks}, core{e->core, e->core_sums, rn, blocks}, act{e->act, e->act_sums, rn, blocks};
     const GemmOperand gxn{e->xn, e->xn_sums, rn, blocks}, gcore{e->core, e->core_sums, rn, blocks}, gact{e->act, e->act_sums, rn, blocks};
     profile_begin(e, KLASS_ELEMENTWISE, 0);
-    launch_step(spl_embed_q4_kernel, dim3(R), dim3(128), 0, e->stream, e->embed_packed, e->embed_scales, e->embed_biases, e->d_tokens, e->h, H);
+    if (gguf) launch_step(spl_embed_gguf_kernel, dim3(R), dim3(256), 0, e->stream, (const unsigned char *)e->g_embed, e->g_embed_format, (const uint32_t *)e->d_tokens, e->h, H);
+    else launch_step(spl_embed_q4_kernel, dim3(R), dim3(128), 0, e->stream, e->embed_packed, e->embed_scales, e->embed_biases, e->d_tokens, e->h, H);
     profile_end(e);
+    // A GGUF-weighted model: the GGUF GEMM (spl_gemm_gguf.cuh) has no fused forms, so its blocks run plain norms and an
+    // unfused SiLU gate (the results are the deferred forms' up to the operand's rounding point).
+    auto ggemm = [&](const SplGgufDev &w, const GemmOperand &op, float *out, const float *residual, int rows) {
+        profile_begin(e, KLASS_GEMM, double(w.bytes()) * ((rows + op.rn - 1) / op.rn));
+        launch_gemm_gguf(e->stream, w, op, out, residual, rows, e->partials, e->partial_floats, e->tc_error);
+        profile_end(e);
+    };
 
     // The attention partials of the widest scan of the step have to fit (checked before anything is launched, so a
     // refused step leaves no slot half-advanced).
@@ -473,12 +492,13 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
         const int live = (l + 1 == g.layers) ? int(t->live_rows) : R;
         int feature_tap = -1;
         for (size_t f = 0; f < e->feature_layers.size(); ++f) if (e->feature_layers[f] == l) feature_tap = int(f);
-        if (l == 0) {
+        if (l == 0 || gguf) {
             profile_begin(e, KLASS_ELEMENTWISE, 0);
             norm(R, L.vec[SPL_VEC_INPUT_NORM], nullptr, xn);
             profile_end(e);
         }
-        fits &= launch_gemm(e, L.in_proj, gxn, e->proj, nullptr, R, l == 0 ? GemmExtras() : scaled);
+        if (gguf) ggemm(L.g_in_proj, gxn, e->proj, nullptr, R);
+        else fits &= launch_gemm(e, L.in_proj, gxn, e->proj, nullptr, R, l == 0 ? GemmExtras() : scaled);
         if (!L.full) {
             SplGdnParams p;
             p.rows = R; p.runs = int(t->run_count); p.channels = sh.C; p.key_heads = g.gdn_key_heads; p.value_heads = g.gdn_value_heads;
@@ -532,7 +552,17 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
             }
             ++full_index;
         }
-        if (live > 0) {
+        if (live > 0 && gguf) {
+            ggemm(L.g_out_proj, gcore, e->h, e->h, live);
+            profile_begin(e, KLASS_ELEMENTWISE, 0);
+            norm(live, L.vec[SPL_VEC_POST_NORM], nullptr, xn);
+            profile_end(e);
+            ggemm(L.g_gate_up, gxn, e->gate_up, nullptr, live);
+            profile_begin(e, KLASS_ELEMENTWISE, 0);
+            launch_step(spl_swiglu_kernel, dim3(g.inter / 64, live), dim3(32), 0, e->stream, (const float *)e->gate_up, e->gate_up_ld, g.inter, act);
+            profile_end(e);
+            ggemm(L.g_down, gact, e->h, e->h, live);
+        } else if (live > 0) {
             // The mixer's output projection adds into the residual stream and leaves the post norm's operand.
             GemmExtras mixer; mixer.emit_weight = L.vec[SPL_VEC_POST_NORM]; mixer.emit_out = &xn; mixer.emit_squares = e->xn_squares;
             fits &= launch_gemm(e, L.out_proj, gcore, e->h, e->h, live, mixer);
@@ -553,10 +583,11 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
     }
     if (t->logit_rows > 0) {
         profile_begin(e, KLASS_OTHER, 0);
-        const int lrn = operand_rn(int(t->logit_rows)), lblocks = (int(t->logit_rows) + lrn - 1) / lrn;
+        const int lrn = gguf ? std::min(operand_rn(int(t->logit_rows)), 64) : operand_rn(int(t->logit_rows)), lblocks = (int(t->logit_rows) + lrn - 1) / lrn;
         norm(int(t->logit_rows), e->final_norm, e->d_gather, SplOperand{e->hsn, e->hsn_sums, lrn, lblocks});
         profile_end(e);
-        fits &= launch_gemm(e, e->head, GemmOperand{e->hsn, e->hsn_sums, lrn, lblocks}, e->logits, nullptr, int(t->logit_rows));
+        if (gguf) ggemm(e->g_head, GemmOperand{e->hsn, e->hsn_sums, lrn, lblocks}, e->logits, nullptr, int(t->logit_rows));
+        else fits &= launch_gemm(e, e->head, GemmOperand{e->hsn, e->hsn_sums, lrn, lblocks}, e->logits, nullptr, int(t->logit_rows));
     }
     if (!fits) return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: the GEMM scratch is smaller than the step needs");
     SPL_CUDA(cudaEventRecord(e->ev_end, e->stream));
@@ -828,6 +859,8 @@ void spl_engine_destroy(spl_engine *e) {
     }
     release_q4(e->head);
     cudaFree(e->embed_packed); cudaFree(e->embed_scales); cudaFree(e->embed_biases); cudaFree(e->final_norm); cudaFree(e->inv_freq);
+    cudaFree(e->g_embed); cudaFree(e->g_head.blocks);
+    for (LayerWeights &L : e->layers) { cudaFree(L.g_in_proj.blocks); cudaFree(L.g_out_proj.blocks); cudaFree(L.g_gate_up.blocks); cudaFree(L.g_down.blocks); }
     for (auto p : e->k_codes) cudaFree(p); for (auto p : e->v_codes) cudaFree(p);
     for (auto p : e->k_scale) cudaFree(p); for (auto p : e->v_scale) cudaFree(p);
     for (auto p : e->state) cudaFree(p); for (auto p : e->conv) cudaFree(p); for (auto p : e->journal) cudaFree(p);
@@ -882,6 +915,116 @@ spl_status spl_weights_set_vector(spl_engine *e, int32_t layer, int32_t kind, co
     if (!*slot) SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(slot), size_t(count) * 2));
     SPL_CUDA(cudaMemcpy(*slot, bf16, size_t(count) * 2, cudaMemcpyHostToDevice));
     return SPL_OK;
+}
+
+// The GGUF twin of a q4 device tensor of the engine.
+static SplGgufDev *gguf_twin(spl_engine *e, const SplQ4Dev *q) {
+    if (q == &e->head) return &e->g_head;
+    for (LayerWeights &L : e->layers) {
+        if (q == &L.in_proj) return &L.g_in_proj;
+        if (q == &L.out_proj) return &L.g_out_proj;
+        if (q == &L.gate_up) return &L.g_gate_up;
+        if (q == &L.down) return &L.g_down;
+    }
+    return nullptr;
+}
+
+// Native blocks [rows][inner / 256] of `format` become columns [n0, n0 + rows) of the GGUF twin of `q`; the twin is
+// allocated (and the q4 tensor it replaces freed) the first time.
+static spl_status upload_gguf_into(spl_engine *e, SplQ4Dev &q, int n0, int rows, int inner, int format, const unsigned char *native, bool device_source) {
+    SplGgufDev *w = gguf_twin(e, &q);
+    if (!w) return e->fail(SPL_ERR_INVALID_ARGUMENT, "no such tensor");
+    if (inner % 256) return e->fail(SPL_ERR_INVALID_ARGUMENT, "a GGUF tensor's inner dimension must be a multiple of 256");
+    if (!w->blocks) {
+        w->n = q.n; w->ld = q.ld; w->tiles = q.tiles; w->k = q.k; w->format = format;
+        SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&w->blocks), w->device_bytes()));
+        SPL_CUDA(cudaMemsetAsync(w->blocks, 0, w->device_bytes(), e->stream));      // columns nobody sets are zero blocks: weights 0
+        e->weight_bytes += w->device_bytes();
+        if (q.codes) { e->weight_bytes -= q.device_bytes(); cudaFree(q.codes); cudaFree(q.sb); q.codes = nullptr; q.sb = nullptr; }
+    } else if (w->format != format) {
+        return e->fail(SPL_ERR_INVALID_ARGUMENT, "tensors fused into one device tensor (qkv, z, a, b; q, k, v; gate, up) must share a GGUF type");
+    }
+    const size_t bytes = size_t(rows) * (inner / 256) * spl_gguf_block_bytes(format);
+    unsigned char *staged = nullptr;
+    if (!device_source) {
+        SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&staged), bytes));
+        SPL_CUDA(cudaMemcpyAsync(staged, native, bytes, cudaMemcpyHostToDevice, e->stream));
+        native = staged;
+    }
+    const size_t items = size_t(rows) * (inner / 256) * spl_gguf_pieces(format);
+    spl_repack_gguf_kernel<<<int(std::min<size_t>((items + 255) / 256, 16384)), 256, 0, e->stream>>>(native, rows, inner / 256, format, w->blocks, n0);
+    const spl_status launched = check_launch(e, "gguf repack");
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    cudaFree(staged);
+    return launched;
+}
+
+static bool gguf_type_ok(int type) { return type == SPL_GGUF_Q4K || type == SPL_GGUF_Q5K || type == SPL_GGUF_Q6K; }
+
+spl_status spl_weights_set_gguf(spl_engine *e, int32_t layer, int32_t kind, int32_t type, int32_t rows, int32_t inner, const uint8_t *blocks) {
+    if (!e || !blocks) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
+    if (!gguf_type_ok(type)) return e->fail(SPL_ERR_INVALID_ARGUMENT, "GGUF type must be 12 (Q4_K), 13 (Q5_K) or 14 (Q6_K)");
+    SPL_CUDA(cudaSetDevice(e->device));
+    if (layer < 0 && kind == SPL_Q4_EMBED) {
+        if (rows != e->g.vocab || inner != e->g.hidden || inner % 256) return e->fail(SPL_ERR_INVALID_ARGUMENT, "embedding shape does not match the geometry");
+        const size_t bytes = size_t(rows) * (inner / 256) * spl_gguf_block_bytes(type);
+        cudaFree(e->g_embed); e->g_embed = nullptr;
+        SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&e->g_embed), bytes));
+        SPL_CUDA(cudaMemcpy(e->g_embed, blocks, bytes, cudaMemcpyHostToDevice));
+        e->g_embed_format = type;
+        return SPL_OK;
+    }
+    Placement pl;
+    const spl_status s = place(e, layer, kind, &pl);
+    if (s != SPL_OK) return s;
+    if (rows != pl.rows || inner != pl.inner) return e->fail(SPL_ERR_INVALID_ARGUMENT, "tensor shape does not match the geometry");
+    return upload_gguf_into(e, *pl.dst, pl.n0, rows, inner, type, blocks, false);
+}
+
+// Seeded synthetic GGUF weights for timing (no host copy of a 27B model exists here): every block tensor as
+// `block_type`, the embedding and the head as `head_type`.
+spl_status spl_weights_synthesize_gguf(spl_engine *e, uint64_t seed, int32_t block_type, int32_t head_type) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
+    if (!gguf_type_ok(block_type) || !gguf_type_ok(head_type)) return e->fail(SPL_ERR_INVALID_ARGUMENT, "GGUF type must be 12 (Q4_K), 13 (Q5_K) or 14 (Q6_K)");
+    SPL_CUDA(cudaSetDevice(e->device));
+    const spl_geometry &g = e->g;
+    if (g.hidden % 256 || g.inter % 256) return e->fail(SPL_ERR_INVALID_ARGUMENT, "GGUF tensors need inner dimensions that are multiples of 256");
+    const size_t most = size_t(std::max(g.vocab, std::max(2 * g.heads * g.head_dim, g.inter))) * (std::max(g.hidden, g.inter) / 256) * 210;
+    unsigned char *staged = nullptr;
+    SPL_CUDA(cudaMalloc(reinterpret_cast<void **>(&staged), most));
+    spl_status result = SPL_OK;
+    auto fill = [&](unsigned char *dst, int rows, int inner, int type, uint64_t stream_seed) {
+        const size_t blocks = size_t(rows) * (inner / 256);
+        spl_synth_gguf_kernel<<<int(std::min<size_t>((blocks + 127) / 128, 65535)), 128, 0, e->stream>>>(dst, blocks, type, stream_seed);
+    };
+    for (int layer = -1; layer < g.layers && result == SPL_OK; ++layer)
+        for (int kind = 0; kind < SPL_Q4_KINDS && result == SPL_OK; ++kind) {
+            if (layer < 0) {
+                if (kind == SPL_Q4_EMBED) {
+                    const size_t bytes = size_t(g.vocab) * (g.hidden / 256) * spl_gguf_block_bytes(head_type);
+                    cudaFree(e->g_embed); e->g_embed = nullptr;
+                    if (cudaMalloc(reinterpret_cast<void **>(&e->g_embed), bytes) != cudaSuccess) { result = e->fail(SPL_ERR_ALLOCATION_FAILED, "embedding table"); break; }
+                    fill(e->g_embed, g.vocab, g.hidden, head_type, seed ^ 0xE3BEDull);
+                    e->g_embed_format = head_type;
+                } else if (kind == SPL_Q4_HEAD) {
+                    fill(staged, g.vocab, g.hidden, head_type, seed ^ 0x4EADull);
+                    result = upload_gguf_into(e, e->head, 0, g.vocab, g.hidden, head_type, staged, true);
+                }
+                continue;
+            }
+            if (kind >= SPL_Q4_EMBED) continue;
+            const bool full_layer = e->layers[layer].full;
+            if ((kind <= SPL_Q4_OUT && full_layer) || (kind >= SPL_Q4_Q && kind <= SPL_Q4_O && !full_layer)) continue;
+            Placement pl;
+            if ((result = place(e, layer, kind, &pl)) != SPL_OK) break;
+            fill(staged, pl.rows, pl.inner, block_type, seed ^ (uint64_t(layer) * 64 + kind + 1) * 0x9E3779B97F4A7C15ull);
+            result = upload_gguf_into(e, *pl.dst, pl.n0, pl.rows, pl.inner, block_type, staged, true);
+        }
+    cudaStreamSynchronize(e->stream);
+    cudaFree(staged);
+    return result;
 }
 
 static uint64_t fnv1a64(const char *s) {
@@ -1623,7 +1766,7 @@ spl_status spl_op_gemm_gguf(int32_t device, int32_t format, const uint8_t *block
         cudaMemsetAsync(w.blocks, 0, w.device_bytes(), e->stream);           // columns past n are zero blocks: weights 0
         cudaMemcpyAsync(d_native, blocks, w.bytes(), cudaMemcpyHostToDevice, e->stream);
         const size_t items = size_t(n) * (k / 256) * spl_gguf_pieces(format);
-        spl_repack_gguf_kernel<<<int(std::min<size_t>((items + 255) / 256, 16384)), 256, 0, e->stream>>>(d_native, n, k / 256, format, w.blocks);
+        spl_repack_gguf_kernel<<<int(std::min<size_t>((items + 255) / 256, 16384)), 256, 0, e->stream>>>(d_native, n, k / 256, format, w.blocks, 0);
         cudaMemsetAsync(d_act, 0, size_t(row_blocks) * rn * k * 2, e->stream);
         cudaMemsetAsync(d_sums, 0, spl_operand_sums_floats(size_t(row_blocks) * rn, k) * 4, e->stream);
         cudaMemsetAsync(d_flag, 0, 64 * sizeof(int), e->stream);

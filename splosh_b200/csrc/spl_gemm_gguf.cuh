@@ -33,8 +33,9 @@ struct SplGgufDev {
     size_t device_bytes() const { return size_t(tiles) * (k / 256) * spl_gguf_pieces(format) * 2048; }
 };
 
-// Native row-major blocks [rows][k / 256][block bytes] -> the tile layout. One thread a (row, super-block, piece).
-__global__ void spl_repack_gguf_kernel(const unsigned char *__restrict__ native, int rows, int supers, int format, unsigned char *tiles) {
+// Native row-major blocks [rows][k / 256][block bytes] -> the tile layout, as columns [n0, n0 + rows) of a (fused) tensor.
+// One thread a (row, super-block, piece).
+__global__ void spl_repack_gguf_kernel(const unsigned char *__restrict__ native, int rows, int supers, int format, unsigned char *tiles, int n0) {
     const int pieces = spl_gguf_pieces(format), bytes = spl_gguf_block_bytes(format);
     const size_t total = size_t(rows) * supers * pieces;
     for (size_t idx = blockIdx.x * size_t(blockDim.x) + threadIdx.x; idx < total; idx += size_t(gridDim.x) * blockDim.x) {
@@ -48,7 +49,7 @@ __global__ void spl_repack_gguf_kernel(const unsigned char *__restrict__ native,
         } else {
             for (int i = 0; i < 16; ++i) out[i] = src[16 * piece + i];
         }
-        const int tile = row >> 7, col = row & 127;
+        const int tile = (n0 + row) >> 7, col = (n0 + row) & 127;
         unsigned char *dst = tiles + ((size_t(tile) * supers + sb) * pieces + piece) * 2048 + col * 16;
         for (int i = 0; i < 16; ++i) dst[i] = out[i];
     }
@@ -317,5 +318,82 @@ spl_gemm_gguf_tc_kernel(const unsigned char *__restrict__ blocks, const __nv_bfl
     if (warp == 13) {
         spl_tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512) : "memory");
+    }
+}
+
+// ---- a GGUF-weighted model's other pieces -----------------------------------------------------
+// One weight of a native block, exactly (fp32; Sources/SploshQuant/GgufQuant.swift:191-230, the form the reference's
+// embedding gather uses, Sources/Shaders/gguf_formats.h:463-501): block `b` of `format`, element i of its 256.
+__device__ __forceinline__ float spl_gguf_decode_one(const unsigned char *b, int format, int i) {
+    if (format == SPL_GGUF_Q6K) {
+        // ql[128] qh[64] scales[16] d: halves of 128, in each four runs of 32 sharing ql / qh bytes
+        const int half = i >> 7, r = i & 127, run = r >> 5, l = r & 31;
+        const unsigned char lo = b[64 * half + l + ((run & 1) ? 32 : 0)];
+        const int nib = (run < 2) ? (lo & 0xF) : (lo >> 4);
+        const int high = (b[128 + 32 * half + l] >> (2 * run)) & 3;
+        const int q = (nib | (high << 4)) - 32;
+        const float d = __half2float(__ushort_as_half(uint16_t(b[208] | (b[209] << 8))));
+        const int scale = int(reinterpret_cast<const signed char *>(b)[192 + 8 * half + 2 * run + (l >> 4)]);
+        return __fmul_rn(__fmul_rn(d, float(scale)), float(q));
+    }
+    const float d = __half2float(__ushort_as_half(uint16_t(b[0] | (b[1] << 8)))), dmin = __half2float(__ushort_as_half(uint16_t(b[2] | (b[3] << 8))));
+    const unsigned char *sc = b + 4;
+    const int j = i >> 5;      // sub-block of 32
+    int scale, minimum;
+    if (j < 4) { scale = sc[j] & 63; minimum = sc[j + 4] & 63; }
+    else { scale = (sc[j + 4] & 0xF) | ((sc[j - 4] >> 6) << 4); minimum = (sc[j + 4] >> 4) | ((sc[j] >> 6) << 4); }
+    const int pair = i >> 6, l = i & 31, upper = (i >> 5) & 1;
+    int q;
+    if (format == SPL_GGUF_Q5K) {
+        const unsigned char ql = b[48 + 32 * pair + l];
+        q = (upper ? (ql >> 4) : (ql & 0xF)) | (((b[16 + l] >> j) & 1) << 4);
+    } else {
+        const unsigned char ql = b[16 + 32 * pair + l];
+        q = upper ? (ql >> 4) : (ql & 0xF);
+    }
+    return __fsub_rn(__fmul_rn(__fmul_rn(d, float(scale)), float(q)), __fmul_rn(dmin, float(minimum)));      // every product rounded on its own, as the host decoders do
+}
+
+// Embedding rows of a native GGUF table [vocab][hidden / 256] blocks: out[r][:] = row token[r], decoded exactly. Grid (rows).
+__global__ void spl_embed_gguf_kernel(const unsigned char *__restrict__ table, int format, const uint32_t *__restrict__ tokens, float *out, int hidden) {
+    spl_grid_begin();
+    const int row = blockIdx.x, bytes = spl_gguf_block_bytes(format);
+    const unsigned char *src = table + size_t(tokens[row]) * (hidden / 256) * bytes;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) out[size_t(row) * hidden + c] = spl_gguf_decode_one(src + size_t(c >> 8) * bytes, format, c & 255);
+}
+
+// act = bf16(silu(gate) * up) of an unfused gate|up output [rows][2 inter] (gate columns first) as the down projection's
+// operand with its per-64 sums (Sources/Shaders/engine.metal:200-219). Grid (inter / 64, rows), 32 threads.
+__global__ void spl_swiglu_kernel(const float *__restrict__ gate_up, int ld, int inter, SplOperand out) {
+    spl_grid_begin();
+    const int group = blockIdx.x, row = blockIdx.y, lane = threadIdx.x, n = group * 64 + 2 * lane;
+    const float2 g = *reinterpret_cast<const float2 *>(gate_up + size_t(row) * ld + n), u = *reinterpret_cast<const float2 *>(gate_up + size_t(row) * ld + inter + n);
+    const float v0 = spl_bf16_to_float(spl_float_to_bf16(spl_silu_exact(g.x) * u.x)), v1 = spl_bf16_to_float(spl_float_to_bf16(spl_silu_exact(g.y) * u.y));
+    *reinterpret_cast<__half2 *>(reinterpret_cast<__half *>(out.values) + out.at(row, n)) = __halves2half2(__float2half_rn(v0), __float2half_rn(v1));
+    float sum = v0 + v1;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    if (lane == 0) out.put_sum(row, group, sum);
+}
+
+// Seeded synthetic blocks for timing: every byte pseudo-random, then the fp16 fields set so that weights have a
+// deviation of about 0.02 (d and dmin small positive numbers). One thread a block.
+__global__ void spl_synth_gguf_kernel(unsigned char *native, size_t blocks, int format, uint64_t seed) {
+    const int bytes = spl_gguf_block_bytes(format);
+    for (size_t idx = blockIdx.x * size_t(blockDim.x) + threadIdx.x; idx < blocks; idx += size_t(gridDim.x) * blockDim.x) {
+        unsigned char *b = native + idx * bytes;
+        for (int i = 0; i < bytes; i += 2) {
+            const uint64_t z = spl_splitmix_at(seed, idx * 128 + (i >> 1));
+            b[i] = uint8_t(z); if (i + 1 < bytes) b[i + 1] = uint8_t(z >> 8);
+        }
+        const float u = float(spl_splitmix_at(seed ^ 0x5151, idx) >> 40) * (1.0f / 16777216.0f);
+        if (format == SPL_GGUF_Q6K) {
+            const uint16_t d = __half_as_ushort(__float2half_rn(2.0e-5f * (0.5f + u)));     // x scale (|s| < 128) x code (|q| <= 32)
+            b[208] = uint8_t(d); b[209] = uint8_t(d >> 8);
+        } else {
+            const float top = format == SPL_GGUF_Q5K ? 31.0f : 15.0f;
+            const uint16_t d = __half_as_ushort(__float2half_rn(0.07f / (32.0f * top) * (0.5f + u))), m = __half_as_ushort(__float2half_rn(0.035f / 32.0f * (0.5f + u)));
+            b[0] = uint8_t(d); b[1] = uint8_t(d >> 8); b[2] = uint8_t(m); b[3] = uint8_t(m >> 8);
+        }
     }
 }

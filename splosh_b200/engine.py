@@ -173,6 +173,8 @@ def lib():
             "spl_weights_set_q4": (i32, [vp, i32, i32, i32, i32, vp, vp, vp]),
             "spl_weights_set_vector": (i32, [vp, i32, i32, vp, i32]),
             "spl_weights_synthesize_q4": (i32, [vp, u64]),
+            "spl_weights_set_gguf": (i32, [vp, i32, i32, i32, i32, i32, vp]),
+            "spl_weights_synthesize_gguf": (i32, [vp, u64, i32, i32]),
             "spl_step": (i32, [vp, C.POINTER(_Row), i32, C.POINTER(_Stats)]),
             "spl_step_launch": (i32, [vp, C.POINTER(_Row), i32]),
             "spl_step_wait": (i32, [vp, C.POINTER(_Stats)]),
@@ -451,6 +453,26 @@ class Engine:
 
     def synthesize_q4(self, seed):
         self._check(lib().spl_weights_synthesize_q4(self.handle, seed))
+
+    def set_gguf(self, layer, kind, gguf_kind, blocks):
+        """One tensor as native GGUF K-quant super-blocks: blocks uint8 [rows, inner / 256, block bytes]; gguf_kind "Q4_K", "Q5_K" or "Q6_K"."""
+        blocks = np.ascontiguousarray(blocks, np.uint8)
+        self._check(lib().spl_weights_set_gguf(self.handle, layer, Q4_KINDS.index(kind), GGUF_TYPE[gguf_kind], blocks.shape[0], blocks.shape[1] * 256, _ptr(blocks)))
+
+    def synthesize_gguf(self, seed, block_kind="Q5_K", head_kind="Q6_K"):
+        self._check(lib().spl_weights_synthesize_gguf(self.handle, seed, GGUF_TYPE[block_kind], GGUF_TYPE[head_kind]))
+
+    def load_gguf_model(self, model):
+        """Copy every tensor of an object with .gguf(layer, kind) -> (gguf kind, blocks) and .vec(layer, kind)."""
+        for layer in range(self.g.layers):
+            full = layer % 4 == 3
+            for kind in (["q", "k", "v", "o"] if full else ["qkv", "z", "a", "b", "out"]) + ["gate", "up", "down"]:
+                self.set_gguf(layer, kind, *model.gguf(layer, kind))
+            for kind in ["input_norm", "post_norm"] + (["q_norm", "k_norm"] if full else ["conv", "a_log", "dt_bias", "gdn_norm"]):
+                self.set_vector(layer, kind, model.vec(layer, kind))
+        self.set_gguf(-1, "embed", *model.gguf(-1, "embed"))
+        self.set_gguf(-1, "head", *model.gguf(-1, "head"))
+        self.set_vector(-1, "final_norm", model.vec(-1, "final_norm"))
 
     def load_model(self, model):
         """Copy every tensor of an object with .q4(layer, kind) / .vec(layer, kind) (the synthetic model of the tests)."""

@@ -34,10 +34,14 @@ def assert_tables_equal(mine, ref):
 class Pair:
     """The CUDA engine and the CPU oracle side by side on the same seeded model."""
 
-    def __init__(self, geometry, config, seed=0x5EED6D17, gpu=True):
+    def __init__(self, geometry, config, seed=0x5EED6D17, gpu=True, gguf=None):
+        """gguf: None for the MLX affine-4 model, or (block kind, head kind), e.g. ("Q5_K", "Q6_K"), for the same model
+        re-quantised to GGUF K-quants on both sides."""
         self.g, self.config = geometry, config
         og = to_oracle_geometry(geometry)
         self.model = O.Model(og, seed)
+        if gguf:
+            self.model.to_gguf(*gguf)
         self.ohost = T.Host(max_slots=config.max_slots, max_rows=config.max_rows, kv_pages=config.kv_pages,
                             max_context=config.max_context, state_units=config.state_units or None,
                             max_logit_rows=config.max_logit_rows or None, vocab=geometry.vocab, kv_heads=geometry.kv_heads,
@@ -46,7 +50,10 @@ class Pair:
         self.engine = None
         if gpu:
             self.engine = S.Engine(geometry, config)
-            self.engine.load_model(self.model)
+            if gguf:
+                self.engine.load_gguf_model(self.model)
+            else:
+                self.engine.load_model(self.model)
 
     def step(self, rows, taps=False):
         """Run one step on both. Returns (gpu logits, oracle logits[, gpu taps, oracle taps])."""

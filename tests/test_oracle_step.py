@@ -68,6 +68,29 @@ def test_verify_rows_equal_ordinary_rows_and_partial_acceptance_replays(toks):
     assert np.abs(a - b).max() < 2e-2 and np.argmax(a) == np.argmax(b)
 
 
+def test_deferred_norm_contract_is_the_plain_norm_up_to_rounding(toks):
+    """The deferred form (operand bf16(h w), sums scaled by the row's rsqrt afterwards: Sources/Shaders/engine_na.metal:365-415,
+    Sources/SploshRuntime/Engine.swift:1439-1451) and the plain RMSNorm (Sources/Shaders/engine.metal:159-178) differ only in
+    where the bf16 rounding of the operand falls: same arg-max, logits within the step's tolerance."""
+    import oracle.oracle as O
+    g = small_geometry()
+    cfg = S.EngineConfig(max_slots=2, max_rows=64, kv_pages=8, max_context=1024)
+    rows = [S.EngineRow(0, toks[i], i, True) for i in range(24)]
+    results = []
+    try:
+        for deferred in (True, False):
+            O.set_norm_contract(deferred)
+            pair = Pair(g, cfg, gpu=False)
+            _, logits = pair.step(rows)
+            results.append(logits)
+    finally:
+        O.set_norm_contract(True)
+    a, b = results
+    assert np.abs(a - b).max() > 0.0                      # the switch does something
+    assert np.abs(a - b).max() < 2e-2 * max(1.0, np.abs(a).max())
+    assert (np.argmax(a, axis=1) == np.argmax(b, axis=1)).mean() > 0.9
+
+
 def test_sessions_do_not_interact(toks):
     """Rows of different slots share only the weights: a session's logits are the same alone or packed
     with others (what makes sharding by session exact)."""
@@ -97,3 +120,22 @@ def test_synthetic_weights_have_the_stated_distribution(oracle):
     u = np.array([lib.orc_uniform_at(777, i) for i in range(5000)])
     assert 0 <= u.min() and u.max() < 1 and abs(u.mean() - 0.5) < 0.02
     assert np.array_equal(synthetic.uniform_at(777, np.arange(5000)), u.astype(np.float32))
+
+
+def test_gguf_weighted_oracle_stays_close_to_the_affine_model(toks):
+    """The same synthetic model re-quantised to Q5_K blocks with a Q6_K embedding and head (the build's own encoder: parity is
+    defined on the decoded blocks) gives logits close to the MLX affine-4 model's: the GGUF branch of the oracle's GEMM and its
+    exact embedding decode are wired to the right tensors."""
+    import oracle.oracle as O
+    g = small_geometry()
+    cfg = S.EngineConfig(max_slots=2, max_rows=64, kv_pages=8, max_context=1024)
+    rows = [S.EngineRow(0, toks[i], i, True) for i in range(16)]
+    O.set_norm_contract(False)
+    try:
+        _, plain = Pair(g, cfg, gpu=False).step(rows)
+        _, gguf = Pair(g, cfg, gpu=False, gguf=("Q5_K", "Q6_K")).step(rows)
+    finally:
+        O.set_norm_contract(True)
+    assert np.abs(plain - gguf).max() > 0.0
+    # Re-quantising 4-bit weights moves every logit of a random model a little: the two stay strongly correlated.
+    assert np.corrcoef(plain.ravel(), gguf.ravel())[0, 1] > 0.9
