@@ -69,9 +69,9 @@ __host__ __device__ constexpr size_t spl_operand_sums_floats(size_t rows_padded,
 struct SplOperand {
     __nv_bfloat16 *values;      // 16-bit cells (fp16 bits of the bf16-rounded values)
     float *sums;               // tiles of split means, see put_sum
-    int rn, blocks;            // rows per block, row blocks
+    int rn, blocks;            // rows per block (16, 32, 64 or 128: a power of two), row blocks
     __device__ __forceinline__ size_t at(int row, int k) const {
-        const int g = k >> 6, kk = k & 63, rb = row / rn, r = row % rn;
+        const int g = k >> 6, kk = k & 63, rb = row >> (31 - __clz(rn)), r = row & (rn - 1);
         return (size_t(g) * blocks + rb) * (size_t(rn) * 64) + size_t(r >> 3) * 512 + (r & 7) * 64 + (((kk >> 3) ^ (r & 7)) << 3) + (kk & 7);
     }
     // The group's sum as the B operand of the GEMM's second term: (hi, lo, hi, lo) with hi + lo = sum / 64 in two fp16
@@ -82,7 +82,7 @@ struct SplOperand {
         const __half hi = __float2half_rn(mean), lo = __float2half_rn(mean - __half2float(hi));
         const __half2 pair = __halves2half2(hi, lo);
         const uint32_t bits = *reinterpret_cast<const uint32_t *>(&pair);
-        const int rb = row / rn, r = row % rn, kk = 4 * (g & 15);
+        const int rb = row >> (31 - __clz(rn)), r = row & (rn - 1), kk = 4 * (g & 15);
         __half *tile = reinterpret_cast<__half *>(sums) + (size_t(g >> 4) * blocks + rb) * (size_t(rn) * 64);
         *reinterpret_cast<uint2 *>(tile + size_t(r >> 3) * 512 + (r & 7) * 64 + (((kk >> 3) ^ (r & 7)) << 3) + (kk & 7)) = make_uint2(bits, bits);
     }
