@@ -30,6 +30,7 @@ SESSIONS, BLOCK = 8, 8
 CONTEXT_LOW, CONTEXT_HIGH = 36 * 1024, 42 * 1024
 PREFILL_PROMPT, PREFILL_CHUNK = 54500, 2048        # BASELINE configuration 2: one 54.5K-token prompt in 2,048-row chunks
 RIDER_PROMPT, RIDER_ROWS = 21000, 64               # configuration 3's prefilling session: 64 prompt rows ride in every 64-row decode step
+GGUF_CONTEXT, GGUF_BLOCK = 171000, 16              # configuration 4: one session at 171K context verifying 16-token blocks on GGUF weights
 # DRAM bytes the GEMM kernel moves per algorithmic byte: measured per tensor shape with ncu (reads + writes), 15.06 GB
 # for the 14.41 GB of a full step's 257 launches.
 GEMM_DRAM_PER_ALGORITHMIC_BYTE = 1.044
@@ -220,11 +221,12 @@ def main():
     extras = not args.no_prefill
     prompt_tokens = int(PREFILL_PROMPT * args.context_scale)
     rider_prompt = int(RIDER_PROMPT * args.context_scale)
+    gguf_context = int(GGUF_CONTEXT * args.context_scale)
     pages = sum((c + BLOCK * steps_total) // 256 + 2 for c in ctx) + (prompt_tokens // 256 + 4 if extras else 0)
     # The engine's span target (how many scan blocks a step should make; the reference tunes it to its GPU, 592 there): one
     # scan block fills an SM here; 608 gives this workload 19 spans of 9 pages, which packs the 148 SMs best.
     cfg = S.EngineConfig(max_slots=SESSIONS + 1, max_rows=max(SESSIONS * BLOCK + RIDER_ROWS, PREFILL_CHUNK) if extras else SESSIONS * BLOCK, kv_pages=pages,
-                         max_context=max(max(ctx) + BLOCK * steps_total, prompt_tokens if extras else 0) + 256, device=local, span_target=SPAN_TARGET,
+                         max_context=max(max(ctx) + BLOCK * steps_total, (prompt_tokens if extras else 0), (gguf_context + GGUF_BLOCK * (args.steps + 4) if extras else 0)) + 256, device=local, span_target=SPAN_TARGET,
                          max_logit_rows=SESSIONS * BLOCK + 8)
     engine = S.Engine(g, cfg)
     from splosh_b200 import synthetic
@@ -383,22 +385,32 @@ def main():
                   "tok_per_s": rows_per_step * args.steps / float(slowest[0])}
     gguf = None
     if extras and world == 1 and g.hidden % 256 == 0:
-        # BASELINE's GGUF configuration: the same 64-row step on a Q5_K_M-style model (Q5_K blocks, Q6_K embedding and head,
-        # pseudo-random blocks made on the device). One way: the MLX tensors are freed as the GGUF ones arrive, so this
-        # comes last.
+        # Configuration 4: Q5_K_M-style weights (Q5_K blocks, Q6_K embedding and head; pseudo-random blocks made on the device),
+        # one session at 171K context verifying 16-token blocks. One way: the MLX tensors are freed as the GGUF ones arrive,
+        # so this comes last. The session's pages hold synthetic KV, its state is seeded.
+        for s_ in range(SESSIONS + 1):
+            engine.reset_slot(s_)
+        engine.step([S.EngineRow(0, 1000, gguf_context - 1, False)])
+        engine.debug_fill_kv(0); engine.debug_fill_state(0, 0x6660)
         engine.synthesize_gguf(WEIGHT_SEED, "Q5_K", "Q6_K")
-        seconds = 0.0
+        at, seconds = gguf_context, 0.0
         for n in range(args.steps + 2):
-            stats, _ = one_step(step_index, True); step_index += 1
+            rows = [S.EngineRow(0, int(splitmix_at(TOKEN_SEED ^ 0x66, at + i) % g.vocab), at + i, True, True) for i in range(GGUF_BLOCK)]
+            stats = engine.step(rows)
+            engine.argmax(248077 if g.vocab == 248320 else g.vocab)
+            at += GGUF_BLOCK
+            engine.accept_verify(0, GGUF_BLOCK, at)
             if n >= 2:
                 seconds += stats.gpu_seconds
         wcount, _ = weights_per_step(g)
         head_weights = g.vocab * g.hidden
         gguf_bytes = (wcount - head_weights) * 176 / 256 + head_weights * 210 / 256
-        gguf = {"workload": "the same 64-row step, every block tensor Q5_K, embedding and head Q6_K (GGUF super-blocks), plain norms, unfused SiLU gate",
-                "ms_per_step": 1000.0 * seconds / args.steps, "tok_per_s": rows_per_step * args.steps / seconds, "weights_gb": gguf_bytes / 1e9,
-                "weights_gbs": gguf_bytes / (seconds / args.steps) / 1e9}
-
+        n_full = g.layers // 4
+        kv_bytes = gguf_context * n_full * 2 * g.kv_heads * (g.head_dim + 4)
+        gguf = {"workload": f"one session at {gguf_context} tokens of context, {GGUF_BLOCK}-row verify blocks, every block tensor Q5_K, embedding and head Q6_K "
+                            "(GGUF super-blocks), plain norms, unfused SiLU gate",
+                "ms_per_step": 1000.0 * seconds / args.steps, "tok_per_s": GGUF_BLOCK * args.steps / seconds, "weights_gb": gguf_bytes / 1e9, "kv_gb": kv_bytes / 1e9,
+                "hbm_gbs": (gguf_bytes + kv_bytes) / (seconds / args.steps) / 1e9}
     if rank == 0:
         peak, peak_source = measured_peak_gbs()
         gemm = prof["gemm_q4"]

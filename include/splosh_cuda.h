@@ -278,6 +278,9 @@ spl_status spl_debug_taps(spl_engine *engine, int32_t enabled);
 /* Test switch: with `enabled` 0 the following steps do not store their rows' keys and values, so the attention scan
  * reads the pool exactly as a test wrote it, the rows' own positions included (the scenes of
  * Tests/SploshOracleTests/AttentionScanCandidateTests.swift:85-200 place large keys there). 1 restores the store. */
+/* Tests: ordinary runs of at least `rows` rows (>= 64; default 512) take the chunked gated-delta scan instead of the
+ * per-token kernel. */
+spl_status spl_debug_gdn_chunk_min(spl_engine *engine, int32_t rows);
 spl_status spl_debug_kv_store(spl_engine *engine, int32_t enabled);
 /* Every wait inside a kernel (a role of a block waiting for another role of the same block) gives up after a time
  * budget, 250 ms unless changed here, and the step then returns SPL_ERR_TIMEOUT with the engine still usable.

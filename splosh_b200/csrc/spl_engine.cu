@@ -72,6 +72,7 @@ struct spl_engine {
     float *xn_squares = nullptr;       // [row][hidden / 64] squares of the residual stream, left by the GEMM that feeds a deferred norm
     float *slots = nullptr;            // partial sums of the GEMM tiles that several blocks share
     size_t slot_floats = 0;
+    int gdn_chunk_min = SPL_GDN_CHUNK_MIN;      // ordinary runs at least this long take the chunked gated-delta scan (spl_debug_gdn_chunk_min)
     int sms = 148;
     int rows_padded = 0, logit_rows_padded = 0;
     int *tc_error = nullptr;
@@ -443,7 +444,7 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
     std::vector<uint32_t> chunk_runs, chunks;
     for (uint32_t r = 0; r < t->run_count; ++r) {
         const uint32_t length = t->runs[r * 3 + 2];
-        if (t->run_info[r * 2] != 0 || length < SPL_GDN_CHUNK_MIN || e->state.empty()) continue;
+        if (t->run_info[r * 2] != 0 || int(length) < e->gdn_chunk_min || e->state.empty()) continue;
         const uint32_t index = uint32_t(chunk_runs.size() / 4);
         chunk_runs.insert(chunk_runs.end(), {t->runs[r * 3], t->runs[r * 3 + 1], length, t->run_info[r * 2 + 1]});
         for (uint32_t first = 0, n = 0; first < length; first += SPL_GDN_CHUNK, ++n)
@@ -502,7 +503,7 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
         if (!L.full) {
             SplGdnParams p;
             p.rows = R; p.runs = int(t->run_count); p.channels = sh.C; p.key_heads = g.gdn_key_heads; p.value_heads = g.gdn_value_heads;
-            p.head_dim = g.gdn_head_dim; p.proj_ld = L.in_proj.ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps; p.chunk_min = chunked_runs > 0 ? SPL_GDN_CHUNK_MIN : 0;
+            p.head_dim = g.gdn_head_dim; p.proj_ld = L.in_proj.ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps; p.chunk_min = chunked_runs > 0 ? e->gdn_chunk_min : 0;
             profile_begin(e, KLASS_GDN, 0);
             launch_step(spl_gdn_conv_kernel, dim3(dim3((sh.C + 255) / 256, t->run_count)), dim3(256), 0, e->stream, 
                 e->proj, L.vec[SPL_VEC_CONV], e->conv[linear_index], e->d_runs, e->d_row_read, e->d_row_write, e->gdn_act, p);
@@ -820,7 +821,7 @@ spl_status create(const spl_geometry *gp, const spl_config *cp, spl_engine *e) {
                     e->slot_floats = std::max(e->slot_floats, gemm_slot_floats(*u.w, e->sms, rn, rbs, u.emit, u.whole));
     }
     if ((s = device_alloc(e, &e->slots, e->slot_floats, &e->scratch_bytes)) != SPL_OK) return s;
-    if (R >= SPL_GDN_CHUNK_MIN && !e->state.empty()) {
+    if (R >= SPL_GDN_CHUNK && !e->state.empty()) {
         e->gdn_chunks_max = R / SPL_GDN_CHUNK + e->c.max_slots;
         if ((s = device_alloc(e, &e->gdn_records, size_t(e->gdn_chunks_max) * g.gdn_value_heads * SPL_GDN_REC_FLOATS, &e->scratch_bytes)) != SPL_OK) return s;
         if ((s = device_alloc(e, &e->gdn_o_raw, size_t(R) * sh.VD, &e->scratch_bytes)) != SPL_OK) return s;
@@ -1313,6 +1314,12 @@ spl_status spl_debug_wait_budget(spl_engine *e, int64_t nanoseconds) {
 spl_status spl_debug_drop_weight_stage(spl_engine *e, int32_t stage) {
     if (!e) return SPL_ERR_INVALID_ARGUMENT;
     g_drop_weight_stage = stage;
+    return SPL_OK;
+}
+
+spl_status spl_debug_gdn_chunk_min(spl_engine *e, int32_t rows) {
+    if (!e || rows < SPL_GDN_CHUNK) return SPL_ERR_INVALID_ARGUMENT;
+    e->gdn_chunk_min = rows;
     return SPL_OK;
 }
 

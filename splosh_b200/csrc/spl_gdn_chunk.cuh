@@ -25,9 +25,12 @@
 #include "spl_gdn.cuh"
 
 #define SPL_GDN_CHUNK 64           // tokens per chunk
-#define SPL_GDN_CHUNK_MIN 64       // ordinary runs at least this long take the chunked path
+#define SPL_GDN_CHUNK_MIN 512      // ordinary runs at least this long take the chunked path by default: below about five chunks the
+                                   // per-token kernel is the faster one (a chunk costs it 83 us; the three kernels here 150 us + 50 us a chunk)
 #define SPL_GDN_SLICES 8           // slices of the value dimension in the scan (16 values each)
 #define SPL_GDN_SLICE (SPL_GDN_D / SPL_GDN_SLICES)
+#define SPL_GDN_LD (SPL_GDN_D + 4)   // floats between rows of D in shared memory
+#define SPL_GDN_PLD (SPL_GDN_CHUNK + 4)   // and between rows of a chunk x chunk matrix
 // Floats of the per-(chunk, value head) record the prepare kernel leaves for the scan.
 #define SPL_GDN_REC_W 0                                             // [64][128]  T diag(b g) K^
 #define SPL_GDN_REC_UV (SPL_GDN_REC_W + 64 * 128)                   // [64][128]  T diag(b) V
@@ -48,11 +51,11 @@ __global__ void __launch_bounds__(256)
 spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restrict__ proj, const uint16_t *__restrict__ a_log,
                              const uint16_t *__restrict__ dt_bias, SplGdnChunkTables tables, float *records, SplGdnParams p) {
     spl_grid_begin();
-    constexpr int D = SPL_GDN_D, C = SPL_GDN_CHUNK;
+    constexpr int D = SPL_GDN_D, C = SPL_GDN_CHUNK, LD = SPL_GDN_LD;      // shared rows of D floats are LD apart: rows read side by side fall in different banks
     extern __shared__ __align__(16) float spl_gdn_chunk_smem[];
-    float *kh = spl_gdn_chunk_smem;            // [C][D] k^
-    float *x = kh + C * D;                      // [C][D] q^, then b g k^, then b v
-    float *am = x + C * D;                      // [C][C] A, then P
+    float *kh = spl_gdn_chunk_smem;            // [C][LD] k^
+    float *x = kh + C * LD;                     // [C][LD] q^, then b g k^, then b v
+    float *am = x + C * LD;                     // [C][C] A, then P
     float *tm = am + C * C;                     // [C][C + 1] T (rows padded against bank conflicts)
     float *g = tm + C * (C + 1);                // [C] log of the running decay product
     float *beta = g + C;                        // [C]
@@ -72,12 +75,12 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
             qv = *reinterpret_cast<const float4 *>(row + hk * D + i4 * 4);
             kv = *reinterpret_cast<const float4 *>(row + KH * D + hk * D + i4 * 4);
         }
-        *reinterpret_cast<float4 *>(kh + tt * D + i4 * 4) = kv;
-        *reinterpret_cast<float4 *>(x + tt * D + i4 * 4) = qv;
+        *reinterpret_cast<float4 *>(kh + tt * LD + i4 * 4) = kv;
+        *reinterpret_cast<float4 *>(x + tt * LD + i4 * 4) = qv;
     }
     __syncthreads();
     for (int tt = warp; tt < C; tt += 8) {
-        const float4 qv = *reinterpret_cast<const float4 *>(x + tt * D + lane * 4), kv = *reinterpret_cast<const float4 *>(kh + tt * D + lane * 4);
+        const float4 qv = *reinterpret_cast<const float4 *>(x + tt * LD + lane * 4), kv = *reinterpret_cast<const float4 *>(kh + tt * LD + lane * 4);
         const float qq = spl_warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
         const float kk = spl_warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
         if (lane == 0) {
@@ -96,7 +99,7 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
     }
     __syncthreads();
     if (tid == 0) { float run = 0.0f; for (int tt = 0; tt < C; ++tt) { run += g[tt]; g[tt] = run; } }
-    for (int idx = tid; idx < C * D; idx += 256) { const int tt = idx / D; kh[idx] *= scal[tt * 2 + 1]; x[idx] *= scal[tt * 2]; }
+    for (int idx = tid; idx < C * D; idx += 256) { const int tt = idx / D, at = tt * LD + idx % D; kh[at] *= scal[tt * 2 + 1]; x[at] *= scal[tt * 2]; }
     __syncthreads();
     const float g_end = g[C - 1];      // rows past the chunk's end have log decay 0, so this is the last token's
     // A[t][s] = b_t (g_t / g_s) (k^_t . k^_s) below the diagonal; P[t][s] = (g_t / g_s) (q^_t . k^_s) on and below it (to the record).
@@ -104,7 +107,7 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
         const int t = idx / C, s = idx % C;
         float ka = 0.0f, qa = 0.0f;
         if (s <= t) {
-            const float4 *kt = reinterpret_cast<const float4 *>(kh + t * D), *ks = reinterpret_cast<const float4 *>(kh + s * D), *qt = reinterpret_cast<const float4 *>(x + t * D);
+            const float4 *kt = reinterpret_cast<const float4 *>(kh + t * LD), *ks = reinterpret_cast<const float4 *>(kh + s * LD), *qt = reinterpret_cast<const float4 *>(x + t * LD);
 #pragma unroll 8
             for (int i = 0; i < D / 4; ++i) {
                 const float4 a4 = kt[i], b4 = ks[i], c4 = qt[i];
@@ -118,19 +121,23 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
     }
     // g_t q^_t and (g_C / g_s) k^_s to the record while q^ is still in shared memory.
     for (int idx = tid; idx < C * D; idx += 256) {
-        const int tt = idx / D;
-        rec[SPL_GDN_REC_QG + idx] = x[idx] * expf(g[tt]);
-        rec[SPL_GDN_REC_KD + idx] = kh[idx] * expf(g_end - g[tt]);
+        const int tt = idx / D, at = tt * LD + idx % D;
+        rec[SPL_GDN_REC_QG + idx] = x[at] * expf(g[tt]);
+        rec[SPL_GDN_REC_KD + idx] = kh[at] * expf(g_end - g[tt]);
     }
     if (tid == 0) rec[SPL_GDN_REC_GC] = expf(g_end);
     __syncthreads();
-    // T = (I + A)^-1 by forward substitution, a thread a column: T[t][c] = [t == c] - sum_{s<t} A[t][s] T[s][c].
-    if (tid < C) {
-        const int c = tid;
+    // T = (I + A)^-1 by forward substitution, four threads a column: T[t][c] = [t == c] - sum_{s<t} A[t][s] T[s][c], the sum
+    // in four interleaved parts added in one fixed order. A column's threads sit in one warp.
+    {
+        const int c = tid >> 2, part = tid & 3;
         for (int t = 0; t < C; ++t) {
-            float acc = t == c ? 1.0f : 0.0f;
-            for (int s = c; s < t; ++s) acc -= am[t * C + s] * tm[s * (C + 1) + c];      // T is lower triangular: T[s][c] = 0 for s < c
-            tm[t * (C + 1) + c] = t >= c ? acc : 0.0f;
+            float acc = 0.0f;
+            for (int s = c + part; s < t; s += 4) acc -= am[t * C + s] * tm[s * (C + 1) + c];      // T is lower triangular: T[s][c] = 0 for s < c
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (part == 0) tm[t * (C + 1) + c] = t > c ? acc : t == c ? 1.0f : 0.0f;
+            __syncwarp();
         }
     }
     __syncthreads();
@@ -141,14 +148,14 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
             float4 v = make_float4(0, 0, 0, 0);
             if (pass == 0) {
                 const float f = beta[tt] * expf(g[tt]);
-                const float4 k4 = *reinterpret_cast<const float4 *>(kh + tt * D + i4 * 4);
+                const float4 k4 = *reinterpret_cast<const float4 *>(kh + tt * LD + i4 * 4);
                 v = make_float4(k4.x * f, k4.y * f, k4.z * f, k4.w * f);
             } else if (tt < int(count)) {
                 const float f = beta[tt];
                 const float4 v4 = *reinterpret_cast<const float4 *>(act + size_t(first + tt) * p.channels + 2 * KH * D + h * D + i4 * 4);
                 v = make_float4(v4.x * f, v4.y * f, v4.z * f, v4.w * f);
             }
-            *reinterpret_cast<float4 *>(x + tt * D + i4 * 4) = v;
+            *reinterpret_cast<float4 *>(x + tt * LD + i4 * 4) = v;
         }
         __syncthreads();
         // out[t][i] = sum_{s<=t} T[t][s] x[s][i]: a thread four rows t and four columns i (rows t, t + 16, t + 32, t + 48: even work).
@@ -160,7 +167,7 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
                 for (int r = 0; r < 4; ++r) acc[r] = make_float4(0, 0, 0, 0);
                 const int t_max = tg + 8 * (4 * round + 3);
                 for (int s = 0; s <= t_max; ++s) {
-                    const float4 xv = *reinterpret_cast<const float4 *>(x + s * D + ig * 4);
+                    const float4 xv = *reinterpret_cast<const float4 *>(x + s * LD + ig * 4);
 #pragma unroll
                     for (int r = 0; r < 4; ++r) {
                         const int t = tg + 8 * (4 * round + r);
@@ -179,7 +186,7 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
     }
 }
 __host__ __device__ constexpr size_t spl_gdn_chunk_prepare_smem() {
-    return sizeof(float) * (2 * SPL_GDN_CHUNK * SPL_GDN_D + SPL_GDN_CHUNK * SPL_GDN_CHUNK + SPL_GDN_CHUNK * (SPL_GDN_CHUNK + 1) + 4 * SPL_GDN_CHUNK);
+    return sizeof(float) * (2 * SPL_GDN_CHUNK * SPL_GDN_LD + SPL_GDN_CHUNK * SPL_GDN_CHUNK + SPL_GDN_CHUNK * (SPL_GDN_CHUNK + 1) + 4 * SPL_GDN_CHUNK);
 }
 
 // Grid (value heads, chunked runs, SPL_GDN_SLICES), 256 threads. The run's chunks in order over one slice of the value
@@ -188,12 +195,12 @@ __global__ void __launch_bounds__(256)
 spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables tables, float *state, const float *__restrict__ journal,
                           float *o_raw, SplGdnParams p) {
     spl_grid_begin();
-    constexpr int D = SPL_GDN_D, C = SPL_GDN_CHUNK, SL = SPL_GDN_SLICE;
+    constexpr int D = SPL_GDN_D, C = SPL_GDN_CHUNK, SL = SPL_GDN_SLICE, LD = SPL_GDN_LD, PLD = SPL_GDN_PLD;
     extern __shared__ __align__(16) float spl_gdn_scan_smem[];
-    float *w_s = spl_gdn_scan_smem;           // [C][D] W, later Kd
-    float *q_s = w_s + C * D;                  // [C][D] g q^
-    float *p_s = q_s + C * D;                  // [C][C] P
-    float *s_s = p_s + C * C;                  // [SL][D + 4] the slice of the state (rows padded)
+    float *w_s = spl_gdn_scan_smem;           // [C][LD] W, later Kd
+    float *q_s = w_s + C * LD;                 // [C][LD] g q^
+    float *p_s = q_s + C * LD;                 // [C][PLD] P
+    float *s_s = p_s + C * PLD;                // [SL][D + 4] the slice of the state (rows padded)
     float *u_s = s_s + SL * (D + 4);           // [C][SL] U
     const int h = blockIdx.x, run = blockIdx.y, slice = blockIdx.z, tid = threadIdx.x;
     const int VH = p.value_heads;
@@ -226,10 +233,12 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
         const float *rec = records + (size_t(chunk) * VH + h) * SPL_GDN_REC_FLOATS;
         const uint32_t first = tables.chunks[chunk * 4 + 1], count = tables.chunks[chunk * 4 + 2];
         for (int idx = tid; idx < C * (D / 4); idx += 256) {
-            reinterpret_cast<float4 *>(w_s)[idx] = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_W)[idx];
-            reinterpret_cast<float4 *>(q_s)[idx] = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_QG)[idx];
+            const int at = (idx / (D / 4)) * LD + (idx % (D / 4)) * 4;
+            *reinterpret_cast<float4 *>(w_s + at) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_W)[idx];
+            *reinterpret_cast<float4 *>(q_s + at) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_QG)[idx];
         }
-        for (int idx = tid; idx < C * (C / 4); idx += 256) reinterpret_cast<float4 *>(p_s)[idx] = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_P)[idx];
+        for (int idx = tid; idx < C * (C / 4); idx += 256)
+            *reinterpret_cast<float4 *>(p_s + (idx / (C / 4)) * PLD + (idx % (C / 4)) * 4) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_P)[idx];
         const float g_end = rec[SPL_GDN_REC_GC];
         __syncthreads();
         // U[t][j] = Uv[t][j] - sum_i W[t][i] S[j][i];  O0[t][j] = sum_i (g q^)[t][i] S[j][i]
@@ -240,7 +249,7 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
 #pragma unroll
             for (int r = 0; r < 4; ++r) o[r] = 0.0f;
             for (int i = 0; i < D; i += 4) {
-                const float4 wv = *reinterpret_cast<const float4 *>(w_s + tq * D + i), qv = *reinterpret_cast<const float4 *>(q_s + tq * D + i);
+                const float4 wv = *reinterpret_cast<const float4 *>(w_s + tq * LD + i), qv = *reinterpret_cast<const float4 *>(q_s + tq * LD + i);
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const float4 sv = *reinterpret_cast<const float4 *>(s_s + (jq * 4 + r) * (D + 4) + i);
@@ -253,13 +262,14 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
         __syncthreads();
         // O[t][j] = O0 + sum_{s<=t} P[t][s] U[s][j]; meanwhile the record's Kd replaces W in shared memory.
         for (int s = 0; s <= tq; ++s) {
-            const float w = p_s[tq * C + s];
+            const float w = p_s[tq * PLD + s];
             const float4 uv = *reinterpret_cast<const float4 *>(u_s + s * SL + jq * 4);
             o[0] += w * uv.x; o[1] += w * uv.y; o[2] += w * uv.z; o[3] += w * uv.w;
         }
         if (tq < int(count))
             *reinterpret_cast<float4 *>(o_raw + size_t(first + tq) * (size_t(VH) * D) + h * D + slice * SL + jq * 4) = make_float4(o[0], o[1], o[2], o[3]);
-        for (int idx = tid; idx < C * (D / 4); idx += 256) reinterpret_cast<float4 *>(w_s)[idx] = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_KD)[idx];
+        for (int idx = tid; idx < C * (D / 4); idx += 256)
+            *reinterpret_cast<float4 *>(w_s + (idx / (D / 4)) * LD + (idx % (D / 4)) * 4) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_KD)[idx];
         __syncthreads();
         // S[j][i] = g_C S[j][i] + sum_s U[s][j] Kd[s][i]: a thread one value row j and eight columns i.
         {
@@ -269,7 +279,7 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
             for (int e = 0; e < 8; ++e) acc[e] = g_end * s_s[j * (D + 4) + i0 + e];
             for (int s = 0; s < C; ++s) {
                 const float us = u_s[s * SL + j];
-                const float4 k0 = *reinterpret_cast<const float4 *>(w_s + s * D + i0), k1 = *reinterpret_cast<const float4 *>(w_s + s * D + i0 + 4);
+                const float4 k0 = *reinterpret_cast<const float4 *>(w_s + s * LD + i0), k1 = *reinterpret_cast<const float4 *>(w_s + s * LD + i0 + 4);
                 acc[0] += us * k0.x; acc[1] += us * k0.y; acc[2] += us * k0.z; acc[3] += us * k0.w;
                 acc[4] += us * k1.x; acc[5] += us * k1.y; acc[6] += us * k1.z; acc[7] += us * k1.w;
             }
@@ -284,7 +294,7 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
     }
 }
 __host__ __device__ constexpr size_t spl_gdn_chunk_scan_smem() {
-    return sizeof(float) * (2 * SPL_GDN_CHUNK * SPL_GDN_D + SPL_GDN_CHUNK * SPL_GDN_CHUNK + SPL_GDN_SLICE * (SPL_GDN_D + 4) + SPL_GDN_CHUNK * SPL_GDN_SLICE);
+    return sizeof(float) * (2 * SPL_GDN_CHUNK * SPL_GDN_LD + SPL_GDN_CHUNK * SPL_GDN_PLD + SPL_GDN_SLICE * (SPL_GDN_D + 4) + SPL_GDN_CHUNK * SPL_GDN_SLICE);
 }
 
 // Gated RMSNorm of whole heads and the bf16 operand of the output projection with its per-64 sums

@@ -195,6 +195,7 @@ def lib():
             "spl_debug_read": (i32, [vp, i32, i32, vp, C.c_size_t]),
             "spl_debug_taps": (i32, [vp, i32]),
             "spl_debug_kv_store": (i32, [vp, i32]),
+            "spl_debug_gdn_chunk_min": (i32, [vp, i32]),
             "spl_debug_wait_budget": (i32, [vp, C.c_int64]),
             "spl_debug_drop_weight_stage": (i32, [vp, i32]),
             "spl_gemm_q4_static_status": (i32, [vp]),
@@ -619,6 +620,10 @@ class Engine:
 
     def debug_kv_store(self, enabled=True):
         self._check(lib().spl_debug_kv_store(self.handle, int(enabled)))
+
+    def debug_gdn_chunk_min(self, rows):
+        """Ordinary runs of at least `rows` rows (default 512) take the chunked gated-delta scan."""
+        self._check(lib().spl_debug_gdn_chunk_min(self.handle, int(rows)))
 
     def debug_profile(self, enabled=True):
         self._check(lib().spl_debug_profile(self.handle, int(enabled)))

@@ -12,7 +12,7 @@ import oracle.oracle as O
 
 pytestmark = pytest.mark.gpu
 
-LOGIT_TOL = 5e-2      # the MLX-weighted step's tolerance (tests/test_gpu_step.py)
+LOGIT_TOL = 3e-2      # the MLX-weighted step's tolerance (tests/test_gpu_step.py)
 
 
 def geometry():

@@ -47,6 +47,7 @@ def test_the_chunked_scan_equals_the_per_token_kernel_on_the_same_tokens():
         e.step([S.EngineRow(0, toks[i], i, False) for i in range(20)])
         e.step([S.EngineRow(0, toks[20 + i], 20 + i, True, True) for i in range(5)])
         e.accept_verify(0, 3, 23)                      # three journal entries wait for the next run
+    a.debug_gdn_chunk_min(64)                          # the long step takes the chunked scan whatever the default threshold
     a.step([S.EngineRow(0, toks[23 + i], 23 + i, i == 699) for i in range(700)])
     fed = 0
     while fed < 700:
@@ -73,6 +74,7 @@ def test_a_prompt_chunk_rides_with_verify_blocks_on_the_27b_shape():
     g = S.b27_geometry(layers=4, vocab=32768)
     pair = Pair(g, S.EngineConfig(max_slots=3, max_rows=160, kv_pages=8, max_context=512, max_logit_rows=24))
     toks = tokens_for(0xC0FFEE00, 400, g.vocab)
+    pair.engine.debug_gdn_chunk_min(64)                # the 136-row run takes the chunked scan (by default only runs of 512 rows and more do)
     pair.step([S.EngineRow(s, toks[50 * s + i], i, False) for s in range(2) for i in range(6 + s)])
     rows = [S.EngineRow(s, toks[100 + 10 * s + i], 6 + s + i, True, True) for s in range(2) for i in range(8)]
     rows += [S.EngineRow(2, toks[200 + i], i, i == 135) for i in range(136)]

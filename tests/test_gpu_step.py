@@ -4,7 +4,7 @@ seeded synthetic model and rows.
 Gates. Tables (rows, runs, pages, attention blocks, spans) bit-exact. Greedy and accepted-draft
 token ids equal to the oracle's. Logits: max |gpu - oracle| <= LOGIT_TOL.
 
-Why LOGIT_TOL is 5e-2 and not smaller: every GEMM input is rounded to bf16. The two sides reach a
+Why LOGIT_TOL is 3e-2 and not smaller: every GEMM input is rounded to bf16. The two sides reach a
 value to be rounded by different fp32 summation orders, so one in ~10^4 values lands on the other
 side of a rounding boundary and differs by one bf16 step (2^-8 relative); a later normalisation
 spreads that over a row. On this random-init model (logit deviation 0.64) the effect is 1e-2 to
@@ -12,7 +12,10 @@ spreads that over a row. On this random-init model (logit deviation 0.64) the ef
 (test_gpu_gemm.py). The reference accepts more between its own kernel paths: an occasional arg-max
 flip and KL < 1e-3 (Sources/SploshCLI/GenerateCommand.swift:592-603, 628). A row's arg-max is
 required to match whenever the oracle's top-1 margin exceeds twice the step's worst logit
-difference; every flip inside that band is counted and reported."""
+difference; every flip inside that band is counted and reported.
+The tolerances are 1.5 x the worst difference any test of the suite observes (every test prints its own): 2.0e-2 on the
+tiny model, 5.4e-2 on the 27B-shape slice, whose contractions are 5,120 to 17,408 long instead of 1,024 to 2,816 (the
+one-step differences of more inputs add up, and a 248K-column head takes the maximum over eight times as many logits)."""
 import numpy as np
 import pytest
 
@@ -22,8 +25,8 @@ from oracle import oracle as O
 from oracle import tables as T
 
 pytestmark = pytest.mark.gpu
-LOGIT_TOL = 5e-2
-SLICE_TOL = 1e-1      # the 27B-shape slice: contractions of 5,120 to 17,408 instead of 1,024 to 2,816
+LOGIT_TOL = 3e-2
+SLICE_TOL = 8e-2      # the 27B-shape slice: contractions of 5,120 to 17,408 instead of 1,024 to 2,816
 
 
 def check(got, ref, vocab, label="", tol=LOGIT_TOL):
