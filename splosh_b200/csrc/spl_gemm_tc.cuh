@@ -157,7 +157,7 @@ __global__ void spl_synth_q4_kernel(uint64_t seed, float factor, int rows, int k
 // ---- PTX wrappers -----------------------------------------------------------------------------
 // Every wait inside a kernel is bounded in time: a wait that outlasts the budget returns false, the kernel sets its error
 // word and unwinds. The budget is a device variable so that a test can shorten it (spl_debug_wait_budget).
-#define SPL_WAIT_HINT_NS 2000u        // suspend-time hint of one poll
+#define SPL_WAIT_HINT_NS 2000u        // suspend-time hint of one poll (100 to 10,000 ns measured: no difference)
 __device__ unsigned long long spl_wait_budget_ns = 250ull * 1000 * 1000;
 
 __device__ __forceinline__ uint32_t spl_smem_addr(const void *p) { return uint32_t(__cvta_generic_to_shared(p)); }
