@@ -323,6 +323,31 @@ spl_status spl_debug_profile(spl_engine *engine, int32_t enabled);
  * Returns accumulated milliseconds and launches since the last reset (reset = enabling). */
 spl_status spl_debug_profile_read(spl_engine *engine, int32_t klass, double *milliseconds, int64_t *launches, double *bytes);
 
+/* ---- The engine's primitives on device buffers ------------------------------------------------
+ * DraftModel builds its own passes out of Engine.gemm / norm / mlpIn / embed on buffers it owns and reuses the target's
+ * lm_head (Sources/SploshRuntime/DraftModel.swift:344-357, 418-468; Engine.swift:1561-1625, 1905-1998). Here: tensors of
+ * the caller's own (spl_tensor_create_*), calls that queue work on the engine's stream over DEVICE pointers the caller
+ * owns (fp32 rows, row-major), and spl_pass_wait as the pass's commitAndWait. Rows per call: at most the engine's
+ * max_rows; a tensor's inner dimension: a multiple of 256, at most the engine's MLP width. Not between spl_step_launch
+ * and spl_step_wait. The calls use the engine's operand scratch, so one pass at a time per engine. */
+typedef struct spl_tensor spl_tensor;
+spl_status spl_tensor_create_q4(spl_engine *engine, int32_t rows, int32_t inner, const uint32_t *packed, const uint16_t *scales,
+                                const uint16_t *biases, spl_tensor **out);                  /* rows a multiple of 16 */
+spl_status spl_tensor_create_vector(spl_engine *engine, const uint16_t *bf16, int32_t count, spl_tensor **out);
+void spl_tensor_destroy(spl_engine *engine, spl_tensor *tensor);
+spl_status spl_pass_begin(spl_engine *engine);
+/* Engine.gemm: out[r][:] = w x in[r][:] (+ residual[r][:]); in [rows][inner], out and residual [rows][w rows]. */
+spl_status spl_pass_gemm(spl_engine *engine, const spl_tensor *weight, const float *device_in, int32_t rows, const float *device_residual, float *device_out);
+/* The target's lm_head: in [rows][hidden] -> out [rows][vocab]. */
+spl_status spl_pass_gemm_head(spl_engine *engine, const float *device_in, int32_t rows, float *device_out);
+/* Engine.norm: out = in * rsqrt(mean in^2 + eps) * weight, fp32 rows of `dim`. */
+spl_status spl_pass_norm(spl_engine *engine, const float *device_in, const spl_tensor *weight, int32_t rows, int32_t dim, float *device_out);
+/* Engine.embed: rows of the target's embedding table for `device_tokens` (uint32 on the device). */
+spl_status spl_pass_embed(spl_engine *engine, const uint32_t *device_tokens, int32_t rows, float *device_out);
+/* Engine.mlpIn: out = bf16(silu(gate x in) * (up x in)) as fp32 rows; scratch [rows][gate rows] holds up x in. */
+spl_status spl_pass_mlp_in(spl_engine *engine, const spl_tensor *gate, const spl_tensor *up, const float *device_in, int32_t rows, float *device_out, float *device_scratch);
+spl_status spl_pass_wait(spl_engine *engine);
+
 /* ---- A GEMM for callers that must not allocate ---------------------------------------------
  * No counterpart in the reference (Metal hands out buffers freely; nothing there is barred from
  * allocating). Some CUDA hosts are: one that gave the whole GPU to its own pool at start-up and has

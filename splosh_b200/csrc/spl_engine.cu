@@ -1794,4 +1794,153 @@ spl_status spl_op_gemm_gguf(int32_t device, int32_t format, const uint8_t *block
     return s;
 }
 
+
+// ---- The engine's primitives on device buffers: what the drafter builds its passes from -------
+// (Sources/SploshRuntime/DraftModel.swift:344-357, 418-468; Engine.gemm / norm / mlpIn / embed, Engine.swift:1561-1625,
+// 1905-1998.) Every call queues on the engine's stream and returns; spl_pass_wait finishes the pass.
+
+struct spl_tensor {
+    SplQ4Dev q;                 // a q4 tensor in the GEMM's device layout, or
+    uint16_t *vec = nullptr;    // a bf16 vector
+    int count = 0;
+};
+
+// fp32 rows -> x * rsqrt(mean x^2 + eps) * w as fp32 rows (Sources/Shaders/engine.metal:159-178). Grid (rows), 256 threads.
+__global__ void __launch_bounds__(256) spl_norm_rows_kernel(const float *__restrict__ in, const uint16_t *__restrict__ weight, float *out, int dim, float eps) {
+    __shared__ float parts[8];
+    spl_grid_begin();
+    const float *x = in + size_t(blockIdx.x) * dim;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < dim; i += 256) ss += x[i] * x[i];
+    ss = spl_warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) parts[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float total = 0.0f;
+    for (int w = 0; w < 8; ++w) total += parts[w];
+    const float inv = 1.0f / sqrtf(total / float(dim) + eps);
+    for (int i = threadIdx.x; i < dim; i += 256) out[size_t(blockIdx.x) * dim + i] = x[i] * inv * spl_bf16_to_float(weight[i]);
+}
+// gate <- bf16(silu(gate) * up), elementwise (Sources/Shaders/engine.metal:200-219).
+__global__ void spl_silu_mul_kernel(float *gate, const float *__restrict__ up, size_t count) {
+    spl_grid_begin();
+    for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x)
+        gate[i] = spl_bf16_to_float(spl_float_to_bf16(spl_silu_exact(gate[i]) * up[i]));
+}
+
+spl_status spl_tensor_create_q4(spl_engine *e, int32_t rows, int32_t inner, const uint32_t *packed, const uint16_t *scales, const uint16_t *biases, spl_tensor **out) {
+    if (!e || !packed || !scales || !biases || !out || rows <= 0 || inner <= 0 || inner % 256) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
+    SPL_CUDA(cudaSetDevice(e->device));
+    if (inner > e->g.inter) return e->fail(SPL_ERR_INVALID_ARGUMENT, "a tensor's inner dimension may not exceed the engine's MLP width (its operand scratch is sized for that)");
+    spl_tensor *t = new spl_tensor;
+    spl_status s = alloc_q4(e, t->q, rows, inner);
+    if (s == SPL_OK) s = upload_q4_into(e, t->q, 0, rows, inner, packed, scales, biases, false);
+    // The GEMM's scratch for partial sums has to hold this tensor's at any row count.
+    size_t need = 0;
+    const int row_blocks = std::max(1, e->c.max_rows / 128);
+    for (int rn : {16, 32, 64, 128})
+        for (int rbs = 1; rbs <= (rn == 128 ? row_blocks : 1); ++rbs) need = std::max(need, gemm_slot_floats(t->q, e->sms, rn, rbs, false, false));
+    if (s == SPL_OK && need > e->slot_floats) {
+        cudaFree(e->slots); e->slots = nullptr;
+        if (cudaMalloc(reinterpret_cast<void **>(&e->slots), need * 4) != cudaSuccess) s = e->fail(SPL_ERR_ALLOCATION_FAILED, "GEMM scratch");
+        else e->slot_floats = need;
+    }
+    if (s != SPL_OK) { cudaFree(t->q.codes); cudaFree(t->q.sb); delete t; return s; }
+    *out = t;
+    return SPL_OK;
+}
+spl_status spl_tensor_create_vector(spl_engine *e, const uint16_t *bf16, int32_t count, spl_tensor **out) {
+    if (!e || !bf16 || !out || count <= 0) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
+    SPL_CUDA(cudaSetDevice(e->device));
+    spl_tensor *t = new spl_tensor;
+    if (cudaMalloc(reinterpret_cast<void **>(&t->vec), size_t(count) * 2) != cudaSuccess) { delete t; return e->fail(SPL_ERR_ALLOCATION_FAILED, "vector"); }
+    cudaMemcpy(t->vec, bf16, size_t(count) * 2, cudaMemcpyHostToDevice);
+    t->count = count;
+    *out = t;
+    return SPL_OK;
+}
+void spl_tensor_destroy(spl_engine *e, spl_tensor *t) {
+    if (!e || !t) return;
+    cudaSetDevice(e->device);
+    cudaStreamSynchronize(e->stream);
+    cudaFree(t->q.codes); cudaFree(t->q.sb); cudaFree(t->vec);
+    delete t;
+}
+
+spl_status spl_pass_begin(spl_engine *e) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
+    SPL_CUDA(cudaSetDevice(e->device));
+    return SPL_OK;
+}
+
+// device_out[r][:] = GEMM(w, device_in[r][:]) (+ device_residual), rows of w.k floats in, w.n floats out (Engine.gemm).
+static spl_status pass_gemm(spl_engine *e, const SplQ4Dev &w, const float *device_in, int rows, const float *device_residual, float *device_out) {
+    if (!device_in || !device_out || rows <= 0 || rows > e->c.max_rows) return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: row count outside the engine's limit");
+    if (w.ld != w.n) return e->fail(SPL_ERR_INVALID_ARGUMENT, "the tensor's row count must be a multiple of 16");
+    const int rn = operand_rn(rows), blocks = (rows + rn - 1) / rn;
+    const SplOperand operand{e->act, e->act_sums, rn, blocks};
+    launch_step(spl_operand_kernel, dim3(rows), dim3(256), 0, e->stream, device_in, operand, w.k);
+    const GemmScratch scratch{e->slots, e->slot_floats, e->tc_error, e->sms};
+    if (!launch_gemm_rows(e->stream, w, GemmOperand{e->act, e->act_sums, rn, blocks}, device_out, device_residual, rows, scratch, GemmExtras(), nullptr))
+        return e->fail(SPL_ERR_INVALID_ROWS, "invalid step rows: the GEMM scratch is smaller than the call needs");
+    return check_launch(e, "spl_pass_gemm");
+}
+spl_status spl_pass_gemm(spl_engine *e, const spl_tensor *weight, const float *device_in, int32_t rows, const float *device_residual, float *device_out) {
+    if (!e || !weight || !weight->q.codes) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
+    SPL_CUDA(cudaSetDevice(e->device));
+    return pass_gemm(e, weight->q, device_in, rows, device_residual, device_out);
+}
+// The target's lm_head on the caller's rows (DraftModel.swift:462-466 reuses it): [rows][hidden] -> [rows][vocab].
+spl_status spl_pass_gemm_head(spl_engine *e, const float *device_in, int32_t rows, float *device_out) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
+    SPL_CUDA(cudaSetDevice(e->device));
+    if (!e->head.codes) return e->fail(SPL_ERR_INVALID_ARGUMENT, "the head is not an MLX affine-4 tensor of this engine");
+    return pass_gemm(e, e->head, device_in, rows, nullptr, device_out);
+}
+spl_status spl_pass_norm(spl_engine *e, const float *device_in, const spl_tensor *weight, int32_t rows, int32_t dim, float *device_out) {
+    if (!e || !device_in || !device_out || !weight || !weight->vec || rows <= 0 || dim <= 0 || weight->count != dim) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
+    SPL_CUDA(cudaSetDevice(e->device));
+    launch_step(spl_norm_rows_kernel, dim3(rows), dim3(256), 0, e->stream, device_in, (const uint16_t *)weight->vec, device_out, int(dim), e->g.eps);
+    return check_launch(e, "spl_pass_norm");
+}
+spl_status spl_pass_embed(spl_engine *e, const uint32_t *device_tokens, int32_t rows, float *device_out) {
+    if (!e || !device_tokens || !device_out || rows <= 0) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
+    SPL_CUDA(cudaSetDevice(e->device));
+    if (e->g_embed) launch_step(spl_embed_gguf_kernel, dim3(rows), dim3(256), 0, e->stream, (const unsigned char *)e->g_embed, e->g_embed_format, device_tokens, device_out, e->g.hidden);
+    else launch_step(spl_embed_q4_kernel, dim3(rows), dim3(128), 0, e->stream, e->embed_packed, e->embed_scales, e->embed_biases, (uint32_t *)device_tokens, device_out, e->g.hidden);
+    return check_launch(e, "spl_pass_embed");
+}
+// Engine.mlpIn (Engine.swift:1905-1967): device_out = bf16(silu(gate x) * (up x)) as fp32 rows; device_scratch holds up x.
+spl_status spl_pass_mlp_in(spl_engine *e, const spl_tensor *gate, const spl_tensor *up, const float *device_in, int32_t rows, float *device_out, float *device_scratch) {
+    if (!e || !gate || !up || !gate->q.codes || !up->q.codes || !device_scratch || gate->q.n != up->q.n || gate->q.k != up->q.k) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
+    SPL_CUDA(cudaSetDevice(e->device));
+    spl_status s = pass_gemm(e, gate->q, device_in, rows, nullptr, device_out);
+    if (s == SPL_OK) s = pass_gemm(e, up->q, device_in, rows, nullptr, device_scratch);
+    if (s != SPL_OK) return s;
+    const size_t count = size_t(rows) * gate->q.n;
+    launch_step(spl_silu_mul_kernel, dim3(int(std::min<size_t>((count + 255) / 256, 4096))), dim3(256), 0, e->stream, device_out, (const float *)device_scratch, count);
+    return check_launch(e, "spl_pass_mlp_in");
+}
+// The pass's end (CommandGraph.commitAndWait): waits for everything queued, reports a kernel that gave up a wait.
+spl_status spl_pass_wait(spl_engine *e) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
+    SPL_CUDA(cudaSetDevice(e->device));
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    int flag[4] = {0, 0, 0, 0};
+    SPL_CUDA(cudaMemcpy(flag, e->tc_error, sizeof flag, cudaMemcpyDeviceToHost));
+    if (flag[0]) {
+        cudaMemset(e->tc_error, 0, sizeof flag);
+        return e->fail(SPL_ERR_TIMEOUT, "a GEMM block of the pass gave up waiting (warp " + std::to_string(flag[0] - 1) + "; first wait " + std::to_string(flag[1]) + ")");
+    }
+    return SPL_OK;
+}
+
 }  // extern "C"

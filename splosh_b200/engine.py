@@ -174,6 +174,16 @@ def lib():
             "spl_weights_set_vector": (i32, [vp, i32, i32, vp, i32]),
             "spl_weights_synthesize_q4": (i32, [vp, u64]),
             "spl_weights_set_gguf": (i32, [vp, i32, i32, i32, i32, i32, vp]),
+            "spl_tensor_create_q4": (i32, [vp, i32, i32, vp, vp, vp, C.POINTER(vp)]),
+            "spl_tensor_create_vector": (i32, [vp, vp, i32, C.POINTER(vp)]),
+            "spl_tensor_destroy": (None, [vp, vp]),
+            "spl_pass_begin": (i32, [vp]),
+            "spl_pass_gemm": (i32, [vp, vp, vp, i32, vp, vp]),
+            "spl_pass_gemm_head": (i32, [vp, vp, i32, vp]),
+            "spl_pass_norm": (i32, [vp, vp, vp, i32, i32, vp]),
+            "spl_pass_embed": (i32, [vp, vp, i32, vp]),
+            "spl_pass_mlp_in": (i32, [vp, vp, vp, vp, i32, vp, vp]),
+            "spl_pass_wait": (i32, [vp]),
             "spl_weights_synthesize_gguf": (i32, [vp, u64, i32, i32]),
             "spl_step": (i32, [vp, C.POINTER(_Row), i32, C.POINTER(_Stats)]),
             "spl_step_launch": (i32, [vp, C.POINTER(_Row), i32]),
@@ -454,6 +464,43 @@ class Engine:
 
     def synthesize_q4(self, seed):
         self._check(lib().spl_weights_synthesize_q4(self.handle, seed))
+
+    # ---- the engine's primitives on device buffers (what the drafter builds its passes from); addresses are ints
+    def tensor_q4(self, packed, scales, biases):
+        packed = np.ascontiguousarray(packed, np.uint32); scales = np.ascontiguousarray(scales, np.uint16); biases = np.ascontiguousarray(biases, np.uint16)
+        out = C.c_void_p()
+        self._check(lib().spl_tensor_create_q4(self.handle, packed.shape[0], packed.shape[1] * 8, _ptr(packed), _ptr(scales), _ptr(biases), C.byref(out)))
+        return out
+
+    def tensor_vector(self, bits):
+        bits = np.ascontiguousarray(bits, np.uint16)
+        out = C.c_void_p()
+        self._check(lib().spl_tensor_create_vector(self.handle, _ptr(bits), bits.size, C.byref(out)))
+        return out
+
+    def tensor_destroy(self, tensor):
+        lib().spl_tensor_destroy(self.handle, tensor)
+
+    def pass_begin(self):
+        self._check(lib().spl_pass_begin(self.handle))
+
+    def pass_gemm(self, tensor, device_in, rows, device_out, device_residual=None):
+        self._check(lib().spl_pass_gemm(self.handle, tensor, C.c_void_p(device_in), rows, C.c_void_p(device_residual) if device_residual else None, C.c_void_p(device_out)))
+
+    def pass_gemm_head(self, device_in, rows, device_out):
+        self._check(lib().spl_pass_gemm_head(self.handle, C.c_void_p(device_in), rows, C.c_void_p(device_out)))
+
+    def pass_norm(self, device_in, weight, rows, dim, device_out):
+        self._check(lib().spl_pass_norm(self.handle, C.c_void_p(device_in), weight, rows, dim, C.c_void_p(device_out)))
+
+    def pass_embed(self, device_tokens, rows, device_out):
+        self._check(lib().spl_pass_embed(self.handle, C.c_void_p(device_tokens), rows, C.c_void_p(device_out)))
+
+    def pass_mlp_in(self, gate, up, device_in, rows, device_out, device_scratch):
+        self._check(lib().spl_pass_mlp_in(self.handle, gate, up, C.c_void_p(device_in), rows, C.c_void_p(device_out), C.c_void_p(device_scratch)))
+
+    def pass_wait(self):
+        self._check(lib().spl_pass_wait(self.handle))
 
     def set_gguf(self, layer, kind, gguf_kind, blocks):
         """One tensor as native GGUF K-quant super-blocks: blocks uint8 [rows, inner / 256, block bytes]; gguf_kind "Q4_K", "Q5_K" or "Q6_K"."""
