@@ -1806,7 +1806,7 @@ struct spl_tensor {
 };
 
 // fp32 rows -> x * rsqrt(mean x^2 + eps) * w as fp32 rows (Sources/Shaders/engine.metal:159-178). Grid (rows), 256 threads.
-__global__ void __launch_bounds__(256) spl_norm_rows_kernel(const float *__restrict__ in, const uint16_t *__restrict__ weight, float *out, int dim, float eps) {
+static __global__ void __launch_bounds__(256) spl_norm_rows_kernel(const float *__restrict__ in, const uint16_t *__restrict__ weight, float *out, int dim, float eps) {
     __shared__ float parts[8];
     spl_grid_begin();
     const float *x = in + size_t(blockIdx.x) * dim;
@@ -1821,7 +1821,7 @@ __global__ void __launch_bounds__(256) spl_norm_rows_kernel(const float *__restr
     for (int i = threadIdx.x; i < dim; i += 256) out[size_t(blockIdx.x) * dim + i] = x[i] * inv * spl_bf16_to_float(weight[i]);
 }
 // gate <- bf16(silu(gate) * up), elementwise (Sources/Shaders/engine.metal:200-219).
-__global__ void spl_silu_mul_kernel(float *gate, const float *__restrict__ up, size_t count) {
+static __global__ void spl_silu_mul_kernel(float *gate, const float *__restrict__ up, size_t count) {
     spl_grid_begin();
     for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < count; i += size_t(gridDim.x) * blockDim.x)
         gate[i] = spl_bf16_to_float(spl_float_to_bf16(spl_silu_exact(gate[i]) * up[i]));
