@@ -222,6 +222,21 @@ spl_status spl_weights_synthesize_q4(spl_engine *engine, uint64_t seed);
  * reference's tile kernels do (one fp32 operation, rounded to fp16, Sources/Shaders/gguf_formats.h:390-438), the
  * embedding gather decodes exactly (:463-501), norms are plain RMSNorms and the SiLU gate a kernel of its own. */
 spl_status spl_weights_set_gguf(spl_engine *engine, int32_t layer, int32_t kind, int32_t type, int32_t rows, int32_t inner, const uint8_t *blocks);
+/* A GGUF file orders the value heads of a gated-delta block differently from the engine (file head i = engine head
+ * 3 (i % 16) + i / 16 for 48 value and 16 key heads, Sources/SploshModel/GgufNames.swift:73-84). Tensors that hold the heads
+ * as rows are re-ordered when they are loaded; the out projection holds them as columns, which cannot move without
+ * re-quantising, so it is given in the file's order (Sources/SploshModel/GgufConvert.swift:18-24) and, with this switch on,
+ * the gated-delta blocks write their outputs in that order, as the reference's `heads` kernels read them
+ * (Sources/Shaders/engine_gguf.metal). Off by default. */
+spl_status spl_weights_gguf_file_order(spl_engine *engine, int32_t enabled);
+/* A llama.cpp GGUF file (versions 2 and 3) of a model of the engine's geometry into the engine: the reference's reader and
+ * converter of such a file (Sources/SploshModel/GgufFile.swift, GgufNames.swift:13-44, GgufConvert.swift:15-32) with the
+ * engine as its destination. Packed weights Q4_K / Q5_K / Q6_K, dense tensors F32 / F16 / BF16 (rounded to bf16, nearest
+ * even); value heads re-ordered where they are rows, channels or elements, the out projection left in file order with
+ * spl_weights_gguf_file_order switched on; ssm_a (-exp(A_log)) turned into A_log; an MTP block left out; a file without
+ * output.weight ties the head to the embedding. `message` (may be null) receives what was wrong with the file. */
+spl_status spl_weights_load_gguf_file(spl_engine *engine, const char *path, char *message, size_t message_bytes);
+spl_status spl_engine_geometry(const spl_engine *engine, spl_geometry *out);
 /* Benchmarking: pseudo-random GGUF blocks for every tensor (`block_type`) and for the embedding and head
  * (`head_type`), generated on the device. */
 spl_status spl_weights_synthesize_gguf(spl_engine *engine, uint64_t seed, int32_t block_type, int32_t head_type);

@@ -75,6 +75,7 @@ def lib():
         L.orc_engine_reset_slot.argtypes = [C.c_void_p, C.c_int, C.c_int]
         L.orc_engine_buffer.restype = C.c_void_p; L.orc_engine_buffer.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_size_t)]
         L.orc_set_norm_contract.argtypes = [C.c_int]
+        L.orc_model_set_out_file_order.argtypes = [C.c_void_p, C.c_int]
         L.orc_model_set_gguf.restype = C.c_int; L.orc_model_set_gguf.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p]
         L.orc_step.restype = C.c_int; L.orc_step.argtypes = [C.c_void_p, C.POINTER(_CTables), C.c_void_p, C.c_void_p, C.c_int]
         L.orc_attention_scan.restype = C.c_int
@@ -261,6 +262,11 @@ class Model:
 
     def gguf(self, layer, kind):
         return self._gguf[(layer, kind)]
+
+    def set_out_file_order(self, enabled=True):
+        """The gated-delta out projections hold their columns in a GGUF file's order of the value heads."""
+        lib().orc_model_set_out_file_order(self.handle, 1 if enabled else 0)
+        self.out_file_order = bool(enabled)
 
     def to_gguf(self, block_kind="Q5_K", head_kind="Q6_K"):
         """Re-quantise every tensor from its MLX affine-4 values to GGUF K-quants: the synthetic GGUF-weighted model

@@ -167,6 +167,10 @@ struct Model {
     std::vector<Layer> layers;
     Q4 embed, head;
     std::vector<uint16_t> final_norm;
+    // The gated-delta out projections hold their columns in a GGUF file's order of the value heads (file head i = engine head
+    // ratio (i % key heads) + i / key heads, Sources/SploshModel/GgufNames.swift:73-84; the out projection stays in file order,
+    // Sources/SploshModel/GgufConvert.swift:18-24): the blocks' outputs are arranged in that order before the projection.
+    bool out_file_order = false;
 };
 
 uint64_t tensor_seed(uint64_t base, int layer, const char *name) {
@@ -487,7 +491,8 @@ void gdn_layer(Engine &e, int linear_index, const Layer &L, const Tables &t, con
             for (int j = 0; j < d; ++j) {
                 const float gate = z[(size_t(r) * VH + h) * d + j];
                 const float result = bf16_to_float(L.vec[V_GDN_NORM][j]) * o[j] * inv * gate / (1.0f + expf(-gate));
-                core.values[(size_t(r) * VH + h) * d + j] = round_bf16(result);
+                const int place = e.m->out_file_order ? KH * (h % per) + h / per : h;
+                core.values[(size_t(r) * VH + place) * d + j] = round_bf16(result);
             }
         }
         core.finish_row(r);
@@ -914,6 +919,7 @@ int orc_model_set_gguf(void *model, int layer, int kind, int format, const uint8
     t->gguf_format = format;
     return 0;
 }
+void orc_model_set_out_file_order(void *model, int enabled) { static_cast<Model *>(model)->out_file_order = enabled != 0; }
 int orc_model_vec(void *model, int layer, int kind, const uint16_t **data, int *count) {
     Model *m = static_cast<Model *>(model);
     const std::vector<uint16_t> *v = kind == V_FINAL_NORM ? &m->final_norm : &m->layers[layer].vec[kind];

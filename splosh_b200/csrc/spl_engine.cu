@@ -72,6 +72,7 @@ struct spl_engine {
     float *xn_squares = nullptr;       // [row][hidden / 64] squares of the residual stream, left by the GEMM that feeds a deferred norm
     float *slots = nullptr;            // partial sums of the GEMM tiles that several blocks share
     size_t slot_floats = 0;
+    bool gdn_out_file_order = false;      // spl_weights_gguf_file_order
     int gdn_chunk_min = SPL_GDN_CHUNK_MIN;      // ordinary runs at least this long take the chunked gated-delta scan (spl_debug_gdn_chunk_min)
     int sms = 148;
     int rows_padded = 0, logit_rows_padded = 0;
@@ -503,7 +504,7 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
         if (!L.full) {
             SplGdnParams p;
             p.rows = R; p.runs = int(t->run_count); p.channels = sh.C; p.key_heads = g.gdn_key_heads; p.value_heads = g.gdn_value_heads;
-            p.head_dim = g.gdn_head_dim; p.proj_ld = L.in_proj.ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps; p.chunk_min = chunked_runs > 0 ? e->gdn_chunk_min : 0;
+            p.head_dim = g.gdn_head_dim; p.proj_ld = L.in_proj.ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps; p.chunk_min = chunked_runs > 0 ? e->gdn_chunk_min : 0; p.out_file_order = e->gdn_out_file_order ? 1 : 0;
             profile_begin(e, KLASS_GDN, 0);
             launch_step(spl_gdn_conv_kernel, dim3(dim3((sh.C + 255) / 256, t->run_count)), dim3(256), 0, e->stream, 
                 e->proj, L.vec[SPL_VEC_CONV], e->conv[linear_index], e->d_runs, e->d_row_read, e->d_row_write, e->gdn_act, p);
@@ -958,6 +959,19 @@ static spl_status upload_gguf_into(spl_engine *e, SplQ4Dev &q, int n0, int rows,
     SPL_CUDA(cudaStreamSynchronize(e->stream));
     cudaFree(staged);
     return launched;
+}
+
+spl_status spl_engine_geometry(const spl_engine *e, spl_geometry *out) {
+    if (!e || !out) return SPL_ERR_INVALID_ARGUMENT;
+    *out = e->g;
+    return SPL_OK;
+}
+
+spl_status spl_weights_gguf_file_order(spl_engine *e, int32_t enabled) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    SPL_NOT_IN_FLIGHT(e);
+    e->gdn_out_file_order = enabled != 0;
+    return SPL_OK;
 }
 
 static bool gguf_type_ok(int type) { return type == SPL_GGUF_Q4K || type == SPL_GGUF_Q5K || type == SPL_GGUF_Q6K; }

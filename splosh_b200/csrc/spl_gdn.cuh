@@ -18,7 +18,18 @@ struct SplGdnParams {
     int proj_ld, z_offset, a_offset, b_offset;     // columns of the fused input projection
     float eps;
     int chunk_min;     // > 0: ordinary runs of at least this many rows are left to the chunked kernels (spl_gdn_chunk.cuh)
+    int out_file_order;     // the out projection's columns are in a GGUF file's order of the value heads (below)
 };
+
+// Where value head h's 128 outputs go among the out projection's inputs. A GGUF file orders the value heads differently from the
+// engine: its head i is the engine's ratio * (i % key_heads) + i / key_heads, ratio = value heads per key head
+// (Sources/SploshModel/GgufNames.swift:73-84). Rows of a weight are moved when such a file is loaded; the out projection has
+// the heads as its columns, which cannot move without re-quantising, so it stays in file order and the blocks write their
+// output in that order instead (Sources/SploshModel/GgufConvert.swift:18-24; the reference's `heads` kernels read it so).
+__device__ __forceinline__ int spl_gdn_out_head(const SplGdnParams &p, int h) {
+    const int ratio = p.value_heads / p.key_heads;
+    return p.out_file_order ? p.key_heads * (h % ratio) + h / ratio : h;
+}
 
 // Conv (k = 4, depthwise, no bias) + SiLU over every channel of every run; then the conv history
 // of every unit a row writes: the last three raw inputs up to and including that row
@@ -257,13 +268,13 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
                 const float r2 = spl_bf16_to_float(uint16_t(w.y)) * ov.z * inv * spl_silu_exact(z.z);
                 const float r3 = spl_bf16_to_float(uint16_t(w.y >> 16)) * ov.w * inv * spl_silu_exact(z.w);
                 const uint16_t b0 = spl_float_to_bf16(r0), b1 = spl_float_to_bf16(r1), b2 = spl_float_to_bf16(r2), b3 = spl_float_to_bf16(r3);
-                *reinterpret_cast<uint2 *>(core.values + core.at(int(row), h * D + lane * 4)) =
+                *reinterpret_cast<uint2 *>(core.values + core.at(int(row), spl_gdn_out_head(p, h) * D + lane * 4)) =
                     spl_operand_pack4(spl_bf16_to_float(b0), spl_bf16_to_float(b1), spl_bf16_to_float(b2), spl_bf16_to_float(b3));
                 // The following GEMM's per-64 sums: a 128-wide head is two quant groups, sixteen lanes each.
                 float gsum = (spl_bf16_to_float(b0) + spl_bf16_to_float(b1)) + (spl_bf16_to_float(b2) + spl_bf16_to_float(b3));
 #pragma unroll
                 for (int o2 = 8; o2 > 0; o2 >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o2);
-                if ((lane & 15) == 0) core.put_sum(int(row), h * 2 + (lane >> 4), gsum);
+                if ((lane & 15) == 0) core.put_sum(int(row), spl_gdn_out_head(p, h) * 2 + (lane >> 4), gsum);
             }
         }
     }

@@ -317,11 +317,11 @@ spl_gdn_chunk_finish_kernel(const float *__restrict__ o_raw, const float *__rest
         const float r2 = spl_bf16_to_float(uint16_t(w.y)) * ov.z * inv * spl_silu_exact(z.z);
         const float r3 = spl_bf16_to_float(uint16_t(w.y >> 16)) * ov.w * inv * spl_silu_exact(z.w);
         const uint16_t b0 = spl_float_to_bf16(r0), b1 = spl_float_to_bf16(r1), b2 = spl_float_to_bf16(r2), b3 = spl_float_to_bf16(r3);
-        *reinterpret_cast<uint2 *>(core.values + core.at(int(row), h * D + lane * 4)) =
+        *reinterpret_cast<uint2 *>(core.values + core.at(int(row), spl_gdn_out_head(p, h) * D + lane * 4)) =
             spl_operand_pack4(spl_bf16_to_float(b0), spl_bf16_to_float(b1), spl_bf16_to_float(b2), spl_bf16_to_float(b3));
         float gsum = (spl_bf16_to_float(b0) + spl_bf16_to_float(b1)) + (spl_bf16_to_float(b2) + spl_bf16_to_float(b3));
 #pragma unroll
         for (int o2 = 8; o2 > 0; o2 >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o2);
-        if ((lane & 15) == 0) core.put_sum(int(row), h * 2 + (lane >> 4), gsum);
+        if ((lane & 15) == 0) core.put_sum(int(row), spl_gdn_out_head(p, h) * 2 + (lane >> 4), gsum);
     }
 }

@@ -185,6 +185,8 @@ def lib():
             "spl_pass_mlp_in": (i32, [vp, vp, vp, vp, i32, vp, vp]),
             "spl_pass_wait": (i32, [vp]),
             "spl_weights_synthesize_gguf": (i32, [vp, u64, i32, i32]),
+            "spl_weights_gguf_file_order": (i32, [vp, i32]),
+            "spl_weights_load_gguf_file": (i32, [vp, C.c_char_p, C.c_char_p, C.c_size_t]),
             "spl_step": (i32, [vp, C.POINTER(_Row), i32, C.POINTER(_Stats)]),
             "spl_step_launch": (i32, [vp, C.POINTER(_Row), i32]),
             "spl_step_wait": (i32, [vp, C.POINTER(_Stats)]),
@@ -506,6 +508,17 @@ class Engine:
         """One tensor as native GGUF K-quant super-blocks: blocks uint8 [rows, inner / 256, block bytes]; gguf_kind "Q4_K", "Q5_K" or "Q6_K"."""
         blocks = np.ascontiguousarray(blocks, np.uint8)
         self._check(lib().spl_weights_set_gguf(self.handle, layer, Q4_KINDS.index(kind), GGUF_TYPE[gguf_kind], blocks.shape[0], blocks.shape[1] * 256, _ptr(blocks)))
+
+    def gguf_file_order(self, enabled=True):
+        """The gated-delta out projections hold their columns in a GGUF file's order of the value heads."""
+        self._check(lib().spl_weights_gguf_file_order(self.handle, int(enabled)))
+
+    def load_gguf_file(self, path):
+        """Every tensor of a llama.cpp GGUF file of this geometry (spl_weights_load_gguf_file)."""
+        message = C.create_string_buffer(512)
+        status = lib().spl_weights_load_gguf_file(self.handle, os.fsencode(path), message, len(message))
+        if status:
+            raise EngineError(status, message.value.decode() or "spl_weights_load_gguf_file failed")
 
     def synthesize_gguf(self, seed, block_kind="Q5_K", head_kind="Q6_K"):
         self._check(lib().spl_weights_synthesize_gguf(self.handle, seed, GGUF_TYPE[block_kind], GGUF_TYPE[head_kind]))

@@ -68,3 +68,56 @@ def test_a_partly_converted_engine_refuses_to_step(plain_norms):
         engine.set_gguf(0, "qkv", *pair.model.gguf(0, "qkv"))
         kind, blocks = pair.model.gguf(0, "z")
         engine.set_gguf(0, "z", "Q4_K", O.quantize_gguf("Q4_K", np.zeros((blocks.shape[0], blocks.shape[1] * 256), np.float32)))
+
+
+def test_a_gguf_file_loads_into_the_engine(plain_norms, tmp_path):
+    """The synthetic GGUF-weighted model written as a llama.cpp GGUF file (value heads in the file's order, -exp(A_log), fp32
+    norms, an MTP block and metadata to skip; tests/gguf_writer.py) and read back by spl_weights_load_gguf_file: the step
+    equals, bit for bit, that of an engine given the same tensors one by one, and matches the oracle that holds the out
+    projections in file order (Sources/SploshModel/GgufNames.swift:73-84, GgufConvert.swift:15-32)."""
+    import gguf_writer
+    g = geometry()
+    cfg = S.EngineConfig(max_slots=2, max_rows=64, kv_pages=8, max_context=1024)
+    pair = Pair(g, cfg, gguf=("Q5_K", "Q6_K"))
+    pair.model.set_out_file_order(True)
+    pair.engine.gguf_file_order(True)
+    path = str(tmp_path / "model.gguf")
+    gguf_writer.write(path, g, pair.model)
+    loaded = S.Engine(g, cfg)
+    loaded.load_gguf_file(path)
+    toks = tokens_for(0xC0FFEE00, 200, g.vocab)
+    for rows in ([S.EngineRow(0, toks[i], i, i % 7 == 0) for i in range(40)],
+                 [S.EngineRow(0, toks[40 + i], 40 + i, True, True) for i in range(8)]):
+        glogits, ologits = pair.step(rows)
+        loaded.step(rows)
+        assert np.array_equal(loaded.all_logits(), glogits)
+        assert np.abs(glogits - ologits).max() < LOGIT_TOL * max(1.0, np.abs(ologits).max())
+    # The head order matters: the same file with the switch off gives something else.
+    loaded.gguf_file_order(False)
+    loaded.reset_slot(0)
+    loaded.step([S.EngineRow(0, toks[i], i, i % 7 == 0) for i in range(40)])
+    pair2 = Pair(g, cfg, gguf=("Q5_K", "Q6_K"), gpu=False)
+    pair2.model.set_out_file_order(True)
+    _, ref = pair2.step([S.EngineRow(0, toks[i], i, i % 7 == 0) for i in range(40)])
+    assert np.abs(loaded.all_logits() - ref).max() > LOGIT_TOL
+
+
+def test_a_broken_gguf_file_is_refused_with_a_message(tmp_path):
+    import gguf_writer
+    g = geometry()
+    cfg = S.EngineConfig(max_slots=1, max_rows=16, kv_pages=4, max_context=512)
+    from helpers import to_oracle_geometry
+    model = O.Model(to_oracle_geometry(g)).to_gguf("Q5_K", "Q6_K")
+    path = str(tmp_path / "model.gguf")
+    gguf_writer.write(path, g, model)
+    raw = open(path, "rb").read()
+    engine = S.Engine(g, cfg)
+    cut = str(tmp_path / "cut.gguf"); open(cut, "wb").write(raw[: len(raw) // 2])
+    with pytest.raises(S.EngineError, match="outside the file"):
+        engine.load_gguf_file(cut)
+    bad = str(tmp_path / "bad.gguf"); open(bad, "wb").write(b"GGUX" + raw[4:])
+    with pytest.raises(S.EngineError, match="not a GGUF file"):
+        engine.load_gguf_file(bad)
+    other = S.Engine(S.tiny_geometry(), cfg)
+    with pytest.raises(S.EngineError, match="shape|elements"):
+        other.load_gguf_file(path)
