@@ -197,9 +197,11 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
     spl_grid_begin();
     constexpr int D = SPL_GDN_D, C = SPL_GDN_CHUNK, SL = SPL_GDN_SLICE, LD = SPL_GDN_LD, PLD = SPL_GDN_PLD;
     extern __shared__ __align__(16) float spl_gdn_scan_smem[];
-    float *w_s = spl_gdn_scan_smem;           // [C][LD] W, later Kd
-    float *q_s = w_s + C * LD;                 // [C][LD] g q^
-    float *p_s = q_s + C * LD;                 // [C][PLD] P
+    // One [C][LD] buffer holds W, then g q^, then Kd in turn: with 64 KB a block three blocks share an SM, and the 384
+    // blocks of a 48-head run are resident at once (with a buffer each for W and g q^ it was two to an SM and a second
+    // wave of 88 blocks doubled the kernel's time).
+    float *w_s = spl_gdn_scan_smem;           // [C][LD] W, then g q^, then Kd
+    float *p_s = w_s + C * LD;                 // [C][PLD] P
     float *s_s = p_s + C * PLD;                // [SL][D + 4] the slice of the state (rows padded)
     float *u_s = s_s + SL * (D + 4);           // [C][SL] U
     const int h = blockIdx.x, run = blockIdx.y, slice = blockIdx.z, tid = threadIdx.x;
@@ -232,11 +234,8 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
     for (int n = 0; n < chunks; ++n, ++chunk) {
         const float *rec = records + (size_t(chunk) * VH + h) * SPL_GDN_REC_FLOATS;
         const uint32_t first = tables.chunks[chunk * 4 + 1], count = tables.chunks[chunk * 4 + 2];
-        for (int idx = tid; idx < C * (D / 4); idx += 256) {
-            const int at = (idx / (D / 4)) * LD + (idx % (D / 4)) * 4;
-            *reinterpret_cast<float4 *>(w_s + at) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_W)[idx];
-            *reinterpret_cast<float4 *>(q_s + at) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_QG)[idx];
-        }
+        for (int idx = tid; idx < C * (D / 4); idx += 256)
+            *reinterpret_cast<float4 *>(w_s + (idx / (D / 4)) * LD + (idx % (D / 4)) * 4) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_W)[idx];
         for (int idx = tid; idx < C * (C / 4); idx += 256)
             *reinterpret_cast<float4 *>(p_s + (idx / (C / 4)) * PLD + (idx % (C / 4)) * 4) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_P)[idx];
         const float g_end = rec[SPL_GDN_REC_GC];
@@ -249,17 +248,27 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
 #pragma unroll
             for (int r = 0; r < 4; ++r) o[r] = 0.0f;
             for (int i = 0; i < D; i += 4) {
-                const float4 wv = *reinterpret_cast<const float4 *>(w_s + tq * LD + i), qv = *reinterpret_cast<const float4 *>(q_s + tq * LD + i);
+                const float4 wv = *reinterpret_cast<const float4 *>(w_s + tq * LD + i);
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
                     const float4 sv = *reinterpret_cast<const float4 *>(s_s + (jq * 4 + r) * (D + 4) + i);
                     u[r] -= wv.x * sv.x + wv.y * sv.y + wv.z * sv.z + wv.w * sv.w;
-                    o[r] += qv.x * sv.x + qv.y * sv.y + qv.z * sv.z + qv.w * sv.w;
                 }
             }
             *reinterpret_cast<float4 *>(u_s + tq * SL + jq * 4) = make_float4(u[0], u[1], u[2], u[3]);
         }
         __syncthreads();
+        for (int idx = tid; idx < C * (D / 4); idx += 256)
+            *reinterpret_cast<float4 *>(w_s + (idx / (D / 4)) * LD + (idx % (D / 4)) * 4) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_QG)[idx];
+        __syncthreads();
+        for (int i = 0; i < D; i += 4) {
+            const float4 qv = *reinterpret_cast<const float4 *>(w_s + tq * LD + i);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const float4 sv = *reinterpret_cast<const float4 *>(s_s + (jq * 4 + r) * (D + 4) + i);
+                o[r] += qv.x * sv.x + qv.y * sv.y + qv.z * sv.z + qv.w * sv.w;
+            }
+        }
         // O[t][j] = O0 + sum_{s<=t} P[t][s] U[s][j]; meanwhile the record's Kd replaces W in shared memory.
         for (int s = 0; s <= tq; ++s) {
             const float w = p_s[tq * PLD + s];
@@ -268,6 +277,7 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
         }
         if (tq < int(count))
             *reinterpret_cast<float4 *>(o_raw + size_t(first + tq) * (size_t(VH) * D) + h * D + slice * SL + jq * 4) = make_float4(o[0], o[1], o[2], o[3]);
+        __syncthreads();          // every thread has finished with g q^
         for (int idx = tid; idx < C * (D / 4); idx += 256)
             *reinterpret_cast<float4 *>(w_s + (idx / (D / 4)) * LD + (idx % (D / 4)) * 4) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_KD)[idx];
         __syncthreads();
@@ -294,7 +304,7 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
     }
 }
 __host__ __device__ constexpr size_t spl_gdn_chunk_scan_smem() {
-    return sizeof(float) * (2 * SPL_GDN_CHUNK * SPL_GDN_LD + SPL_GDN_CHUNK * SPL_GDN_PLD + SPL_GDN_SLICE * (SPL_GDN_D + 4) + SPL_GDN_CHUNK * SPL_GDN_SLICE);
+    return sizeof(float) * (SPL_GDN_CHUNK * SPL_GDN_LD + SPL_GDN_CHUNK * SPL_GDN_PLD + SPL_GDN_SLICE * (SPL_GDN_D + 4) + SPL_GDN_CHUNK * SPL_GDN_SLICE);
 }
 
 // Gated RMSNorm of whole heads and the bf16 operand of the output projection with its per-64 sums
