@@ -370,9 +370,8 @@ spl_status spl_pass_wait(spl_engine *engine);
  * path because cudaMalloc and cudaFree synchronise the whole device.
  * This entry point runs out[r][:] = GEMM(weights, activations[r][:]) (+ residual) on one of the
  * engine's resident weights and calls no cudaMalloc, cudaFree or other allocating routine: the
- * GEMM operand, its per-64 sums, the slots where blocks that share an output tile leave their partial sums
- * and the tiles' tickets live in a static device array of about 12.3 MiB that every GPU loading the library
- * holds until exit.
+ * GEMM operand, its per-64 sums, the partial sums of a cut contraction and the calls' error words live in a
+ * static device array of about 12.3 MiB that every GPU loading the library holds until exit.
  *   - all three buffers are DEVICE pointers: activations fp32 [rows][inner], residual (may be
  *     null, may alias out) and out fp32 [rows][ld], ld = the tensor's columns rounded up to 16;
  *   - rows must be 1..64 and the tensor's inner dimension at most 17408, else SPL_ERR_INVALID_ROWS

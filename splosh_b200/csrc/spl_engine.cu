@@ -1613,7 +1613,7 @@ spl_status spl_kv_import(spl_engine *e, int32_t slot, int32_t token_count, const
 #define SPL_STATIC_OPERAND_BYTES (SPL_STATIC_ROWS * SPL_STATIC_INNER * 2)
 #define SPL_STATIC_SUMS_BYTES (SPL_STATIC_ROWS * ((SPL_STATIC_INNER / 64 + 15) / 16) * 128)      // tiles of split means
 #define SPL_STATIC_CONTROL_BYTES 256       // the error words
-#define SPL_STATIC_SLOTS 320               // slots of 64 x 128 partial sums: a tensor cut in more pieces than that is refused
+#define SPL_STATIC_SLOTS 320               // room for partial sums, in units of 64 x 128 floats: splits x 64 rows x the tensor's columns must fit (else the call is refused)
 #define SPL_STATIC_SLOT_BYTES (SPL_STATIC_SLOTS * 64 * 128 * 4)
 #define SPL_STATIC_BYTES (SPL_STATIC_OPERAND_BYTES + SPL_STATIC_SUMS_BYTES + SPL_STATIC_CONTROL_BYTES + SPL_STATIC_SLOT_BYTES)
 static __device__ __align__(256) unsigned char spl_static_scratch[SPL_STATIC_BYTES];
