@@ -648,22 +648,42 @@ __global__ void spl_attn_merge_kernel(const float *__restrict__ partials, const 
     __shared__ float warp_sums[8];
     const int head = blockIdx.x, row = blockIdx.y, j = threadIdx.x, hd = p.head_dim, record = hd + 2;
     const float *base = partials + (size_t(row) * p.heads + head) * p.spans * record;
-    // The spans' weights once for the block (the first warp; at most 64 spans), then every thread walks its channel with
-    // the loads of four spans in flight and the additions in span order.
+    // The spans' weights and the sum of the weighted totals once for the block (the first warp, a lane a span; at most 64
+    // spans; both numbers of a span are asked for together: one trip to memory), then every thread walks its channel with
+    // the loads of eight spans in flight and the additions in span order.
     __shared__ float weights[64];
+    __shared__ float total;
     if (j < 32) {
-        float top = -INFINITY;
-        for (int s = j; s < p.spans; s += 32) top = fmaxf(top, base[s * record]);
-        top = spl_warp_max(top);
-        for (int s = j; s < p.spans; s += 32) {
-            const float weight = expf(base[s * record] - top);
-            weights[s] = weight;
+        float ref[2], tot[2];
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int s = j + 32 * u;
+            ref[u] = s < p.spans ? base[s * record] : -INFINITY;
+            tot[u] = s < p.spans ? base[s * record + 1] : 0.0f;
         }
+        const float top = spl_warp_max(fmaxf(ref[0], ref[1]));
+        float part = 0.0f;
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+            const int s = j + 32 * u;
+            const float weight = s < p.spans ? expf(ref[u] - top) : 0.0f;
+            if (s < p.spans) weights[s] = weight;
+            if (weight > 0.0f) part += tot[u] * weight;
+        }
+        part = spl_warp_sum(part);
+        if (j == 0) total = part;
     }
     __syncthreads();
-    float sum = 0.0f, acc = 0.0f;
-    for (int s = 0; s < p.spans; ++s) if (weights[s] > 0.0f) sum += base[s * record + 1] * weights[s];
+    const float sum = total;
+    float acc = 0.0f;
     int s = 0;
+    for (; s + 8 <= p.spans; s += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = base[(s + u) * record + 2 + j];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) if (weights[s + u] > 0.0f) acc += v[u] * weights[s + u];
+    }
     for (; s + 4 <= p.spans; s += 4) {
         float v[4];
 #pragma unroll
