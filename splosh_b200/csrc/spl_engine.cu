@@ -489,6 +489,9 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
     GemmExtras scaled; scaled.in_squares = e->xn_squares; scaled.in_dim = H; scaled.eps = g.eps;
     bool fits = true;
     int linear_index = 0, full_index = 0;
+    // The conv kernel cuts long runs in segments of rows, a block each: as many as the step's longest run has.
+    int conv_segments = 1;
+    for (uint32_t r = 0; r < t->run_count; ++r) conv_segments = std::max(conv_segments, int((t->runs[r * 3 + 2] + SPL_GDN_CONV_SEGMENT - 1) / SPL_GDN_CONV_SEGMENT));
     for (int l = 0; l < g.layers; ++l) {
         const LayerWeights &L = e->layers[l];
         const int live = (l + 1 == g.layers) ? int(t->live_rows) : R;
@@ -506,7 +509,7 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
             p.rows = R; p.runs = int(t->run_count); p.channels = sh.C; p.key_heads = g.gdn_key_heads; p.value_heads = g.gdn_value_heads;
             p.head_dim = g.gdn_head_dim; p.proj_ld = L.in_proj.ld; p.z_offset = sh.gdn_z; p.a_offset = sh.gdn_a; p.b_offset = sh.gdn_b; p.eps = g.eps; p.chunk_min = chunked_runs > 0 ? e->gdn_chunk_min : 0; p.out_file_order = e->gdn_out_file_order ? 1 : 0;
             profile_begin(e, KLASS_GDN, 0);
-            launch_step(spl_gdn_conv_kernel, dim3(dim3((sh.C + 255) / 256, t->run_count)), dim3(256), 0, e->stream, 
+            launch_step(spl_gdn_conv_kernel, dim3(dim3((sh.C + 255) / 256, t->run_count, conv_segments)), dim3(256), 0, e->stream, 
                 e->proj, L.vec[SPL_VEC_CONV], e->conv[linear_index], e->d_runs, e->d_row_read, e->d_row_write, e->gdn_act, p);
             profile_end(e);
             profile_begin(e, KLASS_GDN, 0);

@@ -33,7 +33,13 @@ __device__ __forceinline__ int spl_gdn_out_head(const SplGdnParams &p, int h) {
 
 // Conv (k = 4, depthwise, no bias) + SiLU over every channel of every run; then the conv history
 // of every unit a row writes: the last three raw inputs up to and including that row
-// (engine.metal:707-728, 838-849). Grid (ceil(channels / 256), runs), 256 threads.
+// (engine.metal:707-728, 838-849). Grid (ceil(channels / 256), runs, segments), 256 threads: a long run (a prompt chunk) is
+// cut in segments of SPL_GDN_CONV_SEGMENT rows, each a block of its own (the filter has no recurrence: a row needs the
+// three rows before it, which a later segment reads from the projection itself). The units are written by the run's first
+// segment only, after it has read the history it starts from: a speculative run (at most 16 rows) is one segment, and an
+// ordinary run writes one unit, the slot's current one, at its last row, which the first segment does from the run's last
+// three inputs, so the block that reads a unit is the block that overwrites it.
+#define SPL_GDN_CONV_SEGMENT 128
 __global__ void __launch_bounds__(256)
 spl_gdn_conv_kernel(const float *__restrict__ proj, const uint16_t *__restrict__ conv_weight, float *conv_state,
                     const uint32_t *__restrict__ runs, const uint32_t *__restrict__ row_read, const uint32_t *__restrict__ row_write,
@@ -42,32 +48,44 @@ spl_gdn_conv_kernel(const float *__restrict__ proj, const uint16_t *__restrict__
     const int c = blockIdx.x * 256 + threadIdx.x;
     if (c >= p.channels) return;
     const uint32_t start = runs[blockIdx.y * 3 + 1], length = runs[blockIdx.y * 3 + 2];
-    const float *hist = conv_state + (size_t(row_read[start]) * p.channels + c) * 3;
-    float x3 = hist[0], x2 = hist[1], x1 = hist[2];
+    const uint32_t first = blockIdx.z * SPL_GDN_CONV_SEGMENT, last = min(length, first + SPL_GDN_CONV_SEGMENT);
+    if (first >= length) return;
+    float x3, x2, x1;
+    if (first == 0) {
+        const float *hist = conv_state + (size_t(row_read[start]) * p.channels + c) * 3;
+        x3 = hist[0]; x2 = hist[1]; x1 = hist[2];
+    } else {
+        x3 = proj[size_t(start + first - 3) * p.proj_ld + c]; x2 = proj[size_t(start + first - 2) * p.proj_ld + c]; x1 = proj[size_t(start + first - 1) * p.proj_ld + c];
+    }
     const float w0 = spl_bf16_to_float(conv_weight[c * 4]), w1 = spl_bf16_to_float(conv_weight[c * 4 + 1]);
     const float w2 = spl_bf16_to_float(conv_weight[c * 4 + 2]), w3 = spl_bf16_to_float(conv_weight[c * 4 + 3]);
     // Eight rows at a time: their inputs and the units they write are asked for together, then the rows are taken in order.
-    for (uint32_t base = 0; base < length; base += 8) {
+    for (uint32_t base = first; base < last; base += 8) {
         float xs[8];
         uint32_t unit[9];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) xs[u] = base + u < length ? proj[size_t(start + base + u) * p.proj_ld + c] : 0.0f;
+        for (int u = 0; u < 8; ++u) xs[u] = base + u < last ? proj[size_t(start + base + u) * p.proj_ld + c] : 0.0f;
 #pragma unroll
-        for (int u = 0; u < 9; ++u) unit[u] = base + u < length ? row_write[start + base + u] : 0xFFFFFFFFu;      // past the run: "another unit"
+        for (int u = 0; u < 9; ++u) unit[u] = (first == 0 && base + u < length) ? row_write[start + base + u] : 0xFFFFFFFFu;      // past the run: "another unit"
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            if (base + u < length) {
+            if (base + u < last) {
                 const uint32_t row = start + base + u;
                 const float x0 = xs[u];
                 const float y = ((w0 * x3 + w1 * x2) + w2 * x1) + w3 * x0;
                 act[size_t(row) * p.channels + c] = spl_silu_exact(y);
-                if (unit[u + 1] != unit[u]) {
+                if (first == 0 && unit[u + 1] != unit[u]) {
                     float *dst = conv_state + (size_t(unit[u]) * p.channels + c) * 3;
                     dst[0] = x2; dst[1] = x1; dst[2] = x0;
                 }
                 x3 = x2; x2 = x1; x1 = x0;
             }
         }
+    }
+    // A run of more than one segment (ordinary rows, one unit): its last row's unit from the run's last three inputs.
+    if (first == 0 && length > SPL_GDN_CONV_SEGMENT) {
+        float *dst = conv_state + (size_t(row_write[start + length - 1]) * p.channels + c) * 3;
+        dst[0] = proj[size_t(start + length - 3) * p.proj_ld + c]; dst[1] = proj[size_t(start + length - 2) * p.proj_ld + c]; dst[2] = proj[size_t(start + length - 1) * p.proj_ld + c];
     }
 }
 
