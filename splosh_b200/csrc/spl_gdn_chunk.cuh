@@ -230,7 +230,8 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
     int chunk = 0;
     for (; chunk < tables.chunk_count; ++chunk) if (tables.chunks[chunk * 4] == uint32_t(run)) break;
     const int chunks = int((length + C - 1) / C);
-    const int tq = tid >> 2, jq = tid & 3;          // U and O: token tq, values 4 jq .. + 3 of the slice
+    const int tq = tid >> 2, jq = tid & 3;          // U and O: token tq, values jq, jq + 4, jq + 8, jq + 12 of the slice (the four lanes of a token read
+                                                    // neighbouring rows of S, which the rows' padding puts in different banks)
     for (int n = 0; n < chunks; ++n, ++chunk) {
         const float *rec = records + (size_t(chunk) * VH + h) * SPL_GDN_REC_FLOATS;
         const uint32_t first = tables.chunks[chunk * 4 + 1], count = tables.chunks[chunk * 4 + 2];
@@ -243,19 +244,20 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
         // U[t][j] = Uv[t][j] - sum_i W[t][i] S[j][i];  O0[t][j] = sum_i (g q^)[t][i] S[j][i]
         float u[4], o[4];
         {
-            const float4 uv = *reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_UV + tq * D + slice * SL + jq * 4);
-            u[0] = uv.x; u[1] = uv.y; u[2] = uv.z; u[3] = uv.w;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) u[r] = rec[SPL_GDN_REC_UV + tq * D + slice * SL + jq + 4 * r];
 #pragma unroll
             for (int r = 0; r < 4; ++r) o[r] = 0.0f;
             for (int i = 0; i < D; i += 4) {
                 const float4 wv = *reinterpret_cast<const float4 *>(w_s + tq * LD + i);
 #pragma unroll
                 for (int r = 0; r < 4; ++r) {
-                    const float4 sv = *reinterpret_cast<const float4 *>(s_s + (jq * 4 + r) * (D + 4) + i);
+                    const float4 sv = *reinterpret_cast<const float4 *>(s_s + (jq + 4 * r) * (D + 4) + i);
                     u[r] -= wv.x * sv.x + wv.y * sv.y + wv.z * sv.z + wv.w * sv.w;
                 }
             }
-            *reinterpret_cast<float4 *>(u_s + tq * SL + jq * 4) = make_float4(u[0], u[1], u[2], u[3]);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) u_s[tq * SL + jq + 4 * r] = u[r];
         }
         __syncthreads();
         for (int idx = tid; idx < C * (D / 4); idx += 256)
@@ -265,36 +267,36 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
             const float4 qv = *reinterpret_cast<const float4 *>(w_s + tq * LD + i);
 #pragma unroll
             for (int r = 0; r < 4; ++r) {
-                const float4 sv = *reinterpret_cast<const float4 *>(s_s + (jq * 4 + r) * (D + 4) + i);
+                const float4 sv = *reinterpret_cast<const float4 *>(s_s + (jq + 4 * r) * (D + 4) + i);
                 o[r] += qv.x * sv.x + qv.y * sv.y + qv.z * sv.z + qv.w * sv.w;
             }
         }
         // O[t][j] = O0 + sum_{s<=t} P[t][s] U[s][j]; meanwhile the record's Kd replaces W in shared memory.
         for (int s = 0; s <= tq; ++s) {
             const float w = p_s[tq * PLD + s];
-            const float4 uv = *reinterpret_cast<const float4 *>(u_s + s * SL + jq * 4);
-            o[0] += w * uv.x; o[1] += w * uv.y; o[2] += w * uv.z; o[3] += w * uv.w;
+#pragma unroll
+            for (int r = 0; r < 4; ++r) o[r] += w * u_s[s * SL + jq + 4 * r];
         }
         if (tq < int(count))
-            *reinterpret_cast<float4 *>(o_raw + size_t(first + tq) * (size_t(VH) * D) + h * D + slice * SL + jq * 4) = make_float4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) o_raw[size_t(first + tq) * (size_t(VH) * D) + h * D + slice * SL + jq + 4 * r] = o[r];
         __syncthreads();          // every thread has finished with g q^
         for (int idx = tid; idx < C * (D / 4); idx += 256)
             *reinterpret_cast<float4 *>(w_s + (idx / (D / 4)) * LD + (idx % (D / 4)) * 4) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_KD)[idx];
         __syncthreads();
         // S[j][i] = g_C S[j][i] + sum_s U[s][j] Kd[s][i]: a thread one value row j and eight columns i.
         {
-            const int j = tid >> 4, i0 = (tid & 15) * 8;
-            float acc[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) acc[e] = g_end * s_s[j * (D + 4) + i0 + e];
+            const int j = tid >> 4, i0 = (tid & 15) * 4;      // columns i0 .. + 3 and 64 + i0 .. + 3: sixteen lanes read 16-byte pieces side by side
+            float4 lo = *reinterpret_cast<const float4 *>(s_s + j * (D + 4) + i0), hi = *reinterpret_cast<const float4 *>(s_s + j * (D + 4) + 64 + i0);
+            float acc[8] = {g_end * lo.x, g_end * lo.y, g_end * lo.z, g_end * lo.w, g_end * hi.x, g_end * hi.y, g_end * hi.z, g_end * hi.w};
             for (int s = 0; s < C; ++s) {
                 const float us = u_s[s * SL + j];
-                const float4 k0 = *reinterpret_cast<const float4 *>(w_s + s * LD + i0), k1 = *reinterpret_cast<const float4 *>(w_s + s * LD + i0 + 4);
+                const float4 k0 = *reinterpret_cast<const float4 *>(w_s + s * LD + i0), k1 = *reinterpret_cast<const float4 *>(w_s + s * LD + 64 + i0);
                 acc[0] += us * k0.x; acc[1] += us * k0.y; acc[2] += us * k0.z; acc[3] += us * k0.w;
                 acc[4] += us * k1.x; acc[5] += us * k1.y; acc[6] += us * k1.z; acc[7] += us * k1.w;
             }
-#pragma unroll
-            for (int e = 0; e < 8; ++e) s_s[j * (D + 4) + i0 + e] = acc[e];
+            *reinterpret_cast<float4 *>(s_s + j * (D + 4) + i0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            *reinterpret_cast<float4 *>(s_s + j * (D + 4) + 64 + i0) = make_float4(acc[4], acc[5], acc[6], acc[7]);
         }
         __syncthreads();
     }
