@@ -246,6 +246,7 @@ bool configure_device(int device, int *sms) {
         configure_gguf<16, SPL_GGUF_Q5K>(); configure_gguf<32, SPL_GGUF_Q5K>(); configure_gguf<64, SPL_GGUF_Q5K>();
         configure_gguf<16, SPL_GGUF_Q6K>(); configure_gguf<32, SPL_GGUF_Q6K>(); configure_gguf<64, SPL_GGUF_Q6K>();
         configure_scan<256, 6>(); configure_scan<128, 4>();
+        cudaFuncSetAttribute(spl_gdn_recurrence_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_gdn_recurrence_smem()));
         cudaFuncSetAttribute(spl_gdn_chunk_prepare_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_gdn_chunk_prepare_smem()));
         cudaFuncSetAttribute(spl_gdn_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_gdn_chunk_scan_smem()));
         cudaDeviceProp prop;
@@ -513,7 +514,7 @@ spl_status enqueue_step(spl_engine *e, const spl_tables *t) {
                 e->proj, L.vec[SPL_VEC_CONV], e->conv[linear_index], e->d_runs, e->d_row_read, e->d_row_write, e->gdn_act, p);
             profile_end(e);
             profile_begin(e, KLASS_GDN, 0);
-            launch_step(spl_gdn_recurrence_kernel, dim3(dim3(g.gdn_value_heads, t->run_count)), dim3(SPL_GDN_THREADS), 0, e->stream, 
+            launch_step(spl_gdn_recurrence_kernel, dim3(dim3(g.gdn_value_heads, t->run_count)), dim3(SPL_GDN_THREADS), spl_gdn_recurrence_smem(), e->stream, 
                 e->gdn_act, e->proj, L.vec[SPL_VEC_A_LOG], L.vec[SPL_VEC_DT_BIAS], L.vec[SPL_VEC_GDN_NORM], e->state[linear_index],
                 e->journal[linear_index], e->d_runs, e->d_run_info, core, p);
             profile_end(e);
@@ -1474,7 +1475,7 @@ spl_status commit_journal(spl_engine *e, int slot) {
     int linear = 0;
     for (size_t l = 0; l < e->layers.size(); ++l) {
         if (e->layers[l].full) continue;
-        spl_gdn_recurrence_kernel<<<dim3(e->g.gdn_value_heads, 1), SPL_GDN_THREADS, 0, e->stream>>>(
+        spl_gdn_recurrence_kernel<<<dim3(e->g.gdn_value_heads, 1), SPL_GDN_THREADS, spl_gdn_recurrence_smem(), e->stream>>>(
             e->gdn_act, e->proj, e->layers[l].vec[SPL_VEC_A_LOG], e->layers[l].vec[SPL_VEC_DT_BIAS], e->layers[l].vec[SPL_VEC_GDN_NORM],
             e->state[linear], e->journal[linear], e->tables_dev, e->tables_dev + 3, core, p);
         ++linear;

@@ -95,31 +95,55 @@ __device__ __forceinline__ float2 spl_gdn_update2(float2 s, float2 decay, float2
     return spl_fma2(s, decay, spl_mul2(k, delta));
 }
 
-#define SPL_GDN_TC 16          // tokens prepared per pass
+#define SPL_GDN_TC 8           // tokens per pass
 #define SPL_GDN_D 128          // head dim (key and value)
 #define SPL_GDN_THREADS 256
+#define SPL_GDN_PART_LD (SPL_GDN_TC * SPL_GDN_D + 4)      // floats from one column group's partial sums to the next's: four banks on
+
+// Dynamic shared memory of the recurrence kernel: q, k, v, o and the journal-form delta of a pass (5 x TC rows), the journal
+// entries to replay (k and delta, SPL_JOURNAL_ROWS rows each), the eight column groups' partial products, and the two
+// reduced products S0 k and S0 q (TC rows each).
+constexpr size_t spl_gdn_recurrence_smem() {
+    return sizeof(float) * (size_t(7 * SPL_GDN_TC + 2 * SPL_JOURNAL_ROWS) * SPL_GDN_D + 8 * SPL_GDN_PART_LD);
+}
 
 // One thread block per (value head, run): the head's whole 128 x 128 state in registers, a 4 x 16 tile a thread:
 // thread (rg = tid / 8, cg = tid % 8) keeps rows j = 4 rg + r (r < 4) at columns i = 32 c + 4 cg + e (c < 4, e < 4).
-// A token's k and q then cost a thread eight 16-byte loads from shared memory for 64 state elements (a thread that
-// held one row would load as much for 16 elements, and the kernel would be bound by shared-memory bandwidth); row
-// sums are combined over the eight threads of a row group by shuffles; there is no block barrier inside a pass.
-// Per token (engine.metal:763-805):
-//   mem = S k;  delta = (v - mem * decay * invK) * beta * invK;  S = S * decay + k (x) delta;
-//   o = (S q) * invQ
-// then the gated RMSNorm w * o * rsqrt(mean o^2 + eps) * silu(z) rounded to bf16, with its per-64
-// sums (engine.metal:812-833). A speculative run leaves a journal entry per row instead of writing
-// the state; entries accepted from the previous run are replayed first (engine.metal:744-761).
+// A token's k or q then costs a thread four 16-byte loads from shared memory for 64 state elements (a thread that
+// held one row would load as much for 16 elements, and the kernel would be bound by shared-memory bandwidth).
+// Per token (engine.metal:763-805), with k^ = k invK and q^ = q invQ:
+//   mem = S k;  delta = (v - mem * decay * invK) * beta * invK;  S = S * decay + k (x) delta;  o = (S q) * invQ
+// The tokens of a run are taken eight at a time (a pass), and inside a pass nothing waits for a state update: with
+// S0 the state at the start of the pass, G(t) the product of the decays up to token t and d^(t) = delta(t) / invK(t),
+//   decay(t) S(t-1) k^(t) = G(t) S0 k^(t) + sum over s < t of G(t)/G(s) (k^(s) . k^(t)) d^(s)
+//   d^(t) = beta(t) (v(t) - G(t) S0 k^(t)) - sum over s < t of A(t, s) d^(s),   A(t, s) = beta(t) G(t)/G(s) k^(t) . k^(s)
+//   o(t)  = G(t) S0 q^(t) + sum over s <= t of M(t, s) d^(s),                    M(t, s) = G(t)/G(s) q^(t) . k^(s)
+// so the pass is: the two 8 x 8 matrices (64-element half dots, two threads a dot), the products S0 k and S0 q for all
+// eight tokens at once (each thread its tile, partial sums over its 64 columns, the eight column groups added through
+// shared memory), then one thread a value row walks the eight tokens (a chain of multiply-adds on 8 x 8 numbers).
+// The token-serial form of the same pass was a chain of eight (product, reduce, update, product, reduce) rounds and
+// took five times as long.
+// The state moves on by the journal's own rule, S = S * decay + k (x) delta with the product rounded on its own
+// (engine.metal:654-659), applied entry by entry: to the entries accepted from the previous speculative run
+// (engine.metal:744-761), and to a pass's tokens when more of the run follows or an ordinary run writes its state.
+// A speculative run leaves a journal entry per row instead of writing the state, so the state it would reach and the
+// state a later replay reaches are the same numbers. Then the gated RMSNorm w * o * rsqrt(mean o^2 + eps) * silu(z)
+// rounded to bf16, with its per-64 sums (engine.metal:812-833).
 // Grid (value_heads, runs), 256 threads, two blocks to an SM.
 __global__ void __launch_bounds__(SPL_GDN_THREADS, 2)
 spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict__ proj, const uint16_t *__restrict__ a_log,
                           const uint16_t *__restrict__ dt_bias, const uint16_t *__restrict__ norm_weight, float *state, float *journal,
                           const uint32_t *__restrict__ runs, const uint32_t *__restrict__ run_info, SplOperand core, SplGdnParams p) {
-    spl_grid_begin();
-    constexpr int D = SPL_GDN_D, TC = SPL_GDN_TC, NT = SPL_GDN_THREADS, WARPS = NT / 32;
-    constexpr int ZT = (TC + WARPS - 1) / WARPS;      // tokens per warp in the norm passes
-    __shared__ __align__(16) float q_s[TC][D], k_s[TC][D], v_s[TC][D], o_s[TC][D], jk_s[TC][D];
-    __shared__ float scal[TC][4], jdecay[TC];        // invQ, invK, decay, beta per token; decay per replayed entry
+    constexpr int D = SPL_GDN_D, TC = SPL_GDN_TC, NT = SPL_GDN_THREADS, WARPS = NT / 32, PLD = SPL_GDN_PART_LD;
+    static_assert(TC == WARPS, "the norm passes give a warp a token");
+    extern __shared__ __align__(16) float gdn_smem[];
+    float (*q_s)[D] = reinterpret_cast<float (*)[D]>(gdn_smem);
+    float (*k_s)[D] = q_s + TC, (*v_s)[D] = k_s + TC, (*o_s)[D] = v_s + TC, (*d_s)[D] = o_s + TC;
+    float (*pm)[D] = d_s + TC, (*rm)[D] = pm + TC;
+    float (*jk_s)[D] = rm + TC, (*jd_s)[D] = jk_s + SPL_JOURNAL_ROWS;
+    float *part = &jd_s[SPL_JOURNAL_ROWS][0];
+    __shared__ float scal[TC][4], jdecay[SPL_JOURNAL_ROWS];        // invQ, invK, decay, beta per token; decay per replayed entry
+    __shared__ float gam[TC], a_m[TC][TC], m_m[TC][TC];
     const int h = blockIdx.x, run = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int rg = tid >> 3, cg = tid & 7;
     const uint32_t slot = runs[run * 3], start = runs[run * 3 + 1], length = runs[run * 3 + 2];
@@ -129,8 +153,10 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
     const int VH = p.value_heads, KH = p.key_heads, hk = h / (VH / KH);
     float *jhead = journal + (size_t(slot) * SPL_JOURNAL_ROWS * VH + h) * SPL_JOURNAL_WIDTH;
 
-    // Everything the block needs from memory is asked for before anything is waited for: the state, the journal entries
-    // to replay (k into jk_s, delta into o_s, which is free until the first token), and the first tokens' q, k, v.
+    // Everything the block needs from memory is asked for before anything is waited for, and what no kernel of this step
+    // has written (the state and the journal: the previous step's; the run tables: copied before the step's first kernel)
+    // before the wait for the kernels in front: a block that has come onto an SM while the conv kernel runs has its state
+    // on the way. The input projection's columns (gates, z) are two kernels back, the conv's output is one: after the wait.
     float2 S[4][4][2];          // [row r][column chunk c][pair]
     float4 *stored = reinterpret_cast<float4 *>(state + ((size_t(slot) * VH + h) * D + 4 * rg) * D) + cg;
 #pragma unroll
@@ -143,15 +169,77 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
     for (int idx = tid; idx < int(pending) * (2 * D / 4); idx += NT) {
         const int e = idx / (2 * D / 4), i4 = idx % (2 * D / 4);
         const float4 v = *reinterpret_cast<const float4 *>(jhead + size_t(e) * VH * SPL_JOURNAL_WIDTH + i4 * 4);
-        float *dst = i4 < D / 4 ? &jk_s[e][i4 * 4] : &o_s[e][i4 * 4 - D];
+        float *dst = i4 < D / 4 ? &jk_s[e][i4 * 4] : &jd_s[e][i4 * 4 - D];
         *reinterpret_cast<float4 *>(dst) = v;
     }
     if (tid < int(pending)) jdecay[tid] = jhead[size_t(tid) * VH * SPL_JOURNAL_WIDTH + 2 * D];
+    // The first pass's gate inputs and z, one warp a token.
+    float gate_a0 = 0.0f, gate_b0 = 0.0f;
+    float4 z0 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (uint32_t(warp) < length) {
+        const size_t row = start + warp;
+        if (lane == 0) { gate_a0 = proj[row * p.proj_ld + p.a_offset + h]; gate_b0 = proj[row * p.proj_ld + p.b_offset + h]; }
+        z0 = *reinterpret_cast<const float4 *>(proj + row * p.proj_ld + p.z_offset + h * D + lane * 4);
+    }
+    spl_grid_begin();
     const float neg_a = -expf(spl_bf16_to_float(a_log[h])), bias = spl_bf16_to_float(dt_bias[h]);
+
+    // One journal-form update of the thread's tile.
+    auto apply = [&](const float *k_row, const float *delta_row, float decay) {
+        const float4 d4 = *reinterpret_cast<const float4 *>(delta_row + 4 * rg);
+        const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
+        const float2 c2 = make_float2(decay, decay);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float4 kv = *reinterpret_cast<const float4 *>(k_row + 32 * c + 4 * cg);
+#pragma unroll
+            for (int r = 0; r < 4; ++r) {
+                const float2 d2 = make_float2(dl[r], dl[r]);
+                S[r][c][0] = spl_gdn_update2(S[r][c][0], c2, make_float2(kv.x, kv.y), d2);
+                S[r][c][1] = spl_gdn_update2(S[r][c][1], c2, make_float2(kv.z, kv.w), d2);
+            }
+        }
+    };
+    // The thread's partial sums of S x for the pass's tokens (x = k or q), into its column group's plane of `part`.
+    auto product = [&](float (*x_s)[D], int count) {
+#pragma unroll
+        for (int tt = 0; tt < TC; ++tt) {
+            if (tt < count) {
+                float4 xv[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) xv[c] = *reinterpret_cast<const float4 *>(&x_s[tt][32 * c + 4 * cg]);
+                float sum[4];
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    float2 ma = make_float2(0.0f, 0.0f), mb = make_float2(0.0f, 0.0f);
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        ma = spl_fma2(S[r][c][0], make_float2(xv[c].x, xv[c].y), ma);
+                        mb = spl_fma2(S[r][c][1], make_float2(xv[c].z, xv[c].w), mb);
+                    }
+                    sum[r] = (ma.x + ma.y) + (mb.x + mb.y);
+                }
+                *reinterpret_cast<float4 *>(part + cg * PLD + tt * D + 4 * rg) = make_float4(sum[0], sum[1], sum[2], sum[3]);
+            }
+        }
+    };
+    // The eight column groups' partial sums added in a fixed order: four (token, row) pairs a thread.
+    auto reduce = [&](float (*dst)[D], int count) {
+#pragma unroll
+        for (int n = 0; n < TC * D / NT; ++n) {
+            const int idx = tid + NT * n, tt = idx / D, j = idx % D;
+            if (tt < count) {
+                float total = part[tt * D + j];
+#pragma unroll
+                for (int g = 1; g < 8; ++g) total += part[g * PLD + tt * D + j];
+                dst[tt][j] = total;
+            }
+        }
+    };
 
     // A run of no rows with entries to replay is a journal commit (Engine.commitJournal, Engine.swift:889-903): one pass, no tokens.
     for (uint32_t base = 0; base < length || (base == 0 && pending != 0); base += TC) {
-        const int count = min(uint32_t(TC), length - base);
+        const int count = int(min(uint32_t(TC), length - base));
         if (base != 0) __syncthreads();
         // q, k, v of up to TC tokens; one warp a token for the norms and the gates.
         for (int idx = tid; idx < count * 3 * (D / 4); idx += NT) {
@@ -161,54 +249,56 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
             float *dst = kind == 0 ? q_s[tt] : kind == 1 ? k_s[tt] : v_s[tt];
             *reinterpret_cast<float4 *>(dst + i4 * 4) = v;
         }
-        // The gate inputs of this warp's tokens, for the scalars below.
-        float gate_a[ZT], gate_b[ZT];
-#pragma unroll
-        for (int n = 0; n < ZT; ++n) {
-            const int tt = warp + n * WARPS;
-            gate_a[n] = 0.0f; gate_b[n] = 0.0f;
-            if (tt < count && lane == 0) {
-                const size_t row = start + base + tt;
-                gate_a[n] = proj[row * p.proj_ld + p.a_offset + h]; gate_b[n] = proj[row * p.proj_ld + p.b_offset + h];
-            }
+        float gate_a = gate_a0, gate_b = gate_b0;
+        if (base != 0 && warp < count && lane == 0) {
+            const size_t row = start + base + warp;
+            gate_a = proj[row * p.proj_ld + p.a_offset + h]; gate_b = proj[row * p.proj_ld + p.b_offset + h];
         }
         __syncthreads();
-#pragma unroll
-        for (int n = 0; n < ZT; ++n) {
-            const int tt = warp + n * WARPS;
-            if (tt < count) {
-                const float4 qv = *reinterpret_cast<const float4 *>(&q_s[tt][lane * 4]);
-                const float4 kv = *reinterpret_cast<const float4 *>(&k_s[tt][lane * 4]);
-                const float qq = spl_warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
-                const float kk = spl_warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
-                if (lane == 0) {
-                    scal[tt][0] = (1.0f / sqrtf(qq + 1e-6f)) * (1.0f / sqrtf(float(D)));
-                    scal[tt][1] = 1.0f / sqrtf(kk + 1e-6f);
-                    const float x = gate_a[n] + bias;
-                    const float softplus = x > 20.0f ? x : logf(1.0f + expf(x));
-                    scal[tt][2] = expf(neg_a * softplus);
-                    scal[tt][3] = spl_sigmoid(gate_b[n]);
+        if (warp < count) {
+            const float4 qv = *reinterpret_cast<const float4 *>(&q_s[warp][lane * 4]);
+            const float4 kv = *reinterpret_cast<const float4 *>(&k_s[warp][lane * 4]);
+            const float qq = spl_warp_sum(qv.x * qv.x + qv.y * qv.y + qv.z * qv.z + qv.w * qv.w);
+            const float kk = spl_warp_sum(kv.x * kv.x + kv.y * kv.y + kv.z * kv.z + kv.w * kv.w);
+            if (lane == 0) {
+                scal[warp][0] = (1.0f / sqrtf(qq + 1e-6f)) * (1.0f / sqrtf(float(D)));
+                scal[warp][1] = 1.0f / sqrtf(kk + 1e-6f);
+                const float x = gate_a + bias;
+                const float softplus = x > 20.0f ? x : logf(1.0f + expf(x));
+                scal[warp][2] = expf(neg_a * softplus);
+                scal[warp][3] = spl_sigmoid(gate_b);
+            }
+        }
+        __syncthreads();      // the tokens' scalars are written
+        if (count > 0) {
+            // The two matrices: thread = (which, t, s, half of the 128 channels).
+            const int which = tid >> 7, t = (tid >> 4) & 7, s = (tid >> 1) & 7, half = tid & 1;
+            const bool wanted = t < count && (which ? s <= t : s < t);
+            float dot = 0.0f;
+            if (wanted) {
+                const float *x = which ? q_s[t] : k_s[t], *y = k_s[s];
+#pragma unroll 4
+                for (int m = 0; m < D / 8; ++m) {
+                    const float4 a = *reinterpret_cast<const float4 *>(x + 4 * (half + 2 * m)), b = *reinterpret_cast<const float4 *>(y + 4 * (half + 2 * m));
+                    dot += (a.x * b.x + a.y * b.y) + (a.z * b.z + a.w * b.w);
                 }
+            }
+            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+            if (wanted && half == 0) {
+                float ratio = 1.0f;
+                for (int u = s + 1; u <= t; ++u) ratio *= scal[u][2];
+                if (which) m_m[t][s] = ratio * dot * scal[t][0] * scal[s][1];
+                else a_m[t][s] = scal[t][3] * ratio * dot * scal[t][1] * scal[s][1];
+            }
+            if (tid < count) {
+                float g = 1.0f;
+                for (int u = 0; u <= tid; ++u) g *= scal[u][2];
+                gam[tid] = g;
             }
         }
         if (base == 0 && pending != 0) {
             // Replay the accepted entries; a speculative run then stores the state it starts from.
-            for (uint32_t e = 0; e < pending; ++e) {
-                const float4 d4 = *reinterpret_cast<const float4 *>(&o_s[e][4 * rg]);
-                const float dl[4] = {d4.x, d4.y, d4.z, d4.w};
-                const float decay = jdecay[e];
-                const float2 c2 = make_float2(decay, decay);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const float4 kv = *reinterpret_cast<const float4 *>(&jk_s[e][32 * c + 4 * cg]);
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        const float2 d2 = make_float2(dl[r], dl[r]);
-                        S[r][c][0] = spl_gdn_update2(S[r][c][0], c2, make_float2(kv.x, kv.y), d2);
-                        S[r][c][1] = spl_gdn_update2(S[r][c][1], c2, make_float2(kv.z, kv.w), d2);
-                    }
-                }
-            }
+            for (uint32_t e = 0; e < pending; ++e) apply(jk_s[e], jd_s[e], jdecay[e]);
             if (speculative) {
 #pragma unroll
                 for (int r = 0; r < 4; ++r)
@@ -216,84 +306,64 @@ spl_gdn_recurrence_kernel(const float *__restrict__ act, const float *__restrict
                     for (int c = 0; c < 4; ++c) stored[r * (D / 4) + 8 * c] = make_float4(S[r][c][0].x, S[r][c][0].y, S[r][c][1].x, S[r][c][1].y);
             }
         }
-        __syncthreads();      // the tokens' scalars are written; the replay has finished with o_s
-        for (int tt = 0; tt < count; ++tt) {
-            const float inv_q = scal[tt][0], inv_k = scal[tt][1], decay = scal[tt][2], beta = scal[tt][3];
-            float4 kv[4], qv[4];
+        if (count == 0) break;
+        product(k_s, count);
+        __syncthreads();
+        reduce(pm, count);
+        __syncthreads();      // the partial sums of S0 k have been read
+        product(q_s, count);
+        __syncthreads();
+        reduce(rm, count);
+        __syncthreads();
+        if (tid < D) {
+            const int j = tid;
+            float dh[TC];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                kv[c] = *reinterpret_cast<const float4 *>(&k_s[tt][32 * c + 4 * cg]);
-                qv[c] = *reinterpret_cast<const float4 *>(&q_s[tt][32 * c + 4 * cg]);
-            }
-            float mem[4];
+            for (int t = 0; t < TC; ++t) {
+                if (t < count) {
+                    float x = scal[t][3] * (v_s[t][j] - gam[t] * scal[t][1] * pm[t][j]);
 #pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                float2 ma = make_float2(0.0f, 0.0f), mb = make_float2(0.0f, 0.0f);
+                    for (int s = 0; s < t; ++s) x -= a_m[t][s] * dh[s];
+                    dh[t] = x;
+                    float o = gam[t] * scal[t][0] * rm[t][j];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    ma = spl_fma2(S[r][c][0], make_float2(kv[c].x, kv[c].y), ma);
-                    mb = spl_fma2(S[r][c][1], make_float2(kv[c].z, kv[c].w), mb);
+                    for (int s = 0; s <= t; ++s) o += m_m[t][s] * dh[s];
+                    o_s[t][j] = o;
+                    d_s[t][j] = x * scal[t][1];
                 }
-                mem[r] = (ma.x + ma.y) + (mb.x + mb.y);
-            }
-#pragma unroll
-            for (int w = 1; w < 8; w <<= 1)
-#pragma unroll
-                for (int r = 0; r < 4; ++r) mem[r] += __shfl_xor_sync(0xffffffffu, mem[r], w);
-            const float4 v4 = *reinterpret_cast<const float4 *>(&v_s[tt][4 * rg]);
-            const float vl[4] = {v4.x, v4.y, v4.z, v4.w};
-            float delta[4], o[4];
-            const float2 c2 = make_float2(decay, decay);
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                delta[r] = (vl[r] - mem[r] * decay * inv_k) * beta * inv_k;
-                const float2 d2 = make_float2(delta[r], delta[r]);
-                float2 oa = make_float2(0.0f, 0.0f), ob = make_float2(0.0f, 0.0f);
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    S[r][c][0] = spl_gdn_update2(S[r][c][0], c2, make_float2(kv[c].x, kv[c].y), d2);
-                    S[r][c][1] = spl_gdn_update2(S[r][c][1], c2, make_float2(kv[c].z, kv[c].w), d2);
-                    oa = spl_fma2(S[r][c][0], make_float2(qv[c].x, qv[c].y), oa);
-                    ob = spl_fma2(S[r][c][1], make_float2(qv[c].z, qv[c].w), ob);
-                }
-                o[r] = (oa.x + oa.y) + (ob.x + ob.y);
-            }
-#pragma unroll
-            for (int w = 1; w < 8; w <<= 1)
-#pragma unroll
-                for (int r = 0; r < 4; ++r) o[r] += __shfl_xor_sync(0xffffffffu, o[r], w);
-            if (cg == 0) *reinterpret_cast<float4 *>(&o_s[tt][4 * rg]) = make_float4(o[0] * inv_q, o[1] * inv_q, o[2] * inv_q, o[3] * inv_q);
-            if (speculative) {
-                float *entry = jhead + size_t(base + tt) * VH * SPL_JOURNAL_WIDTH;
-                if (tid < D / 4) *reinterpret_cast<float4 *>(entry + 4 * tid) = *reinterpret_cast<const float4 *>(&k_s[tt][4 * tid]);
-                if (cg == 0) *reinterpret_cast<float4 *>(entry + D + 4 * rg) = make_float4(delta[0], delta[1], delta[2], delta[3]);
-                if (tid == 0) entry[2 * D] = decay;
             }
         }
         __syncthreads();
-        // Gated RMSNorm and the bf16 operand, one warp a token.
-#pragma unroll
-        for (int n = 0; n < ZT; ++n) {
-            const int tt = warp + n * WARPS;
-            if (tt < count) {
-                const size_t row = start + base + tt;
-                const float4 z = *reinterpret_cast<const float4 *>(proj + row * p.proj_ld + p.z_offset + h * D + lane * 4);
-                const float4 ov = *reinterpret_cast<const float4 *>(&o_s[tt][lane * 4]);
-                const float inv = 1.0f / sqrtf(spl_warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w) / float(D) + p.eps);
-                const uint2 w = *reinterpret_cast<const uint2 *>(norm_weight + lane * 4);
-                const float r0 = spl_bf16_to_float(uint16_t(w.x)) * ov.x * inv * spl_silu_exact(z.x);
-                const float r1 = spl_bf16_to_float(uint16_t(w.x >> 16)) * ov.y * inv * spl_silu_exact(z.y);
-                const float r2 = spl_bf16_to_float(uint16_t(w.y)) * ov.z * inv * spl_silu_exact(z.z);
-                const float r3 = spl_bf16_to_float(uint16_t(w.y >> 16)) * ov.w * inv * spl_silu_exact(z.w);
-                const uint16_t b0 = spl_float_to_bf16(r0), b1 = spl_float_to_bf16(r1), b2 = spl_float_to_bf16(r2), b3 = spl_float_to_bf16(r3);
-                *reinterpret_cast<uint2 *>(core.values + core.at(int(row), spl_gdn_out_head(p, h) * D + lane * 4)) =
-                    spl_operand_pack4(spl_bf16_to_float(b0), spl_bf16_to_float(b1), spl_bf16_to_float(b2), spl_bf16_to_float(b3));
-                // The following GEMM's per-64 sums: a 128-wide head is two quant groups, sixteen lanes each.
-                float gsum = (spl_bf16_to_float(b0) + spl_bf16_to_float(b1)) + (spl_bf16_to_float(b2) + spl_bf16_to_float(b3));
-#pragma unroll
-                for (int o2 = 8; o2 > 0; o2 >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o2);
-                if ((lane & 15) == 0) core.put_sum(int(row), spl_gdn_out_head(p, h) * 2 + (lane >> 4), gsum);
+        if (speculative) {
+            for (int idx = tid; idx < count * (2 * D / 4); idx += NT) {
+                const int tt = idx / (2 * D / 4), i4 = idx % (2 * D / 4);
+                float *entry = jhead + size_t(base + tt) * VH * SPL_JOURNAL_WIDTH;
+                *reinterpret_cast<float4 *>(entry + 4 * i4) = i4 < D / 4 ? *reinterpret_cast<const float4 *>(&k_s[tt][4 * i4]) : *reinterpret_cast<const float4 *>(&d_s[tt][4 * i4 - D]);
             }
+            if (tid < count) jhead[size_t(base + tid) * VH * SPL_JOURNAL_WIDTH + 2 * D] = scal[tid][2];
+        }
+        if (!speculative || base + TC < length)
+            for (int tt = 0; tt < count; ++tt) apply(k_s[tt], d_s[tt], scal[tt][2]);
+        // Gated RMSNorm and the bf16 operand, one warp a token.
+        if (warp < count) {
+            const int tt = warp;
+            const size_t row = start + base + tt;
+            const float4 z = base == 0 ? z0 : *reinterpret_cast<const float4 *>(proj + row * p.proj_ld + p.z_offset + h * D + lane * 4);
+            const float4 ov = *reinterpret_cast<const float4 *>(&o_s[tt][lane * 4]);
+            const float inv = 1.0f / sqrtf(spl_warp_sum(ov.x * ov.x + ov.y * ov.y + ov.z * ov.z + ov.w * ov.w) / float(D) + p.eps);
+            const uint2 w = *reinterpret_cast<const uint2 *>(norm_weight + lane * 4);
+            const float r0 = spl_bf16_to_float(uint16_t(w.x)) * ov.x * inv * spl_silu_exact(z.x);
+            const float r1 = spl_bf16_to_float(uint16_t(w.x >> 16)) * ov.y * inv * spl_silu_exact(z.y);
+            const float r2 = spl_bf16_to_float(uint16_t(w.y)) * ov.z * inv * spl_silu_exact(z.z);
+            const float r3 = spl_bf16_to_float(uint16_t(w.y >> 16)) * ov.w * inv * spl_silu_exact(z.w);
+            const uint16_t b0 = spl_float_to_bf16(r0), b1 = spl_float_to_bf16(r1), b2 = spl_float_to_bf16(r2), b3 = spl_float_to_bf16(r3);
+            *reinterpret_cast<uint2 *>(core.values + core.at(int(row), spl_gdn_out_head(p, h) * D + lane * 4)) =
+                spl_operand_pack4(spl_bf16_to_float(b0), spl_bf16_to_float(b1), spl_bf16_to_float(b2), spl_bf16_to_float(b3));
+            // The following GEMM's per-64 sums: a 128-wide head is two quant groups, sixteen lanes each.
+            float gsum = (spl_bf16_to_float(b0) + spl_bf16_to_float(b1)) + (spl_bf16_to_float(b2) + spl_bf16_to_float(b3));
+#pragma unroll
+            for (int o2 = 8; o2 > 0; o2 >>= 1) gsum += __shfl_xor_sync(0xffffffffu, gsum, o2);
+            if ((lane & 15) == 0) core.put_sum(int(row), spl_gdn_out_head(p, h) * 2 + (lane >> 4), gsum);
         }
     }
     if (!speculative) {
