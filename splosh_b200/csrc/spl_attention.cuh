@@ -114,7 +114,7 @@ spl_attn_prepare_kernel(const float *__restrict__ proj, const uint16_t *__restri
 // warp reduction (redux) plus a four-way exchange; sums stay per thread until the end of the span.
 // When a maximum moves, the softmax warps rescale O^T in tensor memory before the next value product.
 //
-// Warps: 0-3 and 16-19 softmax (the first half and the second half of the queries), rescale and the partial's output,
+// Warps: 0-3, 16-19 (and 20-23 with three groups) softmax (a share of the queries each), rescale and the partial's output,
 // 4-7 K -> tensor memory, 8-11 V -> tensor memory, 12 and 15 copies (bulk copies of whole 128-token chunks into rings),
 // 13 and 14 tensor-core issue of the score and the value product. Every wait is bounded.
 // Tensor memory (512 columns): S two buffers of NQ columns at 0, O two halves of NQ columns at 96, K operand a ring
@@ -124,7 +124,11 @@ spl_attn_prepare_kernel(const float *__restrict__ proj, const uint16_t *__restri
 #define SPL_ATTN_PSCALE 64.0f         // 4096 / 2^headroom: keeps small probabilities normal in fp16 and large ones finite; removed at the end
 struct SplTrue { static constexpr bool value = true; };
 struct SplFalse { static constexpr bool value = false; };
-#define SPL_ATTN_THREADS 640
+// Softmax warp groups: a group has a share of the queries (the columns of S^T) and four warps, one per quarter of the chunk's
+// tokens (a warp reaches the tensor-memory lanes of its index mod 4). The softmax warps are the block's critical path (busy
+// nine tenths of a chunk's time with two groups), so a 48-column block has three groups of 16 columns.
+__host__ __device__ constexpr int spl_attn_groups(int nq) { return nq % 48 == 0 ? 3 : 2; }
+__host__ __device__ constexpr int spl_attn_threads(int nq) { return 384 + 128 * spl_attn_groups(nq); }
 
 __host__ __device__ constexpr int spl_attn_nq(int per_kv) { return (8 * per_kv + 15) / 16 * 16; }
 // Shared-memory rings of 128-token chunks. K is converted as soon as it lands, so two stages do; V waits for the
@@ -180,16 +184,16 @@ __device__ __forceinline__ uint32_t spl_sw128_offset(int row, int k) {
 }
 
 template <int HD, int PER_KV>
-__global__ void __launch_bounds__(SPL_ATTN_THREADS, 1)
+__global__ void __launch_bounds__(spl_attn_threads(spl_attn_nq(PER_KV)), 1)
 spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ blocks, const uint32_t *__restrict__ row_slot,
                      const uint32_t *__restrict__ row_pos, const uint32_t *__restrict__ page_table, const int8_t *__restrict__ k_codes,
                      const float *__restrict__ k_scale, const int8_t *__restrict__ v_codes, const float *__restrict__ v_scale,
                      float *partials, SplAttnParams p, int *error_flag) {
     spl_grid_begin();
-    constexpr int NQ = spl_attn_nq(PER_KV), NH = NQ / 2, CH = SPL_ATTN_CH, NKS = spl_attn_k_stages(HD), NVS = spl_attn_v_stages(HD), NSS = SPL_ATTN_S_STAGES;
+    constexpr int NQ = spl_attn_nq(PER_KV), GROUPS = spl_attn_groups(NQ), NH = NQ / GROUPS, SW = 4 * GROUPS, NTHREADS = spl_attn_threads(NQ), CH = SPL_ATTN_CH, NKS = spl_attn_k_stages(HD), NVS = spl_attn_v_stages(HD), NSS = SPL_ATTN_S_STAGES;
     constexpr int HALVES = HD / 128, QGROUPS = HD / 64, CHUNK_BYTES = CH * HD, QTILE = NQ * 128, PTILE = 2 * NQ * 128;
     constexpr float LOG2E = 1.4426950408889634f, LN2 = 0.6931471805599453f;
-    static_assert(NH % 8 == 0 && NQ <= 48, "two softmax groups of NQ / 2 queries, eight at a time; tensor memory holds two S and two O of NQ columns below column 192");
+    static_assert(NH % 8 == 0 && NQ <= 48, "softmax groups of NQ / GROUPS queries, eight at a time; tensor memory holds two S and two O of NQ columns below column 192");
     extern __shared__ unsigned char spl_attn_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(spl_attn_smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char *q_tile = smem;                                   // [QGROUPS][NQ rows x 128 B]   B operand of the score product
@@ -222,15 +226,15 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
     if (tid == 0) {
         for (int i = 0; i < NKS; ++i) { spl_mbar_init(&full_k[i], 1); spl_mbar_init(&empty_k[i], 4); }        // the K warps
         for (int i = 0; i < NVS; ++i) { spl_mbar_init(&full_v[i], 1); spl_mbar_init(&empty_v[i], 4); }        // the V warps
-        for (int i = 0; i < NSS; ++i) { spl_mbar_init(&full_sc[i], 1); spl_mbar_init(&empty_sc[i], 8); }      // the softmax warps
+        for (int i = 0; i < NSS; ++i) { spl_mbar_init(&full_sc[i], 1); spl_mbar_init(&empty_sc[i], SW); }      // the softmax warps
         for (int i = 0; i < 3; ++i) { spl_mbar_init(&ka_full[i], 4); spl_mbar_init(&ka_free[i], 1); }
         for (int i = 0; i < 2; ++i) {
             spl_mbar_init(&va_full[i], 4); spl_mbar_init(&va_free[i], 1);
-            spl_mbar_init(&s_full[i], 1); spl_mbar_init(&s_free[i], 8); spl_mbar_init(&p_full[i], 8); spl_mbar_init(&p_free[i], 1);
-            spl_mbar_init(&o_done[i], 1); spl_mbar_init(&x_full[i], 8); spl_mbar_init(&y_full[i], 8);
+            spl_mbar_init(&s_full[i], 1); spl_mbar_init(&s_free[i], SW); spl_mbar_init(&p_full[i], SW); spl_mbar_init(&p_free[i], 1);
+            spl_mbar_init(&o_done[i], 1); spl_mbar_init(&x_full[i], SW); spl_mbar_init(&y_full[i], SW);
             xflag[i] = 0;
         }
-        spl_mbar_init(sum_full, 8);
+        spl_mbar_init(sum_full, SW);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 13) {
@@ -238,7 +242,7 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     // Queries into the swizzled operand tile, zero for padding rows: 16-byte pieces of eight channels.
-    for (int idx = tid; idx < NQ * (HD / 8); idx += SPL_ATTN_THREADS) {
+    for (int idx = tid; idx < NQ * (HD / 8); idx += NTHREADS) {
         const int m = idx / (HD / 8), piece = idx % (HD / 8);
         const int rb = m / PER_KV, hq = m % PER_KV, g = piece >> 3, k8 = piece & 7;
         uint4 v = make_uint4(0, 0, 0, 0);
@@ -436,8 +440,8 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
         if (warp == 8) SPL_AOUT(44, 4);
     } else if (warp < 4 || warp >= 16) {
         // ---- softmax: thread = token of the chunk (scores), = channel of a half (rescale and output); the warp group
-        // (0-3 or 16-19) has the first or the second half of the queries.
-        const int w4 = warp & 3, token = w4 * 32 + lane, sg = warp >= 16 ? 1 : 0, cb = sg * NH;       // cb: first query column of the group
+        // (warps 0-3, 16-19, 20-23) has its share of the queries.
+        const int w4 = warp & 3, token = w4 * 32 + lane, sg = warp < 4 ? 0 : (warp - 12) >> 2, cb = sg * NH;       // cb: first query column of the group
         const uint32_t lane_base = uint32_t(w4 * 32) << 16;
         float *my_next = ref_next + w4 * NQ + cb, *my_factor = ref_factor + w4 * NQ + cb;      // this warp's copy: no cross-warp hazards
         float sum[NH];              // sum of p per query over this thread's tokens; reduced over lanes and warps at the end of the span

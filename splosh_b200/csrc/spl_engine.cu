@@ -394,7 +394,7 @@ bool launch_gemm(spl_engine *e, const SplQ4Dev &w, const GemmOperand &op, float 
 template <int HD, int PER_KV>
 void launch_scan_tc(spl_engine *e, dim3 grid, const SplAttnParams &p, int layer) {
     const size_t smem = spl_attn_smem_bytes(HD, spl_attn_nq(PER_KV));
-    launch_step(spl_attn_scan_kernel<HD, PER_KV>, dim3(grid), dim3(SPL_ATTN_THREADS), smem, e->stream, e->q, e->d_blocks, e->d_row_slot, e->d_row_pos, e->d_page_table,
+    launch_step(spl_attn_scan_kernel<HD, PER_KV>, dim3(grid), dim3(spl_attn_threads(spl_attn_nq(PER_KV))), smem, e->stream, e->q, e->d_blocks, e->d_row_slot, e->d_row_pos, e->d_page_table,
         e->k_codes[layer], e->k_scale[layer], e->v_codes[layer], e->v_scale[layer], e->attn_partials, p, e->tc_error);
 }
 // The scan is built for the head shapes in use: head_dim 256 with six query heads per kv head, and head_dim 128 with four.
