@@ -236,6 +236,17 @@ spl_status spl_weights_gguf_file_order(spl_engine *engine, int32_t enabled);
  * spl_weights_gguf_file_order switched on; ssm_a (-exp(A_log)) turned into A_log; an MTP block left out; a file without
  * output.weight ties the head to the embedding. `message` (may be null) receives what was wrong with the file. */
 spl_status spl_weights_load_gguf_file(spl_engine *engine, const char *path, char *message, size_t message_bytes);
+/* An SPLW artifact, the reference's own weight container (Sources/SploshModel/WeightFile.swift:88-141, Converter.swift:46-82),
+ * of a model of the engine's geometry into the engine: the tensors of ModelWeights.resolve (Sources/SploshModel/ModelWeights.swift:181-248)
+ * under "language_model.", each checked against the geometry. Formats "mlxAffine4" (row-major triplets) and
+ * "mlxAffine4.tiled128" (Sources/SploshModel/Retile.swift: eligible triplets in tiles of 128 rows, put back in rows on the
+ * way); 8-bit packs and GGUF-derived artifacts ("gguf.tiled128") are refused with a message. `message` (may be null)
+ * receives what was wrong with the file, in the reference's words where it has them. */
+spl_status spl_weights_load_splw_file(spl_engine *engine, const char *path, char *message, size_t message_bytes);
+/* The container's own checks without an engine or a GPU (framing, header, quantization, alignment, every record's bounds,
+ * order, alignment and padding, no unaccounted bytes): SPL_OK with the header's format in `message` and the record count in
+ * `tensors` (may be null), or SPL_ERR_INVALID_ARGUMENT with the reason. */
+spl_status spl_splw_check(const char *path, int32_t *tensors, char *message, size_t message_bytes);
 spl_status spl_engine_geometry(const spl_engine *engine, spl_geometry *out);
 /* Benchmarking: pseudo-random GGUF blocks for every tensor (`block_type`) and for the embedding and head
  * (`head_type`), generated on the device. */

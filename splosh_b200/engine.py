@@ -187,6 +187,8 @@ def lib():
             "spl_weights_synthesize_gguf": (i32, [vp, u64, i32, i32]),
             "spl_weights_gguf_file_order": (i32, [vp, i32]),
             "spl_weights_load_gguf_file": (i32, [vp, C.c_char_p, C.c_char_p, C.c_size_t]),
+            "spl_weights_load_splw_file": (i32, [vp, C.c_char_p, C.c_char_p, C.c_size_t]),
+            "spl_splw_check": (i32, [C.c_char_p, C.POINTER(C.c_int32), C.c_char_p, C.c_size_t]),
             "spl_step": (i32, [vp, C.POINTER(_Row), i32, C.POINTER(_Stats)]),
             "spl_step_launch": (i32, [vp, C.POINTER(_Row), i32]),
             "spl_step_wait": (i32, [vp, C.POINTER(_Stats)]),
@@ -520,6 +522,13 @@ class Engine:
         if status:
             raise EngineError(status, message.value.decode() or "spl_weights_load_gguf_file failed")
 
+    def load_splw_file(self, path):
+        """Every tensor of an SPLW artifact of this geometry (spl_weights_load_splw_file)."""
+        message = C.create_string_buffer(512)
+        status = lib().spl_weights_load_splw_file(self.handle, os.fsencode(path), message, len(message))
+        if status:
+            raise EngineError(status, message.value.decode() or "spl_weights_load_splw_file failed")
+
     def synthesize_gguf(self, seed, block_kind="Q5_K", head_kind="Q6_K"):
         self._check(lib().spl_weights_synthesize_gguf(self.handle, seed, GGUF_TYPE[block_kind], GGUF_TYPE[head_kind]))
 
@@ -704,6 +713,16 @@ class Engine:
 
 
 RESIDENT = ["in_proj", "out_proj", "gate_up", "down", "head"]
+
+
+def splw_check(path):
+    """The container checks of an SPLW artifact, no engine needed (spl_splw_check): (format, tensor records)."""
+    message = C.create_string_buffer(512)
+    count = C.c_int32(0)
+    status = lib().spl_splw_check(os.fsencode(path), C.byref(count), message, len(message))
+    if status:
+        raise EngineError(status, message.value.decode() or "spl_splw_check failed")
+    return message.value.decode(), count.value
 
 
 def gemm_q4_static(engine, layer, which, device_activations, rows, device_residual, device_out, stream=None):
