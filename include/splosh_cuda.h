@@ -240,9 +240,15 @@ spl_status spl_weights_load_gguf_file(spl_engine *engine, const char *path, char
  * of a model of the engine's geometry into the engine: the tensors of ModelWeights.resolve (Sources/SploshModel/ModelWeights.swift:181-248)
  * under "language_model.", each checked against the geometry. Formats "mlxAffine4" (row-major triplets) and
  * "mlxAffine4.tiled128" (Sources/SploshModel/Retile.swift: eligible triplets in tiles of 128 rows, put back in rows on the
- * way); 8-bit packs and GGUF-derived artifacts ("gguf.tiled128") are refused with a message. `message` (may be null)
+ * way), and the GGUF-derived "gguf.tiled128" (Sources/SploshModel/GgufConvert.swift:1-33: every 2-D weight as three planes,
+ * put back into native Q4_K / Q5_K / Q6_K blocks; the out projections in file order, so spl_weights_gguf_file_order is
+ * switched on); 8-bit packs are refused with a message. `message` (may be null)
  * receives what was wrong with the file, in the reference's words where it has them. */
 spl_status spl_weights_load_splw_file(spl_engine *engine, const char *path, char *message, size_t message_bytes);
+/* GgufPlanes.unpack (Sources/SploshModel/GgufPlanes.swift:150-190): the three planes of a Q4_K (12), Q5_K (13) or Q6_K (14)
+ * weight, each in tiles of 128 rows (planes of rows rounded up to 128), back into native blocks [rows][inner / 256][144, 176
+ * or 210 bytes]. `plane1` may be null for Q4_K. Host code. */
+spl_status spl_gguf_planes_unpack(int32_t type, const uint8_t *plane0, const uint8_t *plane1, const uint8_t *meta, int32_t rows, int32_t inner, uint8_t *native);
 /* The container's own checks without an engine or a GPU (framing, header, quantization, alignment, every record's bounds,
  * order, alignment and padding, no unaccounted bytes): SPL_OK with the header's format in `message` and the record count in
  * `tensors` (may be null), or SPL_ERR_INVALID_ARGUMENT with the reason. */

@@ -13,8 +13,13 @@
 // "mlxAffine4.tiled128" (the same tensors with the triplets of eligible weights permuted to [tile of 128 rows][group][row in
 // tile][32 bytes of codes] and [tile][group][row] for the sidecars; eligible = name under "language_model." ending in
 // ".weight", not the embedding, rows a multiple of 128). Both are read; the tiled form is put back in rows on the way.
-// The 8-bit packs ("mlxAffine8...") and the GGUF-derived artifacts ("gguf.tiled128", planes of llama.cpp's blocks) are
-// refused with a message: the engine's affine tensors are 4-bit, and a GGUF model goes in through spl_weights_load_gguf_file.
+// A GGUF-derived artifact ("gguf.tiled128", Sources/SploshModel/GgufConvert.swift:1-33) has the same names and dense tensors
+// (value heads already in the engine's order, the out projection's columns in the file's) and holds every 2-D weight as the
+// three planes of Sources/SploshModel/GgufPlanes.swift, records <base>.weight (plane 0, with the ggml type and the logical
+// shape), <base>.plane1 and <base>.meta, rows padded to whole tiles of 128 with zero blocks; the planes are put back into
+// llama.cpp's native blocks (spl_gguf_planes_unpack) and go in through spl_weights_set_gguf, and the engine is told that
+// the out projections are in file order. Q4_K, Q5_K and Q6_K weights; the 8-bit affine packs ("mlxAffine8...") are refused
+// with a message: the engine's affine tensors are 4-bit.
 #include <fcntl.h>
 #include <string.h>
 #include <sys/mman.h>
@@ -126,8 +131,8 @@ struct JsonReader {
 struct Record {
     std::string name, dtype;
     std::vector<int64_t> shape, physical, logical;
-    bool has_logical = false;
-    uint64_t offset = 0, bytes = 0, padding = 0;
+    bool has_logical = false, has_type = false;
+    uint64_t offset = 0, bytes = 0, padding = 0, gguf_type = 0;
 };
 
 bool integer_of(const Json *j, uint64_t *out) { if (!j || j->kind != Json::Number || !j->is_integer) return false; *out = j->integer; return true; }
@@ -186,6 +191,8 @@ struct Container {
             r.name = name->text; r.dtype = dtype->text;
             const Json *logical = item.get("logicalShape");
             if (logical && logical->kind != Json::Null) { if (!shape_of(logical, &r.logical)) return fail("malformed header"); r.has_logical = true; }
+            const Json *type = item.get("ggufType");
+            if (type && type->kind != Json::Null) { if (!integer_of(type, &r.gguf_type)) return fail("malformed header"); r.has_type = true; }
             if (!names.insert(r.name).second) return fail("duplicate tensor: " + r.name);
             static const char *const known[] = {"BF16", "F32", "F16", "U32", "I32", "I64", "U8"};
             if (std::find_if(known, known + 7, [&](const char *k) { return r.dtype == k; }) == known + 7) return fail("unknown dtype: " + r.name);
@@ -216,13 +223,96 @@ void untile(const uint8_t *src, uint8_t *dst, int64_t rows, int64_t groups, int 
         }
 }
 
+// ---- the planes of a GGUF weight (GgufPlanes.swift:1-20) back into native blocks ----
+// A weight of `rows` x `inner` is held as records per (row, group of 32 inputs) in two code planes and per (row, native
+// block of 256) in a meta plane, each plane in tiles of 128 rows: record (row, b of n a row) sits at
+// ((row / 128) * n + b) * 128 + row % 128. Inside a group element e has slot 8 ((e >> 2) & 3) + 4 (e >> 4) + (e & 3).
+// Plane 0 holds a slot's low four bits: word s / 8 of the record's four, at bit 16 (s & 1) + 4 ((s & 7) >> 1). Plane 1 holds
+// the bits above them as a little-endian string of fields (one bit a slot for Q5_K, two for Q6_K). The meta record is the
+// block's scale fields: bytes 0-15 of a Q4_K or Q5_K block; a Q6_K block's sixteen scales (its bytes 192-207), then d (208-209)
+// and two zero bytes.
+struct PlaneShape { int plane1_bytes, meta_bytes, block_bytes, high_width; };
+bool plane_shape(int type, PlaneShape *out) {
+    switch (type) {
+    case 12: *out = {0, 16, 144, 0}; return true;
+    case 13: *out = {4, 16, 176, 1}; return true;
+    case 14: *out = {8, 20, 210, 2}; return true;
+    }
+    return false;
+}
+size_t plane_record(int64_t row, int64_t index, int64_t per_row) { return size_t(((row / 128) * per_row + index) * 128 + row % 128); }
+int plane_slot(int e) { return 8 * ((e >> 2) & 3) + 4 * (e >> 4) + (e & 3); }
+
+// `rows` logical rows out of planes that hold `stored_rows` (a multiple of 128); native: [rows][inner / 256][block bytes].
+bool planes_unpack(int type, const uint8_t *plane0, const uint8_t *plane1, const uint8_t *meta, int64_t rows, int64_t inner, uint8_t *native) {
+    PlaneShape shape;
+    if (!plane_shape(type, &shape) || rows <= 0 || inner <= 0 || inner % 256 != 0) return false;
+    const int64_t groups = inner / 32, blocks = inner / 256;
+    memset(native, 0, size_t(rows * blocks * shape.block_bytes));
+    for (int64_t row = 0; row < rows; ++row)
+        for (int64_t group = 0; group < groups; ++group) {
+            const int64_t block = group / 8; const int j = int(group % 8);
+            uint8_t *b = native + (row * blocks + block) * shape.block_bytes;
+            const uint8_t *codes = plane0 + plane_record(row, group, groups) * 16;
+            const uint8_t *high = shape.plane1_bytes ? plane1 + plane_record(row, group, groups) * size_t(shape.plane1_bytes) : nullptr;
+            uint32_t words[4], high_words[2] = {0, 0};
+            memcpy(words, codes, 16);
+            if (high) memcpy(high_words, high, size_t(shape.plane1_bytes));
+            for (int e = 0; e < 32; ++e) {
+                const int s = plane_slot(e);
+                const uint8_t low = uint8_t((words[s >> 3] >> (16 * (s & 1) + 4 * ((s & 7) >> 1))) & 15u);
+                uint8_t top = 0;
+                if (shape.high_width) { const int per_word = 32 / shape.high_width; top = uint8_t((high_words[s / per_word] >> (shape.high_width * (s % per_word))) & ((1u << shape.high_width) - 1u)); }
+                if (type == 14) {
+                    const int half = j / 4, quarter = j % 4;
+                    b[64 * half + 32 * (quarter & 1) + e] |= uint8_t(low << (4 * (quarter >> 1)));
+                    b[128 + 32 * half + e] |= uint8_t(top << (2 * quarter));
+                } else {
+                    b[(type == 13 ? 48 : 16) + 32 * (j / 2) + e] |= uint8_t(low << (4 * (j % 2)));
+                    if (type == 13) b[16 + e] |= uint8_t(top << j);
+                }
+            }
+            if (j == 0) {
+                const uint8_t *fields = meta + plane_record(row, block, blocks) * size_t(shape.meta_bytes);
+                if (type == 14) { memcpy(b + 192, fields, 16); memcpy(b + 208, fields + 16, 2); }
+                else memcpy(b, fields, 16);
+            }
+        }
+    return true;
+}
+
 struct Loader {
-    spl_engine *engine; spl_geometry g; Container *file; const uint8_t *base; bool tiled; std::string error;
+    spl_engine *engine; spl_geometry g; Container *file; const uint8_t *base; bool tiled = false, gguf = false; std::string error;
     bool fail(const std::string &what) { if (error.empty()) error = what; return false; }
     const Record *find(const std::string &name) { auto it = file->by_name.find("language_model." + name); return it == file->by_name.end() ? nullptr : it->second; }
 
     // One MLX affine-4 triplet by the name of its weight (WeightFile.q4, WeightFile.swift:202-240) into the engine.
+    // One GGUF weight by the name of its plane 0 (WeightFile.gguf, WeightFile.swift:155-199) into the engine as native blocks.
+    bool planes(const std::string &name, int layer, int kind, int64_t rows, int64_t inner) {
+        const Record *w = find(name + ".weight"), *m = find(name + ".meta"), *h = find(name + ".plane1");
+        if (!w) return fail("missing tensor language_model." + name + ".weight");
+        if (w->dtype != "U8") return fail(name + ".weight is " + w->dtype + ", not U8");
+        PlaneShape shape;
+        if (!w->has_type || !plane_shape(int(w->gguf_type), &shape)) return fail(name + ".weight is not a GGUF weight of a type the engine takes (Q4_K, Q5_K, Q6_K)");
+        if (!w->has_logical || w->logical.size() != 2 || w->logical[0] <= 0 || w->logical[1] <= 0) return fail(name + ".weight has no logical shape [rows, inner]");
+        if (w->logical[0] != rows || w->logical[1] != inner) return fail(name + " does not have the geometry's shape");
+        if (inner % 256 != 0) return fail(name + ": a row of " + std::to_string(inner) + " is not a whole number of blocks");
+        const int64_t stored = (rows + 127) / 128 * 128, groups = inner / 32;
+        auto plane = [&](const Record *r, const std::string &which, int64_t bytes) {
+            if (!r) return fail(name + ".weight has no " + which);
+            const std::vector<int64_t> expected = {stored, bytes / stored};
+            if (r->dtype != "U8" || r->bytes != uint64_t(bytes) || r->shape != expected) return fail(which + " does not have the size its type and logical shape give it");
+            return true;
+        };
+        if (!plane(w, name + ".weight", stored * groups * 16) || !plane(m, name + ".meta", stored * (groups / 8) * shape.meta_bytes)) return false;
+        if (shape.plane1_bytes ? !plane(h, name + ".plane1", stored * groups * shape.plane1_bytes) : h != nullptr) return fail(shape.plane1_bytes ? error : name + ".weight has no second plane, yet " + name + ".plane1 exists");
+        std::unique_ptr<uint8_t[]> native(new uint8_t[size_t(rows * (inner / 256) * shape.block_bytes)]);
+        if (!planes_unpack(int(w->gguf_type), base + w->offset, h ? base + h->offset : nullptr, base + m->offset, rows, inner, native.get())) return fail(name + ": the planes cannot be unpacked");
+        if (spl_weights_set_gguf(engine, layer, kind, int32_t(w->gguf_type), int32_t(rows), int32_t(inner), native.get()) != SPL_OK) return fail(name + ": " + spl_last_error_string(engine));
+        return true;
+    }
     bool q4(const std::string &name, int layer, int kind, int64_t rows, int64_t inner) {
+        if (gguf) return planes(name, layer, kind, rows, inner);
         const Record *w = find(name + ".weight"), *s = find(name + ".scales"), *b = find(name + ".biases");
         if (!w) return fail("missing tensor language_model." + name + ".weight");
         if (w->dtype != "U32") return fail(name + ".weight is " + w->dtype + ", not U32");
@@ -277,7 +367,10 @@ struct Loader {
             if (!dense(p + "input_layernorm.weight", layer, SPL_VEC_INPUT_NORM, {H}) || !dense(p + "post_attention_layernorm.weight", layer, SPL_VEC_POST_NORM, {H}) ||
                 !q4(p + "mlp.gate_proj", layer, SPL_Q4_GATE, g.inter, H) || !q4(p + "mlp.up_proj", layer, SPL_Q4_UP, g.inter, H) || !q4(p + "mlp.down_proj", layer, SPL_Q4_DOWN, H, g.inter)) return false;
         }
-        return q4("model.embed_tokens", -1, SPL_Q4_EMBED, g.vocab, H) && q4("lm_head", -1, SPL_Q4_HEAD, g.vocab, H) && dense("model.norm.weight", -1, SPL_VEC_FINAL_NORM, {H});
+        if (!q4("model.embed_tokens", -1, SPL_Q4_EMBED, g.vocab, H) || !q4("lm_head", -1, SPL_Q4_HEAD, g.vocab, H) || !dense("model.norm.weight", -1, SPL_VEC_FINAL_NORM, {H})) return false;
+        // A GGUF-derived artifact leaves the out projections' columns in the file's order of the value heads (GgufConvert.swift:18-24).
+        if (gguf && spl_weights_gguf_file_order(engine, 1) != SPL_OK) return fail(spl_last_error_string(engine));
+        return true;
     }
 };
 
@@ -305,6 +398,12 @@ spl_status say(char *message, size_t message_bytes, const std::string &text, spl
 
 }  // namespace
 
+extern "C" spl_status spl_gguf_planes_unpack(int32_t type, const uint8_t *plane0, const uint8_t *plane1, const uint8_t *meta, int32_t rows, int32_t inner, uint8_t *native) {
+    PlaneShape shape;
+    if (!plane_shape(type, &shape) || !plane0 || !meta || !native || (shape.plane1_bytes && !plane1)) return SPL_ERR_INVALID_ARGUMENT;
+    return planes_unpack(type, plane0, plane1, meta, rows, inner, native) ? SPL_OK : SPL_ERR_INVALID_ARGUMENT;
+}
+
 extern "C" spl_status spl_splw_check(const char *path, int32_t *tensors, char *message, size_t message_bytes) {
     if (tensors) *tensors = 0;
     if (!path) return say(message, message_bytes, "null argument", SPL_ERR_INVALID_ARGUMENT);
@@ -331,8 +430,8 @@ extern "C" spl_status spl_weights_load_splw_file(spl_engine *engine, const char 
     if (!container.parse(static_cast<const uint8_t *>(file.map == MAP_FAILED ? nullptr : file.map), file.size)) return say(message, message_bytes, "weight file invalid: " + container.error, SPL_ERR_INVALID_ARGUMENT);
     if (container.format == "mlxAffine4") loader.tiled = false;
     else if (container.format == "mlxAffine4.tiled128") loader.tiled = true;
-    else if (container.format == "gguf.tiled128") return say(message, message_bytes, "a GGUF-derived artifact (planes of llama.cpp's blocks): load the GGUF file itself with spl_weights_load_gguf_file", SPL_ERR_INVALID_ARGUMENT);
-    else return say(message, message_bytes, "format " + container.format + " is not mlxAffine4 or mlxAffine4.tiled128", SPL_ERR_INVALID_ARGUMENT);
+    else if (container.format == "gguf.tiled128") loader.gguf = true;
+    else return say(message, message_bytes, "format " + container.format + " is not mlxAffine4, mlxAffine4.tiled128 or gguf.tiled128", SPL_ERR_INVALID_ARGUMENT);
     loader.file = &container; loader.base = static_cast<const uint8_t *>(file.map);
     if (!loader.load()) return say(message, message_bytes, loader.error, SPL_ERR_INVALID_ARGUMENT);
     return say(message, message_bytes, "", SPL_OK);

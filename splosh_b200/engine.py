@@ -189,6 +189,7 @@ def lib():
             "spl_weights_load_gguf_file": (i32, [vp, C.c_char_p, C.c_char_p, C.c_size_t]),
             "spl_weights_load_splw_file": (i32, [vp, C.c_char_p, C.c_char_p, C.c_size_t]),
             "spl_splw_check": (i32, [C.c_char_p, C.POINTER(C.c_int32), C.c_char_p, C.c_size_t]),
+            "spl_gguf_planes_unpack": (i32, [i32, vp, vp, vp, i32, i32, vp]),
             "spl_step": (i32, [vp, C.POINTER(_Row), i32, C.POINTER(_Stats)]),
             "spl_step_launch": (i32, [vp, C.POINTER(_Row), i32]),
             "spl_step_wait": (i32, [vp, C.POINTER(_Stats)]),
@@ -723,6 +724,19 @@ def splw_check(path):
     if status:
         raise EngineError(status, message.value.decode() or "spl_splw_check failed")
     return message.value.decode(), count.value
+
+
+def gguf_planes_unpack(kind, plane0, plane1, meta, rows, inner):
+    """The three planes of a GGUF weight back into native blocks (spl_gguf_planes_unpack): uint8 [rows][inner / 256][block bytes]."""
+    import numpy as np
+    type_id, block = {"Q4_K": (12, 144), "Q5_K": (13, 176), "Q6_K": (14, 210)}[kind]
+    native = np.zeros((rows, inner // 256, block), np.uint8)
+    p0, pm = np.ascontiguousarray(plane0, np.uint8), np.ascontiguousarray(meta, np.uint8)
+    p1 = None if plane1 is None else np.ascontiguousarray(plane1, np.uint8)
+    status = lib().spl_gguf_planes_unpack(type_id, _ptr(p0), None if p1 is None else _ptr(p1), _ptr(pm), rows, inner, _ptr(native))
+    if status:
+        raise EngineError(status, "spl_gguf_planes_unpack refused its arguments")
+    return native
 
 
 def gemm_q4_static(engine, layer, which, device_activations, rows, device_residual, device_out, stream=None):

@@ -107,3 +107,23 @@ def test_an_alignment_other_than_128_is_honoured(model, tmp_path):
     path = str(tmp_path / "a256.splw")
     splw_writer.write(path, g, m, alignment=256)
     assert S.engine.splw_check(path)[0] == "mlxAffine4"
+
+
+@pytest.mark.parametrize("kind", ["Q4_K", "Q5_K", "Q6_K"])
+def test_planes_unpack_to_the_native_blocks_they_were_made_of(kind):
+    """GgufPlanes.unpack (Sources/SploshModel/GgufPlanes.swift:150-190) undoes the repack for every bit of a block: random
+    blocks, 200 rows (two tiles, the second padded), through the tests' restatement of the repack and back through
+    spl_gguf_planes_unpack."""
+    rng = np.random.default_rng(7)
+    block_bytes = splw_writer.PLANES[kind][1]
+    blocks = rng.integers(0, 256, (200, 3, block_bytes), dtype=np.uint8)
+    p0, p1, meta = splw_writer.planes_of(kind, blocks)
+    assert p0.size == 256 * 24 * 16 and meta.size == 256 * 3 * splw_writer.PLANES[kind][3]
+    native = S.engine.gguf_planes_unpack(kind, p0, p1, meta, 200, 768)
+    assert np.array_equal(native, blocks)
+    # One element of one row: its nibble is where the layout says (row 130 = tile 1, row 2; group 9; element 21 -> slot 13).
+    if kind != "Q6_K":
+        record = p0.reshape(2, 24, 128, 16)[1, 9, 2]
+        word = int.from_bytes(bytes(record[4:8]), "little")
+        codes = 48 if kind == "Q5_K" else 16
+        assert (word >> (16 * (13 & 1) + 4 * ((13 & 7) >> 1))) & 15 == (int(blocks[130, 1, codes + 32 * 0 + 21]) >> 4) & 15
