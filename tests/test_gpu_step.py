@@ -26,7 +26,7 @@ from oracle import tables as T
 
 pytestmark = pytest.mark.gpu
 LOGIT_TOL = 3e-2
-SLICE_TOL = 8e-2      # the 27B-shape slice: contractions of 5,120 to 17,408 instead of 1,024 to 2,816
+SLICE_TOL = 7.5e-2      # the 27B-shape slice: contractions of 5,120 to 17,408 instead of 1,024 to 2,816
 
 
 def check(got, ref, vocab, label="", tol=LOGIT_TOL):
