@@ -232,6 +232,7 @@ template <int RN> void configure_gemm() {
     cudaFuncSetAttribute(spl_gemm_q4_tc_kernel<RN, SPL_TC_EMIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_tc_smem_bytes(RN)));
     cudaFuncSetAttribute(spl_gemm_q4_tc_kernel<RN, SPL_TC_FUSE>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_tc_smem_bytes(RN)));
     if constexpr (RN < 128) cudaFuncSetAttribute(spl_gemm_q4_narrow_kernel<RN>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_tc_smem_bytes(RN)));
+    if constexpr (RN == 128) cudaFuncSetAttribute(spl_gemm_q4_narrow_kernel<128, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_tc_pair_smem_bytes()));
 }
 template <int RN, int FMT> void configure_gguf() { cudaFuncSetAttribute(spl_gemm_gguf_tc_kernel<RN, FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_gguf_smem_bytes(RN, FMT))); }
 template <int HD, int PER_KV> void configure_scan() { cudaFuncSetAttribute(spl_attn_scan_kernel<HD, PER_KV>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(spl_attn_smem_bytes(HD, spl_attn_nq(PER_KV)))); }
@@ -265,6 +266,8 @@ bool configure_device(int device, int *sms) {
 // Test switch (spl_debug_drop_weight_stage): the q4 GEMM's weight-copy role leaves out this stage of every block's piece, so
 // the roles that wait for it run out of time. -1: off.
 static int g_drop_weight_stage = -1;
+// Test switch (spl_debug_pair_blocks): 0 keeps prompt chunks on the one-tile 128-row block.
+static int g_pair_blocks = 1;
 
 struct GemmCut { int pieces, splits; };
 GemmCut gemm_cut(const SplQ4Dev &w, int sms, int rn, int row_blocks, bool whole) {
@@ -284,7 +287,11 @@ GemmCut gemm_cut(const SplQ4Dev &w, int sms, int rn, int row_blocks, bool whole)
 // partials[split][row][column] (cut tiles, and every tile when the output feeds a deferred norm: `emit`).
 size_t gemm_slot_floats(const SplQ4Dev &w, int sms, int rn, int row_blocks, bool emit, bool whole) {
     const GemmCut cut = gemm_cut(w, sms, rn, row_blocks, whole);
-    if (rn >= 128) return spl_tc_slot_floats(cut.pieces, cut.splits, row_blocks, rn);
+    if (rn >= 128) {
+        // The pair form (two row blocks and more, every tile whole) leaves an output that feeds a deferred norm to the second kernel.
+        const size_t pair = (row_blocks >= 2 && cut.splits == 1 && emit) ? size_t(row_blocks) * rn * w.ld : 0;
+        return std::max(spl_tc_slot_floats(cut.pieces, cut.splits, row_blocks, rn), pair);
+    }
     const int stages = w.k / 256, per = (stages + cut.splits - 1) / cut.splits, splits = (stages + per - 1) / per;
     return (splits > 1 || emit) ? size_t(splits) * row_blocks * rn * w.ld : 0;
 }
@@ -326,6 +333,26 @@ bool launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &o
                         residual, out, x.emit_weight, emit_out, x.emit_squares);
         }
         return true;
+    }
+    if constexpr (RN == 128) {
+        // Prompt chunks (two row blocks and more, so every tile is whole): the pair form, two tiles of the weight a block.
+        if (g_pair_blocks && row_blocks >= 2 && cut.splits == 1 && (w.k / 64) % 2 == 0) {
+            const bool second = x.emit_weight != nullptr;
+            const size_t rows_padded = size_t(op.blocks) * RN;
+            if (second && rows_padded * w.ld > scratch.slot_floats) return false;
+            launch_step(spl_gemm_q4_narrow_kernel<128, true>, dim3(((w.tiles + 1) / 2) * row_blocks), block, spl_tc_pair_smem_bytes(), stream, (const uint32_t *)w.codes, (const uint32_t *)w.sb, op.values, op.sums,
+                        out, w.ld, second ? (const float *)nullptr : residual, second ? scratch.slots : (float *)nullptr, rows, op.blocks, w.k / 64, w.k / 64, scratch.error_flag, w.interleave,
+                        a.act_out, a.fuse, x.in_squares, x.in_dim / 64, float(x.in_dim), x.eps, g_drop_weight_stage);
+            if (launches) ++*launches;
+            if (second) {
+                if (scratch.timed) { profile_end(scratch.timed); profile_begin(scratch.timed, KLASS_ELEMENTWISE, 0); }
+                else if (launches) ++*launches;
+                const long long warps = (long long)rows * ((w.ld + 63) / 64);
+                launch_step(spl_gemm_fixup_rows_kernel, dim3(int(std::min<long long>((warps + 7) / 8, 8LL * scratch.sms))), dim3(256), 0, stream, (const float *)scratch.slots, 1, int(rows_padded), rows, w.ld,
+                            residual, out, x.emit_weight, emit_out, x.emit_squares);
+            }
+            return true;
+        }
     }
     if (x.fuse_act) launch_step(spl_gemm_q4_tc_kernel<RN, SPL_TC_FUSE>, grid, block, spl_tc_smem_bytes(RN), stream, a);
     else if (x.emit_weight && cut.splits == 1) launch_step(spl_gemm_q4_tc_kernel<RN, SPL_TC_EMIT>, grid, block, spl_tc_smem_bytes(RN), stream, a);
@@ -1332,6 +1359,12 @@ spl_status spl_debug_wait_budget(spl_engine *e, int64_t nanoseconds) {
 spl_status spl_debug_drop_weight_stage(spl_engine *e, int32_t stage) {
     if (!e) return SPL_ERR_INVALID_ARGUMENT;
     g_drop_weight_stage = stage;
+    return SPL_OK;
+}
+
+spl_status spl_debug_pair_blocks(spl_engine *e, int32_t enabled) {
+    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+    g_pair_blocks = enabled ? 1 : 0;
     return SPL_OK;
 }
 

@@ -312,6 +312,15 @@ __device__ __forceinline__ void spl_set_barrier(int set) {
 #define SPL_TC_SETS 4            // dequant sets of four warps (a warp writes the tensor-memory lanes of its index mod 4); they take the units in turn
 #define SPL_TC_DEQUANT (SPL_TC_SETS * 128)
 #define SPL_TC_THREADS (SPL_TC_DEQUANT + 128)       // the sets; then a warp that copies weights, a tensor-core issue warp, a warp that copies activations, the other issue warp
+// The pair form of the 128-row block (prefill chunks of two row blocks and more): a block works on two tiles of the weight
+// against one stream of activations, a tile per issuing warp and accumulator. At the tensor pipe's full rate a 128 x 128 block
+// needs 64 bytes of activations a cycle from L2 (an instruction of K = 16 reads 4 KB of them and lasts 64 cycles), 148 SMs
+// three times what L2 delivers; with two tiles the same bytes feed twice the instructions. Tensor memory: two accumulators of
+// 128 columns, three operand slots of 64 with their 8 second-term columns (472 of 512). Shared memory: three stages of
+// activations (two groups: 32 KB), four of codes (two groups of each tile: 18 KB), the two tiles of split means.
+#define SPL_TC_PAIR_BSTAGES 3
+#define SPL_TC_PAIR_CSTAGES 4
+#define SPL_TC_PAIR_AUNITS 3
 
 // The shape of a block by its row count RN (the N of its tcgen05.mma). Narrow blocks (16, 32, 64 rows: decode and verify
 // steps) take stages of four groups and two issuing warps with an accumulator each. The wide block (128 rows: prefill
@@ -329,6 +338,9 @@ __host__ __device__ constexpr size_t spl_tc_bstage_bytes(int rn) { return size_t
 __host__ __device__ constexpr size_t spl_tc_smem_bytes(int rn) {
     return 1024 /* alignment slack */ + size_t(spl_tc_cstages(rn)) * spl_tc_super(rn) * (4096 + 512) + size_t(spl_tc_bstages(rn)) * spl_tc_bstage_bytes(rn)
            + size_t(2) * rn * 128 /* tiles of split means */ + SPL_TC_CONTROL_BYTES;
+}
+__host__ __device__ constexpr size_t spl_tc_pair_smem_bytes() {
+    return 1024 + size_t(SPL_TC_PAIR_CSTAGES) * SPL_TC_SUPER * (4096 + 512) + size_t(SPL_TC_PAIR_BSTAGES) * 2 * 128 * 128 + size_t(2) * 128 * 128 + SPL_TC_CONTROL_BYTES;
 }
 // Floats of the slot array a launch may write: none when every tile is one piece, else a slot of rn x 128 a block.
 __host__ __device__ constexpr size_t spl_tc_slot_floats(int pieces, int splits, int row_blocks, int rn) {
@@ -844,14 +856,16 @@ spl_gemm_q4_tc_kernel(const __grid_constant__ SplGemmArgs a) {
 // GEMM); with more it leaves its partial sums in partials[split][row][column] for spl_gemm_fixup_rows_kernel. Its
 // output stage is stores only: a block reaches it while the others still stream weights at the memory's full rate,
 // and a load issued then waits behind megabytes of queued copies.
-template <int RN>
+template <int RN, bool PAIR = false>
 __global__ void __launch_bounds__(SPL_TC_THREADS, 1)
 spl_gemm_q4_narrow_kernel(const uint32_t *__restrict__ codes, const uint32_t *__restrict__ sb, const __nv_bfloat16 *__restrict__ act,
                       const float *__restrict__ act_sums, float *out, int out_ld, const float *residual, float *partials,
                       int rows, int op_blocks, int groups, int groups_per_split, int *error_flag, int interleave, SplOperand act_out, int fuse,
                       const float *__restrict__ in_squares, int in_groups, float in_dim, float eps, int drop) {
-    constexpr int BST = spl_tc_bstages(RN), CST = spl_tc_cstages(RN), AUN = SPL_TC_AUNITS;
-    constexpr int BTILE = SPL_TC_SUPER * RN * 128, WSTAGE = SPL_TC_SUPER * 4096, QSTAGE = SPL_TC_SUPER * 128, TTILE = RN * 128;
+    static_assert(!PAIR || RN == 128, "the pair form is the 128-row block");
+    constexpr int GPS = PAIR ? 2 : SPL_TC_SUPER;       // groups of the contraction a stage covers (the pair form: two, for each of its two tiles)
+    constexpr int BST = PAIR ? SPL_TC_PAIR_BSTAGES : spl_tc_bstages(RN), CST = PAIR ? SPL_TC_PAIR_CSTAGES : spl_tc_cstages(RN), AUN = PAIR ? SPL_TC_PAIR_AUNITS : SPL_TC_AUNITS;
+    constexpr int BTILE = GPS * RN * 128, WSTAGE = SPL_TC_SUPER * 4096, QSTAGE = SPL_TC_SUPER * 128, TTILE = RN * 128;
     extern __shared__ unsigned char spl_tc_smem_raw[];
     // The swizzled activation tiles must sit on 1,024-byte boundaries.
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(spl_tc_smem_raw) + 1023) & ~uintptr_t(1023));
@@ -869,34 +883,55 @@ spl_gemm_q4_narrow_kernel(const uint32_t *__restrict__ codes, const uint32_t *__
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int W_COPY = SPL_TC_SETS * 4, W_MMA0 = W_COPY + 1, W_COPYB = W_COPY + 2, W_MMA1 = W_COPY + 3;
-    const int tile = blockIdx.x, split = blockIdx.y, rb = blockIdx.z, row_blocks = op_blocks;   // the operand's row blocks (>= gridDim.z)
+    // The pair form's grid is one-dimensional, the row block the fast index: the blocks that run together are then the row
+    // blocks of a few pairs, and a pair's weights come from HBM once and from L2 for the other row blocks.
+    const int run_blocks = PAIR ? (rows + RN - 1) / RN : 1;
+    const int tile = PAIR ? int(blockIdx.x) / run_blocks : int(blockIdx.x), split = PAIR ? 0 : int(blockIdx.y), rb = PAIR ? int(blockIdx.x) % run_blocks : int(blockIdx.z);
+    const int row_blocks = op_blocks;   // the operand's row blocks (>= the grid's)
+    const int tiles_all = (out_ld + 127) / 128;
+    const int tile0 = PAIR ? 2 * tile : tile, tile1 = PAIR ? min(2 * tile + 1, tiles_all - 1) : tile;      // an odd tensor's last pair does its one tile twice
+    const bool has1 = !PAIR || 2 * tile + 1 < tiles_all;
     const int rows_padded = op_blocks * RN;
     const int g_first = split * groups_per_split;
     const int g_count = min(groups_per_split, groups - g_first);
-    const int supers = (g_count + SPL_TC_SUPER - 1) / SPL_TC_SUPER;
-    const int units = (g_count + 1) / 2;            // a unit = two groups = one hand-over from a dequant set
+    const int supers = (g_count + GPS - 1) / GPS;
+    const int units = PAIR ? 2 * supers : (g_count + 1) / 2;            // a unit = two groups of one tile = one hand-over from a dequant set
     // Every block of a GEMM reads the same activation lines. Blocks therefore walk the contraction from
     // different starting points (the order of a sum of groups does not matter beyond fp32 rounding, and it
     // is a fixed function of the tile), so that at any moment they ask L2 for different lines.
-    const int rot = (g_count % SPL_TC_SUPER == 0 && supers > 1) ? int((uint32_t(tile) * 2654435761u >> 12) % uint32_t(supers)) : 0;
+    const int rot = (g_count % GPS == 0 && supers > 1) ? int((uint32_t(tile) * 2654435761u >> 12) % uint32_t(supers)) : 0;
 
     // The thread that copies weights sets up its own barriers and asks for the first stages at once: they are nobody's
     // output (no wait for the predecessor in the stream), and they travel while the block is still being set up.
     const int ahead = min(CST, supers);
     int issued_c = 0, issued_b = 0, issued_t = 0;       // stages and tiles of split means this thread has asked for (copy roles)
+    // Stage j of the block's share of the contraction into slot sc of the code ring: its codes and scale/bias words. The pair
+    // form brings two groups of each of its two tiles (tile 0's at the slot's start, tile 1's after them).
+    auto copy_codes = [&](int sc, int j, int n) {
+        if (PAIR) {
+            spl_mbar_expect_tx(&full_c[sc], 2u * uint32_t(n) * (4096 + 512));
+#pragma unroll
+            for (int m = 0; m < 2; ++m) {
+                const size_t first = size_t(m ? tile1 : tile0) * groups + g_first + size_t(j) * GPS;
+                spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE + m * (GPS * 4096), reinterpret_cast<const unsigned char *>(codes) + first * 4096, uint32_t(n) * 4096, &full_c[sc]);
+                spl_bulk_g2s(q_ring + sc * QSTAGE + m * (GPS * 128), sb + first * 128, uint32_t(n) * 512, &full_c[sc]);
+            }
+        } else {
+            const size_t first = size_t(tile) * groups + g_first + size_t(j) * GPS;
+            spl_mbar_expect_tx(&full_c[sc], uint32_t(n) * (4096 + 512));
+            spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, reinterpret_cast<const unsigned char *>(codes) + first * 4096, uint32_t(n) * 4096, &full_c[sc]);
+            spl_bulk_g2s(q_ring + sc * QSTAGE, sb + first * 128, uint32_t(n) * 512, &full_c[sc]);
+        }
+    };
     if (warp == W_COPY && lane == 0) {
-        const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(codes) + (size_t(tile) * groups + g_first) * 4096;
-        const uint32_t *qsrc = sb + (size_t(tile) * groups + g_first) * 128;
         for (int i = 0; i < CST; ++i) spl_mbar_init(&full_c[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         issued_c = ahead;
         for (int j0 = 0; j0 < ahead; ++j0) {
             const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
-            const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);
+            const int n = min(GPS, g_count - j0 * GPS);
             if (j0 == drop) continue;
-            spl_mbar_expect_tx(&full_c[j0], uint32_t(n) * (4096 + 512));
-            spl_bulk_g2s(w_ring + size_t(j0) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[j0]);
-            spl_bulk_g2s(q_ring + j0 * QSTAGE, qsrc + size_t(j) * QSTAGE, uint32_t(n) * 512, &full_c[j0]);
+            copy_codes(j0, j, n);
         }
     }
     if (warp == 0) {
@@ -926,27 +961,23 @@ spl_gemm_q4_narrow_kernel(const uint32_t *__restrict__ codes, const uint32_t *__
     const uint32_t tmem = *tmem_slot;                 // lane 0, first allocated column
     // Two accumulators, one per issuing warp (instructions of different warps are not ordered against each other);
     // the A ring, 64 columns a unit; the second-term operand, 8 columns a unit.
-    const uint32_t tmem_d = tmem, tmem_a = tmem + 128, tmem_aq = tmem + 128 + AUN * 64;
+    const uint32_t tmem_d = tmem, tmem_a = tmem + (PAIR ? 2 * RN : 128), tmem_aq = tmem_a + AUN * 64;
     bool ok = true;
 
     if (!(warp == W_COPY && lane == 0)) spl_grid_begin();     // the thread that copies weights first asks for some (below)
     if (warp == W_COPY) {
         // ---- copies of weights: codes and their scale/bias words, one ring.
         if (lane == 0) {
-            const unsigned char *wsrc = reinterpret_cast<const unsigned char *>(codes) + (size_t(tile) * groups + g_first) * 4096;
-            const uint32_t *qsrc = sb + (size_t(tile) * groups + g_first) * 128;
             spl_grid_begin();
             for (int j0 = ahead; j0 < supers && ok; ++j0) {
                 const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;      // the stage's source; j0 is its place in the pipeline
-                const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);         // with a rotation every stage is full
+                const int n = min(GPS, g_count - j0 * GPS);         // with a rotation every stage is full
                 const int sc = j0 % CST;
                 ok = spl_mbar_wait(&empty_c[sc], ((j0 / CST) & 1) ^ 1, abort);
                 if (!ok) { if (!*abort) spl_note_wait(error_flag, 10, j0); break; }
                 issued_c = j0 + 1;
                 if (j0 == drop) continue;
-                spl_mbar_expect_tx(&full_c[sc], uint32_t(n) * (4096 + 512));
-                spl_bulk_g2s(w_ring + size_t(sc) * WSTAGE, wsrc + size_t(j) * WSTAGE, uint32_t(n) * 4096, &full_c[sc]);
-                spl_bulk_g2s(q_ring + sc * QSTAGE, qsrc + size_t(j) * QSTAGE, uint32_t(n) * 512, &full_c[sc]);
+                copy_codes(sc, j, n);
             }
         }
     } else if (warp == W_COPYB) {
@@ -957,10 +988,10 @@ spl_gemm_q4_narrow_kernel(const uint32_t *__restrict__ codes, const uint32_t *__
             int mean_tile = -1, mean_loads = 0;
             for (int j0 = 0; j0 < supers && ok; ++j0) {
                 const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
-                const int n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER);
+                const int n = min(GPS, g_count - j0 * GPS);
                 const int sbq = j0 % BST;
                 // The tile of split means that holds this stage's groups (sixteen groups to a tile).
-                const int want = (g_first / SPL_TC_SUPER + j) >> 2;
+                const int want = (g_first + j * GPS) >> 4;
                 if (want != mean_tile) {
                     const int slot = mean_loads & 1;
                     ok = spl_mbar_wait(&empty_t[slot], ((mean_loads >> 1) & 1) ^ 1, abort);
@@ -980,7 +1011,7 @@ spl_gemm_q4_narrow_kernel(const uint32_t *__restrict__ codes, const uint32_t *__
                     spl_bulk_g2s(b_ring + size_t(sbq) * BTILE, bsrc + size_t(j) * BTILE, uint32_t(n) * RN * 128, &full_b[sbq]);
                 } else {
                     for (int u = 0; u < n; ++u) {
-                        const size_t g = size_t(j) * SPL_TC_SUPER + u;
+                        const size_t g = size_t(j) * GPS + u;
                         spl_bulk_g2s(b_ring + size_t(sbq) * BTILE + u * RN * 128, bsrc + g * row_blocks * RN * 128, RN * 128, &full_b[sbq]);
                     }
                 }
@@ -1005,12 +1036,12 @@ spl_gemm_q4_narrow_kernel(const uint32_t *__restrict__ codes, const uint32_t *__
         int slot = m, fa = m;                              // un % AUN, un % (2 AUN)
         uint32_t a_parity = 0;                             // (un / (2 AUN)) & 1
         for (int un = m; un < units && ok; un += 2) {
-            const int j0 = un >> 1, sbq = j0 % BST, n = min(SPL_TC_SUPER, g_count - j0 * SPL_TC_SUPER) - 2 * m;     // groups of this unit: 1 or 2
-            const uint64_t b_desc = b_desc0 + uint64_t((sbq * BTILE + m * 2 * RN * 128) >> 4);
+            const int j0 = un >> 1, sbq = j0 % BST, n = min(GPS, g_count - j0 * GPS) - (PAIR ? 0 : 2 * m);     // groups of this unit: 1 or 2
+            const uint64_t b_desc = b_desc0 + uint64_t((sbq * BTILE + (PAIR ? 0 : m * 2 * RN * 128)) >> 4);      // the pair's two tiles meet the same activations
             const uint32_t a_base = tmem_a + slot * 64;
             // The stage's share of the second term: its 16 values of the contraction are a quarter of a 128-byte row of the tile.
             const int j = j0 + rot < supers ? j0 + rot : j0 + rot - supers;
-            const int quarter = g_first / SPL_TC_SUPER + j, want = quarter >> 2;
+            const int quarter = (g_first + j * GPS) >> 2, want = quarter >> 2;
             if (want != mean_tile) {
                 if (mean_tile >= 0 && spl_elect_one()) spl_tc_commit(&empty_t[mean_slot]);      // every instruction of this warp that read the old tile has been issued
                 __syncwarp();
@@ -1077,7 +1108,7 @@ spl_gemm_q4_narrow_kernel(const uint32_t *__restrict__ codes, const uint32_t *__
             const int j = un >> 1, half = un & 1, sc = j % CST;
             ok = spl_mbar_wait(&full_c[sc], (j / CST) & 1, abort);
             if (!ok) { if (!*abort && lane == 0) spl_note_wait(error_flag, 41, un); break; }
-            const int n = min(SPL_TC_SUPER, g_count - j * SPL_TC_SUPER);      // groups of the stage; this unit has those from 2 * half
+            const int n = PAIR ? 2 * half + min(GPS, g_count - j * GPS) : min(SPL_TC_SUPER, g_count - j * SPL_TC_SUPER);      // code groups of the stage up to this unit's last; the unit has those from 2 * half (the pair form: tile `half`'s two)
             // The unit's codes and scale/bias words are read before anything is converted, so the codes can be handed back at once.
             uint4 lo[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)}, hi[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
             uint32_t sbw[2] = {0u, 0u};
@@ -1132,7 +1163,10 @@ spl_gemm_q4_narrow_kernel(const uint32_t *__restrict__ codes, const uint32_t *__
                 }
             }
             // The unit's share of the second-term operand sits at its place among the stage's sixteen values; the rest is zero.
-            if (half == 0) { spl_tc_st4(tmem_aq + lane_base + slot * 8, aq[0], aq[1], aq[2], aq[3]); spl_tc_st4(tmem_aq + lane_base + slot * 8 + 4, 0u, 0u, 0u, 0u); }
+            // (The pair form's stage is two groups of the contraction: they are the first or the second half of their four.)
+            int place = half;
+            if (PAIR) { const int jsrc = j + rot < supers ? j + rot : j + rot - supers; place = ((g_first + jsrc * GPS) >> 1) & 1; }
+            if (place == 0) { spl_tc_st4(tmem_aq + lane_base + slot * 8, aq[0], aq[1], aq[2], aq[3]); spl_tc_st4(tmem_aq + lane_base + slot * 8 + 4, 0u, 0u, 0u, 0u); }
             else { spl_tc_st4(tmem_aq + lane_base + slot * 8, 0u, 0u, 0u, 0u); spl_tc_st4(tmem_aq + lane_base + slot * 8 + 4, aq[0], aq[1], aq[2], aq[3]); }
             spl_tc_st_wait();
             spl_tc_fence_before();
@@ -1159,10 +1193,15 @@ spl_gemm_q4_narrow_kernel(const uint32_t *__restrict__ codes, const uint32_t *__
         // the accumulators pass through shared memory (the activation ring is idle by now) so that a thread holds the
         // gate and the up value of the same element.
         float *stage = reinterpret_cast<float *>(b_ring);       // [RN][128] fp32
+        // The pair form holds two tiles' sums, one per issuing warp's accumulator: the output stage runs once for each.
+#pragma unroll 1
+        for (int om = 0; om < (PAIR ? 2 : 1); ++om) {
+        const int otile = PAIR ? (om ? tile1 : tile0) : tile;
+        if (PAIR && om == 1 && !has1) break;
         if (ok) {
             spl_tc_fence_after();
-            const int n = tile * 128 + col;
-            const int n_out = interleave > 0 ? (((col & 16) ? interleave : 0) + tile * 64 + (col >> 5) * 16 + (col & 15)) : n;
+            const int n = otile * 128 + col;
+            const int n_out = interleave > 0 ? (((col & 16) ? interleave : 0) + otile * 64 + (col >> 5) * 16 + (col & 15)) : n;
             const bool is_split = partials != nullptr;          // the second kernel finishes: residual, output, the next operand
             float *dst = is_split ? partials + size_t(split) * rows_padded * out_ld : out;
             // (one copy of the body: code that runs once a block is paid for in instruction fetches)
@@ -1171,9 +1210,9 @@ spl_gemm_q4_narrow_kernel(const uint32_t *__restrict__ codes, const uint32_t *__
                 const int c0 = cb * 16;
                 float total[16];
 #pragma unroll
-                for (int a = 0; a < (units > 1 ? 2 : 1); ++a) {
+                for (int a = 0; a < (!PAIR && units > 1 ? 2 : 1); ++a) {
                     uint32_t v[16];
-                    spl_tc_ld16(v, tmem_d + lane_base + a * RN + c0);
+                    spl_tc_ld16(v, tmem_d + lane_base + (PAIR ? om : a) * RN + c0);
 #pragma unroll
                     for (int r = 0; r < 16; ++r) total[r] = a == 0 ? __uint_as_float(v[r]) : total[r] + __uint_as_float(v[r]);
                 }
@@ -1221,10 +1260,12 @@ spl_gemm_q4_narrow_kernel(const uint32_t *__restrict__ codes, const uint32_t *__
                 for (int o = 4; o > 0; o >>= 1) { sa += __shfl_xor_sync(0xffffffffu, sa, o); sb2 += __shfl_xor_sync(0xffffffffu, sb2, o); }
                 if (ok && row < rows) {
                     const uint2 lo8 = spl_operand_pack4(r[0], r[1], r[2], r[3]), hi8 = spl_operand_pack4(r[4], r[5], r[6], r[7]);
-                    *reinterpret_cast<uint4 *>(act_out.values + act_out.at(row, tile * 64 + c8)) = make_uint4(lo8.x, lo8.y, hi8.x, hi8.y);
-                    if ((t & 7) == 0) act_out.put_sum(row, tile, sa + sb2);
+                    *reinterpret_cast<uint4 *>(act_out.values + act_out.at(row, otile * 64 + c8)) = make_uint4(lo8.x, lo8.y, hi8.x, hi8.y);
+                    if ((t & 7) == 0) act_out.put_sum(row, otile, sa + sb2);
                 }
             }
+            if (PAIR) spl_named_barrier<1, SPL_TC_SETS * 128>();      // the staged sums have been read: the other tile's may follow
+        }
         }
     }
     if (!ok) { *abort_word = 1; atomicExch(error_flag, 1 + warp); }

@@ -211,6 +211,7 @@ def lib():
             "spl_debug_taps": (i32, [vp, i32]),
             "spl_debug_kv_store": (i32, [vp, i32]),
             "spl_debug_gdn_chunk_min": (i32, [vp, i32]),
+            "spl_debug_pair_blocks": (i32, [vp, i32]),
             "spl_debug_wait_budget": (i32, [vp, C.c_int64]),
             "spl_debug_drop_weight_stage": (i32, [vp, i32]),
             "spl_gemm_q4_static_status": (i32, [vp]),
@@ -694,6 +695,10 @@ class Engine:
     def debug_gdn_chunk_min(self, rows):
         """Ordinary runs of at least `rows` rows (default 512) take the chunked gated-delta scan."""
         self._check(lib().spl_debug_gdn_chunk_min(self.handle, int(rows)))
+
+    def debug_pair_blocks(self, enabled=True):
+        """Prompt chunks' GEMMs on the pair form of the 128-row block (default) or on the one-tile block."""
+        self._check(lib().spl_debug_pair_blocks(self.handle, int(enabled)))
 
     def debug_profile(self, enabled=True):
         self._check(lib().spl_debug_profile(self.handle, int(enabled)))
