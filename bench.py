@@ -340,7 +340,7 @@ def main():
         gemm_tflops = gemm_flops / (shares["gemm_q4"]["ms"] * 1e-3) / 1e12 if shares["gemm_q4"]["ms"] > 0 else 0.0
         prefill = {"workload": f"one session, {prompt_tokens}-token prompt in {PREFILL_CHUNK}-row chunks, {g.layers} blocks", "tok_per_s": prompt_tokens / seconds,
                    "seconds": seconds, "steps": -(-prompt_tokens // PREFILL_CHUNK), "gpu_launches": count,
-                   "gemm": {"tflops": gemm_tflops, "peak_tflops": tensor_peak, "frac": gemm_tflops / tensor_peak,
+                   "gemm": {"kernel": "spl_gemm_q4_narrow_kernel<128, true> (the pair form of the 128-row block)", "tflops": gemm_tflops, "peak_tflops": tensor_peak, "frac": gemm_tflops / tensor_peak,
                             "peak_source": "measured (MEASURED_PEAKS.json bf16_tflops_sustained)" if peaks else "fallback (1.4 PFLOP/s sustained, an earlier measurement on this pool)",
                             "flops": "2 x the blocks' weights per prompt token (the head runs for the prompt's last token only)"},
                    "class_ms": {k: v["ms"] for k, v in shares.items()}}
