@@ -283,13 +283,32 @@ GemmCut gemm_cut(const SplQ4Dev &w, int sms, int rn, int row_blocks, bool whole)
     return {w.tiles * best, best};
 }
 
+// The pair form of the 128-row block (two tiles of the weight a block): into how many runs of whole stages every pair's
+// contraction is cut, by the same count of waves x work a block with a fixed cost per block; 0 when the form does not apply
+// (the switch is off, or the contraction is not whole stages of 256).
+int pair_splits(const SplQ4Dev &w, int sms, int row_blocks, bool whole) {
+    if (!g_pair_blocks || w.k % 256 != 0) return 0;
+    const int pairs = (w.tiles + 1) / 2, stages = w.k / 256;
+    int best = 1; double best_cost = 1e30;
+    for (int s = 1; s <= stages && s <= 16 && !(whole && s > 1); ++s) {
+        const int per = (stages + s - 1) / s;
+        if (s > 1 && per < 2) break;
+        const int waves = (pairs * s * row_blocks + sms - 1) / sms;
+        const double cost = double(waves) * (per * 8 + 20.0) + (s > 1 ? 12.0 : 0.0);      // a stage of 256 is eight groups of work for two tiles
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
+    }
+    const int per = (stages + best - 1) / best;
+    return (stages + per - 1) / per;
+}
+
 // Floats of scratch a GEMM on `w` may leave for its second kernel: the wide block's slots, or the narrow block's
 // partials[split][row][column] (cut tiles, and every tile when the output feeds a deferred norm: `emit`).
 size_t gemm_slot_floats(const SplQ4Dev &w, int sms, int rn, int row_blocks, bool emit, bool whole) {
     const GemmCut cut = gemm_cut(w, sms, rn, row_blocks, whole);
     if (rn >= 128) {
-        // The pair form (two row blocks and more, every tile whole) leaves an output that feeds a deferred norm to the second kernel.
-        const size_t pair = (row_blocks >= 2 && cut.splits == 1 && emit) ? size_t(row_blocks) * rn * w.ld : 0;
+        // The pair form leaves cut contractions, and an output that feeds a deferred norm, to the second kernel.
+        const int ps = pair_splits(w, sms, row_blocks, whole);
+        const size_t pair = (ps > 1 || (ps == 1 && emit)) ? size_t(ps) * row_blocks * rn * w.ld : 0;
         return std::max(spl_tc_slot_floats(cut.pieces, cut.splits, row_blocks, rn), pair);
     }
     const int stages = w.k / 256, per = (stages + cut.splits - 1) / cut.splits, splits = (stages + per - 1) / per;
@@ -335,20 +354,22 @@ bool launch_gemm_tc(cudaStream_t stream, const SplQ4Dev &w, const GemmOperand &o
         return true;
     }
     if constexpr (RN == 128) {
-        // Prompt chunks (two row blocks and more, so every tile is whole): the pair form, two tiles of the weight a block.
-        if (g_pair_blocks && row_blocks >= 2 && cut.splits == 1 && (w.k / 64) % 2 == 0) {
-            const bool second = x.emit_weight != nullptr;
+        // The pair form, two tiles of the weight a block against one stream of activations.
+        const int splits = pair_splits(w, scratch.sms, row_blocks, x.fuse_act != nullptr);
+        if (splits > 0) {
+            const int stages = w.k / 256, per = (stages + splits - 1) / splits;
+            const bool second = splits > 1 || x.emit_weight != nullptr;
             const size_t rows_padded = size_t(op.blocks) * RN;
-            if (second && rows_padded * w.ld > scratch.slot_floats) return false;
-            launch_step(spl_gemm_q4_narrow_kernel<128, true>, dim3(((w.tiles + 1) / 2) * row_blocks), block, spl_tc_pair_smem_bytes(), stream, (const uint32_t *)w.codes, (const uint32_t *)w.sb, op.values, op.sums,
-                        out, w.ld, second ? (const float *)nullptr : residual, second ? scratch.slots : (float *)nullptr, rows, op.blocks, w.k / 64, w.k / 64, scratch.error_flag, w.interleave,
+            if (second && size_t(splits) * rows_padded * w.ld > scratch.slot_floats) return false;
+            launch_step(spl_gemm_q4_narrow_kernel<128, true>, dim3(((w.tiles + 1) / 2) * row_blocks, splits), block, spl_tc_pair_smem_bytes(), stream, (const uint32_t *)w.codes, (const uint32_t *)w.sb, op.values, op.sums,
+                        out, w.ld, second ? (const float *)nullptr : residual, second ? scratch.slots : (float *)nullptr, rows, op.blocks, w.k / 64, per * 4, scratch.error_flag, w.interleave,
                         a.act_out, a.fuse, x.in_squares, x.in_dim / 64, float(x.in_dim), x.eps, g_drop_weight_stage);
             if (launches) ++*launches;
             if (second) {
                 if (scratch.timed) { profile_end(scratch.timed); profile_begin(scratch.timed, KLASS_ELEMENTWISE, 0); }
                 else if (launches) ++*launches;
                 const long long warps = (long long)rows * ((w.ld + 63) / 64);
-                launch_step(spl_gemm_fixup_rows_kernel, dim3(int(std::min<long long>((warps + 7) / 8, 8LL * scratch.sms))), dim3(256), 0, stream, (const float *)scratch.slots, 1, int(rows_padded), rows, w.ld,
+                launch_step(spl_gemm_fixup_rows_kernel, dim3(int(std::min<long long>((warps + 7) / 8, 8LL * scratch.sms))), dim3(256), 0, stream, (const float *)scratch.slots, splits, int(rows_padded), rows, w.ld,
                             residual, out, x.emit_weight, emit_out, x.emit_squares);
             }
             return true;

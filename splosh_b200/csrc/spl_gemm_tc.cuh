@@ -883,10 +883,10 @@ spl_gemm_q4_narrow_kernel(const uint32_t *__restrict__ codes, const uint32_t *__
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int W_COPY = SPL_TC_SETS * 4, W_MMA0 = W_COPY + 1, W_COPYB = W_COPY + 2, W_MMA1 = W_COPY + 3;
-    // The pair form's grid is one-dimensional, the row block the fast index: the blocks that run together are then the row
+    // The pair form's grid has pair and row block in one dimension, the row block the fast index (the splits in the second): the blocks that run together are then the row
     // blocks of a few pairs, and a pair's weights come from HBM once and from L2 for the other row blocks.
     const int run_blocks = PAIR ? (rows + RN - 1) / RN : 1;
-    const int tile = PAIR ? int(blockIdx.x) / run_blocks : int(blockIdx.x), split = PAIR ? 0 : int(blockIdx.y), rb = PAIR ? int(blockIdx.x) % run_blocks : int(blockIdx.z);
+    const int tile = PAIR ? int(blockIdx.x) / run_blocks : int(blockIdx.x), split = int(blockIdx.y), rb = PAIR ? int(blockIdx.x) % run_blocks : int(blockIdx.z);
     const int row_blocks = op_blocks;   // the operand's row blocks (>= the grid's)
     const int tiles_all = (out_ld + 127) / 128;
     const int tile0 = PAIR ? 2 * tile : tile, tile1 = PAIR ? min(2 * tile + 1, tiles_all - 1) : tile;      // an odd tensor's last pair does its one tile twice
