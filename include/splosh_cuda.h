@@ -313,9 +313,9 @@ spl_status spl_debug_taps(spl_engine *engine, int32_t enabled);
 /* Tests: ordinary runs of at least `rows` rows (>= 64; default 512) take the chunked gated-delta scan instead of the
  * per-token kernel. */
 spl_status spl_debug_gdn_chunk_min(spl_engine *engine, int32_t rows);
-/* Tests and measurements: with `enabled` 0 the GEMMs of a prompt chunk (two row blocks of 128 and more) run on the block
- * that works on one tile of the weight, instead of the pair form that works on two against one stream of activations
- * (process-wide; default 1). */
+/* Tests and measurements: with `enabled` 0 the GEMMs of steps of more than 64 rows run on the 128-row block that works on
+ * one tile of the weight, instead of the pair form that works on two against one stream of activations (process-wide,
+ * `engine` may be null; default 1). */
 spl_status spl_debug_pair_blocks(spl_engine *engine, int32_t enabled);
 spl_status spl_debug_kv_store(spl_engine *engine, int32_t enabled);
 /* Every wait inside a kernel (a role of a block waiting for another role of the same block) gives up after a time

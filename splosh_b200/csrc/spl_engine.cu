@@ -1383,8 +1383,7 @@ spl_status spl_debug_drop_weight_stage(spl_engine *e, int32_t stage) {
     return SPL_OK;
 }
 
-spl_status spl_debug_pair_blocks(spl_engine *e, int32_t enabled) {
-    if (!e) return SPL_ERR_INVALID_ARGUMENT;
+spl_status spl_debug_pair_blocks(spl_engine *, int32_t enabled) {
     g_pair_blocks = enabled ? 1 : 0;
     return SPL_OK;
 }

@@ -721,6 +721,11 @@ class Engine:
 RESIDENT = ["in_proj", "out_proj", "gate_up", "down", "head"]
 
 
+def debug_pair_blocks(enabled=True):
+    """Steps of more than 64 rows on the pair form of the 128-row GEMM block (default) or on the one-tile block (process-wide)."""
+    lib().spl_debug_pair_blocks(None, int(enabled))
+
+
 def splw_check(path):
     """The container checks of an SPLW artifact, no engine needed (spl_splw_check): (format, tensor records)."""
     message = C.create_string_buffer(512)

@@ -37,6 +37,19 @@ def test_output_widths_that_do_not_fill_a_tile(oracle, n, k):
     case(oracle, n, k, 20, n + k, residual=n % 2 == 0)
 
 
+@pytest.mark.parametrize("pair", [True, False])
+@pytest.mark.parametrize("n,k,rows", [(3104, 1024, 300), (1024, 2816, 129), (5632, 1024, 257), (48, 1024, 200), (5120, 6144, 128), (2176, 5120, 520)])
+def test_the_two_128_row_blocks(oracle, pair, n, k, rows):
+    """Steps of more than 64 rows: the pair form (two tiles of the weight a block: an odd tile count, 25, whose last pair does
+    its one tile twice; one row block with the contraction cut; several row blocks) and, with the switch off, the block of
+    one tile."""
+    S.engine.debug_pair_blocks(pair)
+    try:
+        case(oracle, n, k, rows, 1000 + rows)
+    finally:
+        S.engine.debug_pair_blocks(True)
+
+
 @pytest.mark.parametrize("k", [256, 768, 1280, 2304])
 @pytest.mark.parametrize("rows", [5, 64])
 def test_short_contractions_with_odd_stage_counts(oracle, k, rows):
