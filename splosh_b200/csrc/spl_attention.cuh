@@ -207,9 +207,9 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
     uint64_t *bars = reinterpret_cast<uint64_t *>(xsum + 4 * NQ);
     uint64_t *full_k = bars, *empty_k = full_k + NKS, *full_v = empty_k + NKS, *empty_v = full_v + NVS, *full_sc = empty_v + NVS, *empty_sc = full_sc + NSS,
              *ka_full = empty_sc + NSS, *ka_free = ka_full + 3, *va_full = ka_free + 3,
-             *va_free = va_full + 2, *s_full = va_free + 2, *s_free = s_full + 2, *p_full = s_free + 2, *p_free = p_full + 2, *o_done = p_free + 2, *x_full = o_done + 2, *y_full = x_full + 2, *sum_full = y_full + 2;
+             *va_free = va_full + 2, *s_full = va_free + 2, *s_free = s_full + 2, *p_full = s_free + 2, *p_free = p_full + 2, *o_done = p_free + 2, *x_full = o_done + 2, *y_full = x_full + 2 * GROUPS, *sum_full = y_full + 2 * GROUPS;      // x_full, y_full: [group][chunk parity]
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(sum_full + 1);
-    int *xflag = reinterpret_cast<int *>(tmem_slot + 1);          // [2] last chunk (+1) of each parity whose scores called for a raise
+    int *xflag = reinterpret_cast<int *>(tmem_slot + 1);          // [group][2] last chunk (+1) of each parity whose scores called for a raise
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kv_head = blockIdx.x % p.kv_heads, span = blockIdx.x / p.kv_heads, block = blockIdx.y;
@@ -231,8 +231,9 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
         for (int i = 0; i < 2; ++i) {
             spl_mbar_init(&va_full[i], 4); spl_mbar_init(&va_free[i], 1);
             spl_mbar_init(&s_full[i], 1); spl_mbar_init(&s_free[i], SW); spl_mbar_init(&p_full[i], SW); spl_mbar_init(&p_free[i], 1);
-            spl_mbar_init(&o_done[i], 1); spl_mbar_init(&x_full[i], SW); spl_mbar_init(&y_full[i], SW);
-            xflag[i] = 0;
+            spl_mbar_init(&o_done[i], 1);
+            // A group's references are its own columns': its four warps agree among themselves whether to raise them.
+            for (int grp = 0; grp < GROUPS; ++grp) { spl_mbar_init(&x_full[grp * 2 + i], 4); spl_mbar_init(&y_full[grp * 2 + i], 4); xflag[grp * 2 + i] = 0; }
         }
         spl_mbar_init(sum_full, SW);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -497,11 +498,11 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                 const bool any_over = __any_sync(0xffffffffu, over > SPL_ATTN_HEADROOM);
                 SPL_A1(2);
                 if (lane == 0) {
-                    if (any_over) atomicMax(xflag + par, i + 1);
-                    spl_mbar_arrive(&x_full[par]);
+                    if (any_over) atomicMax(xflag + sg * 2 + par, i + 1);
+                    spl_mbar_arrive(&x_full[sg * 2 + par]);
                 }
-                if (!spl_mbar_wait(&x_full[par], (i >> 1) & 1)) return false;
-                const bool raise = *reinterpret_cast<volatile int *>(xflag + par) == i + 1;
+                if (!spl_mbar_wait(&x_full[sg * 2 + par], (i >> 1) & 1)) return false;
+                const bool raise = *reinterpret_cast<volatile int *>(xflag + sg * 2 + par) == i + 1;
                 SPL_A1(3);
                 // The probability tile of two chunks ago has been read (and with it that chunk's value product has finished,
                 // so a wait on the previous chunk's completion cannot see a stale phase).
@@ -524,8 +525,8 @@ spl_attn_scan_kernel(const __half *__restrict__ q, const uint32_t *__restrict__ 
                         }
                     }
                     __syncwarp();
-                    if (lane == 0) spl_mbar_arrive(&y_full[par]);
-                    if (!spl_mbar_wait(&y_full[par], raises[par] & 1)) return false;
+                    if (lane == 0) spl_mbar_arrive(&y_full[sg * 2 + par]);
+                    if (!spl_mbar_wait(&y_full[sg * 2 + par], raises[par] & 1)) return false;
                     ++raises[par];
                     if (lane < NH) {
                         const int n = cb + lane;
