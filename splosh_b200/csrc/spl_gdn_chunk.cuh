@@ -189,28 +189,59 @@ __host__ __device__ constexpr size_t spl_gdn_chunk_prepare_smem() {
     return sizeof(float) * (2 * SPL_GDN_CHUNK * SPL_GDN_LD + SPL_GDN_CHUNK * SPL_GDN_CHUNK + SPL_GDN_CHUNK * (SPL_GDN_CHUNK + 1) + 4 * SPL_GDN_CHUNK);
 }
 
+// The scan's matrix products run on the tensor cores' warp-level instruction (m16n8k8, tf32 operands, fp32 accumulators):
+// they are fp32 products of small matrices in a chain (each chunk's depend on the state the one before left), which the
+// block-wide tcgen05 pipeline with its barriers does not suit, and on the CUDA cores they were bound by the shared-memory
+// reads of their operands (a thread's four outputs took five 16-byte loads a step). Every operand is split in two tf32
+// numbers, x = hi + lo with hi = tf32(x) and lo = tf32(x - hi), and a product is three instructions, lo x hi + hi x lo +
+// hi x hi (lo x lo is below 2^-22 of the term): fp32 accuracy to within the rounding of the sums.
+__device__ __forceinline__ void spl_split_tf32(float x, uint32_t &hi, uint32_t &lo) {
+    asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(hi) : "f"(x));
+    const float rest = x - __uint_as_float(hi);
+    asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(lo) : "f"(rest));
+}
+// c += a b for a 16 x 8 (row-major) and b 8 x 8 (column-major) in the instruction's register layout: with g = lane / 4 and
+// t = lane % 4, a = {(g, t), (g + 8, t), (g, t + 4), (g + 8, t + 4)}, b = {(k = t, n = g), (k = t + 4, n = g)},
+// c = {(g, 2t), (g, 2t + 1), (g + 8, 2t), (g + 8, 2t + 1)}.
+__device__ __forceinline__ void spl_mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void spl_mma_3xtf32(float (&c)[4], const float (&a)[4], const float (&b)[2]) {
+    uint32_t ah[4], al[4], bh[2], bl[2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) spl_split_tf32(a[i], ah[i], al[i]);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) spl_split_tf32(b[i], bh[i], bl[i]);
+    spl_mma_tf32(c, al, bh); spl_mma_tf32(c, ah, bl); spl_mma_tf32(c, ah, bh);
+}
+
+#define SPL_GDN_KLD (SPL_GDN_D + 8)     // floats between rows of Kd: read as a product's k x n operand, whose lanes go four rows by eight columns
+#define SPL_GDN_ULD 24                  // floats between rows of U (sixteen values a row): the same pattern over its rows
+
 // Grid (value heads, chunked runs, SPL_GDN_SLICES), 256 threads. The run's chunks in order over one slice of the value
-// dimension: the slice of S in shared memory, U and O of the chunk formed from the prepared record.
+// dimension: the slice of S in shared memory, U and O of the chunk formed from the prepared record. Eight warps: for the
+// 64 x 16 products (U, O) warp w has tokens 16 (w / 2) ... + 15 and values 8 (w % 2) ... + 7 of the slice; for the state's
+// 16 x 128 update it has columns 16 w ... + 15.
 __global__ void __launch_bounds__(256)
 spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables tables, float *state, const float *__restrict__ journal,
                           float *o_raw, SplGdnParams p) {
     spl_grid_begin();
-    constexpr int D = SPL_GDN_D, C = SPL_GDN_CHUNK, SL = SPL_GDN_SLICE, LD = SPL_GDN_LD, PLD = SPL_GDN_PLD;
+    constexpr int D = SPL_GDN_D, C = SPL_GDN_CHUNK, SL = SPL_GDN_SLICE, LD = SPL_GDN_LD, PLD = SPL_GDN_PLD, KLD = SPL_GDN_KLD, ULD = SPL_GDN_ULD, SLD = D + 4;
     extern __shared__ __align__(16) float spl_gdn_scan_smem[];
-    // One [C][LD] buffer holds W, then g q^, then Kd in turn: with 64 KB a block three blocks share an SM, and the 384
-    // blocks of a 48-head run are resident at once (with a buffer each for W and g q^ it was two to an SM and a second
-    // wave of 88 blocks doubled the kernel's time).
-    float *w_s = spl_gdn_scan_smem;           // [C][LD] W, then g q^, then Kd
-    float *p_s = w_s + C * LD;                 // [C][PLD] P
-    float *s_s = p_s + C * PLD;                // [SL][D + 4] the slice of the state (rows padded)
-    float *u_s = s_s + SL * (D + 4);           // [C][SL] U
+    // One buffer holds W, then g q^ (rows LD apart), then Kd (rows KLD apart) in turn: three blocks share an SM, and the 384
+    // blocks of a 48-head run are resident at once.
+    float *w_s = spl_gdn_scan_smem;           // [C][KLD] W, then g q^, then Kd
+    float *p_s = w_s + C * KLD;                // [C][PLD] P
+    float *s_s = p_s + C * PLD;                // [SL][SLD] the slice of the state (rows padded)
+    float *u_s = s_s + SL * SLD;               // [C][ULD] U
     const int h = blockIdx.x, run = blockIdx.y, slice = blockIdx.z, tid = threadIdx.x;
     const int VH = p.value_heads;
     const uint32_t slot = tables.runs[run * 4], length = tables.runs[run * 4 + 2], pending = tables.runs[run * 4 + 3];
     float *stored = state + ((size_t(slot) * VH + h) * D + slice * SL) * D;
     for (int idx = tid; idx < SL * (D / 4); idx += 256) {
         const int j = idx / (D / 4), i4 = idx % (D / 4);
-        *reinterpret_cast<float4 *>(s_s + j * (D + 4) + i4 * 4) = *reinterpret_cast<const float4 *>(stored + j * D + i4 * 4);
+        *reinterpret_cast<float4 *>(s_s + j * SLD + i4 * 4) = *reinterpret_cast<const float4 *>(stored + j * D + i4 * 4);
     }
     __syncthreads();
     // Journal entries accepted from the run before are replayed first, with the update's one expression (engine.metal:654-659).
@@ -221,7 +252,7 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
             const float decay = entry[2 * D];
             for (int idx = tid; idx < SL * D; idx += 256) {
                 const int j = idx / D, i = idx % D;
-                s_s[j * (D + 4) + i] = __fmaf_rn(s_s[j * (D + 4) + i], decay, __fmul_rn(entry[i], entry[D + slice * SL + j]));
+                s_s[j * SLD + i] = __fmaf_rn(s_s[j * SLD + i], decay, __fmul_rn(entry[i], entry[D + slice * SL + j]));
             }
             __syncthreads();
         }
@@ -230,8 +261,8 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
     int chunk = 0;
     for (; chunk < tables.chunk_count; ++chunk) if (tables.chunks[chunk * 4] == uint32_t(run)) break;
     const int chunks = int((length + C - 1) / C);
-    const int tq = tid >> 2, jq = tid & 3;          // U and O: token tq, values jq, jq + 4, jq + 8, jq + 12 of the slice (the four lanes of a token read
-                                                    // neighbouring rows of S, which the rows' padding puts in different banks)
+    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    const int m0 = 16 * (warp >> 1), n0 = 8 * (warp & 1);          // the warp's tokens and values of the slice in the 64 x 16 products
     for (int n = 0; n < chunks; ++n, ++chunk) {
         const float *rec = records + (size_t(chunk) * VH + h) * SPL_GDN_REC_FLOATS;
         const uint32_t first = tables.chunks[chunk * 4 + 1], count = tables.chunks[chunk * 4 + 2];
@@ -240,73 +271,70 @@ spl_gdn_chunk_scan_kernel(const float *__restrict__ records, SplGdnChunkTables t
         for (int idx = tid; idx < C * (C / 4); idx += 256)
             *reinterpret_cast<float4 *>(p_s + (idx / (C / 4)) * PLD + (idx % (C / 4)) * 4) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_P)[idx];
         const float g_end = rec[SPL_GDN_REC_GC];
+        // Uv of the thread's four outputs (tokens m0 + g and + 8, values n0 + 2t and + 1), asked for before the product.
+        const float2 uv0 = *reinterpret_cast<const float2 *>(rec + SPL_GDN_REC_UV + (m0 + g) * D + slice * SL + n0 + 2 * t);
+        const float2 uv1 = *reinterpret_cast<const float2 *>(rec + SPL_GDN_REC_UV + (m0 + g + 8) * D + slice * SL + n0 + 2 * t);
         __syncthreads();
-        // U[t][j] = Uv[t][j] - sum_i W[t][i] S[j][i];  O0[t][j] = sum_i (g q^)[t][i] S[j][i]
-        float u[4], o[4];
-        {
+        // x[token][value] = sum_i X[token][i] S[value][i] for X = W or g q^ in w_s.
+        auto against_state = [&](float (&acc)[4]) {
 #pragma unroll
-            for (int r = 0; r < 4; ++r) u[r] = rec[SPL_GDN_REC_UV + tq * D + slice * SL + jq + 4 * r];
-#pragma unroll
-            for (int r = 0; r < 4; ++r) o[r] = 0.0f;
-            for (int i = 0; i < D; i += 4) {
-                const float4 wv = *reinterpret_cast<const float4 *>(w_s + tq * LD + i);
-#pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const float4 sv = *reinterpret_cast<const float4 *>(s_s + (jq + 4 * r) * (D + 4) + i);
-                    u[r] -= wv.x * sv.x + wv.y * sv.y + wv.z * sv.z + wv.w * sv.w;
-                }
+            for (int i = 0; i < 4; ++i) acc[i] = 0.0f;
+#pragma unroll 4
+            for (int k0 = 0; k0 < D; k0 += 8) {
+                const float a[4] = {w_s[(m0 + g) * LD + k0 + t], w_s[(m0 + g + 8) * LD + k0 + t], w_s[(m0 + g) * LD + k0 + t + 4], w_s[(m0 + g + 8) * LD + k0 + t + 4]};
+                const float b[2] = {s_s[(n0 + g) * SLD + k0 + t], s_s[(n0 + g) * SLD + k0 + t + 4]};
+                spl_mma_3xtf32(acc, a, b);
             }
-#pragma unroll
-            for (int r = 0; r < 4; ++r) u_s[tq * SL + jq + 4 * r] = u[r];
-        }
+        };
+        // U[t][j] = Uv[t][j] - sum_i W[t][i] S[j][i]
+        float acc[4];
+        against_state(acc);
+        *reinterpret_cast<float2 *>(u_s + (m0 + g) * ULD + n0 + 2 * t) = make_float2(uv0.x - acc[0], uv0.y - acc[1]);
+        *reinterpret_cast<float2 *>(u_s + (m0 + g + 8) * ULD + n0 + 2 * t) = make_float2(uv1.x - acc[2], uv1.y - acc[3]);
         __syncthreads();
         for (int idx = tid; idx < C * (D / 4); idx += 256)
             *reinterpret_cast<float4 *>(w_s + (idx / (D / 4)) * LD + (idx % (D / 4)) * 4) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_QG)[idx];
         __syncthreads();
-        for (int i = 0; i < D; i += 4) {
-            const float4 qv = *reinterpret_cast<const float4 *>(w_s + tq * LD + i);
-#pragma unroll
-            for (int r = 0; r < 4; ++r) {
-                const float4 sv = *reinterpret_cast<const float4 *>(s_s + (jq + 4 * r) * (D + 4) + i);
-                o[r] += qv.x * sv.x + qv.y * sv.y + qv.z * sv.z + qv.w * sv.w;
-            }
+        // O[t][j] = sum_i (g q^)[t][i] S[j][i] + sum_{s<=t} P[t][s] U[s][j]   (P is zero above the diagonal: its tiles there are left out)
+        float o[4];
+        against_state(o);
+        for (int k0 = 0; k0 < m0 + 16; k0 += 8) {
+            const float a[4] = {p_s[(m0 + g) * PLD + k0 + t], p_s[(m0 + g + 8) * PLD + k0 + t], p_s[(m0 + g) * PLD + k0 + t + 4], p_s[(m0 + g + 8) * PLD + k0 + t + 4]};
+            const float b[2] = {u_s[(k0 + t) * ULD + n0 + g], u_s[(k0 + t + 4) * ULD + n0 + g]};
+            spl_mma_3xtf32(o, a, b);
         }
-        // O[t][j] = O0 + sum_{s<=t} P[t][s] U[s][j]; meanwhile the record's Kd replaces W in shared memory.
-        for (int s = 0; s <= tq; ++s) {
-            const float w = p_s[tq * PLD + s];
-#pragma unroll
-            for (int r = 0; r < 4; ++r) o[r] += w * u_s[s * SL + jq + 4 * r];
-        }
-        if (tq < int(count))
-#pragma unroll
-            for (int r = 0; r < 4; ++r) o_raw[size_t(first + tq) * (size_t(VH) * D) + h * D + slice * SL + jq + 4 * r] = o[r];
+        if (m0 + g < int(count))
+            *reinterpret_cast<float2 *>(o_raw + size_t(first + m0 + g) * (size_t(VH) * D) + h * D + slice * SL + n0 + 2 * t) = make_float2(o[0], o[1]);
+        if (m0 + g + 8 < int(count))
+            *reinterpret_cast<float2 *>(o_raw + size_t(first + m0 + g + 8) * (size_t(VH) * D) + h * D + slice * SL + n0 + 2 * t) = make_float2(o[2], o[3]);
         __syncthreads();          // every thread has finished with g q^
         for (int idx = tid; idx < C * (D / 4); idx += 256)
-            *reinterpret_cast<float4 *>(w_s + (idx / (D / 4)) * LD + (idx % (D / 4)) * 4) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_KD)[idx];
+            *reinterpret_cast<float4 *>(w_s + (idx / (D / 4)) * KLD + (idx % (D / 4)) * 4) = reinterpret_cast<const float4 *>(rec + SPL_GDN_REC_KD)[idx];
         __syncthreads();
-        // S[j][i] = g_C S[j][i] + sum_s U[s][j] Kd[s][i]: a thread one value row j and eight columns i.
-        {
-            const int j = tid >> 4, i0 = (tid & 15) * 4;      // columns i0 .. + 3 and 64 + i0 .. + 3: sixteen lanes read 16-byte pieces side by side
-            float4 lo = *reinterpret_cast<const float4 *>(s_s + j * (D + 4) + i0), hi = *reinterpret_cast<const float4 *>(s_s + j * (D + 4) + 64 + i0);
-            float acc[8] = {g_end * lo.x, g_end * lo.y, g_end * lo.z, g_end * lo.w, g_end * hi.x, g_end * hi.y, g_end * hi.z, g_end * hi.w};
-            for (int s = 0; s < C; ++s) {
-                const float us = u_s[s * SL + j];
-                const float4 k0 = *reinterpret_cast<const float4 *>(w_s + s * LD + i0), k1 = *reinterpret_cast<const float4 *>(w_s + s * LD + 64 + i0);
-                acc[0] += us * k0.x; acc[1] += us * k0.y; acc[2] += us * k0.z; acc[3] += us * k0.w;
-                acc[4] += us * k1.x; acc[5] += us * k1.y; acc[6] += us * k1.z; acc[7] += us * k1.w;
+        // S[j][i] = g_C S[j][i] + sum_s U[s][j] Kd[s][i]: the warp's sixteen columns, two tiles of eight.
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int c0 = 16 * warp + 8 * half;
+            const float2 lo = *reinterpret_cast<const float2 *>(s_s + g * SLD + c0 + 2 * t), hi = *reinterpret_cast<const float2 *>(s_s + (g + 8) * SLD + c0 + 2 * t);
+            float sacc[4] = {g_end * lo.x, g_end * lo.y, g_end * hi.x, g_end * hi.y};
+#pragma unroll 4
+            for (int k0 = 0; k0 < C; k0 += 8) {
+                const float a[4] = {u_s[(k0 + t) * ULD + g], u_s[(k0 + t) * ULD + g + 8], u_s[(k0 + t + 4) * ULD + g], u_s[(k0 + t + 4) * ULD + g + 8]};
+                const float b[2] = {w_s[(k0 + t) * KLD + c0 + g], w_s[(k0 + t + 4) * KLD + c0 + g]};
+                spl_mma_3xtf32(sacc, a, b);
             }
-            *reinterpret_cast<float4 *>(s_s + j * (D + 4) + i0) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-            *reinterpret_cast<float4 *>(s_s + j * (D + 4) + 64 + i0) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            *reinterpret_cast<float2 *>(s_s + g * SLD + c0 + 2 * t) = make_float2(sacc[0], sacc[1]);
+            *reinterpret_cast<float2 *>(s_s + (g + 8) * SLD + c0 + 2 * t) = make_float2(sacc[2], sacc[3]);
         }
         __syncthreads();
     }
     for (int idx = tid; idx < SL * (D / 4); idx += 256) {
         const int j = idx / (D / 4), i4 = idx % (D / 4);
-        *reinterpret_cast<float4 *>(stored + j * D + i4 * 4) = *reinterpret_cast<const float4 *>(s_s + j * (D + 4) + i4 * 4);
+        *reinterpret_cast<float4 *>(stored + j * D + i4 * 4) = *reinterpret_cast<const float4 *>(s_s + j * SLD + i4 * 4);
     }
 }
 __host__ __device__ constexpr size_t spl_gdn_chunk_scan_smem() {
-    return sizeof(float) * (SPL_GDN_CHUNK * SPL_GDN_LD + SPL_GDN_CHUNK * SPL_GDN_PLD + SPL_GDN_SLICE * (SPL_GDN_D + 4) + SPL_GDN_CHUNK * SPL_GDN_SLICE);
+    return sizeof(float) * (SPL_GDN_CHUNK * SPL_GDN_KLD + SPL_GDN_CHUNK * SPL_GDN_PLD + SPL_GDN_SLICE * (SPL_GDN_D + 4) + SPL_GDN_CHUNK * SPL_GDN_ULD);
 }
 
 // Gated RMSNorm of whole heads and the bf16 operand of the output projection with its per-64 sums
