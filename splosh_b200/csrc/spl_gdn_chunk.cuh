@@ -193,12 +193,13 @@ __host__ __device__ constexpr size_t spl_gdn_chunk_prepare_smem() {
 // they are fp32 products of small matrices in a chain (each chunk's depend on the state the one before left), which the
 // block-wide tcgen05 pipeline with its barriers does not suit, and on the CUDA cores they were bound by the shared-memory
 // reads of their operands (a thread's four outputs took five 16-byte loads a step). Every operand is split in two tf32
-// numbers, x = hi + lo with hi = tf32(x) and lo = tf32(x - hi), and a product is three instructions, lo x hi + hi x lo +
+// numbers, x = hi + lo with hi the upper 19 bits of x and lo those of x - hi, and a product is three instructions, lo x hi + hi x lo +
 // hi x hi (lo x lo is below 2^-22 of the term): fp32 accuracy to within the rounding of the sums.
 __device__ __forceinline__ void spl_split_tf32(float x, uint32_t &hi, uint32_t &lo) {
-    asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(hi) : "f"(x));
-    const float rest = x - __uint_as_float(hi);
-    asm("cvt.rna.tf32.f32 %0, %1;\n" : "=r"(lo) : "f"(rest));
+    // The instruction reads the upper 19 bits of an operand register: hi is x with the rest cleared, lo the exact remainder
+    // (of which the instruction again reads the upper 19 bits: what it drops is below 2^-21 of x).
+    hi = __float_as_uint(x) & 0xFFFFE000u;
+    lo = __float_as_uint(x - __uint_as_float(hi));
 }
 // c += a b for a 16 x 8 (row-major) and b 8 x 8 (column-major) in the instruction's register layout: with g = lane / 4 and
 // t = lane % 4, a = {(g, t), (g + 8, t), (g, t + 4), (g + 8, t + 4)}, b = {(k = t, n = g), (k = t + 4, n = g)},
