@@ -46,18 +46,49 @@ struct SplGdnChunkTables {
     int run_count, chunk_count;
 };
 
+// The matrix products of the prepare and scan kernels run on the tensor cores' warp-level instruction (m16n8k8, tf32
+// operands, fp32 accumulators): they are fp32 products of small matrices in a chain (a chunk's depend on the state the one
+// before left; T on A), which the block-wide tcgen05 pipeline with its barriers does not suit, and on the CUDA cores they were bound by the shared-memory
+// reads of their operands (a thread's four outputs took five 16-byte loads a step). Every operand is split in two tf32
+// numbers, x = hi + lo with hi the upper 19 bits of x and lo those of x - hi, and a product is three instructions, lo x hi + hi x lo +
+// hi x hi (lo x lo is below 2^-22 of the term): fp32 accuracy to within the rounding of the sums.
+__device__ __forceinline__ void spl_split_tf32(float x, uint32_t &hi, uint32_t &lo) {
+    // The instruction reads the upper 19 bits of an operand register: hi is x with the rest cleared, lo the exact remainder
+    // (of which the instruction again reads the upper 19 bits: what it drops is below 2^-21 of x).
+    hi = __float_as_uint(x) & 0xFFFFE000u;
+    lo = __float_as_uint(x - __uint_as_float(hi));
+}
+// c += a b for a 16 x 8 (row-major) and b 8 x 8 (column-major) in the instruction's register layout: with g = lane / 4 and
+// t = lane % 4, a = {(g, t), (g + 8, t), (g, t + 4), (g + 8, t + 4)}, b = {(k = t, n = g), (k = t + 4, n = g)},
+// c = {(g, 2t), (g, 2t + 1), (g + 8, 2t), (g + 8, 2t + 1)}.
+__device__ __forceinline__ void spl_mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void spl_mma_3xtf32(float (&c)[4], const float (&a)[4], const float (&b)[2]) {
+    uint32_t ah[4], al[4], bh[2], bl[2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) spl_split_tf32(a[i], ah[i], al[i]);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) spl_split_tf32(b[i], bh[i], bl[i]);
+    spl_mma_tf32(c, al, bh); spl_mma_tf32(c, ah, bl); spl_mma_tf32(c, ah, bh);
+}
+
+#define SPL_GDN_KLD (SPL_GDN_D + 8)     // floats between rows of a D-wide matrix read as a product's k x n operand, whose lanes go four rows by eight columns
+#define SPL_GDN_TLD (SPL_GDN_CHUNK + 4)   // floats between rows of T
+
 // Grid (value heads, chunks), 256 threads. Everything of a chunk that does not depend on the state it starts from.
 __global__ void __launch_bounds__(256)
 spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restrict__ proj, const uint16_t *__restrict__ a_log,
                              const uint16_t *__restrict__ dt_bias, SplGdnChunkTables tables, float *records, SplGdnParams p) {
     spl_grid_begin();
-    constexpr int D = SPL_GDN_D, C = SPL_GDN_CHUNK, LD = SPL_GDN_LD;      // shared rows of D floats are LD apart: rows read side by side fall in different banks
+    constexpr int D = SPL_GDN_D, C = SPL_GDN_CHUNK, LD = SPL_GDN_LD, KLD = SPL_GDN_KLD, TLD = SPL_GDN_TLD;      // shared rows are padded: rows read side by side fall in different banks
     extern __shared__ __align__(16) float spl_gdn_chunk_smem[];
     float *kh = spl_gdn_chunk_smem;            // [C][LD] k^
-    float *x = kh + C * LD;                     // [C][LD] q^, then b g k^, then b v
-    float *am = x + C * LD;                     // [C][C] A, then P
-    float *tm = am + C * C;                     // [C][C + 1] T (rows padded against bank conflicts)
-    float *g = tm + C * (C + 1);                // [C] log of the running decay product
+    float *x = kh + C * LD;                     // [C][LD] q^, then (rows KLD apart: the k x n operand of a product) b g k^, then b v
+    float *am = x + C * KLD;                    // [C][C] A
+    float *tm = am + C * C;                     // [C][TLD] T
+    float *g = tm + C * TLD;                    // [C] log of the running decay product
     float *beta = g + C;                        // [C]
     float *scal = beta + C;                     // [C][2] invQ, invK
     const int h = blockIdx.x, chunk = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -103,21 +134,35 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
     __syncthreads();
     const float g_end = g[C - 1];      // rows past the chunk's end have log decay 0, so this is the last token's
     // A[t][s] = b_t (g_t / g_s) (k^_t . k^_s) below the diagonal; P[t][s] = (g_t / g_s) (q^_t . k^_s) on and below it (to the record).
-    for (int idx = tid; idx < C * C; idx += 256) {
-        const int t = idx / C, s = idx % C;
-        float ka = 0.0f, qa = 0.0f;
-        if (s <= t) {
-            const float4 *kt = reinterpret_cast<const float4 *>(kh + t * LD), *ks = reinterpret_cast<const float4 *>(kh + s * LD), *qt = reinterpret_cast<const float4 *>(x + t * LD);
-#pragma unroll 8
-            for (int i = 0; i < D / 4; ++i) {
-                const float4 a4 = kt[i], b4 = ks[i], c4 = qt[i];
-                ka += a4.x * b4.x + a4.y * b4.y + a4.z * b4.z + a4.w * b4.w;
-                qa += c4.x * b4.x + c4.y * b4.y + c4.z * b4.z + c4.w * b4.w;
+    // Tiles of 16 tokens t by 8 tokens s on and below the diagonal (twenty of 32), both products of a tile together: they
+    // share the k^_s operand.
+    {
+        const int gq = lane >> 2, tq = lane & 3;
+        for (int tile = warp; tile < 20; tile += 8) {
+            const int mt = tile < 2 ? 0 : tile < 6 ? 1 : tile < 12 ? 2 : 3, nt = tile - (mt == 0 ? 0 : mt == 1 ? 2 : mt == 2 ? 6 : 12);
+            const int m0 = 16 * mt, n0 = 8 * nt;
+            float ka[4] = {0.0f, 0.0f, 0.0f, 0.0f}, qa[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+            for (int k0 = 0; k0 < D; k0 += 8) {
+                const float b[2] = {kh[(n0 + gq) * LD + k0 + tq], kh[(n0 + gq) * LD + k0 + tq + 4]};
+                const float ak[4] = {kh[(m0 + gq) * LD + k0 + tq], kh[(m0 + gq + 8) * LD + k0 + tq], kh[(m0 + gq) * LD + k0 + tq + 4], kh[(m0 + gq + 8) * LD + k0 + tq + 4]};
+                const float aq[4] = {x[(m0 + gq) * LD + k0 + tq], x[(m0 + gq + 8) * LD + k0 + tq], x[(m0 + gq) * LD + k0 + tq + 4], x[(m0 + gq + 8) * LD + k0 + tq + 4]};
+                spl_mma_3xtf32(ka, ak, b);
+                spl_mma_3xtf32(qa, aq, b);
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int t = m0 + gq + 8 * (e >> 1), s = n0 + 2 * tq + (e & 1);
+                const float ratio = s <= t ? expf(g[t] - g[s]) : 0.0f;
+                am[t * C + s] = s < t ? beta[t] * ratio * ka[e] : 0.0f;
+                rec[SPL_GDN_REC_P + t * C + s] = s <= t ? ratio * qa[e] : 0.0f;
             }
         }
-        const float ratio = s <= t ? expf(g[t] - g[s]) : 0.0f;
-        am[idx] = s < t ? beta[t] * ratio * ka : 0.0f;
-        rec[SPL_GDN_REC_P + idx] = s <= t ? ratio * qa : 0.0f;
+        // The tiles above the diagonal are zero.
+        for (int idx = tid; idx < C * C; idx += 256) {
+            const int t = idx / C, s = idx % C;
+            if ((s >> 3) > 2 * (t >> 4) + 1) { am[idx] = 0.0f; rec[SPL_GDN_REC_P + idx] = 0.0f; }
+        }
     }
     // g_t q^_t and (g_C / g_s) k^_s to the record while q^ is still in shared memory.
     for (int idx = tid; idx < C * D; idx += 256) {
@@ -133,10 +178,10 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
         const int c = tid >> 2, part = tid & 3;
         for (int t = 0; t < C; ++t) {
             float acc = 0.0f;
-            for (int s = c + part; s < t; s += 4) acc -= am[t * C + s] * tm[s * (C + 1) + c];      // T is lower triangular: T[s][c] = 0 for s < c
+            for (int s = c + part; s < t; s += 4) acc -= am[t * C + s] * tm[s * TLD + c];      // T is lower triangular: T[s][c] = 0 for s < c
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (part == 0) tm[t * (C + 1) + c] = t > c ? acc : t == c ? 1.0f : 0.0f;
+            if (part == 0) tm[t * TLD + c] = t > c ? acc : t == c ? 1.0f : 0.0f;
             __syncwarp();
         }
     }
@@ -155,69 +200,45 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
                 const float4 v4 = *reinterpret_cast<const float4 *>(act + size_t(first + tt) * p.channels + 2 * KH * D + h * D + i4 * 4);
                 v = make_float4(v4.x * f, v4.y * f, v4.z * f, v4.w * f);
             }
-            *reinterpret_cast<float4 *>(x + tt * LD + i4 * 4) = v;
+            *reinterpret_cast<float4 *>(x + tt * KLD + i4 * 4) = v;
         }
         __syncthreads();
-        // out[t][i] = sum_{s<=t} T[t][s] x[s][i]: a thread four rows t and four columns i (rows t, t + 16, t + 32, t + 48: even work).
+        // out[t][i] = sum_{s<=t} T[t][s] x[s][i]: warp w has tokens 16 (w / 2) ... + 15 and columns 64 (w % 2) ... + 63, eight tiles
+        // of eight columns that share the T operand; T is lower triangular, so the sum stops at the warp's last token.
         {
-            const int ig = tid & 31, tg = tid >> 5;       // columns 4 ig .. + 3; rows tg, tg + 8, ... (8 of them, in two rounds of four)
-            for (int round = 0; round < 2; ++round) {
-                float4 acc[4];
+            const int gq = lane >> 2, tq = lane & 3, m0 = 16 * (warp >> 1), c0 = 64 * (warp & 1);
+            float acc[8][4];
 #pragma unroll
-                for (int r = 0; r < 4; ++r) acc[r] = make_float4(0, 0, 0, 0);
-                const int t_max = tg + 8 * (4 * round + 3);
-                for (int s = 0; s <= t_max; ++s) {
-                    const float4 xv = *reinterpret_cast<const float4 *>(x + s * LD + ig * 4);
+            for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        const int t = tg + 8 * (4 * round + r);
-                        const float w = s <= t ? tm[t * (C + 1) + s] : 0.0f;
-                        acc[r].x += w * xv.x; acc[r].y += w * xv.y; acc[r].z += w * xv.z; acc[r].w += w * xv.w;
-                    }
+                for (int e = 0; e < 4; ++e) acc[nt][e] = 0.0f;
+            for (int k0 = 0; k0 < m0 + 16; k0 += 8) {
+                const float a[4] = {tm[(m0 + gq) * TLD + k0 + tq], tm[(m0 + gq + 8) * TLD + k0 + tq], tm[(m0 + gq) * TLD + k0 + tq + 4], tm[(m0 + gq + 8) * TLD + k0 + tq + 4]};
+                uint32_t ah[4], al[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) spl_split_tf32(a[e], ah[e], al[e]);
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt) {
+                    uint32_t bh[2], bl[2];
+                    spl_split_tf32(x[(k0 + tq) * KLD + c0 + 8 * nt + gq], bh[0], bl[0]);
+                    spl_split_tf32(x[(k0 + tq + 4) * KLD + c0 + 8 * nt + gq], bh[1], bl[1]);
+                    spl_mma_tf32(acc[nt], al, bh); spl_mma_tf32(acc[nt], ah, bl); spl_mma_tf32(acc[nt], ah, bh);
                 }
+            }
+            float *out = rec + (pass == 0 ? SPL_GDN_REC_W : SPL_GDN_REC_UV);
 #pragma unroll
-                for (int r = 0; r < 4; ++r) {
-                    const int t = tg + 8 * (4 * round + r);
-                    *reinterpret_cast<float4 *>(rec + (pass == 0 ? SPL_GDN_REC_W : SPL_GDN_REC_UV) + t * D + ig * 4) = acc[r];
-                }
+            for (int nt = 0; nt < 8; ++nt) {
+                *reinterpret_cast<float2 *>(out + (m0 + gq) * D + c0 + 8 * nt + 2 * tq) = make_float2(acc[nt][0], acc[nt][1]);
+                *reinterpret_cast<float2 *>(out + (m0 + gq + 8) * D + c0 + 8 * nt + 2 * tq) = make_float2(acc[nt][2], acc[nt][3]);
             }
         }
         __syncthreads();
     }
 }
 __host__ __device__ constexpr size_t spl_gdn_chunk_prepare_smem() {
-    return sizeof(float) * (2 * SPL_GDN_CHUNK * SPL_GDN_LD + SPL_GDN_CHUNK * SPL_GDN_CHUNK + SPL_GDN_CHUNK * (SPL_GDN_CHUNK + 1) + 4 * SPL_GDN_CHUNK);
+    return sizeof(float) * (SPL_GDN_CHUNK * SPL_GDN_LD + SPL_GDN_CHUNK * SPL_GDN_KLD + SPL_GDN_CHUNK * SPL_GDN_CHUNK + SPL_GDN_CHUNK * SPL_GDN_TLD + 4 * SPL_GDN_CHUNK);
 }
 
-// The scan's matrix products run on the tensor cores' warp-level instruction (m16n8k8, tf32 operands, fp32 accumulators):
-// they are fp32 products of small matrices in a chain (each chunk's depend on the state the one before left), which the
-// block-wide tcgen05 pipeline with its barriers does not suit, and on the CUDA cores they were bound by the shared-memory
-// reads of their operands (a thread's four outputs took five 16-byte loads a step). Every operand is split in two tf32
-// numbers, x = hi + lo with hi the upper 19 bits of x and lo those of x - hi, and a product is three instructions, lo x hi + hi x lo +
-// hi x hi (lo x lo is below 2^-22 of the term): fp32 accuracy to within the rounding of the sums.
-__device__ __forceinline__ void spl_split_tf32(float x, uint32_t &hi, uint32_t &lo) {
-    // The instruction reads the upper 19 bits of an operand register: hi is x with the rest cleared, lo the exact remainder
-    // (of which the instruction again reads the upper 19 bits: what it drops is below 2^-21 of x).
-    hi = __float_as_uint(x) & 0xFFFFE000u;
-    lo = __float_as_uint(x - __uint_as_float(hi));
-}
-// c += a b for a 16 x 8 (row-major) and b 8 x 8 (column-major) in the instruction's register layout: with g = lane / 4 and
-// t = lane % 4, a = {(g, t), (g + 8, t), (g, t + 4), (g + 8, t + 4)}, b = {(k = t, n = g), (k = t + 4, n = g)},
-// c = {(g, 2t), (g, 2t + 1), (g + 8, 2t), (g + 8, 2t + 1)}.
-__device__ __forceinline__ void spl_mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
-    asm volatile("mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
-}
-__device__ __forceinline__ void spl_mma_3xtf32(float (&c)[4], const float (&a)[4], const float (&b)[2]) {
-    uint32_t ah[4], al[4], bh[2], bl[2];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) spl_split_tf32(a[i], ah[i], al[i]);
-#pragma unroll
-    for (int i = 0; i < 2; ++i) spl_split_tf32(b[i], bh[i], bl[i]);
-    spl_mma_tf32(c, al, bh); spl_mma_tf32(c, ah, bl); spl_mma_tf32(c, ah, bh);
-}
-
-#define SPL_GDN_KLD (SPL_GDN_D + 8)     // floats between rows of Kd: read as a product's k x n operand, whose lanes go four rows by eight columns
 #define SPL_GDN_ULD 24                  // floats between rows of U (sixteen values a row): the same pattern over its rows
 
 // Grid (value heads, chunked runs, SPL_GDN_SLICES), 256 threads. The run's chunks in order over one slice of the value
