@@ -86,11 +86,12 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
     extern __shared__ __align__(16) float spl_gdn_chunk_smem[];
     float *kh = spl_gdn_chunk_smem;            // [C][LD] k^
     float *x = kh + C * LD;                     // [C][LD] q^, then (rows KLD apart: the k x n operand of a product) b g k^, then b v
-    float *am = x + C * KLD;                    // [C][C] A
-    float *tm = am + C * C;                     // [C][TLD] T
+    float *am = x + C * KLD;                    // [C][TLD] A
+    float *tm = am + C * TLD;                   // [C][TLD] T
     float *g = tm + C * TLD;                    // [C] log of the running decay product
     float *beta = g + C;                        // [C]
     float *scal = beta + C;                     // [C][2] invQ, invK
+    float *eg = scal + 2 * C, *ed = eg + C;    // [C] each: g_t and g_C / g_t as numbers (g holds logarithms)
     const int h = blockIdx.x, chunk = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t first = tables.chunks[chunk * 4 + 1], count = tables.chunks[chunk * 4 + 2];
     const int VH = p.value_heads, KH = p.key_heads, hk = h / (VH / KH);
@@ -133,6 +134,8 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
     for (int idx = tid; idx < C * D; idx += 256) { const int tt = idx / D, at = tt * LD + idx % D; kh[at] *= scal[tt * 2 + 1]; x[at] *= scal[tt * 2]; }
     __syncthreads();
     const float g_end = g[C - 1];      // rows past the chunk's end have log decay 0, so this is the last token's
+    if (tid < C) { eg[tid] = expf(g[tid]); ed[tid] = expf(g_end - g[tid]); }
+    __syncthreads();
     // A[t][s] = b_t (g_t / g_s) (k^_t . k^_s) below the diagonal; P[t][s] = (g_t / g_s) (q^_t . k^_s) on and below it (to the record).
     // Tiles of 16 tokens t by 8 tokens s on and below the diagonal (twenty of 32), both products of a tile together: they
     // share the k^_s operand.
@@ -154,45 +157,77 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
             for (int e = 0; e < 4; ++e) {
                 const int t = m0 + gq + 8 * (e >> 1), s = n0 + 2 * tq + (e & 1);
                 const float ratio = s <= t ? expf(g[t] - g[s]) : 0.0f;
-                am[t * C + s] = s < t ? beta[t] * ratio * ka[e] : 0.0f;
+                am[t * TLD + s] = s < t ? beta[t] * ratio * ka[e] : 0.0f;
                 rec[SPL_GDN_REC_P + t * C + s] = s <= t ? ratio * qa[e] : 0.0f;
             }
         }
         // The tiles above the diagonal are zero.
         for (int idx = tid; idx < C * C; idx += 256) {
             const int t = idx / C, s = idx % C;
-            if ((s >> 3) > 2 * (t >> 4) + 1) { am[idx] = 0.0f; rec[SPL_GDN_REC_P + idx] = 0.0f; }
+            if ((s >> 3) > 2 * (t >> 4) + 1) { am[t * TLD + s] = 0.0f; rec[SPL_GDN_REC_P + idx] = 0.0f; }
         }
     }
     // g_t q^_t and (g_C / g_s) k^_s to the record while q^ is still in shared memory.
     for (int idx = tid; idx < C * D; idx += 256) {
         const int tt = idx / D, at = tt * LD + idx % D;
-        rec[SPL_GDN_REC_QG + idx] = x[at] * expf(g[tt]);
-        rec[SPL_GDN_REC_KD + idx] = kh[at] * expf(g_end - g[tt]);
+        rec[SPL_GDN_REC_QG + idx] = x[at] * eg[tt];
+        rec[SPL_GDN_REC_KD + idx] = kh[at] * ed[tt];
     }
     if (tid == 0) rec[SPL_GDN_REC_GC] = expf(g_end);
     __syncthreads();
-    // T = (I + A)^-1 by forward substitution, four threads a column: T[t][c] = [t == c] - sum_{s<t} A[t][s] T[s][c], the sum
-    // in four interleaved parts added in one fixed order. A column's threads sit in one warp.
+    // T = (I + A)^-1 in blocks of sixteen tokens. The four diagonal blocks by forward substitution, side by side, four
+    // threads a column: T[t][c] = [t == c] - sum_{c <= s < t} A[t][s] T[s][c], the sum in four interleaved parts added in one
+    // fixed order (a column's threads sit in one warp). Then the blocks below the diagonal, a sub-diagonal at a time:
+    // T(i, j) = -T(i, i) sum_{j <= k < i} A(i, k) T(k, j), two small products a warp (a block's eight columns each).
     {
-        const int c = tid >> 2, part = tid & 3;
-        for (int t = 0; t < C; ++t) {
+        const int blk = tid >> 6, c = (tid & 63) >> 2, part = tid & 3, base = 16 * blk;
+        for (int t = 0; t < 16; ++t) {
             float acc = 0.0f;
-            for (int s = c + part; s < t; s += 4) acc -= am[t * C + s] * tm[s * TLD + c];      // T is lower triangular: T[s][c] = 0 for s < c
+            for (int sx = c + part; sx < t; sx += 4) acc -= am[(base + t) * TLD + base + sx] * tm[(base + sx) * TLD + base + c];
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (part == 0) tm[t * TLD + c] = t > c ? acc : t == c ? 1.0f : 0.0f;
+            if (part == 0) tm[(base + t) * TLD + base + c] = t > c ? acc : t == c ? 1.0f : 0.0f;
             __syncwarp();
         }
+        // The blocks above the diagonal are zero.
+        for (int idx = tid; idx < C * C; idx += 256) { const int t = idx / C, sx = idx % C; if ((sx >> 4) > (t >> 4)) tm[t * TLD + sx] = 0.0f; }
     }
     __syncthreads();
+    {
+        const int gq = lane >> 2, tq = lane & 3;
+        float *scratch = x + warp * 16 * 12;          // [16][12] a warp: the inner sum, handed from the first product's result layout to the second's operand layout (x is free here)
+        for (int d = 1; d < 4; ++d) {
+            if (warp < 2 * (4 - d)) {
+                const int i = d + (warp >> 1), j = i - d, n0 = 16 * j + 8 * (warp & 1);
+                float inner[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                for (int k0 = 16 * j; k0 < 16 * i; k0 += 8) {
+                    const float a[4] = {am[(16 * i + gq) * TLD + k0 + tq], am[(16 * i + gq + 8) * TLD + k0 + tq], am[(16 * i + gq) * TLD + k0 + tq + 4], am[(16 * i + gq + 8) * TLD + k0 + tq + 4]};
+                    const float b[2] = {tm[(k0 + tq) * TLD + n0 + gq], tm[(k0 + tq + 4) * TLD + n0 + gq]};
+                    spl_mma_3xtf32(inner, a, b);
+                }
+                scratch[gq * 12 + 2 * tq] = inner[0]; scratch[gq * 12 + 2 * tq + 1] = inner[1];
+                scratch[(gq + 8) * 12 + 2 * tq] = inner[2]; scratch[(gq + 8) * 12 + 2 * tq + 1] = inner[3];
+                __syncwarp();
+                float out[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int k0 = 0; k0 < 16; k0 += 8) {
+                    const float a[4] = {tm[(16 * i + gq) * TLD + 16 * i + k0 + tq], tm[(16 * i + gq + 8) * TLD + 16 * i + k0 + tq], tm[(16 * i + gq) * TLD + 16 * i + k0 + tq + 4], tm[(16 * i + gq + 8) * TLD + 16 * i + k0 + tq + 4]};
+                    const float b[2] = {scratch[(k0 + tq) * 12 + gq], scratch[(k0 + tq + 4) * 12 + gq]};
+                    spl_mma_3xtf32(out, a, b);
+                }
+                tm[(16 * i + gq) * TLD + n0 + 2 * tq] = -out[0]; tm[(16 * i + gq) * TLD + n0 + 2 * tq + 1] = -out[1];
+                tm[(16 * i + gq + 8) * TLD + n0 + 2 * tq] = -out[2]; tm[(16 * i + gq + 8) * TLD + n0 + 2 * tq + 1] = -out[3];
+            }
+            __syncthreads();
+        }
+    }
     // W = T diag(b g) K^ and Uv = T diag(b) V: x <- b g k^, product, then x <- b v, product.
     for (int pass = 0; pass < 2; ++pass) {
         for (int idx = tid; idx < C * (D / 4); idx += 256) {
             const int tt = idx / (D / 4), i4 = idx % (D / 4);
             float4 v = make_float4(0, 0, 0, 0);
             if (pass == 0) {
-                const float f = beta[tt] * expf(g[tt]);
+                const float f = beta[tt] * eg[tt];
                 const float4 k4 = *reinterpret_cast<const float4 *>(kh + tt * LD + i4 * 4);
                 v = make_float4(k4.x * f, k4.y * f, k4.z * f, k4.w * f);
             } else if (tt < int(count)) {
@@ -236,7 +271,7 @@ spl_gdn_chunk_prepare_kernel(const float *__restrict__ act, const float *__restr
     }
 }
 __host__ __device__ constexpr size_t spl_gdn_chunk_prepare_smem() {
-    return sizeof(float) * (SPL_GDN_CHUNK * SPL_GDN_LD + SPL_GDN_CHUNK * SPL_GDN_KLD + SPL_GDN_CHUNK * SPL_GDN_CHUNK + SPL_GDN_CHUNK * SPL_GDN_TLD + 4 * SPL_GDN_CHUNK);
+    return sizeof(float) * (SPL_GDN_CHUNK * SPL_GDN_LD + SPL_GDN_CHUNK * SPL_GDN_KLD + 2 * SPL_GDN_CHUNK * SPL_GDN_TLD + 6 * SPL_GDN_CHUNK);
 }
 
 #define SPL_GDN_ULD 24                  // floats between rows of U (sixteen values a row): the same pattern over its rows
