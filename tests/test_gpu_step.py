@@ -252,6 +252,33 @@ def test_long_context_attention_and_span_split(toks):
         assert np.abs(gl - results[0][0]).max() <= 2e-2
 
 
+def test_sixteen_row_verify_blocks_accepted_across_the_recurrence_kernels_pass_boundary(toks):
+    """The longest speculative run (16 rows, Engine.swift:300) is two eight-token passes of the recurrence kernel, the state
+    moved on between them by the journal's rule; accepting 11, then 9, then all 16 rows replays entries from both passes.
+    Logits of every block, then state and journal, against the oracle."""
+    g = S.tiny_geometry()
+    pair = Pair(g, S.EngineConfig(max_slots=2, max_rows=64, kv_pages=8, max_context=1024))
+    gl, ol = pair.step([S.EngineRow(0, toks[i], i, i == 19) for i in range(20)])
+    check(gl, ol, g.vocab, "prompt")
+    position = 20
+    for n, accepted in enumerate((11, 9, 16, 3)):
+        rows = [S.EngineRow(0, toks[100 + 20 * n + i], position + i, True, True) for i in range(16)]
+        if n == 1:          # another slot's ordinary rows ride along: 13 rows, two passes that store the state
+            rows += [S.EngineRow(1, toks[300 + i], i, i == 12) for i in range(13)]
+        gl, ol = pair.step(rows)
+        worst = check(gl, ol, g.vocab, f"16-row block {n}")
+        pair.accept(0, accepted, position + accepted)
+        position += accepted
+    gl, ol = pair.step([S.EngineRow(0, toks[400], position, True), S.EngineRow(1, toks[401], 13, True)])
+    check(gl, ol, g.vocab, "decode rows after the blocks")
+    for index in range(3):
+        for which, tol in (("state", 2e-3), ("journal", 5e-3)):
+            ob = pair.oengine.buffer(which, index); gb = pair.engine.debug_read(which, index, ob.size)
+            worst = float(np.abs(gb - ob).max() / max(1.0, np.abs(ob).max()))
+            observed(f"{which} of gated-delta block {index} after 16-row verify blocks accepted 11, 9, 16, 3: {worst:.2e} of the largest (<= {tol})")
+            assert worst <= tol, (which, index)
+
+
 def test_rejected_steps_leave_the_engine_usable(toks):
     g = S.tiny_geometry()
     engine = S.Engine(g, S.EngineConfig(max_slots=2, max_rows=32, kv_pages=2, max_context=1024))
