@@ -402,6 +402,15 @@ def main():
             engine.accept_verify(0, GGUF_BLOCK, at)
             if n >= 2:
                 seconds += stats.gpu_seconds
+        # Two more steps with events around every launch, for the classes' shares.
+        engine.debug_profile(True)
+        for n in range(2):
+            rows = [S.EngineRow(0, int(splitmix_at(TOKEN_SEED ^ 0x66, at + i) % g.vocab), at + i, True, True) for i in range(GGUF_BLOCK)]
+            engine.step(rows)
+            at += GGUF_BLOCK
+            engine.accept_verify(0, GGUF_BLOCK, at)
+        gguf_shares = engine.profile_read()
+        engine.debug_profile(False)
         wcount, _ = weights_per_step(g)
         head_weights = g.vocab * g.hidden
         gguf_bytes = (wcount - head_weights) * 176 / 256 + head_weights * 210 / 256
@@ -410,7 +419,8 @@ def main():
         gguf = {"workload": f"one session at {gguf_context} tokens of context, {GGUF_BLOCK}-row verify blocks, every block tensor Q5_K, embedding and head Q6_K "
                             "(GGUF super-blocks), plain norms, unfused SiLU gate",
                 "ms_per_step": 1000.0 * seconds / args.steps, "tok_per_s": GGUF_BLOCK * args.steps / seconds, "weights_gb": gguf_bytes / 1e9, "kv_gb": kv_bytes / 1e9,
-                "hbm_gbs": (gguf_bytes + kv_bytes) / (seconds / args.steps) / 1e9}
+                "hbm_gbs": (gguf_bytes + kv_bytes) / (seconds / args.steps) / 1e9,
+                "class_ms_per_step": {k: v["ms"] / 2 for k, v in gguf_shares.items()}}
     if rank == 0:
         peak, peak_source = measured_peak_gbs()
         gemm = prof["gemm_q4"]
