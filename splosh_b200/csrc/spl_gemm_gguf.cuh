@@ -13,10 +13,13 @@
 // fp16 weights and store them into tensor memory as the A operand, the activations (held as fp16) are the B operand.
 //
 // Device layout of a weight (private to this library): for each tile of 128 output columns and each super-block,
-// the columns' native blocks cut in 16-byte pieces, [piece][column][16 bytes] (a column's thread reads its piece
-// beside its neighbours': no bank conflicts). Q4_K: header (d, dmin, 12 scale bytes), then 8 pieces of 4-bit codes.
-// Q5_K: header, 2 pieces of fifth bits, 8 of codes. Q6_K is reordered: 16 scales, (d, padding), 8 pieces of low
-// nibbles, 4 of high bits.
+// the columns' blocks cut in 16-byte pieces, [piece][column][16 bytes] (a column's thread reads its piece beside its
+// neighbours': no bank conflicts). Q4_K keeps the native bytes: header (d, dmin, 12 scale bytes), then 8 pieces of 4-bit
+// codes. Q5_K and Q6_K are widened to ONE BYTE A CODE when they are repacked (the fifth bit, or the two high bits, merged
+// into the nibble then, once, and not by every block of every step): header pieces first (Q5_K: d, dmin, scale bytes;
+// Q6_K: 16 scales, then d), then 16 pieces of codes in contraction order. The dequant stage was bound by its integer
+// instructions, not by memory: the wider layout reads 272 (288) bytes a block where the native one has 176 (210), and
+// forms a weight from a byte permute, a subtraction and a multiply-add.
 #pragma once
 #include "spl_gemm_tc.cuh"
 
@@ -24,7 +27,7 @@
 #define SPL_GGUF_Q5K 13
 #define SPL_GGUF_Q6K 14
 __host__ __device__ constexpr int spl_gguf_block_bytes(int format) { return format == SPL_GGUF_Q6K ? 210 : format == SPL_GGUF_Q5K ? 176 : 144; }
-__host__ __device__ constexpr int spl_gguf_pieces(int format) { return format == SPL_GGUF_Q6K ? 14 : format == SPL_GGUF_Q5K ? 11 : 9; }
+__host__ __device__ constexpr int spl_gguf_pieces(int format) { return format == SPL_GGUF_Q6K ? 18 : format == SPL_GGUF_Q5K ? 17 : 9; }
 
 struct SplGgufDev {
     int n = 0, ld = 0, tiles = 0, k = 0, format = 0;
@@ -43,9 +46,29 @@ __global__ void spl_repack_gguf_kernel(const unsigned char *__restrict__ native,
         const unsigned char *src = native + (size_t(row) * supers + sb) * bytes;
         unsigned char out[16];
         if (format == SPL_GGUF_Q6K) {
-            // native: ql[128] qh[64] scales[16] d[2]  ->  scales, (d, 0...), ql, qh
-            const int from = piece == 0 ? 192 : piece == 1 ? 208 : piece < 10 ? 16 * (piece - 2) : 128 + 16 * (piece - 10);
-            for (int i = 0; i < 16; ++i) out[i] = (piece == 1 && i >= 2) ? 0 : src[from + i];
+            // native: ql[128] qh[64] scales[16] d[2]  ->  scales, (d, 0...), then a byte a code: piece 2 + 4 g + 2 part + q4
+            // holds elements 64 g + 32 part + 16 q4 .. + 15 (low nibble from ql, two high bits from qh)
+            if (piece < 2) {
+                for (int i = 0; i < 16; ++i) out[i] = piece == 0 ? src[192 + i] : i < 2 ? src[208 + i] : 0;
+            } else {
+                const int c = piece - 2, g = c >> 2, part = (c >> 1) & 1, q4 = c & 1, half128 = g >> 1, hi = g & 1;
+                for (int i = 0; i < 16; ++i) {
+                    const int low = src[64 * half128 + 32 * part + 16 * q4 + i], high = src[128 + 32 * half128 + 16 * q4 + i];
+                    out[i] = uint8_t(((low >> (4 * hi)) & 15) | (((high >> (4 * hi + 2 * part)) & 3) << 4));
+                }
+            }
+        } else if (format == SPL_GGUF_Q5K) {
+            // native: d dmin scales[12] qh[32] qs[128]  ->  header, then a byte a code: piece 1 + 4 g + 2 part + q4 holds
+            // elements 16 q4 .. + 15 of sub-block 2 g + part (nibble from qs, fifth bit from qh)
+            if (piece == 0) {
+                for (int i = 0; i < 16; ++i) out[i] = src[i];
+            } else {
+                const int c = piece - 1, g = c >> 2, part = (c >> 1) & 1, q4 = c & 1;
+                for (int i = 0; i < 16; ++i) {
+                    const int l = 16 * q4 + i;
+                    out[i] = uint8_t(((src[48 + 32 * g + l] >> (4 * part)) & 15) | (((src[16 + l] >> (2 * g + part)) & 1) << 4));
+                }
+            }
         } else {
             for (int i = 0; i < 16; ++i) out[i] = src[16 * piece + i];
         }
@@ -55,10 +78,12 @@ __global__ void spl_repack_gguf_kernel(const unsigned char *__restrict__ native,
     }
 }
 
-#define SPL_GG_CSTAGES 3
+// Stages of weight blocks in flight: three, or two where the widened blocks beside 64 rows of activations would not fit
+// (as many as fit, five at 16 rows, were measured: no change, the kernel does not wait for memory).
+__host__ __device__ constexpr int spl_gguf_cstages(int rn, int format) { return (rn >= 64 && format != SPL_GGUF_Q4K) ? 2 : 3; }
 #define SPL_GG_THREADS 480       // warps 0-3, 8-11 and 4-7: three dequant sets; 12 copies; 13-14 tensor-core issue
 __host__ __device__ constexpr size_t spl_gguf_smem_bytes(int rn, int format) {
-    return 1024 + size_t(SPL_GG_CSTAGES) * spl_gguf_pieces(format) * 2048 + size_t(4) * SPL_TC_SUPER * rn * 128 + 1024;
+    return 1024 + size_t(spl_gguf_cstages(rn, format)) * spl_gguf_pieces(format) * 2048 + size_t(4) * SPL_TC_SUPER * rn * 128 + 1024;
 }
 __device__ __forceinline__ float spl_half_bits_to_float(uint32_t bits) { return __half2float(__ushort_as_half(uint16_t(bits))); }
 // Two fp32 values -> one register of two fp16, each rounded to nearest even.
@@ -68,15 +93,18 @@ __device__ __forceinline__ uint32_t spl_pack_half2(float lo, float hi) {
     return out;
 }
 
-// Byte `B` of `word` as a float, exactly. The integer-to-float conversion runs at a quarter of the other instructions' rate
-// and bounded this kernel when every code went through it; three bytes in four are instead placed under the exponent of
-// 2^23 by a byte permute (where the byte is the number 2^23 + byte) and 2^23 is subtracted, and the fourth still takes the
-// conversion, whose pipe is otherwise idle (measured: 11.0 ms of GEMM a step with four conversions, 10.3 with none, 10.0
-// with one).
+// Bytes `B` and `B + 1` of `word` less `bias`, as two floats, exactly: ONE byte permute places both bytes under the fp16
+// exponent of 2^10 (where a byte is the number 1024 + byte), and the mixed-precision addition (an fp16 term plus an fp32
+// term, in fp32) takes 1024 + bias away. The logic pipe bounds this kernel, and this is one of its instructions for two
+// codes. Measured, GEMM a 16-row step: every code through the integer-to-float conversion (a quarter-rate pipe) 11.0 ms;
+// a permute a code under the fp32 exponent of 2^23 and a subtraction 10.3 ms on the native layout, 8.4 ms on this one.
 template <int B>
-__device__ __forceinline__ float spl_byte_to_float(uint32_t word) {
-    if (B >= 3) return float(word >> 24);
-    return __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7650 | B)) - 8388608.0f;
+__device__ __forceinline__ float2 spl_bytes_to_float2(uint32_t word, float bias) {
+    const uint32_t pair = __byte_perm(word, 0x64006400u, 0x7050 | B | ((B + 1) << 8));
+    float2 x;
+    asm("{\n .reg .b16 lo, hi;\n mov.b32 {lo, hi}, %2;\n add.rn.f32.f16 %0, lo, %3;\n add.rn.f32.f16 %1, hi, %3;\n}\n"
+        : "=f"(x.x), "=f"(x.y) : "r"(pair), "f"(-1024.0f - bias));
+    return x;
 }
 
 // One 64-group of one column into 32 registers of fp16 pairs (k = 2c, 2c + 1 in register c). `stage` is the super-block's
@@ -96,23 +124,20 @@ __device__ __forceinline__ void spl_gguf_dequant64(const unsigned char *stage, i
 #pragma unroll
             for (int e = 0; e < 2; ++e) s[e] = d * float(int8_t((scw[(sbase + e) >> 2] >> (8 * ((sbase + e) & 3))) & 0xFFu));
 #pragma unroll
-            for (int q4 = 0; q4 < 2; ++q4) {              // sixteen elements a piece
-                const uint4 ql = *reinterpret_cast<const uint4 *>(stage + (2 + 4 * half128 + 2 * part + q4) * 2048 + col * 16);
-                const uint4 qh = *reinterpret_cast<const uint4 *>(stage + (10 + 2 * half128 + q4) * 2048 + col * 16);
-                const uint32_t lw[4] = {ql.x, ql.y, ql.z, ql.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
+            for (int q4 = 0; q4 < 2; ++q4) {              // sixteen codes a piece
+                const uint4 q = *reinterpret_cast<const uint4 *>(stage + (2 + 4 * g + 2 * part + q4) * 2048 + col * 16);
+                const uint32_t cw[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
                 for (int w = 0; w < 4; ++w) {
-                    const uint32_t low = (lw[w] >> (4 * hi)) & 0x0F0F0F0Fu, high = ((hw[w] >> (4 * hi + 2 * part)) & 0x03030303u) << 4;
-                    const uint32_t code = low | high;
-                    const float v[4] = {(spl_byte_to_float<0>(code) - 32.0f) * s[q4], (spl_byte_to_float<1>(code) - 32.0f) * s[q4],
-                                        (spl_byte_to_float<2>(code) - 32.0f) * s[q4], (spl_byte_to_float<3>(code) - 32.0f) * s[q4]};
-                    a[16 * part + 8 * q4 + 2 * w] = spl_pack_half2(v[0], v[1]);
-                    a[16 * part + 8 * q4 + 2 * w + 1] = spl_pack_half2(v[2], v[3]);
+                    const uint32_t code = cw[w];
+                    const float2 s2 = make_float2(s[q4], s[q4]);
+                    const float2 v01 = spl_mul2(spl_bytes_to_float2<0>(code, 32.0f), s2), v23 = spl_mul2(spl_bytes_to_float2<2>(code, 32.0f), s2);
+                    a[16 * part + 8 * q4 + 2 * w] = spl_pack_half2(v01.x, v01.y);
+                    a[16 * part + 8 * q4 + 2 * w + 1] = spl_pack_half2(v23.x, v23.y);
                 }
             }
         }
     } else {
-        constexpr int QH = FMT == SPL_GGUF_Q5K ? 1 : 0, CODES = FMT == SPL_GGUF_Q5K ? 3 : 1;      // first piece of fifth bits, of codes
         const uint4 header = *reinterpret_cast<const uint4 *>(stage + col * 16);
         const float d = spl_half_bits_to_float(header.x & 0xFFFFu), dmin = spl_half_bits_to_float(header.x >> 16);
         // scale bytes: header bytes 4..15 = words y, z, w (get_scale_min_k4 of the format; gguf_formats.h:160-178)
@@ -129,23 +154,38 @@ __device__ __forceinline__ void spl_gguf_dequant64(const unsigned char *stage, i
             }
             s[part] = d * float(scale); m[part] = -dmin * float(minimum);
         }
+        if (FMT == SPL_GGUF_Q5K) {
 #pragma unroll
-        for (int q4 = 0; q4 < 2; ++q4) {                  // sixteen bytes of codes: elements l = 16 q4 .. + 15 of both sub-blocks
-            const uint4 qs = *reinterpret_cast<const uint4 *>(stage + (CODES + 2 * g + q4) * 2048 + col * 16);
-            uint4 qh = make_uint4(0, 0, 0, 0);
-            if (FMT == SPL_GGUF_Q5K) qh = *reinterpret_cast<const uint4 *>(stage + (QH + q4) * 2048 + col * 16);
-            const uint32_t cw[4] = {qs.x, qs.y, qs.z, qs.w}, hw[4] = {qh.x, qh.y, qh.z, qh.w};
+            for (int part = 0; part < 2; ++part)
 #pragma unroll
-            for (int w = 0; w < 4; ++w)
+                for (int q4 = 0; q4 < 2; ++q4) {          // sixteen codes a piece: elements l = 16 q4 .. + 15 of sub-block 2 g + part
+                    const uint4 q = *reinterpret_cast<const uint4 *>(stage + (1 + 4 * g + 2 * part + q4) * 2048 + col * 16);
+                    const uint32_t cw[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-                for (int part = 0; part < 2; ++part) {
-                    uint32_t code = (cw[w] >> (4 * part)) & 0x0F0F0F0Fu;
-                    if (FMT == SPL_GGUF_Q5K) code |= ((hw[w] >> (2 * g + part)) & 0x01010101u) << 4;
-                    const float v[4] = {fmaf(spl_byte_to_float<0>(code), s[part], m[part]), fmaf(spl_byte_to_float<1>(code), s[part], m[part]),
-                                        fmaf(spl_byte_to_float<2>(code), s[part], m[part]), fmaf(spl_byte_to_float<3>(code), s[part], m[part])};
-                    a[16 * part + 8 * q4 + 2 * w] = spl_pack_half2(v[0], v[1]);
-                    a[16 * part + 8 * q4 + 2 * w + 1] = spl_pack_half2(v[2], v[3]);
+                    for (int w = 0; w < 4; ++w) {
+                        const uint32_t code = cw[w];
+                        const float2 s2 = make_float2(s[part], s[part]), m2 = make_float2(m[part], m[part]);
+                        const float2 v01 = spl_fma2(spl_bytes_to_float2<0>(code, 0.0f), s2, m2), v23 = spl_fma2(spl_bytes_to_float2<2>(code, 0.0f), s2, m2);
+                        a[16 * part + 8 * q4 + 2 * w] = spl_pack_half2(v01.x, v01.y);
+                        a[16 * part + 8 * q4 + 2 * w + 1] = spl_pack_half2(v23.x, v23.y);
+                    }
                 }
+        } else {
+#pragma unroll
+            for (int q4 = 0; q4 < 2; ++q4) {              // sixteen bytes of codes: elements l = 16 q4 .. + 15 of both sub-blocks
+                const uint4 qs = *reinterpret_cast<const uint4 *>(stage + (1 + 2 * g + q4) * 2048 + col * 16);
+                const uint32_t cw[4] = {qs.x, qs.y, qs.z, qs.w};
+#pragma unroll
+                for (int w = 0; w < 4; ++w)
+#pragma unroll
+                    for (int part = 0; part < 2; ++part) {
+                        const uint32_t code = (cw[w] >> (4 * part)) & 0x0F0F0F0Fu;
+                        const float2 s2 = make_float2(s[part], s[part]), m2 = make_float2(m[part], m[part]);
+                        const float2 v01 = spl_fma2(spl_bytes_to_float2<0>(code, 0.0f), s2, m2), v23 = spl_fma2(spl_bytes_to_float2<2>(code, 0.0f), s2, m2);
+                        a[16 * part + 8 * q4 + 2 * w] = spl_pack_half2(v01.x, v01.y);
+                        a[16 * part + 8 * q4 + 2 * w + 1] = spl_pack_half2(v23.x, v23.y);
+                    }
+            }
         }
     }
 }
@@ -156,7 +196,7 @@ template <int RN, int FMT>
 __global__ void __launch_bounds__(SPL_GG_THREADS, 1)
 spl_gemm_gguf_tc_kernel(const unsigned char *__restrict__ blocks, const __nv_bfloat16 *__restrict__ act, float *out, int out_ld,
                         const float *residual, float *partials, int rows, int op_blocks, int supers_total, int supers_per_split, int *error_flag) {
-    constexpr int BST = 4, CST = SPL_GG_CSTAGES, AST = 8, ASUP = 2, PIECES = spl_gguf_pieces(FMT);
+    constexpr int BST = 4, CST = spl_gguf_cstages(RN, FMT), ASUP = 2, AST = 4 * ASUP, PIECES = spl_gguf_pieces(FMT);
     constexpr int BTILE = SPL_TC_SUPER * RN * 128, WSTAGE = PIECES * 2048;
     extern __shared__ unsigned char spl_gg_smem_raw[];
     unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(spl_gg_smem_raw) + 1023) & ~uintptr_t(1023));
