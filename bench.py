@@ -414,11 +414,12 @@ def main():
         wcount, _ = weights_per_step(g)
         head_weights = g.vocab * g.hidden
         gguf_bytes = (wcount - head_weights) * 176 / 256 + head_weights * 210 / 256
+        device_bytes = (wcount - head_weights) * 272 / 256 + head_weights * 288 / 256      # the library's layout: a byte a code for Q5_K and Q6_K
         n_full = g.layers // 4
         kv_bytes = gguf_context * n_full * 2 * g.kv_heads * (g.head_dim + 4)
         gguf = {"workload": f"one session at {gguf_context} tokens of context, {GGUF_BLOCK}-row verify blocks, every block tensor Q5_K, embedding and head Q6_K "
                             "(GGUF super-blocks), plain norms, unfused SiLU gate",
-                "ms_per_step": 1000.0 * seconds / args.steps, "tok_per_s": GGUF_BLOCK * args.steps / seconds, "weights_gb": gguf_bytes / 1e9, "kv_gb": kv_bytes / 1e9,
+                "ms_per_step": 1000.0 * seconds / args.steps, "tok_per_s": GGUF_BLOCK * args.steps / seconds, "weights_gb": gguf_bytes / 1e9, "weights_read_gb": device_bytes / 1e9, "kv_gb": kv_bytes / 1e9,
                 "hbm_gbs": (gguf_bytes + kv_bytes) / (seconds / args.steps) / 1e9,
                 "class_ms_per_step": {k: v["ms"] / 2 for k, v in gguf_shares.items()}}
     if rank == 0:
