@@ -1343,20 +1343,30 @@ __global__ void __launch_bounds__(256) spl_gemm_fixup_rows_kernel(const float *_
         const int row = int(item / groups), group = int(item % groups), n = group * 64 + 2 * lane;
         const bool inside = n < ld;
         float2 x = make_float2(0.0f, 0.0f);
+        uint32_t w2 = 0u;
         if (inside) {
+            // Everything is asked for before anything is added (the sums stay in split order): one trip to L2, not one a split.
             const float *src = partials + size_t(row) * ld + n;
-            x = __ldcg(reinterpret_cast<const float2 *>(src));
-            for (int sp = 1; sp < splits; ++sp) {
-                const float2 part = __ldcg(reinterpret_cast<const float2 *>(src + size_t(sp) * rows_padded * ld));
-                x.x += part.x; x.y += part.y;
+            float2 res = make_float2(0.0f, 0.0f);
+            if (residual) res = *reinterpret_cast<const float2 *>(residual + size_t(row) * ld + n);
+            if (emit_weight) w2 = *reinterpret_cast<const uint32_t *>(emit_weight + n);
+            for (int sp0 = 0; sp0 < splits; sp0 += 4) {
+                float2 part[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u)
+                    part[u] = sp0 + u < splits ? __ldcg(reinterpret_cast<const float2 *>(src + size_t(sp0 + u) * rows_padded * ld)) : make_float2(0.0f, 0.0f);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    if (sp0 + u == 0) x = part[u];
+                    else if (sp0 + u < splits) { x.x += part[u].x; x.y += part[u].y; }
+                }
             }
-            if (residual) { const float2 res = *reinterpret_cast<const float2 *>(residual + size_t(row) * ld + n); x.x += res.x; x.y += res.y; }
+            if (residual) { x.x += res.x; x.y += res.y; }
             *reinterpret_cast<float2 *>(out + size_t(row) * ld + n) = x;
         }
         if (emit_weight) {
             float v0 = 0.0f, v1 = 0.0f;
             if (inside) {
-                const uint32_t w2 = *reinterpret_cast<const uint32_t *>(emit_weight + n);
                 v0 = spl_bf16_to_float(spl_float_to_bf16(x.x * spl_bf16_to_float(uint16_t(w2 & 0xFFFFu))));
                 v1 = spl_bf16_to_float(spl_float_to_bf16(x.y * spl_bf16_to_float(uint16_t(w2 >> 16))));
                 *reinterpret_cast<__half2 *>(reinterpret_cast<__half *>(emit_out.values) + emit_out.at(row, n)) = __halves2half2(__float2half_rn(v0), __float2half_rn(v1));
