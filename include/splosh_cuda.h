@@ -220,7 +220,9 @@ spl_status spl_weights_synthesize_q4(spl_engine *engine, uint64_t seed);
  * share a device tensor (qkv, z, a, b; q, k, v; gate, up) must share a type. Once the head is GGUF the engine steps as
  * a GGUF-weighted model and wants every GEMM tensor and the embedding as GGUF: its GEMMs form weights as the
  * reference's tile kernels do (one fp32 operation, rounded to fp16, Sources/Shaders/gguf_formats.h:390-438), the
- * embedding gather decodes exactly (:463-501), norms are plain RMSNorms and the SiLU gate a kernel of its own. */
+ * embedding gather decodes exactly (:463-501), norms are plain RMSNorms and the SiLU gate a kernel of its own.
+ * Device memory: Q4_K byte for byte; Q5_K and Q6_K tensors are kept at one byte a code (272 and 288 bytes a
+ * super-block), so the GEMMs form a weight without extracting its bits anew every step. */
 spl_status spl_weights_set_gguf(spl_engine *engine, int32_t layer, int32_t kind, int32_t type, int32_t rows, int32_t inner, const uint8_t *blocks);
 /* A GGUF file orders the value heads of a gated-delta block differently from the engine (file head i = engine head
  * 3 (i % 16) + i / 16 for 48 value and 16 key heads, Sources/SploshModel/GgufNames.swift:73-84). Tensors that hold the heads
