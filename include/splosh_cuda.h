@@ -386,6 +386,53 @@ spl_status spl_pass_embed(spl_engine *engine, const uint32_t *device_tokens, int
 spl_status spl_pass_mlp_in(spl_engine *engine, const spl_tensor *gate, const spl_tensor *up, const float *device_in, int32_t rows, float *device_out, float *device_scratch);
 spl_status spl_pass_wait(spl_engine *engine);
 
+/* ---- The DFlash 2 block-diffusion drafter (Sources/SploshRuntime/DraftModel.swift) -----------------
+ * A draft pass proposes a whole block at once: [anchor, mask x (block - 1)] through a few non-causal layers that attend
+ * over the block and a sliding window of context made from the target's hidden states at its tap layers
+ * (spl_features_enable), then a selector traces one path through the top candidates of every position. Built from the
+ * primitives above plus the drafter's own kernels (Sources/Shaders/draft.metal: dynamic convolution, K/V ring store,
+ * windowed attention). Heads are 128 wide. The checkpoint's linear layers are quantised to MLX affine-4 on the way in
+ * (DraftModel.quantize, :635-727; `minmax_ranges` non-zero restores MLX's range rule, SPLOSH_DRAFT_QUANT=minmax there). */
+typedef struct spl_draft spl_draft;
+typedef struct spl_draft_config {
+    int32_t layers, heads, kv_heads;          /* 5, 32, 8 in the reference's checkpoint */
+    int32_t group_size;                       /* channels per dynamic-convolution group: 16 (hidden / 16 groups) */
+    int32_t rank;                             /* the selector's codebook width: 256 */
+    int32_t window, ring_capacity;            /* 2048; ring positions per slot: 2304 (>= window + max_block) */
+    int32_t block_size, max_block;            /* 8; 16 */
+    int32_t candidates;                       /* 16 */
+    int32_t mask_token;                       /* 248070 */
+    int32_t minmax_ranges;
+} spl_draft_config;
+typedef struct spl_draft_request { int32_t slot, anchor, start, block, isolate_prefix; } spl_draft_request;      /* DraftRequest (:29-42) */
+typedef struct spl_draft_context_entry { int32_t slot, position, engine_row; } spl_draft_context_entry;
+/* Needs the engine's feature taps enabled and max_slots * max_block <= max_rows. */
+spl_status spl_draft_create(spl_engine *engine, const spl_draft_config *config, spl_draft **out);
+void spl_draft_destroy(spl_draft *draft);
+/* One tensor of the checkpoint by its safetensors name (DraftModel.swift:172-203: "layers.N.self_attn.q_proj.weight",
+ * "fc.weight", "norm.weight", "candidate_selector.predecessor_codebook", ...), bf16 [rows][inner]. The draft copies. */
+spl_status spl_draft_set_tensor(spl_draft *draft, const char *name, const uint16_t *bf16, int32_t rows, int32_t inner);
+spl_status spl_draft_reset_slot(spl_draft *draft, int32_t slot);
+spl_status spl_draft_truncate(spl_draft *draft, int32_t slot, int32_t token_count);
+int32_t spl_draft_context_length(const spl_draft *draft, int32_t slot, int32_t start);
+/* DraftModel.pushContext: straight after an engine step, the step rows to fold into the context and their positions. */
+spl_status spl_draft_push_context(spl_draft *draft, const spl_draft_context_entry *entries, int32_t count);
+/* DraftModel.propose. Outputs request after request, a request's block - 1 drafted positions in order: tokens [drafted],
+ * candidates [drafted][candidates], probabilities [drafted][candidates] (temperature > 0; may be null otherwise).
+ * `random_state` is the selector's SplitMix64 state, advanced by every draw. */
+spl_status spl_draft_propose(spl_draft *draft, const spl_draft_request *requests, int32_t count, float temperature, int32_t vocab_limit,
+                             uint64_t *random_state, int32_t *tokens, int32_t *candidates, float *probabilities);
+/* Host arithmetic, no device: DraftModel.quantize on row-major bf16 [rows][inner] (inner a multiple of 64), and
+ * CandidateSelector.select (:479-531) for one request: ids and values [drafted][k] are the top candidates of every
+ * position, hidden_rows [drafted][hidden] the draft's final hidden states, codebooks bf16 [vocab][rank]. */
+spl_status spl_draft_quantize_q4(const uint16_t *bf16, int32_t rows, int32_t inner, int32_t fitted, uint32_t *packed, uint16_t *scales, uint16_t *biases);
+spl_status spl_draft_select(int32_t drafted, int32_t k, int32_t rank, int32_t hidden, int32_t anchor, const int32_t *ids, const float *values,
+                            const float *hidden_rows, const float *hidden_projection, const uint16_t *predecessor, const uint16_t *successor,
+                            float temperature, uint64_t *random_state, int32_t *tokens, float *probabilities);
+/* For tests: the last block pass's buffers. 0 logits [picked][vocab], 1 selected hidden rows [picked][hidden], 2 / 3 layer
+ * `index`'s K / V ring (fp16), 4 the block's residual stream after the last layer. */
+spl_status spl_draft_debug_read(spl_draft *draft, int32_t what, int32_t index, void *dst, uint64_t bytes);
+
 /* ---- A GEMM for callers that must not allocate ---------------------------------------------
  * No counterpart in the reference (Metal hands out buffers freely; nothing there is barred from
  * allocating). Some CUDA hosts are: one that gave the whole GPU to its own pool at start-up and has

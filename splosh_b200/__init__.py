@@ -7,5 +7,7 @@ host over it that mirrors the reference's Swift `Engine` interface
 from .engine import (Engine, EngineConfig, EngineRow, EngineError, Geometry, Host, StepStats, tiny_geometry, b27_geometry,
                      gemm_q4, gemm_gguf, greedy_accept, library_path, Sampler, Planner, PackSession)
 
-__all__ = ["Engine", "EngineConfig", "EngineRow", "EngineError", "Geometry", "Host", "StepStats", "tiny_geometry",
+from .draft import DraftModel, DraftConfig, DraftRequest, DraftProposal
+
+__all__ = ["DraftModel", "DraftConfig", "DraftRequest", "DraftProposal", "Engine", "EngineConfig", "EngineRow", "EngineError", "Geometry", "Host", "StepStats", "tiny_geometry",
            "b27_geometry", "gemm_q4", "gemm_gguf", "greedy_accept", "library_path", "Sampler", "Planner", "PackSession"]

@@ -1,0 +1,167 @@
+// spl_draft.cuh — the kernels of the DFlash 2 block-diffusion drafter that are its own (Sources/Shaders/draft.metal);
+// everything linear in a draft pass runs on the engine's q4 GEMM, its norms and its embedding gather
+// (Sources/SploshRuntime/DraftModel.swift:418-468).
+#pragma once
+#include "spl_common.cuh"
+
+#define SPL_DRAFT_HEAD_DIM 128
+
+// Full-width rotary embedding of element i of a 128-wide head at `position`: pairs (i, i + 64) (draft.metal:13-19).
+__device__ __forceinline__ float spl_draft_rope(float x, float paired, int i, uint32_t position, float theta) {
+    const int half = SPL_DRAFT_HEAD_DIM >> 1, slot = i < half ? i : i - half;
+    const float angle = float(position) * powf(theta, -(2.0f * float(slot)) / float(SPL_DRAFT_HEAD_DIM));
+    return x * cosf(angle) + (i < half ? -paired : paired) * sinf(angle);
+}
+
+// Grouped dynamic causal convolution (kernel size 2) over the rows of one block (draft.metal:21-57):
+//   out[t][c] = sum over o in {0, 1} of (base[which][o][c] + dynamic[t][which][o][c / group_size]) * in[t - o][c]
+// with in[t - o] zero before the block's first row (row_offset[t] is the row's index in its block); `accumulate` adds the
+// result into out (the residual). Grid (ceil(hidden / 256), rows), 256 threads.
+__global__ void __launch_bounds__(256)
+spl_draft_conv_kernel(const float *__restrict__ in, const float *__restrict__ dynamic, const uint16_t *__restrict__ base, float *out,
+                      int hidden, int group_size, int groups, int which, int accumulate, const uint32_t *__restrict__ row_offset) {
+    spl_grid_begin();
+    const int c = blockIdx.x * 256 + threadIdx.x, t = blockIdx.y;
+    if (c >= hidden) return;
+    const int group = c / group_size;
+    const uint32_t in_block = row_offset[t];
+    float acc = 0.0f;
+#pragma unroll
+    for (int o = 0; o < 2; ++o) {
+        if (in_block < uint32_t(o)) continue;
+        const int tap = which * 2 + o;
+        const float kernel = spl_bf16_to_float(base[size_t(tap) * hidden + c]) + dynamic[size_t(t) * (4 * groups) + tap * groups + group];
+        acc += kernel * in[size_t(t - o) * hidden + c];
+    }
+    const size_t index = size_t(t) * hidden + c;
+    out[index] = accumulate ? out[index] + acc : acc;
+}
+
+// Draft K and V into the per-slot context ring (draft.metal:59-100): K is RMSNorm (plain weight) then rotary, V verbatim;
+// ring [slot][position % capacity][kv head][128] fp16. Grid (kv_heads, rows), 32 threads.
+__global__ void __launch_bounds__(32)
+spl_draft_kv_store_kernel(const float *__restrict__ kproj, const float *__restrict__ vproj, const uint16_t *__restrict__ norm_weight,
+                          const uint32_t *__restrict__ row_slot, const uint32_t *__restrict__ row_pos, __half *kring, __half *vring,
+                          int kv_heads, int capacity, float eps, float theta) {
+    spl_grid_begin();
+    constexpr int D = SPL_DRAFT_HEAD_DIM;
+    const int head = blockIdx.x, row = blockIdx.y, lane = threadIdx.x;
+    const size_t base = (size_t(row) * kv_heads + head) * D;
+    float partial = 0.0f;
+    for (int i = lane; i < D; i += 32) { const float x = kproj[base + i]; partial += x * x; }
+    const float inv = 1.0f / sqrtf(spl_warp_sum(partial) / float(D) + eps);
+    const uint32_t position = row_pos[row];
+    const size_t dst = ((size_t(row_slot[row]) * capacity + position % uint32_t(capacity)) * kv_heads + head) * D;
+    for (int i = lane; i < D; i += 32) {
+        const int pi = i < D / 2 ? i + D / 2 : i - D / 2;
+        const float x = kproj[base + i] * inv * spl_bf16_to_float(norm_weight[i]);
+        const float paired = kproj[base + pi] * inv * spl_bf16_to_float(norm_weight[pi]);
+        kring[dst + i] = __float2half_rn(spl_draft_rope(x, paired, i, position, theta));
+        vring[dst + i] = __float2half_rn(vproj[base + i]);
+    }
+}
+
+// Draft attention, non-causal within a sliding window (draft.metal:102-192): query row r sees every ring position in
+// [row_lo[r], row_hi[r]) closer than `window`: the accumulated context plus the rows of its own block. The reference runs
+// a 128-thread group per (head, row), thread j owning channel j, and walks the visible positions in chunks of 128 with a
+// running maximum; this kernel is that walk (same chunking, same order of the sums) with the query heads of one kv head
+// side by side in one block, so a chunk's keys and values are read once for all of them. Queries get their RMSNorm and
+// rotary embedding here. G = heads / kv_heads (at most 8). Grid (kv_heads, rows), 128 threads.
+template <int G>
+__global__ void __launch_bounds__(128)
+spl_draft_attention_kernel(const float *__restrict__ qproj, const uint16_t *__restrict__ norm_weight, const uint32_t *__restrict__ row_slot,
+                           const uint32_t *__restrict__ row_pos, const uint32_t *__restrict__ row_lo, const uint32_t *__restrict__ row_hi,
+                           const __half *__restrict__ kring, const __half *__restrict__ vring, float *out, int heads, int kv_heads,
+                           int capacity, int window, float scale, float eps, float theta) {
+    constexpr int D = SPL_DRAFT_HEAD_DIM;
+    __shared__ float query[G][D];
+    __shared__ float scores[G][D];
+    spl_grid_begin();
+    const int kv_head = blockIdx.x, row = blockIdx.y, j = threadIdx.x;
+    const uint32_t position = row_pos[row];
+    const int pj = j < D / 2 ? j + D / 2 : j - D / 2;
+#pragma unroll
+    for (int g = 0; g < G; ++g) scores[g][j] = qproj[(size_t(row) * heads + kv_head * G + g) * D + j];
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+        float ss = 0.0f;
+        for (int i = 0; i < D; ++i) ss += scores[g][i] * scores[g][i];
+        const float inv = 1.0f / sqrtf(ss / float(D) + eps);
+        query[g][j] = spl_draft_rope(scores[g][j] * inv * spl_bf16_to_float(norm_weight[j]), scores[g][pj] * inv * spl_bf16_to_float(norm_weight[pj]), j, position, theta);
+    }
+    __syncthreads();
+
+    const uint32_t first_visible = position + 1u > uint32_t(window) ? position + 1u - uint32_t(window) : 0u;
+    const uint32_t lo = max(row_lo[row], first_visible), hi = row_hi[row];
+    const uint32_t chunks = hi > lo ? (hi - lo + D - 1) / D : 0u;
+    const size_t ring_base = size_t(row_slot[row]) * capacity;
+    float run_max[G], run_sum[G], acc[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) { run_max[g] = -INFINITY; run_sum[g] = 0.0f; acc[g] = 0.0f; }
+    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+        const uint32_t first = lo + chunk * D;
+        float score[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) score[g] = -INFINITY;
+        if (first + j < hi) {
+            const __half *k = kring + ((ring_base + (first + j) % uint32_t(capacity)) * kv_heads + kv_head) * D;
+            float d[G];
+#pragma unroll
+            for (int g = 0; g < G; ++g) d[g] = 0.0f;
+            for (int i = 0; i < D; i += 8) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(k + i);
+                const __half2 *h2 = reinterpret_cast<const __half2 *>(&raw);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const float2 kk = __half22float2(h2[u]);
+#pragma unroll
+                    for (int g = 0; g < G; ++g) { d[g] += query[g][i + 2 * u] * kk.x; d[g] += query[g][i + 2 * u + 1] * kk.y; }
+                }
+            }
+#pragma unroll
+            for (int g = 0; g < G; ++g) score[g] = d[g] * scale;
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) scores[g][j] = score[g];
+        __syncthreads();
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            float chunk_max = -INFINITY;
+            for (int t = 0; t < D; ++t) chunk_max = fmaxf(chunk_max, scores[g][t]);
+            const float new_max = fmaxf(run_max[g], chunk_max), rescale = expf(run_max[g] - new_max);
+            acc[g] *= rescale; run_sum[g] *= rescale; run_max[g] = new_max;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int g = 0; g < G; ++g) scores[g][j] = expf(score[g] - run_max[g]);
+        __syncthreads();
+        const uint32_t count = min(uint32_t(D), hi - first);
+        for (uint32_t t = 0; t < count; ++t) {
+            const float v = __half2float(vring[((ring_base + (first + t) % uint32_t(capacity)) * kv_heads + kv_head) * D + j]);
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+                const float prob = scores[g][t];
+                if (prob > 0.0f) { run_sum[g] += prob; acc[g] += prob * v; }
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) out[(size_t(row) * heads + kv_head * G + g) * D + j] = acc[g] / run_sum[g];
+}
+
+// selected[p][:] = rows[gather[p]][:] (sp_gather_rows). Grid (ceil(hidden / 256), picked), 256 threads.
+__global__ void __launch_bounds__(256)
+spl_draft_gather_kernel(const float *__restrict__ rows, const uint32_t *__restrict__ gather, float *selected, int hidden) {
+    spl_grid_begin();
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c < hidden) selected[size_t(blockIdx.y) * hidden + c] = rows[size_t(gather[blockIdx.y]) * hidden + c];
+}
+
+// features[i][:] = engine feature rows[engine_row[i]][:] (the context pass's memcpy of Engine.featureRow, DraftModel.swift:337-339).
+__global__ void __launch_bounds__(256)
+spl_draft_take_features_kernel(const float *__restrict__ features, const uint32_t *__restrict__ engine_row, float *out, int width) {
+    spl_grid_begin();
+    for (int c = blockIdx.x * 256 + threadIdx.x; c < width; c += gridDim.x * 256) out[size_t(blockIdx.y) * width + c] = features[size_t(engine_row[blockIdx.y]) * width + c];
+}

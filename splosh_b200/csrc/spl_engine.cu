@@ -1683,6 +1683,9 @@ static void *spl_static_address[64] = {};
 // earlier call left there is ever multiplied. Grid (rows), 256 threads.
 __global__ void __launch_bounds__(256)
 spl_operand_kernel(const float *__restrict__ input, SplOperand out, int inner) {
+    // A pass queues this kernel behind the one that wrote `input`, and behind the GEMM that still reads the operand this
+    // one overwrites: it may not run ahead of either.
+    spl_grid_begin();
     const int row = blockIdx.x;
     for (int base = 0; base < inner; base += 1024) {
         const int i = base + threadIdx.x * 4;
@@ -2015,3 +2018,5 @@ spl_status spl_pass_wait(spl_engine *e) {
 }
 
 }  // extern "C"
+
+#include "spl_draft_impl.cuh"

@@ -240,6 +240,17 @@ def lib():
             "spl_debug_profile_read": (i32, [vp, i32, C.POINTER(C.c_double), C.POINTER(C.c_int64), C.POINTER(C.c_double)]),
             "spl_op_gemm_q4": (i32, [i32, vp, vp, vp, i32, i32, vp, i32, vp, vp]),
             "spl_gemm_q4_static": (i32, [vp, i32, i32, vp, i32, vp, vp, vp]),
+            "spl_draft_create": (i32, [vp, vp, vp]),
+            "spl_draft_destroy": (None, [vp]),
+            "spl_draft_set_tensor": (i32, [vp, C.c_char_p, vp, i32, i32]),
+            "spl_draft_reset_slot": (i32, [vp, i32]),
+            "spl_draft_truncate": (i32, [vp, i32, i32]),
+            "spl_draft_context_length": (i32, [vp, i32, i32]),
+            "spl_draft_push_context": (i32, [vp, vp, i32]),
+            "spl_draft_propose": (i32, [vp, vp, i32, C.c_float, i32, vp, vp, vp, vp]),
+            "spl_draft_quantize_q4": (i32, [vp, i32, i32, i32, vp, vp, vp]),
+            "spl_draft_select": (i32, [i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, C.c_float, vp, vp, vp]),
+            "spl_draft_debug_read": (i32, [vp, i32, i32, vp, C.c_uint64]),
         }
         for name, (res, args) in sig.items():
             fn = getattr(L, name)
