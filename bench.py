@@ -200,6 +200,7 @@ def main():
     ap.add_argument("--layers", type=int, default=64, help="blocks of the 27B shape (64 is the benchmark; fewer for ncu captures)")
     ap.add_argument("--context-scale", type=float, default=1.0, help="scales the session contexts (1.0 is the benchmark)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-draft", action="store_true", help="leave out the drafter's measurement")
     ap.add_argument("--no-prefill", action="store_true", help="leave out the prefill, rider, strong-scaling and GGUF measurements that follow the timed region")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0")); world = int(os.environ.get("WORLD_SIZE", "1")); local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -383,6 +384,68 @@ def main():
             dist.all_reduce(slowest, op=dist.ReduceOp.MAX)
         strong = {"workload": f"the 8 sessions split over {world} GPU(s), {len(share)} per GPU, 8-row verify blocks", "ms_per_step": 1000.0 * float(slowest[0]) / args.steps,
                   "tok_per_s": rows_per_step * args.steps / float(slowest[0])}
+    draft = None
+    if extras and world == 1 and not args.no_draft:
+        # The DFlash 2 drafter beside the target (DraftModel.swift): 5 layers, 32 query and 8 kv heads of 128, the target's
+        # width, its linear layers quantised to MLX affine-4 (MLX's range rule here: seconds instead of a minute of host
+        # time for the fitted ranges), random weights of the checkpoint's shapes (one array a shape, used by every layer).
+        # Context: the feature rows of one 64-row step pushed at consecutive positions until every slot's window of 2,048
+        # is full; then a draft pass of one block a session.
+        taps = [l for l in (5, 19, 33, 47, 61) if l < g.layers - 1] or [0]
+        engine.enable_features(taps)
+        dconfig = S.DraftConfig(mask_token=min(248070, g.vocab - 1), minmax_ranges=True)
+        dm = S.DraftModel(engine, dconfig)
+        rng = np.random.default_rng(WEIGHT_SEED & 0xFFFFFFFF)
+
+        def bf16_of(shape, deviation, mean=0.0):
+            x = rng.standard_normal(shape, dtype=np.float32) * np.float32(deviation) + np.float32(mean)
+            b = x.view(np.uint32)
+            return ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+
+        H, I, A, KV, GR = g.hidden, g.inter, dconfig.heads * 128, dconfig.kv_heads * 128, g.hidden // dconfig.group_size
+        per_layer = {"input_layernorm.weight": bf16_of(H, 0.02, 1.0), "post_attention_layernorm.weight": bf16_of(H, 0.02, 1.0),
+                     "self_attn.q_norm.weight": bf16_of(128, 0.02, 1.0), "self_attn.k_norm.weight": bf16_of(128, 0.02, 1.0),
+                     "attention_conv.base_kernel": bf16_of((4, H), 0.2, 0.5), "mlp_conv.base_kernel": bf16_of((4, H), 0.2, 0.5),
+                     "self_attn.q_proj.weight": bf16_of((A, H), 0.02), "self_attn.k_proj.weight": bf16_of((KV, H), 0.02),
+                     "self_attn.o_proj.weight": bf16_of((H, A), 0.02), "mlp.gate_proj.weight": bf16_of((I, H), 0.02),
+                     "mlp.down_proj.weight": bf16_of((H, I), 0.02), "attention_conv.kernel_projection.weight": bf16_of((4 * GR, H), 0.01)}
+        per_layer["self_attn.v_proj.weight"] = per_layer["self_attn.k_proj.weight"]
+        per_layer["mlp.up_proj.weight"] = per_layer["mlp.gate_proj.weight"]
+        per_layer["mlp_conv.kernel_projection.weight"] = per_layer["attention_conv.kernel_projection.weight"]
+        for layer in range(dconfig.layers):
+            for name, bits in per_layer.items():
+                dm.set_tensor(f"layers.{layer}.{name}", bits)
+        dm.set_tensor("fc.weight", bf16_of((H, H * len(taps)), 0.01))
+        dm.set_tensor("hidden_norm.weight", per_layer["input_layernorm.weight"])
+        dm.set_tensor("norm.weight", per_layer["input_layernorm.weight"])
+        dm.set_tensor("candidate_selector.hidden_projection.weight", bf16_of((dconfig.rank, H), 0.05))
+        codebook = bf16_of((g.vocab, dconfig.rank), 0.5)
+        dm.set_tensor("candidate_selector.predecessor_codebook", codebook)
+        dm.set_tensor("candidate_selector.successor_codebook", codebook)
+        del per_layer, codebook
+        one_step(step_index, False); step_index += 1
+        pushes = dconfig.window // BLOCK
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for n in range(pushes):
+            dm.push_context([(s_, n * BLOCK + i, s_ * BLOCK + i) for s_ in range(SESSIONS) for i in range(BLOCK)])
+        push_ms = 1000.0 * (time.perf_counter() - t0) / pushes
+        at = pushes * BLOCK
+        passes = {}
+        for block, isolate in ((8, False), (16, True)):
+            requests = [S.DraftRequest(s_, int(splitmix_at(TOKEN_SEED ^ 0xD4AF, s_) % 200000), at, block, isolate) for s_ in range(SESSIONS)]
+            for _ in range(2):
+                dm.propose(requests, vocab_limit=min(248077, g.vocab))
+            t0 = time.perf_counter()
+            for _ in range(args.steps):
+                dm.propose(requests, vocab_limit=min(248077, g.vocab))
+            passes[block] = 1000.0 * (time.perf_counter() - t0) / args.steps
+        draft = {"workload": f"DFlash 2 drafter ({dconfig.layers} layers, {dconfig.heads}/{dconfig.kv_heads} heads of 128, MLX 4-bit g64, random weights) beside the target: "
+                             f"{SESSIONS} sessions, every context window full ({dconfig.window} positions), one block a session per pass; wall time through "
+                             "spl_draft_propose (block pass, top-16 on the device, selector on the host)",
+                 "ms_per_pass_8_row_blocks": passes[8], "ms_per_pass_16_row_blocks": passes[16], "context_push_ms_per_64_rows": push_ms, "taps": taps}
+        dm.close()
+        engine.enable_features(enabled=False)
     gguf = None
     if extras and world == 1 and g.hidden % 256 == 0:
         # Configuration 4: Q5_K_M-style weights (Q5_K blocks, Q6_K embedding and head; pseudo-random blocks made on the device),
@@ -459,6 +522,8 @@ def main():
             line["strong"] = strong
         if gguf is not None:
             line["gguf"] = gguf
+        if draft:
+            line["draft"] = draft
         if not args.no_cpu_baseline and world == 1:
             value, cores, sample = cpu_baseline()
             line["cpu_baseline"] = {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample}

@@ -76,6 +76,7 @@ spl_draft_attention_kernel(const float *__restrict__ qproj, const uint16_t *__re
     constexpr int D = SPL_DRAFT_HEAD_DIM;
     __shared__ float query[G][D];
     __shared__ float scores[G][D];
+    __shared__ float warp_max[G][4];
     spl_grid_begin();
     const int kv_head = blockIdx.x, row = blockIdx.y, j = threadIdx.x;
     const uint32_t position = row_pos[row];
@@ -122,28 +123,28 @@ spl_draft_attention_kernel(const float *__restrict__ qproj, const uint16_t *__re
 #pragma unroll
             for (int g = 0; g < G; ++g) score[g] = d[g] * scale;
         }
-#pragma unroll
-        for (int g = 0; g < G; ++g) scores[g][j] = score[g];
-        __syncthreads();
+        // The chunk's maximum: the four warps' maxima meet in shared memory (a maximum does not depend on the order).
 #pragma unroll
         for (int g = 0; g < G; ++g) {
-            float chunk_max = -INFINITY;
-            for (int t = 0; t < D; ++t) chunk_max = fmaxf(chunk_max, scores[g][t]);
-            const float new_max = fmaxf(run_max[g], chunk_max), rescale = expf(run_max[g] - new_max);
-            acc[g] *= rescale; run_sum[g] *= rescale; run_max[g] = new_max;
+            const float m = spl_warp_max(score[g]);
+            if ((j & 31) == 0) warp_max[g][j >> 5] = m;
         }
         __syncthreads();
 #pragma unroll
-        for (int g = 0; g < G; ++g) scores[g][j] = expf(score[g] - run_max[g]);
+        for (int g = 0; g < G; ++g) {
+            const float chunk_max = fmaxf(fmaxf(warp_max[g][0], warp_max[g][1]), fmaxf(warp_max[g][2], warp_max[g][3]));
+            const float new_max = fmaxf(run_max[g], chunk_max), rescale = expf(run_max[g] - new_max);
+            acc[g] *= rescale; run_sum[g] *= rescale; run_max[g] = new_max;
+            scores[g][j] = expf(score[g] - new_max);
+        }
         __syncthreads();
+        // Positions in order, as the reference adds them; a position past the row's range has probability zero and is not read.
         const uint32_t count = min(uint32_t(D), hi - first);
+#pragma unroll 8
         for (uint32_t t = 0; t < count; ++t) {
             const float v = __half2float(vring[((ring_base + (first + t) % uint32_t(capacity)) * kv_heads + kv_head) * D + j]);
 #pragma unroll
-            for (int g = 0; g < G; ++g) {
-                const float prob = scores[g][t];
-                if (prob > 0.0f) { run_sum[g] += prob; acc[g] += prob * v; }
-            }
+            for (int g = 0; g < G; ++g) { const float prob = scores[g][t]; run_sum[g] += prob; acc[g] += prob * v; }
         }
         __syncthreads();
     }
@@ -164,4 +165,91 @@ __global__ void __launch_bounds__(256)
 spl_draft_take_features_kernel(const float *__restrict__ features, const uint32_t *__restrict__ engine_row, float *out, int width) {
     spl_grid_begin();
     for (int c = blockIdx.x * 256 + threadIdx.x; c < width; c += gridDim.x * 256) out[size_t(blockIdx.y) * width + c] = features[size_t(engine_row[blockIdx.y]) * width + c];
+}
+
+// The selector's projection of the drafted positions' hidden states (CandidateSelector.select's matrix-vector product,
+// DraftModel.swift:499-502): projected[p][r] = sum over h of projection[r][h] * selected[p][h]. Grid (picked, ceil(rank / 32)),
+// 256 threads: a block takes 32 ranks of one position, a warp four of them.
+__global__ void __launch_bounds__(256)
+spl_draft_project_kernel(const float *__restrict__ projection, const float *__restrict__ selected, float *projected, int rank, int hidden) {
+    spl_grid_begin();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const float *x = selected + size_t(blockIdx.x) * hidden;
+    for (int r = blockIdx.y * 32 + warp; r < min(rank, int(blockIdx.y) * 32 + 32); r += 8) {
+        const float *m = projection + size_t(r) * hidden;
+        float sum = 0.0f;
+        for (int h = lane; h < hidden; h += 32) sum += m[h] * x[h];
+        sum = spl_warp_sum(sum);
+        if (lane == 0) projected[size_t(blockIdx.x) * rank + r] = sum;
+    }
+}
+
+// The best (value descending, index ascending) of a block of 256 threads' candidates; every thread gets it. index 0x7fffffff: none.
+__device__ __forceinline__ void spl_draft_block_best(float &bv, int &bi, float *best_v, int *best_i) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    __syncthreads();                 // the last round's readers are done with the arrays
+    if ((threadIdx.x & 31) == 0) { best_v[threadIdx.x >> 5] = bv; best_i[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    bv = best_v[0]; bi = best_i[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) {
+        const float ov = best_v[w]; const int oi = best_i[w];
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+}
+
+// The k largest of [0, limit) per logit row, descending, the lower index first among equal values (TopK.select,
+// Sampler.swift:19-52), in two kernels so that a row is many blocks' work: the k best of each of `segments` stretches of
+// the row (k rounds of a block-wide selection, as the one-kernel form does over the whole row), then the k best of those.
+// Grid (rows, segments), 256 threads; candidates [rows][segments][k], index -1 where a stretch ran out (NaN and -inf never qualify).
+__global__ void __launch_bounds__(256)
+spl_draft_topk_segment_kernel(const float *__restrict__ logits, int ld, int limit, int k, int segments, float *cand_v, int32_t *cand_i) {
+    __shared__ float best_v[8];
+    __shared__ int best_i[8];
+    spl_grid_begin();
+    const int length = (limit + segments - 1) / segments, begin = blockIdx.y * length, end = min(limit, begin + length);
+    const float *x = logits + size_t(blockIdx.x) * ld;
+    float last_v = INFINITY; int last_i = -1;
+    for (int round = 0; round < k; ++round) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int i = begin + threadIdx.x; i < end; i += 256) {
+            const float v = x[i];
+            const bool after = v < last_v || (v == last_v && i > last_i);
+            if (after && v > -INFINITY && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
+        }
+        spl_draft_block_best(bv, bi, best_v, best_i);
+        const bool none = bi == 0x7fffffff;
+        if (threadIdx.x == 0) {
+            const size_t at = (size_t(blockIdx.x) * segments + blockIdx.y) * k + round;
+            cand_v[at] = none ? -INFINITY : bv; cand_i[at] = none ? -1 : bi;
+        }
+        if (none) { last_v = -INFINITY; last_i = 0x7ffffffe; } else { last_v = bv; last_i = bi; }
+    }
+}
+// Grid (rows), 256 threads; ids and values [rows][k]: fewer than k selectable values leave the reference's untouched slots, id 0 at -inf.
+__global__ void __launch_bounds__(256)
+spl_draft_topk_merge_kernel(const float *__restrict__ cand_v, const int32_t *__restrict__ cand_i, int count, int k, int32_t *ids, float *values) {
+    __shared__ float best_v[8];
+    __shared__ int best_i[8];
+    spl_grid_begin();
+    const float *cv = cand_v + size_t(blockIdx.x) * count;
+    const int32_t *ci = cand_i + size_t(blockIdx.x) * count;
+    float last_v = INFINITY; int last_i = -1;
+    for (int round = 0; round < k; ++round) {
+        float bv = -INFINITY; int bi = 0x7fffffff;
+        for (int c = threadIdx.x; c < count; c += 256) {
+            const float v = cv[c]; const int i = ci[c];
+            const bool after = v < last_v || (v == last_v && i > last_i);
+            if (i >= 0 && after && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
+        }
+        spl_draft_block_best(bv, bi, best_v, best_i);
+        const bool none = bi == 0x7fffffff;
+        if (threadIdx.x == 0) { ids[size_t(blockIdx.x) * k + round] = none ? 0 : bi; values[size_t(blockIdx.x) * k + round] = none ? -INFINITY : bv; }
+        if (none) { last_v = -INFINITY; last_i = 0x7ffffffe; } else { last_v = bv; last_i = bi; }
+    }
 }

@@ -9,6 +9,8 @@
 #include "spl_draft.cuh"
 #include <thread>
 
+#define SPL_DRAFT_TOPK_SEGMENTS 16
+
 // ---- host arithmetic shared with the tests (no device needed) ---------------------------------
 static inline float draft_bf16_float(uint16_t bits) { uint32_t u = uint32_t(bits) << 16; float f; memcpy(&f, &u, 4); return f; }
 static inline uint16_t draft_float_bf16(float v) {            // DraftModel.bf16 (:721-724)
@@ -103,6 +105,8 @@ struct spl_draft {
     float *dh = nullptr, *x = nullptr, *xc = nullptr, *t = nullptr, *dyn = nullptr, *qp = nullptr, *kp = nullptr, *vp = nullptr, *ao = nullptr,
           *gate = nullptr, *up = nullptr, *dn = nullptr, *selected = nullptr, *logits = nullptr, *top_values = nullptr;
     int32_t *top_ids = nullptr;
+    float *cand_values = nullptr; int32_t *cand_ids = nullptr;     // the candidates of the row's stretches [picked][segments][candidates]
+    float *projection_dev = nullptr, *projected = nullptr;      // the selector's matrix [rank][hidden] and its products with the drafted rows [picked][rank]
     int last_picked = 0;
     std::string error;
 };
@@ -171,21 +175,14 @@ spl_status spl_draft_quantize_q4(const uint16_t *bf16, int32_t rows, int32_t inn
     return SPL_OK;
 }
 
-spl_status spl_draft_select(int32_t drafted, int32_t k, int32_t rank, int32_t hidden, int32_t anchor, const int32_t *ids, const float *values,
-                            const float *hidden_rows, const float *hidden_projection, const uint16_t *predecessor, const uint16_t *successor,
-                            float temperature, uint64_t *random_state, int32_t *tokens, float *probabilities) {
-    if (drafted < 0 || k < 1 || rank < 1 || hidden < 1 || !ids || !values || !hidden_rows || !hidden_projection || !predecessor || !successor || !tokens ||
-        (temperature > 0.0f && (!random_state || !probabilities))) return SPL_ERR_INVALID_ARGUMENT;
-    std::vector<float> projected(rank), gated(rank), scores(k), q(k);
+// The path through the candidates given every position's projected hidden state [drafted][rank] (DraftModel.swift:503-529).
+static spl_status draft_select_projected(int drafted, int k, int rank, int anchor, const int32_t *ids, const float *values, const float *projected_rows,
+                                         const uint16_t *predecessor, const uint16_t *successor, float temperature, uint64_t *random_state, int32_t *tokens,
+                                         float *probabilities) {
+    std::vector<float> gated(rank), scores(k), q(k);
     int predecessor_token = anchor;
     for (int position = 0; position < drafted; ++position) {
-        const float *hs = hidden_rows + size_t(position) * hidden;
-        for (int r = 0; r < rank; ++r) {
-            const float *m = hidden_projection + size_t(r) * hidden;
-            float sum = 0.0f;
-            for (int h = 0; h < hidden; ++h) sum += m[h] * hs[h];
-            projected[r] = sum;
-        }
+        const float *projected = projected_rows + size_t(position) * rank;
         const uint16_t *before = predecessor + size_t(predecessor_token) * rank;
         for (int r = 0; r < rank; ++r) gated[r] = draft_bf16_float(before[r]) * projected[r];
         for (int c = 0; c < k; ++c) {
@@ -217,6 +214,22 @@ spl_status spl_draft_select(int32_t drafted, int32_t k, int32_t rank, int32_t hi
     return SPL_OK;
 }
 
+spl_status spl_draft_select(int32_t drafted, int32_t k, int32_t rank, int32_t hidden, int32_t anchor, const int32_t *ids, const float *values,
+                            const float *hidden_rows, const float *hidden_projection, const uint16_t *predecessor, const uint16_t *successor,
+                            float temperature, uint64_t *random_state, int32_t *tokens, float *probabilities) {
+    if (drafted < 0 || k < 1 || rank < 1 || hidden < 1 || !ids || !values || !hidden_rows || !hidden_projection || !predecessor || !successor || !tokens ||
+        (temperature > 0.0f && (!random_state || !probabilities))) return SPL_ERR_INVALID_ARGUMENT;
+    std::vector<float> projected(size_t(std::max(drafted, 1)) * rank);
+    for (int position = 0; position < drafted; ++position)
+        for (int r = 0; r < rank; ++r) {
+            const float *m = hidden_projection + size_t(r) * hidden, *hs = hidden_rows + size_t(position) * hidden;
+            float sum = 0.0f;
+            for (int h = 0; h < hidden; ++h) sum += m[h] * hs[h];
+            projected[size_t(position) * rank + r] = sum;
+        }
+    return draft_select_projected(drafted, k, rank, anchor, ids, values, projected.data(), predecessor, successor, temperature, random_state, tokens, probabilities);
+}
+
 void spl_draft_destroy(spl_draft *d) {
     if (!d) return;
     spl_engine *e = d->e;
@@ -230,7 +243,7 @@ void spl_draft_destroy(spl_draft *d) {
     for (spl_tensor *t : {d->fc, d->hidden_norm, d->final_norm}) spl_tensor_destroy(e, t);
     for (void *p : {(void *)d->c_features, (void *)d->c_hidden, (void *)d->c_normed, (void *)d->c_meta, (void *)d->wide_act, (void *)d->wide_sums, (void *)d->b_meta, (void *)d->dh,
                     (void *)d->x, (void *)d->xc, (void *)d->t, (void *)d->dyn, (void *)d->qp, (void *)d->kp, (void *)d->vp, (void *)d->ao, (void *)d->gate, (void *)d->up, (void *)d->dn,
-                    (void *)d->selected, (void *)d->logits, (void *)d->top_values, (void *)d->top_ids}) cudaFree(p);
+                    (void *)d->selected, (void *)d->logits, (void *)d->top_values, (void *)d->top_ids, (void *)d->projection_dev, (void *)d->projected, (void *)d->cand_values, (void *)d->cand_ids}) cudaFree(p);
     delete d;
 }
 
@@ -261,7 +274,9 @@ spl_status spl_draft_create(spl_engine *e, const spl_draft_config *config, spl_d
               draft_alloc(&d->b_meta, BR * 7) && draft_alloc(&d->dh, BR * H) && draft_alloc(&d->x, BR * H) && draft_alloc(&d->xc, BR * H) && draft_alloc(&d->t, BR * H) &&
               draft_alloc(&d->dyn, BR * 4 * d->groups) && draft_alloc(&d->qp, BR * d->attention) && draft_alloc(&d->kp, BR * d->kv) && draft_alloc(&d->vp, BR * d->kv) &&
               draft_alloc(&d->ao, BR * d->attention) && draft_alloc(&d->gate, BR * d->inter) && draft_alloc(&d->up, BR * d->inter) && draft_alloc(&d->dn, BR * H) &&
-              draft_alloc(&d->selected, BR * H) && draft_alloc(&d->logits, BR * size_t(d->vocab)) && draft_alloc(&d->top_values, BR * 64) && draft_alloc(&d->top_ids, BR * 64);
+              draft_alloc(&d->selected, BR * H) && draft_alloc(&d->logits, BR * size_t(d->vocab)) && draft_alloc(&d->top_values, BR * 64) && draft_alloc(&d->top_ids, BR * 64) &&
+              draft_alloc(&d->projection_dev, size_t(c.rank) * H) && draft_alloc(&d->projected, BR * c.rank) &&
+              draft_alloc(&d->cand_values, BR * SPL_DRAFT_TOPK_SEGMENTS * 64) && draft_alloc(&d->cand_ids, BR * SPL_DRAFT_TOPK_SEGMENTS * 64);
     for (DraftLayer &L : d->layers)
         ok = ok && draft_alloc(&L.k_ring, size_t(e->c.max_slots) * c.ring_capacity * d->kv) && draft_alloc(&L.v_ring, size_t(e->c.max_slots) * c.ring_capacity * d->kv) &&
              draft_alloc(&L.c_k, CR * d->kv) && draft_alloc(&L.c_v, CR * d->kv);
@@ -297,6 +312,7 @@ spl_status spl_draft_set_tensor(spl_draft *d, const char *name, const uint16_t *
         if (!shape(d->c.rank, H)) return wrong();
         d->hidden_projection.resize(size_t(rows) * inner);
         for (size_t i = 0; i < d->hidden_projection.size(); ++i) d->hidden_projection[i] = draft_bf16_float(bf16[i]);
+        SPL_CUDA(cudaMemcpy(d->projection_dev, d->hidden_projection.data(), d->hidden_projection.size() * 4, cudaMemcpyHostToDevice));
         return SPL_OK;
     }
     if (n == "candidate_selector.predecessor_codebook" || n == "candidate_selector.successor_codebook") {
@@ -487,21 +503,24 @@ spl_status spl_draft_propose(spl_draft *d, const spl_draft_request *requests, in
     s = spl_pass_gemm_head(e, d->selected, picked, d->logits);
     if (s != SPL_OK) return s;
     // The candidates of every drafted position: TopK.select over the first `vocab_limit` logits (Sampler.swift:19-52), on the device.
-    spl_topk_kernel<<<picked, 1024, 0, e->stream>>>(d->logits, d->vocab, vocab_limit, int(c.candidates), d->top_ids, d->top_values);
+    launch_step(spl_draft_project_kernel, dim3(picked, (c.rank + 31) / 32), dim3(256), 0, e->stream, (const float *)d->projection_dev, (const float *)d->selected, d->projected, int(c.rank), H);
+    launch_step(spl_draft_topk_segment_kernel, dim3(picked, SPL_DRAFT_TOPK_SEGMENTS), dim3(256), 0, e->stream, (const float *)d->logits, d->vocab, int(vocab_limit), int(c.candidates),
+                SPL_DRAFT_TOPK_SEGMENTS, d->cand_values, d->cand_ids);
+    launch_step(spl_draft_topk_merge_kernel, dim3(picked), dim3(256), 0, e->stream, (const float *)d->cand_values, (const int32_t *)d->cand_ids, SPL_DRAFT_TOPK_SEGMENTS * int(c.candidates),
+                int(c.candidates), d->top_ids, d->top_values);
     s = check_launch(e, "draft block");
     if (s == SPL_OK) s = spl_pass_wait(e);
     if (s != SPL_OK) return s;
     d->last_picked = picked;
     const int k = c.candidates;
-    std::vector<float> values(size_t(picked) * k), hidden_rows(size_t(picked) * H);
+    std::vector<float> values(size_t(picked) * k), projected(size_t(picked) * c.rank);
     SPL_CUDA(cudaMemcpy(candidates, d->top_ids, size_t(picked) * k * 4, cudaMemcpyDeviceToHost));
     SPL_CUDA(cudaMemcpy(values.data(), d->top_values, values.size() * 4, cudaMemcpyDeviceToHost));
-    SPL_CUDA(cudaMemcpy(hidden_rows.data(), d->selected, hidden_rows.size() * 4, cudaMemcpyDeviceToHost));
+    SPL_CUDA(cudaMemcpy(projected.data(), d->projected, projected.size() * 4, cudaMemcpyDeviceToHost));
     for (int i = 0; i < count; ++i) {
         const int first = first_picked[i], drafted = requests[i].block - 1;
-        s = spl_draft_select(drafted, k, c.rank, H, requests[i].anchor, candidates + size_t(first) * k, values.data() + size_t(first) * k, hidden_rows.data() + size_t(first) * H,
-                             d->hidden_projection.data(), d->predecessor.data(), d->successor.data(), temperature, random_state, tokens + first,
-                             probabilities ? probabilities + size_t(first) * k : nullptr);
+        s = draft_select_projected(drafted, k, c.rank, requests[i].anchor, candidates + size_t(first) * k, values.data() + size_t(first) * k, projected.data() + size_t(first) * c.rank,
+                                   d->predecessor.data(), d->successor.data(), temperature, random_state, tokens + first, probabilities ? probabilities + size_t(first) * k : nullptr);
         if (s != SPL_OK) return s;
     }
     return SPL_OK;
