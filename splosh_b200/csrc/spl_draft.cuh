@@ -66,12 +66,14 @@ spl_draft_kv_store_kernel(const float *__restrict__ kproj, const float *__restri
 // a 128-thread group per (head, row), thread j owning channel j, and walks the visible positions in chunks of 128 with a
 // running maximum; this kernel is that walk (same chunking, same order of the sums) with the query heads of one kv head
 // side by side in one block, so a chunk's keys and values are read once for all of them. Queries get their RMSNorm and
-// rotary embedding here. G = heads / kv_heads (at most 8). Grid (kv_heads, rows), 128 threads.
+// rotary embedding here. G = heads / kv_heads (at most 8). The chunks are dealt to gridDim.z spans that run side by side and
+// leave partial results for the merge kernel (the reference's sp_draft_attention_span, draft.metal:194-277: the walk of a
+// full window is eighteen chunks in sequence otherwise). Grid (kv_heads, rows, spans), 128 threads.
 template <int G>
 __global__ void __launch_bounds__(128)
 spl_draft_attention_kernel(const float *__restrict__ qproj, const uint16_t *__restrict__ norm_weight, const uint32_t *__restrict__ row_slot,
                            const uint32_t *__restrict__ row_pos, const uint32_t *__restrict__ row_lo, const uint32_t *__restrict__ row_hi,
-                           const __half *__restrict__ kring, const __half *__restrict__ vring, float *out, int heads, int kv_heads,
+                           const __half *__restrict__ kring, const __half *__restrict__ vring, float *partials, int heads, int kv_heads,
                            int capacity, int window, float scale, float eps, float theta) {
     constexpr int D = SPL_DRAFT_HEAD_DIM;
     __shared__ float query[G][D];
@@ -96,11 +98,12 @@ spl_draft_attention_kernel(const float *__restrict__ qproj, const uint16_t *__re
     const uint32_t first_visible = position + 1u > uint32_t(window) ? position + 1u - uint32_t(window) : 0u;
     const uint32_t lo = max(row_lo[row], first_visible), hi = row_hi[row];
     const uint32_t chunks = hi > lo ? (hi - lo + D - 1) / D : 0u;
+    const uint32_t per_span = (chunks + gridDim.z - 1) / gridDim.z, chunk_begin = blockIdx.z * per_span, chunk_end = min(chunks, chunk_begin + per_span);
     const size_t ring_base = size_t(row_slot[row]) * capacity;
     float run_max[G], run_sum[G], acc[G];
 #pragma unroll
     for (int g = 0; g < G; ++g) { run_max[g] = -INFINITY; run_sum[g] = 0.0f; acc[g] = 0.0f; }
-    for (uint32_t chunk = 0; chunk < chunks; ++chunk) {
+    for (uint32_t chunk = chunk_begin; chunk < chunk_end; ++chunk) {
         const uint32_t first = lo + chunk * D;
         float score[G];
 #pragma unroll
@@ -148,8 +151,32 @@ spl_draft_attention_kernel(const float *__restrict__ qproj, const uint16_t *__re
         }
         __syncthreads();
     }
+    // The span's share: [running maximum, running sum, 128 accumulated values] per (row, head, span) (draft.metal:194-199).
 #pragma unroll
-    for (int g = 0; g < G; ++g) out[(size_t(row) * heads + kv_head * G + g) * D + j] = acc[g] / run_sum[g];
+    for (int g = 0; g < G; ++g) {
+        float *p = partials + ((size_t(row) * heads + kv_head * G + g) * gridDim.z + blockIdx.z) * (D + 2);
+        if (j == 0) { p[0] = run_max[g]; p[1] = run_sum[g]; }
+        p[2 + j] = acc[g];
+    }
+}
+
+// The spans of a (row, head) put together (sp_draft_attention_merge, draft.metal:279-300). Grid (heads, rows), 128 threads.
+__global__ void __launch_bounds__(128)
+spl_draft_attention_merge_kernel(const float *__restrict__ partials, float *out, int heads, int spans) {
+    constexpr int D = SPL_DRAFT_HEAD_DIM;
+    spl_grid_begin();
+    const int head = blockIdx.x, row = blockIdx.y, j = threadIdx.x;
+    const float *p = partials + (size_t(row) * heads + head) * spans * (D + 2);
+    float top = -INFINITY;
+    for (int s = 0; s < spans; ++s) top = fmaxf(top, p[s * (D + 2)]);
+    float sum = 0.0f, acc = 0.0f;
+    for (int s = 0; s < spans; ++s) {
+        const float m = p[s * (D + 2)];
+        if (m == -INFINITY) continue;               // a span without a visible position
+        const float w = expf(m - top);
+        sum += p[s * (D + 2) + 1] * w; acc += p[s * (D + 2) + 2 + j] * w;
+    }
+    out[(size_t(row) * heads + head) * D + j] = acc / sum;
 }
 
 // selected[p][:] = rows[gather[p]][:] (sp_gather_rows). Grid (ceil(hidden / 256), picked), 256 threads.

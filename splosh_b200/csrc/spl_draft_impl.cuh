@@ -10,6 +10,7 @@
 #include <thread>
 
 #define SPL_DRAFT_TOPK_SEGMENTS 16
+#define SPL_DRAFT_ATTENTION_SPANS 8       // the reference walks eight; a span here is a block of four query heads
 
 // ---- host arithmetic shared with the tests (no device needed) ---------------------------------
 static inline float draft_bf16_float(uint16_t bits) { uint32_t u = uint32_t(bits) << 16; float f; memcpy(&f, &u, 4); return f; }
@@ -105,6 +106,7 @@ struct spl_draft {
     float *dh = nullptr, *x = nullptr, *xc = nullptr, *t = nullptr, *dyn = nullptr, *qp = nullptr, *kp = nullptr, *vp = nullptr, *ao = nullptr,
           *gate = nullptr, *up = nullptr, *dn = nullptr, *selected = nullptr, *logits = nullptr, *top_values = nullptr;
     int32_t *top_ids = nullptr;
+    float *attention_partials = nullptr;                          // [rows][heads][spans][2 + 128]
     float *cand_values = nullptr; int32_t *cand_ids = nullptr;     // the candidates of the row's stretches [picked][segments][candidates]
     float *projection_dev = nullptr, *projected = nullptr;      // the selector's matrix [rank][hidden] and its products with the drafted rows [picked][rank]
     int last_picked = 0;
@@ -162,9 +164,10 @@ static spl_status draft_gemm_wide(spl_draft *d, const SplQ4Dev &w, const float *
 template <int G>
 static void draft_attention_launch(spl_draft *d, const DraftLayer &L, int rows, const uint32_t *slots, const uint32_t *positions, const uint32_t *lo, const uint32_t *hi) {
     spl_engine *e = d->e;
-    launch_step(spl_draft_attention_kernel<G>, dim3(d->c.kv_heads, rows), dim3(128), 0, e->stream, (const float *)d->qp, (const uint16_t *)L.q_norm->vec, slots, positions, lo, hi,
-                (const __half *)L.k_ring, (const __half *)L.v_ring, d->ao, int(d->c.heads), int(d->c.kv_heads), int(d->c.ring_capacity), int(d->c.window),
-                1.0f / sqrtf(float(SPL_DRAFT_HEAD_DIM)), e->g.eps, e->g.rope_theta);
+    launch_step(spl_draft_attention_kernel<G>, dim3(d->c.kv_heads, rows, SPL_DRAFT_ATTENTION_SPANS), dim3(128), 0, e->stream, (const float *)d->qp, (const uint16_t *)L.q_norm->vec, slots,
+                positions, lo, hi, (const __half *)L.k_ring, (const __half *)L.v_ring, d->attention_partials, int(d->c.heads), int(d->c.kv_heads), int(d->c.ring_capacity),
+                int(d->c.window), 1.0f / sqrtf(float(SPL_DRAFT_HEAD_DIM)), e->g.eps, e->g.rope_theta);
+    launch_step(spl_draft_attention_merge_kernel, dim3(d->c.heads, rows), dim3(128), 0, e->stream, (const float *)d->attention_partials, d->ao, int(d->c.heads), SPL_DRAFT_ATTENTION_SPANS);
 }
 
 extern "C" {
@@ -243,7 +246,7 @@ void spl_draft_destroy(spl_draft *d) {
     for (spl_tensor *t : {d->fc, d->hidden_norm, d->final_norm}) spl_tensor_destroy(e, t);
     for (void *p : {(void *)d->c_features, (void *)d->c_hidden, (void *)d->c_normed, (void *)d->c_meta, (void *)d->wide_act, (void *)d->wide_sums, (void *)d->b_meta, (void *)d->dh,
                     (void *)d->x, (void *)d->xc, (void *)d->t, (void *)d->dyn, (void *)d->qp, (void *)d->kp, (void *)d->vp, (void *)d->ao, (void *)d->gate, (void *)d->up, (void *)d->dn,
-                    (void *)d->selected, (void *)d->logits, (void *)d->top_values, (void *)d->top_ids, (void *)d->projection_dev, (void *)d->projected, (void *)d->cand_values, (void *)d->cand_ids}) cudaFree(p);
+                    (void *)d->selected, (void *)d->logits, (void *)d->top_values, (void *)d->top_ids, (void *)d->projection_dev, (void *)d->projected, (void *)d->cand_values, (void *)d->cand_ids, (void *)d->attention_partials}) cudaFree(p);
     delete d;
 }
 
@@ -276,7 +279,7 @@ spl_status spl_draft_create(spl_engine *e, const spl_draft_config *config, spl_d
               draft_alloc(&d->ao, BR * d->attention) && draft_alloc(&d->gate, BR * d->inter) && draft_alloc(&d->up, BR * d->inter) && draft_alloc(&d->dn, BR * H) &&
               draft_alloc(&d->selected, BR * H) && draft_alloc(&d->logits, BR * size_t(d->vocab)) && draft_alloc(&d->top_values, BR * 64) && draft_alloc(&d->top_ids, BR * 64) &&
               draft_alloc(&d->projection_dev, size_t(c.rank) * H) && draft_alloc(&d->projected, BR * c.rank) &&
-              draft_alloc(&d->cand_values, BR * SPL_DRAFT_TOPK_SEGMENTS * 64) && draft_alloc(&d->cand_ids, BR * SPL_DRAFT_TOPK_SEGMENTS * 64);
+              draft_alloc(&d->attention_partials, BR * c.heads * SPL_DRAFT_ATTENTION_SPANS * (SPL_DRAFT_HEAD_DIM + 2)) && draft_alloc(&d->cand_values, BR * SPL_DRAFT_TOPK_SEGMENTS * 64) && draft_alloc(&d->cand_ids, BR * SPL_DRAFT_TOPK_SEGMENTS * 64);
     for (DraftLayer &L : d->layers)
         ok = ok && draft_alloc(&L.k_ring, size_t(e->c.max_slots) * c.ring_capacity * d->kv) && draft_alloc(&L.v_ring, size_t(e->c.max_slots) * c.ring_capacity * d->kv) &&
              draft_alloc(&L.c_k, CR * d->kv) && draft_alloc(&L.c_v, CR * d->kv);

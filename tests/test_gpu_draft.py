@@ -167,3 +167,33 @@ def test_context_bookkeeping_and_refusals(setup):
         draft.set_tensor("layers.9.mlp.up_proj.weight", np.zeros((16, 256), np.uint16))             # no such layer
     with pytest.raises(S.EngineError):
         S.DraftModel(engine, S.DraftConfig(layers=1, heads=3, kv_heads=2))
+
+
+def test_a_window_of_several_chunks_and_spans():
+    """A context longer than one 128-position chunk: the attention's spans run side by side and are merged; the window cuts
+    the oldest positions and the ring has wrapped."""
+    g = S.tiny_geometry()
+    model = O.Model(O.tiny_geometry())
+    engine = S.Engine(g, S.EngineConfig(max_slots=1, max_rows=64, kv_pages=4, max_context=1024))
+    engine.load_model(model)
+    engine.enable_features(TAPS)
+    config = S.DraftConfig(layers=1, heads=4, kv_heads=2, group_size=16, rank=32, window=300, ring_capacity=320, block_size=8, max_block=16,
+                           candidates=8, mask_token=31999)
+    tensors = checkpoint(g, config, seed=23)
+    draft = S.DraftModel(engine, config)
+    for name, bits in tensors.items():
+        draft.set_tensor(name, bits)
+    oracle = OD.Draft(model, config, tensors, TAPS)
+    for chunk in range(6):
+        feed(engine, draft, oracle, 0, 62 * chunk, 62, 40 + chunk)          # 372 positions: the ring of 320 has wrapped
+    assert draft.context_length(0, 372) == 299
+    requests = [S.DraftRequest(0, 4321, 372, 16, False)]
+    draft.propose(requests, vocab_limit=31000)
+    want = oracle.propose(requests)
+    logits = draft.debug_read(0, (15, g.vocab))
+    selected = draft.debug_read(1, (15, g.hidden))
+    observed(f"draft block pass over a 300-position window (3 chunks, 8 spans, wrapped ring): max |logit - restatement| {np.abs(logits - want['logits']).max():.3e} "
+             f"(largest {np.abs(want['logits']).max():.2f}); hidden rows {np.abs(selected - want['selected']).max():.3e} of {np.abs(want['selected']).max():.2f}")
+    assert np.abs(selected - want["selected"]).max() <= 2e-2 * np.abs(want["selected"]).max()
+    assert np.abs(logits - want["logits"]).max() <= 2e-2 * np.abs(want["logits"]).max()
+    draft.close(); engine.close()
