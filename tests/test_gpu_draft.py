@@ -1,6 +1,11 @@
 """The DFlash 2 drafter (Sources/SploshRuntime/DraftModel.swift; Sources/Shaders/draft.metal) on the device against its
 numpy restatement (oracle/draft.py): the context pass over the target's feature rows, the block pass (dynamic
-convolutions, K/V ring, windowed non-causal attention, the engine's GEMMs) and the candidate selector."""
+convolutions, K/V ring, windowed non-causal attention, the engine's GEMMs) and the candidate selector.
+
+Tolerance of the block pass: 2 % of the largest value. The restatement itself moves by 0.5 % of its largest logit when its
+inputs move by 1e-6 (seeded check): every GEMM rounds its activations to bf16, the rings hold fp16, the MLP's product is
+rounded to bf16, and a value that crosses a rounding boundary jumps by 2^-8 of itself. The pieces that have no such
+boundary are held tighter: the rings to one fp16 step, the candidates and the selector's path exactly."""
 import numpy as np
 import pytest
 
