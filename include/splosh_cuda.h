@@ -429,6 +429,18 @@ spl_status spl_draft_quantize_q4(const uint16_t *bf16, int32_t rows, int32_t inn
 spl_status spl_draft_select(int32_t drafted, int32_t k, int32_t rank, int32_t hidden, int32_t anchor, const int32_t *ids, const float *values,
                             const float *hidden_rows, const float *hidden_projection, const uint16_t *predecessor, const uint16_t *successor,
                             float temperature, uint64_t *random_state, int32_t *tokens, float *probabilities);
+/* The checkpoint as the reference reads it: a bf16 safetensors file (MappedFile / SafetensorsHeader, DraftModel.swift:742-794).
+ * The file is mapped read-only for the call; refusals say why in `message` ("missing tensor <name>", "<name> is F16 [..];
+ * expected BF16 [..]", "bad safetensors header", ...). spl_draft_tensor_count / _expected list what the drafter asks for. */
+spl_status spl_draft_load_safetensors(spl_draft *draft, const char *path, char *message, size_t message_bytes);
+int32_t spl_draft_tensor_count(const spl_draft *draft);
+spl_status spl_draft_tensor_expected(const spl_draft *draft, int32_t index, char *name, uint64_t name_bytes, int64_t *shape, int32_t *dimensions);
+/* DraftModel.exportContext / importContext (:285-311): a slot's K and V rings (spl_draft_context_bytes of them, layer by
+ * layer, K then V, fp16) and the range [first, end) of positions valid in them for a prefix of `token_count` tokens.
+ * *first < 0 after an export: nothing useful is held (the reference's nil). A snapshot of another size resets the slot. */
+uint64_t spl_draft_context_bytes(const spl_draft *draft);
+spl_status spl_draft_export_context(spl_draft *draft, int32_t slot, int32_t token_count, int32_t *first, int32_t *end, void *rings);
+spl_status spl_draft_import_context(spl_draft *draft, int32_t slot, int32_t first, int32_t end, const void *rings, uint64_t bytes);
 /* For tests: the last block pass's buffers. 0 logits [picked][vocab], 1 selected hidden rows [picked][hidden], 2 / 3 layer
  * `index`'s K / V ring (fp16), 4 the block's residual stream after the last layer. */
 spl_status spl_draft_debug_read(spl_draft *draft, int32_t what, int32_t index, void *dst, uint64_t bytes);

@@ -357,6 +357,85 @@ static spl_status draft_complete(spl_draft *d) {
     return all ? SPL_OK : draft_fail(d, SPL_ERR_INVALID_ARGUMENT, "missing tensors");
 }
 
+spl_status spl_draft_reset_slot(spl_draft *d, int32_t slot);
+// The checkpoint's tensors in the order the reference asks for them (DraftModel.swift:172-203), with their shapes.
+static void draft_expected(const spl_draft *d, std::vector<std::string> *names, std::vector<std::vector<int64_t>> *shapes) {
+    const int64_t H = d->hidden, D = SPL_DRAFT_HEAD_DIM;
+    auto add = [&](const std::string &n, std::vector<int64_t> shape) { names->push_back(n); shapes->push_back(std::move(shape)); };
+    for (int index = 0; index < d->c.layers; ++index) {
+        const std::string p = "layers." + std::to_string(index) + ".";
+        add(p + "input_layernorm.weight", {H}); add(p + "post_attention_layernorm.weight", {H});
+        add(p + "self_attn.q_norm.weight", {D}); add(p + "self_attn.k_norm.weight", {D});
+        add(p + "attention_conv.base_kernel", {2, 2, H}); add(p + "mlp_conv.base_kernel", {2, 2, H});
+        add(p + "self_attn.q_proj.weight", {d->attention, H}); add(p + "self_attn.k_proj.weight", {d->kv, H}); add(p + "self_attn.v_proj.weight", {d->kv, H});
+        add(p + "self_attn.o_proj.weight", {H, d->attention});
+        add(p + "mlp.gate_proj.weight", {d->inter, H}); add(p + "mlp.up_proj.weight", {d->inter, H}); add(p + "mlp.down_proj.weight", {H, d->inter});
+        add(p + "attention_conv.kernel_projection.weight", {4 * d->groups, H}); add(p + "mlp_conv.kernel_projection.weight", {4 * d->groups, H});
+    }
+    add("fc.weight", {H, d->feature_width}); add("hidden_norm.weight", {H}); add("norm.weight", {H});
+    add("candidate_selector.hidden_projection.weight", {d->c.rank, H});
+    add("candidate_selector.predecessor_codebook", {d->vocab, d->c.rank}); add("candidate_selector.successor_codebook", {d->vocab, d->c.rank});
+}
+int32_t spl_draft_tensor_count(const spl_draft *d) {
+    if (!d) return 0;
+    std::vector<std::string> names; std::vector<std::vector<int64_t>> shapes;
+    draft_expected(d, &names, &shapes);
+    return int32_t(names.size());
+}
+// Tensor `index` of the checkpoint: its name and its shape (up to four dimensions, *dimensions of them).
+spl_status spl_draft_tensor_expected(const spl_draft *d, int32_t index, char *name, uint64_t name_bytes, int64_t *shape, int32_t *dimensions) {
+    if (!d || !name || !name_bytes || !shape || !dimensions) return SPL_ERR_INVALID_ARGUMENT;
+    std::vector<std::string> names; std::vector<std::vector<int64_t>> shapes;
+    draft_expected(d, &names, &shapes);
+    if (index < 0 || index >= int(names.size()) || names[index].size() + 1 > name_bytes) return SPL_ERR_INVALID_ARGUMENT;
+    memcpy(name, names[index].c_str(), names[index].size() + 1);
+    *dimensions = int32_t(shapes[index].size());
+    for (size_t i = 0; i < shapes[index].size(); ++i) shape[i] = shapes[index][i];
+    return SPL_OK;
+}
+
+// ---- context snapshots (DraftModel.exportContext / importContext, :285-311) ----
+// The slot's rings as they stand for a prefix of `token_count` tokens: [first, end) and the rings' bytes, layer by layer, K then V.
+uint64_t spl_draft_context_bytes(const spl_draft *d) { return d ? uint64_t(d->c.layers) * 2 * d->c.ring_capacity * d->kv * 2 : 0; }
+// *first < 0 on return: nothing useful is held for that prefix (the reference's nil); `rings` is then untouched.
+spl_status spl_draft_export_context(spl_draft *d, int32_t slot, int32_t token_count, int32_t *first, int32_t *end, void *rings) {
+    if (!d || slot < 0 || slot >= int(d->context_end.size()) || !first || !end || !rings) return SPL_ERR_INVALID_ARGUMENT;
+    spl_engine *e = d->e;
+    SPL_NOT_IN_FLIGHT(e);
+    *first = -1; *end = 0;
+    if (d->context_end[slot] < token_count) return SPL_OK;
+    // Positions evaluated after the prefix overwrote ring entries one capacity back.
+    const int begin = std::max(d->context_first[slot], d->context_end[slot] + d->c.max_block - d->c.ring_capacity);
+    if (begin >= token_count) return SPL_OK;
+    SPL_CUDA(cudaSetDevice(e->device));
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    const size_t per_slot = size_t(d->c.ring_capacity) * d->kv * 2;
+    uint8_t *out = static_cast<uint8_t *>(rings);
+    for (DraftLayer &L : d->layers) {
+        SPL_CUDA(cudaMemcpy(out, reinterpret_cast<const uint8_t *>(L.k_ring) + slot * per_slot, per_slot, cudaMemcpyDeviceToHost)); out += per_slot;
+        SPL_CUDA(cudaMemcpy(out, reinterpret_cast<const uint8_t *>(L.v_ring) + slot * per_slot, per_slot, cudaMemcpyDeviceToHost)); out += per_slot;
+    }
+    *first = begin; *end = token_count;
+    return SPL_OK;
+}
+// A snapshot of another size resets the slot, as the reference does.
+spl_status spl_draft_import_context(spl_draft *d, int32_t slot, int32_t first, int32_t end, const void *rings, uint64_t bytes) {
+    if (!d || slot < 0 || slot >= int(d->context_end.size()) || !rings || first < 0 || end < first) return SPL_ERR_INVALID_ARGUMENT;
+    spl_engine *e = d->e;
+    SPL_NOT_IN_FLIGHT(e);
+    if (bytes != spl_draft_context_bytes(d)) return spl_draft_reset_slot(d, slot);
+    SPL_CUDA(cudaSetDevice(e->device));
+    SPL_CUDA(cudaStreamSynchronize(e->stream));
+    const size_t per_slot = size_t(d->c.ring_capacity) * d->kv * 2;
+    const uint8_t *in = static_cast<const uint8_t *>(rings);
+    for (DraftLayer &L : d->layers) {
+        SPL_CUDA(cudaMemcpy(reinterpret_cast<uint8_t *>(L.k_ring) + slot * per_slot, in, per_slot, cudaMemcpyHostToDevice)); in += per_slot;
+        SPL_CUDA(cudaMemcpy(reinterpret_cast<uint8_t *>(L.v_ring) + slot * per_slot, in, per_slot, cudaMemcpyHostToDevice)); in += per_slot;
+    }
+    d->context_first[slot] = first; d->context_end[slot] = end;
+    return SPL_OK;
+}
+
 // ---- context (DraftModel.swift:277-359) ----
 spl_status spl_draft_reset_slot(spl_draft *d, int32_t slot) {
     if (!d || slot < 0 || slot >= int(d->context_end.size())) return SPL_ERR_INVALID_ARGUMENT;

@@ -436,3 +436,58 @@ extern "C" spl_status spl_weights_load_splw_file(spl_engine *engine, const char 
     if (!loader.load()) return say(message, message_bytes, loader.error, SPL_ERR_INVALID_ARGUMENT);
     return say(message, message_bytes, "", SPL_OK);
 }
+
+// The drafter's checkpoint, a bf16 safetensors file (MappedFile and SafetensorsHeader, Sources/SploshRuntime/DraftModel.swift:742-794):
+// an 8-byte little-endian header length, a JSON object of {dtype, shape, data_offsets} per tensor name ("__metadata__" aside),
+// then the data. Every tensor the drafter asks for is handed to spl_draft_set_tensor; refusals carry the reference's reasons.
+extern "C" spl_status spl_draft_load_safetensors(spl_draft *draft, const char *path, char *message, size_t message_bytes) {
+    if (!draft || !path) return say(message, message_bytes, "null argument", SPL_ERR_INVALID_ARGUMENT);
+    Mapping file;
+    const int opened = file.open_file(path);
+    if (opened == 1) return say(message, message_bytes, std::string("draft model: cannot open ") + path, SPL_ERR_INVALID_ARGUMENT);
+    if (opened == 2 || file.size <= 16 || file.map == MAP_FAILED) return say(message, message_bytes, std::string("draft model: cannot map ") + path, SPL_ERR_INVALID_ARGUMENT);
+    const uint8_t *base = static_cast<const uint8_t *>(file.map);
+    uint64_t header_length = 0;
+    memcpy(&header_length, base, 8);
+    if (header_length == 0 || header_length > file.size - 8) return say(message, message_bytes, "draft model: bad safetensors header", SPL_ERR_INVALID_ARGUMENT);
+    JsonReader reader{reinterpret_cast<const char *>(base + 8), reinterpret_cast<const char *>(base + 8 + header_length)};
+    const Json header = reader.value();
+    reader.space();
+    if (!reader.ok || reader.p != reader.end || header.kind != Json::Object) return say(message, message_bytes, "draft model: safetensors header is not an object", SPL_ERR_INVALID_ARGUMENT);
+    struct Entry { std::string dtype; std::vector<int64_t> shape; uint64_t offset = 0, length = 0; };
+    std::vector<std::pair<std::string, Entry>> entries;
+    for (const auto &field : header.fields) {
+        if (field.first == "__metadata__") continue;
+        const Json &t = field.second;
+        Entry en;
+        uint64_t begin = 0, end = 0;
+        const Json *dtype = t.kind == Json::Object ? t.get("dtype") : nullptr, *offsets = t.kind == Json::Object ? t.get("data_offsets") : nullptr;
+        if (!dtype || dtype->kind != Json::String || !shape_of(t.get("shape"), &en.shape) || !offsets || offsets->kind != Json::Array || offsets->items.size() != 2 ||
+            !integer_of(&offsets->items[0], &begin) || !integer_of(&offsets->items[1], &end) || end < begin || 8 + header_length + end > file.size)
+            return say(message, message_bytes, "draft model: malformed tensor entry " + field.first, SPL_ERR_INVALID_ARGUMENT);
+        en.dtype = dtype->text; en.offset = 8 + header_length + begin; en.length = end - begin;
+        entries.emplace_back(field.first, std::move(en));
+    }
+    auto shape_text = [](const std::vector<int64_t> &shape) {
+        std::string out = "[";
+        for (size_t i = 0; i < shape.size(); ++i) out += (i ? ", " : "") + std::to_string(shape[i]);
+        return out + "]";
+    };
+    const int count = spl_draft_tensor_count(draft);
+    for (int index = 0; index < count; ++index) {
+        char name[160]; int64_t dims[4]; int32_t nd = 0;
+        if (spl_draft_tensor_expected(draft, index, name, sizeof name, dims, &nd) != SPL_OK) return say(message, message_bytes, "draft model: no such tensor", SPL_ERR_INVALID_ARGUMENT);
+        const std::vector<int64_t> want(dims, dims + nd);
+        const Entry *found = nullptr;
+        for (const auto &en : entries) if (en.first == name) { found = &en.second; break; }
+        if (!found) return say(message, message_bytes, std::string("draft model: missing tensor ") + name, SPL_ERR_INVALID_ARGUMENT);
+        int64_t elements = 1;
+        for (int64_t v : want) elements *= v;
+        if (found->dtype != "BF16" || found->shape != want || found->length != uint64_t(elements) * 2)
+            return say(message, message_bytes, std::string("draft model: ") + name + " is " + found->dtype + " " + shape_text(found->shape) + "; expected BF16 " + shape_text(want), SPL_ERR_INVALID_ARGUMENT);
+        const int64_t rows = nd == 1 ? 1 : want[0];
+        const spl_status s = spl_draft_set_tensor(draft, name, reinterpret_cast<const uint16_t *>(base + found->offset), int32_t(rows), int32_t(elements / rows));
+        if (s != SPL_OK) return say(message, message_bytes, std::string("draft model: ") + name + " was refused", s);
+    }
+    return say(message, message_bytes, "", SPL_OK);
+}

@@ -112,6 +112,34 @@ class DraftModel:
         rows, inner = (1, bits.size) if bits.ndim == 1 else (bits.shape[0], int(np.prod(bits.shape[1:])))
         self.engine._check(lib().spl_draft_set_tensor(self.handle, name.encode(), _ptr(bits), rows, inner))
 
+    def load_safetensors(self, path):
+        """DraftModel.init(engine:safetensorsURL:): every tensor of the bf16 checkpoint at `path`."""
+        message = C.create_string_buffer(512)
+        status = lib().spl_draft_load_safetensors(self.handle, str(path).encode(), message, len(message))
+        if status:
+            raise EngineError(status, message.value.decode())
+
+    def expected_tensors(self):
+        """(name, shape) of every tensor the drafter asks for, in the reference's order."""
+        out = []
+        for index in range(lib().spl_draft_tensor_count(self.handle)):
+            name = C.create_string_buffer(160); shape = (C.c_int64 * 4)(); nd = C.c_int32()
+            self.engine._check(lib().spl_draft_tensor_expected(self.handle, index, name, len(name), C.cast(shape, C.c_void_p), C.cast(C.byref(nd), C.c_void_p)))
+            out.append((name.value.decode(), tuple(shape[i] for i in range(nd.value))))
+        return out
+
+    def export_context(self, slot, token_count):
+        """DraftModel.exportContext: (first, end, rings) for a prefix of `token_count` tokens, or None when nothing useful is held."""
+        rings = np.empty(lib().spl_draft_context_bytes(self.handle), np.uint8)
+        first, end = C.c_int32(), C.c_int32()
+        self.engine._check(lib().spl_draft_export_context(self.handle, slot, token_count, C.cast(C.byref(first), C.c_void_p), C.cast(C.byref(end), C.c_void_p), _ptr(rings)))
+        return None if first.value < 0 else (first.value, end.value, rings)
+
+    def import_context(self, slot, snapshot):
+        first, end, rings = snapshot
+        rings = np.ascontiguousarray(rings, np.uint8)
+        self.engine._check(lib().spl_draft_import_context(self.handle, slot, first, end, _ptr(rings), rings.nbytes))
+
     def reset_slot(self, slot):
         self.engine._check(lib().spl_draft_reset_slot(self.handle, slot))
 

@@ -251,6 +251,12 @@ def lib():
             "spl_draft_quantize_q4": (i32, [vp, i32, i32, i32, vp, vp, vp]),
             "spl_draft_select": (i32, [i32, i32, i32, i32, i32, vp, vp, vp, vp, vp, vp, C.c_float, vp, vp, vp]),
             "spl_draft_debug_read": (i32, [vp, i32, i32, vp, C.c_uint64]),
+            "spl_draft_load_safetensors": (i32, [vp, C.c_char_p, C.c_char_p, C.c_size_t]),
+            "spl_draft_tensor_count": (i32, [vp]),
+            "spl_draft_tensor_expected": (i32, [vp, i32, C.c_char_p, C.c_uint64, vp, vp]),
+            "spl_draft_context_bytes": (C.c_uint64, [vp]),
+            "spl_draft_export_context": (i32, [vp, i32, i32, vp, vp, vp]),
+            "spl_draft_import_context": (i32, [vp, i32, i32, i32, vp, C.c_uint64]),
         }
         for name, (res, args) in sig.items():
             fn = getattr(L, name)

@@ -13,6 +13,7 @@ import splosh_b200 as S
 from helpers import observed
 from oracle import draft as OD
 from oracle import oracle as O
+from safetensors_writer import write as write_safetensors
 
 pytestmark = pytest.mark.gpu
 
@@ -202,3 +203,59 @@ def test_a_window_of_several_chunks_and_spans():
     assert np.abs(selected - want["selected"]).max() <= 2e-2 * np.abs(want["selected"]).max()
     assert np.abs(logits - want["logits"]).max() <= 2e-2 * np.abs(want["logits"]).max()
     draft.close(); engine.close()
+
+
+def test_a_safetensors_checkpoint_and_a_context_snapshot(setup, tmp_path):
+    """The checkpoint from a bf16 safetensors file steps like the one given tensor by tensor; a slot's context exported and
+    imported into another slot drafts the same block; refused files say why in the reference's words."""
+    g, engine, draft, oracle, tensors = setup
+    shaped = dict(tensors)
+    for layer in range(CONFIG.layers):
+        for name in ("attention_conv.base_kernel", "mlp_conv.base_kernel"):
+            shaped[f"layers.{layer}.{name}"] = tensors[f"layers.{layer}.{name}"].reshape(2, 2, g.hidden)
+    assert dict(draft.expected_tensors()) == {n: tuple(np.shape(b)) for n, b in shaped.items()}
+    path = tmp_path / "draft.safetensors"
+    write_safetensors(path, shaped, metadata={"format": "pt"})
+    loaded = S.DraftModel(engine, CONFIG)
+    loaded.load_safetensors(path)
+    for d in (draft, loaded):
+        d.reset_slot(0); d.reset_slot(1)
+    engine.reset_slot(0)
+    rng = np.random.default_rng(77)
+    toks = rng.integers(0, 31000, 20)
+    engine.step([S.EngineRow(0, int(toks[i]), i, i == 19) for i in range(20)])
+    for d in (draft, loaded):
+        d.push_context([(0, i, i) for i in range(20)])
+    request = [S.DraftRequest(0, 4242, 20, 8)]
+    a = draft.propose(request, vocab_limit=31000)[0]
+    logits_a = draft.debug_read(0, (7, g.vocab))
+    b = loaded.propose(request, vocab_limit=31000)[0]
+    assert np.array_equal(logits_a, loaded.debug_read(0, (7, g.vocab))) and a.tokens == b.tokens and a.candidates == b.candidates
+    # the slot's context into slot 1 of the same drafter
+    snapshot = draft.export_context(0, 20)
+    assert snapshot is not None and snapshot[0] == 0 and snapshot[1] == 20 and draft.export_context(0, 25) is None
+    draft.import_context(1, snapshot)
+    assert draft.context_length(1, 20) == 20
+    c = draft.propose([S.DraftRequest(1, 4242, 20, 8)], vocab_limit=31000)[0]
+    assert np.array_equal(logits_a, draft.debug_read(0, (7, g.vocab))) and c.tokens == a.tokens
+    draft.import_context(1, (0, 20, snapshot[2][:-2]))                 # a snapshot of another size resets the slot
+    assert draft.context_length(1, 20) == 0
+    # refusals
+    fresh = S.DraftModel(engine, CONFIG)
+    write_safetensors(path, shaped, drop=("norm.weight",))
+    with pytest.raises(S.EngineError, match="missing tensor norm.weight"):
+        fresh.load_safetensors(path)
+    write_safetensors(path, shaped, lie={"fc.weight": "F16"})
+    with pytest.raises(S.EngineError, match=r"fc.weight is F16 \[1024, 2048\]; expected BF16 \[1024, 2048\]"):
+        fresh.load_safetensors(path)
+    bad = dict(shaped); bad["hidden_norm.weight"] = shaped["hidden_norm.weight"][:512]
+    write_safetensors(path, bad)
+    with pytest.raises(S.EngineError, match=r"hidden_norm.weight is BF16 \[512\]; expected BF16 \[1024\]"):
+        fresh.load_safetensors(path)
+    with open(path, "wb") as f:
+        f.write(b"\xff" * 64)
+    with pytest.raises(S.EngineError, match="bad safetensors header"):
+        fresh.load_safetensors(path)
+    with pytest.raises(S.EngineError, match="cannot open"):
+        fresh.load_safetensors(tmp_path / "nothing.safetensors")
+    loaded.close(); fresh.close()
