@@ -160,6 +160,167 @@ spl_draft_attention_kernel(const float *__restrict__ qproj, const uint16_t *__re
     }
 }
 
+// The same attention on the tensor cores (the warp-level instruction, fp16 operands, fp32 sums): one block per (kv head,
+// request, span). A request's rows x the kv head's G query heads are the M dimension (32 or 64 queries, 16 to a warp); the
+// span's positions come through shared memory 64 at a time: S = Q K^T, the row-wise running maximum and sum, P (rounded to
+// fp16) times V. Every (query, position) pair is masked by the row's own range [max(lo, position + 1 - window), hi). The
+// result is the span's partial [maximum, sum, 128 values] per (row, head) for the merge kernel, as the other form leaves it.
+// requests[2 r], [2 r + 1]: first row and row count of request r (count x G <= 64). Grid (kv_heads, requests, spans), 128 threads.
+__device__ __forceinline__ void spl_draft_mma_f16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+template <int G>
+__global__ void __launch_bounds__(128)
+spl_draft_attention_mma_kernel(const float *__restrict__ qproj, const uint16_t *__restrict__ norm_weight, const uint32_t *__restrict__ requests,
+                               const uint32_t *__restrict__ row_slot, const uint32_t *__restrict__ row_pos, const uint32_t *__restrict__ row_lo,
+                               const uint32_t *__restrict__ row_hi, const __half *__restrict__ kring, const __half *__restrict__ vring, float *partials,
+                               int heads, int kv_heads, int capacity, int window, float scale, float eps, float theta) {
+    constexpr int D = SPL_DRAFT_HEAD_DIM, LD = D + 8, TK = 64;       // a row of 136 halves: the fragments' 32-bit loads meet no bank twice
+    __shared__ __align__(16) __half ks[TK][LD];
+    __shared__ __align__(16) __half qv[64][LD];                     // the queries first, then every chunk's values
+    __shared__ uint32_t q_lo[64], q_hi[64];
+    spl_grid_begin();
+    const int kv_head = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const uint32_t row0 = requests[2 * blockIdx.y], count = requests[2 * blockIdx.y + 1];
+    const int queries = int(count) * G, mtiles = (queries + 15) / 16;
+    // Queries: RMSNorm and rotary embedding, to fp16; a warp a query, a lane the elements lane, lane + 32 and their partners 64 on.
+    for (int q = warp; q < 64; q += 4) {
+        if (q < queries) {
+            const uint32_t row = row0 + q / G;
+            const float *src = qproj + (size_t(row) * heads + kv_head * G + q % G) * D;
+            const float x0 = src[lane], x1 = src[lane + 32], y0 = src[lane + 64], y1 = src[lane + 96];
+            const float inv = 1.0f / sqrtf(spl_warp_sum(x0 * x0 + x1 * x1 + y0 * y0 + y1 * y1) / float(D) + eps);
+            const float w0 = spl_bf16_to_float(norm_weight[lane]), w1 = spl_bf16_to_float(norm_weight[lane + 32]);
+            const float w2 = spl_bf16_to_float(norm_weight[lane + 64]), w3 = spl_bf16_to_float(norm_weight[lane + 96]);
+            const float a0 = x0 * inv * w0, a1 = x1 * inv * w1, b0 = y0 * inv * w2, b1 = y1 * inv * w3;
+            const uint32_t position = row_pos[row];
+            qv[q][lane] = __float2half_rn(spl_draft_rope(a0, b0, lane, position, theta));
+            qv[q][lane + 32] = __float2half_rn(spl_draft_rope(a1, b1, lane + 32, position, theta));
+            qv[q][lane + 64] = __float2half_rn(spl_draft_rope(b0, a0, lane + 64, position, theta));
+            qv[q][lane + 96] = __float2half_rn(spl_draft_rope(b1, a1, lane + 96, position, theta));
+            if (lane == 0) {
+                const uint32_t first_visible = position + 1u > uint32_t(window) ? position + 1u - uint32_t(window) : 0u;
+                q_lo[q] = max(row_lo[row], first_visible); q_hi[q] = row_hi[row];
+            }
+        } else {
+            qv[q][lane] = qv[q][lane + 32] = qv[q][lane + 64] = qv[q][lane + 96] = __float2half_rn(0.0f);
+            if (lane == 0) { q_lo[q] = 0xFFFFFFFFu; q_hi[q] = 0u; }
+        }
+    }
+    __syncthreads();
+    const bool computing = warp < mtiles;
+    const int m0 = warp * 16;
+    uint32_t qa[8][4];                                              // the warp's sixteen queries as A fragments, eight steps of the 128 channels
+    uint32_t lo_a = 0xFFFFFFFFu, hi_a = 0u, lo_b = 0xFFFFFFFFu, hi_b = 0u;
+    if (computing) {
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+            qa[kk][0] = *reinterpret_cast<const uint32_t *>(&qv[m0 + g][16 * kk + 2 * t]);
+            qa[kk][1] = *reinterpret_cast<const uint32_t *>(&qv[m0 + g + 8][16 * kk + 2 * t]);
+            qa[kk][2] = *reinterpret_cast<const uint32_t *>(&qv[m0 + g][16 * kk + 2 * t + 8]);
+            qa[kk][3] = *reinterpret_cast<const uint32_t *>(&qv[m0 + g + 8][16 * kk + 2 * t + 8]);
+        }
+        lo_a = q_lo[m0 + g]; hi_a = q_hi[m0 + g]; lo_b = q_lo[m0 + g + 8]; hi_b = q_hi[m0 + g + 8];
+    }
+    // The request's whole range, dealt to the spans in runs of chunks.
+    uint32_t lo_all = 0xFFFFFFFFu, hi_all = 0u;
+    for (int q = 0; q < queries; q += G) { lo_all = min(lo_all, q_lo[q]); hi_all = max(hi_all, q_hi[q]); }
+    const uint32_t chunks = hi_all > lo_all ? (hi_all - lo_all + TK - 1) / TK : 0u;
+    const uint32_t per_span = (chunks + gridDim.z - 1) / gridDim.z, chunk_begin = blockIdx.z * per_span, chunk_end = min(chunks, chunk_begin + per_span);
+    const size_t ring_base = size_t(row_slot[row0]) * capacity;
+    float o[16][4];
+#pragma unroll
+    for (int n = 0; n < 16; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+    float max_a = -INFINITY, max_b = -INFINITY, sum_a = 0.0f, sum_b = 0.0f;
+    __syncthreads();                                                // the queries are in registers: their place takes the values
+    for (uint32_t chunk = chunk_begin; chunk < chunk_end; ++chunk) {
+        const uint32_t first = lo_all + chunk * TK;
+        // 64 positions' keys and values, sixteen bytes a thread and turn; positions past the range are zero.
+        for (int idx = threadIdx.x; idx < TK * (D / 8); idx += 128) {
+            const int token = idx / (D / 8), piece = idx % (D / 8);
+            uint4 kk = make_uint4(0, 0, 0, 0), vv = make_uint4(0, 0, 0, 0);
+            if (first + token < hi_all) {
+                const size_t at = ((ring_base + (first + token) % uint32_t(capacity)) * kv_heads + kv_head) * D + piece * 8;
+                kk = *reinterpret_cast<const uint4 *>(kring + at); vv = *reinterpret_cast<const uint4 *>(vring + at);
+            }
+            *reinterpret_cast<uint4 *>(&ks[token][piece * 8]) = kk; *reinterpret_cast<uint4 *>(&qv[token][piece * 8]) = vv;
+        }
+        __syncthreads();
+        if (computing) {
+            float sc[8][4];
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.0f;
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t b0 = *reinterpret_cast<const uint32_t *>(&ks[8 * n + g][16 * kk + 2 * t]);
+                    const uint32_t b1 = *reinterpret_cast<const uint32_t *>(&ks[8 * n + g][16 * kk + 2 * t + 8]);
+                    spl_draft_mma_f16(sc[n], qa[kk], b0, b1);
+                }
+            }
+            // Scale, mask by the rows' own ranges, the rows' maxima over the chunk (a row lives in a quad of lanes).
+            float cm_a = -INFINITY, cm_b = -INFINITY;
+#pragma unroll
+            for (int n = 0; n < 8; ++n)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const uint32_t position = first + 8 * n + 2 * t + e;
+                    sc[n][e] = (position >= lo_a && position < hi_a) ? sc[n][e] * scale : -INFINITY;
+                    sc[n][2 + e] = (position >= lo_b && position < hi_b) ? sc[n][2 + e] * scale : -INFINITY;
+                    cm_a = fmaxf(cm_a, sc[n][e]); cm_b = fmaxf(cm_b, sc[n][2 + e]);
+                }
+            cm_a = fmaxf(cm_a, __shfl_xor_sync(0xffffffffu, cm_a, 1)); cm_a = fmaxf(cm_a, __shfl_xor_sync(0xffffffffu, cm_a, 2));
+            cm_b = fmaxf(cm_b, __shfl_xor_sync(0xffffffffu, cm_b, 1)); cm_b = fmaxf(cm_b, __shfl_xor_sync(0xffffffffu, cm_b, 2));
+            const float new_a = fmaxf(max_a, cm_a), new_b = fmaxf(max_b, cm_b);
+            const float rs_a = new_a == -INFINITY ? 1.0f : expf(max_a - new_a), rs_b = new_b == -INFINITY ? 1.0f : expf(max_b - new_b);
+            max_a = new_a; max_b = new_b; sum_a *= rs_a; sum_b *= rs_b;
+#pragma unroll
+            for (int n = 0; n < 16; ++n) { o[n][0] *= rs_a; o[n][1] *= rs_a; o[n][2] *= rs_b; o[n][3] *= rs_b; }
+            uint32_t pa[4][4];                                      // P as A fragments: four steps of sixteen positions
+            float ps_a = 0.0f, ps_b = 0.0f;
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
+                const float p0 = new_a == -INFINITY ? 0.0f : expf(sc[n][0] - new_a), p1 = new_a == -INFINITY ? 0.0f : expf(sc[n][1] - new_a);
+                const float p2 = new_b == -INFINITY ? 0.0f : expf(sc[n][2] - new_b), p3 = new_b == -INFINITY ? 0.0f : expf(sc[n][3] - new_b);
+                const __half2 ha = __floats2half2_rn(p0, p1), hb = __floats2half2_rn(p2, p3);
+                // the sums take the rounded probabilities, the ones the product uses
+                ps_a += __low2float(ha) + __high2float(ha); ps_b += __low2float(hb) + __high2float(hb);
+                pa[n >> 1][(n & 1) * 2] = *reinterpret_cast<const uint32_t *>(&ha);
+                pa[n >> 1][(n & 1) * 2 + 1] = *reinterpret_cast<const uint32_t *>(&hb);
+            }
+            ps_a += __shfl_xor_sync(0xffffffffu, ps_a, 1); ps_a += __shfl_xor_sync(0xffffffffu, ps_a, 2);
+            ps_b += __shfl_xor_sync(0xffffffffu, ps_b, 1); ps_b += __shfl_xor_sync(0xffffffffu, ps_b, 2);
+            sum_a += ps_a; sum_b += ps_b;
+            // O += P V: the values' fragments come transposed out of their rows (ldmatrix.trans), two channel tiles a load.
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int n2 = 0; n2 < 8; ++n2) {
+                    uint32_t b0, b1, b2, b3;
+                    const uint32_t address = uint32_t(__cvta_generic_to_shared(&qv[16 * j + (lane & 15)][16 * n2 + 8 * (lane >> 4)]));
+                    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(b0), "=r"(b1), "=r"(b2), "=r"(b3) : "r"(address));
+                    spl_draft_mma_f16(o[2 * n2], pa[j], b0, b1);
+                    spl_draft_mma_f16(o[2 * n2 + 1], pa[j], b2, b3);
+                }
+        }
+        __syncthreads();
+    }
+    if (computing) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int q = m0 + g + 8 * half;
+            if (q < queries) {
+                const uint32_t row = row0 + q / G;
+                float *p = partials + ((size_t(row) * heads + kv_head * G + q % G) * gridDim.z + blockIdx.z) * (D + 2);
+                if (t == 0) { p[0] = half ? max_b : max_a; p[1] = half ? sum_b : sum_a; }
+#pragma unroll
+                for (int n = 0; n < 16; ++n) { p[2 + 8 * n + 2 * t] = o[n][2 * half]; p[2 + 8 * n + 2 * t + 1] = o[n][2 * half + 1]; }
+            }
+        }
+    }
+}
+
 // The spans of a (row, head) put together (sp_draft_attention_merge, draft.metal:279-300). Grid (heads, rows), 128 threads.
 __global__ void __launch_bounds__(128)
 spl_draft_attention_merge_kernel(const float *__restrict__ partials, float *out, int heads, int spans) {

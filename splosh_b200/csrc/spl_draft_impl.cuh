@@ -102,7 +102,7 @@ struct spl_draft {
     uint32_t *c_meta = nullptr;                            // engine row, slot, position: three runs of context_rows
     __nv_bfloat16 *wide_act = nullptr; float *wide_sums = nullptr;      // the fc GEMM's operand: its inner dimension is the taps' width, wider than the engine's scratch
     // the block pass
-    uint32_t *b_meta = nullptr;                            // tokens, slot, position, lo, hi, gather, offset: seven runs of block_rows
+    uint32_t *b_meta = nullptr;                            // tokens, slot, position, lo, hi, gather, offset: seven runs of the rows; then (first row, rows) per request
     float *dh = nullptr, *x = nullptr, *xc = nullptr, *t = nullptr, *dyn = nullptr, *qp = nullptr, *kp = nullptr, *vp = nullptr, *ao = nullptr,
           *gate = nullptr, *up = nullptr, *dn = nullptr, *selected = nullptr, *logits = nullptr, *top_values = nullptr;
     int32_t *top_ids = nullptr;
@@ -162,11 +162,19 @@ static spl_status draft_gemm_wide(spl_draft *d, const SplQ4Dev &w, const float *
 }
 
 template <int G>
-static void draft_attention_launch(spl_draft *d, const DraftLayer &L, int rows, const uint32_t *slots, const uint32_t *positions, const uint32_t *lo, const uint32_t *hi) {
+static void draft_attention_launch(spl_draft *d, const DraftLayer &L, int rows, int requests, const uint32_t *request_rows, const uint32_t *slots, const uint32_t *positions,
+                                   const uint32_t *lo, const uint32_t *hi) {
     spl_engine *e = d->e;
-    launch_step(spl_draft_attention_kernel<G>, dim3(d->c.kv_heads, rows, SPL_DRAFT_ATTENTION_SPANS), dim3(128), 0, e->stream, (const float *)d->qp, (const uint16_t *)L.q_norm->vec, slots,
-                positions, lo, hi, (const __half *)L.k_ring, (const __half *)L.v_ring, d->attention_partials, int(d->c.heads), int(d->c.kv_heads), int(d->c.ring_capacity),
-                int(d->c.window), 1.0f / sqrtf(float(SPL_DRAFT_HEAD_DIM)), e->g.eps, e->g.rope_theta);
+    const float scale = 1.0f / sqrtf(float(SPL_DRAFT_HEAD_DIM));
+    if (d->c.max_block * G <= 64)
+        // a request's rows x G query heads fit the tensor-core form's 64 queries a block
+        launch_step(spl_draft_attention_mma_kernel<G>, dim3(d->c.kv_heads, requests, SPL_DRAFT_ATTENTION_SPANS), dim3(128), 0, e->stream, (const float *)d->qp,
+                    (const uint16_t *)L.q_norm->vec, request_rows, slots, positions, lo, hi, (const __half *)L.k_ring, (const __half *)L.v_ring, d->attention_partials,
+                    int(d->c.heads), int(d->c.kv_heads), int(d->c.ring_capacity), int(d->c.window), scale, e->g.eps, e->g.rope_theta);
+    else
+        launch_step(spl_draft_attention_kernel<G>, dim3(d->c.kv_heads, rows, SPL_DRAFT_ATTENTION_SPANS), dim3(128), 0, e->stream, (const float *)d->qp, (const uint16_t *)L.q_norm->vec, slots,
+                    positions, lo, hi, (const __half *)L.k_ring, (const __half *)L.v_ring, d->attention_partials, int(d->c.heads), int(d->c.kv_heads), int(d->c.ring_capacity),
+                    int(d->c.window), scale, e->g.eps, e->g.rope_theta);
     launch_step(spl_draft_attention_merge_kernel, dim3(d->c.heads, rows), dim3(128), 0, e->stream, (const float *)d->attention_partials, d->ao, int(d->c.heads), SPL_DRAFT_ATTENTION_SPANS);
 }
 
@@ -274,7 +282,7 @@ spl_status spl_draft_create(spl_engine *e, const spl_draft_config *config, spl_d
     const size_t wide = std::max<size_t>(d->feature_width, 256);
     bool ok = draft_alloc(&d->c_features, CR * d->feature_width) && draft_alloc(&d->c_hidden, CR * H) && draft_alloc(&d->c_normed, CR * H) && draft_alloc(&d->c_meta, CR * 3) &&
               draft_alloc(&d->wide_act, RP * wide) && draft_alloc(&d->wide_sums, spl_operand_sums_floats(RP, wide)) &&
-              draft_alloc(&d->b_meta, BR * 7) && draft_alloc(&d->dh, BR * H) && draft_alloc(&d->x, BR * H) && draft_alloc(&d->xc, BR * H) && draft_alloc(&d->t, BR * H) &&
+              draft_alloc(&d->b_meta, BR * 9) && draft_alloc(&d->dh, BR * H) && draft_alloc(&d->x, BR * H) && draft_alloc(&d->xc, BR * H) && draft_alloc(&d->t, BR * H) &&
               draft_alloc(&d->dyn, BR * 4 * d->groups) && draft_alloc(&d->qp, BR * d->attention) && draft_alloc(&d->kp, BR * d->kv) && draft_alloc(&d->vp, BR * d->kv) &&
               draft_alloc(&d->ao, BR * d->attention) && draft_alloc(&d->gate, BR * d->inter) && draft_alloc(&d->up, BR * d->inter) && draft_alloc(&d->dn, BR * H) &&
               draft_alloc(&d->selected, BR * H) && draft_alloc(&d->logits, BR * size_t(d->vocab)) && draft_alloc(&d->top_values, BR * 64) && draft_alloc(&d->top_ids, BR * 64) &&
@@ -525,8 +533,9 @@ spl_status spl_draft_propose(spl_draft *d, const spl_draft_request *requests, in
     if (vocab_limit <= 0 || vocab_limit > d->vocab || c.candidates > vocab_limit) return draft_fail(d, SPL_ERR_INVALID_ARGUMENT, "vocabulary limit");
     if (temperature > 0.0f && (!random_state || !probabilities)) return SPL_ERR_INVALID_ARGUMENT;
     const size_t R = size_t(rows);
-    std::vector<uint32_t> meta(R * 7);
-    uint32_t *m_tokens = meta.data(), *m_slot = m_tokens + R, *m_pos = m_slot + R, *m_lo = m_pos + R, *m_hi = m_lo + R, *m_gather = m_hi + R, *m_offset = m_gather + R;
+    std::vector<uint32_t> meta(R * 9);
+    uint32_t *m_tokens = meta.data(), *m_slot = m_tokens + R, *m_pos = m_slot + R, *m_lo = m_pos + R, *m_hi = m_lo + R, *m_gather = m_hi + R, *m_offset = m_gather + R,
+             *m_requests = m_offset + R;
     std::vector<int> first_picked;
     int row = 0, picked = 0;
     for (int i = 0; i < count; ++i) {
@@ -534,6 +543,7 @@ spl_status spl_draft_propose(spl_draft *d, const spl_draft_request *requests, in
         // Without contiguous context up to the anchor, the block attends only to itself.
         const int first = d->context_end[r.slot] == r.start ? d->context_first[r.slot] : r.start;
         first_picked.push_back(picked);
+        m_requests[2 * i] = uint32_t(row); m_requests[2 * i + 1] = uint32_t(r.block);
         for (int offset = 0; offset < r.block; ++offset) {
             m_tokens[row] = uint32_t(offset == 0 ? r.anchor : c.mask_token);
             m_slot[row] = uint32_t(r.slot); m_pos[row] = uint32_t(r.start + offset); m_lo[row] = uint32_t(first);
@@ -545,7 +555,7 @@ spl_status spl_draft_propose(spl_draft *d, const spl_draft_request *requests, in
     }
     SPL_CUDA(cudaSetDevice(e->device));
     SPL_CUDA(cudaMemcpyAsync(d->b_meta, meta.data(), meta.size() * 4, cudaMemcpyHostToDevice, e->stream));
-    const uint32_t *b_tokens = d->b_meta, *b_slot = b_tokens + R, *b_pos = b_slot + R, *b_lo = b_pos + R, *b_hi = b_lo + R, *b_gather = b_hi + R, *b_offset = b_gather + R;
+    const uint32_t *b_tokens = d->b_meta, *b_slot = b_tokens + R, *b_pos = b_slot + R, *b_lo = b_pos + R, *b_hi = b_lo + R, *b_gather = b_hi + R, *b_offset = b_gather + R, *b_requests = b_offset + R;
     const int H = d->hidden, G = c.heads / c.kv_heads;
     auto conv = [&](const float *in, const spl_tensor *base, float *out, int which, int accumulate) {
         launch_step(spl_draft_conv_kernel, dim3((H + 255) / 256, rows), dim3(256), 0, e->stream, in, (const float *)d->dyn, (const uint16_t *)base->vec, out, H, int(c.group_size),
@@ -563,10 +573,10 @@ spl_status spl_draft_propose(spl_draft *d, const spl_draft_request *requests, in
         if (s == SPL_OK) s = spl_pass_gemm(e, L.v, d->xc, rows, nullptr, d->vp);
         if (s != SPL_OK) break;
         draft_kv_store(d, L, d->kp, d->vp, b_slot, b_pos, rows);
-        if (G == 1) draft_attention_launch<1>(d, L, rows, b_slot, b_pos, b_lo, b_hi);
-        else if (G == 2) draft_attention_launch<2>(d, L, rows, b_slot, b_pos, b_lo, b_hi);
-        else if (G == 4) draft_attention_launch<4>(d, L, rows, b_slot, b_pos, b_lo, b_hi);
-        else draft_attention_launch<8>(d, L, rows, b_slot, b_pos, b_lo, b_hi);
+        if (G == 1) draft_attention_launch<1>(d, L, rows, count, b_requests, b_slot, b_pos, b_lo, b_hi);
+        else if (G == 2) draft_attention_launch<2>(d, L, rows, count, b_requests, b_slot, b_pos, b_lo, b_hi);
+        else if (G == 4) draft_attention_launch<4>(d, L, rows, count, b_requests, b_slot, b_pos, b_lo, b_hi);
+        else draft_attention_launch<8>(d, L, rows, count, b_requests, b_slot, b_pos, b_lo, b_hi);
         s = spl_pass_gemm(e, L.o, d->ao, rows, nullptr, d->t);
         if (s != SPL_OK) break;
         conv(d->t, L.attention_base, d->dh, 1, 1);
