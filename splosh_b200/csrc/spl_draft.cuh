@@ -394,7 +394,9 @@ __device__ __forceinline__ void spl_draft_block_best(float &bv, int &bi, float *
 // The k largest of [0, limit) per logit row, descending, the lower index first among equal values (TopK.select,
 // Sampler.swift:19-52), in two kernels so that a row is many blocks' work: the k best of each of `segments` stretches of
 // the row (k rounds of a block-wide selection, as the one-kernel form does over the whole row), then the k best of those.
+// A stretch is at most 256 x 64 values: a thread keeps its 64 in registers, so the k rounds read the row once.
 // Grid (rows, segments), 256 threads; candidates [rows][segments][k], index -1 where a stretch ran out (NaN and -inf never qualify).
+#define SPL_DRAFT_TOPK_STRETCH (256 * 64)
 __global__ void __launch_bounds__(256)
 spl_draft_topk_segment_kernel(const float *__restrict__ logits, int ld, int limit, int k, int segments, float *cand_v, int32_t *cand_i) {
     __shared__ float best_v[8];
@@ -402,13 +404,18 @@ spl_draft_topk_segment_kernel(const float *__restrict__ logits, int ld, int limi
     spl_grid_begin();
     const int length = (limit + segments - 1) / segments, begin = blockIdx.y * length, end = min(limit, begin + length);
     const float *x = logits + size_t(blockIdx.x) * ld;
+    float mine[64];
+#pragma unroll
+    for (int e = 0; e < 64; ++e) { const int i = begin + int(threadIdx.x) + 256 * e; mine[e] = i < end ? x[i] : -INFINITY; }
     float last_v = INFINITY; int last_i = -1;
     for (int round = 0; round < k; ++round) {
         float bv = -INFINITY; int bi = 0x7fffffff;
-        for (int i = begin + threadIdx.x; i < end; i += 256) {
-            const float v = x[i];
+#pragma unroll
+        for (int e = 0; e < 64; ++e) {
+            const float v = mine[e];
+            const int i = begin + int(threadIdx.x) + 256 * e;          // ascending in e: the first of equal values is the lowest index
             const bool after = v < last_v || (v == last_v && i > last_i);
-            if (after && v > -INFINITY && (v > bv || (v == bv && i < bi))) { bv = v; bi = i; }
+            if (after && v > -INFINITY && v > bv) { bv = v; bi = i; }
         }
         spl_draft_block_best(bv, bi, best_v, best_i);
         const bool none = bi == 0x7fffffff;

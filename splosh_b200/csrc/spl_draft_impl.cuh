@@ -9,7 +9,6 @@
 #include "spl_draft.cuh"
 #include <thread>
 
-#define SPL_DRAFT_TOPK_SEGMENTS 16
 #define SPL_DRAFT_ATTENTION_SPANS 8       // the reference walks eight; a span here is a block of four query heads
 
 // ---- host arithmetic shared with the tests (no device needed) ---------------------------------
@@ -109,7 +108,7 @@ struct spl_draft {
     float *attention_partials = nullptr;                          // [rows][heads][spans][2 + 128]
     float *cand_values = nullptr; int32_t *cand_ids = nullptr;     // the candidates of the row's stretches [picked][segments][candidates]
     float *projection_dev = nullptr, *projected = nullptr;      // the selector's matrix [rank][hidden] and its products with the drafted rows [picked][rank]
-    int last_picked = 0;
+    int last_picked = 0, topk_segments = 16;                     // stretches a row of logits is cut in: each at most SPL_DRAFT_TOPK_STRETCH values
     std::string error;
 };
 
@@ -276,6 +275,7 @@ spl_status spl_draft_create(spl_engine *e, const spl_draft_config *config, spl_d
     d->attention = c.heads * SPL_DRAFT_HEAD_DIM; d->kv = c.kv_heads * SPL_DRAFT_HEAD_DIM;
     d->feature_width = int(e->feature_layers.size()) * e->g.hidden;
     d->context_rows = e->c.max_rows; d->block_rows = e->c.max_slots * c.max_block;
+    d->topk_segments = std::max(16, (e->g.vocab + SPL_DRAFT_TOPK_STRETCH - 1) / SPL_DRAFT_TOPK_STRETCH);
     d->layers.resize(c.layers);
     d->context_first.assign(e->c.max_slots, 0); d->context_end.assign(e->c.max_slots, 0);
     const size_t CR = d->context_rows, BR = d->block_rows, H = d->hidden, RP = size_t((e->c.max_rows + 127) / 128) * 128;
@@ -287,7 +287,7 @@ spl_status spl_draft_create(spl_engine *e, const spl_draft_config *config, spl_d
               draft_alloc(&d->ao, BR * d->attention) && draft_alloc(&d->gate, BR * d->inter) && draft_alloc(&d->up, BR * d->inter) && draft_alloc(&d->dn, BR * H) &&
               draft_alloc(&d->selected, BR * H) && draft_alloc(&d->logits, BR * size_t(d->vocab)) && draft_alloc(&d->top_values, BR * 64) && draft_alloc(&d->top_ids, BR * 64) &&
               draft_alloc(&d->projection_dev, size_t(c.rank) * H) && draft_alloc(&d->projected, BR * c.rank) &&
-              draft_alloc(&d->attention_partials, BR * c.heads * SPL_DRAFT_ATTENTION_SPANS * (SPL_DRAFT_HEAD_DIM + 2)) && draft_alloc(&d->cand_values, BR * SPL_DRAFT_TOPK_SEGMENTS * 64) && draft_alloc(&d->cand_ids, BR * SPL_DRAFT_TOPK_SEGMENTS * 64);
+              draft_alloc(&d->attention_partials, BR * c.heads * SPL_DRAFT_ATTENTION_SPANS * (SPL_DRAFT_HEAD_DIM + 2)) && draft_alloc(&d->cand_values, BR * d->topk_segments * 64) && draft_alloc(&d->cand_ids, BR * d->topk_segments * 64);
     for (DraftLayer &L : d->layers)
         ok = ok && draft_alloc(&L.k_ring, size_t(e->c.max_slots) * c.ring_capacity * d->kv) && draft_alloc(&L.v_ring, size_t(e->c.max_slots) * c.ring_capacity * d->kv) &&
              draft_alloc(&L.c_k, CR * d->kv) && draft_alloc(&L.c_v, CR * d->kv);
@@ -596,9 +596,9 @@ spl_status spl_draft_propose(spl_draft *d, const spl_draft_request *requests, in
     if (s != SPL_OK) return s;
     // The candidates of every drafted position: TopK.select over the first `vocab_limit` logits (Sampler.swift:19-52), on the device.
     launch_step(spl_draft_project_kernel, dim3(picked, (c.rank + 31) / 32), dim3(256), 0, e->stream, (const float *)d->projection_dev, (const float *)d->selected, d->projected, int(c.rank), H);
-    launch_step(spl_draft_topk_segment_kernel, dim3(picked, SPL_DRAFT_TOPK_SEGMENTS), dim3(256), 0, e->stream, (const float *)d->logits, d->vocab, int(vocab_limit), int(c.candidates),
-                SPL_DRAFT_TOPK_SEGMENTS, d->cand_values, d->cand_ids);
-    launch_step(spl_draft_topk_merge_kernel, dim3(picked), dim3(256), 0, e->stream, (const float *)d->cand_values, (const int32_t *)d->cand_ids, SPL_DRAFT_TOPK_SEGMENTS * int(c.candidates),
+    launch_step(spl_draft_topk_segment_kernel, dim3(picked, d->topk_segments), dim3(256), 0, e->stream, (const float *)d->logits, d->vocab, int(vocab_limit), int(c.candidates),
+                d->topk_segments, d->cand_values, d->cand_ids);
+    launch_step(spl_draft_topk_merge_kernel, dim3(picked), dim3(256), 0, e->stream, (const float *)d->cand_values, (const int32_t *)d->cand_ids, d->topk_segments * int(c.candidates),
                 int(c.candidates), d->top_ids, d->top_values);
     s = check_launch(e, "draft block");
     if (s == SPL_OK) s = spl_pass_wait(e);
