@@ -198,7 +198,7 @@ def test_a_window_of_several_chunks_and_spans():
     want = oracle.propose(requests)
     logits = draft.debug_read(0, (15, g.vocab))
     selected = draft.debug_read(1, (15, g.hidden))
-    observed(f"draft block pass over a 300-position window (3 chunks, 8 spans, wrapped ring): max |logit - restatement| {np.abs(logits - want['logits']).max():.3e} "
+    observed(f"draft block pass over a 300-position window (5 turns of 64 positions over 8 spans, wrapped ring): max |logit - restatement| {np.abs(logits - want['logits']).max():.3e} "
              f"(largest {np.abs(want['logits']).max():.2f}); hidden rows {np.abs(selected - want['selected']).max():.3e} of {np.abs(want['selected']).max():.2f}")
     assert np.abs(selected - want["selected"]).max() <= 2e-2 * np.abs(want["selected"]).max()
     assert np.abs(logits - want["logits"]).max() <= 2e-2 * np.abs(want["logits"]).max()
