@@ -175,15 +175,17 @@ def test_context_bookkeeping_and_refusals(setup):
         S.DraftModel(engine, S.DraftConfig(layers=1, heads=3, kv_heads=2))
 
 
-def test_a_window_of_several_chunks_and_spans():
-    """A context longer than one 128-position chunk: the attention's spans run side by side and are merged; the window cuts
-    the oldest positions and the ring has wrapped."""
+@pytest.mark.parametrize("heads, kv_heads", [(4, 2), (8, 1)])
+def test_a_window_of_several_chunks_and_spans(heads, kv_heads):
+    """A context longer than one chunk: the attention's spans run side by side and are merged; the window cuts the oldest
+    positions and the ring has wrapped. Two query heads a kv head take the tensor-core form (a request's queries fit its 64);
+    eight take the walk on the CUDA cores."""
     g = S.tiny_geometry()
     model = O.Model(O.tiny_geometry())
     engine = S.Engine(g, S.EngineConfig(max_slots=1, max_rows=64, kv_pages=4, max_context=1024))
     engine.load_model(model)
     engine.enable_features(TAPS)
-    config = S.DraftConfig(layers=1, heads=4, kv_heads=2, group_size=16, rank=32, window=300, ring_capacity=320, block_size=8, max_block=16,
+    config = S.DraftConfig(layers=1, heads=heads, kv_heads=kv_heads, group_size=16, rank=32, window=300, ring_capacity=320, block_size=8, max_block=16,
                            candidates=8, mask_token=31999)
     tensors = checkpoint(g, config, seed=23)
     draft = S.DraftModel(engine, config)
@@ -198,7 +200,7 @@ def test_a_window_of_several_chunks_and_spans():
     want = oracle.propose(requests)
     logits = draft.debug_read(0, (15, g.vocab))
     selected = draft.debug_read(1, (15, g.hidden))
-    observed(f"draft block pass over a 300-position window (5 turns of 64 positions over 8 spans, wrapped ring): max |logit - restatement| {np.abs(logits - want['logits']).max():.3e} "
+    observed(f"draft block pass over a 300-position window ({heads} heads on {kv_heads} kv heads, 8 spans, wrapped ring): max |logit - restatement| {np.abs(logits - want['logits']).max():.3e} "
              f"(largest {np.abs(want['logits']).max():.2f}); hidden rows {np.abs(selected - want['selected']).max():.3e} of {np.abs(want['selected']).max():.2f}")
     assert np.abs(selected - want["selected"]).max() <= 2e-2 * np.abs(want["selected"]).max()
     assert np.abs(logits - want["logits"]).max() <= 2e-2 * np.abs(want["logits"]).max()
